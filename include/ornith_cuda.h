@@ -1,0 +1,266 @@
+/* C ABI of libornith_cuda.so: the sm_100a replacement for ornith-rs's device
+ * layer (src/metal/mod.rs, `Context` + `Dispatch`) and everything that layer
+ * runs on the decode hot path.
+ *
+ * The reference binds kernels one dispatch at a time
+ * (`ctx.kernel(name).arr(..).out(..).bytes(..).groups(..)`, e.g.
+ * src/ops/kquant.rs:578-593).  This ABI is op-level instead: one entry point
+ * per function of src/ops/ and src/model/ that the MTP depth-1 decode step
+ * calls, so the Rust crate keeps its public API (generate_step,
+ * generate_step_mtp, FrSpec, WeightStore) and forwards here.
+ *
+ * Conventions
+ *   - every function returns an int32 status: 0 ok, negative = error
+ *     (ORN_ERR_*); nothing aborts.  orn_last_error() gives the message.
+ *   - handles are opaque and owned by the library; one orn_ctx per (thread,
+ *     device); not thread-safe; all work is ordered on the context's stream.
+ *   - "dev" pointers are device memory from orn_alloc (or any CUDA
+ *     allocation on the context's device); "host" pointers are host memory.
+ *   - activations are bfloat16 (raw uint16), accumulators float32.
+ *   - a compute entry point never touches host memory and never falls back to
+ *     the CPU.
+ */
+#ifndef ORNITH_CUDA_H
+#define ORNITH_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ORN_OK 0
+#define ORN_ERR_ARG (-1)
+#define ORN_ERR_ALLOC (-2)
+#define ORN_ERR_CUDA (-3)
+#define ORN_ERR_TIMEOUT (-4)
+#define ORN_ERR_IO (-5)
+#define ORN_ERR_STATE (-6)
+
+/* weight formats (src/ops/linear.rs:23-40 `Linear = Mlx | K`, src/ops/kquant.rs:298-347) */
+#define ORN_Q4K 0  /* ggml Q4_K, three tensors: qs / scales / dm       */
+#define ORN_Q6K 1  /* ggml Q6_K, three tensors: ql|qh / scales / d     */
+#define ORN_A8 2   /* mlx affine, 8 bits, group 64: codes/scales/biases */
+#define ORN_BF16 3 /* dense bfloat16                                    */
+
+typedef struct orn_ctx orn_ctx;
+typedef struct orn_linear orn_linear;
+typedef struct orn_model orn_model;
+typedef struct orn_cache orn_cache;
+
+/* model dimensions (src/model/config.rs:9-158) */
+typedef struct {
+  int32_t hidden, n_layers, full_attn_interval;
+  int32_t n_heads, n_kv_heads, head_dim, rope_dims;
+  float rope_theta;
+  int32_t gdn_k_heads, gdn_v_heads, gdn_head_dim, gdn_conv_kernel;
+  int32_t n_experts, top_k, expert_inter, shared_inter, norm_topk_prob;
+  int32_t vocab;
+  float rms_eps;
+  int32_t max_ctx;
+} orn_config;
+
+/* ---- context and memory: replaces metal::Context (src/metal/mod.rs:433-519,612-646) */
+int32_t orn_ctx_create(int32_t device, orn_ctx** out);
+int32_t orn_ctx_destroy(orn_ctx* ctx);
+int32_t orn_sync(orn_ctx* ctx);                        /* Context::sync */
+const char* orn_last_error(orn_ctx* ctx);
+int32_t orn_alloc(orn_ctx* ctx, size_t nbytes, void** dev_out);   /* Context::alloc */
+int32_t orn_free(orn_ctx* ctx, void* dev);
+int32_t orn_memset(orn_ctx* ctx, void* dev, int32_t byte, size_t nbytes);
+int32_t orn_upload(orn_ctx* ctx, void* dev, const void* host, size_t nbytes);   /* Array::from_slice */
+int32_t orn_download(orn_ctx* ctx, void* host, const void* dev, size_t nbytes); /* Array::to_vec (syncs) */
+
+/* ---- weights: replaces KMatrix / QuantMatrix / dense Array (src/ops/kquant.rs:349-411,
+ * src/weights.rs:132-279).  Tensors are in the artifact's layout:
+ *   Q4_K: w = qs bytes [E,O,K/2], s = scales u8 [E,O,K/256,12], b = dm f16 [E,O,K/256,2]
+ *   Q6_K: w = ql|qh bytes [E,O,K/256*192], s = i8 [E,O,K/256,16], b = d f16 [E,O,K/256]
+ *   A8  : w = codes u8 [E,O,K], s = scales bf16 [E,O,K/64], b = biases bf16 [E,O,K/64]
+ *   BF16: w = bf16 [E,O,K]
+ * The library copies them into its own HBM layout (16-byte-aligned streams).
+ * Shape rules follow KMatrix::new: K % 256 == 0 for k-quants, K % 64 == 0 for
+ * A8, K % 8 == 0 for BF16; violations return ORN_ERR_ARG. */
+int32_t orn_linear_create(orn_ctx* ctx, int32_t kind, int32_t E, int32_t O, int32_t K,
+                          const void* host_w, const void* host_s, const void* host_b,
+                          orn_linear** out);
+/* seeded synthetic weights ~ N(0, std) quantised on the GPU (no reference
+ * counterpart: the reference's artifacts come from tools/forge_q4k.py) */
+int32_t orn_linear_create_random(orn_ctx* ctx, int32_t kind, int32_t E, int32_t O, int32_t K,
+                                 uint64_t seed, float std, orn_linear** out);
+/* copy a matrix back to host in the artifact layout (for checkers) */
+int32_t orn_linear_export(orn_ctx* ctx, const orn_linear* lin, void* host_w, void* host_s,
+                          void* host_b);
+int32_t orn_linear_sizes(const orn_linear* lin, size_t* w_bytes, size_t* s_bytes, size_t* b_bytes);
+int32_t orn_linear_destroy(orn_ctx* ctx, orn_linear* lin);
+/* FrSpec::prune (src/frspec.rs:115-135): row gather of every head tensor */
+int32_t orn_linear_gather_rows(orn_ctx* ctx, const orn_linear* lin, const uint32_t* host_ids,
+                               int32_t n, orn_linear** out);
+
+/* ---- k-quant ops (src/ops/kquant.rs) */
+/* kquant::dequantize -> q4k_dequantize / q6k_dequantize (kernels/q4k.metal:64-96,
+ * kernels/q6k.metal:47-77): expert e of lin to float [O,K] */
+int32_t orn_kq_dequantize(orn_ctx* ctx, const orn_linear* lin, int32_t e, float* dev_out);
+/* Linear::matmul at M <= 4 rows -> kquant::qmv / quantized_matmul / matmul
+ * (src/ops/linear.rs:23-80, kquant.rs:539-595, quantized.rs:249-333,
+ * matmul.rs:334-437): y[M,O] = x[M,K] W^T.  Every row is computed with the
+ * one-row arithmetic (src/ops/invariant.rs:78-116).  out_f32 != 0 stores
+ * float, else bfloat16.  M > 4 is processed in groups of 4. */
+int32_t orn_gemv(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x, int32_t M,
+                 void* dev_y, int32_t out_f32);
+/* Linear::gather_matmul -> kquant::gather_qmv / gather_mv (kquant.rs:741-770,
+ * matmul.rs:649-711): row r = W[rhs[r]] . x[lhs[r]], bf16 out [rows,O] */
+int32_t orn_gather_gemv(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x,
+                        const uint32_t* dev_lhs, const uint32_t* dev_rhs, int32_t rows,
+                        uint16_t* dev_y);
+/* ops::embedding (src/ops/embedding.rs:18-47) for the affine-8 table */
+int32_t orn_embedding(orn_ctx* ctx, const orn_linear* table, const uint32_t* dev_ids, int32_t T,
+                      uint16_t* dev_out);
+
+/* ---- norms and elementwise (src/ops/norm.rs:19-220, elementwise.rs) */
+int32_t orn_rms_norm(orn_ctx* ctx, const uint16_t* dev_x, const uint16_t* dev_w /*nullable*/,
+                     int32_t rows, int32_t n, float eps, uint16_t* dev_out);
+int32_t orn_add_rms_norm(orn_ctx* ctx, const uint16_t* dev_a, const uint16_t* dev_b,
+                         const uint16_t* dev_w, int32_t rows, int32_t n, float eps,
+                         uint16_t* dev_h, uint16_t* dev_out);
+int32_t orn_rms_norm_gated(orn_ctx* ctx, const uint16_t* dev_x, const uint16_t* dev_w,
+                           const uint16_t* dev_z, int32_t rows, int32_t n, float eps,
+                           uint16_t* dev_out);
+int32_t orn_sigmoid_gate(orn_ctx* ctx, const uint16_t* dev_gate, const uint16_t* dev_x, int32_t n,
+                         int32_t inner, uint16_t* dev_out);
+int32_t orn_swiglu(orn_ctx* ctx, const uint16_t* dev_g, const uint16_t* dev_u, int32_t n,
+                   uint16_t* dev_out);
+
+/* ---- MoE (src/ops/moe.rs, kernels/moe.metal) */
+int32_t orn_softmax_precise(orn_ctx* ctx, const uint16_t* dev_x, int32_t rows, int32_t n,
+                            uint16_t* dev_out);                       /* softmax.rs:18-51 */
+int32_t orn_router_topk(orn_ctx* ctx, const uint16_t* dev_gates, int32_t rows, int32_t n,
+                        int32_t k, uint32_t* dev_inds, uint16_t* dev_scores); /* moe.rs:113-134 */
+int32_t orn_moe_combine(orn_ctx* ctx, const uint16_t* dev_scores, const uint16_t* dev_y,
+                        const uint16_t* dev_gate, const uint16_t* dev_shared, int32_t T, int32_t k,
+                        int32_t dim, int32_t normalize, uint16_t* dev_out);  /* moe.rs:548-596 */
+/* sparse_moe_block (moe.rs:662-741) / sparse_moe_block_dense (:902-937) */
+int32_t orn_moe_block(orn_ctx* ctx, const orn_linear* gate, const orn_linear* sw_gate,
+                      const orn_linear* sw_up, const orn_linear* sw_down,
+                      const orn_linear* sh_gate, const orn_linear* sh_up,
+                      const orn_linear* sh_down, const orn_linear* sh_egate,
+                      const uint16_t* dev_x, int32_t T, int32_t top_k, int32_t norm_topk,
+                      uint16_t* dev_out, uint32_t* dev_inds_out /*nullable*/);
+
+/* ---- gated delta net (src/ops/gdn.rs:191-413) */
+int32_t orn_gdn_front(orn_ctx* ctx, const uint16_t* dev_conv_state, const uint16_t* dev_qkv,
+                      const uint16_t* dev_conv_w, const uint16_t* dev_a, const uint16_t* dev_b,
+                      const uint16_t* dev_a_log, const uint16_t* dev_dt_bias, int32_t T,
+                      int32_t Hk, int32_t Hv, int32_t Dh, int32_t Kc, float eps,
+                      uint16_t* dev_conv_next, uint16_t* dev_q, uint16_t* dev_k, uint16_t* dev_v,
+                      uint16_t* dev_beta, float* dev_g);
+/* gated_delta_kernel(_into): state [Hv,128,128] f32 updated in place; if
+ * dev_snaps != NULL the state after token t is also written to snaps[t]. */
+int32_t orn_gated_delta(orn_ctx* ctx, const uint16_t* dev_q, const uint16_t* dev_k,
+                        const uint16_t* dev_v, const float* dev_g, const uint16_t* dev_beta,
+                        float* dev_state, int32_t T, int32_t Hk, int32_t Hv, uint16_t* dev_y,
+                        float* dev_snaps /*nullable*/);
+
+/* ---- attention (src/ops/rope.rs:23-89, src/ops/sdpa.rs:122-229) */
+int32_t orn_rope(orn_ctx* ctx, uint16_t* dev_x, int32_t T, int32_t H, int32_t hd, int32_t dims,
+                 float theta, int32_t offset);
+int32_t orn_sdpa_decode(orn_ctx* ctx, const uint16_t* dev_q, const uint16_t* dev_kc,
+                        const uint16_t* dev_vc, int32_t T, int32_t Hq, int32_t Hkv, int32_t hd,
+                        int32_t cap, int32_t offset, float scale, uint16_t* dev_out);
+
+/* ---- greedy sampling (src/ops/sample.rs:134-147,186-191) */
+int32_t orn_greedy(orn_ctx* ctx, const uint16_t* dev_logits, int32_t T, int32_t V,
+                   int32_t normalize, uint32_t* dev_tokens);
+
+/* ---- model (src/model/qwen3_5.rs, mtp.rs, cache.rs; src/weights.rs) */
+int32_t orn_model_create(orn_ctx* ctx, const orn_config* cfg, orn_model** out);
+int32_t orn_model_destroy(orn_model* m);
+/* attach a weight under its artifact name (qwen3_5.rs:102-158, mtp.rs:96-143);
+ * the model takes ownership of lin */
+int32_t orn_model_set_linear(orn_model* m, const char* name, orn_linear* lin);
+/* plain bf16 tensor (norm weights, conv1d, A_log, dt_bias), copied from host */
+int32_t orn_model_set_tensor(orn_model* m, const char* name, const uint16_t* host, size_t n);
+/* random-init every weight of the config-4 mix (expert gate/up Q4_K, expert
+ * down Q6_K, everything else affine-8, MTP head bf16) from one seed */
+int32_t orn_model_init_random(orn_model* m, uint64_t seed);
+/* TextModel::load + MtpHead::load (src/weights.rs:41-279): safetensors shards
+ * + config.json in `dir`; mtp sidecar if present */
+int32_t orn_model_load(orn_ctx* ctx, const char* dir, int32_t max_ctx, orn_model** out);
+/* look a weight up again (checkers export it for the CPU oracle) */
+int32_t orn_model_get_linear(orn_model* m, const char* name, const orn_linear** out);
+int32_t orn_model_get_tensor(orn_model* m, const char* name, const uint16_t** dev_out, size_t* n);
+int32_t orn_model_config(const orn_model* m, orn_config* out);
+size_t orn_model_weight_bytes(const orn_model* m);
+/* FrSpec::load (src/frspec.rs:67-113): ids file = u32 n + n x u32 LE */
+int32_t orn_frspec_load(orn_model* m, const char* ids_path);
+int32_t orn_frspec_set(orn_model* m, const uint32_t* host_ids, int32_t n);
+
+int32_t orn_cache_create(orn_model* m, orn_cache** out);     /* make_cache + make_mtp_cache */
+int32_t orn_cache_destroy(orn_cache* c);
+int32_t orn_cache_reset(orn_cache* c);
+int32_t orn_cache_offset(const orn_cache* c);
+/* TextModel::forward_hidden: T <= 4 rows per call; dev_normed [T,H] */
+int32_t orn_forward(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_t T,
+                    uint16_t* dev_normed, uint16_t* dev_pre_norm /*nullable*/);
+/* forward_capture + TrunkCapture::rewind(keep) (qwen3_5.rs:190-229,324-348) */
+int32_t orn_forward_capture(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_t T,
+                            uint16_t* dev_normed);
+int32_t orn_cache_rewind(orn_cache* c, int32_t keep);
+/* lm_head + greedy_token for T hidden rows (generate.rs:139-150) */
+int32_t orn_head_greedy(orn_model* m, const uint16_t* dev_hidden, int32_t T,
+                        uint32_t* host_tokens, uint16_t* dev_logits_out /*nullable*/);
+
+typedef int32_t (*orn_token_cb)(uint32_t token, void* user); /* return 0 to stop */
+
+/* generate::generate_step with the Greedy sampler (src/generate.rs:162-206).
+ * Caches end holding the prompt plus every token shown to on_token. */
+int32_t orn_generate_step(orn_model* m, orn_cache* c, const uint32_t* host_prompt,
+                          int32_t n_prompt, int32_t max_tokens, int32_t prefill_step,
+                          orn_token_cb on_token, void* user);
+
+typedef struct {
+  int32_t cycles, drafted, accepted;
+  int32_t reached_by_depth[8], accepted_by_depth[8];
+} orn_mtp_stats; /* MtpStats, src/mtp_generate.rs:66-84 */
+
+/* harness device for controlled acceptance (no reference counterpart): with
+ * probability p the draft for generated position i is replaced by stream[i] */
+typedef struct {
+  const uint32_t* stream;
+  int32_t len;
+  float p;
+  uint64_t seed;
+} orn_force_draft;
+
+#define ORN_POLICY_CYCLE 0
+#define ORN_POLICY_COMMITTED 1
+/* mtp_generate::generate_step_mtp with the Greedy sampler
+ * (src/mtp_generate.rs:150-317); use_frspec drafts through the pruned head */
+int32_t orn_generate_step_mtp(orn_model* m, orn_cache* c, const uint32_t* host_prompt,
+                              int32_t n_prompt, int32_t depth, int32_t max_tokens,
+                              int32_t prefill_step, int32_t policy, int32_t use_frspec,
+                              const orn_force_draft* force /*nullable*/, orn_token_cb on_token,
+                              void* user, orn_mtp_stats* stats);
+
+/* per-phase device time of the last generate call, milliseconds (the
+ * reference's ORNITH_PROF report, src/main.rs:256-422, reduced to phases) */
+typedef struct {
+  float prefill_ms, draft_ms, verify_ms, head_ms, total_ms;
+  int64_t kernel_launches;
+  int64_t verify_steps, draft_steps, ar_steps;
+} orn_prof;
+int32_t orn_get_prof(orn_model* m, orn_prof* out);
+
+/* host copies of the shared elementary functions, so that a checker can
+ * compare them with its own restatement without a GPU */
+float orn_host_expf(float x);
+float orn_host_logf(float x);
+float orn_host_log1pf(float x);
+void orn_host_sincosf(float a, float* s, float* c);
+float orn_host_sigmoid_bf(float x);
+float orn_host_softplus_bf(float x);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

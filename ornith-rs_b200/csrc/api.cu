@@ -1,0 +1,354 @@
+// C ABI: context, memory, weight handles and the op-level entry points.
+// The model-level entry points live in model.cu.
+#include <cuda_fp16.h>
+
+#include <cstdio>
+#include <cstring>
+
+#include "orn_internal.h"
+
+#define CK(call)                     \
+  do {                               \
+    int rc__ = (call);               \
+    if (rc__ != ORN_OK) return rc__; \
+  } while (0)
+
+extern "C" {
+
+int32_t orn_ctx_create(int32_t device, orn_ctx** out) {
+  if (!out) return ORN_ERR_ARG;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) return ORN_ERR_CUDA;
+  if (device < 0 || device >= count) return ORN_ERR_ARG;
+  if (cudaSetDevice(device) != cudaSuccess) return ORN_ERR_CUDA;
+  orn_ctx* c = new orn_ctx();
+  c->device = device;
+  if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
+    delete c;
+    return ORN_ERR_CUDA;
+  }
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) c->sm_count = prop.multiProcessorCount;
+  *out = c;
+  return ORN_OK;
+}
+
+int32_t orn_ctx_destroy(orn_ctx* ctx) {
+  if (!ctx) return ORN_ERR_ARG;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return ORN_OK;
+}
+
+int32_t orn_sync(orn_ctx* ctx) {
+  if (!ctx) return ORN_ERR_ARG;
+  ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return ORN_OK;
+}
+
+const char* orn_last_error(orn_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+
+int32_t orn_alloc(orn_ctx* ctx, size_t nbytes, void** dev_out) {
+  if (!ctx || !dev_out) return ORN_ERR_ARG;
+  *dev_out = nullptr;
+  cudaSetDevice(ctx->device);
+  cudaError_t e = cudaMalloc(dev_out, nbytes ? nbytes : 16);
+  if (e != cudaSuccess) {
+    ctx->err = std::string("cudaMalloc: ") + cudaGetErrorString(e);
+    cudaGetLastError();
+    return ORN_ERR_ALLOC;
+  }
+  return ORN_OK;
+}
+
+int32_t orn_free(orn_ctx* ctx, void* dev) {
+  if (!ctx) return ORN_ERR_ARG;
+  if (!dev) return ORN_OK;
+  ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ORN_CHECK_CUDA(ctx, cudaFree(dev));
+  return ORN_OK;
+}
+
+int32_t orn_memset(orn_ctx* ctx, void* dev, int32_t byte, size_t nbytes) {
+  if (!ctx || !dev) return ORN_ERR_ARG;
+  ORN_CHECK_CUDA(ctx, cudaMemsetAsync(dev, byte, nbytes, ctx->stream));
+  return ORN_OK;
+}
+
+int32_t orn_upload(orn_ctx* ctx, void* dev, const void* host, size_t nbytes) {
+  if (!ctx || !dev || !host) return ORN_ERR_ARG;
+  ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(dev, host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+  // the host buffer may be pageable and reused by the caller right away
+  ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return ORN_OK;
+}
+
+int32_t orn_download(orn_ctx* ctx, void* host, const void* dev, size_t nbytes) {
+  if (!ctx || !dev || !host) return ORN_ERR_ARG;
+  ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(host, dev, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
+  ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return ORN_OK;
+}
+
+// ---------------------------------------------------------------- weights
+static int check_linear_shape(orn_ctx* ctx, int kind, int E, int O, int K) {
+  if (E < 1 || O < 1 || K < 1) ORN_FAIL(ctx, ORN_ERR_ARG, "linear: non-positive dimension");
+  if ((kind == ORN_Q4K || kind == ORN_Q6K) && K % 256 != 0)
+    ORN_FAIL(ctx, ORN_ERR_ARG, "k-quant matrix: K must be a multiple of 256");
+  if (kind == ORN_A8 && K % 64 != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "affine-8 matrix: K must be a multiple of 64");
+  if (kind == ORN_BF16 && K % 8 != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "bf16 matrix: K must be a multiple of 8");
+  if (kind < ORN_Q4K || kind > ORN_BF16) ORN_FAIL(ctx, ORN_ERR_ARG, "linear: unknown kind");
+  return ORN_OK;
+}
+
+static int linear_alloc(orn_ctx* ctx, int kind, int E, int O, int K, orn_linear** out) {
+  CK(check_linear_shape(ctx, kind, E, O, K));
+  orn_linear* L = new orn_linear();
+  L->kind = kind; L->E = E; L->O = O; L->K = K;
+  linear_alloc_sizes(kind, E, O, K, &L->w_bytes, &L->s_bytes, &L->b_bytes);
+  int rc = orn_alloc(ctx, L->w_bytes, (void**)&L->w);
+  if (rc == ORN_OK && L->s_bytes) rc = orn_alloc(ctx, L->s_bytes, (void**)&L->s);
+  if (rc == ORN_OK && L->b_bytes) rc = orn_alloc(ctx, L->b_bytes, (void**)&L->b);
+  if (rc != ORN_OK) {
+    cudaFree(L->w); cudaFree(L->s); cudaFree(L->b);
+    delete L;
+    return rc;
+  }
+  *out = L;
+  return ORN_OK;
+}
+
+int32_t orn_linear_create(orn_ctx* ctx, int32_t kind, int32_t E, int32_t O, int32_t K,
+                          const void* host_w, const void* host_s, const void* host_b,
+                          orn_linear** out) {
+  if (!ctx || !out || !host_w) return ORN_ERR_ARG;
+  *out = nullptr;
+  CK(check_linear_shape(ctx, kind, E, O, K));
+  if (kind != ORN_BF16 && (!host_s || !host_b)) ORN_FAIL(ctx, ORN_ERR_ARG, "quantised matrix needs three tensors");
+  size_t aw, as, ab;
+  linear_artifact_sizes(kind, E, O, K, &aw, &as, &ab);
+  orn_linear* L = nullptr;
+  CK(linear_alloc(ctx, kind, E, O, K, &L));
+  // stage the artifact tensors on the device, then repack there
+  uint8_t *dw = nullptr, *ds = nullptr, *db = nullptr;
+  int rc = ORN_OK;
+  if (kind == ORN_BF16 || kind == ORN_Q6K) {
+    // layouts coincide: upload straight into place
+    rc = orn_upload(ctx, L->w, host_w, aw);
+    if (rc == ORN_OK && as) rc = orn_upload(ctx, L->s, host_s, as);
+    if (rc == ORN_OK && ab) rc = orn_upload(ctx, L->b, host_b, ab);
+  } else {
+    rc = orn_upload(ctx, L->w, host_w, aw);
+    if (rc == ORN_OK) rc = orn_alloc(ctx, as, (void**)&ds);
+    if (rc == ORN_OK) rc = orn_alloc(ctx, ab, (void**)&db);
+    if (rc == ORN_OK) rc = orn_upload(ctx, ds, host_s, as);
+    if (rc == ORN_OK) rc = orn_upload(ctx, db, host_b, ab);
+    if (rc == ORN_OK) rc = k_linear_pack(ctx, ctx->stream, L, L->w, ds, db);
+    if (rc == ORN_OK) rc = orn_sync(ctx);
+    cudaFree(dw); cudaFree(ds); cudaFree(db);
+  }
+  if (rc != ORN_OK) {
+    orn_linear_destroy(ctx, L);
+    return rc;
+  }
+  *out = L;
+  return ORN_OK;
+}
+
+int32_t orn_linear_create_random(orn_ctx* ctx, int32_t kind, int32_t E, int32_t O, int32_t K,
+                                 uint64_t seed, float std, orn_linear** out) {
+  if (!ctx || !out) return ORN_ERR_ARG;
+  *out = nullptr;
+  orn_linear* L = nullptr;
+  CK(linear_alloc(ctx, kind, E, O, K, &L));
+  int rc = k_linear_random(ctx, ctx->stream, L, seed, std);
+  if (rc != ORN_OK) {
+    orn_linear_destroy(ctx, L);
+    return rc;
+  }
+  *out = L;
+  return ORN_OK;
+}
+
+int32_t orn_linear_sizes(const orn_linear* lin, size_t* w, size_t* s, size_t* b) {
+  if (!lin || !w || !s || !b) return ORN_ERR_ARG;
+  linear_artifact_sizes(lin->kind, lin->E, lin->O, lin->K, w, s, b);
+  return ORN_OK;
+}
+
+int32_t orn_linear_export(orn_ctx* ctx, const orn_linear* lin, void* host_w, void* host_s,
+                          void* host_b) {
+  if (!ctx || !lin || !host_w) return ORN_ERR_ARG;
+  size_t aw, as, ab;
+  linear_artifact_sizes(lin->kind, lin->E, lin->O, lin->K, &aw, &as, &ab);
+  if (lin->kind == ORN_BF16 || lin->kind == ORN_Q6K) {
+    CK(orn_download(ctx, host_w, lin->w, aw));
+    if (as) CK(orn_download(ctx, host_s, lin->s, as));
+    if (ab) CK(orn_download(ctx, host_b, lin->b, ab));
+    return ORN_OK;
+  }
+  if (!host_s || !host_b) return ORN_ERR_ARG;
+  uint8_t *ds = nullptr, *db = nullptr;
+  int rc = orn_alloc(ctx, as, (void**)&ds);
+  if (rc == ORN_OK) rc = orn_alloc(ctx, ab, (void**)&db);
+  if (rc == ORN_OK) rc = orn_download(ctx, host_w, lin->w, aw);
+  if (rc == ORN_OK) {
+    // unpack the header stream only; the code stream is already in place
+    rc = k_linear_unpack(ctx, ctx->stream, lin, nullptr, ds, db);
+    if (rc == ORN_OK) rc = orn_download(ctx, host_s, ds, as);
+    if (rc == ORN_OK) rc = orn_download(ctx, host_b, db, ab);
+  }
+  cudaFree(ds); cudaFree(db);
+  return rc;
+}
+
+int32_t orn_linear_destroy(orn_ctx* ctx, orn_linear* lin) {
+  if (!lin) return ORN_OK;
+  if (ctx) cudaStreamSynchronize(ctx->stream);
+  if (lin->owns) { cudaFree(lin->w); cudaFree(lin->s); cudaFree(lin->b); }
+  delete lin;
+  return ORN_OK;
+}
+
+int32_t orn_linear_gather_rows(orn_ctx* ctx, const orn_linear* lin, const uint32_t* host_ids,
+                               int32_t n, orn_linear** out) {
+  if (!ctx || !lin || !host_ids || !out || n < 1) return ORN_ERR_ARG;
+  if (lin->E != 1) ORN_FAIL(ctx, ORN_ERR_ARG, "gather_rows: dense matrices only");
+  for (int i = 0; i < n; ++i)
+    if (host_ids[i] >= (uint32_t)lin->O) ORN_FAIL(ctx, ORN_ERR_ARG, "gather_rows: id out of range");
+  orn_linear* L = nullptr;
+  CK(linear_alloc(ctx, lin->kind, 1, n, lin->K, &L));
+  uint32_t* dids = nullptr;
+  int rc = orn_alloc(ctx, sizeof(uint32_t) * (size_t)n, (void**)&dids);
+  if (rc == ORN_OK) rc = orn_upload(ctx, dids, host_ids, sizeof(uint32_t) * (size_t)n);
+  if (rc == ORN_OK) rc = k_linear_gather_rows(ctx, ctx->stream, lin, dids, n, L);
+  if (rc == ORN_OK) rc = orn_sync(ctx);
+  cudaFree(dids);
+  if (rc != ORN_OK) { orn_linear_destroy(ctx, L); return rc; }
+  *out = L;
+  return ORN_OK;
+}
+
+// ---------------------------------------------------------------- ops
+int32_t orn_kq_dequantize(orn_ctx* ctx, const orn_linear* lin, int32_t e, float* dev_out) {
+  if (!ctx || !lin || !dev_out) return ORN_ERR_ARG;
+  if (e < 0 || e >= lin->E) ORN_FAIL(ctx, ORN_ERR_ARG, "kq_dequantize: expert out of range");
+  return k_kq_dequantize(ctx, ctx->stream, lin, e, dev_out);
+}
+
+int32_t orn_gemv(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x, int32_t M, void* dev_y,
+                 int32_t out_f32) {
+  if (!ctx || !lin || !dev_x || !dev_y || M < 1) return ORN_ERR_ARG;
+  if (lin->E != 1) ORN_FAIL(ctx, ORN_ERR_ARG, "gemv: expert-stacked matrix needs gather_gemv");
+  return k_gemv(ctx, ctx->stream, lin, dev_x, M, dev_y, out_f32);
+}
+
+int32_t orn_gather_gemv(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x,
+                        const uint32_t* dev_lhs, const uint32_t* dev_rhs, int32_t rows,
+                        uint16_t* dev_y) {
+  if (!ctx || !lin || !dev_x || !dev_lhs || !dev_rhs || !dev_y || rows < 0) return ORN_ERR_ARG;
+  if (rows > 65535) ORN_FAIL(ctx, ORN_ERR_ARG, "gather_gemv: more than 65535 routed rows");
+  return k_gather_gemv(ctx, ctx->stream, lin, dev_x, dev_lhs, dev_rhs, rows, dev_y);
+}
+
+int32_t orn_embedding(orn_ctx* ctx, const orn_linear* table, const uint32_t* dev_ids, int32_t T,
+                      uint16_t* dev_out) {
+  if (!ctx || !table || !dev_ids || !dev_out || T < 1) return ORN_ERR_ARG;
+  return k_embedding(ctx, ctx->stream, table, dev_ids, T, dev_out);
+}
+
+int32_t orn_rms_norm(orn_ctx* ctx, const uint16_t* x, const uint16_t* w, int32_t rows, int32_t n,
+                     float eps, uint16_t* out) {
+  if (!ctx || !x || !out || rows < 1 || n < 1) return ORN_ERR_ARG;
+  return k_rms_norm(ctx, ctx->stream, x, w, rows, n, eps, out);
+}
+int32_t orn_add_rms_norm(orn_ctx* ctx, const uint16_t* a, const uint16_t* b, const uint16_t* w,
+                         int32_t rows, int32_t n, float eps, uint16_t* h, uint16_t* out) {
+  if (!ctx || !a || !b || !h || !out || rows < 1 || n < 1) return ORN_ERR_ARG;
+  return k_add_rms_norm(ctx, ctx->stream, a, b, w, rows, n, eps, h, out);
+}
+int32_t orn_rms_norm_gated(orn_ctx* ctx, const uint16_t* x, const uint16_t* w, const uint16_t* z,
+                           int32_t rows, int32_t n, float eps, uint16_t* out) {
+  if (!ctx || !x || !w || !z || !out || rows < 1 || n < 1) return ORN_ERR_ARG;
+  return k_rms_norm_gated(ctx, ctx->stream, x, w, z, rows, n, eps, out);
+}
+int32_t orn_sigmoid_gate(orn_ctx* ctx, const uint16_t* gate, const uint16_t* x, int32_t n,
+                         int32_t inner, uint16_t* out) {
+  if (!ctx || !gate || !x || !out || n < 1 || inner < 1) return ORN_ERR_ARG;
+  return k_sigmoid_gate(ctx, ctx->stream, gate, x, n, inner, out);
+}
+int32_t orn_swiglu(orn_ctx* ctx, const uint16_t* g, const uint16_t* u, int32_t n, uint16_t* out) {
+  if (!ctx || !g || !u || !out || n < 1) return ORN_ERR_ARG;
+  return k_swiglu(ctx, ctx->stream, g, u, n, out);
+}
+int32_t orn_softmax_precise(orn_ctx* ctx, const uint16_t* x, int32_t rows, int32_t n, uint16_t* out) {
+  if (!ctx || !x || !out || rows < 1 || n < 1) return ORN_ERR_ARG;
+  return k_softmax_precise(ctx, ctx->stream, x, rows, n, out);
+}
+int32_t orn_router_topk(orn_ctx* ctx, const uint16_t* gates, int32_t rows, int32_t n, int32_t k,
+                        uint32_t* inds, uint16_t* scores) {
+  if (!ctx || !gates || !inds || !scores || rows < 1 || k < 1) return ORN_ERR_ARG;
+  return k_router_topk(ctx, ctx->stream, gates, rows, n, k, inds, scores);
+}
+int32_t orn_moe_combine(orn_ctx* ctx, const uint16_t* scores, const uint16_t* y,
+                        const uint16_t* gate, const uint16_t* shared, int32_t T, int32_t k,
+                        int32_t dim, int32_t normalize, uint16_t* out) {
+  if (!ctx || !scores || !y || !gate || !shared || !out || T < 1) return ORN_ERR_ARG;
+  return k_moe_combine(ctx, ctx->stream, scores, y, gate, shared, T, k, dim, normalize, out);
+}
+
+int32_t orn_gdn_front(orn_ctx* ctx, const uint16_t* conv_state, const uint16_t* qkv,
+                      const uint16_t* conv_w, const uint16_t* a, const uint16_t* b,
+                      const uint16_t* a_log, const uint16_t* dt_bias, int32_t T, int32_t Hk,
+                      int32_t Hv, int32_t Dh, int32_t Kc, float eps, uint16_t* conv_next,
+                      uint16_t* q, uint16_t* k, uint16_t* v, uint16_t* beta, float* g) {
+  if (!ctx || !conv_state || !qkv || !conv_w || !a || !b || !a_log || !dt_bias || !conv_next ||
+      !q || !k || !v || !beta || !g || T < 1)
+    return ORN_ERR_ARG;
+  return k_gdn_front(ctx, ctx->stream, conv_state, qkv, conv_w, a, b, a_log, dt_bias, T, Hk, Hv, Dh,
+                     Kc, eps, conv_next, q, k, v, beta, g, nullptr);
+}
+int32_t orn_gated_delta(orn_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                        const float* g, const uint16_t* beta, float* state, int32_t T, int32_t Hk,
+                        int32_t Hv, uint16_t* y, float* snaps) {
+  if (!ctx || !q || !k || !v || !g || !beta || !state || !y || T < 1) return ORN_ERR_ARG;
+  return k_gated_delta(ctx, ctx->stream, q, k, v, g, beta, state, T, Hk, Hv, y, snaps);
+}
+
+int32_t orn_rope(orn_ctx* ctx, uint16_t* x, int32_t T, int32_t H, int32_t hd, int32_t dims,
+                 float theta, int32_t offset) {
+  if (!ctx || !x || T < 1 || dims > hd || dims % 2) return ORN_ERR_ARG;
+  float lnb = (float)(log((double)theta) / (double)(dims / 2));
+  return k_rope(ctx, ctx->stream, x, T, H, hd, dims, lnb, nullptr, offset);
+}
+int32_t orn_sdpa_decode(orn_ctx* ctx, const uint16_t* q, const uint16_t* kc, const uint16_t* vc,
+                        int32_t T, int32_t Hq, int32_t Hkv, int32_t hd, int32_t cap,
+                        int32_t offset, float scale, uint16_t* out) {
+  if (!ctx || !q || !kc || !vc || !out || T < 1) return ORN_ERR_ARG;
+  if (offset + T > cap) ORN_FAIL(ctx, ORN_ERR_ARG, "sdpa_decode: window exceeds the cache capacity");
+  return k_sdpa_decode(ctx, ctx->stream, q, kc, vc, T, Hq, Hkv, hd, cap, nullptr, offset, scale, out);
+}
+
+int32_t orn_greedy(orn_ctx* ctx, const uint16_t* logits, int32_t T, int32_t V, int32_t normalize,
+                   uint32_t* tokens) {
+  if (!ctx || !logits || !tokens || T < 1 || V < 1) return ORN_ERR_ARG;
+  float* scratch = nullptr;
+  CK(orn_alloc(ctx, sizeof(float) * greedy_scratch_floats(T, V), (void**)&scratch));
+  int rc = k_greedy(ctx, ctx->stream, logits, T, V, normalize, tokens, scratch);
+  if (rc == ORN_OK) rc = orn_sync(ctx);
+  cudaFree(scratch);
+  return rc;
+}
+
+// host copies of the elementary functions
+float orn_host_expf(float x) { return orn_expf(x); }
+float orn_host_logf(float x) { return orn_logf(x); }
+float orn_host_log1pf(float x) { return orn_log1pf(x); }
+void orn_host_sincosf(float a, float* s, float* c) { orn_sincosf(a, s, c); }
+float orn_host_sigmoid_bf(float x) { return orn_sigmoid_bf(x); }
+float orn_host_softplus_bf(float x) { return orn_softplus_bf(x); }
+
+}  // extern "C"

@@ -1,0 +1,144 @@
+// Internal types shared by the translation units of libornith_cuda.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/ornith_cuda.h"
+#include "orn_common.cuh"
+
+struct orn_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  int64_t launches = 0;  // kernels launched through this context
+  int sm_count = 148;
+};
+
+// Device-resident weight matrix [E, O, K].
+//   Q4_K: w = nibble bytes [E,O,K/2]; s = 16-byte records [E,O,K/256] =
+//         {d f16, dmin f16, scales[12]} so one aligned 128-bit load brings a
+//         block's whole header; b unused.
+//   Q6_K: w = ql|qh bytes [E,O,K/256*192]; s = int8 scales [E,O,K/256,16];
+//         b = d f16 [E,O,K/256].
+//   A8  : w = codes [E,O,K]; s = u32 records [E,O,K/64] = {scale bf16, bias bf16}.
+//   BF16: w = bf16 [E,O,K].
+struct orn_linear {
+  int kind = 0, E = 1, O = 0, K = 0;
+  uint8_t* w = nullptr;
+  uint8_t* s = nullptr;
+  uint8_t* b = nullptr;
+  size_t w_bytes = 0, s_bytes = 0, b_bytes = 0;  // device sizes
+  bool owns = true;
+};
+
+// POD view passed to kernels by value
+struct LinDev {
+  int kind, E, O, K;
+  const uint8_t* w;
+  const uint8_t* s;
+  const uint8_t* b;
+};
+static inline LinDev lin_dev(const orn_linear* l) {
+  return LinDev{l->kind, l->E, l->O, l->K, l->w, l->s, l->b};
+}
+
+#define ORN_CHECK_CUDA(ctx, call)                                              \
+  do {                                                                         \
+    cudaError_t e__ = (call);                                                  \
+    if (e__ != cudaSuccess) {                                                  \
+      (ctx)->err = std::string(#call) + ": " + cudaGetErrorString(e__);        \
+      return ORN_ERR_CUDA;                                                     \
+    }                                                                          \
+  } while (0)
+
+#define ORN_FAIL(ctx, code, msg) \
+  do {                           \
+    (ctx)->err = (msg);          \
+    return (code);               \
+  } while (0)
+
+static inline int orn_launch_check(orn_ctx* ctx, const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    ctx->err = std::string(what) + ": " + cudaGetErrorString(e);
+    return ORN_ERR_CUDA;
+  }
+  ctx->launches += 1;
+  return ORN_OK;
+}
+
+// ---- kernel launchers (each returns ORN_OK or an error, work on s) ---------
+// linear.cu
+int k_gemv(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, int M, void* y,
+           int out_f32);
+int k_gather_gemv(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x,
+                  const uint32_t* lhs, const uint32_t* rhs, int rows, bf16_t* y);
+int k_kq_dequantize(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, int e, float* out);
+int k_embedding(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const uint32_t* ids, int T,
+                bf16_t* out);
+int k_linear_pack(orn_ctx* ctx, cudaStream_t s, orn_linear* L, const uint8_t* dw,
+                  const uint8_t* ds, const uint8_t* db);
+int k_linear_unpack(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, uint8_t* dw, uint8_t* ds,
+                    uint8_t* db);
+int k_linear_random(orn_ctx* ctx, cudaStream_t s, orn_linear* L, uint64_t seed, float std);
+int k_linear_gather_rows(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const uint32_t* ids,
+                         int n, orn_linear* out);
+int k_fill_bf16(orn_ctx* ctx, cudaStream_t s, bf16_t* p, size_t n, uint64_t seed, float mean,
+                float std);
+void linear_alloc_sizes(int kind, int E, int O, int K, size_t* w, size_t* s, size_t* b);
+void linear_artifact_sizes(int kind, int E, int O, int K, size_t* w, size_t* s, size_t* b);
+
+// ops.cu
+int k_rms_norm(orn_ctx* ctx, cudaStream_t s, const bf16_t* x, const bf16_t* w, int rows, int n,
+               float eps, bf16_t* out);
+int k_add_rms_norm(orn_ctx* ctx, cudaStream_t s, const bf16_t* a, const bf16_t* b,
+                   const bf16_t* w, int rows, int n, float eps, bf16_t* h, bf16_t* out);
+int k_rms_norm_gated(orn_ctx* ctx, cudaStream_t s, const bf16_t* x, const bf16_t* w,
+                     const bf16_t* z, int rows, int n, float eps, bf16_t* out);
+int k_sigmoid_gate(orn_ctx* ctx, cudaStream_t s, const bf16_t* gate, const bf16_t* x, int n,
+                   int inner, bf16_t* out);
+int k_swiglu(orn_ctx* ctx, cudaStream_t s, const bf16_t* g, const bf16_t* u, int n, bf16_t* out);
+int k_add(orn_ctx* ctx, cudaStream_t s, const bf16_t* a, const bf16_t* b, int n, bf16_t* out);
+int k_softmax_precise(orn_ctx* ctx, cudaStream_t s, const bf16_t* x, int rows, int n, bf16_t* out);
+int k_router_topk(orn_ctx* ctx, cudaStream_t s, const bf16_t* gates, int rows, int n, int k,
+                  uint32_t* inds, bf16_t* scores);
+int k_moe_combine(orn_ctx* ctx, cudaStream_t s, const bf16_t* scores, const bf16_t* y,
+                  const bf16_t* gate, const bf16_t* shared, int T, int k, int dim, int normalize,
+                  bf16_t* out);
+int k_split_qgate(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, int T, int Hq, int hd, bf16_t* q,
+                  bf16_t* gate);
+int k_concat2(orn_ctx* ctx, cudaStream_t s, const bf16_t* a, const bf16_t* b, int T, int n,
+              bf16_t* out);
+
+// gdn.cu
+int k_gdn_front(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv_state, const bf16_t* qkv,
+                const bf16_t* cw, const bf16_t* a, const bf16_t* b, const bf16_t* a_log,
+                const bf16_t* dt_bias, int T, int Hk, int Hv, int Dh, int Kc, float eps,
+                bf16_t* conv_next, bf16_t* q, bf16_t* k, bf16_t* v, bf16_t* beta, float* g,
+                bf16_t* conv_input_keep);
+int k_gated_delta(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* k, const bf16_t* v,
+                  const float* g, const bf16_t* beta, float* state, int T, int Hk, int Hv,
+                  bf16_t* y, float* snaps);
+int k_gated_delta_ring(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* k,
+                       const bf16_t* v, const float* g, const bf16_t* beta, float* ring,
+                       int nring, const int* cur, int final_only, int T, int Hk, int Hv,
+                       bf16_t* y);
+
+// attn.cu
+int k_rope(orn_ctx* ctx, cudaStream_t s, bf16_t* x, int T, int H, int hd, int dims, float lnb,
+           const int* dev_offset, int offset_add);
+int k_kv_append(orn_ctx* ctx, cudaStream_t s, const bf16_t* k, const bf16_t* v, int T, int Hkv,
+                int hd, int cap, const int* dev_offset, int offset_add, bf16_t* kc, bf16_t* vc);
+int k_sdpa_decode(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* kc,
+                  const bf16_t* vc, int T, int Hq, int Hkv, int hd, int cap, const int* dev_offset,
+                  int offset_add, float scale, bf16_t* out);
+
+// sample.cu
+int k_greedy(orn_ctx* ctx, cudaStream_t s, const bf16_t* logits, int T, int V, int normalize,
+             uint32_t* tokens, float* scratch /* [T, 2*ceil(V/1024)] */);
+size_t greedy_scratch_floats(int T, int V);

@@ -1,0 +1,127 @@
+// Greedy sampling over the vocabulary: bf16 log-softmax then argmax with the
+// lowest index winning ties, and the raw-logit argmax of the draft chain.
+//
+// Replaces looped_logsumexp / vs_Subtract / argmax of the reference
+// (kernels/mlx/.../logsumexp.h:3-74, arg_reduce.metal:53-66) as dispatched by
+// src/ops/sample.rs:134-147,186-191.
+//
+// lp_i = bf(x_i - lse) with lse = bf(max + log sum exp(x - max)).  Because the
+// subtraction is monotone, argmax(lp) is the lowest index whose lp equals
+// bf(max - lse); so one pass produces per-1024-logit chunk (max, sum), and a
+// second, single-CTA pass merges the chunks in ascending order and scans only
+// the first chunk whose maximum reaches the winning lp value.
+#include "orn_internal.h"
+
+namespace {
+
+__global__ void __launch_bounds__(256)
+lse_chunk_kernel(const bf16_t* __restrict__ logits, int V, int nc, float* __restrict__ scratch) {
+  __shared__ float red[32];
+  const int b = blockIdx.x, t = blockIdx.y;
+  const bf16_t* x = logits + (int64_t)t * V + (int64_t)b * 1024;
+  const int n = min(1024, V - b * 1024);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float v[4];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int idx = 4 * threadIdx.x + i;
+    v[i] = idx < n ? bf2f(x[idx]) : -INFINITY;
+    m = fmaxf(m, v[i]);
+  }
+  m = warp_max(m);
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  m = warp_max(red[lane & 7]);
+  __syncthreads();
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (4 * threadIdx.x + i < n) acc = acc + orn_expf(v[i] - m);
+  acc = warp_sum(acc);
+  if (threadIdx.x < 32) red[threadIdx.x] = 0.f;
+  __syncthreads();
+  if (lane == 0) red[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    float s = warp_sum(red[lane]);
+    if (lane == 0) {
+      scratch[((int64_t)t * nc + b) * 2 + 0] = m;
+      scratch[((int64_t)t * nc + b) * 2 + 1] = s;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+greedy_finish_kernel(const bf16_t* __restrict__ logits, int V, int nc, int normalize,
+                     const float* __restrict__ scratch, uint32_t* __restrict__ tokens) {
+  extern __shared__ float sh[];  // m[nc], e[nc]
+  __shared__ float red[32];
+  __shared__ float s_lse, s_target;
+  __shared__ int s_chunk;
+  __shared__ unsigned int s_best;
+  const int t = blockIdx.x;
+  const float* sc = scratch + (int64_t)t * nc * 2;
+  float* sm = sh;
+  float* se = sh + nc;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float m = -INFINITY;
+  for (int b = threadIdx.x; b < nc; b += blockDim.x) {
+    sm[b] = sc[2 * b];
+    m = fmaxf(m, sm[b]);
+  }
+  m = warp_max(m);
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  const float M = warp_max(red[lane & 7]);
+  for (int b = threadIdx.x; b < nc; b += blockDim.x) se[b] = orn_expf(sm[b] - M);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float lse = 0.f, target = M;
+    if (normalize) {
+      float S = 0.f;
+      for (int b = 0; b < nc; ++b) S = fmaf(sc[2 * b + 1], se[b], S);
+      lse = bfr(M + orn_logf(S));
+      target = bfr(M - lse);
+    }
+    int chunk = 0;
+    for (int b = 0; b < nc; ++b) {
+      float lp = normalize ? bfr(sm[b] - lse) : sm[b];
+      if (lp == target) { chunk = b; break; }
+    }
+    s_lse = lse; s_target = target; s_chunk = chunk; s_best = 0xffffffffu;
+  }
+  __syncthreads();
+  const int b = s_chunk;
+  const bf16_t* x = logits + (int64_t)t * V + (int64_t)b * 1024;
+  const int n = min(1024, V - b * 1024);
+  unsigned int best = 0xffffffffu;
+#pragma unroll
+  for (int i = 3; i >= 0; --i) {
+    int idx = 4 * threadIdx.x + i;
+    if (idx < n) {
+      float lp = normalize ? bfr(bf2f(x[idx]) - s_lse) : bf2f(x[idx]);
+      if (lp == s_target) best = (unsigned int)(b * 1024 + idx);
+    }
+  }
+  best = warp_min_u32(best);
+  if (lane == 0) atomicMin(&s_best, best);
+  __syncthreads();
+  if (threadIdx.x == 0) tokens[t] = s_best;
+}
+}  // namespace
+
+size_t greedy_scratch_floats(int T, int V) { return (size_t)T * 2 * ((V + 1023) / 1024); }
+
+int k_greedy(orn_ctx* ctx, cudaStream_t s, const bf16_t* logits, int T, int V, int normalize,
+             uint32_t* tokens, float* scratch) {
+  const int nc = (V + 1023) / 1024;
+  dim3 grid(nc, T);
+  lse_chunk_kernel<<<grid, 256, 0, s>>>(logits, V, nc, scratch);
+  int rc = orn_launch_check(ctx, "lse_chunk");
+  if (rc != ORN_OK) return rc;
+  size_t shm = sizeof(float) * 2 * (size_t)nc;
+  if (shm > 40000) ORN_FAIL(ctx, ORN_ERR_ARG, "greedy: vocabulary too large");
+  greedy_finish_kernel<<<T, 256, shm, s>>>(logits, V, nc, normalize, scratch, tokens);
+  return orn_launch_check(ctx, "greedy_finish");
+}

@@ -1,0 +1,64 @@
+"""Generates the golden fixtures from the reference's own numpy tools.
+
+Run where the reference tree is mounted:
+    python tests/golden/make_golden.py /path/to/ornith-rs
+It imports tools/q4k.py and tools/aq.py from that tree (the only importable
+pieces of the reference's arithmetic) and writes small .npz files next to this
+script.  The tests read only the .npz files.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def main(ref_root):
+    sys.path.insert(0, os.path.join(ref_root, "tools"))
+    import aq
+    import q4k
+
+    rng = np.random.default_rng(20240607)
+
+    # 1. Q4_K field packing: 8 scales + 8 mins <-> 12 bytes
+    sc = rng.integers(0, 64, (64, 8)).astype(np.uint8)
+    mn = rng.integers(0, 64, (64, 8)).astype(np.uint8)
+    packed = q4k.put_scale_min_k4(sc, mn)
+    for j in range(8):
+        d, m = q4k.get_scale_min_k4(j, packed)
+        assert np.array_equal(d, sc[:, j]) and np.array_equal(m, mn[:, j])
+
+    # 2. Q4_K quantise + dequantise of real-looking weights, and of raw random blocks
+    w = (rng.standard_t(4, (24, 256)) * 0.015).astype(np.float32)
+    blocks_q = q4k.quantize(w)
+    deq_q = q4k.dequantize(blocks_q)
+    blocks_r = rng.integers(0, 256, (24, q4k.BLOCK_BYTES)).astype(np.uint8)
+    # keep d and dmin finite, positive halves
+    dm = (np.abs(rng.standard_normal((24, 2))) * 1e-3).astype(np.float16)
+    blocks_r[:, 0:4] = dm.view(np.uint8).reshape(24, 4)
+    deq_r = q4k.dequantize(blocks_r)
+    qs_q, scales_q, dm_q = q4k.split(blocks_q, 24, 1)
+    qs_r, scales_r, dm_r = q4k.split(blocks_r, 24, 1)
+    np.savez_compressed(
+        os.path.join(HERE, "q4k_golden.npz"),
+        sc=sc, mn=mn, packed=packed, w=w,
+        blocks_q=blocks_q, deq_q=deq_q, qs_q=qs_q, scales_q=scales_q, dm_q=dm_q.view(np.uint16),
+        blocks_r=blocks_r, deq_r=deq_r, qs_r=qs_r, scales_r=scales_r, dm_r=dm_r.view(np.uint16))
+
+    # 3. affine 8-bit group-64 quantise + pack
+    wa = (rng.standard_normal((16, 256)) * 0.02).astype(np.float32)
+    q, s, b = aq.quantize(wa, group_size=64, bits=8)
+    words = aq.pack(q, 8, 256 // 4)
+    deq = (s[:, None] * q.astype(np.float32) + b[:, None]).reshape(16, 256)
+    np.savez_compressed(os.path.join(HERE, "a8_golden.npz"), w=wa, q=q.reshape(16, 256), scales=s.reshape(16, 4),
+                        biases=b.reshape(16, 4), words=words, deq=deq)
+
+    # 4. bfloat16 rounding as the tool states it (ties to even)
+    xs = rng.standard_normal(4096).astype(np.float32) * np.float32(10.0) ** rng.integers(-6, 6, 4096)
+    np.savez_compressed(os.path.join(HERE, "bf16_golden.npz"), x=xs.astype(np.float32), r=aq.bf16(xs))
+    print("wrote fixtures to", HERE)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,245 @@
+"""Seeded synthetic inputs for the tests: bfloat16 helpers, the three
+quantisers, raw-field generators and a tiny model in the artifact layout."""
+import numpy as np
+
+import oracle as orc
+
+Q4K, Q6K, A8, BF16 = 0, 1, 2, 3
+
+
+# ------------------------------------------------------------------ bfloat16
+def f32_to_bf16(x):
+    """Round to nearest even, as src/array.rs:229-237."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    u = u + 0x7FFF + ((u >> 16) & 1)
+    return (u >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(h):
+    return (np.ascontiguousarray(h, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def rel_err(a, b):
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    return np.abs(a - b) / np.maximum(np.abs(b), 1e-30)
+
+
+# ------------------------------------------------------------------ Q4_K
+def put_scale_min_k4(sc, mn):
+    """8 six-bit scales + 8 mins -> 12 bytes (inverse of get_scale_min_k4)."""
+    sc = np.asarray(sc, np.uint8)
+    mn = np.asarray(mn, np.uint8)
+    out = np.zeros(sc.shape[:-1] + (12,), np.uint8)
+    for j in range(4):
+        out[..., j] = sc[..., j] & 63
+        out[..., j + 4] = mn[..., j] & 63
+    for j in range(4, 8):
+        out[..., j + 4] = (sc[..., j] & 0xF) | ((mn[..., j] & 0xF) << 4)
+        out[..., j - 4] |= (sc[..., j] >> 4) << 6
+        out[..., j] |= (mn[..., j] >> 4) << 6
+    return out
+
+
+def raw_q4k(rng, E, O, K):
+    """Raw-field Q4_K as in the single mat-vec benchmark config: d, dmin =
+    f16(|N(0,1)| 1e-3), scales/mins uniform 0..63, uniform nibbles."""
+    nb = K // 256
+    n = E * O * nb
+    dm = (np.abs(rng.standard_normal((n, 2))) * 1e-3).astype(np.float16)
+    sc = rng.integers(0, 64, (n, 8)).astype(np.uint8)
+    mn = rng.integers(0, 64, (n, 8)).astype(np.uint8)
+    scales = put_scale_min_k4(sc, mn)
+    qs = rng.integers(0, 256, (n, 128)).astype(np.uint8)
+    return orc.Weights(Q4K, E, O, K, qs, scales, dm.view(np.uint16))
+
+
+def raw_q6k(rng, E, O, K):
+    nb = K // 256
+    n = E * O * nb
+    d = (np.abs(rng.standard_normal(n)) * 1e-3).astype(np.float16)
+    scales = rng.integers(-128, 128, (n, 16)).astype(np.int8)
+    w = rng.integers(0, 256, (n, 192)).astype(np.uint8)
+    return orc.Weights(Q6K, E, O, K, w, scales.view(np.uint8), d.view(np.uint16))
+
+
+def quantize_q4k(w):
+    """Plain min/max Q4_K writer (the shape of ggml's quantize_row_q4_K_ref as
+    restated in the reference's tools/q4k.py:122-161)."""
+    w = np.asarray(w, np.float32)
+    E_O = w.shape[:-1]
+    K = w.shape[-1]
+    x = w.reshape(-1, 256)
+    g = x.reshape(-1, 8, 32)
+    lo = np.minimum(g.min(-1), 0.0)
+    hi = g.max(-1)
+    scale = (hi - lo) / 15.0
+    mn = -lo
+    d = (scale.max(-1, keepdims=True) / 63.0).astype(np.float16).astype(np.float32)
+    dm = (mn.max(-1, keepdims=True) / 63.0).astype(np.float16).astype(np.float32)
+    sc = np.where(d > 0, np.clip(np.rint(scale / np.where(d > 0, d, 1)), 0, 63), 0)
+    m = np.where(dm > 0, np.clip(np.rint(mn / np.where(dm > 0, dm, 1)), 0, 63), 0)
+    ds, ms = d * sc, dm * m
+    q = np.clip(np.rint((g + ms[..., None]) / np.where(ds > 0, ds, 1)[..., None]), 0, 15)
+    q = np.where((ds > 0)[..., None], q, 0).astype(np.uint8).reshape(-1, 256)
+    qs = np.empty((len(x), 128), np.uint8)
+    for h in range(4):
+        qs[:, 32 * h:32 * h + 32] = q[:, 64 * h:64 * h + 32] | (q[:, 64 * h + 32:64 * h + 64] << 4)
+    scales = put_scale_min_k4(sc.astype(np.uint8), m.astype(np.uint8))
+    dmh = np.concatenate([d, dm], -1).astype(np.float16)
+    return qs, scales, dmh.view(np.uint16), (E_O, K)
+
+
+def quantize_q6k(w):
+    """Round-to-nearest Q6_K: 16 sub-blocks of 16, signed int8 sub-scales."""
+    w = np.asarray(w, np.float32)
+    x = w.reshape(-1, 256)
+    g = x.reshape(-1, 16, 16)
+    sub = np.abs(g).max(-1) / 31.0
+    d = (sub.max(-1, keepdims=True) / 127.0).astype(np.float16).astype(np.float32)
+    sc = np.where(d > 0, np.clip(np.rint(sub / np.where(d > 0, d, 1)), 1, 127), 0).astype(np.int8)
+    ds = d * sc
+    q = np.where((ds > 0)[..., None], np.clip(np.rint(g / np.where(ds > 0, ds, 1)[..., None]), -32, 31), 0)
+    q = (q + 32).astype(np.uint8).reshape(-1, 256)
+    ql = np.zeros((len(x), 128), np.uint8)
+    qh = np.zeros((len(x), 64), np.uint8)
+    for n in range(2):
+        for c in range(4):
+            v = q[:, 128 * n + 32 * c:128 * n + 32 * c + 32]
+            lo4, hi2 = v & 0xF, v >> 4
+            base = 64 * n + (32 if (c & 1) else 0)
+            if c < 2:
+                ql[:, base:base + 32] |= lo4
+            else:
+                ql[:, base:base + 32] |= lo4 << 4
+            qh[:, 32 * n:32 * n + 32] |= hi2 << (2 * c)
+    return np.concatenate([ql, qh], 1), sc.view(np.uint8), d.astype(np.float16).view(np.uint16)
+
+
+def quantize_a8(w):
+    """mlx affine quantise, 8 bits, group 64 (the rule restated in the
+    reference's tools/aq.py:34-72): scale = (max-min)/255, bias = min."""
+    w = np.asarray(w, np.float32)
+    g = w.reshape(-1, 64)
+    lo, hi = g.min(-1), g.max(-1)
+    scale = np.maximum((hi - lo) / 255.0, 1e-8)
+    sb = f32_to_bf16(scale)
+    bb = f32_to_bf16(lo)
+    s, b = bf16_to_f32(sb), bf16_to_f32(bb)
+    q = np.clip(np.rint((g - b[:, None]) / s[:, None]), 0, 255).astype(np.uint8)
+    return q, sb, bb
+
+
+def make_weights(rng, kind, E, O, K, std=0.02):
+    w = (rng.standard_normal((E * O, K)) * std).astype(np.float32)
+    if kind == Q4K:
+        qs, scales, dm, _ = quantize_q4k(w)
+        return orc.Weights(Q4K, E, O, K, qs, scales, dm)
+    if kind == Q6K:
+        q, sc, d = quantize_q6k(w)
+        return orc.Weights(Q6K, E, O, K, q, sc, d)
+    if kind == A8:
+        q, s, b = quantize_a8(w)
+        return orc.Weights(A8, E, O, K, q, s, b)
+    return orc.Weights(BF16, E, O, K, f32_to_bf16(w))
+
+
+# ------------------------------------------------------------------ tiny model
+def tiny_config(cfg_cls, **over):
+    """A small model with every structural feature of the 35B-A3B: three
+    gated-delta layers per full-attention layer, GQA, a routed MoE with a
+    shared expert, an MTP head."""
+    d = dict(hidden=512, n_layers=4, full_attn_interval=4, n_heads=4, n_kv_heads=2, head_dim=256,
+             rope_dims=64, rope_theta=1e7, gdn_k_heads=2, gdn_v_heads=4, gdn_head_dim=128,
+             gdn_conv_kernel=4, n_experts=16, top_k=4, expert_inter=256, shared_inter=256,
+             norm_topk_prob=1, vocab=1536, rms_eps=1e-6, max_ctx=96)
+    d.update(over)
+    return cfg_cls(**d)
+
+
+def tiny_model_weights(cfg, seed=0):
+    """name -> Weights | uint16 tensor, in the benchmark's quantisation mix."""
+    rng = np.random.default_rng(seed)
+    H = cfg.hidden
+    D = 2 * cfg.gdn_k_heads * cfg.gdn_head_dim + cfg.gdn_v_heads * cfg.gdn_head_dim
+    VD = cfg.gdn_v_heads * cfg.gdn_head_dim
+    QD, KVD = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    W = {}
+
+    def ten(name, n, mean, std):
+        W[name] = f32_to_bf16(mean + std * rng.standard_normal(n).astype(np.float32))
+
+    def moe(p, dense):
+        q4, q6, a8 = (BF16, BF16, BF16) if dense else (Q4K, Q6K, A8)
+        W[p + "gate"] = make_weights(rng, a8, 1, cfg.n_experts, H)
+        W[p + "switch_mlp.gate_proj"] = make_weights(rng, q4, cfg.n_experts, cfg.expert_inter, H)
+        W[p + "switch_mlp.up_proj"] = make_weights(rng, q4, cfg.n_experts, cfg.expert_inter, H)
+        W[p + "switch_mlp.down_proj"] = make_weights(rng, q6, cfg.n_experts, H, cfg.expert_inter)
+        W[p + "shared_expert.gate_proj"] = make_weights(rng, q4, 1, cfg.shared_inter, H)
+        W[p + "shared_expert.up_proj"] = make_weights(rng, q4, 1, cfg.shared_inter, H)
+        W[p + "shared_expert.down_proj"] = make_weights(rng, q6, 1, H, cfg.shared_inter)
+        W[p + "shared_expert_gate"] = make_weights(rng, a8, 1, 1, H)
+
+    W["embed_tokens"] = make_weights(rng, A8, 1, cfg.vocab, H)
+    W["lm_head"] = make_weights(rng, A8, 1, cfg.vocab, H)
+    ten("norm.weight", H, 1.0, 0.05)
+    for i in range(cfg.n_layers):
+        lp = "layers.%d." % i
+        ten(lp + "input_layernorm.weight", H, 1.0, 0.05)
+        ten(lp + "post_attention_layernorm.weight", H, 1.0, 0.05)
+        if (i + 1) % cfg.full_attn_interval != 0:
+            a = lp + "linear_attn."
+            W[a + "in_proj_qkv"] = make_weights(rng, A8, 1, D, H)
+            W[a + "in_proj_z"] = make_weights(rng, A8, 1, VD, H)
+            W[a + "in_proj_a.weight"] = make_weights(rng, BF16, 1, cfg.gdn_v_heads, H)
+            W[a + "in_proj_b.weight"] = make_weights(rng, BF16, 1, cfg.gdn_v_heads, H)
+            W[a + "out_proj"] = make_weights(rng, A8, 1, H, VD)
+            ten(a + "conv1d.weight", D * cfg.gdn_conv_kernel, 0.0, 0.2)
+            ten(a + "dt_bias", cfg.gdn_v_heads, 0.0, 0.3)
+            ten(a + "A_log", cfg.gdn_v_heads, 0.0, 0.3)
+            ten(a + "norm.weight", cfg.gdn_head_dim, 1.0, 0.05)
+        else:
+            a = lp + "self_attn."
+            W[a + "q_proj"] = make_weights(rng, A8, 1, 2 * QD, H)
+            W[a + "k_proj"] = make_weights(rng, A8, 1, KVD, H)
+            W[a + "v_proj"] = make_weights(rng, A8, 1, KVD, H)
+            W[a + "o_proj"] = make_weights(rng, A8, 1, H, QD)
+            ten(a + "q_norm.weight", cfg.head_dim, 1.0, 0.05)
+            ten(a + "k_norm.weight", cfg.head_dim, 1.0, 0.05)
+        moe(lp + "mlp.", False)
+    lp = "mtp.layers.0."
+    ten("mtp.pre_fc_norm_embedding.weight", H, 1.0, 0.05)
+    ten("mtp.pre_fc_norm_hidden.weight", H, 1.0, 0.05)
+    W["mtp.fc.weight"] = make_weights(rng, BF16, 1, H, 2 * H)
+    ten("mtp.norm.weight", H, 1.0, 0.05)
+    ten(lp + "input_layernorm.weight", H, 1.0, 0.05)
+    ten(lp + "post_attention_layernorm.weight", H, 1.0, 0.05)
+    W[lp + "self_attn.q_proj.weight"] = make_weights(rng, BF16, 1, 2 * QD, H)
+    W[lp + "self_attn.k_proj.weight"] = make_weights(rng, BF16, 1, KVD, H)
+    W[lp + "self_attn.v_proj.weight"] = make_weights(rng, BF16, 1, KVD, H)
+    W[lp + "self_attn.o_proj.weight"] = make_weights(rng, BF16, 1, H, QD)
+    ten(lp + "self_attn.q_norm.weight", cfg.head_dim, 1.0, 0.05)
+    ten(lp + "self_attn.k_norm.weight", cfg.head_dim, 1.0, 0.05)
+    moe(lp + "mlp.", True)
+    return W
+
+
+def gather_rows_weights(W, ids):
+    """FrSpec::prune on host tensors (row gather of every head tensor)."""
+    ids = np.asarray(ids)
+    rw = W.w.reshape(W.O, -1)[ids]
+    rs = None if W.s is None else W.s.reshape(W.O, -1)[ids]
+    rb = None if W.b is None else W.b.reshape(W.O, -1)[ids]
+    return orc.Weights(W.kind, 1, len(ids), W.K, rw, rs, rb)
+
+
+def upload_model(pkg, ctx, cfg, weights):
+    """Register the same tensors with the CUDA library."""
+    m = pkg.TextModel(ctx, cfg)
+    for name, w in weights.items():
+        if isinstance(w, orc.Weights):
+            lin = pkg.Linear.from_numpy(ctx, w.kind, w.w, w.s, w.b, E=w.E, O=w.O, K=w.K)
+            m.set_linear(name, lin)
+        else:
+            m.set_tensor(name, w)
+    return m
