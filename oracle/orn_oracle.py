@@ -1,6 +1,7 @@
-"""ctypes binding of the CPU oracle (oracle/liborn_oracle.so) for the tests.
+"""TEST INFRASTRUCTURE: ctypes binding of the CPU oracle (liborn_oracle.so).
 
-The oracle is test infrastructure: nothing under the package imports this.
+Used by the tests, by the smoke check and by the CPU-baseline leg of the
+benchmark.  Nothing under the package imports this.
 """
 import ctypes as C
 import os
@@ -8,8 +9,7 @@ import subprocess
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(ORACLE_DIR, "liborn_oracle.so")
 
 Q4K, Q6K, A8, BF16 = 0, 1, 2, 3

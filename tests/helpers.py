@@ -2,7 +2,7 @@
 quantisers, raw-field generators and a tiny model in the artifact layout."""
 import numpy as np
 
-import oracle as orc
+import orn_oracle as orc
 
 Q4K, Q6K, A8, BF16 = 0, 1, 2, 3
 

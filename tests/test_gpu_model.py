@@ -1,0 +1,145 @@
+"""The CUDA model and generation loops against the CPU oracle (tiny model), and
+size-independent properties at the real dimensions."""
+import numpy as np
+import pytest
+
+import helpers as hp
+import orn_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tiny(pkg, ctx):
+    cfg = hp.tiny_config(pkg.Config)
+    W = hp.tiny_model_weights(cfg, seed=5)
+    om = orc.Model(cfg, W)
+    gm = hp.upload_model(pkg, ctx, cfg, W)
+    yield cfg, W, om, gm
+    gm.free()
+    om.free()
+
+
+def test_forward_matches_oracle(pkg, ctx, tiny):
+    cfg, W, om, gm = tiny
+    ids = np.array([3, 77, 1500, 9, 12, 800, 41], np.uint32)
+    oc = om.new_cache()
+    gc = gm.make_cache()
+    for a, b in [(0, 1), (1, 3), (3, 7)]:
+        ref = om.forward(oc, ids[a:b])
+        got = gm.forward(gc, ids[a:b]).numpy()
+        assert np.array_equal(got, ref), (a, b)
+    assert gc.offset == 7
+    # logits and greedy tokens of the last rows
+    rt, rl = om.head_greedy(ref, 4, want_logits=True)
+    gt, gl = gm.head_greedy(ctx.upload(ref), 4, want_logits=True)
+    assert np.array_equal(gl.numpy(), rl) and gt.tolist() == rt.tolist()
+    om.free_cache(oc)
+    gc.free()
+
+
+def test_capture_and_rewind(pkg, ctx, tiny):
+    """forward_capture + rewind(keep) leaves the caches as if only `keep`
+    tokens had been stepped (tests/mtp.rs:177-234)."""
+    cfg, W, om, gm = tiny
+    ids = np.array([10, 20, 30, 40, 50], np.uint32)
+    for keep in (1, 2):
+        a, b = gm.make_cache(), gm.make_cache()
+        gm.forward(a, ids[:2])
+        gm.forward(b, ids[:2])
+        gm.forward(a, ids[2:4], capture=True)
+        a.rewind(keep)
+        for t in range(keep):
+            gm.forward(b, ids[2 + t:3 + t])
+        assert a.offset == b.offset == 2 + keep
+        ya = gm.forward(a, ids[4:5]).numpy()
+        yb = gm.forward(b, ids[4:5]).numpy()
+        assert np.array_equal(ya, yb)
+        a.free()
+        b.free()
+
+
+def test_generate_matches_oracle(pkg, ctx, tiny):
+    cfg, W, om, gm = tiny
+    prompt = np.array([5, 900, 33, 1201, 8, 64, 700], np.uint32)
+    ref = om.generate(prompt, 24)
+    c = gm.make_cache()
+    got = pkg.generate_step(gm, c, prompt, 24)
+    assert got == ref
+    assert c.offset == len(prompt) + 24
+    # on_token returning False stops, the stopping token included
+    seen = []
+    c.reset()
+    out = pkg.generate_step(gm, c, prompt, 24, on_token=lambda t: (seen.append(t) or len(seen) < 5))
+    assert out == ref[:5] and c.offset == len(prompt) + 5
+    c.free()
+
+
+@pytest.mark.parametrize("policy", [0, 1])
+@pytest.mark.parametrize("p", [0.0, 0.5, 0.9])
+def test_mtp_matches_oracle_and_autoregressive(pkg, ctx, tiny, policy, p):
+    """BASELINE config 4 on the tiny model: emitted ids byte-identical to the
+    non-speculative run, accepted counts equal to the oracle's."""
+    cfg, W, om, gm = tiny
+    prompt = np.array([5, 900, 33, 1201, 8, 64, 700], np.uint32)
+    ar = om.generate(prompt, 30)
+    force = (ar, p, 42) if p > 0 else None
+    ref, rst = om.generate_mtp(prompt, 1, 30, policy=policy, force=force)
+    c = gm.make_cache()
+    got, gst = pkg.generate_step_mtp(gm, c, prompt, 1, 30, policy=policy, force=force)
+    assert got == ar == ref
+    assert (gst.cycles, gst.drafted, gst.accepted) == (rst.cycles, rst.drafted, rst.accepted)
+    assert list(gst.accepted_by_depth) == list(rst.accepted_by_depth)
+    assert c.offset == len(prompt) + 30
+    c.free()
+
+
+def test_mtp_depth2_and_frspec(pkg, ctx, tiny):
+    cfg, W, om, gm = tiny
+    prompt = np.array([1, 2, 3, 4], np.uint32)
+    ar = om.generate(prompt, 16)
+    rng = np.random.default_rng(0)
+    ids = np.sort(rng.choice(cfg.vocab, 512, replace=False)).astype(np.uint32)
+    om.set_frspec(hp.gather_rows_weights(W["lm_head"], ids), ids)
+    gm.set_frspec(ids)
+    c = gm.make_cache()
+    for depth, fr in [(2, False), (1, True), (3, True)]:
+        c.reset()
+        ref, rst = om.generate_mtp(prompt, depth, 16, policy=1, frspec=fr, force=(ar, 0.7, 9))
+        got, gst = pkg.generate_step_mtp(gm, c, prompt, depth, 16, policy=1, frspec=fr, force=(ar, 0.7, 9))
+        assert got == ar == ref
+        assert (gst.cycles, gst.drafted, gst.accepted) == (rst.cycles, rst.drafted, rst.accepted)
+    c.free()
+    # bad id lists are refused (src/frspec.rs:78-100)
+    with pytest.raises(pkg.OrnError):
+        gm.set_frspec(np.array([1, 1], np.uint32))
+    with pytest.raises(pkg.OrnError):
+        gm.set_frspec(np.array([cfg.vocab], np.uint32))
+
+
+def test_full_size_layers_mtp_equals_autoregressive(pkg, ctx):
+    """Real layer dimensions (hidden 2048, 256 experts top-8, 16/2 heads, vocab
+    248320) at 4 layers, random-init on the GPU: speculative output is
+    byte-identical to non-speculative output on the engine itself."""
+    cfg = pkg.qwen35_config(max_ctx=160, n_layers=4)
+    m = pkg.TextModel(ctx, cfg)
+    m.init_random(7)
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, cfg.vocab, 9).astype(np.uint32)
+    c = m.make_cache()
+    ar = pkg.generate_step(m, c, prompt, 40)
+    assert len(set(ar)) > 3  # not a degenerate stream
+    for p in (0.0, 0.9):
+        c.reset()
+        got, st = pkg.generate_step_mtp(m, c, prompt, 1, 40, force=(ar, p, 5) if p else None)
+        assert got == ar
+        if p:
+            assert st.accepted >= st.drafted // 2
+    # FR-Spec with a seeded sorted unique subset of 65536 ids
+    ids = np.sort(rng.choice(cfg.vocab, 65536, replace=False)).astype(np.uint32)
+    m.set_frspec(ids)
+    c.reset()
+    got, st = pkg.generate_step_mtp(m, c, prompt, 1, 40, frspec=True, force=(ar, 0.5, 6))
+    assert got == ar
+    c.free()
+    m.free()

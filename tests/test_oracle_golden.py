@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 import helpers as hp
-import oracle as orc
+import orn_oracle as orc
 
 G = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
