@@ -1,0 +1,337 @@
+"""Benchmark: MTP depth-1 greedy speculative decode of a random-init
+Qwen3.5-MoE 35B-A3B (k-quant mix) at batch 1, on N GPUs of one node.
+
+  python bench.py --gpus 1 --steps 5 --warmup 3
+  python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+  python bench.py --impl reference      (the CPU restatement on the host cores)
+
+One "step" is one 200-token generation from a 51-token prompt (BASELINE config
+4: drafts forced to the target with probability p so that acceptance is
+controlled).  `value` is generated tokens / device time of the decode loop
+(CUDA events on the library's stream, weights and caches resident in HBM).
+`e2e` is generated tokens / host wall-clock of the whole public call
+`orn_generate_step_mtp` (prompt upload, prefill, every per-cycle device->host
+read of targets and drafts included).  At N > 1 every rank decodes its own
+sequence on a replica ("weak" scaling); there is no data-path collective.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "MTP-depth-1 decode tok/s (35B-A3B k-quant, batch 1)"
+PROMPT_LEN, GEN_TOKENS, FORCE_P, SEED = 51, 200, 0.5, 20240611
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def load_pkg():
+    import __graft_entry__ as ge
+    return ge.load_package()
+
+
+def step_bytes(cfg, T):
+    """Algorithmic bytes one trunk forward of T rows must move (weights at their
+    format size: Q4_K 144 B and Q6_K 210 B per 256 weights, affine-8 8.5 bit,
+    bf16 2 B; gated-delta state read once and written once per row)."""
+    H, V = cfg.hidden, cfg.vocab
+    a8 = lambda o, k: o * k * 1.0625
+    q4 = lambda o, k: o * k * 0.5625
+    q6 = lambda o, k: o * k * 0.8203125
+    D = 2 * cfg.gdn_k_heads * 128 + cfg.gdn_v_heads * 128
+    VD, QD, KVD = cfg.gdn_v_heads * 128, cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    n_lin = sum(1 for i in range(cfg.n_layers) if (i + 1) % cfg.full_attn_interval)
+    n_att = cfg.n_layers - n_lin
+    gdn = a8(D, H) + a8(VD, H) + a8(H, VD) + 2 * cfg.gdn_v_heads * H * 2 + D * 4 * 2
+    state = cfg.gdn_v_heads * 128 * 128 * 4 * (1 + T)
+    att = a8(2 * QD, H) + 2 * a8(KVD, H) + a8(H, QD)
+    expert = 2 * q4(cfg.expert_inter, H) + q6(H, cfg.expert_inter)
+    k, E = cfg.top_k, cfg.n_experts
+    distinct = E * (1.0 - (1.0 - k / E) ** T)  # expected distinct routed experts for T rows
+    moe = a8(E, H) + distinct * expert + 2 * q4(cfg.shared_inter, H) + q6(H, cfg.shared_inter) + a8(1, H)
+    head = a8(V, H)
+    return n_lin * (gdn + state) + n_att * att + cfg.n_layers * moe + head
+
+
+def draft_bytes(cfg, head_rows):
+    H = cfg.hidden
+    QD, KVD = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    bf = lambda o, k: o * k * 2.0
+    expert = 3 * bf(cfg.expert_inter, H)
+    return (bf(H, 2 * H) + bf(2 * QD, H) + 2 * bf(KVD, H) + bf(H, QD) + bf(cfg.n_experts, H)
+            + (cfg.top_k + 1) * expert + head_rows * H * 1.0625)
+
+
+def cpu_arm(pkg, ctx, max_seconds=25.0):
+    """The reference's scalar CPU path (the C restatement under oracle/) timed on
+    this host.  Sample: one 3:1 period of the stack (4 of 40 layers, real layer
+    sizes) plus the MTP head and the full lm_head, MTP depth-1 cycles with the
+    same forced-draft rule; the per-cycle layer time is scaled by 10 to the 40
+    layers."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import orn_oracle as orc
+
+    cfg4 = pkg.qwen35_config(max_ctx=128, n_layers=4)
+    gm = pkg.TextModel(ctx, cfg4)
+    gm.init_random(SEED)
+    gm.make_cache().free()  # resolves the weight table
+    om = orc.export_gpu_model(gm)
+    gm.free()
+    threads = os.cpu_count() or 1
+    rng = np.random.default_rng(SEED)
+    ids = rng.integers(0, cfg4.vocab, 2).astype(np.uint32)
+    cache = om.new_cache()
+    om.forward(cache, ids[:1])  # warm
+    t_layers, t_head, n = 0.0, 0.0, 0
+    t_start = time.perf_counter()
+    while n < 3 or (time.perf_counter() - t_start < max_seconds and n < 12):
+        t0 = time.perf_counter()
+        h = om.forward(cache, ids)                      # a 2-row verify window through 4 layers
+        t1 = time.perf_counter()
+        om.head_greedy(h, 2)                            # lm_head + greedy for both rows
+        t2 = time.perf_counter()
+        t_layers += t1 - t0
+        t_head += t2 - t1
+        n += 1
+    om.free_cache(cache)
+    om.free()
+    verify_s = 10.0 * t_layers / n + t_head / n
+    # draft level: MTP head is one attention layer with bf16 weights + lm_head row: bounded by head time / 2
+    draft_s = t_head / n / 2 + (t_layers / n) / 4
+    tok_per_cycle = 1.0 + FORCE_P
+    value = tok_per_cycle / (verify_s + draft_s)
+    return {"value": value, "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": "%d verify windows (T=2) through 4 of 40 layers + full lm_head on the C oracle with "
+                      "OpenMP over rows; layer time x10, draft level estimated from the same parts; "
+                      "%.1f s of CPU work" % (n, time.perf_counter() - t_start)}
+
+
+def kernel_roofline(pkg, ctx, model, cfg, iters=20):
+    """The dominant kernel: the affine-8 dequant mat-vec at verify width 2 on the
+    [8192, 2048] gated-delta input projections, cycling through the 30 layers'
+    matrices (535 MB > L2) so that every launch reads from HBM."""
+    names = ["layers.%d.linear_attn.in_proj_qkv" % i for i in range(cfg.n_layers)
+             if (i + 1) % cfg.full_attn_interval]
+    lins = [model.get_linear(n) for n in names]
+    rng = np.random.default_rng(1)
+    x = ctx.upload((rng.standard_normal((2, cfg.hidden)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16))
+    y = ctx.empty((2, lins[0].O), np.uint16)
+    lib = ctx._lib
+    for L in lins:  # warm-up
+        lib.orn_gemv(ctx.h, L.h, x.ptr, 2, y.ptr, 0)
+    ctx.timer_start()
+    n = 0
+    for _ in range(iters):
+        for L in lins:
+            lib.orn_gemv(ctx.h, L.h, x.ptr, 2, y.ptr, 0)
+            n += 1
+    ms = ctx.timer_stop()
+    per = ms / n
+    alg = lins[0].O * lins[0].K * 1.0625 + 2 * lins[0].K * 2 + 2 * lins[0].O * 2
+    peak, which = peaks()
+    ach = alg / (per * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "gemv_kernel<A8, M=2> [8192x2048]", "achieved": ach, "peak": peak,
+            "peak_source": which, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+            "launch_us": per * 1e3, "algorithmic_bytes": alg}
+
+
+def ours(args):
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = load_pkg()
+    ctx = pkg.Context(local)
+    cfg = pkg.qwen35_config(max_ctx=512)
+    model = pkg.TextModel(ctx, cfg)
+    model.init_random(SEED)
+    cache = model.make_cache()
+    rng = np.random.default_rng(SEED + rank)
+    prompt = rng.integers(0, cfg.vocab, PROMPT_LEN).astype(np.uint32)
+    # the non-speculative stream: the target the forced drafts come from, and the parity check
+    ar = pkg.generate_step(model, cache, prompt, GEN_TOKENS)
+    ar_prof = model.prof()
+
+    def one():
+        cache.reset()
+        t0 = time.perf_counter()
+        toks, st = pkg.generate_step_mtp(model, cache, prompt, 1, GEN_TOKENS, force=(ar, FORCE_P, SEED))
+        wall = time.perf_counter() - t0
+        return toks, st, model.prof(), wall
+
+    for _ in range(args.warmup):
+        toks, st, _, _ = one()
+        assert toks == ar, "speculative output differs from the autoregressive output"
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            import torch
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    dev_ms, walls, launches, cycles, accepted = 0.0, 0.0, 0, 0, 0
+    for _ in range(args.steps):
+        toks, st, prof, wall = one()
+        dev_ms += prof.total_ms
+        walls += wall
+        launches += prof.kernel_launches
+        cycles += st.cycles
+        accepted += st.accepted
+    barrier()
+    clocks = sampler.stop()
+    assert toks == ar
+
+    if dist is not None:
+        import torch
+        t = torch.tensor([dev_ms, walls], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, walls = t.tolist()
+    total_tokens = world * args.steps * GEN_TOKENS
+    value = total_tokens / (dev_ms * 1e-3)
+    e2e = total_tokens / walls
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    roof = kernel_roofline(pkg, ctx, model, cfg)
+    peak, which = peaks()
+    vb, db = step_bytes(cfg, 2), draft_bytes(cfg, cfg.vocab)
+    cyc_s = dev_ms * 1e-3 / max(cycles, 1)
+    step_roof = {"bytes_per_cycle": vb + db, "verify_bytes": vb, "draft_bytes": db,
+                 "cycle_ms": cyc_s * 1e3, "achieved_gbs": (vb + db) / cyc_s / 1e9,
+                 "frac": (vb + db) / cyc_s / 1e9 / peak, "peak_source": which,
+                 "ar_ms_per_token": ar_prof.total_ms / GEN_TOKENS,
+                 "ar_frac": step_bytes(cfg, 1) / (ar_prof.total_ms * 1e-3 / GEN_TOKENS) / 1e9 / peak}
+    cache.free()
+    model.free()
+    line = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations, f32 accumulate",
+        "data": "synthetic (random-init weights, random prompt ids)",
+        "config": {"workload": "BASELINE config 4: 40-layer 35B-A3B, Q4_K/Q6_K experts + affine-8 dense + bf16 MTP head, "
+                               "51-token prompt, 200 greedy tokens, MTP depth 1, forced-draft p=%.2f" % FORCE_P,
+                   "l2_policy": "weights read per step (2.7 GB) exceed L2 (126 MB)", "parallelism": "replica per GPU"},
+        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": PROMPT_LEN * 4,
+                "d2h_bytes_per_step": int(16 * cycles / args.steps) + 4},
+        "gpu_launches": launches, "clocks": clocks, "roofline": roof, "step_roofline": step_roof,
+        "acceptance": accepted / max(cycles, 1), "tokens_per_cycle": args.steps * GEN_TOKENS / max(cycles, 1),
+        "mtp_equals_autoregressive": True,
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_arm(pkg, ctx)
+    print(json.dumps(line))
+    ctx.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def reference(args):
+    """The reference's own CPU statement of the path (its Metal path cannot run
+    on Linux): the C restatement under oracle/, all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    pkg = load_pkg()
+    try:
+        ctx = pkg.Context(0)
+    except Exception as e:  # the weights of the sample are generated on the GPU
+        print(json.dumps({"impl": "reference", "unavailable": "no CUDA device to generate the sample weights: %s" % e}))
+        return
+    cb = cpu_arm(pkg, ctx, max_seconds=max(10.0, 8.0 * args.steps))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": GEN_TOKENS / cb["value"] * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 activations, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "BASELINE config 4 (bounded sample, see cpu_baseline.sample)"},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+    ctx.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference(args)
+    else:
+        ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -72,6 +72,11 @@ int32_t orn_memset(orn_ctx* ctx, void* dev, int32_t byte, size_t nbytes);
 int32_t orn_upload(orn_ctx* ctx, void* dev, const void* host, size_t nbytes);   /* Array::from_slice */
 int32_t orn_download(orn_ctx* ctx, void* host, const void* dev, size_t nbytes); /* Array::to_vec (syncs) */
 
+/* device-side stopwatch on the context's stream (CUDA events; the reference's
+ * ORNITH_PROF GPUStart/GPUEnd sums, src/metal/mod.rs:197-284) */
+int32_t orn_timer_start(orn_ctx* ctx);
+int32_t orn_timer_stop(orn_ctx* ctx, float* ms_out); /* synchronises */
+
 /* ---- weights: replaces KMatrix / QuantMatrix / dense Array (src/ops/kquant.rs:349-411,
  * src/weights.rs:132-279).  Tensors are in the artifact's layout:
  *   Q4_K: w = qs bytes [E,O,K/2], s = scales u8 [E,O,K/256,12], b = dm f16 [E,O,K/256,2]
@@ -92,6 +97,7 @@ int32_t orn_linear_create_random(orn_ctx* ctx, int32_t kind, int32_t E, int32_t 
 int32_t orn_linear_export(orn_ctx* ctx, const orn_linear* lin, void* host_w, void* host_s,
                           void* host_b);
 int32_t orn_linear_sizes(const orn_linear* lin, size_t* w_bytes, size_t* s_bytes, size_t* b_bytes);
+int32_t orn_linear_info(const orn_linear* lin, int32_t* kind, int32_t* E, int32_t* O, int32_t* K);
 int32_t orn_linear_destroy(orn_ctx* ctx, orn_linear* lin);
 /* FrSpec::prune (src/frspec.rs:115-135): row gather of every head tensor */
 int32_t orn_linear_gather_rows(orn_ctx* ctx, const orn_linear* lin, const uint32_t* host_ids,

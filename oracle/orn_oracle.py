@@ -325,3 +325,43 @@ class Model:
         if self.h:
             lib().orc_model_free(self.h)
             self.h = None
+
+
+def model_weight_names(cfg):
+    """(linears, tensors): every weight name of a model with this config."""
+    lin, ten = ["embed_tokens", "lm_head"], ["norm.weight"]
+    moe = ["gate", "switch_mlp.gate_proj", "switch_mlp.up_proj", "switch_mlp.down_proj",
+           "shared_expert.gate_proj", "shared_expert.up_proj", "shared_expert.down_proj", "shared_expert_gate"]
+    for i in range(cfg.n_layers):
+        lp = "layers.%d." % i
+        ten += [lp + "input_layernorm.weight", lp + "post_attention_layernorm.weight"]
+        if (i + 1) % cfg.full_attn_interval != 0:
+            a = lp + "linear_attn."
+            lin += [a + n for n in ("in_proj_qkv", "in_proj_z", "in_proj_a.weight", "in_proj_b.weight", "out_proj")]
+            ten += [a + n for n in ("conv1d.weight", "dt_bias", "A_log", "norm.weight")]
+        else:
+            a = lp + "self_attn."
+            lin += [a + n for n in ("q_proj", "k_proj", "v_proj", "o_proj")]
+            ten += [a + "q_norm.weight", a + "k_norm.weight"]
+        lin += [lp + "mlp." + n for n in moe]
+    lp = "mtp.layers.0."
+    ten += ["mtp.pre_fc_norm_embedding.weight", "mtp.pre_fc_norm_hidden.weight", "mtp.norm.weight",
+            lp + "input_layernorm.weight", lp + "post_attention_layernorm.weight",
+            lp + "self_attn.q_norm.weight", lp + "self_attn.k_norm.weight"]
+    lin += ["mtp.fc.weight"] + [lp + "self_attn.%s_proj.weight" % c for c in "qkvo"] + [lp + "mlp." + n for n in moe]
+    return lin, ten
+
+
+def export_gpu_model(gpu_model):
+    """Download every weight of a CUDA-side model into an oracle Model (the same
+    bytes on both sides)."""
+    cfg = gpu_model.cfg
+    lins, tens = model_weight_names(cfg)
+    W = {}
+    for n in lins:
+        L = gpu_model.get_linear(n)
+        w, s, b = L.export()
+        W[n] = Weights(L.kind, L.E, L.O, L.K, w, s if s.size else None, b if b.size else None)
+    for n in tens:
+        W[n] = gpu_model.get_tensor(n)
+    return Model(cfg, W)

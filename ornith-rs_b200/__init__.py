@@ -89,6 +89,14 @@ class Context:
             self.check(self._lib.orn_upload(self.h, b.ptr, arr.ctypes.data, arr.nbytes), "orn_upload")
         return b
 
+    def timer_start(self):
+        self.check(self._lib.orn_timer_start(self.h), "orn_timer_start")
+
+    def timer_stop(self):
+        ms = C.c_float()
+        self.check(self._lib.orn_timer_stop(self.h, C.byref(ms)), "orn_timer_stop")
+        return ms.value
+
     def close(self):
         if self.h:
             self._lib.orn_ctx_destroy(self.h)
@@ -235,9 +243,9 @@ class TextModel:
     def get_linear(self, name):
         h = C.c_void_p()
         self.ctx.check(self.ctx._lib.orn_model_get_linear(self.h, name.encode(), C.byref(h)), "orn_model_get_linear")
-        a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
-        self.ctx._lib.orn_linear_sizes(h, C.byref(a), C.byref(b), C.byref(c))
-        return Linear(self.ctx, h, -1, 0, 0, 0, owned=False)
+        k, e, o, kk = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
+        self.ctx._lib.orn_linear_info(h, C.byref(k), C.byref(e), C.byref(o), C.byref(kk))
+        return Linear(self.ctx, h, k.value, e.value, o.value, kk.value, owned=False)
 
     def get_tensor(self, name):
         p, n = C.c_void_p(), C.c_size_t()

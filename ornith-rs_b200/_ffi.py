@@ -67,6 +67,9 @@ SIGNATURES = {
     "orn_linear_create_random": (i32, [vp, i32, i32, i32, i32, u64, f32, c_void_pp]),
     "orn_linear_export": (i32, [vp, vp, vp, vp, vp]),
     "orn_linear_sizes": (i32, [vp, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]),
+    "orn_linear_info": (i32, [vp] + [C.POINTER(i32)] * 4),
+    "orn_timer_start": (i32, [vp]),
+    "orn_timer_stop": (i32, [vp, C.POINTER(f32)]),
     "orn_linear_destroy": (i32, [vp, vp]),
     "orn_linear_gather_rows": (i32, [vp, vp, vp, i32, c_void_pp]),
     "orn_kq_dequantize": (i32, [vp, vp, i32, vp]),

@@ -38,6 +38,8 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
   if (!ctx) return ORN_ERR_ARG;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->t0) cudaEventDestroy(ctx->t0);
+  if (ctx->t1) cudaEventDestroy(ctx->t1);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return ORN_OK;
@@ -46,6 +48,24 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
 int32_t orn_sync(orn_ctx* ctx) {
   if (!ctx) return ORN_ERR_ARG;
   ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return ORN_OK;
+}
+
+int32_t orn_timer_start(orn_ctx* ctx) {
+  if (!ctx) return ORN_ERR_ARG;
+  if (!ctx->t0) {
+    ORN_CHECK_CUDA(ctx, cudaEventCreate(&ctx->t0));
+    ORN_CHECK_CUDA(ctx, cudaEventCreate(&ctx->t1));
+  }
+  ORN_CHECK_CUDA(ctx, cudaEventRecord(ctx->t0, ctx->stream));
+  return ORN_OK;
+}
+
+int32_t orn_timer_stop(orn_ctx* ctx, float* ms_out) {
+  if (!ctx || !ms_out || !ctx->t0) return ORN_ERR_ARG;
+  ORN_CHECK_CUDA(ctx, cudaEventRecord(ctx->t1, ctx->stream));
+  ORN_CHECK_CUDA(ctx, cudaEventSynchronize(ctx->t1));
+  ORN_CHECK_CUDA(ctx, cudaEventElapsedTime(ms_out, ctx->t0, ctx->t1));
   return ORN_OK;
 }
 
@@ -176,6 +196,12 @@ int32_t orn_linear_create_random(orn_ctx* ctx, int32_t kind, int32_t E, int32_t 
 int32_t orn_linear_sizes(const orn_linear* lin, size_t* w, size_t* s, size_t* b) {
   if (!lin || !w || !s || !b) return ORN_ERR_ARG;
   linear_artifact_sizes(lin->kind, lin->E, lin->O, lin->K, w, s, b);
+  return ORN_OK;
+}
+
+int32_t orn_linear_info(const orn_linear* lin, int32_t* kind, int32_t* E, int32_t* O, int32_t* K) {
+  if (!lin || !kind || !E || !O || !K) return ORN_ERR_ARG;
+  *kind = lin->kind; *E = lin->E; *O = lin->O; *K = lin->K;
   return ORN_OK;
 }
 

@@ -17,6 +17,7 @@ struct orn_ctx {
   std::string err;
   int64_t launches = 0;  // kernels launched through this context
   int sm_count = 148;
+  cudaEvent_t t0 = nullptr, t1 = nullptr;  // orn_timer_start / orn_timer_stop
 };
 
 // Device-resident weight matrix [E, O, K].
