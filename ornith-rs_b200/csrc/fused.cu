@@ -1,0 +1,1143 @@
+// Persistent fused kernels of the decode step.
+//
+// A decode step at batch 1 reads ~2.7 GB of weights through ~240 dependent
+// stages of a few microseconds each, so the step is organised as six kernels
+// per layer, each a grid of (SM count x k) CTAs that
+//   1. rebuilds its small input redundantly per CTA in shared memory (residual
+//      add, RMS norm, gated norm, router softmax + top-k, SwiGLU inputs ...),
+//   2. streams its share of weight rows with 128-bit coalesced loads, dequantises
+//      in registers against the staged activations and folds with warp shuffles,
+//   3. applies the elementwise tail in the epilogue (bf16 store, SwiGLU, the MoE
+//      combine).
+// The arithmetic of every stage is the arithmetic of the stand-alone kernels in
+// linear.cu / ops.cu / gdn.cu / attn.cu (same rounding points, same reduction
+// orders), which is what the parity tests hold both paths to.
+//
+// Reference functions covered: Linear::matmul / gather_matmul
+// (src/ops/linear.rs:23-144), add_rms_norm / rms_norm_gated (src/ops/norm.rs),
+// sparse_moe_block (src/ops/moe.rs:662-741), gdn_front + gated_delta_kernel
+// (src/ops/gdn.rs:191-413), Attention::forward (src/model/qwen3_5.rs:430-474).
+#include "orn_internal.h"
+#include "orn_quant.cuh"
+#include "fused.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int SB = 4;  // row steps whose loads are issued together
+
+// ---------------------------------------------------------------------------
+// activation staging: a row of K floats re-ordered so that lane l's pieces of
+// unit (l + 32 s) are 16-byte neighbours of lane l+1's: conflict-free LDS.128
+// ---------------------------------------------------------------------------
+template <int KIND> struct Lay;
+template <> struct Lay<ORN_A8>   { static constexpr int P = 4, WPU = 16, NS = 1; };
+template <> struct Lay<ORN_Q4K>  { static constexpr int P = 8, WPU = 32, NS = 2; };
+template <> struct Lay<ORN_Q6K>  { static constexpr int P = 4, WPU = 16, NS = 0; };
+template <> struct Lay<ORN_BF16> { static constexpr int P = 2, WPU = 8,  NS = 0; };
+
+template <int KIND> ORN_D int src_index(int u, int p);
+template <> ORN_D int src_index<ORN_A8>(int u, int p) { return 16 * u + 4 * p; }
+template <> ORN_D int src_index<ORN_Q4K>(int u, int p) {
+  int base = (u >> 3) * 256 + 64 * ((u & 7) >> 1) + 16 * (u & 1);
+  return p < 4 ? base + 4 * p : base + 32 + 4 * (p - 4);
+}
+template <> ORN_D int src_index<ORN_Q6K>(int u, int p) {
+  return (u >> 4) * 256 + 128 * ((u & 15) >> 3) + 4 * (u & 7) + 32 * p;
+}
+template <> ORN_D int src_index<ORN_BF16>(int u, int p) { return 8 * u + 4 * p; }
+
+struct XStage {
+  float* xs;    // [rows][S][P][32] float4
+  float* sums;  // [rows][units][NS]
+  int units, S, rows;
+};
+
+__host__ __device__ inline int kind_wpu(int kind) { return kind == ORN_Q4K ? 32 : kind == ORN_BF16 ? 8 : 16; }
+__host__ __device__ inline int kind_p(int kind) { return kind == ORN_Q4K ? 8 : kind == ORN_BF16 ? 2 : 4; }
+__host__ __device__ inline int kind_ns(int kind) { return kind == ORN_A8 ? 1 : kind == ORN_Q4K ? 2 : 0; }
+__host__ __device__ inline size_t stage_floats(int kind, int rows, int K) {
+  int units = K / kind_wpu(kind);
+  int S = (units + 31) / 32;
+  return (size_t)rows * S * kind_p(kind) * 32 * 4 + (size_t)rows * units * kind_ns(kind);
+}
+
+// carve a stage out of shared memory (returns the next free float)
+ORN_D float* stage_carve(float* base, int kind, int rows, int K, XStage& X) {
+  X.units = K / kind_wpu(kind);
+  X.S = (X.units + 31) / 32;
+  X.rows = rows;
+  X.xs = base;
+  X.sums = base + (size_t)rows * X.S * kind_p(kind) * 32 * 4;
+  return X.sums + (size_t)rows * X.units * kind_ns(kind);
+}
+
+// lin: [rows][K] floats (row stride `stride`) -> stage; block-wide, no sync inside
+template <int KIND>
+ORN_D void stage_fill(const float* lin, int stride, const XStage& X) {
+  constexpr int P = Lay<KIND>::P;
+  const int total = X.rows * X.S * P * 32;
+  for (int slot = threadIdx.x; slot < total; slot += blockDim.x) {
+    const int lane = slot & 31;
+    const int p = (slot >> 5) % P;
+    const int s = (slot / (32 * P)) % X.S;
+    const int m = slot / (32 * P * X.S);
+    const int u = lane + 32 * s;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (u < X.units) v = *reinterpret_cast<const float4*>(lin + (size_t)m * stride + src_index<KIND>(u, p));
+    reinterpret_cast<float4*>(X.xs)[slot] = v;
+  }
+  if (Lay<KIND>::NS == 1) {
+    for (int i = threadIdx.x; i < X.rows * X.units; i += blockDim.x) {
+      const int m = i / X.units, u = i - m * X.units;
+      const float* src = lin + (size_t)m * stride + 16 * u;
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) s = s + src[k];
+      X.sums[i] = s;
+    }
+  } else if (Lay<KIND>::NS == 2) {
+    for (int i = threadIdx.x; i < X.rows * X.units; i += blockDim.x) {
+      const int m = i / X.units, u = i - m * X.units;
+      const float* src = lin + (size_t)m * stride + src_index<ORN_Q4K>(u, 0);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) { s0 = s0 + src[k]; s1 = s1 + src[32 + k]; }
+      X.sums[2 * i] = s0;
+      X.sums[2 * i + 1] = s1;
+    }
+  }
+}
+ORN_D void stage_fill_kind(int kind, const float* lin, int stride, const XStage& X) {
+  switch (kind) {
+    case ORN_A8: stage_fill<ORN_A8>(lin, stride, X); break;
+    case ORN_Q4K: stage_fill<ORN_Q4K>(lin, stride, X); break;
+    case ORN_Q6K: stage_fill<ORN_Q6K>(lin, stride, X); break;
+    default: stage_fill<ORN_BF16>(lin, stride, X); break;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// weight units (the arithmetic of linear.cu's Fmt<>, activations from registers)
+// ---------------------------------------------------------------------------
+template <int KIND> struct WU;
+
+template <> struct WU<ORN_A8> {
+  struct W { uint4 q; uint32_t sb; };
+  ORN_D static void load(const LinDev& L, int64_t row, int u, W& w) {
+    w.q = ldg128_stream(L.w + row * L.K + 16 * u);
+    w.sb = __ldg(reinterpret_cast<const uint32_t*>(L.s) + row * (L.K >> 6) + (u >> 2));
+  }
+  ORN_D static float fold(const W& w, const float* x, const float* sm, int, float acc) {
+    const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
+    float s1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      s1 = fmaf(x[4 * k + 0], byte_f<0>(qw[k]), s1);
+      s1 = fmaf(x[4 * k + 1], byte_f<1>(qw[k]), s1);
+      s1 = fmaf(x[4 * k + 2], byte_f<2>(qw[k]), s1);
+      s1 = fmaf(x[4 * k + 3], byte_f<3>(qw[k]), s1);
+    }
+    acc = fmaf(bf_lo(w.sb), s1, acc);
+    acc = fmaf(bf_hi(w.sb), sm[0], acc);
+    return acc;
+  }
+};
+
+template <> struct WU<ORN_Q4K> {
+  struct W { uint4 q; uint4 meta; };
+  ORN_D static void load(const LinDev& L, int64_t row, int u, W& w) {
+    const int nb = L.K >> 8;
+    w.q = ldg128_stream(L.w + (row * nb + (u >> 3)) * 128 + 16 * (u & 7));
+    w.meta = ldg128(L.s + (row * nb + (u >> 3)) * 16);
+  }
+  ORN_D static float fold(const W& w, const float* x, const float* sm, int u, float acc) {
+    const int g = (u & 7) >> 1;
+    const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
+    float lo = 0.f, hi = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t l4 = qw[k] & 0x0F0F0F0Fu, h4 = (qw[k] >> 4) & 0x0F0F0F0Fu;
+      lo = fmaf(x[4 * k + 0], byte_f<0>(l4), lo);
+      lo = fmaf(x[4 * k + 1], byte_f<1>(l4), lo);
+      lo = fmaf(x[4 * k + 2], byte_f<2>(l4), lo);
+      lo = fmaf(x[4 * k + 3], byte_f<3>(l4), lo);
+      hi = fmaf(x[16 + 4 * k + 0], byte_f<0>(h4), hi);
+      hi = fmaf(x[16 + 4 * k + 1], byte_f<1>(h4), hi);
+      hi = fmaf(x[16 + 4 * k + 2], byte_f<2>(h4), hi);
+      hi = fmaf(x[16 + 4 * k + 3], byte_f<3>(h4), hi);
+    }
+    const float d = h2f((uint16_t)(w.meta.x & 0xffff)), dmin = h2f((uint16_t)(w.meta.x >> 16));
+    float s1, m1, s2, m2;
+    q4k_scale_min(2 * g, w.meta.y, w.meta.z, w.meta.w, &s1, &m1);
+    q4k_scale_min(2 * g + 1, w.meta.y, w.meta.z, w.meta.w, &s2, &m2);
+    float t = s1 * lo;
+    t = fmaf(s2, hi, t);
+    float mt = m1 * sm[0];
+    mt = fmaf(m2, sm[1], mt);
+    acc = fmaf(d, t, acc);
+    acc = fmaf(-dmin, mt, acc);
+    return acc;
+  }
+};
+
+template <> struct WU<ORN_Q6K> {
+  struct W { uint32_t qa, qb, qh, sc4; float d; };
+  ORN_D static void load(const LinDev& L, int64_t row, int u, W& w) {
+    const int nb = L.K >> 8;
+    const int blk = u >> 4, j = u & 15, half = j >> 3, l0 = 4 * (j & 7);
+    const uint8_t* base = L.w + (row * nb + blk) * 192;
+    w.qa = ldg32_stream(base + 64 * half + l0);
+    w.qb = ldg32_stream(base + 64 * half + 32 + l0);
+    w.qh = ldg32_stream(base + 128 + 32 * half + l0);
+    const uint2 s8 = __ldg(reinterpret_cast<const uint2*>(L.s + (row * nb + blk) * 16 + 8 * half));
+    const int is = l0 >> 4;
+    const uint32_t lo = s8.x >> (8 * is), hi = s8.y >> (8 * is);
+    w.sc4 = (lo & 0xff) | (((lo >> 16) & 0xff) << 8) | ((hi & 0xff) << 16) | (((hi >> 16) & 0xff) << 24);
+    w.d = h2f(__ldg(reinterpret_cast<const uint16_t*>(L.b) + row * nb + blk));
+  }
+  ORN_D static float fold(const W& w, const float* x, const float*, int, float acc) {
+    const uint32_t q1 = (w.qa & 0x0F0F0F0Fu) | ((w.qh & 0x03030303u) << 4);
+    const uint32_t q2 = (w.qb & 0x0F0F0F0Fu) | ((w.qh & 0x0C0C0C0Cu) << 2);
+    const uint32_t q3 = ((w.qa >> 4) & 0x0F0F0F0Fu) | (w.qh & 0x30303030u);
+    const uint32_t q4 = ((w.qb >> 4) & 0x0F0F0F0Fu) | ((w.qh & 0xC0C0C0C0u) >> 2);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    s0 = fmaf(x[0], byte_m32_f<0>(q1), s0); s0 = fmaf(x[1], byte_m32_f<1>(q1), s0);
+    s0 = fmaf(x[2], byte_m32_f<2>(q1), s0); s0 = fmaf(x[3], byte_m32_f<3>(q1), s0);
+    s1 = fmaf(x[4], byte_m32_f<0>(q2), s1); s1 = fmaf(x[5], byte_m32_f<1>(q2), s1);
+    s1 = fmaf(x[6], byte_m32_f<2>(q2), s1); s1 = fmaf(x[7], byte_m32_f<3>(q2), s1);
+    s2 = fmaf(x[8], byte_m32_f<0>(q3), s2); s2 = fmaf(x[9], byte_m32_f<1>(q3), s2);
+    s2 = fmaf(x[10], byte_m32_f<2>(q3), s2); s2 = fmaf(x[11], byte_m32_f<3>(q3), s2);
+    s3 = fmaf(x[12], byte_m32_f<0>(q4), s3); s3 = fmaf(x[13], byte_m32_f<1>(q4), s3);
+    s3 = fmaf(x[14], byte_m32_f<2>(q4), s3); s3 = fmaf(x[15], byte_m32_f<3>(q4), s3);
+    const float c0 = (float)(int8_t)(w.sc4 & 0xff), c1 = (float)(int8_t)((w.sc4 >> 8) & 0xff);
+    const float c2 = (float)(int8_t)((w.sc4 >> 16) & 0xff), c3 = (float)(int8_t)(w.sc4 >> 24);
+    float t = c0 * s0;
+    t = fmaf(c1, s1, t);
+    t = fmaf(c2, s2, t);
+    t = fmaf(c3, s3, t);
+    return fmaf(w.d, t, acc);
+  }
+};
+
+template <> struct WU<ORN_BF16> {
+  struct W { uint4 q; };
+  ORN_D static void load(const LinDev& L, int64_t row, int u, W& w) {
+    w.q = ldg128_stream(L.w + (row * L.K + 8 * u) * 2);
+  }
+  ORN_D static float fold(const W& w, const float* x, const float*, int, float acc) {
+    float f[8];
+    widen8(w.q, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = fmaf(x[i], f[i], acc);
+    return acc;
+  }
+};
+
+// One warp: dots of R weight rows (rowbase .. rowbase+R-1, `nvalid` of them
+// real) against M staged activation rows m0 .. m0+M-1.  Lane partials in
+// ascending unit order, then the xor-16..1 butterfly.
+template <int KIND, int M, int R>
+ORN_D void warp_rows_dot(const LinDev& L, int64_t rowbase, int nvalid, const XStage& X, int m0, int lane,
+                         float (&acc)[R][M]) {
+  using U = WU<KIND>;
+  constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+  for (int s0 = 0; s0 < X.S; s0 += SB) {
+    typename U::W w[SB][R];
+#pragma unroll
+    for (int sb = 0; sb < SB; ++sb) {
+      const int u = lane + 32 * (s0 + sb);
+      if (u < X.units) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          if (r < nvalid) U::load(L, rowbase + r, u, w[sb][r]);
+      }
+    }
+#pragma unroll
+    for (int sb = 0; sb < SB; ++sb) {
+      const int s = s0 + sb;
+      const int u = lane + 32 * s;
+      if (u < X.units) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          float xv[P * 4];
+          const float4* xp = reinterpret_cast<const float4*>(X.xs) + ((size_t)((m0 + m) * X.S + s) * P) * 32 + lane;
+#pragma unroll
+          for (int p = 0; p < P; ++p) {
+            const float4 v = xp[p * 32];
+            xv[4 * p] = v.x; xv[4 * p + 1] = v.y; xv[4 * p + 2] = v.z; xv[4 * p + 3] = v.w;
+          }
+          float sm[NS > 0 ? NS : 1];
+#pragma unroll
+          for (int i = 0; i < NS; ++i) sm[i] = X.sums[((size_t)(m0 + m) * X.units + u) * NS + i];
+#pragma unroll
+          for (int r = 0; r < R; ++r)
+            if (r < nvalid) acc[r][m] = U::fold(w[sb][r], xv, sm, u, acc[r][m]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+}
+
+// ---------------------------------------------------------------------------
+// block-wide RMS statistics in the order of the stand-alone rms kernels:
+// virtual thread t owns elements 4t..4t+3, 32 virtual threads fold by
+// butterfly, the warp sums (zero padded to 32) fold by butterfly again.
+// lin holds `rows` rows of n raw values (stride `stride`); inv[m] receives
+// 1/sqrt(sumsq/n + eps).  `red` is rows*32 floats of shared memory.
+// ---------------------------------------------------------------------------
+ORN_D void block_rms_inv(const float* lin, int stride, int rows, int n, float eps, float* red, float* inv) {
+  const int lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < rows * 32; i += blockDim.x) red[i] = 0.f;
+  __syncthreads();
+  const int nvt = (n + 3) / 4;
+  const int nvt_pad = ((nvt + 31) / 32) * 32;
+  for (int m = 0; m < rows; ++m) {
+    for (int vt = threadIdx.x; vt < nvt_pad; vt += blockDim.x) {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = 4 * vt + i;
+        if (idx < n) {
+          const float v = lin[(size_t)m * stride + idx];
+          acc = fmaf(v, v, acc);
+        }
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) red[m * 32 + (vt >> 5)] = acc;
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  for (int m = warp; m < rows; m += (blockDim.x >> 5)) {
+    const float total = warp_sum(red[m * 32 + lane]);
+    if (lane == 0) inv[m] = orn_rsqrtf(total / (float)n + eps);
+  }
+  __syncthreads();
+}
+
+// ---------------------------------------------------------------------------
+// prologues: build lin[M][K] (floats holding bfloat16 values) in shared memory
+// ---------------------------------------------------------------------------
+struct Prologue {
+  int mode;            // PRO_*
+  int K;               // length of the staged row
+  const bf16_t* a;     // ADDNORM: [M][K] ; PLAIN: [M][K] ; GATED: y [M][K] ; MTPJOIN: trunk hidden [M][K/2]
+  const bf16_t* b;     // ADDNORM: second addend or null ; GATED: z [M][K]
+  const bf16_t* w;     // norm weight ([K], GATED: [128], MTPJOIN: pre_fc_norm_embedding [K/2])
+  const bf16_t* w2;    // MTPJOIN: pre_fc_norm_hidden
+  bf16_t* sum_out;     // ADDNORM: where CTA 0 stores bf(a+b) (may be null)
+  bf16_t* norm_out;    // where CTA 0 stores the staged row as bfloat16 (may be null)
+  LinDev emb;          // MTPJOIN: embedding table
+  const uint32_t* ids; // MTPJOIN: token ids [M]
+  float eps;
+};
+
+// scratch: red[M*32 + M] floats
+template <int M>
+ORN_D void run_prologue(const Prologue& P, float* lin, float* red) {
+  const int K = P.K;
+  float* inv = red + M * 32;
+  if (P.mode == PRO_ADDNORM) {
+    for (int i = threadIdx.x; i < M * K; i += blockDim.x) {
+      float v = bf2f(P.a[i]);
+      if (P.b != nullptr) v = bfr(v + bf2f(P.b[i]));
+      lin[i] = v;
+      if (P.sum_out != nullptr && blockIdx.x == 0) P.sum_out[i] = f2bf(v);
+    }
+    __syncthreads();
+    block_rms_inv(lin, K, M, K, P.eps, red, inv);
+    for (int i = threadIdx.x; i < M * K; i += blockDim.x) {
+      const int m = i / K, c = i - m * K;
+      lin[i] = bfr(bf2f(P.w[c]) * bfr(lin[i] * inv[m]));
+    }
+  } else if (P.mode == PRO_PLAIN) {
+    for (int i = threadIdx.x; i < M * K; i += blockDim.x) lin[i] = bf2f(P.a[i]);
+  } else if (P.mode == PRO_GATED) {
+    // rms_norm_gated over 128-wide heads (kernels/ornith_norm.metal:119-185)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int heads = K / 128;
+    for (int pair = warp; pair < M * heads; pair += kWarps) {
+      const int base = pair * 128 + 4 * lane;
+      float xv[4];
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { xv[i] = bf2f(P.a[base + i]); acc = fmaf(xv[i], xv[i], acc); }
+      acc = warp_sum(acc);
+      const float iv = orn_rsqrtf(acc / 128.0f + P.eps);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float normed = bfr(bf2f(P.w[4 * lane + i]) * bfr(xv[i] * iv));
+        float g = bf2f(P.b[base + i]);
+        g = g * orn_sigmoid_f32(g);
+        lin[base + i] = bfr(g * normed);
+      }
+    }
+  } else {  // PRO_MTPJOIN: [norm(embed(id)) | norm(trunk hidden)] (src/model/mtp.rs:179-187)
+    const int H = K / 2;
+    for (int i = threadIdx.x; i < M * H; i += blockDim.x) {
+      const int m = i / H, c = i - m * H;
+      const int64_t row = P.ids[m];
+      const uint32_t sb = reinterpret_cast<const uint32_t*>(P.emb.s)[row * (H >> 6) + (c >> 6)];
+      lin[(size_t)m * K + c] = bfr(fmaf(bf_lo(sb), (float)P.emb.w[row * H + c], bf_hi(sb)));
+      lin[(size_t)m * K + H + c] = bf2f(P.a[i]);
+    }
+    __syncthreads();
+    block_rms_inv(lin, K, M, H, P.eps, red, inv);
+    for (int i = threadIdx.x; i < M * H; i += blockDim.x) {
+      const int m = i / H, c = i - m * H;
+      lin[(size_t)m * K + c] = bfr(bf2f(P.w[c]) * bfr(lin[(size_t)m * K + c] * inv[m]));
+    }
+    __syncthreads();
+    block_rms_inv(lin + H, K, M, H, P.eps, red, inv);
+    for (int i = threadIdx.x; i < M * H; i += blockDim.x) {
+      const int m = i / H, c = i - m * H;
+      lin[(size_t)m * K + H + c] = bfr(bf2f(P.w2[c]) * bfr(lin[(size_t)m * K + H + c] * inv[m]));
+    }
+  }
+  __syncthreads();
+  if (P.norm_out != nullptr && blockIdx.x == 0)
+    for (int i = threadIdx.x; i < M * K; i += blockDim.x) P.norm_out[i] = f2bf(lin[i]);
+}
+
+// ---------------------------------------------------------------------------
+// kernel 1: prologue + up to four row jobs over the same staged input
+// ---------------------------------------------------------------------------
+struct RowJob {
+  LinDev lin;    // weight matrix (E == 1)
+  LinDev lin2;   // EPI_SWIGLU: the "up" matrix paired with lin ("gate")
+  bf16_t* out;   // [M][O]
+  int epi;       // EPI_STORE | EPI_SWIGLU
+  int tasks;     // ceil(O / R)
+};
+struct RowJobs {
+  RowJob job[4];
+  int njobs;
+  int kinds_mask;  // bit k set when some job has weights of kind k
+};
+
+template <int KIND, int M, int R>
+ORN_D void run_row_task(const RowJob& J, int task, const XStage& X, int lane) {
+  const int row0 = task * R;
+  const int nvalid = min(R, J.lin.O - row0);
+  float acc[R][M];
+  warp_rows_dot<KIND, M, R>(J.lin, row0, nvalid, X, 0, lane, acc);
+  if (J.epi == EPI_SWIGLU) {
+    float up[R][M];
+    warp_rows_dot<KIND, M, R>(J.lin2, row0, nvalid, X, 0, lane, up);
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        if (r < nvalid)
+#pragma unroll
+          for (int m = 0; m < M; ++m)
+            J.out[(size_t)m * J.lin.O + row0 + r] = f2bf(orn_swiglu_bf(bfr(acc[r][m]), bfr(up[r][m])));
+    }
+  } else if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (r < nvalid)
+#pragma unroll
+        for (int m = 0; m < M; ++m) J.out[(size_t)m * J.lin.O + row0 + r] = f2bf(acc[r][m]);
+  }
+}
+
+template <int M, int R>
+__global__ void __launch_bounds__(kThreads) k_norm_gemv(Prologue P, RowJobs J) {
+  extern __shared__ __align__(16) float smem[];
+  float* lin = smem;
+  float* red = lin + (size_t)M * P.K;
+  float* next = red + M * 32 + M;
+  next = smem + (((next - smem) + 3) & ~3);
+  XStage X[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    if (J.kinds_mask & (1 << k)) next = stage_carve(next, k, M, P.K, X[k]);
+  run_prologue<M>(P, lin, red);
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    if (J.kinds_mask & (1 << k)) stage_fill_kind(k, lin, P.K, X[k]);
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int gw = blockIdx.x * kWarps + (threadIdx.x >> 5);
+  const int GW = gridDim.x * kWarps;
+  int total = 0;
+  for (int j = 0; j < J.njobs; ++j) total += J.job[j].tasks;
+  for (int t = gw; t < total; t += GW) {
+    int j = 0, tt = t;
+    while (tt >= J.job[j].tasks) { tt -= J.job[j].tasks; ++j; }
+    const RowJob& job = J.job[j];
+    switch (job.lin.kind) {
+      case ORN_A8: run_row_task<ORN_A8, M, R>(job, tt, X[ORN_A8], lane); break;
+      case ORN_Q4K: run_row_task<ORN_Q4K, M, R>(job, tt, X[ORN_Q4K], lane); break;
+      case ORN_Q6K: run_row_task<ORN_Q6K, M, R>(job, tt, X[ORN_Q6K], lane); break;
+      default: run_row_task<ORN_BF16, M, R>(job, tt, X[ORN_BF16], lane); break;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// kernel 2: router top-k in the prologue, routed expert gate/up + SwiGLU
+// ---------------------------------------------------------------------------
+struct MoeUpParams {
+  const bf16_t* logits;  // [M][E] router logits
+  const bf16_t* x;       // [M][H] normed input
+  LinDev gate, up;       // [E, I, H]
+  uint32_t* inds;        // [M][k] out (CTA 0)
+  bf16_t* scores;        // [M][k] out (CTA 0)
+  bf16_t* act;           // [M*k][I] out
+  int E, k, H, I;
+};
+
+// softmax (mlx softmax.h:10-99, float accumulate) then router_top_k
+// (kernels/moe.metal:568-614) for one token by one warp; results to shared
+ORN_D void warp_softmax_topk(const bf16_t* logits, int n, int k, float* probs /*[n] smem*/,
+                             float* red /*[32] smem*/, uint32_t* inds, float* scores, int lane) {
+  float mx = -INFINITY;
+  for (int i = lane; i < n; i += 32) mx = fmaxf(mx, bf2f(logits[i]));
+  mx = warp_max(mx);
+  const int nvt = (n + 3) / 4;
+  const int nvw = (nvt + 31) / 32;
+  red[lane] = 0.f;
+  __syncwarp();
+  for (int vw = 0; vw < nvw; ++vw) {
+    const int vt = vw * 32 + lane;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = 4 * vt + i;
+      if (idx < n) {
+        const float e = orn_expf(bf2f(logits[idx]) - mx);
+        probs[idx] = e;
+        acc = acc + e;
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) red[vw] = acc;
+  }
+  __syncwarp();
+  const float inv = 1.0f / warp_sum(red[lane]);
+  __syncwarp();
+  for (int i = lane; i < n; i += 32) probs[i] = bfr(probs[i] * inv);
+  __syncwarp();
+  constexpr int kMaxPerLane = 16;
+  float v[kMaxPerLane];
+  int held = 0;
+#pragma unroll
+  for (int s = 0; s < kMaxPerLane; ++s) {
+    const int i = lane + 32 * s;
+    v[s] = -INFINITY;
+    if (i < n) { v[s] = probs[i]; held = s + 1; }
+  }
+  for (int r = 0; r < k; ++r) {
+    float best = -INFINITY;
+    uint32_t besti = 0;
+#pragma unroll
+    for (int s = 0; s < kMaxPerLane; ++s) {
+      const uint32_t i = lane + 32 * s;
+      if (s < held && (v[s] > best || (v[s] == best && i > besti))) { best = v[s]; besti = i; }
+    }
+    const float m = warp_max(best);
+    const uint32_t mi = warp_max_u32(best == m ? besti + 1 : 0u) - 1;
+#pragma unroll
+    for (int s = 0; s < kMaxPerLane; ++s)
+      if ((mi & 31) == (uint32_t)lane && (mi >> 5) == (uint32_t)s) v[s] = -INFINITY;
+    if (lane == 0) {
+      inds[k - 1 - r] = mi;
+      scores[k - 1 - r] = probs[mi];
+    }
+  }
+  __syncwarp();
+}
+
+template <int KIND, int M, int R>
+__global__ void __launch_bounds__(kThreads) k_moe_up(MoeUpParams P) {
+  extern __shared__ __align__(16) float smem[];
+  float* lin = smem;                                   // [M][H]
+  float* probs = lin + (size_t)M * P.H;                // [M][E]
+  float* red = probs + (size_t)M * P.E;                // [M][32]
+  float* scores = red + M * 32;                        // [M][k]
+  uint32_t* inds = reinterpret_cast<uint32_t*>(scores + M * P.k);  // [M][k]
+  float* next = reinterpret_cast<float*>(inds + M * P.k);
+  next = smem + (((next - smem) + 3) & ~3);
+  XStage X;
+  stage_carve(next, KIND, M, P.H, X);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (warp < M)
+    warp_softmax_topk(P.logits + (size_t)warp * P.E, P.E, P.k, probs + (size_t)warp * P.E, red + warp * 32,
+                      inds + warp * P.k, scores + warp * P.k, lane);
+  for (int i = threadIdx.x; i < M * P.H; i += blockDim.x) lin[i] = bf2f(P.x[i]);
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < M * P.k; i += blockDim.x) {
+      P.inds[i] = inds[i];
+      P.scores[i] = f2bf(scores[i]);
+    }
+  stage_fill<KIND>(lin, P.H, X);
+  __syncthreads();
+  const int per = (P.I + R - 1) / R;
+  const int total = M * P.k * per;
+  const int gw = blockIdx.x * kWarps + warp, GW = gridDim.x * kWarps;
+  for (int t = gw; t < total; t += GW) {
+    const int mj = t / per, og = t - mj * per;
+    const int m = mj / P.k;
+    const int64_t e = inds[mj];
+    const int row0 = og * R;
+    const int nvalid = min(R, P.I - row0);
+    float g[R][1], u[R][1];
+    warp_rows_dot<KIND, 1, R>(P.gate, e * P.I + row0, nvalid, X, m, lane, g);
+    warp_rows_dot<KIND, 1, R>(P.up, e * P.I + row0, nvalid, X, m, lane, u);
+    if (lane == 0)
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        if (r < nvalid) P.act[(size_t)mj * P.I + row0 + r] = f2bf(orn_swiglu_bf(bfr(g[r][0]), bfr(u[r][0])));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// kernel 3: routed down projections + shared down + combine
+// (kernels/moe.metal:207-244 arithmetic in the epilogue)
+// ---------------------------------------------------------------------------
+struct MoeDownParams {
+  const bf16_t* act;     // [M*k][I]
+  const bf16_t* sact;    // [M][SI]
+  const uint32_t* inds;  // [M][k]
+  const bf16_t* scores;  // [M][k]
+  const bf16_t* gs;      // [M] shared-expert gate logits
+  LinDev down;           // [E, H, I]
+  LinDev sh_down;        // [1, H, SI]
+  bf16_t* out;           // [M][H]
+  int k, H, I, SI, normalize;
+};
+
+template <int KIND, int M>
+__global__ void __launch_bounds__(kThreads) k_moe_down(MoeDownParams P) {
+  extern __shared__ __align__(16) float smem[];
+  const int rows = M * P.k;
+  float* lin = smem;                                   // [rows][I] then [M][SI]
+  float* lin2 = lin + (size_t)rows * P.I;
+  float* wts = lin2 + (size_t)M * P.SI;                // [M][k] normalised scores
+  float* gsig = wts + rows;                            // [M]
+  uint32_t* inds = reinterpret_cast<uint32_t*>(gsig + M);
+  float* next = reinterpret_cast<float*>(inds + rows);
+  next = smem + (((next - smem) + 3) & ~3);
+  XStage X, XS;
+  next = stage_carve(next, KIND, rows, P.I, X);
+  stage_carve(next, KIND, M, P.SI, XS);
+  for (int i = threadIdx.x; i < rows * P.I; i += blockDim.x) lin[i] = bf2f(P.act[i]);
+  for (int i = threadIdx.x; i < M * P.SI; i += blockDim.x) lin2[i] = bf2f(P.sact[i]);
+  if (threadIdx.x < M) {
+    const int m = threadIdx.x;
+    float denom = 0.f;
+    if (P.normalize)
+      for (int j = 0; j < P.k; ++j) denom = bfr(bf2f(P.scores[m * P.k + j]) + denom);
+    for (int j = 0; j < P.k; ++j) {
+      const float s = bf2f(P.scores[m * P.k + j]);
+      wts[m * P.k + j] = P.normalize ? bfr(s / denom) : s;
+      inds[m * P.k + j] = P.inds[m * P.k + j];
+    }
+    gsig[m] = orn_sigmoid_bf(bf2f(P.gs[m]));
+  }
+  __syncthreads();
+  stage_fill<KIND>(lin, P.I, X);
+  stage_fill<KIND>(lin2, P.SI, XS);
+  __syncthreads();
+  using U = WU<KIND>;
+  constexpr int PP = Lay<KIND>::P, NS = Lay<KIND>::NS;
+  constexpr int KMAX = 8;
+  const int lane = threadIdx.x & 31;
+  const int gw = blockIdx.x * kWarps + (threadIdx.x >> 5), GW = gridDim.x * kWarps;
+  for (int c = gw; c < P.H; c += GW) {
+    float outv[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      float accj[KMAX + 1];
+#pragma unroll
+      for (int j = 0; j <= KMAX; ++j) accj[j] = 0.f;
+      // routed rows: all k experts' units of this step are requested before any is consumed
+      for (int s = 0; s < X.S; ++s) {
+        const int u = lane + 32 * s;
+        if (u < X.units) {
+          typename U::W w[KMAX];
+#pragma unroll
+          for (int j = 0; j < KMAX; ++j)
+            if (j < P.k) U::load(P.down, (int64_t)inds[m * P.k + j] * P.H + c, u, w[j]);
+#pragma unroll
+          for (int j = 0; j < KMAX; ++j)
+            if (j < P.k) {
+              float xv[PP * 4];
+              const float4* xp = reinterpret_cast<const float4*>(X.xs) + ((size_t)((m * P.k + j) * X.S + s) * PP) * 32 + lane;
+#pragma unroll
+              for (int p = 0; p < PP; ++p) {
+                const float4 v = xp[p * 32];
+                xv[4 * p] = v.x; xv[4 * p + 1] = v.y; xv[4 * p + 2] = v.z; xv[4 * p + 3] = v.w;
+              }
+              float sm[NS > 0 ? NS : 1];
+#pragma unroll
+              for (int i = 0; i < NS; ++i) sm[i] = X.sums[((size_t)(m * P.k + j) * X.units + u) * NS + i];
+              accj[j] = U::fold(w[j], xv, sm, u, accj[j]);
+            }
+        }
+      }
+      float sd[1][1];
+      warp_rows_dot<KIND, 1, 1>(P.sh_down, c, 1, XS, m, lane, sd);
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j)
+        if (j < P.k) {
+          const float d = warp_sum(accj[j]);
+          const float weighted = bfr(bfr(d) * wts[m * P.k + j]);
+          acc = bfr(weighted + acc);
+        }
+      const float gated = bfr(gsig[m] * bfr(sd[0][0]));
+      outv[m] = acc + gated;
+    }
+    if (lane == 0)
+#pragma unroll
+      for (int m = 0; m < M; ++m) P.out[(size_t)m * P.H + c] = f2bf(outv[m]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// kernel 4: gated-delta front end + recurrence in one launch
+// ---------------------------------------------------------------------------
+struct GdnParams {
+  const bf16_t* conv;   // [S + T][D]: cached window rows then this call's qkv rows
+  const bf16_t* cw;     // [D][Kc]
+  const bf16_t* a_in;   // [T][Hv]
+  const bf16_t* b_in;   // [T][Hv]
+  const bf16_t* a_log;  // [Hv]
+  const bf16_t* dt_bias;
+  float* ring;          // [nring][Hv][128][128]
+  const int* cur;
+  bf16_t* y;            // [T][Hv][128]
+  int T, S, Kc, D, Hk, Hv, nring, final_only;
+  float q_scale, k_scale, eps;
+};
+
+constexpr int kGdnRows = 16;
+constexpr int kGdnMaxT = 4;
+
+__global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
+  __shared__ float s_q[kGdnMaxT][128], s_k[kGdnMaxT][128], s_v[kGdnMaxT][kGdnRows];
+  __shared__ float s_g[kGdnMaxT], s_beta[kGdnMaxT];
+  const int hv = blockIdx.y;
+  const int hk = hv / (p.Hv / p.Hk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int key_dim = p.Hk * 128;
+  // ---- front end (kernels/gdn_front.metal:65-190): warp 0 -> q head, warp 1 -> k head
+  for (int t = 0; t < p.T; ++t) {
+    const int c0 = (warp == 0 ? hk * 128 : key_dim + hk * 128) + 4 * lane;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < p.Kc; ++i) {
+      const uint2 xv = *reinterpret_cast<const uint2*>(p.conv + (size_t)(t + i) * p.D + c0);
+      const float xs[4] = {bf_lo(xv.x), bf_hi(xv.x), bf_lo(xv.y), bf_hi(xv.y)};
+#pragma unroll
+      for (int r = 0; r < 4; ++r) acc[r] = fmaf(xs[r], bf2f(p.cw[(size_t)(c0 + r) * p.Kc + i]), acc[r]);
+    }
+    float yv[4];
+    float sum = 0.f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) { yv[r] = orn_silu_bf(bfr(acc[r])); sum = fmaf(yv[r], yv[r], sum); }
+    sum = warp_sum(sum);
+    const float inv = orn_rsqrtf(sum / 128.0f + p.eps);
+    const float sc = warp == 0 ? p.q_scale : p.k_scale;
+    float* dst = warp == 0 ? s_q[t] : s_k[t];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) dst[4 * lane + r] = bfr(sc * bfr(yv[r] * inv));
+  }
+  // value rows of this CTA and the per-head gates
+  const int row = blockIdx.x * kGdnRows + (threadIdx.x >> 2);
+  const int lir = threadIdx.x & 3;
+  if (lir == 0) {
+    const int c = 2 * key_dim + hv * 128 + row;
+    for (int t = 0; t < p.T; ++t) {
+      float acc = 0.f;
+      for (int i = 0; i < p.Kc; ++i)
+        acc = fmaf(bf2f(p.conv[(size_t)(t + i) * p.D + c]), bf2f(p.cw[(size_t)c * p.Kc + i]), acc);
+      s_v[t][threadIdx.x >> 2] = orn_silu_bf(bfr(acc));
+    }
+  }
+  if (threadIdx.x < p.T) {
+    const int t = threadIdx.x;
+    const size_t i = (size_t)t * p.Hv + hv;
+    const float sp = orn_softplus_bf(bfr(bf2f(p.a_in[i]) + bf2f(p.dt_bias[hv])));
+    const float decay = orn_expf(bf2f(p.a_log[hv]));
+    s_g[t] = orn_expf((-decay) * sp);
+    s_beta[t] = orn_sigmoid_bf(bf2f(p.b_in[i]));
+  }
+  __syncthreads();
+  // ---- recurrence (kernels/gated_delta.metal:36-142)
+  const size_t ssz = (size_t)p.Hv * 128 * 128;
+  const size_t off = ((size_t)hv * 128 + row) * 128 + lir * 32;
+  const int cur = *p.cur;
+  const float* sin = p.ring + (size_t)(cur % p.nring) * ssz + off;
+  float S[32];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 v4 = *reinterpret_cast<const float4*>(sin + 4 * i);
+    S[4 * i] = v4.x; S[4 * i + 1] = v4.y; S[4 * i + 2] = v4.z; S[4 * i + 3] = v4.w;
+  }
+  for (int t = 0; t < p.T; ++t) {
+    const float* kf = s_k[t] + lir * 32;
+    const float* qf = s_q[t] + lir * 32;
+    const float gt = s_g[t], bt = s_beta[t], vt = s_v[t][threadIdx.x >> 2];
+    float part[8];
+#pragma unroll
+    for (int pb = 0; pb < 8; ++pb) {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int e = pb * 4 + i;
+        S[e] = S[e] * gt;
+        acc = fmaf(S[e], kf[e], acc);
+      }
+      part[pb] = acc;
+    }
+    float kv = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
+    kv = kv + __shfl_xor_sync(0xffffffffu, kv, 1);
+    kv = kv + __shfl_xor_sync(0xffffffffu, kv, 2);
+    const float delta = (vt - kv) * bt;
+#pragma unroll
+    for (int pb = 0; pb < 8; ++pb) {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int e = pb * 4 + i;
+        S[e] = fmaf(kf[e], delta, S[e]);
+        acc = fmaf(S[e], qf[e], acc);
+      }
+      part[pb] = acc;
+    }
+    float o = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
+    o = o + __shfl_xor_sync(0xffffffffu, o, 1);
+    o = o + __shfl_xor_sync(0xffffffffu, o, 2);
+    if (lir == 0) p.y[((size_t)t * p.Hv + hv) * 128 + row] = f2bf(o);
+    float* sout = nullptr;
+    if (!p.final_only) sout = p.ring + (size_t)((cur + 1 + t) % p.nring) * ssz + off;
+    else if (t + 1 == p.T) sout = p.ring + (size_t)((cur + 1) % p.nring) * ssz + off;
+    if (sout != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        *reinterpret_cast<float4*>(sout + 4 * i) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// kernel 5: q/k norm + rotary + KV append + attention + output gate
+// ---------------------------------------------------------------------------
+struct AttnParams {
+  const bf16_t* qg;      // [T][Hq][2*256]: query | gate
+  const bf16_t* k;       // [T][Hkv][256]
+  const bf16_t* v;       // [T][Hkv][256]
+  const bf16_t* q_norm;  // [256]
+  const bf16_t* k_norm;  // [256]
+  bf16_t* kc;            // [Hkv][cap][256]
+  bf16_t* vc;
+  const int* pos;
+  bf16_t* out;           // [T][Hq*256] gated attention output
+  int T, Hq, Hkv, cap, rope_dims;
+  float lnb, scale, eps;
+};
+
+// norm + rope of one 256-wide head row by one warp (8 dims per lane); the
+// result (bfloat16 values as floats) goes to dst[256]
+ORN_D void warp_norm_rope(const bf16_t* src, const bf16_t* w, float eps, int rope_dims, float lnb, int position,
+                          float* dst, float* red /*[2]*/, int lane) {
+  // rms over 256 = 64 virtual threads of 4 -> two virtual warps
+  float xv[8];
+  widen8(ldg128(src + 8 * lane), xv);
+  // lane holds elements 8l..8l+7 = virtual threads 2l, 2l+1; virtual warp = (2l+j)/32
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { a0 = fmaf(xv[i], xv[i], a0); a1 = fmaf(xv[4 + i], xv[4 + i], a1); }
+  // virtual warp 0 = lanes 0..15 (both halves), virtual warp 1 = lanes 16..31.  Its butterfly over
+  // virtual lanes (xor 16,8,4,2,1 of the virtual index 2l+j) is: xor 8,4,2,1 across lanes, then j.
+  // virtual index v = 2*(lane&15) + j; xor 16 <-> lane xor 8; xor 8 <-> lane xor 4; xor 4 <-> lane xor 2;
+  // xor 2 <-> lane xor 1; xor 1 <-> j.
+  float b0 = a0 + __shfl_xor_sync(0xffffffffu, a0, 8);
+  float b1 = a1 + __shfl_xor_sync(0xffffffffu, a1, 8);
+  b0 = b0 + __shfl_xor_sync(0xffffffffu, b0, 4); b1 = b1 + __shfl_xor_sync(0xffffffffu, b1, 4);
+  b0 = b0 + __shfl_xor_sync(0xffffffffu, b0, 2); b1 = b1 + __shfl_xor_sync(0xffffffffu, b1, 2);
+  b0 = b0 + __shfl_xor_sync(0xffffffffu, b0, 1); b1 = b1 + __shfl_xor_sync(0xffffffffu, b1, 1);
+  const float vw = b0 + b1;  // sum of this lane's virtual warp
+  const float other = __shfl_xor_sync(0xffffffffu, vw, 16);
+  const float w0 = lane < 16 ? vw : other, w1 = lane < 16 ? other : vw;
+  // second level: butterfly of [w0, w1, 0, ...] = w0 + w1 after exact additions of zero
+  const float total = (w0 + 0.f) + (w1 + 0.f);
+  (void)red;
+  const float inv = orn_rsqrtf(total / 256.0f + eps);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[8 * lane + i] = bfr(bf2f(w[8 * lane + i]) * bfr(xv[i] * inv));
+  __syncwarp();
+  const int half = rope_dims / 2;
+  for (int i = lane; i < half; i += 32) {
+    const float inv_freq = orn_expf(-(float)i * lnb);
+    const float ang = (float)position * inv_freq;
+    float sn, cs;
+    orn_sincosf(ang, &sn, &cs);
+    const float x1 = dst[i], x2 = dst[i + half];
+    const float t1 = x2 * sn, t2 = x2 * cs;
+    dst[i] = bfr(fmaf(x1, cs, -t1));
+    dst[i + half] = bfr(fmaf(x1, sn, t2));
+  }
+  __syncwarp();
+}
+
+__global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
+  constexpr int HD = 256;
+  __shared__ float s_o[32][HD];
+  __shared__ float s_q[HD];
+  __shared__ float s_knew[kGdnMaxT][HD];
+  __shared__ float s_max[32], s_sum[32], s_f[32];
+  const int h = blockIdx.x, r = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int group = p.Hq / p.Hkv;
+  const int kvh = h / group;
+  const int pos = *p.pos;
+  if (warp == 0)
+    warp_norm_rope(p.qg + ((size_t)r * p.Hq + h) * 2 * HD, p.q_norm, p.eps, p.rope_dims, p.lnb, pos + r, s_q, nullptr, lane);
+  else if (warp <= p.T)
+    warp_norm_rope(p.k + ((size_t)(warp - 1) * p.Hkv + kvh) * HD, p.k_norm, p.eps, p.rope_dims, p.lnb, pos + warp - 1,
+                   s_knew[warp - 1], nullptr, lane);
+  __syncthreads();
+  // one CTA per kv head appends the window's keys and values to the cache
+  if (r == 0 && (h % group) == 0) {
+    for (int i = threadIdx.x; i < p.T * HD; i += blockDim.x) {
+      const int t = i / HD, d = i - t * HD;
+      if (pos + t < p.cap) {
+        p.kc[((size_t)kvh * p.cap + pos + t) * HD + d] = f2bf(s_knew[t][d]);
+        p.vc[((size_t)kvh * p.cap + pos + t) * HD + d] = p.v[((size_t)t * p.Hkv + kvh) * HD + d];
+      }
+    }
+  }
+  int L = pos + r + 1;
+  if (L > p.cap) L = p.cap;
+  float qs[8], o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { qs[i] = s_q[8 * lane + i] * p.scale; o[i] = 0.f; }
+  float mx = -INFINITY, sm = 0.f;
+  for (int n = warp; n < L; n += 32) {
+    float kf[8], vf[8];
+    if (n >= pos) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) kf[i] = s_knew[n - pos][8 * lane + i];
+      widen8(ldg128(p.v + ((size_t)(n - pos) * p.Hkv + kvh) * HD + 8 * lane), vf);
+    } else {
+      const size_t rowoff = ((size_t)kvh * p.cap + n) * HD + 8 * lane;
+      widen8(*reinterpret_cast<const uint4*>(p.kc + rowoff), kf);
+      widen8(*reinterpret_cast<const uint4*>(p.vc + rowoff), vf);
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = fmaf(qs[i], kf[i], acc);
+    const float score = warp_sum(acc);
+    const float nm = fmaxf(mx, score);
+    const float factor = orn_expf(mx - nm);
+    const float e = orn_expf(score - nm);
+    mx = nm;
+    sm = fmaf(sm, factor, e);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = fmaf(o[i], factor, e * vf[i]);
+  }
+  if (lane == 0) { s_max[warp] = mx; s_sum[warp] = sm; }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s_o[warp][8 * lane + i] = o[i];
+  __syncthreads();
+  if (warp == 0) {
+    const float M = warp_max(s_max[lane]);
+    const float f = orn_expf(s_max[lane] - M);
+    s_f[lane] = f;
+    const float S = warp_sum(s_sum[lane] * f);
+    if (lane == 0) s_sum[0] = S;
+  }
+  __syncthreads();
+  if (threadIdx.x < HD) {
+    const int d = threadIdx.x;
+    float a[32];
+#pragma unroll
+    for (int g = 0; g < 32; ++g) a[g] = s_o[g][d] * s_f[g];
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+      for (int i = 0; i < off; ++i) a[i] = a[i] + a[i + off];
+    const float att = bfr(a[0] / s_sum[0]);
+    const float gate = bf2f(p.qg[((size_t)r * p.Hq + h) * 2 * HD + HD + d]);
+    p.out[((size_t)r * p.Hq + h) * HD + d] = f2bf(orn_sigmoid_bf(gate) * att);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+int persistent_grid(orn_ctx* ctx) { return ctx->sm_count * 2; }
+
+template <typename Kern>
+int set_smem(orn_ctx* ctx, Kern kern, size_t bytes) {
+  if (bytes > 220 * 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "fused kernel: staged activations exceed shared memory");
+  if (bytes > 48 * 1024)
+    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  return ORN_OK;
+}
+
+template <int M>
+int launch_norm_gemv(orn_ctx* ctx, cudaStream_t s, const Prologue& P, RowJobs& J) {
+  constexpr int R = 2;
+  size_t fl = (size_t)M * P.K + M * 33 + 4;
+  J.kinds_mask = 0;
+  for (int j = 0; j < J.njobs; ++j) {
+    J.kinds_mask |= 1 << J.job[j].lin.kind;
+    J.job[j].tasks = (J.job[j].lin.O + R - 1) / R;
+    if (J.job[j].lin.K != P.K) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: weight K differs from the staged row");
+    if (J.job[j].epi == EPI_SWIGLU && J.job[j].lin2.kind != J.job[j].lin.kind)
+      ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: gate and up projections must share a format");
+  }
+  for (int k = 0; k < 4; ++k)
+    if (J.kinds_mask & (1 << k)) fl += stage_floats(k, M, P.K);
+  const size_t bytes = fl * sizeof(float);
+  int rc = set_smem(ctx, k_norm_gemv<M, R>, bytes);
+  if (rc != ORN_OK) return rc;
+  k_norm_gemv<M, R><<<persistent_grid(ctx), kThreads, bytes, s>>>(P, J);
+  return orn_launch_check(ctx, "k_norm_gemv");
+}
+
+template <int KIND, int M>
+int launch_moe_up_k(orn_ctx* ctx, cudaStream_t s, const MoeUpParams& P) {
+  constexpr int R = 2;
+  const size_t fl = (size_t)M * P.H + (size_t)M * P.E + M * 32 + 2 * M * P.k + 4 + stage_floats(KIND, M, P.H);
+  const size_t bytes = fl * sizeof(float);
+  int rc = set_smem(ctx, k_moe_up<KIND, M, R>, bytes);
+  if (rc != ORN_OK) return rc;
+  k_moe_up<KIND, M, R><<<persistent_grid(ctx), kThreads, bytes, s>>>(P);
+  return orn_launch_check(ctx, "k_moe_up");
+}
+
+template <int KIND, int M>
+int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
+  const int rows = M * P.k;
+  const size_t fl = (size_t)rows * P.I + (size_t)M * P.SI + 2 * rows + M + 4 + stage_floats(KIND, rows, P.I) +
+                    stage_floats(KIND, M, P.SI);
+  const size_t bytes = fl * sizeof(float);
+  int rc = set_smem(ctx, k_moe_down<KIND, M>, bytes);
+  if (rc != ORN_OK) return rc;
+  k_moe_down<KIND, M><<<persistent_grid(ctx), kThreads, bytes, s>>>(P);
+  return orn_launch_check(ctx, "k_moe_down");
+}
+
+}  // namespace
+
+int f_norm_gemv(orn_ctx* ctx, cudaStream_t s, int M, const FusedPrologue& fp, const FusedJob* jobs, int njobs) {
+  if (njobs < 1 || njobs > 4) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: 1..4 jobs");
+  Prologue P;
+  P.mode = fp.mode; P.K = fp.K; P.a = fp.a; P.b = fp.b; P.w = fp.w; P.w2 = fp.w2; P.sum_out = fp.sum_out;
+  P.norm_out = fp.norm_out; P.ids = fp.ids; P.eps = fp.eps;
+  P.emb = fp.emb ? lin_dev(fp.emb) : LinDev{0, 0, 0, 0, nullptr, nullptr, nullptr};
+  RowJobs J;
+  J.njobs = njobs;
+  for (int j = 0; j < njobs; ++j) {
+    J.job[j].lin = lin_dev(jobs[j].lin);
+    J.job[j].lin2 = jobs[j].lin2 ? lin_dev(jobs[j].lin2) : J.job[j].lin;
+    J.job[j].out = jobs[j].out;
+    J.job[j].epi = jobs[j].epi;
+  }
+  switch (M) {
+    case 1: return launch_norm_gemv<1>(ctx, s, P, J);
+    case 2: return launch_norm_gemv<2>(ctx, s, P, J);
+    case 3: return launch_norm_gemv<3>(ctx, s, P, J);
+    case 4: return launch_norm_gemv<4>(ctx, s, P, J);
+  }
+  ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: 1..4 rows");
+}
+
+int f_moe_up(orn_ctx* ctx, cudaStream_t s, int M, const bf16_t* logits, const bf16_t* x, const orn_linear* gate,
+             const orn_linear* up, int k, uint32_t* inds, bf16_t* scores, bf16_t* act) {
+  if (gate->kind != up->kind) ORN_FAIL(ctx, ORN_ERR_ARG, "moe: gate and up experts must share a format");
+  MoeUpParams P;
+  P.logits = logits; P.x = x; P.gate = lin_dev(gate); P.up = lin_dev(up); P.inds = inds; P.scores = scores;
+  P.act = act; P.E = gate->E; P.k = k; P.H = gate->K; P.I = gate->O;
+  if (P.E > 512) ORN_FAIL(ctx, ORN_ERR_ARG, "moe: more than 512 experts");
+#define ORN_UP(KIND)                                                   \
+  switch (M) {                                                         \
+    case 1: return launch_moe_up_k<KIND, 1>(ctx, s, P);                \
+    case 2: return launch_moe_up_k<KIND, 2>(ctx, s, P);                \
+    case 3: return launch_moe_up_k<KIND, 3>(ctx, s, P);                \
+    case 4: return launch_moe_up_k<KIND, 4>(ctx, s, P);                \
+  }
+  switch (gate->kind) {
+    case ORN_Q4K: ORN_UP(ORN_Q4K) break;
+    case ORN_Q6K: ORN_UP(ORN_Q6K) break;
+    case ORN_A8: ORN_UP(ORN_A8) break;
+    default: ORN_UP(ORN_BF16) break;
+  }
+#undef ORN_UP
+  ORN_FAIL(ctx, ORN_ERR_ARG, "moe_up: 1..4 rows");
+}
+
+int f_moe_down(orn_ctx* ctx, cudaStream_t s, int M, const bf16_t* act, const bf16_t* sact, const uint32_t* inds,
+               const bf16_t* scores, const bf16_t* gs, const orn_linear* down, const orn_linear* sh_down, int k,
+               int normalize, bf16_t* out) {
+  if (down->kind != sh_down->kind) ORN_FAIL(ctx, ORN_ERR_ARG, "moe: routed and shared down projections must share a format");
+  MoeDownParams P;
+  P.act = act; P.sact = sact; P.inds = inds; P.scores = scores; P.gs = gs; P.down = lin_dev(down);
+  P.sh_down = lin_dev(sh_down); P.out = out; P.k = k; P.H = down->O; P.I = down->K; P.SI = sh_down->K;
+  P.normalize = normalize;
+  if (k > 8) ORN_FAIL(ctx, ORN_ERR_ARG, "moe: top_k above 8");
+#define ORN_DN(KIND)                                                   \
+  switch (M) {                                                         \
+    case 1: return launch_moe_down_k<KIND, 1>(ctx, s, P);              \
+    case 2: return launch_moe_down_k<KIND, 2>(ctx, s, P);              \
+    case 3: return launch_moe_down_k<KIND, 3>(ctx, s, P);              \
+    case 4: return launch_moe_down_k<KIND, 4>(ctx, s, P);              \
+  }
+  switch (down->kind) {
+    case ORN_Q4K: ORN_DN(ORN_Q4K) break;
+    case ORN_Q6K: ORN_DN(ORN_Q6K) break;
+    case ORN_A8: ORN_DN(ORN_A8) break;
+    default: ORN_DN(ORN_BF16) break;
+  }
+#undef ORN_DN
+  ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: 1..4 rows");
+}
+
+int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, const bf16_t* a, const bf16_t* b,
+          const bf16_t* a_log, const bf16_t* dt_bias, float* ring, int nring, const int* cur, int final_only, int T,
+          int Hk, int Hv, int Kc, float eps, bf16_t* y) {
+  if (T > kGdnMaxT) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gdn: at most 4 rows");
+  if (!final_only && T + 1 > nring) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gdn: window wider than the state ring");
+  GdnParams p;
+  p.conv = conv; p.cw = cw; p.a_in = a; p.b_in = b; p.a_log = a_log; p.dt_bias = dt_bias; p.ring = ring;
+  p.cur = cur; p.y = y; p.T = T; p.S = Kc - 1; p.Kc = Kc; p.D = 2 * Hk * 128 + Hv * 128; p.Hk = Hk; p.Hv = Hv;
+  p.nring = nring; p.final_only = final_only;
+  const float inv_scale = 1.0f / sqrtf(128.0f);
+  p.q_scale = bfr(inv_scale * inv_scale);
+  p.k_scale = bfr(inv_scale);
+  p.eps = eps;
+  dim3 grid(128 / kGdnRows, Hv);
+  k_gdn<<<grid, kGdnRows * 4, 0, s>>>(p);
+  return orn_launch_check(ctx, "k_gdn");
+}
+
+int f_attn(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, const bf16_t* k, const bf16_t* v, const bf16_t* q_norm,
+           const bf16_t* k_norm, bf16_t* kc, bf16_t* vc, const int* pos, int T, int Hq, int Hkv, int hd, int cap,
+           int rope_dims, float lnb, float eps, bf16_t* out) {
+  if (hd != 256) ORN_FAIL(ctx, ORN_ERR_ARG, "fused attention: head_dim must be 256");
+  if (T > kGdnMaxT) ORN_FAIL(ctx, ORN_ERR_ARG, "fused attention: at most 4 rows");
+  AttnParams p;
+  p.qg = qg; p.k = k; p.v = v; p.q_norm = q_norm; p.k_norm = k_norm; p.kc = kc; p.vc = vc; p.pos = pos; p.out = out;
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.cap = cap; p.rope_dims = rope_dims; p.lnb = lnb;
+  p.scale = 1.0f / sqrtf((float)hd);
+  p.eps = eps;
+  dim3 grid(Hq, T);
+  k_attn<<<grid, 1024, 0, s>>>(p);
+  return orn_launch_check(ctx, "k_attn");
+}

@@ -24,50 +24,11 @@
 #include <cuda_fp16.h>
 
 #include "orn_internal.h"
+#include "orn_quant.cuh"
 
 namespace {
 
 constexpr int kWarpsPerBlock = 4;
-
-// float(byte i of w), exact: 0x4B0000bb is 2^23 + bb
-template <int I>
-ORN_D float byte_f(uint32_t w) {
-  return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 + I)) - 8388608.0f;
-}
-// float(byte i of w) - 32, exact
-template <int I>
-ORN_D float byte_m32_f(uint32_t w) {
-  return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 + I)) - 8388640.0f;
-}
-ORN_D float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
-ORN_D float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
-
-// 8 bf16 -> 8 floats
-ORN_D void widen8(const uint4& v, float* f) {
-  f[0] = bf_lo(v.x); f[1] = bf_hi(v.x);
-  f[2] = bf_lo(v.y); f[3] = bf_hi(v.y);
-  f[4] = bf_lo(v.z); f[5] = bf_hi(v.z);
-  f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
-}
-
-// kernels/q4k.metal:43-56 (get_scale_min_k4) on the 12 scale bytes held as
-// three words (bytes 0-3, 4-7, 8-11)
-ORN_D void q4k_scale_min(int j, uint32_t s0, uint32_t s1, uint32_t s2, float* sc, float* mn) {
-  uint32_t q_j, q_j4;
-  if (j < 4) {
-    q_j = (s0 >> (8 * j)) & 0xff;
-    q_j4 = (s1 >> (8 * j)) & 0xff;
-    *sc = (float)(q_j & 63);
-    *mn = (float)(q_j4 & 63);
-  } else {
-    int jj = j - 4;
-    uint32_t a = (s2 >> (8 * jj)) & 0xff;   // q[j+4]
-    uint32_t lo = (s0 >> (8 * jj)) & 0xff;  // q[j-4]
-    uint32_t hi = (s1 >> (8 * jj)) & 0xff;  // q[j]
-    *sc = (float)((a & 0xF) | ((lo >> 6) << 4));
-    *mn = (float)((a >> 4) | ((hi >> 6) << 4));
-  }
-}
 
 // ---------------------------------------------------------------------------
 // per-format unit: activation registers + weight registers + fold

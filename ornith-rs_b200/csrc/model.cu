@@ -13,6 +13,7 @@
 #include <cstring>
 #include <memory>
 
+#include "fused.h"
 #include "orn_internal.h"
 
 #define CK(call)                     \
@@ -387,9 +388,41 @@ int commit(orn_cache* c, int keep, int ring_step) {
   return ORN_OK;
 }
 
-// the trunk over T <= kMaxRows rows whose ids are already on the device
-int forward_dev(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int T, bool capture,
-                bf16_t* normed_out, bf16_t* pre_norm_out) {
+bool use_fused() {
+  // ORN_UNFUSED=1 runs the one-kernel-per-op control path (same arithmetic)
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ORN_UNFUSED");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// MoE block from the pre-norm pair (a, b): h = bf(a+b) -> w.h, norm with `nw`,
+// router + shared expert + routed experts + combine -> w.mo   (three kernels)
+int moe_fused(orn_model* m, const Moe& moe, const bf16_t* a, const bf16_t* b, const bf16_t* nw, int T) {
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  Workspace& w = m->ws;
+  const orn_config& c = m->cfg;
+  FusedPrologue fp;
+  fp.mode = PRO_ADDNORM; fp.K = c.hidden; fp.a = a; fp.b = b; fp.w = nw; fp.sum_out = w.h; fp.norm_out = w.normed2;
+  fp.eps = c.rms_eps;
+  FusedJob jobs[3];
+  jobs[0].lin = moe.gate; jobs[0].out = w.gates;
+  jobs[1].lin = moe.sh_gate; jobs[1].lin2 = moe.sh_up; jobs[1].out = w.sact; jobs[1].epi = EPI_SWIGLU;
+  jobs[2].lin = moe.sh_egate; jobs[2].out = w.gs;
+  CK(f_norm_gemv(ctx, s, T, fp, jobs, 3));
+  CK(f_moe_up(ctx, s, T, w.gates, w.normed2, moe.sw_gate, moe.sw_up, c.top_k, w.inds, w.scores, w.eact));
+  CK(f_moe_down(ctx, s, T, w.eact, w.sact, w.inds, w.scores, w.gs, moe.sw_down, moe.sh_down, c.top_k,
+                c.norm_topk_prob, w.mo));
+  return ORN_OK;
+}
+
+// The 40 layers.  On return the residual stream is bf(w.h + w.mo), not yet
+// added: the add belongs to whatever norm comes next (the final norm here, the
+// next layer's input norm inside the loop), as in add_rms_norm (norm.rs).
+int trunk_layers(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int T, bool capture) {
   orn_ctx* ctx = m->ctx;
   cudaStream_t s = ctx->stream;
   Workspace& w = m->ws;
@@ -397,24 +430,109 @@ int forward_dev(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int T, boo
   const int H = c.hidden;
   if (T < 1 || T > kMaxRows) ORN_FAIL(ctx, ORN_ERR_ARG, "forward: 1..4 rows per call");
   if (cc->h_pos + T > c.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "forward: context exceeds max_ctx");
-  CK(k_embedding(ctx, s, m->embed, dev_ids, T, w.x));
-  CK(k_rms_norm(ctx, s, w.x, m->layers[0].input_ln, T, H, c.rms_eps, w.normed));
+  if (!use_fused()) {
+    CK(k_embedding(ctx, s, m->embed, dev_ids, T, w.x));
+    CK(k_rms_norm(ctx, s, w.x, m->layers[0].input_ln, T, H, c.rms_eps, w.normed));
+    for (int i = 0; i < c.n_layers; ++i) {
+      const Layer& ly = m->layers[i];
+      if (ly.linear) CK(gdn_layer(m, ly, w.normed, T, cc->conv[i], cc->ring[i], cc->cur, capture, w.r));
+      else
+        CK(attention(m, ly.q_proj, ly.k_proj, ly.v_proj, ly.o_proj, ly.q_norm, ly.k_norm, w.normed, T,
+                     cc->kc[i], cc->vc[i], cc->pos, w.r));
+      CK(k_add_rms_norm(ctx, s, w.x, w.r, ly.post_ln, T, H, c.rms_eps, w.h, w.normed2));
+      CK(moe_block(m, ly.moe, w.normed2, T, w.mo, nullptr));
+      if (i + 1 < c.n_layers)
+        CK(k_add_rms_norm(ctx, s, w.h, w.mo, m->layers[i + 1].input_ln, T, H, c.rms_eps, w.x, w.normed));
+    }
+    return ORN_OK;
+  }
+  const int S = c.gdn_conv_kernel - 1, D = conv_dim(c);
+  const int VD = c.gdn_v_heads * c.gdn_head_dim, QD = c.n_heads * c.head_dim;
+  CK(k_embedding(ctx, s, m->embed, dev_ids, T, w.memb));
+  const bf16_t* pa = w.memb;
+  const bf16_t* pb = nullptr;
   for (int i = 0; i < c.n_layers; ++i) {
     const Layer& ly = m->layers[i];
-    if (ly.linear) CK(gdn_layer(m, ly, w.normed, T, cc->conv[i], cc->ring[i], cc->cur, capture, w.r));
-    else
-      CK(attention(m, ly.q_proj, ly.k_proj, ly.v_proj, ly.o_proj, ly.q_norm, ly.k_norm, w.normed, T,
-                   cc->kc[i], cc->vc[i], cc->pos, w.r));
-    CK(k_add_rms_norm(ctx, s, w.x, w.r, ly.post_ln, T, H, c.rms_eps, w.h, w.normed2));
-    CK(moe_block(m, ly.moe, w.normed2, T, w.mo, nullptr));
-    const bf16_t* nw = (i + 1 < c.n_layers) ? m->layers[i + 1].input_ln : m->norm;
-    CK(k_add_rms_norm(ctx, s, w.h, w.mo, nw, T, H, c.rms_eps, w.x, w.normed));
+    FusedPrologue fp;
+    fp.mode = PRO_ADDNORM; fp.K = H; fp.a = pa; fp.b = pb; fp.w = ly.input_ln; fp.sum_out = w.x; fp.eps = c.rms_eps;
+    if (ly.linear) {
+      bf16_t* conv = cc->conv[i];
+      FusedJob jobs[4];
+      jobs[0].lin = ly.in_qkv; jobs[0].out = conv + (size_t)S * D;
+      jobs[1].lin = ly.in_z; jobs[1].out = w.z;
+      jobs[2].lin = ly.in_b; jobs[2].out = w.bb;
+      jobs[3].lin = ly.in_a; jobs[3].out = w.aa;
+      CK(f_norm_gemv(ctx, s, T, fp, jobs, 4));
+      CK(f_gdn(ctx, s, conv, ly.conv_w, w.aa, w.bb, ly.a_log, ly.dt_bias, cc->ring[i], kRing, cc->cur,
+               capture ? 0 : 1, T, c.gdn_k_heads, c.gdn_v_heads, c.gdn_conv_kernel, 1e-6f, w.gy));
+      FusedPrologue gp;
+      gp.mode = PRO_GATED; gp.K = VD; gp.a = w.gy; gp.b = w.z; gp.w = ly.gdn_norm; gp.eps = c.rms_eps;
+      FusedJob oj;
+      oj.lin = ly.out_proj; oj.out = w.r;
+      CK(f_norm_gemv(ctx, s, T, gp, &oj, 1));
+    } else {
+      FusedJob jobs[3];
+      jobs[0].lin = ly.q_proj; jobs[0].out = w.qg;
+      jobs[1].lin = ly.k_proj; jobs[1].out = w.ak;
+      jobs[2].lin = ly.v_proj; jobs[2].out = w.av;
+      CK(f_norm_gemv(ctx, s, T, fp, jobs, 3));
+      CK(f_attn(ctx, s, w.qg, w.ak, w.av, ly.q_norm, ly.k_norm, cc->kc[i], cc->vc[i], cc->pos, T, c.n_heads,
+                c.n_kv_heads, c.head_dim, c.max_ctx, c.rope_dims, m->lnb, c.rms_eps, w.agated));
+      FusedPrologue gp;
+      gp.mode = PRO_PLAIN; gp.K = QD; gp.a = w.agated;
+      FusedJob oj;
+      oj.lin = ly.o_proj; oj.out = w.r;
+      CK(f_norm_gemv(ctx, s, T, gp, &oj, 1));
+    }
+    CK(moe_fused(m, ly.moe, w.x, w.r, ly.post_ln, T));
+    pa = w.h;
+    pb = w.mo;
   }
-  if (normed_out) ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(normed_out, w.normed, sizeof(bf16_t) * (size_t)T * H, cudaMemcpyDeviceToDevice, s));
-  if (pre_norm_out) ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(pre_norm_out, w.x, sizeof(bf16_t) * (size_t)T * H, cudaMemcpyDeviceToDevice, s));
+  return ORN_OK;
+}
+
+// The final add + norm, alone or as the prologue of the lm_head mat-vec
+// (generate.rs:139-150: `lm_head.matmul(h)`), then the bookkeeping of the call.
+int trunk_finish(orn_model* m, orn_cache* cc, int T, bool capture, bf16_t* normed_out, bf16_t* pre_norm_out,
+                 const orn_linear* head, bf16_t* logits) {
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  Workspace& w = m->ws;
+  const orn_config& c = m->cfg;
+  const int H = c.hidden;
+  if (head != nullptr && use_fused()) {
+    FusedPrologue fp;
+    fp.mode = PRO_ADDNORM; fp.K = H; fp.a = w.h; fp.b = w.mo; fp.w = m->norm; fp.sum_out = pre_norm_out;
+    fp.norm_out = normed_out; fp.eps = c.rms_eps;
+    FusedJob j;
+    j.lin = head; j.out = logits;
+    CK(f_norm_gemv(ctx, s, T, fp, &j, 1));
+  } else {
+    CK(k_add_rms_norm(ctx, s, w.h, w.mo, m->norm, T, H, c.rms_eps, w.x, w.normed));
+    if (normed_out) ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(normed_out, w.normed, sizeof(bf16_t) * (size_t)T * H, cudaMemcpyDeviceToDevice, s));
+    if (pre_norm_out) ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(pre_norm_out, w.x, sizeof(bf16_t) * (size_t)T * H, cudaMemcpyDeviceToDevice, s));
+    if (head != nullptr) CK(k_gemv(ctx, s, head, w.normed, T, logits, 0));
+  }
   if (capture) cc->cap_T = T;
   else CK(commit(cc, T, 1));
   return ORN_OK;
+}
+
+// the trunk over T <= kMaxRows rows whose ids are already on the device
+int forward_dev(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int T, bool capture,
+                bf16_t* normed_out, bf16_t* pre_norm_out) {
+  CK(trunk_layers(m, cc, dev_ids, T, capture));
+  return trunk_finish(m, cc, T, capture, normed_out, pre_norm_out, nullptr, nullptr);
+}
+
+// trunk + lm_head + greedy for every row: tokens land in dev_tokens, the
+// post-norm hidden rows in normed_out
+int forward_greedy_dev(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int T, bool capture,
+                       bf16_t* normed_out, uint32_t* dev_tokens) {
+  Workspace& w = m->ws;
+  CK(trunk_layers(m, cc, dev_ids, T, capture));
+  CK(trunk_finish(m, cc, T, capture, normed_out, nullptr, m->lm_head, w.logits));
+  return k_greedy(m->ctx, m->ctx->stream, w.logits, T, m->lm_head->O, 1, dev_tokens, w.greedy_scratch);
 }
 
 int upload_ids(orn_model* m, const uint32_t* host_ids, int T) {
@@ -425,9 +543,12 @@ int upload_ids(orn_model* m, const uint32_t* host_ids, int T) {
   return ORN_OK;
 }
 
-// MtpHead::hidden (mtp.rs:166-217) for T rows; ids on the device
-int mtp_hidden(orn_model* m, orn_cache* cc, const bf16_t* trunk_hidden, const uint32_t* dev_ids,
-               int T, bf16_t* out) {
+// MtpHead::hidden / forward (mtp.rs:150-217) for T rows; ids on the device.
+// head != null: logits of `head` over the post-norm hidden (the draft chain);
+// kv_only: only the head's KV rows are wanted (the Committed re-encode discards
+// the hidden, mtp_generate.rs:292-301).
+int mtp_step(orn_model* m, orn_cache* cc, const bf16_t* trunk_hidden, const uint32_t* dev_ids, int T,
+             const orn_linear* head, bf16_t* hidden_out, bf16_t* logits, bool kv_only) {
   orn_ctx* ctx = m->ctx;
   cudaStream_t s = ctx->stream;
   Workspace& w = m->ws;
@@ -436,19 +557,57 @@ int mtp_hidden(orn_model* m, orn_cache* cc, const bf16_t* trunk_hidden, const ui
   const int H = c.hidden;
   if (!h.present) ORN_FAIL(ctx, ORN_ERR_STATE, "mtp: the model has no MTP head");
   if (cc->h_mtp_pos + T > c.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "mtp: context exceeds max_ctx");
-  CK(k_embedding(ctx, s, m->embed, dev_ids, T, w.memb));
-  CK(k_rms_norm(ctx, s, w.memb, h.pre_fc_norm_embedding, T, H, c.rms_eps, w.me));
-  CK(k_rms_norm(ctx, s, trunk_hidden, h.pre_fc_norm_hidden, T, H, c.rms_eps, w.mh));
-  CK(k_concat2(ctx, s, w.me, w.mh, T, H, w.mjoined));
-  CK(k_gemv(ctx, s, h.fc, w.mjoined, T, w.mx, 0));
-  CK(k_rms_norm(ctx, s, w.mx, h.input_ln, T, H, c.rms_eps, w.normed));
-  CK(attention(m, h.q_proj, h.k_proj, h.v_proj, h.o_proj, h.q_norm, h.k_norm, w.normed, T, cc->mtp_kc,
-               cc->mtp_vc, cc->mtp_pos, w.r));
-  CK(k_add(ctx, s, w.mx, w.r, T * H, w.h));
-  CK(k_rms_norm(ctx, s, w.h, h.post_ln, T, H, c.rms_eps, w.normed2));
-  CK(moe_block(m, h.moe, w.normed2, T, w.mo, nullptr));
-  CK(k_add(ctx, s, w.h, w.mo, T * H, w.h));
-  CK(k_rms_norm(ctx, s, w.h, h.norm, T, H, c.rms_eps, out));
+  if (!use_fused()) {
+    CK(k_embedding(ctx, s, m->embed, dev_ids, T, w.memb));
+    CK(k_rms_norm(ctx, s, w.memb, h.pre_fc_norm_embedding, T, H, c.rms_eps, w.me));
+    CK(k_rms_norm(ctx, s, trunk_hidden, h.pre_fc_norm_hidden, T, H, c.rms_eps, w.mh));
+    CK(k_concat2(ctx, s, w.me, w.mh, T, H, w.mjoined));
+    CK(k_gemv(ctx, s, h.fc, w.mjoined, T, w.mx, 0));
+    CK(k_rms_norm(ctx, s, w.mx, h.input_ln, T, H, c.rms_eps, w.normed));
+    CK(attention(m, h.q_proj, h.k_proj, h.v_proj, h.o_proj, h.q_norm, h.k_norm, w.normed, T, cc->mtp_kc,
+                 cc->mtp_vc, cc->mtp_pos, w.r));
+    CK(k_add(ctx, s, w.mx, w.r, T * H, w.h));
+    CK(k_rms_norm(ctx, s, w.h, h.post_ln, T, H, c.rms_eps, w.normed2));
+    CK(moe_block(m, h.moe, w.normed2, T, w.mo, nullptr));
+    CK(k_add(ctx, s, w.h, w.mo, T * H, w.h));
+    CK(k_rms_norm(ctx, s, w.h, h.norm, T, H, c.rms_eps, hidden_out));
+    if (head != nullptr) CK(k_gemv(ctx, s, head, hidden_out, T, logits, 0));
+  } else {
+    const int QD = c.n_heads * c.head_dim;
+    FusedPrologue jp;
+    jp.mode = PRO_MTPJOIN; jp.K = 2 * H; jp.a = trunk_hidden; jp.w = h.pre_fc_norm_embedding;
+    jp.w2 = h.pre_fc_norm_hidden; jp.emb = m->embed; jp.ids = dev_ids; jp.eps = c.rms_eps;
+    FusedJob fj;
+    fj.lin = h.fc; fj.out = w.mx;
+    CK(f_norm_gemv(ctx, s, T, jp, &fj, 1));
+    FusedPrologue fp;
+    fp.mode = PRO_ADDNORM; fp.K = H; fp.a = w.mx; fp.w = h.input_ln; fp.eps = c.rms_eps;
+    FusedJob jobs[3];
+    jobs[0].lin = h.q_proj; jobs[0].out = w.qg;
+    jobs[1].lin = h.k_proj; jobs[1].out = w.ak;
+    jobs[2].lin = h.v_proj; jobs[2].out = w.av;
+    CK(f_norm_gemv(ctx, s, T, fp, jobs, 3));
+    CK(f_attn(ctx, s, w.qg, w.ak, w.av, h.q_norm, h.k_norm, cc->mtp_kc, cc->mtp_vc, cc->mtp_pos, T, c.n_heads,
+              c.n_kv_heads, c.head_dim, c.max_ctx, c.rope_dims, m->lnb, c.rms_eps, w.agated));
+    if (!kv_only) {
+      FusedPrologue gp;
+      gp.mode = PRO_PLAIN; gp.K = QD; gp.a = w.agated;
+      FusedJob oj;
+      oj.lin = h.o_proj; oj.out = w.r;
+      CK(f_norm_gemv(ctx, s, T, gp, &oj, 1));
+      CK(moe_fused(m, h.moe, w.mx, w.r, h.post_ln, T));
+      if (head != nullptr) {
+        FusedPrologue hp;
+        hp.mode = PRO_ADDNORM; hp.K = H; hp.a = w.h; hp.b = w.mo; hp.w = h.norm; hp.norm_out = hidden_out;
+        hp.eps = c.rms_eps;
+        FusedJob hj;
+        hj.lin = head; hj.out = logits;
+        CK(f_norm_gemv(ctx, s, T, hp, &hj, 1));
+      } else {
+        CK(k_add_rms_norm(ctx, s, w.h, w.mo, h.norm, T, H, c.rms_eps, w.x, hidden_out));
+      }
+    }
+  }
   add_int_kernel<<<1, 1, 0, s>>>(cc->mtp_pos, T);
   CK(orn_launch_check(ctx, "add_int"));
   cc->h_mtp_pos += T;
@@ -833,8 +992,7 @@ int32_t orn_generate_step(orn_model* m, orn_cache* c, const uint32_t* prompt, in
   uint32_t y = 0;
   // step (generate.rs:139-150) on the last prompt token
   CK(upload_ids(m, prompt + done, 1));
-  CK(forward_dev(m, c, w.ids, 1, false, w.vh, nullptr));
-  CK(head_greedy_dev(m, m->lm_head, w.vh, 1, 1, w.logits, w.targets));
+  CK(forward_greedy_dev(m, c, w.ids, 1, false, w.vh, w.targets));
   CK(orn_download(ctx, &y, w.targets, 4));
   {
     float ms = 0.f;
@@ -846,8 +1004,7 @@ int32_t orn_generate_step(orn_model* m, orn_cache* c, const uint32_t* prompt, in
   while (n != max_tokens) {
     // the next step is taken before the token is handed out (generate.rs:195-205);
     // the sampled token stays on the device and feeds the next forward directly
-    CK(forward_dev(m, c, w.targets, 1, false, w.vh, nullptr));
-    CK(head_greedy_dev(m, m->lm_head, w.vh, 1, 1, w.logits, w.targets));
+    CK(forward_greedy_dev(m, c, w.targets, 1, false, w.vh, w.targets));
     uint32_t next = 0;
     CK(orn_download(ctx, &next, w.targets, 4));
     m->prof.ar_steps += 1;
@@ -891,8 +1048,7 @@ int32_t orn_generate_step_mtp(orn_model* m, orn_cache* c, const uint32_t* prompt
   CK(prefill(m, c, prompt, n_prompt, prefill_step, &done));
   cudaEventRecord(m->ev[3], s);
   CK(upload_ids(m, prompt + done, 1));
-  CK(forward_dev(m, c, w.ids, 1, false, w.hrow, nullptr));
-  CK(head_greedy_dev(m, m->lm_head, w.hrow, 1, 1, w.logits, w.targets));
+  CK(forward_greedy_dev(m, c, w.ids, 1, false, w.hrow, w.targets));
   uint32_t primary = 0;
   CK(orn_download(ctx, &primary, w.targets, 4));
   {
@@ -919,13 +1075,13 @@ int32_t orn_generate_step_mtp(orn_model* m, orn_cache* c, const uint32_t* prompt
     const bf16_t* dh_in = w.hrow;
     for (int i = 0; i < want; ++i) {
       bf16_t* dh_out = w.dh + (size_t)(i & 1) * H;
-      CK(mtp_hidden(m, c, dh_in, w.window + i, 1, dh_out));
+      CK(mtp_step(m, c, dh_in, w.window + i, 1, dlm, dh_out, w.dlogits, false));
       if (use_frspec) {
-        CK(head_greedy_dev(m, dlm, dh_out, 1, 0, w.dlogits, w.local));
+        CK(k_greedy(ctx, s, w.dlogits, 1, dlm->O, 0, w.local, w.greedy_scratch));
         gather_u32_kernel<<<1, 1, 0, s>>>(m->fr_ids, w.local, w.window + i + 1);
         CK(orn_launch_check(ctx, "gather_u32"));
       } else {
-        CK(head_greedy_dev(m, dlm, dh_out, 1, 0, w.dlogits, w.window + i + 1));
+        CK(k_greedy(ctx, s, w.dlogits, 1, dlm->O, 0, w.window + i + 1, w.greedy_scratch));
       }
       if (force && force->p > 0.f && emitted + 1 + i < force->len) {
         uint64_t rnd = splitmix64(force->seed + cycle_idx * 8 + (uint64_t)i);
@@ -942,8 +1098,7 @@ int32_t orn_generate_step_mtp(orn_model* m, orn_cache* c, const uint32_t* prompt
     cycle_idx += 1;
     // ---- verify: one trunk forward over the window, all rows' targets at once
     const int n_rows = want + 1;
-    CK(forward_dev(m, c, w.window, n_rows, true, w.vh, nullptr));
-    CK(head_greedy_dev(m, m->lm_head, w.vh, n_rows, 1, w.logits, w.targets));
+    CK(forward_greedy_dev(m, c, w.window, n_rows, true, w.vh, w.targets));
     m->prof.verify_steps += 1;
     // the one host round trip of the cycle (mtp_generate.rs:250-254)
     ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(hbuf, w.targets, 4 * (size_t)n_rows, cudaMemcpyDeviceToHost, s));
@@ -963,7 +1118,7 @@ int32_t orn_generate_step_mtp(orn_model* m, orn_cache* c, const uint32_t* prompt
     CK(orn_cache_rewind(c, k + 1));
     if (policy == ORN_POLICY_COMMITTED) {
       CK(set_mtp_pos(c, cycle_off + 1));
-      if (k > 0) CK(mtp_hidden(m, c, w.vh, w.window + 1, k, w.dh));
+      if (k > 0) CK(mtp_step(m, c, w.vh, w.window + 1, k, nullptr, w.dh, nullptr, true));
     }
     copy_bf16_kernel<<<(H + 255) / 256, 256, 0, s>>>(w.vh + (size_t)k * H, w.hrow, H);
     CK(orn_launch_check(ctx, "copy_bf16"));
