@@ -30,6 +30,11 @@ int32_t orn_ctx_create(int32_t device, orn_ctx** out) {
   }
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) c->sm_count = prop.multiProcessorCount;
+  if (cudaMalloc((void**)&c->dev_err, sizeof(int)) != cudaSuccess || cudaMemset(c->dev_err, 0, sizeof(int)) != cudaSuccess) {
+    cudaStreamDestroy(c->stream);
+    delete c;
+    return ORN_ERR_ALLOC;
+  }
   *out = c;
   return ORN_OK;
 }
@@ -40,6 +45,7 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   if (ctx->t0) cudaEventDestroy(ctx->t0);
   if (ctx->t1) cudaEventDestroy(ctx->t1);
+  cudaFree(ctx->dev_err);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return ORN_OK;
@@ -47,7 +53,13 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
 
 int32_t orn_sync(orn_ctx* ctx) {
   if (!ctx) return ORN_ERR_ARG;
+  int flag = 0;
+  ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(&flag, ctx->dev_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (flag != 0) {
+    cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream);
+    ORN_FAIL(ctx, ORN_ERR_TIMEOUT, "a kernel gave up waiting for its own asynchronous copies");
+  }
   return ORN_OK;
 }
 

@@ -17,15 +17,15 @@
 // (src/ops/linear.rs:23-144), add_rms_norm / rms_norm_gated (src/ops/norm.rs),
 // sparse_moe_block (src/ops/moe.rs:662-741), gdn_front + gated_delta_kernel
 // (src/ops/gdn.rs:191-413), Attention::forward (src/model/qwen3_5.rs:430-474).
+#include <algorithm>
+
 #include "orn_internal.h"
 #include "orn_quant.cuh"
 #include "fused.h"
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
-constexpr int SB = 4;  // row steps whose loads are issued together
+constexpr int kFusedThreads = 512;  // one CTA per SM: 16 warps, each with its own weight ring
 
 // ---------------------------------------------------------------------------
 // activation staging: a row of K floats re-ordered so that lane l's pieces of
@@ -129,6 +129,11 @@ template <> struct WU<ORN_A8> {
     w.q = ldg128_stream(L.w + row * L.K + 16 * u);
     w.sb = __ldg(reinterpret_cast<const uint32_t*>(L.s) + row * (L.K >> 6) + (u >> 2));
   }
+  // the same unit out of a row staged in shared memory: [codes K][sb K/16]
+  ORN_D static void lds(const uint8_t* b0, const uint8_t* b1, const LinDev&, int64_t, int u, W& w) {
+    w.q = *reinterpret_cast<const uint4*>(b0 + 16 * u);
+    w.sb = *reinterpret_cast<const uint32_t*>(b1 + 4 * (u >> 2));
+  }
   ORN_D static float fold(const W& w, const float* x, const float* sm, int, float acc) {
     const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
     float s1 = 0.f;
@@ -151,6 +156,11 @@ template <> struct WU<ORN_Q4K> {
     const int nb = L.K >> 8;
     w.q = ldg128_stream(L.w + (row * nb + (u >> 3)) * 128 + 16 * (u & 7));
     w.meta = ldg128(L.s + (row * nb + (u >> 3)) * 16);
+  }
+  // staged row: [codes nb*128][headers nb*16]
+  ORN_D static void lds(const uint8_t* b0, const uint8_t* b1, const LinDev&, int64_t, int u, W& w) {
+    w.q = *reinterpret_cast<const uint4*>(b0 + 16 * u);
+    w.meta = *reinterpret_cast<const uint4*>(b1 + (u >> 3) * 16);
   }
   ORN_D static float fold(const W& w, const float* x, const float* sm, int u, float acc) {
     const int g = (u & 7) >> 1;
@@ -197,6 +207,20 @@ template <> struct WU<ORN_Q6K> {
     w.sc4 = (lo & 0xff) | (((lo >> 16) & 0xff) << 8) | ((hi & 0xff) << 16) | (((hi >> 16) & 0xff) << 24);
     w.d = h2f(__ldg(reinterpret_cast<const uint16_t*>(L.b) + row * nb + blk));
   }
+  // staged row: [ql|qh nb*192][scales nb*16]; the 2-byte super-scale comes from global memory
+  ORN_D static void lds(const uint8_t* b0, const uint8_t* b1, const LinDev& L, int64_t row, int u, W& w) {
+    const int nb = L.K >> 8;
+    const int blk = u >> 4, j = u & 15, half = j >> 3, l0 = 4 * (j & 7);
+    const uint8_t* base = b0 + blk * 192;
+    w.qa = *reinterpret_cast<const uint32_t*>(base + 64 * half + l0);
+    w.qb = *reinterpret_cast<const uint32_t*>(base + 64 * half + 32 + l0);
+    w.qh = *reinterpret_cast<const uint32_t*>(base + 128 + 32 * half + l0);
+    const uint2 s8 = *reinterpret_cast<const uint2*>(b1 + blk * 16 + 8 * half);
+    const int is = l0 >> 4;
+    const uint32_t lo = s8.x >> (8 * is), hi = s8.y >> (8 * is);
+    w.sc4 = (lo & 0xff) | (((lo >> 16) & 0xff) << 8) | ((hi & 0xff) << 16) | (((hi >> 16) & 0xff) << 24);
+    w.d = h2f(__ldg(reinterpret_cast<const uint16_t*>(L.b) + row * nb + blk));
+  }
   ORN_D static float fold(const W& w, const float* x, const float*, int, float acc) {
     const uint32_t q1 = (w.qa & 0x0F0F0F0Fu) | ((w.qh & 0x03030303u) << 4);
     const uint32_t q2 = (w.qb & 0x0F0F0F0Fu) | ((w.qh & 0x0C0C0C0Cu) << 2);
@@ -226,6 +250,9 @@ template <> struct WU<ORN_BF16> {
   ORN_D static void load(const LinDev& L, int64_t row, int u, W& w) {
     w.q = ldg128_stream(L.w + (row * L.K + 8 * u) * 2);
   }
+  ORN_D static void lds(const uint8_t* b0, const uint8_t*, const LinDev&, int64_t, int u, W& w) {
+    w.q = *reinterpret_cast<const uint4*>(b0 + 16 * u);
+  }
   ORN_D static float fold(const W& w, const float* x, const float*, int, float acc) {
     float f[8];
     widen8(w.q, f);
@@ -235,57 +262,176 @@ template <> struct WU<ORN_BF16> {
   }
 };
 
-// One warp: dots of R weight rows (rowbase .. rowbase+R-1, `nvalid` of them
-// real) against M staged activation rows m0 .. m0+M-1.  Lane partials in
-// ascending unit order, then the xor-16..1 butterfly.
-template <int KIND, int M, int R>
-ORN_D void warp_rows_dot(const LinDev& L, int64_t rowbase, int nvalid, const XStage& X, int m0, int lane,
-                         float (&acc)[R][M]) {
+// ---------------------------------------------------------------------------
+// weight streaming: per-warp rings of shared-memory slots filled by bulk async
+// copies (cp.async.bulk, the 1-D TMA form) that complete on an mbarrier.
+// Rows of every format are contiguous in HBM, so one or two bulk copies bring a
+// whole row (codes, then scales/headers); lane 0 of a warp issues the copies for
+// the warp's next tasks, all 32 lanes wait on the slot's barrier and read their
+// own 16-byte pieces (consecutive lanes, consecutive addresses: no bank
+// conflicts).  A warp only ever waits for copies it issued itself, so there is
+// no cross-warp dependency; the wait is bounded and reports through `err`.
+// ---------------------------------------------------------------------------
+ORN_D uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+ORN_D void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+ORN_D void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+ORN_D void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+ORN_D bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+ORN_D void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+ORN_D void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+constexpr uint32_t kWaitLimit = 1u << 22;  // try_wait rounds before giving up (each round already blocks a while)
+
+// A row is streamed in chunks of kChunkSteps lane-steps (32 units each).  Bytes
+// of the two streams per step; a chunk of `units` units (a multiple of 8) is
+// [stream 0][stream 1], both multiples of 16 bytes.
+constexpr int kChunkSteps = 4;
+__host__ __device__ inline uint32_t step_bytes0(int kind) { return kind == ORN_Q6K ? 384 : 512; }
+__host__ __device__ inline uint32_t step_bytes1(int kind) {
+  return kind == ORN_A8 ? 32 : kind == ORN_Q4K ? 64 : kind == ORN_Q6K ? 32 : 0;
+}
+__host__ __device__ inline uint32_t units_bytes0(int kind, int units) { return kind == ORN_Q6K ? units * 12 : units * 16; }
+__host__ __device__ inline uint32_t units_bytes1(int kind, int units) {
+  return kind == ORN_A8 ? units : kind == ORN_Q4K ? units * 2 : kind == ORN_Q6K ? units : 0;
+}
+__host__ __device__ inline int kind_units(int kind, int K) { return K / kind_wpu(kind); }
+// largest chunk of a row, in bytes
+__host__ __device__ inline uint32_t chunk_bytes_max(int kind, int K) {
+  int units = kind_units(kind, K);
+  if (units > 32 * kChunkSteps) units = 32 * kChunkSteps;
+  return units_bytes0(kind, units) + units_bytes1(kind, units);
+}
+__host__ __device__ inline int row_chunks(int kind, int K) {
+  return (kind_units(kind, K) + 32 * kChunkSteps - 1) / (32 * kChunkSteps);
+}
+
+struct Ring {
+  uint32_t bar0;       // shared address of this warp's first barrier
+  uint32_t buf0;       // shared address of this warp's first slot
+  uint8_t* buf;        // generic address of the same
+  uint32_t slot_bytes;
+  int depth;
+  int* err;
+};
+
+// lane 0: request chunk c of a row of L into a slot at byte offset `off`;
+// returns the bytes requested (0 when the row has no such chunk)
+ORN_D uint32_t chunk_units(const LinDev& L, int c) {
+  const int units = kind_units(L.kind, L.K) - 32 * kChunkSteps * c;
+  return units <= 0 ? 0 : (units > 32 * kChunkSteps ? 32 * kChunkSteps : units);
+}
+ORN_D uint32_t chunk_bytes(const LinDev& L, int c) {
+  const int u = chunk_units(L, c);
+  return units_bytes0(L.kind, u) + units_bytes1(L.kind, u);
+}
+ORN_D void ring_copy_chunk(const Ring& R, int slot, uint32_t off, const LinDev& L, int64_t row, int c) {
+  const int u = chunk_units(L, c);
+  if (u == 0) return;
+  const uint32_t b0 = units_bytes0(L.kind, u), b1 = units_bytes1(L.kind, u);
+  const int tot = kind_units(L.kind, L.K);
+  const uint32_t bar = R.bar0 + 8 * slot;
+  const uint32_t dst = R.buf0 + slot * R.slot_bytes + off;
+  bulk_g2s(dst, L.w + row * (int64_t)units_bytes0(L.kind, tot) + (int64_t)c * kChunkSteps * step_bytes0(L.kind), b0, bar);
+  if (b1)
+    bulk_g2s(dst + b0, L.s + row * (int64_t)units_bytes1(L.kind, tot) + (int64_t)c * kChunkSteps * step_bytes1(L.kind),
+             b1, bar);
+}
+// all lanes: wait for a slot; false after the bounded wait ran out
+ORN_D bool ring_wait(const Ring& R, int slot, uint32_t parity) {
+  const uint32_t bar = R.bar0 + 8 * slot;
+  for (uint32_t it = 0; it < kWaitLimit; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  if ((threadIdx.x & 31) == 0) atomicExch(R.err, 1);
+  return false;
+}
+
+// carve the rings of all warps out of shared memory and initialise the barriers
+ORN_D void ring_setup(Ring& R, uint8_t* base, uint32_t slot_bytes, int depth, int* err) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base);
+  uint8_t* bufs = base + (((size_t)nwarps * depth * 8 + 127) & ~(size_t)127);
+  R.bar0 = smem_u32(bars + (size_t)warp * depth);
+  R.buf = bufs + (size_t)warp * depth * slot_bytes;
+  R.buf0 = smem_u32(R.buf);
+  R.slot_bytes = slot_bytes;
+  R.depth = depth;
+  R.err = err;
+  if (lane == 0)
+    for (int i = 0; i < depth; ++i) mbar_init(R.bar0 + 8 * i, 1);
+  fence_mbar_init();
+  fence_proxy_async();
+}
+__host__ __device__ inline size_t ring_bytes(int nwarps, int depth, uint32_t slot_bytes) {
+  return (((size_t)nwarps * depth * 8 + 127) & ~(size_t)127) + (size_t)nwarps * depth * slot_bytes;
+}
+
+// One warp, chunk c of one staged weight row (at `buf`): adds the chunk's units
+// to the lane partials acc[m] of activation rows m0 .. m0+M-1.  Units are
+// visited in ascending order within a lane across chunks; the caller zeroes
+// acc before chunk 0 and folds the lanes (warp_sum) after the last chunk.
+template <int KIND, int M>
+ORN_D void warp_chunk_dot(const uint8_t* buf, const LinDev& L, int64_t row, int c, const XStage& X, int m0, int lane,
+                          float (&acc)[M]) {
   using U = WU<KIND>;
   constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
+  const int cu = chunk_units(L, c);
+  // virtual stream bases so that absolute unit numbers index the chunk
+  const uint8_t* b0 = buf - (size_t)c * kChunkSteps * step_bytes0(KIND);
+  const uint8_t* b1 = buf + units_bytes0(KIND, cu) - (size_t)c * kChunkSteps * step_bytes1(KIND);
+  const int s_end = min(X.S, (c + 1) * kChunkSteps);
+  for (int s = c * kChunkSteps; s < s_end; ++s) {
+    const int u = lane + 32 * s;
+    if (u < X.units) {
+      typename U::W w;
+      U::lds(b0, b1, L, row, u, w);
 #pragma unroll
-  for (int r = 0; r < R; ++r)
+      for (int m = 0; m < M; ++m) {
+        float xv[P * 4];
+        const float4* xp = reinterpret_cast<const float4*>(X.xs) + ((size_t)((m0 + m) * X.S + s) * P) * 32 + lane;
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
-  for (int s0 = 0; s0 < X.S; s0 += SB) {
-    typename U::W w[SB][R];
-#pragma unroll
-    for (int sb = 0; sb < SB; ++sb) {
-      const int u = lane + 32 * (s0 + sb);
-      if (u < X.units) {
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-          if (r < nvalid) U::load(L, rowbase + r, u, w[sb][r]);
-      }
-    }
-#pragma unroll
-    for (int sb = 0; sb < SB; ++sb) {
-      const int s = s0 + sb;
-      const int u = lane + 32 * s;
-      if (u < X.units) {
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          float xv[P * 4];
-          const float4* xp = reinterpret_cast<const float4*>(X.xs) + ((size_t)((m0 + m) * X.S + s) * P) * 32 + lane;
-#pragma unroll
-          for (int p = 0; p < P; ++p) {
-            const float4 v = xp[p * 32];
-            xv[4 * p] = v.x; xv[4 * p + 1] = v.y; xv[4 * p + 2] = v.z; xv[4 * p + 3] = v.w;
-          }
-          float sm[NS > 0 ? NS : 1];
-#pragma unroll
-          for (int i = 0; i < NS; ++i) sm[i] = X.sums[((size_t)(m0 + m) * X.units + u) * NS + i];
-#pragma unroll
-          for (int r = 0; r < R; ++r)
-            if (r < nvalid) acc[r][m] = U::fold(w[sb][r], xv, sm, u, acc[r][m]);
+        for (int p = 0; p < P; ++p) {
+          const float4 v = xp[p * 32];
+          xv[4 * p] = v.x; xv[4 * p + 1] = v.y; xv[4 * p + 2] = v.z; xv[4 * p + 3] = v.w;
         }
+        float sm[NS > 0 ? NS : 1];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) sm[i] = X.sums[((size_t)(m0 + m) * X.units + u) * NS + i];
+        acc[m] = U::fold(w, xv, sm, u, acc[m]);
       }
     }
   }
-#pragma unroll
-  for (int r = 0; r < R; ++r)
-#pragma unroll
-    for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+}
+
+template <int M>
+ORN_D void warp_chunk_dot_kind(const uint8_t* buf, const LinDev& L, int64_t row, int c, const XStage* X, int m0,
+                               int lane, float (&acc)[M]) {
+  switch (L.kind) {
+    case ORN_A8: warp_chunk_dot<ORN_A8, M>(buf, L, row, c, X[ORN_A8], m0, lane, acc); break;
+    case ORN_Q4K: warp_chunk_dot<ORN_Q4K, M>(buf, L, row, c, X[ORN_Q4K], m0, lane, acc); break;
+    case ORN_Q6K: warp_chunk_dot<ORN_Q6K, M>(buf, L, row, c, X[ORN_Q6K], m0, lane, acc); break;
+    default: warp_chunk_dot<ORN_BF16, M>(buf, L, row, c, X[ORN_BF16], m0, lane, acc); break;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -366,7 +512,7 @@ ORN_D void run_prologue(const Prologue& P, float* lin, float* red) {
     // rms_norm_gated over 128-wide heads (kernels/ornith_norm.metal:119-185)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int heads = K / 128;
-    for (int pair = warp; pair < M * heads; pair += kWarps) {
+    for (int pair = warp; pair < M * heads; pair += (blockDim.x >> 5)) {
       const int base = pair * 128 + 4 * lane;
       float xv[4];
       float acc = 0.f;
@@ -417,7 +563,7 @@ struct RowJob {
   LinDev lin2;   // EPI_SWIGLU: the "up" matrix paired with lin ("gate")
   bf16_t* out;   // [M][O]
   int epi;       // EPI_STORE | EPI_SWIGLU
-  int tasks;     // ceil(O / R)
+  int tasks;     // rows of the job (one task per output row, or per gate/up pair)
 };
 struct RowJobs {
   RowJob job[4];
@@ -425,62 +571,93 @@ struct RowJobs {
   int kinds_mask;  // bit k set when some job has weights of kind k
 };
 
-template <int KIND, int M, int R>
-ORN_D void run_row_task(const RowJob& J, int task, const XStage& X, int lane) {
-  const int row0 = task * R;
-  const int nvalid = min(R, J.lin.O - row0);
-  float acc[R][M];
-  warp_rows_dot<KIND, M, R>(J.lin, row0, nvalid, X, 0, lane, acc);
-  if (J.epi == EPI_SWIGLU) {
-    float up[R][M];
-    warp_rows_dot<KIND, M, R>(J.lin2, row0, nvalid, X, 0, lane, up);
-    if (lane == 0) {
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-        if (r < nvalid)
-#pragma unroll
-          for (int m = 0; m < M; ++m)
-            J.out[(size_t)m * J.lin.O + row0 + r] = f2bf(orn_swiglu_bf(bfr(acc[r][m]), bfr(up[r][m])));
-    }
-  } else if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-      if (r < nvalid)
-#pragma unroll
-        for (int m = 0; m < M; ++m) J.out[(size_t)m * J.lin.O + row0 + r] = f2bf(acc[r][m]);
-  }
+// task t of the concatenated job list -> (job, row)
+ORN_D void job_of_task(const RowJobs& J, int t, int& j, int& row) {
+  j = 0;
+  while (t >= J.job[j].tasks) { t -= J.job[j].tasks; ++j; }
+  row = t;
 }
 
-template <int M, int R>
-__global__ void __launch_bounds__(kThreads) k_norm_gemv(Prologue P, RowJobs J) {
-  extern __shared__ __align__(16) float smem[];
-  float* lin = smem;
-  float* red = lin + (size_t)M * P.K;
-  float* next = red + M * 32 + M;
-  next = smem + (((next - smem) + 3) & ~3);
+template <int M>
+__global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJobs J, uint32_t slot_bytes, int depth,
+                                                                int nchunk, int* err) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  float* smem = reinterpret_cast<float*>(smem_raw);
+  // stages first, then a region used by the prologue's scratch and, after it, by the rings
+  float* next = smem;
   XStage X[4];
 #pragma unroll
   for (int k = 0; k < 4; ++k)
     if (J.kinds_mask & (1 << k)) next = stage_carve(next, k, M, P.K, X[k]);
+  uint8_t* region = reinterpret_cast<uint8_t*>(smem) + ((((uint8_t*)next - (uint8_t*)smem) + 127) & ~(size_t)127);
+  float* lin = reinterpret_cast<float*>(region);
+  float* red = lin + (size_t)M * P.K;
   run_prologue<M>(P, lin, red);
 #pragma unroll
   for (int k = 0; k < 4; ++k)
     if (J.kinds_mask & (1 << k)) stage_fill_kind(k, lin, P.K, X[k]);
+  __syncthreads();  // lin is dead from here on; the rings take its place
+  Ring R;
+  ring_setup(R, region, slot_bytes, depth, err);
   __syncthreads();
   const int lane = threadIdx.x & 31;
-  const int gw = blockIdx.x * kWarps + (threadIdx.x >> 5);
-  const int GW = gridDim.x * kWarps;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int GW = gridDim.x * (blockDim.x >> 5);
   int total = 0;
   for (int j = 0; j < J.njobs; ++j) total += J.job[j].tasks;
-  for (int t = gw; t < total; t += GW) {
-    int j = 0, tt = t;
-    while (tt >= J.job[j].tasks) { tt -= J.job[j].tasks; ++j; }
+  const int mine = (gw < total ? (total - gw + GW - 1) / GW : 0) * nchunk;
+  auto issue = [&](int i) {  // lane 0
+    int j, row;
+    const int ti = i / nchunk, c = i - ti * nchunk;
+    job_of_task(J, gw + ti * GW, j, row);
     const RowJob& job = J.job[j];
-    switch (job.lin.kind) {
-      case ORN_A8: run_row_task<ORN_A8, M, R>(job, tt, X[ORN_A8], lane); break;
-      case ORN_Q4K: run_row_task<ORN_Q4K, M, R>(job, tt, X[ORN_Q4K], lane); break;
-      case ORN_Q6K: run_row_task<ORN_Q6K, M, R>(job, tt, X[ORN_Q6K], lane); break;
-      default: run_row_task<ORN_BF16, M, R>(job, tt, X[ORN_BF16], lane); break;
+    const int slot = i % depth;
+    const uint32_t cb = chunk_bytes(job.lin, c);
+    mbar_expect_tx(R.bar0 + 8 * slot, job.epi == EPI_SWIGLU ? 2 * cb : cb);
+    ring_copy_chunk(R, slot, 0, job.lin, row, c);
+    if (job.epi == EPI_SWIGLU) ring_copy_chunk(R, slot, cb, job.lin2, row, c);
+  };
+  int issued = 0;
+  if (lane == 0)
+    for (; issued < depth && issued < mine; ++issued) issue(issued);
+  issued = __shfl_sync(0xffffffffu, issued, 0);
+  float acc[M], up[M];
+  for (int i = 0; i < mine; ++i) {
+    const int slot = i % depth;
+    if (!ring_wait(R, slot, (i / depth) & 1)) return;
+    int j, row;
+    const int ti = i / nchunk, c = i - ti * nchunk;
+    job_of_task(J, gw + ti * GW, j, row);
+    const RowJob& job = J.job[j];
+    const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
+    if (c == 0) {
+#pragma unroll
+      for (int m = 0; m < M; ++m) { acc[m] = 0.f; up[m] = 0.f; }
+    }
+    warp_chunk_dot_kind<M>(buf, job.lin, row, c, X, 0, lane, acc);
+    if (job.epi == EPI_SWIGLU) warp_chunk_dot_kind<M>(buf + chunk_bytes(job.lin, c), job.lin2, row, c, X, 0, lane, up);
+    if (c == nchunk - 1) {
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[m] = warp_sum(acc[m]);
+      if (job.epi == EPI_SWIGLU) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) up[m] = warp_sum(up[m]);
+        if (lane == 0)
+#pragma unroll
+          for (int m = 0; m < M; ++m)
+            job.out[(size_t)m * job.lin.O + row] = f2bf(orn_swiglu_bf(bfr(acc[m]), bfr(up[m])));
+      } else if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) job.out[(size_t)m * job.lin.O + row] = f2bf(acc[m]);
+      }
+    }
+    __syncwarp();
+    if (issued < mine) {
+      if (lane == 0) {
+        fence_proxy_async();
+        issue(issued);
+      }
+      ++issued;
     }
   }
 }
@@ -559,18 +736,19 @@ ORN_D void warp_softmax_topk(const bf16_t* logits, int n, int k, float* probs /*
   __syncwarp();
 }
 
-template <int KIND, int M, int R>
-__global__ void __launch_bounds__(kThreads) k_moe_up(MoeUpParams P) {
-  extern __shared__ __align__(16) float smem[];
-  float* lin = smem;                                   // [M][H]
+template <int KIND, int M>
+__global__ void __launch_bounds__(kFusedThreads, 1) k_moe_up(MoeUpParams P, uint32_t slot_bytes, int depth, int* err) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  float* smem = reinterpret_cast<float*>(smem_raw);
+  XStage X;
+  float* next = stage_carve(smem, KIND, M, P.H, X);
+  uint32_t* inds = reinterpret_cast<uint32_t*>(next);  // [M][k], lives through the kernel
+  next += M * P.k;
+  uint8_t* region = reinterpret_cast<uint8_t*>(smem) + ((((uint8_t*)next - (uint8_t*)smem) + 127) & ~(size_t)127);
+  float* lin = reinterpret_cast<float*>(region);       // [M][H]
   float* probs = lin + (size_t)M * P.H;                // [M][E]
   float* red = probs + (size_t)M * P.E;                // [M][32]
   float* scores = red + M * 32;                        // [M][k]
-  uint32_t* inds = reinterpret_cast<uint32_t*>(scores + M * P.k);  // [M][k]
-  float* next = reinterpret_cast<float*>(inds + M * P.k);
-  next = smem + (((next - smem) + 3) & ~3);
-  XStage X;
-  stage_carve(next, KIND, M, P.H, X);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (warp < M)
     warp_softmax_topk(P.logits + (size_t)warp * P.E, P.E, P.k, probs + (size_t)warp * P.E, red + warp * 32,
@@ -584,22 +762,53 @@ __global__ void __launch_bounds__(kThreads) k_moe_up(MoeUpParams P) {
     }
   stage_fill<KIND>(lin, P.H, X);
   __syncthreads();
-  const int per = (P.I + R - 1) / R;
-  const int total = M * P.k * per;
-  const int gw = blockIdx.x * kWarps + warp, GW = gridDim.x * kWarps;
-  for (int t = gw; t < total; t += GW) {
-    const int mj = t / per, og = t - mj * per;
+  Ring R;
+  ring_setup(R, region, slot_bytes, depth, err);
+  __syncthreads();
+  const int total = M * P.k * P.I;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + warp, GW = gridDim.x * (blockDim.x >> 5);
+  const int nchunk = row_chunks(KIND, P.H);
+  const int mine = (gw < total ? (total - gw + GW - 1) / GW : 0) * nchunk;
+  auto issue = [&](int i) {  // lane 0
+    const int ti = i / nchunk, c = i - ti * nchunk;
+    const int t = gw + ti * GW;
+    const int mj = t / P.I, o = t - mj * P.I;
+    const int64_t row = (int64_t)inds[mj] * P.I + o;
+    const int slot = i % depth;
+    const uint32_t cb = chunk_bytes(P.gate, c);
+    mbar_expect_tx(R.bar0 + 8 * slot, 2 * cb);
+    ring_copy_chunk(R, slot, 0, P.gate, row, c);
+    ring_copy_chunk(R, slot, cb, P.up, row, c);
+  };
+  int issued = 0;
+  if (lane == 0)
+    for (; issued < depth && issued < mine; ++issued) issue(issued);
+  issued = __shfl_sync(0xffffffffu, issued, 0);
+  float g[1], u[1];
+  for (int i = 0; i < mine; ++i) {
+    const int slot = i % depth;
+    if (!ring_wait(R, slot, (i / depth) & 1)) return;
+    const int ti = i / nchunk, c = i - ti * nchunk;
+    const int t = gw + ti * GW;
+    const int mj = t / P.I, o = t - mj * P.I;
     const int m = mj / P.k;
-    const int64_t e = inds[mj];
-    const int row0 = og * R;
-    const int nvalid = min(R, P.I - row0);
-    float g[R][1], u[R][1];
-    warp_rows_dot<KIND, 1, R>(P.gate, e * P.I + row0, nvalid, X, m, lane, g);
-    warp_rows_dot<KIND, 1, R>(P.up, e * P.I + row0, nvalid, X, m, lane, u);
-    if (lane == 0)
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-        if (r < nvalid) P.act[(size_t)mj * P.I + row0 + r] = f2bf(orn_swiglu_bf(bfr(g[r][0]), bfr(u[r][0])));
+    const int64_t row = (int64_t)inds[mj] * P.I + o;
+    const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
+    if (c == 0) { g[0] = 0.f; u[0] = 0.f; }
+    warp_chunk_dot<KIND, 1>(buf, P.gate, row, c, X, m, lane, g);
+    warp_chunk_dot<KIND, 1>(buf + chunk_bytes(P.gate, c), P.up, row, c, X, m, lane, u);
+    if (c == nchunk - 1) {
+      const float gs = warp_sum(g[0]), us = warp_sum(u[0]);
+      if (lane == 0) P.act[(size_t)mj * P.I + o] = f2bf(orn_swiglu_bf(bfr(gs), bfr(us)));
+    }
+    __syncwarp();
+    if (issued < mine) {
+      if (lane == 0) {
+        fence_proxy_async();
+        issue(issued);
+      }
+      ++issued;
+    }
   }
 }
 
@@ -620,19 +829,20 @@ struct MoeDownParams {
 };
 
 template <int KIND, int M>
-__global__ void __launch_bounds__(kThreads) k_moe_down(MoeDownParams P) {
-  extern __shared__ __align__(16) float smem[];
+__global__ void __launch_bounds__(kFusedThreads, 1) k_moe_down(MoeDownParams P, uint32_t slot_bytes, int depth, int* err) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  float* smem = reinterpret_cast<float*>(smem_raw);
   const int rows = M * P.k;
-  float* lin = smem;                                   // [rows][I] then [M][SI]
-  float* lin2 = lin + (size_t)rows * P.I;
-  float* wts = lin2 + (size_t)M * P.SI;                // [M][k] normalised scores
+  XStage X, XS;
+  float* next = stage_carve(smem, KIND, rows, P.I, X);
+  next = stage_carve(next, KIND, M, P.SI, XS);
+  float* wts = next;                                   // [M][k] normalised scores
   float* gsig = wts + rows;                            // [M]
   uint32_t* inds = reinterpret_cast<uint32_t*>(gsig + M);
-  float* next = reinterpret_cast<float*>(inds + rows);
-  next = smem + (((next - smem) + 3) & ~3);
-  XStage X, XS;
-  next = stage_carve(next, KIND, rows, P.I, X);
-  stage_carve(next, KIND, M, P.SI, XS);
+  next = reinterpret_cast<float*>(inds + rows);
+  uint8_t* region = reinterpret_cast<uint8_t*>(smem) + ((((uint8_t*)next - (uint8_t*)smem) + 127) & ~(size_t)127);
+  float* lin = reinterpret_cast<float*>(region);       // [rows][I] then [M][SI]
+  float* lin2 = lin + (size_t)rows * P.I;
   for (int i = threadIdx.x; i < rows * P.I; i += blockDim.x) lin[i] = bf2f(P.act[i]);
   for (int i = threadIdx.x; i < M * P.SI; i += blockDim.x) lin2[i] = bf2f(P.sact[i]);
   if (threadIdx.x < M) {
@@ -641,8 +851,8 @@ __global__ void __launch_bounds__(kThreads) k_moe_down(MoeDownParams P) {
     if (P.normalize)
       for (int j = 0; j < P.k; ++j) denom = bfr(bf2f(P.scores[m * P.k + j]) + denom);
     for (int j = 0; j < P.k; ++j) {
-      const float s = bf2f(P.scores[m * P.k + j]);
-      wts[m * P.k + j] = P.normalize ? bfr(s / denom) : s;
+      const float sc = bf2f(P.scores[m * P.k + j]);
+      wts[m * P.k + j] = P.normalize ? bfr(sc / denom) : sc;
       inds[m * P.k + j] = P.inds[m * P.k + j];
     }
     gsig[m] = orn_sigmoid_bf(bf2f(P.gs[m]));
@@ -651,59 +861,71 @@ __global__ void __launch_bounds__(kThreads) k_moe_down(MoeDownParams P) {
   stage_fill<KIND>(lin, P.I, X);
   stage_fill<KIND>(lin2, P.SI, XS);
   __syncthreads();
-  using U = WU<KIND>;
-  constexpr int PP = Lay<KIND>::P, NS = Lay<KIND>::NS;
-  constexpr int KMAX = 8;
+  Ring R;
+  ring_setup(R, region, slot_bytes, depth, err);
+  __syncthreads();
+  // a warp owns output columns c = gw, gw+GW, ...; per column it consumes the
+  // M*k routed rows in (m, j) order and then the shared expert's row
   const int lane = threadIdx.x & 31;
-  const int gw = blockIdx.x * kWarps + (threadIdx.x >> 5), GW = gridDim.x * kWarps;
-  for (int c = gw; c < P.H; c += GW) {
-    float outv[M];
-#pragma unroll
-    for (int m = 0; m < M; ++m) {
-      float accj[KMAX + 1];
-#pragma unroll
-      for (int j = 0; j <= KMAX; ++j) accj[j] = 0.f;
-      // routed rows: all k experts' units of this step are requested before any is consumed
-      for (int s = 0; s < X.S; ++s) {
-        const int u = lane + 32 * s;
-        if (u < X.units) {
-          typename U::W w[KMAX];
-#pragma unroll
-          for (int j = 0; j < KMAX; ++j)
-            if (j < P.k) U::load(P.down, (int64_t)inds[m * P.k + j] * P.H + c, u, w[j]);
-#pragma unroll
-          for (int j = 0; j < KMAX; ++j)
-            if (j < P.k) {
-              float xv[PP * 4];
-              const float4* xp = reinterpret_cast<const float4*>(X.xs) + ((size_t)((m * P.k + j) * X.S + s) * PP) * 32 + lane;
-#pragma unroll
-              for (int p = 0; p < PP; ++p) {
-                const float4 v = xp[p * 32];
-                xv[4 * p] = v.x; xv[4 * p + 1] = v.y; xv[4 * p + 2] = v.z; xv[4 * p + 3] = v.w;
-              }
-              float sm[NS > 0 ? NS : 1];
-#pragma unroll
-              for (int i = 0; i < NS; ++i) sm[i] = X.sums[((size_t)(m * P.k + j) * X.units + u) * NS + i];
-              accj[j] = U::fold(w[j], xv, sm, u, accj[j]);
-            }
-        }
-      }
-      float sd[1][1];
-      warp_rows_dot<KIND, 1, 1>(P.sh_down, c, 1, XS, m, lane, sd);
-      float acc = 0.f;
-#pragma unroll
-      for (int j = 0; j < KMAX; ++j)
-        if (j < P.k) {
-          const float d = warp_sum(accj[j]);
-          const float weighted = bfr(bfr(d) * wts[m * P.k + j]);
-          acc = bfr(weighted + acc);
-        }
-      const float gated = bfr(gsig[m] * bfr(sd[0][0]));
-      outv[m] = acc + gated;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), GW = gridDim.x * (blockDim.x >> 5);
+  const int per = rows + 1;
+  const int cols = gw < P.H ? (P.H - gw + GW - 1) / GW : 0;
+  const int mine = cols * per;
+  auto issue = [&](int i) {  // lane 0
+    const int ci = i / per, q = i - ci * per;
+    const int c = gw + ci * GW;
+    const int slot = i % depth;
+    // the intermediate sizes are short enough for one chunk per row (checked at launch)
+    if (q < rows) {
+      mbar_expect_tx(R.bar0 + 8 * slot, chunk_bytes(P.down, 0));
+      ring_copy_chunk(R, slot, 0, P.down, (int64_t)inds[q] * P.H + c, 0);
+    } else {
+      mbar_expect_tx(R.bar0 + 8 * slot, chunk_bytes(P.sh_down, 0));
+      ring_copy_chunk(R, slot, 0, P.sh_down, c, 0);
     }
-    if (lane == 0)
+  };
+  int issued = 0;
+  if (lane == 0)
+    for (; issued < depth && issued < mine; ++issued) issue(issued);
+  issued = __shfl_sync(0xffffffffu, issued, 0);
+  float acc[M];
 #pragma unroll
-      for (int m = 0; m < M; ++m) P.out[(size_t)m * P.H + c] = f2bf(outv[m]);
+  for (int m = 0; m < M; ++m) acc[m] = 0.f;
+  for (int i = 0; i < mine; ++i) {
+    const int slot = i % depth;
+    if (!ring_wait(R, slot, (i / depth) & 1)) return;
+    const int ci = i / per, q = i - ci * per;
+    const int c = gw + ci * GW;
+    const uint8_t* rowbuf = R.buf + (size_t)slot * slot_bytes;
+    if (q < rows) {
+      float d[1] = {0.f};
+      warp_chunk_dot<KIND, 1>(rowbuf, P.down, (int64_t)inds[q] * P.H + c, 0, X, q, lane, d);
+      const float weighted = bfr(bfr(warp_sum(d[0])) * wts[q]);
+      const int m = q / P.k;
+#pragma unroll
+      for (int mm = 0; mm < M; ++mm)
+        if (mm == m) acc[mm] = bfr(weighted + acc[mm]);
+    } else {
+      float sd[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) sd[m] = 0.f;
+      warp_chunk_dot<KIND, M>(rowbuf, P.sh_down, c, 0, XS, 0, lane, sd);
+#pragma unroll
+      for (int m = 0; m < M; ++m) sd[m] = warp_sum(sd[m]);
+      if (lane == 0)
+#pragma unroll
+        for (int m = 0; m < M; ++m) P.out[(size_t)m * P.H + c] = f2bf(acc[m] + bfr(gsig[m] * bfr(sd[m])));
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    }
+    __syncwarp();
+    if (issued < mine) {
+      if (lane == 0) {
+        fence_proxy_async();
+        issue(issued);
+      }
+      ++issued;
+    }
   }
 }
 
@@ -980,57 +1202,97 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-int persistent_grid(orn_ctx* ctx) { return ctx->sm_count * 2; }
+constexpr size_t kSmemBudget = 200 * 1024;
 
 template <typename Kern>
 int set_smem(orn_ctx* ctx, Kern kern, size_t bytes) {
-  if (bytes > 220 * 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "fused kernel: staged activations exceed shared memory");
+  if (bytes > 227 * 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "fused kernel: staged activations exceed shared memory");
   if (bytes > 48 * 1024)
     ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
   return ORN_OK;
 }
 
+// ring depth that fits beside `fixed` bytes of stages, and the dynamic shared
+// memory of the launch: max(prologue scratch, rings) shares one region
+int plan_smem(orn_ctx* ctx, size_t fixed, size_t scratch, uint32_t slot_bytes, int* depth, size_t* total) {
+  const int nwarps = kFusedThreads / 32;
+  fixed = (fixed + 127) & ~(size_t)127;
+  int d = 8;
+  while (d > 2 && fixed + ring_bytes(nwarps, d, slot_bytes) > kSmemBudget) --d;
+  const size_t rb = ring_bytes(nwarps, d, slot_bytes);
+  *depth = d;
+  *total = fixed + (rb > scratch ? rb : scratch) + 128;
+  if (*total > 227 * 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "fused kernel: rows too long for the shared-memory rings");
+  return ORN_OK;
+}
+
 template <int M>
 int launch_norm_gemv(orn_ctx* ctx, cudaStream_t s, const Prologue& P, RowJobs& J) {
-  constexpr int R = 2;
-  size_t fl = (size_t)M * P.K + M * 33 + 4;
   J.kinds_mask = 0;
+  uint32_t slot = 0;
+  int nchunk = 1;
   for (int j = 0; j < J.njobs; ++j) {
-    J.kinds_mask |= 1 << J.job[j].lin.kind;
-    J.job[j].tasks = (J.job[j].lin.O + R - 1) / R;
-    if (J.job[j].lin.K != P.K) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: weight K differs from the staged row");
-    if (J.job[j].epi == EPI_SWIGLU && J.job[j].lin2.kind != J.job[j].lin.kind)
-      ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: gate and up projections must share a format");
+    RowJob& job = J.job[j];
+    J.kinds_mask |= 1 << job.lin.kind;
+    job.tasks = job.lin.O;
+    if (job.lin.K != P.K) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: weight K differs from the staged row");
+    if (job.lin.K % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: K must be a multiple of 256");
+    uint32_t rb = chunk_bytes_max(job.lin.kind, job.lin.K);
+    nchunk = std::max(nchunk, row_chunks(job.lin.kind, job.lin.K));
+    if (job.epi == EPI_SWIGLU) {
+      if (job.lin2.kind != job.lin.kind || job.lin2.K != job.lin.K || job.lin2.O != job.lin.O)
+        ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: gate and up projections must share format and shape");
+      rb *= 2;
+    }
+    slot = rb > slot ? rb : slot;
   }
+  size_t fixed = 0;
   for (int k = 0; k < 4; ++k)
-    if (J.kinds_mask & (1 << k)) fl += stage_floats(k, M, P.K);
-  const size_t bytes = fl * sizeof(float);
-  int rc = set_smem(ctx, k_norm_gemv<M, R>, bytes);
+    if (J.kinds_mask & (1 << k)) fixed += stage_floats(k, M, P.K) * sizeof(float);
+  const size_t scratch = ((size_t)M * P.K + M * 33 + 8) * sizeof(float);
+  int depth;
+  size_t bytes;
+  int rc = plan_smem(ctx, fixed, scratch, slot, &depth, &bytes);
   if (rc != ORN_OK) return rc;
-  k_norm_gemv<M, R><<<persistent_grid(ctx), kThreads, bytes, s>>>(P, J);
+  rc = set_smem(ctx, k_norm_gemv<M>, bytes);
+  if (rc != ORN_OK) return rc;
+  k_norm_gemv<M><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, J, slot, depth, nchunk, ctx->dev_err);
   return orn_launch_check(ctx, "k_norm_gemv");
 }
 
 template <int KIND, int M>
 int launch_moe_up_k(orn_ctx* ctx, cudaStream_t s, const MoeUpParams& P) {
-  constexpr int R = 2;
-  const size_t fl = (size_t)M * P.H + (size_t)M * P.E + M * 32 + 2 * M * P.k + 4 + stage_floats(KIND, M, P.H);
-  const size_t bytes = fl * sizeof(float);
-  int rc = set_smem(ctx, k_moe_up<KIND, M, R>, bytes);
+  if (P.H % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_up: hidden must be a multiple of 256");
+  const size_t fixed = stage_floats(KIND, M, P.H) * sizeof(float) + (size_t)M * P.k * 4;
+  const size_t scratch = ((size_t)M * P.H + (size_t)M * P.E + M * 32 + M * P.k + 8) * sizeof(float);
+  const uint32_t slot = 2 * chunk_bytes_max(KIND, P.H);
+  int depth;
+  size_t bytes;
+  int rc = plan_smem(ctx, fixed, scratch, slot, &depth, &bytes);
   if (rc != ORN_OK) return rc;
-  k_moe_up<KIND, M, R><<<persistent_grid(ctx), kThreads, bytes, s>>>(P);
+  rc = set_smem(ctx, k_moe_up<KIND, M>, bytes);
+  if (rc != ORN_OK) return rc;
+  k_moe_up<KIND, M><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, slot, depth, ctx->dev_err);
   return orn_launch_check(ctx, "k_moe_up");
 }
 
 template <int KIND, int M>
 int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
+  if (P.I % 256 || P.SI % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: intermediate sizes must be multiples of 256");
   const int rows = M * P.k;
-  const size_t fl = (size_t)rows * P.I + (size_t)M * P.SI + 2 * rows + M + 4 + stage_floats(KIND, rows, P.I) +
-                    stage_floats(KIND, M, P.SI);
-  const size_t bytes = fl * sizeof(float);
-  int rc = set_smem(ctx, k_moe_down<KIND, M>, bytes);
+  const size_t fixed = (stage_floats(KIND, rows, P.I) + stage_floats(KIND, M, P.SI) + 2 * rows + M) * sizeof(float);
+  const size_t scratch = ((size_t)rows * P.I + (size_t)M * P.SI + 8) * sizeof(float);
+  if (row_chunks(KIND, P.I) != 1 || row_chunks(KIND, P.SI) != 1)
+    ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: intermediate size too long for one streamed chunk");
+  const uint32_t r0 = chunk_bytes_max(KIND, P.I), r1 = chunk_bytes_max(KIND, P.SI);
+  const uint32_t slot = r0 > r1 ? r0 : r1;
+  int depth;
+  size_t bytes;
+  int rc = plan_smem(ctx, fixed, scratch, slot, &depth, &bytes);
   if (rc != ORN_OK) return rc;
-  k_moe_down<KIND, M><<<persistent_grid(ctx), kThreads, bytes, s>>>(P);
+  rc = set_smem(ctx, k_moe_down<KIND, M>, bytes);
+  if (rc != ORN_OK) return rc;
+  k_moe_down<KIND, M><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, slot, depth, ctx->dev_err);
   return orn_launch_check(ctx, "k_moe_down");
 }
 

@@ -18,6 +18,7 @@ struct orn_ctx {
   int64_t launches = 0;  // kernels launched through this context
   int sm_count = 148;
   cudaEvent_t t0 = nullptr, t1 = nullptr;  // orn_timer_start / orn_timer_stop
+  int* dev_err = nullptr;  // set by a kernel whose bounded wait ran out
 };
 
 // Device-resident weight matrix [E, O, K].
