@@ -326,7 +326,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--gen-tokens", type=int, default=200, help="tokens per generation (profiling runs use fewer)")
+    ap.add_argument("--prompt-len", type=int, default=51)
     args = ap.parse_args()
+    global GEN_TOKENS, PROMPT_LEN
+    GEN_TOKENS, PROMPT_LEN = args.gen_tokens, args.prompt_len
     if args.impl == "reference":
         reference(args)
     else:

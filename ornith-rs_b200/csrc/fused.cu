@@ -23,6 +23,14 @@
 #include "orn_quant.cuh"
 #include "fused.h"
 
+#ifdef ORN_DEBUG_CLOCKS
+__device__ long long g_dbg[32];
+#define DBG(i) do { if (blockIdx.x == 3 && threadIdx.x == 0) g_dbg[i] = clock64(); } while (0)
+extern "C" int orn_debug_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_dbg, sizeof(long long) * 32); }
+#else
+#define DBG(i)
+#endif
+
 namespace {
 
 constexpr int kFusedThreads = 512;  // one CTA per SM: 16 warps, each with its own weight ring
@@ -73,39 +81,32 @@ ORN_D float* stage_carve(float* base, int kind, int rows, int K, XStage& X) {
   return X.sums + (size_t)rows * X.units * kind_ns(kind);
 }
 
-// lin: [rows][K] floats (row stride `stride`) -> stage; block-wide, no sync inside
+// lin: [rows][K] floats (row stride `stride`) -> stage; block-wide, no sync
+// inside.  A thread owns whole units: it moves the unit's P pieces to their
+// permuted places and, for the formats that need it, adds the unit's elements
+// in ascending order into the staged sum.
 template <int KIND>
 ORN_D void stage_fill(const float* lin, int stride, const XStage& X) {
-  constexpr int P = Lay<KIND>::P;
-  const int total = X.rows * X.S * P * 32;
-  for (int slot = threadIdx.x; slot < total; slot += blockDim.x) {
-    const int lane = slot & 31;
-    const int p = (slot >> 5) % P;
-    const int s = (slot / (32 * P)) % X.S;
-    const int m = slot / (32 * P * X.S);
-    const int u = lane + 32 * s;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (u < X.units) v = *reinterpret_cast<const float4*>(lin + (size_t)m * stride + src_index<KIND>(u, p));
-    reinterpret_cast<float4*>(X.xs)[slot] = v;
-  }
-  if (Lay<KIND>::NS == 1) {
-    for (int i = threadIdx.x; i < X.rows * X.units; i += blockDim.x) {
-      const int m = i / X.units, u = i - m * X.units;
-      const float* src = lin + (size_t)m * stride + 16 * u;
-      float s = 0.f;
-#pragma unroll
-      for (int k = 0; k < 16; ++k) s = s + src[k];
-      X.sums[i] = s;
-    }
-  } else if (Lay<KIND>::NS == 2) {
-    for (int i = threadIdx.x; i < X.rows * X.units; i += blockDim.x) {
-      const int m = i / X.units, u = i - m * X.units;
-      const float* src = lin + (size_t)m * stride + src_index<ORN_Q4K>(u, 0);
+  constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
+  const int padded = X.S * 32;  // unit slots per row, including the empty tail
+  for (int m = 0; m < X.rows; ++m) {
+    const float* src = lin + (size_t)m * stride;
+    float4* dst = reinterpret_cast<float4*>(X.xs) + (size_t)m * padded * P;
+    for (int u = threadIdx.x; u < padded; u += blockDim.x) {
+      const int lane = u & 31, s = u >> 5;
       float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int k = 0; k < 16; ++k) { s0 = s0 + src[k]; s1 = s1 + src[32 + k]; }
-      X.sums[2 * i] = s0;
-      X.sums[2 * i + 1] = s1;
+      for (int p = 0; p < P; ++p) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (u < X.units) v = *reinterpret_cast<const float4*>(src + src_index<KIND>(u, p));
+        dst[(s * P + p) * 32 + lane] = v;
+        if (NS == 1 || (NS == 2 && p < 4)) { s0 = s0 + v.x; s0 = s0 + v.y; s0 = s0 + v.z; s0 = s0 + v.w; }
+        if (NS == 2 && p >= 4) { s1 = s1 + v.x; s1 = s1 + v.y; s1 = s1 + v.z; s1 = s1 + v.w; }
+      }
+      if (u < X.units) {
+        if (NS == 1) X.sums[(size_t)m * X.units + u] = s0;
+        if (NS == 2) { X.sums[((size_t)m * X.units + u) * 2] = s0; X.sums[((size_t)m * X.units + u) * 2 + 1] = s1; }
+      }
     }
   }
 }
@@ -284,23 +285,25 @@ ORN_D void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
+constexpr uint32_t kWaitHintNs = 200000;  // a waiting warp may be suspended this long per try
 ORN_D bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kWaitHintNs)
       : "memory");
   return ok != 0;
 }
 ORN_D void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 ORN_D void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
-constexpr uint32_t kWaitLimit = 1u << 22;  // try_wait rounds before giving up (each round already blocks a while)
+constexpr int kDownCols = 2;  // consecutive output columns a warp takes per bulk copy in the down projection
+constexpr uint32_t kWaitLimit = 1u << 14;  // try_wait rounds before giving up (each round may sleep kWaitHintNs)
 
 // A row is streamed in chunks of kChunkSteps lane-steps (32 units each).  Bytes
 // of the two streams per step; a chunk of `units` units (a multiple of 8) is
@@ -386,19 +389,18 @@ __host__ __device__ inline size_t ring_bytes(int nwarps, int depth, uint32_t slo
   return (((size_t)nwarps * depth * 8 + 127) & ~(size_t)127) + (size_t)nwarps * depth * slot_bytes;
 }
 
-// One warp, chunk c of one staged weight row (at `buf`): adds the chunk's units
+// One warp, chunk c of one staged weight row (streams at p0 / p1): adds the chunk's units
 // to the lane partials acc[m] of activation rows m0 .. m0+M-1.  Units are
 // visited in ascending order within a lane across chunks; the caller zeroes
 // acc before chunk 0 and folds the lanes (warp_sum) after the last chunk.
 template <int KIND, int M>
-ORN_D void warp_chunk_dot(const uint8_t* buf, const LinDev& L, int64_t row, int c, const XStage& X, int m0, int lane,
-                          float (&acc)[M]) {
+ORN_D void warp_chunk_dot(const uint8_t* p0, const uint8_t* p1, const LinDev& L, int64_t row, int c, const XStage& X,
+                          int m0, int lane, float (&acc)[M]) {
   using U = WU<KIND>;
   constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
-  const int cu = chunk_units(L, c);
   // virtual stream bases so that absolute unit numbers index the chunk
-  const uint8_t* b0 = buf - (size_t)c * kChunkSteps * step_bytes0(KIND);
-  const uint8_t* b1 = buf + units_bytes0(KIND, cu) - (size_t)c * kChunkSteps * step_bytes1(KIND);
+  const uint8_t* b0 = p0 - (size_t)c * kChunkSteps * step_bytes0(KIND);
+  const uint8_t* b1 = p1 - (size_t)c * kChunkSteps * step_bytes1(KIND);
   const int s_end = min(X.S, (c + 1) * kChunkSteps);
   for (int s = c * kChunkSteps; s < s_end; ++s) {
     const int u = lane + 32 * s;
@@ -423,14 +425,47 @@ ORN_D void warp_chunk_dot(const uint8_t* buf, const LinDev& L, int64_t row, int 
   }
 }
 
-template <int M>
-ORN_D void warp_chunk_dot_kind(const uint8_t* buf, const LinDev& L, int64_t row, int c, const XStage* X, int m0,
-                               int lane, float (&acc)[M]) {
-  switch (L.kind) {
-    case ORN_A8: warp_chunk_dot<ORN_A8, M>(buf, L, row, c, X[ORN_A8], m0, lane, acc); break;
-    case ORN_Q4K: warp_chunk_dot<ORN_Q4K, M>(buf, L, row, c, X[ORN_Q4K], m0, lane, acc); break;
-    case ORN_Q6K: warp_chunk_dot<ORN_Q6K, M>(buf, L, row, c, X[ORN_Q6K], m0, lane, acc); break;
-    default: warp_chunk_dot<ORN_BF16, M>(buf, L, row, c, X[ORN_BF16], m0, lane, acc); break;
+// The same for R weight rows at once (row r's streams at p0 + r*st0, p1 + r*st1):
+// the staged activations of a step are read once and folded into R rows.  The
+// four steps of a chunk are unrolled so that every shared-memory access is a
+// hoisted base plus an immediate.
+template <int KIND, int M, int R>
+ORN_D void warp_chunk_dot_rows(const uint8_t* p0, uint32_t st0, const uint8_t* p1, uint32_t st1, const LinDev& L,
+                               int64_t row, int nvalid, int c, const XStage& X, int m0, int lane, float (&acc)[R][M]) {
+  using U = WU<KIND>;
+  constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
+  const int s_base = c * kChunkSteps;
+  const uint8_t* b0 = p0 - (size_t)c * kChunkSteps * step_bytes0(KIND);
+  const uint8_t* b1 = p1 - (size_t)c * kChunkSteps * step_bytes1(KIND);
+  const float4* xbase = reinterpret_cast<const float4*>(X.xs) + (size_t)(m0 * X.S + s_base) * (P * 32) + lane;
+  const int xrow = X.S * P * 32;  // float4 per activation row
+  const float* sbase = X.sums + ((size_t)m0 * X.units + 32 * s_base + lane) * NS;
+  const int srow = X.units * NS;
+#pragma unroll
+  for (int ss = 0; ss < kChunkSteps; ++ss) {
+    const int u = lane + 32 * (s_base + ss);
+    if (u < X.units) {
+      typename U::W w[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        if (r < nvalid) U::lds(b0 + r * st0, b1 + r * st1, L, row + r, u, w[r]);
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float xv[P * 4];
+        const float4* xp = xbase + m * xrow + ss * (P * 32);
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+          const float4 v = xp[p * 32];
+          xv[4 * p] = v.x; xv[4 * p + 1] = v.y; xv[4 * p + 2] = v.z; xv[4 * p + 3] = v.w;
+        }
+        float sm[NS > 0 ? NS : 1];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) sm[i] = sbase[m * srow + ss * 32 * NS + i];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          if (r < nvalid) acc[r][m] = U::fold(w[r], xv, sm, u, acc[r][m]);
+      }
+    }
   }
 }
 
@@ -450,13 +485,12 @@ ORN_D void block_rms_inv(const float* lin, int stride, int rows, int n, float ep
   for (int m = 0; m < rows; ++m) {
     for (int vt = threadIdx.x; vt < nvt_pad; vt += blockDim.x) {
       float acc = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int idx = 4 * vt + i;
-        if (idx < n) {
-          const float v = lin[(size_t)m * stride + idx];
-          acc = fmaf(v, v, acc);
-        }
+      if (4 * vt < n) {  // n is a multiple of 4 here
+        const float4 v = *reinterpret_cast<const float4*>(lin + (size_t)m * stride + 4 * vt);
+        acc = fmaf(v.x, v.x, acc);
+        acc = fmaf(v.y, v.y, acc);
+        acc = fmaf(v.z, v.z, acc);
+        acc = fmaf(v.w, v.w, acc);
       }
       acc = warp_sum(acc);
       if (lane == 0) red[m * 32 + (vt >> 5)] = acc;
@@ -488,31 +522,61 @@ struct Prologue {
   float eps;
 };
 
-// scratch: red[M*32 + M] floats
+// scratch: red[M*32 + M] floats.  Every loop walks (row m, 8-element group) so
+// that no index needs a division and global traffic is 128-bit.
 template <int M>
 ORN_D void run_prologue(const Prologue& P, float* lin, float* red) {
   const int K = P.K;
   float* inv = red + M * 32;
   if (P.mode == PRO_ADDNORM) {
-    for (int i = threadIdx.x; i < M * K; i += blockDim.x) {
-      float v = bf2f(P.a[i]);
-      if (P.b != nullptr) v = bfr(v + bf2f(P.b[i]));
-      lin[i] = v;
-      if (P.sum_out != nullptr && blockIdx.x == 0) P.sum_out[i] = f2bf(v);
+    // the norm weight does not depend on the statistics: fetch it before the reduction
+    float wv[4] = {0.f, 0.f, 0.f, 0.f};
+    const int c0 = threadIdx.x * 4;  // K <= 4 * blockDim.x is checked at launch
+    if (c0 < K) {
+      const uint2 ww = __ldg(reinterpret_cast<const uint2*>(P.w + c0));
+      wv[0] = bf_lo(ww.x); wv[1] = bf_hi(ww.x); wv[2] = bf_lo(ww.y); wv[3] = bf_hi(ww.y);
     }
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+      if (c0 < K) {
+        const uint2 av = __ldg(reinterpret_cast<const uint2*>(P.a + (size_t)m * K + c0));
+        float v[4] = {bf_lo(av.x), bf_hi(av.x), bf_lo(av.y), bf_hi(av.y)};
+        if (P.b != nullptr) {
+          const uint2 bv = __ldg(reinterpret_cast<const uint2*>(P.b + (size_t)m * K + c0));
+          v[0] = bfr(v[0] + bf_lo(bv.x)); v[1] = bfr(v[1] + bf_hi(bv.x));
+          v[2] = bfr(v[2] + bf_lo(bv.y)); v[3] = bfr(v[3] + bf_hi(bv.y));
+        }
+        *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) = make_float4(v[0], v[1], v[2], v[3]);
+        if (P.sum_out != nullptr && blockIdx.x == 0) {
+          uint2 o;
+          o.x = (uint32_t)f2bf(v[0]) | ((uint32_t)f2bf(v[1]) << 16);
+          o.y = (uint32_t)f2bf(v[2]) | ((uint32_t)f2bf(v[3]) << 16);
+          *reinterpret_cast<uint2*>(P.sum_out + (size_t)m * K + c0) = o;
+        }
+      }
     __syncthreads();
     block_rms_inv(lin, K, M, K, P.eps, red, inv);
-    for (int i = threadIdx.x; i < M * K; i += blockDim.x) {
-      const int m = i / K, c = i - m * K;
-      lin[i] = bfr(bf2f(P.w[c]) * bfr(lin[i] * inv[m]));
-    }
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+      if (c0 < K) {
+        float4 v = *reinterpret_cast<const float4*>(lin + (size_t)m * K + c0);
+        const float iv = inv[m];
+        v.x = bfr(wv[0] * bfr(v.x * iv)); v.y = bfr(wv[1] * bfr(v.y * iv));
+        v.z = bfr(wv[2] * bfr(v.z * iv)); v.w = bfr(wv[3] * bfr(v.w * iv));
+        *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) = v;
+      }
   } else if (P.mode == PRO_PLAIN) {
-    for (int i = threadIdx.x; i < M * K; i += blockDim.x) lin[i] = bf2f(P.a[i]);
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+      for (int c = threadIdx.x * 4; c < K; c += blockDim.x * 4) {
+        const uint2 av = __ldg(reinterpret_cast<const uint2*>(P.a + (size_t)m * K + c));
+        *reinterpret_cast<float4*>(lin + (size_t)m * K + c) = make_float4(bf_lo(av.x), bf_hi(av.x), bf_lo(av.y), bf_hi(av.y));
+      }
   } else if (P.mode == PRO_GATED) {
     // rms_norm_gated over 128-wide heads (kernels/ornith_norm.metal:119-185)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int heads = K / 128;
-    for (int pair = warp; pair < M * heads; pair += (blockDim.x >> 5)) {
+    const int pairs = M * (K >> 7);
+    for (int pair = warp; pair < pairs; pair += (blockDim.x >> 5)) {
       const int base = pair * 128 + 4 * lane;
       float xv[4];
       float acc = 0.f;
@@ -529,30 +593,37 @@ ORN_D void run_prologue(const Prologue& P, float* lin, float* red) {
       }
     }
   } else {  // PRO_MTPJOIN: [norm(embed(id)) | norm(trunk hidden)] (src/model/mtp.rs:179-187)
-    const int H = K / 2;
-    for (int i = threadIdx.x; i < M * H; i += blockDim.x) {
-      const int m = i / H, c = i - m * H;
+    const int H = K >> 1;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
       const int64_t row = P.ids[m];
-      const uint32_t sb = reinterpret_cast<const uint32_t*>(P.emb.s)[row * (H >> 6) + (c >> 6)];
-      lin[(size_t)m * K + c] = bfr(fmaf(bf_lo(sb), (float)P.emb.w[row * H + c], bf_hi(sb)));
-      lin[(size_t)m * K + H + c] = bf2f(P.a[i]);
+      for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const uint32_t sb = reinterpret_cast<const uint32_t*>(P.emb.s)[row * (H >> 6) + (c >> 6)];
+        lin[(size_t)m * K + c] = bfr(fmaf(bf_lo(sb), (float)P.emb.w[row * H + c], bf_hi(sb)));
+        lin[(size_t)m * K + H + c] = bf2f(P.a[(size_t)m * H + c]);
+      }
     }
     __syncthreads();
     block_rms_inv(lin, K, M, H, P.eps, red, inv);
-    for (int i = threadIdx.x; i < M * H; i += blockDim.x) {
-      const int m = i / H, c = i - m * H;
-      lin[(size_t)m * K + c] = bfr(bf2f(P.w[c]) * bfr(lin[(size_t)m * K + c] * inv[m]));
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      const float w = bf2f(P.w[c]);
+#pragma unroll
+      for (int m = 0; m < M; ++m) lin[(size_t)m * K + c] = bfr(w * bfr(lin[(size_t)m * K + c] * inv[m]));
     }
     __syncthreads();
     block_rms_inv(lin + H, K, M, H, P.eps, red, inv);
-    for (int i = threadIdx.x; i < M * H; i += blockDim.x) {
-      const int m = i / H, c = i - m * H;
-      lin[(size_t)m * K + H + c] = bfr(bf2f(P.w2[c]) * bfr(lin[(size_t)m * K + H + c] * inv[m]));
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      const float w = bf2f(P.w2[c]);
+#pragma unroll
+      for (int m = 0; m < M; ++m) lin[(size_t)m * K + H + c] = bfr(w * bfr(lin[(size_t)m * K + H + c] * inv[m]));
     }
   }
   __syncthreads();
-  if (P.norm_out != nullptr && blockIdx.x == 0)
-    for (int i = threadIdx.x; i < M * K; i += blockDim.x) P.norm_out[i] = f2bf(lin[i]);
+  if (P.norm_out != nullptr && blockIdx.x == 0) {
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+      for (int c = threadIdx.x; c < K; c += blockDim.x) P.norm_out[(size_t)m * K + c] = f2bf(lin[(size_t)m * K + c]);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -563,7 +634,10 @@ struct RowJob {
   LinDev lin2;   // EPI_SWIGLU: the "up" matrix paired with lin ("gate")
   bf16_t* out;   // [M][O]
   int epi;       // EPI_STORE | EPI_SWIGLU
-  int tasks;     // rows of the job (one task per output row, or per gate/up pair)
+  int tasks;     // row pairs of the job
+  int units;     // lane units per row
+  int nchunk;    // streamed chunks per row
+  uint32_t rb0, rb1;  // bytes per row of the two streams
 };
 struct RowJobs {
   RowJob job[4];
@@ -571,95 +645,167 @@ struct RowJobs {
   int kinds_mask;  // bit k set when some job has weights of kind k
 };
 
-// task t of the concatenated job list -> (job, row)
-ORN_D void job_of_task(const RowJobs& J, int t, int& j, int& row) {
-  j = 0;
-  while (t >= J.job[j].tasks) { t -= J.job[j].tasks; ++j; }
-  row = t;
+constexpr int kRowsPerTask = 2;  // consecutive weight rows a warp takes per task
+
+// a warp's position in its task sequence: row pairs gw, gw+GW, ... of the
+// concatenated jobs, each in `nchunk` chunks; no divisions
+struct Cursor {
+  int j, t, c;  // job, task (row pair) within the job, chunk
+  ORN_D bool valid(const RowJobs& J) const { return j < J.njobs; }
+  ORN_D void settle(const RowJobs& J) {
+    while (j < J.njobs && t >= J.job[j].tasks) { t -= J.job[j].tasks; ++j; }
+  }
+  ORN_D void advance(const RowJobs& J, int GW) {
+    if (++c == J.job[j].nchunk) {
+      c = 0;
+      t += GW;
+      settle(J);
+    }
+  }
+};
+
+ORN_D int job_chunk_units(const RowJob& job, int c) {
+  const int u = job.units - 32 * kChunkSteps * c;
+  return u > 32 * kChunkSteps ? 32 * kChunkSteps : u;
 }
 
-template <int M>
+// lane 0: request chunk c of rows [row, row+n) of matrix L into a slot at byte
+// offset `off`, laid out [n x stream 0][n x stream 1].  Whole rows (nchunk == 1)
+// are contiguous in HBM and travel as one copy per stream.
+ORN_D void job_copy_tile(const Ring& R, int slot, uint32_t off, const RowJob& job, const LinDev& L, int row, int n,
+                         int c, uint32_t b0, uint32_t b1) {
+  const uint32_t bar = R.bar0 + 8 * slot;
+  const uint32_t dst = R.buf0 + slot * R.slot_bytes + off;
+  if (job.nchunk == 1) {
+    bulk_g2s(dst, L.w + (int64_t)row * job.rb0, n * b0, bar);
+    if (b1) bulk_g2s(dst + kRowsPerTask * b0, L.s + (int64_t)row * job.rb1, n * b1, bar);
+  } else {
+    for (int r = 0; r < n; ++r) {
+      bulk_g2s(dst + r * b0, L.w + (int64_t)(row + r) * job.rb0 + (int64_t)c * kChunkSteps * step_bytes0(L.kind), b0, bar);
+      if (b1)
+        bulk_g2s(dst + kRowsPerTask * b0 + r * b1,
+                 L.s + (int64_t)(row + r) * job.rb1 + (int64_t)c * kChunkSteps * step_bytes1(L.kind), b1, bar);
+    }
+  }
+}
+
+// tile dot for the formats present in MASK only (keeps the kernel small)
+template <int M, int MASK>
+ORN_D void tile_dot_masked(const uint8_t* buf, uint32_t b0, uint32_t b1, const LinDev& L, int64_t row, int nvalid, int c,
+                           const XStage* X, int lane, float (&acc)[kRowsPerTask][M]) {
+  const uint8_t* p1 = buf + kRowsPerTask * b0;
+  if ((MASK & (1 << ORN_A8)) && L.kind == ORN_A8)
+    warp_chunk_dot_rows<ORN_A8, M, kRowsPerTask>(buf, b0, p1, b1, L, row, nvalid, c, X[ORN_A8], 0, lane, acc);
+  else if ((MASK & (1 << ORN_Q4K)) && L.kind == ORN_Q4K)
+    warp_chunk_dot_rows<ORN_Q4K, M, kRowsPerTask>(buf, b0, p1, b1, L, row, nvalid, c, X[ORN_Q4K], 0, lane, acc);
+  else if ((MASK & (1 << ORN_Q6K)) && L.kind == ORN_Q6K)
+    warp_chunk_dot_rows<ORN_Q6K, M, kRowsPerTask>(buf, b0, p1, b1, L, row, nvalid, c, X[ORN_Q6K], 0, lane, acc);
+  else if ((MASK & (1 << ORN_BF16)) && L.kind == ORN_BF16)
+    warp_chunk_dot_rows<ORN_BF16, M, kRowsPerTask>(buf, b0, p1, b1, L, row, nvalid, c, X[ORN_BF16], 0, lane, acc);
+}
+
+template <int M, int MASK>
 __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJobs J, uint32_t slot_bytes, int depth,
-                                                                int nchunk, int* err) {
+                                                                uint32_t ring_off, int* err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* smem = reinterpret_cast<float*>(smem_raw);
-  // stages first, then a region used by the prologue's scratch and, after it, by the rings
+  const int lane = threadIdx.x & 31;
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int GW = gridDim.x * (blockDim.x >> 5);
+  // The weights do not depend on the activations: the rings are set up and the
+  // first `depth` tiles of every warp requested before the prologue runs, so
+  // that HBM is busy while the CTA rebuilds its input.
+  DBG(0);
+  Ring R;
+  ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
+  __syncthreads();
+  DBG(1);
+  Cursor pc{0, gw, 0}, cc{0, gw, 0};
+  pc.settle(J);
+  cc.settle(J);
+  int pslot = 0;
+  auto issue = [&]() {  // all lanes keep the cursor; lane 0 issues
+    const RowJob& job = J.job[pc.j];
+    if (lane == 0) {
+      const int u = job_chunk_units(job, pc.c);
+      const uint32_t b0 = units_bytes0(job.lin.kind, u), b1 = units_bytes1(job.lin.kind, u);
+      const int row = pc.t * kRowsPerTask;
+      const int n = min(kRowsPerTask, job.lin.O - row);
+      mbar_expect_tx(R.bar0 + 8 * pslot, (job.epi == EPI_SWIGLU ? 2 : 1) * n * (b0 + b1));
+      job_copy_tile(R, pslot, 0, job, job.lin, row, n, pc.c, b0, b1);
+      if (job.epi == EPI_SWIGLU) job_copy_tile(R, pslot, kRowsPerTask * (b0 + b1), job, job.lin2, row, n, pc.c, b0, b1);
+    }
+    pc.advance(J, GW);
+    if (++pslot == depth) pslot = 0;
+  };
+  for (int i = 0; i < depth && pc.valid(J); ++i) issue();
+  DBG(2);
+
+  // stages, then the prologue's scratch
   float* next = smem;
   XStage X[4];
 #pragma unroll
   for (int k = 0; k < 4; ++k)
-    if (J.kinds_mask & (1 << k)) next = stage_carve(next, k, M, P.K, X[k]);
-  uint8_t* region = reinterpret_cast<uint8_t*>(smem) + ((((uint8_t*)next - (uint8_t*)smem) + 127) & ~(size_t)127);
-  float* lin = reinterpret_cast<float*>(region);
+    if (MASK & (1 << k)) next = stage_carve(next, k, M, P.K, X[k]);
+  float* lin = smem + (((next - smem) + 31) & ~31);
   float* red = lin + (size_t)M * P.K;
   run_prologue<M>(P, lin, red);
-#pragma unroll
-  for (int k = 0; k < 4; ++k)
-    if (J.kinds_mask & (1 << k)) stage_fill_kind(k, lin, P.K, X[k]);
-  __syncthreads();  // lin is dead from here on; the rings take its place
-  Ring R;
-  ring_setup(R, region, slot_bytes, depth, err);
+  DBG(3);
+  if (MASK & (1 << ORN_Q4K)) stage_fill<ORN_Q4K>(lin, P.K, X[ORN_Q4K]);
+  if (MASK & (1 << ORN_Q6K)) stage_fill<ORN_Q6K>(lin, P.K, X[ORN_Q6K]);
+  if (MASK & (1 << ORN_A8)) stage_fill<ORN_A8>(lin, P.K, X[ORN_A8]);
+  if (MASK & (1 << ORN_BF16)) stage_fill<ORN_BF16>(lin, P.K, X[ORN_BF16]);
   __syncthreads();
-  const int lane = threadIdx.x & 31;
-  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int GW = gridDim.x * (blockDim.x >> 5);
-  int total = 0;
-  for (int j = 0; j < J.njobs; ++j) total += J.job[j].tasks;
-  const int mine = (gw < total ? (total - gw + GW - 1) / GW : 0) * nchunk;
-  auto issue = [&](int i) {  // lane 0
-    int j, row;
-    const int ti = i / nchunk, c = i - ti * nchunk;
-    job_of_task(J, gw + ti * GW, j, row);
-    const RowJob& job = J.job[j];
-    const int slot = i % depth;
-    const uint32_t cb = chunk_bytes(job.lin, c);
-    mbar_expect_tx(R.bar0 + 8 * slot, job.epi == EPI_SWIGLU ? 2 * cb : cb);
-    ring_copy_chunk(R, slot, 0, job.lin, row, c);
-    if (job.epi == EPI_SWIGLU) ring_copy_chunk(R, slot, cb, job.lin2, row, c);
-  };
-  int issued = 0;
-  if (lane == 0)
-    for (; issued < depth && issued < mine; ++issued) issue(issued);
-  issued = __shfl_sync(0xffffffffu, issued, 0);
-  float acc[M], up[M];
-  for (int i = 0; i < mine; ++i) {
-    const int slot = i % depth;
-    if (!ring_wait(R, slot, (i / depth) & 1)) return;
-    int j, row;
-    const int ti = i / nchunk, c = i - ti * nchunk;
-    job_of_task(J, gw + ti * GW, j, row);
-    const RowJob& job = J.job[j];
+  DBG(4);
+
+  float acc[kRowsPerTask][M], up[kRowsPerTask][M];
+  int slot = 0;
+  uint32_t parity = 0;
+  int dbg_n = 0;
+  while (cc.valid(J)) {
+    if (!ring_wait(R, slot, parity)) return;
+    if (dbg_n < 8) { DBG(5 + 2 * dbg_n); }
+    const RowJob& job = J.job[cc.j];
     const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
-    if (c == 0) {
+    const int cu = job_chunk_units(job, cc.c);
+    const uint32_t b0 = units_bytes0(job.lin.kind, cu), b1 = units_bytes1(job.lin.kind, cu);
+    const int row = cc.t * kRowsPerTask;
+    const int nvalid = min(kRowsPerTask, job.lin.O - row);
+    if (cc.c == 0) {
 #pragma unroll
-      for (int m = 0; m < M; ++m) { acc[m] = 0.f; up[m] = 0.f; }
+      for (int r = 0; r < kRowsPerTask; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) { acc[r][m] = 0.f; up[r][m] = 0.f; }
     }
-    warp_chunk_dot_kind<M>(buf, job.lin, row, c, X, 0, lane, acc);
-    if (job.epi == EPI_SWIGLU) warp_chunk_dot_kind<M>(buf + chunk_bytes(job.lin, c), job.lin2, row, c, X, 0, lane, up);
-    if (c == nchunk - 1) {
+    if (dbg_n == 0) { DBG(20); }
+    tile_dot_masked<M, MASK>(buf, b0, b1, job.lin, row, nvalid, cc.c, X, lane, acc);
+    if (dbg_n == 0) { DBG(21); }
+    if (job.epi == EPI_SWIGLU)
+      tile_dot_masked<M, MASK>(buf + kRowsPerTask * (b0 + b1), b0, b1, job.lin2, row, nvalid, cc.c, X, lane, up);
+    if (dbg_n == 0) { DBG(22); }
+    if (cc.c == job.nchunk - 1) {
 #pragma unroll
-      for (int m = 0; m < M; ++m) acc[m] = warp_sum(acc[m]);
-      if (job.epi == EPI_SWIGLU) {
+      for (int r = 0; r < kRowsPerTask; ++r)
 #pragma unroll
-        for (int m = 0; m < M; ++m) up[m] = warp_sum(up[m]);
-        if (lane == 0)
-#pragma unroll
-          for (int m = 0; m < M; ++m)
-            job.out[(size_t)m * job.lin.O + row] = f2bf(orn_swiglu_bf(bfr(acc[m]), bfr(up[m])));
-      } else if (lane == 0) {
-#pragma unroll
-        for (int m = 0; m < M; ++m) job.out[(size_t)m * job.lin.O + row] = f2bf(acc[m]);
-      }
+        for (int m = 0; m < M; ++m) {
+          float v = warp_sum(acc[r][m]);
+          if (job.epi == EPI_SWIGLU) v = orn_swiglu_bf(bfr(v), bfr(warp_sum(up[r][m])));
+          if (lane == 0 && r < nvalid) job.out[(size_t)m * job.lin.O + row + r] = f2bf(v);
+        }
     }
+    if (dbg_n == 0) { DBG(23); }
     __syncwarp();
-    if (issued < mine) {
-      if (lane == 0) {
-        fence_proxy_async();
-        issue(issued);
-      }
-      ++issued;
+    if (pc.valid(J)) {
+      if (lane == 0) fence_proxy_async();
+      issue();  // refills the slot just consumed
     }
+    if (dbg_n == 0) { DBG(24); }
+    cc.advance(J, GW);
+    if (++slot == depth) { slot = 0; parity ^= 1; }
+    if (dbg_n < 8) { DBG(6 + 2 * dbg_n); }
+    ++dbg_n;
   }
+  DBG(30);
 }
 
 // ---------------------------------------------------------------------------
@@ -765,50 +911,98 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_moe_up(MoeUpParams P, uint
   Ring R;
   ring_setup(R, region, slot_bytes, depth, err);
   __syncthreads();
-  const int total = M * P.k * P.I;
+  // task sequence of a warp: (mj, op) = routed row mj, pair op of consecutive expert output rows, starting
+  // at flat index gw and stepping by GW, each in `nchunk` chunks; positions advance without divisions
+  constexpr int RT = kRowsPerTask;
   const int gw = blockIdx.x * (blockDim.x >> 5) + warp, GW = gridDim.x * (blockDim.x >> 5);
-  const int nchunk = row_chunks(KIND, P.H);
-  const int mine = (gw < total ? (total - gw + GW - 1) / GW : 0) * nchunk;
-  auto issue = [&](int i) {  // lane 0
-    const int ti = i / nchunk, c = i - ti * nchunk;
-    const int t = gw + ti * GW;
-    const int mj = t / P.I, o = t - mj * P.I;
-    const int64_t row = (int64_t)inds[mj] * P.I + o;
-    const int slot = i % depth;
-    const uint32_t cb = chunk_bytes(P.gate, c);
-    mbar_expect_tx(R.bar0 + 8 * slot, 2 * cb);
-    ring_copy_chunk(R, slot, 0, P.gate, row, c);
-    ring_copy_chunk(R, slot, cb, P.up, row, c);
+  const int nmj = M * P.k;
+  const int npair = (P.I + RT - 1) / RT;
+  const int units = X.units;
+  const int nchunk = (units + 32 * kChunkSteps - 1) / (32 * kChunkSteps);
+  const uint32_t rb0 = units_bytes0(KIND, units), rb1 = units_bytes1(KIND, units);
+  struct Pos {
+    int mj, op, c;
   };
-  int issued = 0;
-  if (lane == 0)
-    for (; issued < depth && issued < mine; ++issued) issue(issued);
-  issued = __shfl_sync(0xffffffffu, issued, 0);
-  float g[1], u[1];
-  for (int i = 0; i < mine; ++i) {
-    const int slot = i % depth;
-    if (!ring_wait(R, slot, (i / depth) & 1)) return;
-    const int ti = i / nchunk, c = i - ti * nchunk;
-    const int t = gw + ti * GW;
-    const int mj = t / P.I, o = t - mj * P.I;
-    const int m = mj / P.k;
-    const int64_t row = (int64_t)inds[mj] * P.I + o;
+  auto settle = [&](Pos& q) {
+    while (q.mj < nmj && q.op >= npair) { q.op -= npair; ++q.mj; }
+  };
+  auto advance = [&](Pos& q) {
+    if (++q.c == nchunk) { q.c = 0; q.op += GW; settle(q); }
+  };
+  auto cunits = [&](int c) {
+    const int u = units - 32 * kChunkSteps * c;
+    return u > 32 * kChunkSteps ? 32 * kChunkSteps : u;
+  };
+  Pos pp{0, gw, 0}, cp{0, gw, 0};
+  settle(pp);
+  settle(cp);
+  int pslot = 0;
+  // slot layout: [gate: RT x stream 0][gate: RT x stream 1][up: RT x stream 0][up: RT x stream 1]
+  auto issue = [&]() {
+    if (lane == 0) {
+      const int o = pp.op * RT;
+      const int n = min(RT, P.I - o);
+      const int64_t row = (int64_t)inds[pp.mj] * P.I + o;
+      const int u = cunits(pp.c);
+      const uint32_t b0 = units_bytes0(KIND, u), b1 = units_bytes1(KIND, u);
+      const uint32_t bar = R.bar0 + 8 * pslot;
+      const uint32_t dst = R.buf0 + pslot * R.slot_bytes;
+      const uint32_t half = RT * (b0 + b1);
+      mbar_expect_tx(bar, 2 * n * (b0 + b1));
+      if (nchunk == 1) {
+        bulk_g2s(dst, P.gate.w + row * rb0, n * b0, bar);
+        if (b1) bulk_g2s(dst + RT * b0, P.gate.s + row * rb1, n * b1, bar);
+        bulk_g2s(dst + half, P.up.w + row * rb0, n * b0, bar);
+        if (b1) bulk_g2s(dst + half + RT * b0, P.up.s + row * rb1, n * b1, bar);
+      } else {
+        for (int r = 0; r < n; ++r) {
+          const int64_t o0 = (row + r) * rb0 + (int64_t)pp.c * kChunkSteps * step_bytes0(KIND);
+          const int64_t o1 = (row + r) * rb1 + (int64_t)pp.c * kChunkSteps * step_bytes1(KIND);
+          bulk_g2s(dst + r * b0, P.gate.w + o0, b0, bar);
+          if (b1) bulk_g2s(dst + RT * b0 + r * b1, P.gate.s + o1, b1, bar);
+          bulk_g2s(dst + half + r * b0, P.up.w + o0, b0, bar);
+          if (b1) bulk_g2s(dst + half + RT * b0 + r * b1, P.up.s + o1, b1, bar);
+        }
+      }
+    }
+    advance(pp);
+    if (++pslot == depth) pslot = 0;
+  };
+  for (int i = 0; i < depth && pp.mj < nmj; ++i) issue();
+  float g[RT][1], u[RT][1];
+  int slot = 0;
+  uint32_t parity = 0;
+  while (cp.mj < nmj) {
+    if (!ring_wait(R, slot, parity)) return;
+    int m = 0;
+    for (int t = P.k; t <= cp.mj; t += P.k) ++m;  // m = mj / k without a division
+    const int o = cp.op * RT;
+    const int nvalid = min(RT, P.I - o);
+    const int64_t row = (int64_t)inds[cp.mj] * P.I + o;
     const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
-    if (c == 0) { g[0] = 0.f; u[0] = 0.f; }
-    warp_chunk_dot<KIND, 1>(buf, P.gate, row, c, X, m, lane, g);
-    warp_chunk_dot<KIND, 1>(buf + chunk_bytes(P.gate, c), P.up, row, c, X, m, lane, u);
-    if (c == nchunk - 1) {
-      const float gs = warp_sum(g[0]), us = warp_sum(u[0]);
-      if (lane == 0) P.act[(size_t)mj * P.I + o] = f2bf(orn_swiglu_bf(bfr(gs), bfr(us)));
+    const int cu = cunits(cp.c);
+    const uint32_t cb0 = units_bytes0(KIND, cu), cb1 = units_bytes1(KIND, cu);
+    const uint32_t half = RT * (cb0 + cb1);
+    if (cp.c == 0) {
+#pragma unroll
+      for (int r = 0; r < RT; ++r) { g[r][0] = 0.f; u[r][0] = 0.f; }
+    }
+    warp_chunk_dot_rows<KIND, 1, RT>(buf, cb0, buf + RT * cb0, cb1, P.gate, row, nvalid, cp.c, X, m, lane, g);
+    warp_chunk_dot_rows<KIND, 1, RT>(buf + half, cb0, buf + half + RT * cb0, cb1, P.up, row, nvalid, cp.c, X, m, lane, u);
+    if (cp.c == nchunk - 1) {
+#pragma unroll
+      for (int r = 0; r < RT; ++r) {
+        const float gs = warp_sum(g[r][0]), us = warp_sum(u[r][0]);
+        if (lane == 0 && r < nvalid) P.act[(size_t)cp.mj * P.I + o + r] = f2bf(orn_swiglu_bf(bfr(gs), bfr(us)));
+      }
     }
     __syncwarp();
-    if (issued < mine) {
-      if (lane == 0) {
-        fence_proxy_async();
-        issue(issued);
-      }
-      ++issued;
+    if (pp.mj < nmj) {
+      if (lane == 0) fence_proxy_async();
+      issue();
     }
+    advance(cp);
+    if (++slot == depth) { slot = 0; parity ^= 1; }
   }
 }
 
@@ -864,68 +1058,94 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_moe_down(MoeDownParams P, 
   Ring R;
   ring_setup(R, region, slot_bytes, depth, err);
   __syncthreads();
-  // a warp owns output columns c = gw, gw+GW, ...; per column it consumes the
-  // M*k routed rows in (m, j) order and then the shared expert's row
+  // A warp owns groups of kDownCols consecutive output columns (group gw,
+  // gw+GW, ...).  Consecutive columns are consecutive weight rows of one expert,
+  // so one pair of bulk copies brings a group's rows of one routed expert.  Per
+  // group the warp consumes the M*k routed tiles in (m, j) order and then the
+  // shared expert's tile.  Rows here are short (one chunk each, checked at launch).
   const int lane = threadIdx.x & 31;
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), GW = gridDim.x * (blockDim.x >> 5);
-  const int per = rows + 1;
-  const int cols = gw < P.H ? (P.H - gw + GW - 1) / GW : 0;
-  const int mine = cols * per;
-  auto issue = [&](int i) {  // lane 0
-    const int ci = i / per, q = i - ci * per;
-    const int c = gw + ci * GW;
-    const int slot = i % depth;
-    // the intermediate sizes are short enough for one chunk per row (checked at launch)
-    if (q < rows) {
-      mbar_expect_tx(R.bar0 + 8 * slot, chunk_bytes(P.down, 0));
-      ring_copy_chunk(R, slot, 0, P.down, (int64_t)inds[q] * P.H + c, 0);
-    } else {
-      mbar_expect_tx(R.bar0 + 8 * slot, chunk_bytes(P.sh_down, 0));
-      ring_copy_chunk(R, slot, 0, P.sh_down, c, 0);
-    }
+  const int ngroups = P.H / kDownCols;
+  const uint32_t b0 = units_bytes0(KIND, X.units), b1 = units_bytes1(KIND, X.units);      // routed row
+  const uint32_t sb0 = units_bytes0(KIND, XS.units), sb1 = units_bytes1(KIND, XS.units);  // shared row
+  struct Pos {
+    int g, q;
   };
-  int issued = 0;
-  if (lane == 0)
-    for (; issued < depth && issued < mine; ++issued) issue(issued);
-  issued = __shfl_sync(0xffffffffu, issued, 0);
-  float acc[M];
+  auto advance = [&](Pos& t) {
+    if (++t.q > rows) { t.q = 0; t.g += GW; }
+  };
+  Pos pp{gw, 0}, cp{gw, 0};
+  int pslot = 0;
+  auto issue = [&]() {
+    if (lane == 0) {
+      const uint32_t bar = R.bar0 + 8 * pslot;
+      const uint32_t dst = R.buf0 + pslot * R.slot_bytes;
+      const int c0 = pp.g * kDownCols;
+      if (pp.q < rows) {
+        const int64_t row = (int64_t)inds[pp.q] * P.H + c0;
+        mbar_expect_tx(bar, kDownCols * (b0 + b1));
+        bulk_g2s(dst, P.down.w + row * b0, kDownCols * b0, bar);
+        if (b1) bulk_g2s(dst + kDownCols * b0, P.down.s + row * b1, kDownCols * b1, bar);
+      } else {
+        mbar_expect_tx(bar, kDownCols * (sb0 + sb1));
+        bulk_g2s(dst, P.sh_down.w + (int64_t)c0 * sb0, kDownCols * sb0, bar);
+        if (sb1) bulk_g2s(dst + kDownCols * sb0, P.sh_down.s + (int64_t)c0 * sb1, kDownCols * sb1, bar);
+      }
+    }
+    advance(pp);
+    if (++pslot == depth) pslot = 0;
+  };
+  for (int i = 0; i < depth && pp.g < ngroups; ++i) issue();
+  float acc[kDownCols][M];
 #pragma unroll
-  for (int m = 0; m < M; ++m) acc[m] = 0.f;
-  for (int i = 0; i < mine; ++i) {
-    const int slot = i % depth;
-    if (!ring_wait(R, slot, (i / depth) & 1)) return;
-    const int ci = i / per, q = i - ci * per;
-    const int c = gw + ci * GW;
-    const uint8_t* rowbuf = R.buf + (size_t)slot * slot_bytes;
-    if (q < rows) {
-      float d[1] = {0.f};
-      warp_chunk_dot<KIND, 1>(rowbuf, P.down, (int64_t)inds[q] * P.H + c, 0, X, q, lane, d);
-      const float weighted = bfr(bfr(warp_sum(d[0])) * wts[q]);
-      const int m = q / P.k;
+  for (int r = 0; r < kDownCols; ++r)
 #pragma unroll
-      for (int mm = 0; mm < M; ++mm)
-        if (mm == m) acc[mm] = bfr(weighted + acc[mm]);
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+  int slot = 0;
+  uint32_t parity = 0;
+  while (cp.g < ngroups) {
+    if (!ring_wait(R, slot, parity)) return;
+    const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
+    const int c0 = cp.g * kDownCols;
+    if (cp.q < rows) {
+      const int64_t row = (int64_t)inds[cp.q] * P.H + c0;
+      const float w = wts[cp.q];
+      int m = 0;
+      for (int t = P.k; t <= cp.q; t += P.k) ++m;  // m = q / k without a division
+      float d[kDownCols][1];
+#pragma unroll
+      for (int r = 0; r < kDownCols; ++r) d[r][0] = 0.f;
+      warp_chunk_dot_rows<KIND, 1, kDownCols>(buf, b0, buf + kDownCols * b0, b1, P.down, row, kDownCols, 0, X, cp.q, lane, d);
+#pragma unroll
+      for (int r = 0; r < kDownCols; ++r) {
+        const float weighted = bfr(bfr(warp_sum(d[r][0])) * w);
+#pragma unroll
+        for (int mm = 0; mm < M; ++mm)
+          if (mm == m) acc[r][mm] = bfr(weighted + acc[r][mm]);
+      }
     } else {
-      float sd[M];
+      float sd[kDownCols][M];
 #pragma unroll
-      for (int m = 0; m < M; ++m) sd[m] = 0.f;
-      warp_chunk_dot<KIND, M>(rowbuf, P.sh_down, c, 0, XS, 0, lane, sd);
+      for (int r = 0; r < kDownCols; ++r)
 #pragma unroll
-      for (int m = 0; m < M; ++m) sd[m] = warp_sum(sd[m]);
-      if (lane == 0)
+        for (int m = 0; m < M; ++m) sd[r][m] = 0.f;
+      warp_chunk_dot_rows<KIND, M, kDownCols>(buf, sb0, buf + kDownCols * sb0, sb1, P.sh_down, c0, kDownCols, 0, XS, 0, lane, sd);
 #pragma unroll
-        for (int m = 0; m < M; ++m) P.out[(size_t)m * P.H + c] = f2bf(acc[m] + bfr(gsig[m] * bfr(sd[m])));
+      for (int r = 0; r < kDownCols; ++r)
 #pragma unroll
-      for (int m = 0; m < M; ++m) acc[m] = 0.f;
+        for (int m = 0; m < M; ++m) {
+          const float v = warp_sum(sd[r][m]);
+          if (lane == 0) P.out[(size_t)m * P.H + c0 + r] = f2bf(acc[r][m] + bfr(gsig[m] * bfr(v)));
+          acc[r][m] = 0.f;
+        }
     }
     __syncwarp();
-    if (issued < mine) {
-      if (lane == 0) {
-        fence_proxy_async();
-        issue(issued);
-      }
-      ++issued;
+    if (pp.g < ngroups) {
+      if (lane == 0) fence_proxy_async();
+      issue();
     }
+    advance(cp);
+    if (++slot == depth) { slot = 0; parity ^= 1; }
   }
 }
 
@@ -1202,13 +1422,18 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-constexpr size_t kSmemBudget = 200 * 1024;
+constexpr size_t kSmemBudget = 220 * 1024;
 
+// raise a kernel's dynamic shared-memory limit once (per kernel, per process)
 template <typename Kern>
 int set_smem(orn_ctx* ctx, Kern kern, size_t bytes) {
+  static std::map<const void*, bool> granted;  // keyed by kernel address (instantiations share a type)
   if (bytes > 227 * 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "fused kernel: staged activations exceed shared memory");
-  if (bytes > 48 * 1024)
-    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  const void* key = reinterpret_cast<const void*>(kern);
+  if (bytes > 48 * 1024 && !granted[key]) {
+    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    granted[key] = true;
+  }
   return ORN_OK;
 }
 
@@ -1218,7 +1443,7 @@ int plan_smem(orn_ctx* ctx, size_t fixed, size_t scratch, uint32_t slot_bytes, i
   const int nwarps = kFusedThreads / 32;
   fixed = (fixed + 127) & ~(size_t)127;
   int d = 8;
-  while (d > 2 && fixed + ring_bytes(nwarps, d, slot_bytes) > kSmemBudget) --d;
+  while (d > 1 && fixed + ring_bytes(nwarps, d, slot_bytes) > kSmemBudget) --d;
   const size_t rb = ring_bytes(nwarps, d, slot_bytes);
   *depth = d;
   *total = fixed + (rb > scratch ? rb : scratch) + 128;
@@ -1226,19 +1451,41 @@ int plan_smem(orn_ctx* ctx, size_t fixed, size_t scratch, uint32_t slot_bytes, i
   return ORN_OK;
 }
 
+template <int M, int MASK>
+int launch_norm_gemv_mask(orn_ctx* ctx, cudaStream_t s, const Prologue& P, const RowJobs& J, uint32_t slot) {
+  size_t fixed = 0;
+  for (int k = 0; k < 4; ++k)
+    if (MASK & (1 << k)) fixed += stage_floats(k, M, P.K) * sizeof(float);
+  // stages + prologue scratch stay live beside the rings (the rings are filled while the prologue runs)
+  fixed += ((size_t)M * P.K + M * 33 + 64) * sizeof(float);
+  fixed = (fixed + 127) & ~(size_t)127;
+  int depth;
+  size_t bytes;
+  int rc = plan_smem(ctx, fixed, 0, slot, &depth, &bytes);
+  if (rc != ORN_OK) return rc;
+  rc = set_smem(ctx, k_norm_gemv<M, MASK>, bytes);
+  if (rc != ORN_OK) return rc;
+  k_norm_gemv<M, MASK><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, J, slot, depth, (uint32_t)fixed, ctx->dev_err);
+  return orn_launch_check(ctx, "k_norm_gemv");
+}
+
 template <int M>
 int launch_norm_gemv(orn_ctx* ctx, cudaStream_t s, const Prologue& P, RowJobs& J) {
   J.kinds_mask = 0;
   uint32_t slot = 0;
-  int nchunk = 1;
+  if (P.mode == PRO_ADDNORM && P.K > 4 * kFusedThreads)
+    ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: hidden size above 2048 is not supported by the norm prologue");
   for (int j = 0; j < J.njobs; ++j) {
     RowJob& job = J.job[j];
     J.kinds_mask |= 1 << job.lin.kind;
-    job.tasks = job.lin.O;
     if (job.lin.K != P.K) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: weight K differs from the staged row");
     if (job.lin.K % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: K must be a multiple of 256");
-    uint32_t rb = chunk_bytes_max(job.lin.kind, job.lin.K);
-    nchunk = std::max(nchunk, row_chunks(job.lin.kind, job.lin.K));
+    job.tasks = (job.lin.O + kRowsPerTask - 1) / kRowsPerTask;
+    job.units = kind_units(job.lin.kind, job.lin.K);
+    job.nchunk = row_chunks(job.lin.kind, job.lin.K);
+    job.rb0 = units_bytes0(job.lin.kind, job.units);
+    job.rb1 = units_bytes1(job.lin.kind, job.units);
+    uint32_t rb = kRowsPerTask * chunk_bytes_max(job.lin.kind, job.lin.K);
     if (job.epi == EPI_SWIGLU) {
       if (job.lin2.kind != job.lin.kind || job.lin2.K != job.lin.K || job.lin2.O != job.lin.O)
         ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: gate and up projections must share format and shape");
@@ -1246,18 +1493,18 @@ int launch_norm_gemv(orn_ctx* ctx, cudaStream_t s, const Prologue& P, RowJobs& J
     }
     slot = rb > slot ? rb : slot;
   }
-  size_t fixed = 0;
-  for (int k = 0; k < 4; ++k)
-    if (J.kinds_mask & (1 << k)) fixed += stage_floats(k, M, P.K) * sizeof(float);
-  const size_t scratch = ((size_t)M * P.K + M * 33 + 8) * sizeof(float);
-  int depth;
-  size_t bytes;
-  int rc = plan_smem(ctx, fixed, scratch, slot, &depth, &bytes);
-  if (rc != ORN_OK) return rc;
-  rc = set_smem(ctx, k_norm_gemv<M>, bytes);
-  if (rc != ORN_OK) return rc;
-  k_norm_gemv<M><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, J, slot, depth, nchunk, ctx->dev_err);
-  return orn_launch_check(ctx, "k_norm_gemv");
+  // one instantiation per set of formats present, so that a kernel carries only the code it runs
+  switch (J.kinds_mask) {
+    case 1: return launch_norm_gemv_mask<M, 1>(ctx, s, P, J, slot);
+    case 2: return launch_norm_gemv_mask<M, 2>(ctx, s, P, J, slot);
+    case 4: return launch_norm_gemv_mask<M, 4>(ctx, s, P, J, slot);
+    case 8: return launch_norm_gemv_mask<M, 8>(ctx, s, P, J, slot);
+    case 5: return launch_norm_gemv_mask<M, 5>(ctx, s, P, J, slot);    // Q4_K + affine-8
+    case 12: return launch_norm_gemv_mask<M, 12>(ctx, s, P, J, slot);  // affine-8 + bf16
+    case 9: return launch_norm_gemv_mask<M, 9>(ctx, s, P, J, slot);    // Q4_K + bf16
+    case 6: return launch_norm_gemv_mask<M, 6>(ctx, s, P, J, slot);    // Q6_K + affine-8
+    default: return launch_norm_gemv_mask<M, 15>(ctx, s, P, J, slot);
+  }
 }
 
 template <int KIND, int M>
@@ -1265,7 +1512,7 @@ int launch_moe_up_k(orn_ctx* ctx, cudaStream_t s, const MoeUpParams& P) {
   if (P.H % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_up: hidden must be a multiple of 256");
   const size_t fixed = stage_floats(KIND, M, P.H) * sizeof(float) + (size_t)M * P.k * 4;
   const size_t scratch = ((size_t)M * P.H + (size_t)M * P.E + M * 32 + M * P.k + 8) * sizeof(float);
-  const uint32_t slot = 2 * chunk_bytes_max(KIND, P.H);
+  const uint32_t slot = 2 * kRowsPerTask * chunk_bytes_max(KIND, P.H);
   int depth;
   size_t bytes;
   int rc = plan_smem(ctx, fixed, scratch, slot, &depth, &bytes);
@@ -1284,8 +1531,9 @@ int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
   const size_t scratch = ((size_t)rows * P.I + (size_t)M * P.SI + 8) * sizeof(float);
   if (row_chunks(KIND, P.I) != 1 || row_chunks(KIND, P.SI) != 1)
     ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: intermediate size too long for one streamed chunk");
+  if (P.H % kDownCols) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: hidden must be even");
   const uint32_t r0 = chunk_bytes_max(KIND, P.I), r1 = chunk_bytes_max(KIND, P.SI);
-  const uint32_t slot = r0 > r1 ? r0 : r1;
+  const uint32_t slot = kDownCols * (r0 > r1 ? r0 : r1);
   int depth;
   size_t bytes;
   int rc = plan_smem(ctx, fixed, scratch, slot, &depth, &bytes);

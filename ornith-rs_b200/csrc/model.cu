@@ -63,7 +63,7 @@ struct Workspace {
   uint32_t *inds, *lhs, *ident;
   bf16_t *logits, *dlogits;
   float* greedy_scratch;
-  uint32_t *ids, *window, *targets, *local;
+  uint32_t *ids, *window, *targets, *local, *mailbox;
   bf16_t *vh, *hrow, *dh, *memb, *me, *mh, *mjoined, *mx;
 };
 
@@ -73,6 +73,12 @@ __global__ void iota_div_kernel(uint32_t* lhs, uint32_t* ident, int n, int k) {
 }
 __global__ void set_u32_kernel(uint32_t* p, uint32_t v) { *p = v; }
 __global__ void set_int_kernel(int* p, int v) { *p = v; }
+// mailbox = {primary, force flag[3], force token[3]} written by the host before each cycle;
+// slot < 0 places the primary at the head of the window, slot i applies draft i's override
+__global__ void mailbox_apply_kernel(const uint32_t* mb, uint32_t* window, int slot) {
+  if (slot < 0) window[0] = mb[0];
+  else if (mb[1 + slot] != 0) window[slot + 1] = mb[4 + slot];
+}
 __global__ void add_int_kernel(int* p, int v) { *p += v; }
 // FrSpec::map_id (src/frspec.rs:137-148, kernels/moe.metal:68-74 gather_u32)
 __global__ void gather_u32_kernel(const uint32_t* table, const uint32_t* idx, uint32_t* out) {
@@ -134,6 +140,15 @@ struct orn_cache {
   int *pos = nullptr, *cur = nullptr, *mtp_pos = nullptr;  // device scalars
   int h_pos = 0, h_cur = 0, h_mtp_pos = 0;                 // host mirrors
   int cap_T = 0;                                           // rows of the last capture window
+  // CUDA graphs of one decode cycle / one autoregressive step, keyed by shape;
+  // every kernel argument in them is a fixed address, positions live on the device
+  struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    int seen = 0;
+    int64_t launches = 0;
+  };
+  std::map<int, StepGraph> graphs;
+  uint32_t* mailbox_h = nullptr;  // pinned
 };
 
 namespace {
@@ -178,7 +193,7 @@ int build_workspace(orn_model* m) {
   CK(ws_alloc(m, &w.logits, R * (size_t)c.vocab)); CK(ws_alloc(m, &w.dlogits, (size_t)c.vocab));
   CK(ws_alloc(m, &w.greedy_scratch, greedy_scratch_floats(kMaxRows, c.vocab)));
   CK(ws_alloc(m, &w.ids, (size_t)8)); CK(ws_alloc(m, &w.window, (size_t)8));
-  CK(ws_alloc(m, &w.targets, (size_t)8)); CK(ws_alloc(m, &w.local, (size_t)1));
+  CK(ws_alloc(m, &w.targets, (size_t)8)); CK(ws_alloc(m, &w.local, (size_t)1)); CK(ws_alloc(m, &w.mailbox, (size_t)16));
   CK(ws_alloc(m, &w.vh, R * H)); CK(ws_alloc(m, &w.hrow, H)); CK(ws_alloc(m, &w.dh, R * H));
   CK(ws_alloc(m, &w.memb, R * H)); CK(ws_alloc(m, &w.me, R * H)); CK(ws_alloc(m, &w.mh, R * H));
   CK(ws_alloc(m, &w.mjoined, R * 2 * H)); CK(ws_alloc(m, &w.mx, R * H));
@@ -628,6 +643,81 @@ int head_greedy_dev(orn_model* m, const orn_linear* head, const bf16_t* hidden, 
   return k_greedy(m->ctx, m->ctx->stream, logits, T, head->O, normalize, dev_tokens, m->ws.greedy_scratch);
 }
 
+// One speculative cycle on the device: window[0] = primary, `want` draft levels
+// (mtp_generate.rs:99-135) with the harness's forced-draft overrides read from the
+// mailbox, then the verify forward with every row's greedy target.
+int cycle_body(orn_model* m, orn_cache* c, int want, bool use_frspec) {
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  Workspace& w = m->ws;
+  const int H = m->cfg.hidden;
+  const orn_linear* dlm = use_frspec ? m->fr_head : m->lm_head;
+  mailbox_apply_kernel<<<1, 1, 0, s>>>(w.mailbox, w.window, -1);
+  CK(orn_launch_check(ctx, "mailbox_apply"));
+  const bf16_t* dh_in = w.hrow;
+  for (int i = 0; i < want; ++i) {
+    bf16_t* dh_out = w.dh + (size_t)(i & 1) * H;
+    CK(mtp_step(m, c, dh_in, w.window + i, 1, dlm, dh_out, w.dlogits, false));
+    if (use_frspec) {
+      CK(k_greedy(ctx, s, w.dlogits, 1, dlm->O, 0, w.local, w.greedy_scratch));
+      gather_u32_kernel<<<1, 1, 0, s>>>(m->fr_ids, w.local, w.window + i + 1);
+      CK(orn_launch_check(ctx, "gather_u32"));
+    } else {
+      CK(k_greedy(ctx, s, w.dlogits, 1, dlm->O, 0, w.window + i + 1, w.greedy_scratch));
+    }
+    mailbox_apply_kernel<<<1, 1, 0, s>>>(w.mailbox, w.window, i);
+    CK(orn_launch_check(ctx, "mailbox_apply"));
+    dh_in = dh_out;
+  }
+  return forward_greedy_dev(m, c, w.window, want + 1, true, w.vh, w.targets);
+}
+
+// one autoregressive step: the token in targets[0] goes in, its successor comes out
+int ar_body(orn_model* m, orn_cache* c) {
+  Workspace& w = m->ws;
+  return forward_greedy_dev(m, c, w.targets, 1, false, w.vh, w.targets);
+}
+
+// Run a step body eagerly the first time a shape is seen, capture it into a CUDA
+// graph the second time and replay it afterwards.  The host-side bookkeeping the
+// body does (positions, counters) is repeated by hand on a replay.
+int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar*/, int want, bool use_frspec) {
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  const int key = kind * 64 + want * 2 + (use_frspec ? 1 : 0);
+  orn_cache::StepGraph& g = c->graphs[key];
+  const int n_rows = want + 1;
+  if (c->h_pos + n_rows > m->cfg.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "forward: context exceeds max_ctx");
+  if (kind == 0 && c->h_mtp_pos + want > m->cfg.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "mtp: context exceeds max_ctx");
+  static int no_graph = -1;
+  if (no_graph < 0) { const char* e = getenv("ORN_NO_GRAPH"); no_graph = (e && e[0] == '1') ? 1 : 0; }
+  if (g.exec != nullptr) {
+    ORN_CHECK_CUDA(ctx, cudaGraphLaunch(g.exec, s));
+    ctx->launches += g.launches;
+    if (kind == 0) { c->h_mtp_pos += want; c->cap_T = n_rows; }
+    else { c->h_pos += 1; c->h_cur += 1; }
+    return ORN_OK;
+  }
+  if (g.seen == 0 || no_graph || !use_fused()) {
+    g.seen += 1;
+    return kind == 0 ? cycle_body(m, c, want, use_frspec) : ar_body(m, c);
+  }
+  const int64_t l0 = ctx->launches;
+  ORN_CHECK_CUDA(ctx, cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+  int rc = kind == 0 ? cycle_body(m, c, want, use_frspec) : ar_body(m, c);
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(s, &graph);
+  if (rc != ORN_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+  if (e != cudaSuccess) ORN_FAIL(ctx, ORN_ERR_CUDA, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(e));
+  e = cudaGraphInstantiate(&g.exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) { g.exec = nullptr; ORN_FAIL(ctx, ORN_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e)); }
+  g.launches = ctx->launches - l0;
+  // the capture recorded the work without running it; the host bookkeeping it did stands
+  ORN_CHECK_CUDA(ctx, cudaGraphLaunch(g.exec, s));
+  return ORN_OK;
+}
+
 // generate::prefill (src/generate.rs:90-136): everything but the last prompt
 // token.  Rows are computed with one-row arithmetic, so the chunk width (the
 // reference's prefill_step) cannot change the result; chunks are cut to the
@@ -902,6 +992,10 @@ int32_t orn_cache_create(orn_model* m, orn_cache** out) {
     if (rc == ORN_OK) rc = orn_upload(m->ctx, k->conv_table, table.data(), sizeof(bf16_t*) * table.size());
   }
   if (rc != ORN_OK) { orn_cache_destroy(k); return rc; }
+  if (cudaMallocHost((void**)&k->mailbox_h, 16 * sizeof(uint32_t)) != cudaSuccess) {
+    orn_cache_destroy(k);
+    ORN_FAIL(m->ctx, ORN_ERR_ALLOC, "cache_create: pinned mailbox");
+  }
   k->cur = k->pos + 1;
   k->mtp_pos = k->pos + 2;
   *out = k;
@@ -916,6 +1010,9 @@ int32_t orn_cache_destroy(orn_cache* k) {
   for (auto p : k->conv) cudaFree(p);
   for (auto p : k->ring) cudaFree(p);
   cudaFree(k->mtp_kc); cudaFree(k->mtp_vc); cudaFree(k->pos); cudaFree(k->conv_table);
+  for (auto& g : k->graphs)
+    if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+  if (k->mailbox_h) cudaFreeHost(k->mailbox_h);
   delete k;
   return ORN_OK;
 }
@@ -1004,7 +1101,7 @@ int32_t orn_generate_step(orn_model* m, orn_cache* c, const uint32_t* prompt, in
   while (n != max_tokens) {
     // the next step is taken before the token is handed out (generate.rs:195-205);
     // the sampled token stays on the device and feeds the next forward directly
-    CK(forward_greedy_dev(m, c, w.targets, 1, false, w.vh, w.targets));
+    CK(run_step(m, c, 1, 0, false));
     uint32_t next = 0;
     CK(orn_download(ctx, &next, w.targets, 4));
     m->prof.ar_steps += 1;
@@ -1069,36 +1166,23 @@ int32_t orn_generate_step_mtp(orn_model* m, orn_cache* c, const uint32_t* prompt
     int want = max_tokens - (emitted + 1);
     if (want < 0) want = 0;
     if (want > depth) want = depth;
-    // ---- draft (mtp_generate.rs:99-135): window built on the device
-    set_u32_kernel<<<1, 1, 0, s>>>(w.window, primary);
-    CK(orn_launch_check(ctx, "set_u32"));
-    const bf16_t* dh_in = w.hrow;
+    // ---- draft + verify on the device; the host only fills the mailbox
+    uint32_t* mb = c->mailbox_h;
+    for (int i = 0; i < 16; ++i) mb[i] = 0;
+    mb[0] = primary;
     for (int i = 0; i < want; ++i) {
-      bf16_t* dh_out = w.dh + (size_t)(i & 1) * H;
-      CK(mtp_step(m, c, dh_in, w.window + i, 1, dlm, dh_out, w.dlogits, false));
-      if (use_frspec) {
-        CK(k_greedy(ctx, s, w.dlogits, 1, dlm->O, 0, w.local, w.greedy_scratch));
-        gather_u32_kernel<<<1, 1, 0, s>>>(m->fr_ids, w.local, w.window + i + 1);
-        CK(orn_launch_check(ctx, "gather_u32"));
-      } else {
-        CK(k_greedy(ctx, s, w.dlogits, 1, dlm->O, 0, w.window + i + 1, w.greedy_scratch));
-      }
       if (force && force->p > 0.f && emitted + 1 + i < force->len) {
         uint64_t rnd = splitmix64(force->seed + cycle_idx * 8 + (uint64_t)i);
         float uni = (float)(rnd >> 40) * (1.0f / 16777216.0f);
-        if (uni < force->p) {
-          set_u32_kernel<<<1, 1, 0, s>>>(w.window + i + 1, force->stream[emitted + 1 + i]);
-          CK(orn_launch_check(ctx, "set_u32"));
-        }
+        if (uni < force->p) { mb[1 + i] = 1; mb[4 + i] = force->stream[emitted + 1 + i]; }
       }
-      dh_in = dh_out;
-      m->prof.draft_steps += 1;
     }
+    ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(w.mailbox, mb, 16 * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+    CK(run_step(m, c, 0, want, use_frspec != 0));
+    m->prof.draft_steps += want;
     if (want > 0) { stats->cycles += 1; stats->drafted += want; }
     cycle_idx += 1;
-    // ---- verify: one trunk forward over the window, all rows' targets at once
     const int n_rows = want + 1;
-    CK(forward_greedy_dev(m, c, w.window, n_rows, true, w.vh, w.targets));
     m->prof.verify_steps += 1;
     // the one host round trip of the cycle (mtp_generate.rs:250-254)
     ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(hbuf, w.targets, 4 * (size_t)n_rows, cudaMemcpyDeviceToHost, s));
