@@ -129,6 +129,18 @@ int32_t orn_rms_norm(orn_ctx* ctx, const uint16_t* dev_x, const uint16_t* dev_w 
 int32_t orn_add_rms_norm(orn_ctx* ctx, const uint16_t* dev_a, const uint16_t* dev_b,
                          const uint16_t* dev_w, int32_t rows, int32_t n, float eps,
                          uint16_t* dev_h, uint16_t* dev_out);
+/* The decode layers' fused form of add_rms_norm followed by up to four
+ * Linear::matmul over the same normed rows (src/model/qwen3_5.rs:478-565 runs
+ * input_layernorm then in_proj_qkv / in_proj_z / in_proj_a / in_proj_b;
+ * norm.rs:19-220, linear.rs:23-80): h = bf16(a + b) (b nullable: h = a),
+ * x = w * bf16(h * rsqrt(mean(h^2) + eps)), outs[j][M, O_j] = x lins[j]^T.
+ * One persistent kernel; results are bit-identical to orn_add_rms_norm +
+ * orn_gemv.  M <= 4, K <= 2048, njobs <= 4; dev_h / dev_normed (nullable)
+ * receive h and x. */
+int32_t orn_add_norm_gemv(orn_ctx* ctx, const uint16_t* dev_a, const uint16_t* dev_b /*nullable*/,
+                          const uint16_t* dev_w, int32_t M, int32_t K, float eps,
+                          const orn_linear* const* lins, uint16_t* const* dev_outs, int32_t njobs,
+                          uint16_t* dev_h /*nullable*/, uint16_t* dev_normed /*nullable*/);
 int32_t orn_rms_norm_gated(orn_ctx* ctx, const uint16_t* dev_x, const uint16_t* dev_w,
                            const uint16_t* dev_z, int32_t rows, int32_t n, float eps,
                            uint16_t* dev_out);

@@ -286,6 +286,8 @@ class Model:
 
     def forward(self, cache, ids):
         ids = np.ascontiguousarray(ids, np.uint32)
+        if lib().orc_cache_offset(cache) + len(ids) > self.cfg.max_ctx:
+            raise ValueError("oracle forward: the window would pass max_ctx=%d" % self.cfg.max_ctx)
         out = np.zeros((len(ids), self.cfg.hidden), np.uint16)
         lib().orc_forward(self.h, cache, ptr(ids), len(ids), ptr(out), None)
         return out

@@ -323,6 +323,22 @@ class Cache:
             self.h = None
 
 
+def add_norm_gemv(ctx, a, b, w, M, K, eps, lins, want_h=False, want_normed=False):
+    """add_rms_norm followed by up to four Linear::matmul over the same rows, one
+    persistent kernel (src/model/qwen3_5.rs:478-565, norm.rs:19-220, linear.rs:23-80).
+    Returns (outs, h, normed)."""
+    n = len(lins)
+    outs = [ctx.empty((M, L.O), np.uint16) for L in lins]
+    lin_arr = (C.c_void_p * n)(*[L.h for L in lins])
+    out_arr = (C.c_void_p * n)(*[o.ptr for o in outs])
+    h = ctx.empty((M, K), np.uint16) if want_h else None
+    normed = ctx.empty((M, K), np.uint16) if want_normed else None
+    ctx.check(ctx._lib.orn_add_norm_gemv(ctx.h, _p(a), _p(b) if b is not None else None, _p(w), M, K, eps,
+                                         lin_arr, out_arr, n, h.ptr if h else None,
+                                         normed.ptr if normed else None), "orn_add_norm_gemv")
+    return outs, h, normed
+
+
 def generate_step(model, cache, prompt, max_tokens, prefill_step=2048, on_token=None):
     """generate::generate_step with the Greedy sampler (src/generate.rs:162-206).
     Returns the list of emitted tokens; `on_token(tok) -> bool` may stop early."""

@@ -78,6 +78,7 @@ SIGNATURES = {
     "orn_embedding": (i32, [vp, vp, vp, i32, vp]),
     "orn_rms_norm": (i32, [vp, vp, vp, i32, i32, f32, vp]),
     "orn_add_rms_norm": (i32, [vp, vp, vp, vp, i32, i32, f32, vp, vp]),
+    "orn_add_norm_gemv": (i32, [vp, vp, vp, vp, i32, i32, f32, vp, vp, i32, vp, vp]),
     "orn_rms_norm_gated": (i32, [vp, vp, vp, vp, i32, i32, f32, vp]),
     "orn_sigmoid_gate": (i32, [vp, vp, vp, i32, i32, vp]),
     "orn_swiglu": (i32, [vp, vp, vp, i32, vp]),

@@ -6,12 +6,68 @@
 #include <cstring>
 
 #include "orn_internal.h"
+#include "fused.h"
 
 #define CK(call)                     \
   do {                               \
     int rc__ = (call);               \
     if (rc__ != ORN_OK) return rc__; \
   } while (0)
+
+// ---- ORN_KTIME=1: device time per kernel name, printed when the context is destroyed ----
+struct orn_ktime {
+  std::vector<cudaEvent_t> ev;
+  std::vector<const char*> name;
+  size_t n = 0;
+  std::map<std::string, std::pair<double, long>> agg;
+};
+
+static void ktime_flush(orn_ctx* ctx) {
+  orn_ktime* k = ctx->kt;
+  if (k->n == 0) return;
+  cudaEventSynchronize(k->ev[k->n - 1]);
+  for (size_t i = 1; i < k->n; ++i) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, k->ev[i - 1], k->ev[i]) == cudaSuccess) {
+      auto& a = k->agg[k->name[i]];
+      a.first += ms;
+      a.second += 1;
+    }
+  }
+  k->n = 0;
+}
+
+void orn_ktime_mark(orn_ctx* ctx, const char* what) {
+  orn_ktime* k = ctx->kt;
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(ctx->stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return;
+  if (k->n == k->ev.size()) {
+    if (k->ev.size() < 16384) {
+      cudaEvent_t e;
+      if (cudaEventCreate(&e) != cudaSuccess) return;
+      k->ev.push_back(e);
+      k->name.push_back(what);
+    } else {
+      ktime_flush(ctx);
+    }
+  }
+  k->name[k->n] = what;
+  cudaEventRecord(k->ev[k->n], ctx->stream);
+  k->n += 1;
+}
+
+static void ktime_report(orn_ctx* ctx) {
+  ktime_flush(ctx);
+  double total = 0;
+  for (auto& kv : ctx->kt->agg) total += kv.second.first;
+  fprintf(stderr, "[ORN_KTIME] %-28s %10s %10s %8s %6s\n", "kernel", "launches", "total ms", "avg us", "share");
+  for (auto& kv : ctx->kt->agg)
+    fprintf(stderr, "[ORN_KTIME] %-28s %10ld %10.3f %8.2f %5.1f%%\n", kv.first.c_str(), kv.second.second,
+            kv.second.first, 1e3 * kv.second.first / kv.second.second, 100.0 * kv.second.first / total);
+  for (cudaEvent_t e : ctx->kt->ev) cudaEventDestroy(e);
+  delete ctx->kt;
+  ctx->kt = nullptr;
+}
 
 extern "C" {
 
@@ -35,6 +91,8 @@ int32_t orn_ctx_create(int32_t device, orn_ctx** out) {
     delete c;
     return ORN_ERR_ALLOC;
   }
+  const char* kt = getenv("ORN_KTIME");
+  if (kt && kt[0] == '1') c->kt = new orn_ktime();
   *out = c;
   return ORN_OK;
 }
@@ -43,6 +101,7 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
   if (!ctx) return ORN_ERR_ARG;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->kt) ktime_report(ctx);
   if (ctx->t0) cudaEventDestroy(ctx->t0);
   if (ctx->t1) cudaEventDestroy(ctx->t1);
   cudaFree(ctx->dev_err);
@@ -307,6 +366,20 @@ int32_t orn_add_rms_norm(orn_ctx* ctx, const uint16_t* a, const uint16_t* b, con
                          int32_t rows, int32_t n, float eps, uint16_t* h, uint16_t* out) {
   if (!ctx || !a || !b || !h || !out || rows < 1 || n < 1) return ORN_ERR_ARG;
   return k_add_rms_norm(ctx, ctx->stream, a, b, w, rows, n, eps, h, out);
+}
+int32_t orn_add_norm_gemv(orn_ctx* ctx, const uint16_t* a, const uint16_t* b, const uint16_t* w, int32_t M,
+                          int32_t K, float eps, const orn_linear* const* lins, uint16_t* const* outs,
+                          int32_t njobs, uint16_t* h, uint16_t* normed) {
+  if (!ctx || !a || !w || !lins || !outs || M < 1 || M > 4 || njobs < 1 || njobs > 4) return ORN_ERR_ARG;
+  FusedPrologue fp;
+  fp.mode = PRO_ADDNORM; fp.K = K; fp.a = a; fp.b = b; fp.w = w; fp.eps = eps; fp.sum_out = h; fp.norm_out = normed;
+  FusedJob jobs[4];
+  for (int j = 0; j < njobs; ++j) {
+    if (!lins[j] || !outs[j] || lins[j]->E != 1) return ORN_ERR_ARG;
+    jobs[j].lin = lins[j];
+    jobs[j].out = outs[j];
+  }
+  return f_norm_gemv(ctx, ctx->stream, M, fp, jobs, njobs);
 }
 int32_t orn_rms_norm_gated(orn_ctx* ctx, const uint16_t* x, const uint16_t* w, const uint16_t* z,
                            int32_t rows, int32_t n, float eps, uint16_t* out) {

@@ -18,6 +18,9 @@
 // sparse_moe_block (src/ops/moe.rs:662-741), gdn_front + gated_delta_kernel
 // (src/ops/gdn.rs:191-413), Attention::forward (src/model/qwen3_5.rs:430-474).
 #include <algorithm>
+#include <cstdio>
+#include <set>
+#include <string>
 
 #include "orn_internal.h"
 #include "orn_quant.cuh"
@@ -25,7 +28,7 @@
 
 #ifdef ORN_DEBUG_CLOCKS
 __device__ long long g_dbg[32];
-#define DBG(i) do { if (blockIdx.x == 3 && threadIdx.x == 0) g_dbg[i] = clock64(); } while (0)
+#define DBG(i) do { if (blockIdx.x == 3 && threadIdx.x == 0 && J.job[0].lin.O == 8192) g_dbg[i] = clock64(); } while (0)
 extern "C" int orn_debug_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_dbg, sizeof(long long) * 32); }
 #else
 #define DBG(i)
@@ -1424,6 +1427,15 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
 // ---------------------------------------------------------------------------
 constexpr size_t kSmemBudget = 220 * 1024;
 
+// launch label for the per-kernel time report (ORN_KTIME=1): kernel, rows, first job's shape
+const char* launch_label(orn_ctx* ctx, const char* kern, int M, int kind, int O, int K) {
+  if (!ctx->kt) return kern;
+  static std::set<std::string> pool;
+  char buf[96];
+  snprintf(buf, sizeof buf, "%s M=%d kind=%d %dx%d", kern, M, kind, O, K);
+  return pool.insert(buf).first->c_str();
+}
+
 // raise a kernel's dynamic shared-memory limit once (per kernel, per process)
 template <typename Kern>
 int set_smem(orn_ctx* ctx, Kern kern, size_t bytes) {
@@ -1466,7 +1478,7 @@ int launch_norm_gemv_mask(orn_ctx* ctx, cudaStream_t s, const Prologue& P, const
   rc = set_smem(ctx, k_norm_gemv<M, MASK>, bytes);
   if (rc != ORN_OK) return rc;
   k_norm_gemv<M, MASK><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, J, slot, depth, (uint32_t)fixed, ctx->dev_err);
-  return orn_launch_check(ctx, "k_norm_gemv");
+  return orn_launch_check(ctx, launch_label(ctx, "k_norm_gemv", M, J.job[0].lin.kind, J.job[0].lin.O, P.K));
 }
 
 template <int M>
@@ -1520,7 +1532,7 @@ int launch_moe_up_k(orn_ctx* ctx, cudaStream_t s, const MoeUpParams& P) {
   rc = set_smem(ctx, k_moe_up<KIND, M>, bytes);
   if (rc != ORN_OK) return rc;
   k_moe_up<KIND, M><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, slot, depth, ctx->dev_err);
-  return orn_launch_check(ctx, "k_moe_up");
+  return orn_launch_check(ctx, launch_label(ctx, "k_moe_up", M, KIND, P.I, P.H));
 }
 
 template <int KIND, int M>
@@ -1541,7 +1553,7 @@ int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
   rc = set_smem(ctx, k_moe_down<KIND, M>, bytes);
   if (rc != ORN_OK) return rc;
   k_moe_down<KIND, M><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, slot, depth, ctx->dev_err);
-  return orn_launch_check(ctx, "k_moe_down");
+  return orn_launch_check(ctx, launch_label(ctx, "k_moe_down", M, KIND, P.H, P.I));
 }
 
 }  // namespace

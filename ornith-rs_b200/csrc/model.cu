@@ -691,6 +691,7 @@ int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar*/, int want, b
   if (kind == 0 && c->h_mtp_pos + want > m->cfg.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "mtp: context exceeds max_ctx");
   static int no_graph = -1;
   if (no_graph < 0) { const char* e = getenv("ORN_NO_GRAPH"); no_graph = (e && e[0] == '1') ? 1 : 0; }
+  if (ctx->kt) no_graph = 1;  // per-kernel times need eager launches
   if (g.exec != nullptr) {
     ORN_CHECK_CUDA(ctx, cudaGraphLaunch(g.exec, s));
     ctx->launches += g.launches;

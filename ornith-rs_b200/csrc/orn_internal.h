@@ -19,7 +19,12 @@ struct orn_ctx {
   int sm_count = 148;
   cudaEvent_t t0 = nullptr, t1 = nullptr;  // orn_timer_start / orn_timer_stop
   int* dev_err = nullptr;  // set by a kernel whose bounded wait ran out
+  struct orn_ktime* kt = nullptr;  // per-kernel device times when ORN_KTIME=1 (eager launches only)
 };
+
+// Records an event after the launch just made and attributes the device time
+// since the previous mark to `what` (api.cu).
+void orn_ktime_mark(orn_ctx* ctx, const char* what);
 
 // Device-resident weight matrix [E, O, K].
 //   Q4_K: w = nibble bytes [E,O,K/2]; s = 16-byte records [E,O,K/256] =
@@ -71,6 +76,7 @@ static inline int orn_launch_check(orn_ctx* ctx, const char* what) {
     return ORN_ERR_CUDA;
   }
   ctx->launches += 1;
+  if (ctx->kt) orn_ktime_mark(ctx, what);
   return ORN_OK;
 }
 
