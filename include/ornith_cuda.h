@@ -189,6 +189,18 @@ int32_t orn_sdpa_decode(orn_ctx* ctx, const uint16_t* dev_q, const uint16_t* dev
 /* ---- greedy sampling (src/ops/sample.rs:134-147,186-191) */
 int32_t orn_greedy(orn_ctx* ctx, const uint16_t* dev_logits, int32_t T, int32_t V,
                    int32_t normalize, uint32_t* dev_tokens);
+/* The same result as orn_greedy without allocating anything.  No counterpart in
+ * the reference (its Metal buffers come from a pool, src/metal/mod.rs:137-143):
+ * this is for callers that must not call the device allocator.  The kernels'
+ * scratch is a fixed 8 KB array in the library's device memory, so T <= 4 and
+ * V <= 262144; anything larger returns ORN_ERR_ARG (use orn_greedy).  The work
+ * is queued on the context's stream and the call returns without waiting
+ * (orn_sync or a download waits).  The first call on each device looks the
+ * array's address up once; make that first call before any stream capture
+ * begins.  All calls on a device share the one array: calls that may overlap in
+ * time race on it, so keep them on one stream or serialise them. */
+int32_t orn_greedy_static(orn_ctx* ctx, const uint16_t* dev_logits, int32_t T, int32_t V,
+                          int32_t normalize, uint32_t* dev_tokens);
 
 /* ---- model (src/model/qwen3_5.rs, mtp.rs, cache.rs; src/weights.rs) */
 int32_t orn_model_create(orn_ctx* ctx, const orn_config* cfg, orn_model** out);

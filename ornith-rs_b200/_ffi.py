@@ -91,6 +91,7 @@ SIGNATURES = {
     "orn_rope": (i32, [vp, vp, i32, i32, i32, i32, f32, i32]),
     "orn_sdpa_decode": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
     "orn_greedy": (i32, [vp, vp, i32, i32, i32, vp]),
+    "orn_greedy_static": (i32, [vp, vp, i32, i32, i32, vp]),
     "orn_model_create": (i32, [vp, C.POINTER(Config), c_void_pp]),
     "orn_model_destroy": (i32, [vp]),
     "orn_model_set_linear": (i32, [vp, C.c_char_p, vp]),

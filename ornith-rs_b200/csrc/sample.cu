@@ -125,3 +125,59 @@ int k_greedy(orn_ctx* ctx, cudaStream_t s, const bf16_t* logits, int T, int V, i
   greedy_finish_kernel<<<T, 256, shm, s>>>(logits, V, nc, normalize, scratch, tokens);
   return orn_launch_check(ctx, "greedy_finish");
 }
+
+// ---------------------------------------------------------------------------
+// Greedy sampling without any allocation.
+//
+// orn_greedy borrows its [T, 2*ceil(V/1024)] floats of scratch from the device
+// allocator on every call.  Some callers must not touch the allocator at all: a
+// decode loop that runs with the allocator's device-wide lock held elsewhere
+// (another thread loading weights), a host thread whose latency budget cannot
+// absorb an allocation that may synchronise the whole device, or code that has
+// already begun recording work on its stream and may no longer call routines
+// that allocate.  For them the same two kernels run on a fixed scratch array
+// that lives in the module's global memory.
+//
+// The array is sized for the largest decode window and vocabulary the engine
+// serves: 4 rows of at most 262144 logits = 2048 floats (8 KB).  Larger inputs
+// are refused; orn_greedy serves them.
+//
+// Nothing in the array has to start at zero: the first kernel writes every
+// element the second one reads.
+//
+// Every call on a device shares the one array.  Two calls whose kernels may
+// overlap in time (different streams or contexts of the same device, or two
+// host threads) race on it; callers serialise them, e.g. by using one stream.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int kStaticGreedyMaxT = 4;
+constexpr int kStaticGreedyMaxV = 262144;
+constexpr size_t kStaticGreedyFloats = (size_t)kStaticGreedyMaxT * 2 * (kStaticGreedyMaxV / 1024);
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_ptr[kMaxDevices];   // device address of the array, per device
+bool g_static_scratch_ready[kMaxDevices];
+}  // namespace
+
+static __device__ __align__(256) float g_greedy_static_scratch[kStaticGreedyFloats];
+
+extern "C" int32_t orn_greedy_static(orn_ctx* ctx, const uint16_t* logits, int32_t T, int32_t V, int32_t normalize,
+                                     uint32_t* tokens) {
+  if (!ctx || !logits || !tokens || T < 1 || V < 1) return ORN_ERR_ARG;
+  if (T > kStaticGreedyMaxT || V > kStaticGreedyMaxV)
+    ORN_FAIL(ctx, ORN_ERR_ARG,
+             "orn_greedy_static: at most 4 rows of at most 262144 logits fit the fixed 8 KB scratch; "
+             "use orn_greedy for larger inputs");
+  const int dev = ctx->device;
+  if (dev < 0 || dev >= kMaxDevices) ORN_FAIL(ctx, ORN_ERR_ARG, "orn_greedy_static: device index above 63");
+  if (!g_static_scratch_ready[dev]) {
+    // one-time set-up per device, with that device current: ask the runtime where this
+    // device's copy of the array lives (the array's name is not a device address on the host)
+    ORN_CHECK_CUDA(ctx, cudaSetDevice(dev));
+    float* p = nullptr;
+    ORN_CHECK_CUDA(ctx, cudaGetSymbolAddress((void**)&p, g_greedy_static_scratch));
+    if (p == nullptr) ORN_FAIL(ctx, ORN_ERR_CUDA, "orn_greedy_static: no device address for the scratch array");
+    g_static_scratch_ptr[dev] = p;
+    g_static_scratch_ready[dev] = true;
+  }
+  return k_greedy(ctx, ctx->stream, (const bf16_t*)logits, T, V, normalize, tokens, g_static_scratch_ptr[dev]);
+}
