@@ -7,7 +7,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libornith_cuda.so")
+LIB_PATH = os.environ.get("ORN_CUDA_LIB") or os.path.join(_HERE, "libornith_cuda.so")  # the override serves A/B timing of builds
 
 Q4K, Q6K, A8, BF16 = 0, 1, 2, 3
 POLICY_CYCLE, POLICY_COMMITTED = 0, 1

@@ -91,6 +91,8 @@ int32_t orn_ctx_create(int32_t device, orn_ctx** out) {
     delete c;
     return ORN_ERR_ALLOC;
   }
+  const char* np = getenv("ORN_NO_PDL");
+  if (np && np[0] == '1') c->pdl = false;
   const char* kt = getenv("ORN_KTIME");
   if (kt && kt[0] == '1') c->kt = new orn_ktime();
   *out = c;
@@ -199,15 +201,16 @@ static int linear_alloc(orn_ctx* ctx, int kind, int E, int O, int K, orn_linear*
   CK(check_linear_shape(ctx, kind, E, O, K));
   orn_linear* L = new orn_linear();
   L->kind = kind; L->E = E; L->O = O; L->K = K;
-  linear_alloc_sizes(kind, E, O, K, &L->w_bytes, &L->s_bytes, &L->b_bytes);
+  const RecGeom g = rec_geom(kind, K);
+  L->rec = g.rec;
+  L->w_bytes = (size_t)E * O * g.rec;
   int rc = orn_alloc(ctx, L->w_bytes, (void**)&L->w);
-  if (rc == ORN_OK && L->s_bytes) rc = orn_alloc(ctx, L->s_bytes, (void**)&L->s);
-  if (rc == ORN_OK && L->b_bytes) rc = orn_alloc(ctx, L->b_bytes, (void**)&L->b);
   if (rc != ORN_OK) {
-    cudaFree(L->w); cudaFree(L->s); cudaFree(L->b);
     delete L;
     return rc;
   }
+  L->s = L->w + g.b0;
+  L->b = L->w + g.b0 + g.b1;
   *out = L;
   return ORN_OK;
 }
@@ -223,21 +226,19 @@ int32_t orn_linear_create(orn_ctx* ctx, int32_t kind, int32_t E, int32_t O, int3
   linear_artifact_sizes(kind, E, O, K, &aw, &as, &ab);
   orn_linear* L = nullptr;
   CK(linear_alloc(ctx, kind, E, O, K, &L));
-  // stage the artifact tensors on the device, then repack there
-  uint8_t *dw = nullptr, *ds = nullptr, *db = nullptr;
   int rc = ORN_OK;
-  if (kind == ORN_BF16 || kind == ORN_Q6K) {
-    // layouts coincide: upload straight into place
-    rc = orn_upload(ctx, L->w, host_w, aw);
-    if (rc == ORN_OK && as) rc = orn_upload(ctx, L->s, host_s, as);
-    if (rc == ORN_OK && ab) rc = orn_upload(ctx, L->b, host_b, ab);
+  if (kind == ORN_BF16) {
+    rc = orn_upload(ctx, L->w, host_w, aw);  // a bf16 record is the row itself
   } else {
-    rc = orn_upload(ctx, L->w, host_w, aw);
+    // stage the artifact tensors on the device, then build the row records there
+    uint8_t *dw = nullptr, *ds = nullptr, *db = nullptr;
+    rc = orn_alloc(ctx, aw, (void**)&dw);
     if (rc == ORN_OK) rc = orn_alloc(ctx, as, (void**)&ds);
     if (rc == ORN_OK) rc = orn_alloc(ctx, ab, (void**)&db);
+    if (rc == ORN_OK) rc = orn_upload(ctx, dw, host_w, aw);
     if (rc == ORN_OK) rc = orn_upload(ctx, ds, host_s, as);
     if (rc == ORN_OK) rc = orn_upload(ctx, db, host_b, ab);
-    if (rc == ORN_OK) rc = k_linear_pack(ctx, ctx->stream, L, L->w, ds, db);
+    if (rc == ORN_OK) rc = k_linear_pack(ctx, ctx->stream, L, dw, ds, db);
     if (rc == ORN_OK) rc = orn_sync(ctx);
     cudaFree(dw); cudaFree(ds); cudaFree(db);
   }
@@ -281,31 +282,24 @@ int32_t orn_linear_export(orn_ctx* ctx, const orn_linear* lin, void* host_w, voi
   if (!ctx || !lin || !host_w) return ORN_ERR_ARG;
   size_t aw, as, ab;
   linear_artifact_sizes(lin->kind, lin->E, lin->O, lin->K, &aw, &as, &ab);
-  if (lin->kind == ORN_BF16 || lin->kind == ORN_Q6K) {
-    CK(orn_download(ctx, host_w, lin->w, aw));
-    if (as) CK(orn_download(ctx, host_s, lin->s, as));
-    if (ab) CK(orn_download(ctx, host_b, lin->b, ab));
-    return ORN_OK;
-  }
+  if (lin->kind == ORN_BF16) return orn_download(ctx, host_w, lin->w, aw);
   if (!host_s || !host_b) return ORN_ERR_ARG;
-  uint8_t *ds = nullptr, *db = nullptr;
-  int rc = orn_alloc(ctx, as, (void**)&ds);
+  uint8_t *dw = nullptr, *ds = nullptr, *db = nullptr;
+  int rc = orn_alloc(ctx, aw, (void**)&dw);
+  if (rc == ORN_OK) rc = orn_alloc(ctx, as, (void**)&ds);
   if (rc == ORN_OK) rc = orn_alloc(ctx, ab, (void**)&db);
-  if (rc == ORN_OK) rc = orn_download(ctx, host_w, lin->w, aw);
-  if (rc == ORN_OK) {
-    // unpack the header stream only; the code stream is already in place
-    rc = k_linear_unpack(ctx, ctx->stream, lin, nullptr, ds, db);
-    if (rc == ORN_OK) rc = orn_download(ctx, host_s, ds, as);
-    if (rc == ORN_OK) rc = orn_download(ctx, host_b, db, ab);
-  }
-  cudaFree(ds); cudaFree(db);
+  if (rc == ORN_OK) rc = k_linear_unpack(ctx, ctx->stream, lin, dw, ds, db);
+  if (rc == ORN_OK) rc = orn_download(ctx, host_w, dw, aw);
+  if (rc == ORN_OK) rc = orn_download(ctx, host_s, ds, as);
+  if (rc == ORN_OK) rc = orn_download(ctx, host_b, db, ab);
+  cudaFree(dw); cudaFree(ds); cudaFree(db);
   return rc;
 }
 
 int32_t orn_linear_destroy(orn_ctx* ctx, orn_linear* lin) {
   if (!lin) return ORN_OK;
   if (ctx) cudaStreamSynchronize(ctx->stream);
-  if (lin->owns) { cudaFree(lin->w); cudaFree(lin->s); cudaFree(lin->b); }
+  if (lin->owns) cudaFree(lin->w);
   delete lin;
   return ORN_OK;
 }

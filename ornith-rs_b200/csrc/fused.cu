@@ -26,17 +26,18 @@
 #include "orn_quant.cuh"
 #include "fused.h"
 
-#ifdef ORN_DEBUG_CLOCKS
-__device__ long long g_dbg[32];
-#define DBG(i) do { if (blockIdx.x == 3 && threadIdx.x == 0 && J.job[0].lin.O == 8192) g_dbg[i] = clock64(); } while (0)
-extern "C" int orn_debug_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_dbg, sizeof(long long) * 32); }
-#else
-#define DBG(i)
-#endif
-
 namespace {
 
-constexpr int kFusedThreads = 512;  // one CTA per SM: 16 warps, each with its own weight ring
+// Out-of-line copies of the elementary functions: these kernels run each piece of code once or
+// twice per launch, so instruction-cache misses cost more than calls do.
+__device__ __noinline__ float expf_call(float x) { return orn_expf(x); }
+__device__ __noinline__ float silu_bf_call(float x) { return orn_silu_bf(x); }
+__device__ __noinline__ float sigmoid_bf_call(float x) { return orn_sigmoid_bf(x); }
+__device__ __noinline__ float sigmoid_f32_call(float x) { return orn_sigmoid_f32(x); }
+__device__ __noinline__ float softplus_bf_call(float x) { return orn_softplus_bf(x); }
+__device__ __noinline__ void sincosf_call(float a, float* sn, float* cs) { orn_sincosf(a, sn, cs); }
+
+constexpr int kFusedThreads = 256;  // one CTA per SM: 8 warps (up to 255 registers each), each with its own weight ring
 
 // ---------------------------------------------------------------------------
 // activation staging: a row of K floats re-ordered so that lane l's pieces of
@@ -89,7 +90,7 @@ ORN_D float* stage_carve(float* base, int kind, int rows, int K, XStage& X) {
 // permuted places and, for the formats that need it, adds the unit's elements
 // in ascending order into the staged sum.
 template <int KIND>
-ORN_D void stage_fill(const float* lin, int stride, const XStage& X) {
+__device__ __noinline__ void stage_fill(const float* lin, int stride, const XStage& X) {
   constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
   const int padded = X.S * 32;  // unit slots per row, including the empty tail
   for (int m = 0; m < X.rows; ++m) {
@@ -129,14 +130,10 @@ template <int KIND> struct WU;
 
 template <> struct WU<ORN_A8> {
   struct W { uint4 q; uint32_t sb; };
-  ORN_D static void load(const LinDev& L, int64_t row, int u, W& w) {
-    w.q = ldg128_stream(L.w + row * L.K + 16 * u);
-    w.sb = __ldg(reinterpret_cast<const uint32_t*>(L.s) + row * (L.K >> 6) + (u >> 2));
-  }
-  // the same unit out of a row staged in shared memory: [codes K][sb K/16]
-  ORN_D static void lds(const uint8_t* b0, const uint8_t* b1, const LinDev&, int64_t, int u, W& w) {
-    w.q = *reinterpret_cast<const uint4*>(b0 + 16 * u);
-    w.sb = *reinterpret_cast<const uint32_t*>(b1 + 4 * (u >> 2));
+  // unit u of a row record staged in shared memory: [codes K][{scale, bias} K/64]
+  ORN_D static void lds(const uint8_t* rec, uint32_t off1, uint32_t, int u, W& w) {
+    w.q = *reinterpret_cast<const uint4*>(rec + 16 * u);
+    w.sb = *reinterpret_cast<const uint32_t*>(rec + off1 + 4 * (u >> 2));
   }
   ORN_D static float fold(const W& w, const float* x, const float* sm, int, float acc) {
     const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
@@ -156,15 +153,10 @@ template <> struct WU<ORN_A8> {
 
 template <> struct WU<ORN_Q4K> {
   struct W { uint4 q; uint4 meta; };
-  ORN_D static void load(const LinDev& L, int64_t row, int u, W& w) {
-    const int nb = L.K >> 8;
-    w.q = ldg128_stream(L.w + (row * nb + (u >> 3)) * 128 + 16 * (u & 7));
-    w.meta = ldg128(L.s + (row * nb + (u >> 3)) * 16);
-  }
-  // staged row: [codes nb*128][headers nb*16]
-  ORN_D static void lds(const uint8_t* b0, const uint8_t* b1, const LinDev&, int64_t, int u, W& w) {
-    w.q = *reinterpret_cast<const uint4*>(b0 + 16 * u);
-    w.meta = *reinterpret_cast<const uint4*>(b1 + (u >> 3) * 16);
+  // staged row record: [codes nb*128][headers nb*16]
+  ORN_D static void lds(const uint8_t* rec, uint32_t off1, uint32_t, int u, W& w) {
+    w.q = *reinterpret_cast<const uint4*>(rec + 16 * u);
+    w.meta = *reinterpret_cast<const uint4*>(rec + off1 + (u >> 3) * 16);
   }
   ORN_D static float fold(const W& w, const float* x, const float* sm, int u, float acc) {
     const int g = (u & 7) >> 1;
@@ -198,32 +190,18 @@ template <> struct WU<ORN_Q4K> {
 
 template <> struct WU<ORN_Q6K> {
   struct W { uint32_t qa, qb, qh, sc4; float d; };
-  ORN_D static void load(const LinDev& L, int64_t row, int u, W& w) {
-    const int nb = L.K >> 8;
+  // staged row record: [ql|qh nb*192][scales nb*16][d nb*2]
+  ORN_D static void lds(const uint8_t* rec, uint32_t off1, uint32_t off2, int u, W& w) {
     const int blk = u >> 4, j = u & 15, half = j >> 3, l0 = 4 * (j & 7);
-    const uint8_t* base = L.w + (row * nb + blk) * 192;
-    w.qa = ldg32_stream(base + 64 * half + l0);
-    w.qb = ldg32_stream(base + 64 * half + 32 + l0);
-    w.qh = ldg32_stream(base + 128 + 32 * half + l0);
-    const uint2 s8 = __ldg(reinterpret_cast<const uint2*>(L.s + (row * nb + blk) * 16 + 8 * half));
-    const int is = l0 >> 4;
-    const uint32_t lo = s8.x >> (8 * is), hi = s8.y >> (8 * is);
-    w.sc4 = (lo & 0xff) | (((lo >> 16) & 0xff) << 8) | ((hi & 0xff) << 16) | (((hi >> 16) & 0xff) << 24);
-    w.d = h2f(__ldg(reinterpret_cast<const uint16_t*>(L.b) + row * nb + blk));
-  }
-  // staged row: [ql|qh nb*192][scales nb*16]; the 2-byte super-scale comes from global memory
-  ORN_D static void lds(const uint8_t* b0, const uint8_t* b1, const LinDev& L, int64_t row, int u, W& w) {
-    const int nb = L.K >> 8;
-    const int blk = u >> 4, j = u & 15, half = j >> 3, l0 = 4 * (j & 7);
-    const uint8_t* base = b0 + blk * 192;
+    const uint8_t* base = rec + blk * 192;
     w.qa = *reinterpret_cast<const uint32_t*>(base + 64 * half + l0);
     w.qb = *reinterpret_cast<const uint32_t*>(base + 64 * half + 32 + l0);
     w.qh = *reinterpret_cast<const uint32_t*>(base + 128 + 32 * half + l0);
-    const uint2 s8 = *reinterpret_cast<const uint2*>(b1 + blk * 16 + 8 * half);
+    const uint2 s8 = *reinterpret_cast<const uint2*>(rec + off1 + blk * 16 + 8 * half);
     const int is = l0 >> 4;
     const uint32_t lo = s8.x >> (8 * is), hi = s8.y >> (8 * is);
     w.sc4 = (lo & 0xff) | (((lo >> 16) & 0xff) << 8) | ((hi & 0xff) << 16) | (((hi >> 16) & 0xff) << 24);
-    w.d = h2f(__ldg(reinterpret_cast<const uint16_t*>(L.b) + row * nb + blk));
+    w.d = h2f(*reinterpret_cast<const uint16_t*>(rec + off2 + 2 * blk));
   }
   ORN_D static float fold(const W& w, const float* x, const float*, int, float acc) {
     const uint32_t q1 = (w.qa & 0x0F0F0F0Fu) | ((w.qh & 0x03030303u) << 4);
@@ -251,11 +229,8 @@ template <> struct WU<ORN_Q6K> {
 
 template <> struct WU<ORN_BF16> {
   struct W { uint4 q; };
-  ORN_D static void load(const LinDev& L, int64_t row, int u, W& w) {
-    w.q = ldg128_stream(L.w + (row * L.K + 8 * u) * 2);
-  }
-  ORN_D static void lds(const uint8_t* b0, const uint8_t*, const LinDev&, int64_t, int u, W& w) {
-    w.q = *reinterpret_cast<const uint4*>(b0 + 16 * u);
+  ORN_D static void lds(const uint8_t* rec, uint32_t, uint32_t, int u, W& w) {
+    w.q = *reinterpret_cast<const uint4*>(rec + 16 * u);
   }
   ORN_D static float fold(const W& w, const float* x, const float*, int, float acc) {
     float f[8];
@@ -269,10 +244,10 @@ template <> struct WU<ORN_BF16> {
 // ---------------------------------------------------------------------------
 // weight streaming: per-warp rings of shared-memory slots filled by bulk async
 // copies (cp.async.bulk, the 1-D TMA form) that complete on an mbarrier.
-// Rows of every format are contiguous in HBM, so one or two bulk copies bring a
-// whole row (codes, then scales/headers); lane 0 of a warp issues the copies for
-// the warp's next tasks, all 32 lanes wait on the slot's barrier and read their
-// own 16-byte pieces (consecutive lanes, consecutive addresses: no bank
+// Weight rows are contiguous records in HBM (codes, then scales), so ONE bulk
+// copy brings a tile of R consecutive rows; lane 0 of a warp issues the copies
+// for the warp's next tiles, all 32 lanes wait on the slot's barrier and read
+// their own 16-byte pieces (consecutive lanes, consecutive addresses: no bank
 // conflicts).  A warp only ever waits for copies it issued itself, so there is
 // no cross-warp dependency; the wait is bounded and reports through `err`.
 // ---------------------------------------------------------------------------
@@ -305,31 +280,19 @@ ORN_D bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 ORN_D void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 ORN_D void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
-constexpr int kDownCols = 2;  // consecutive output columns a warp takes per bulk copy in the down projection
 constexpr uint32_t kWaitLimit = 1u << 14;  // try_wait rounds before giving up (each round may sleep kWaitHintNs)
 
-// A row is streamed in chunks of kChunkSteps lane-steps (32 units each).  Bytes
-// of the two streams per step; a chunk of `units` units (a multiple of 8) is
-// [stream 0][stream 1], both multiples of 16 bytes.
-constexpr int kChunkSteps = 4;
-__host__ __device__ inline uint32_t step_bytes0(int kind) { return kind == ORN_Q6K ? 384 : 512; }
-__host__ __device__ inline uint32_t step_bytes1(int kind) {
-  return kind == ORN_A8 ? 32 : kind == ORN_Q4K ? 64 : kind == ORN_Q6K ? 32 : 0;
+// Rows per tile by format and row length class (0: K <= 512, 1: K <= 2048, 2: longer), chosen so
+// that a tile is at most 9216 bytes: 8 warps x 2 slots of that fit beside the staged activations.
+constexpr int kSlotMax = 9216;
+__host__ __device__ constexpr int k_class(int K) { return K <= 512 ? 0 : K <= 2048 ? 1 : 2; }
+__host__ __device__ constexpr int tile_rows(int kind, int kc) {
+  return kind == ORN_A8    ? (kc == 0 ? 8 : kc == 1 ? 4 : 2)
+         : kind == ORN_Q4K ? (kc == 0 ? 8 : 4)
+         : kind == ORN_Q6K ? (kc == 2 ? 2 : 4)
+                           : (kc == 0 ? 8 : kc == 1 ? 2 : 1);
 }
-__host__ __device__ inline uint32_t units_bytes0(int kind, int units) { return kind == ORN_Q6K ? units * 12 : units * 16; }
-__host__ __device__ inline uint32_t units_bytes1(int kind, int units) {
-  return kind == ORN_A8 ? units : kind == ORN_Q4K ? units * 2 : kind == ORN_Q6K ? units : 0;
-}
-__host__ __device__ inline int kind_units(int kind, int K) { return K / kind_wpu(kind); }
-// largest chunk of a row, in bytes
-__host__ __device__ inline uint32_t chunk_bytes_max(int kind, int K) {
-  int units = kind_units(kind, K);
-  if (units > 32 * kChunkSteps) units = 32 * kChunkSteps;
-  return units_bytes0(kind, units) + units_bytes1(kind, units);
-}
-__host__ __device__ inline int row_chunks(int kind, int K) {
-  return (kind_units(kind, K) + 32 * kChunkSteps - 1) / (32 * kChunkSteps);
-}
+__host__ __device__ constexpr int pad_m(int M) { return M == 3 ? 4 : M; }
 
 struct Ring {
   uint32_t bar0;       // shared address of this warp's first barrier
@@ -340,27 +303,11 @@ struct Ring {
   int* err;
 };
 
-// lane 0: request chunk c of a row of L into a slot at byte offset `off`;
-// returns the bytes requested (0 when the row has no such chunk)
-ORN_D uint32_t chunk_units(const LinDev& L, int c) {
-  const int units = kind_units(L.kind, L.K) - 32 * kChunkSteps * c;
-  return units <= 0 ? 0 : (units > 32 * kChunkSteps ? 32 * kChunkSteps : units);
-}
-ORN_D uint32_t chunk_bytes(const LinDev& L, int c) {
-  const int u = chunk_units(L, c);
-  return units_bytes0(L.kind, u) + units_bytes1(L.kind, u);
-}
-ORN_D void ring_copy_chunk(const Ring& R, int slot, uint32_t off, const LinDev& L, int64_t row, int c) {
-  const int u = chunk_units(L, c);
-  if (u == 0) return;
-  const uint32_t b0 = units_bytes0(L.kind, u), b1 = units_bytes1(L.kind, u);
-  const int tot = kind_units(L.kind, L.K);
+// lane 0: one bulk copy of `bytes` (a multiple of 16) into a slot
+ORN_D void ring_fill(const Ring& R, int slot, const uint8_t* src, uint32_t bytes) {
   const uint32_t bar = R.bar0 + 8 * slot;
-  const uint32_t dst = R.buf0 + slot * R.slot_bytes + off;
-  bulk_g2s(dst, L.w + row * (int64_t)units_bytes0(L.kind, tot) + (int64_t)c * kChunkSteps * step_bytes0(L.kind), b0, bar);
-  if (b1)
-    bulk_g2s(dst + b0, L.s + row * (int64_t)units_bytes1(L.kind, tot) + (int64_t)c * kChunkSteps * step_bytes1(L.kind),
-             b1, bar);
+  mbar_expect_tx(bar, bytes);
+  bulk_g2s(R.buf0 + slot * R.slot_bytes, src, bytes, bar);
 }
 // all lanes: wait for a slot; false after the bounded wait ran out
 ORN_D bool ring_wait(const Ring& R, int slot, uint32_t parity) {
@@ -392,84 +339,86 @@ __host__ __device__ inline size_t ring_bytes(int nwarps, int depth, uint32_t slo
   return (((size_t)nwarps * depth * 8 + 127) & ~(size_t)127) + (size_t)nwarps * depth * slot_bytes;
 }
 
-// One warp, chunk c of one staged weight row (streams at p0 / p1): adds the chunk's units
-// to the lane partials acc[m] of activation rows m0 .. m0+M-1.  Units are
-// visited in ascending order within a lane across chunks; the caller zeroes
-// acc before chunk 0 and folds the lanes (warp_sum) after the last chunk.
-template <int KIND, int M>
-ORN_D void warp_chunk_dot(const uint8_t* p0, const uint8_t* p1, const LinDev& L, int64_t row, int c, const XStage& X,
-                          int m0, int lane, float (&acc)[M]) {
+// One warp, a tile of R staged row records (record r at buf + r*rec): adds every unit of the rows
+// to the lane partials acc[r*MP + m] of activation rows m0 .. m0+M-1 (MP = M padded to a power of
+// two).  A lane visits its units in ascending order, the staged activations of a lane-step are
+// read once and folded into all R rows.
+template <int KIND, int M, int R, bool TAIL>
+ORN_D void tile_step(const uint8_t* buf, uint32_t rec, uint32_t off1, uint32_t off2, int ss, int units, const float4* xb,
+                     int xrow, const float* sb, int srow, int lane, float* acc) {
   using U = WU<KIND>;
-  constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
-  // virtual stream bases so that absolute unit numbers index the chunk
-  const uint8_t* b0 = p0 - (size_t)c * kChunkSteps * step_bytes0(KIND);
-  const uint8_t* b1 = p1 - (size_t)c * kChunkSteps * step_bytes1(KIND);
-  const int s_end = min(X.S, (c + 1) * kChunkSteps);
-  for (int s = c * kChunkSteps; s < s_end; ++s) {
-    const int u = lane + 32 * s;
-    if (u < X.units) {
-      typename U::W w;
-      U::lds(b0, b1, L, row, u, w);
+  constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS, MP = pad_m(M);
+  const int u = lane + 32 * ss;
+  if (TAIL && u >= units) return;
+  typename U::W w[R];
 #pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float xv[P * 4];
-        const float4* xp = reinterpret_cast<const float4*>(X.xs) + ((size_t)((m0 + m) * X.S + s) * P) * 32 + lane;
+  for (int r = 0; r < R; ++r) U::lds(buf + r * rec, off1, off2, u, w[r]);
 #pragma unroll
-        for (int p = 0; p < P; ++p) {
-          const float4 v = xp[p * 32];
-          xv[4 * p] = v.x; xv[4 * p + 1] = v.y; xv[4 * p + 2] = v.z; xv[4 * p + 3] = v.w;
-        }
-        float sm[NS > 0 ? NS : 1];
+  for (int m = 0; m < M; ++m) {
+    float xv[P * 4];
+    const float4* xp = xb + m * xrow + ss * (P * 32);
 #pragma unroll
-        for (int i = 0; i < NS; ++i) sm[i] = X.sums[((size_t)(m0 + m) * X.units + u) * NS + i];
-        acc[m] = U::fold(w, xv, sm, u, acc[m]);
-      }
+    for (int p = 0; p < P; ++p) {
+      const float4 v = xp[p * 32];
+      xv[4 * p] = v.x; xv[4 * p + 1] = v.y; xv[4 * p + 2] = v.z; xv[4 * p + 3] = v.w;
     }
+    float sm[NS > 0 ? NS : 1];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) sm[i] = sb[m * srow + ss * 32 * NS + i];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r * MP + m] = U::fold(w[r], xv, sm, u, acc[r * MP + m]);
   }
 }
 
-// The same for R weight rows at once (row r's streams at p0 + r*st0, p1 + r*st1):
-// the staged activations of a step are read once and folded into R rows.  The
-// four steps of a chunk are unrolled so that every shared-memory access is a
-// hoisted base plus an immediate.
 template <int KIND, int M, int R>
-ORN_D void warp_chunk_dot_rows(const uint8_t* p0, uint32_t st0, const uint8_t* p1, uint32_t st1, const LinDev& L,
-                               int64_t row, int nvalid, int c, const XStage& X, int m0, int lane, float (&acc)[R][M]) {
-  using U = WU<KIND>;
+ORN_D void tile_dot(const uint8_t* buf, const LinDev& L, const XStage& X, int m0, int lane, float* acc) {
   constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
-  const int s_base = c * kChunkSteps;
-  const uint8_t* b0 = p0 - (size_t)c * kChunkSteps * step_bytes0(KIND);
-  const uint8_t* b1 = p1 - (size_t)c * kChunkSteps * step_bytes1(KIND);
-  const float4* xbase = reinterpret_cast<const float4*>(X.xs) + (size_t)(m0 * X.S + s_base) * (P * 32) + lane;
-  const int xrow = X.S * P * 32;  // float4 per activation row
-  const float* sbase = X.sums + ((size_t)m0 * X.units + 32 * s_base + lane) * NS;
+  const RecGeom g = rec_geom(KIND, L.K);
+  const float4* xb = reinterpret_cast<const float4*>(X.xs) + (size_t)m0 * X.S * (P * 32) + lane;
+  const int xrow = X.S * P * 32;
+  const float* sb = X.sums + ((size_t)m0 * X.units + lane) * NS;
   const int srow = X.units * NS;
+  // the last lane-step may be partial; one checked copy of the loop body serves both (a second,
+  // unchecked copy costs more in instruction-cache misses than the check costs in issue slots)
+  for (int ss = 0; ss < X.S; ++ss)
+    tile_step<KIND, M, R, true>(buf, g.rec, g.b0, g.b0 + g.b1, ss, X.units, xb, xrow, sb, srow, lane, acc);
+}
+
+// Butterfly over V values per lane (V a power of two <= 32) in reduce-scatter form: at the level
+// with xor mask m a lane keeps half of its values and adds its partner's copies of them, so each
+// value goes through exactly the additions of the plain xor-16..1 butterfly (a + b is commutative,
+// both partners hold the same sum) with V-1 + (5 - log2 V) shuffles instead of 5 V.  Returns the
+// lane's value; `which` is its index.  Lanes that differ only in the low 5 - log2 V bits hold copies.
+template <int V>
+ORN_D float rs_butterfly(float* v, int lane, int& which) {
+  int idx = 0;
+  int n = V;
 #pragma unroll
-  for (int ss = 0; ss < kChunkSteps; ++ss) {
-    const int u = lane + 32 * (s_base + ss);
-    if (u < X.units) {
-      typename U::W w[R];
+  for (int mask = 16; mask >= 1; mask >>= 1) {
+    if (n > 1) {
+      const int h = n >> 1;
+      const bool upper = (lane & mask) != 0;
 #pragma unroll
-      for (int r = 0; r < R; ++r)
-        if (r < nvalid) U::lds(b0 + r * st0, b1 + r * st1, L, row + r, u, w[r]);
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float xv[P * 4];
-        const float4* xp = xbase + m * xrow + ss * (P * 32);
-#pragma unroll
-        for (int p = 0; p < P; ++p) {
-          const float4 v = xp[p * 32];
-          xv[4 * p] = v.x; xv[4 * p + 1] = v.y; xv[4 * p + 2] = v.z; xv[4 * p + 3] = v.w;
+      for (int i = 0; i < V / 2; ++i) {
+        if (i < h) {
+          const float send = upper ? v[i] : v[i + h];
+          const float keep = upper ? v[i + h] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
         }
-        float sm[NS > 0 ? NS : 1];
-#pragma unroll
-        for (int i = 0; i < NS; ++i) sm[i] = sbase[m * srow + ss * 32 * NS + i];
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-          if (r < nvalid) acc[r][m] = U::fold(w[r], xv, sm, u, acc[r][m]);
       }
+      idx = idx * 2 + (upper ? 1 : 0);
+      n = h;
+    } else {
+      v[0] = v[0] + __shfl_xor_sync(0xffffffffu, v[0], mask);
     }
   }
+  which = idx;
+  return v[0];
+}
+template <>
+ORN_D float rs_butterfly<1>(float* v, int, int& which) {
+  which = 0;
+  return warp_sum(v[0]);
 }
 
 // ---------------------------------------------------------------------------
@@ -479,13 +428,16 @@ ORN_D void warp_chunk_dot_rows(const uint8_t* p0, uint32_t st0, const uint8_t* p
 // lin holds `rows` rows of n raw values (stride `stride`); inv[m] receives
 // 1/sqrt(sumsq/n + eps).  `red` is rows*32 floats of shared memory.
 // ---------------------------------------------------------------------------
-ORN_D void block_rms_inv(const float* lin, int stride, int rows, int n, float eps, float* red, float* inv) {
+__device__ __noinline__ void block_rms_inv(const float* lin, int stride, int rows, int n, float eps, float* red, float* inv) {
   const int lane = threadIdx.x & 31;
+#pragma unroll 1
   for (int i = threadIdx.x; i < rows * 32; i += blockDim.x) red[i] = 0.f;
   __syncthreads();
   const int nvt = (n + 3) / 4;
   const int nvt_pad = ((nvt + 31) / 32) * 32;
+#pragma unroll 1
   for (int m = 0; m < rows; ++m) {
+#pragma unroll 1
     for (int vt = threadIdx.x; vt < nvt_pad; vt += blockDim.x) {
       float acc = 0.f;
       if (4 * vt < n) {  // n is a multiple of 4 here
@@ -501,6 +453,7 @@ ORN_D void block_rms_inv(const float* lin, int stride, int rows, int n, float ep
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5;
+#pragma unroll 1
   for (int m = warp; m < rows; m += (blockDim.x >> 5)) {
     const float total = warp_sum(red[m * 32 + lane]);
     if (lane == 0) inv[m] = orn_rsqrtf(total / (float)n + eps);
@@ -525,106 +478,165 @@ struct Prologue {
   float eps;
 };
 
-// scratch: red[M*32 + M] floats.  Every loop walks (row m, 8-element group) so
-// that no index needs a division and global traffic is 128-bit.
-template <int M>
-ORN_D void run_prologue(const Prologue& P, float* lin, float* red) {
+// The prologues off the hottest path (plain copy, gated norm over heads, MTP join), one
+// out-of-line copy shared by every instantiation; M is a run-time count here.
+__device__ __noinline__ void prologue_other(const Prologue& P, int M, float* lin, float* red) {
   const int K = P.K;
   float* inv = red + M * 32;
-  if (P.mode == PRO_ADDNORM) {
-    // the norm weight does not depend on the statistics: fetch it before the reduction
-    float wv[4] = {0.f, 0.f, 0.f, 0.f};
-    const int c0 = threadIdx.x * 4;  // K <= 4 * blockDim.x is checked at launch
-    if (c0 < K) {
-      const uint2 ww = __ldg(reinterpret_cast<const uint2*>(P.w + c0));
-      wv[0] = bf_lo(ww.x); wv[1] = bf_hi(ww.x); wv[2] = bf_lo(ww.y); wv[3] = bf_hi(ww.y);
+  if (P.mode == PRO_PLAIN) {
+#pragma unroll 1
+    for (int c = threadIdx.x * 4; c < M * K; c += blockDim.x * 4) {
+      const uint2 av = __ldg(reinterpret_cast<const uint2*>(P.a + c));
+      *reinterpret_cast<float4*>(lin + c) = make_float4(bf_lo(av.x), bf_hi(av.x), bf_lo(av.y), bf_hi(av.y));
     }
-#pragma unroll
-    for (int m = 0; m < M; ++m)
-      if (c0 < K) {
-        const uint2 av = __ldg(reinterpret_cast<const uint2*>(P.a + (size_t)m * K + c0));
-        float v[4] = {bf_lo(av.x), bf_hi(av.x), bf_lo(av.y), bf_hi(av.y)};
-        if (P.b != nullptr) {
-          const uint2 bv = __ldg(reinterpret_cast<const uint2*>(P.b + (size_t)m * K + c0));
-          v[0] = bfr(v[0] + bf_lo(bv.x)); v[1] = bfr(v[1] + bf_hi(bv.x));
-          v[2] = bfr(v[2] + bf_lo(bv.y)); v[3] = bfr(v[3] + bf_hi(bv.y));
-        }
-        *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) = make_float4(v[0], v[1], v[2], v[3]);
-        if (P.sum_out != nullptr && blockIdx.x == 0) {
-          uint2 o;
-          o.x = (uint32_t)f2bf(v[0]) | ((uint32_t)f2bf(v[1]) << 16);
-          o.y = (uint32_t)f2bf(v[2]) | ((uint32_t)f2bf(v[3]) << 16);
-          *reinterpret_cast<uint2*>(P.sum_out + (size_t)m * K + c0) = o;
-        }
-      }
-    __syncthreads();
-    block_rms_inv(lin, K, M, K, P.eps, red, inv);
-#pragma unroll
-    for (int m = 0; m < M; ++m)
-      if (c0 < K) {
-        float4 v = *reinterpret_cast<const float4*>(lin + (size_t)m * K + c0);
-        const float iv = inv[m];
-        v.x = bfr(wv[0] * bfr(v.x * iv)); v.y = bfr(wv[1] * bfr(v.y * iv));
-        v.z = bfr(wv[2] * bfr(v.z * iv)); v.w = bfr(wv[3] * bfr(v.w * iv));
-        *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) = v;
-      }
-  } else if (P.mode == PRO_PLAIN) {
-#pragma unroll
-    for (int m = 0; m < M; ++m)
-      for (int c = threadIdx.x * 4; c < K; c += blockDim.x * 4) {
-        const uint2 av = __ldg(reinterpret_cast<const uint2*>(P.a + (size_t)m * K + c));
-        *reinterpret_cast<float4*>(lin + (size_t)m * K + c) = make_float4(bf_lo(av.x), bf_hi(av.x), bf_lo(av.y), bf_hi(av.y));
-      }
   } else if (P.mode == PRO_GATED) {
-    // rms_norm_gated over 128-wide heads (kernels/ornith_norm.metal:119-185)
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // rms_norm_gated over 128-wide heads (kernels/ornith_norm.metal:119-185): a warp per (row, head)
+    // pair, four pairs in flight per warp so that their loads overlap
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int pairs = M * (K >> 7);
-    for (int pair = warp; pair < pairs; pair += (blockDim.x >> 5)) {
-      const int base = pair * 128 + 4 * lane;
-      float xv[4];
-      float acc = 0.f;
+    const uint2 wv = __ldg(reinterpret_cast<const uint2*>(P.w + 4 * lane));
+    const float wf[4] = {bf_lo(wv.x), bf_hi(wv.x), bf_lo(wv.y), bf_hi(wv.y)};
+    for (int p0 = warp; p0 < pairs; p0 += 4 * nw) {
+      uint2 av[4], zv[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { xv[i] = bf2f(P.a[base + i]); acc = fmaf(xv[i], xv[i], acc); }
-      acc = warp_sum(acc);
-      const float iv = orn_rsqrtf(acc / 128.0f + P.eps);
+      for (int j = 0; j < 4; ++j) {
+        const int pair = p0 + j * nw;
+        if (pair < pairs) {
+          av[j] = __ldg(reinterpret_cast<const uint2*>(P.a + pair * 128 + 4 * lane));
+          zv[j] = __ldg(reinterpret_cast<const uint2*>(P.b + pair * 128 + 4 * lane));
+        }
+      }
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        const int pair = p0 + j * nw;
+        if (pair >= pairs) break;
+        const int base = pair * 128 + 4 * lane;
+        const uint2 a2 = j == 0 ? av[0] : j == 1 ? av[1] : j == 2 ? av[2] : av[3];
+        const uint2 z2 = j == 0 ? zv[0] : j == 1 ? zv[1] : j == 2 ? zv[2] : zv[3];
+        const float xv[4] = {bf_lo(a2.x), bf_hi(a2.x), bf_lo(a2.y), bf_hi(a2.y)};
+        const float gz[4] = {bf_lo(z2.x), bf_hi(z2.x), bf_lo(z2.y), bf_hi(z2.y)};
+        float acc = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float normed = bfr(bf2f(P.w[4 * lane + i]) * bfr(xv[i] * iv));
-        float g = bf2f(P.b[base + i]);
-        g = g * orn_sigmoid_f32(g);
-        lin[base + i] = bfr(g * normed);
+        for (int i = 0; i < 4; ++i) acc = fmaf(xv[i], xv[i], acc);
+        acc = warp_sum(acc);
+        const float iv = orn_rsqrtf(acc / 128.0f + P.eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float normed = bfr(wf[i] * bfr(xv[i] * iv));
+          float g = gz[i];
+          g = g * sigmoid_f32_call(g);
+          lin[base + i] = bfr(g * normed);
+        }
       }
     }
   } else {  // PRO_MTPJOIN: [norm(embed(id)) | norm(trunk hidden)] (src/model/mtp.rs:179-187)
     const int H = K >> 1;
-#pragma unroll
     for (int m = 0; m < M; ++m) {
-      const int64_t row = P.ids[m];
+      int64_t row = P.ids[m];
+      if (row >= P.emb.O) row = P.emb.O - 1;  // an id outside the table (argmax over NaN logits) must not fault
+#pragma unroll 1
       for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        const uint32_t sb = reinterpret_cast<const uint32_t*>(P.emb.s)[row * (H >> 6) + (c >> 6)];
-        lin[(size_t)m * K + c] = bfr(fmaf(bf_lo(sb), (float)P.emb.w[row * H + c], bf_hi(sb)));
+        const uint32_t sb = reinterpret_cast<const uint32_t*>(P.emb.s + row * P.emb.rec)[c >> 6];
+        lin[(size_t)m * K + c] = bfr(fmaf(bf_lo(sb), (float)P.emb.w[row * P.emb.rec + c], bf_hi(sb)));
         lin[(size_t)m * K + H + c] = bf2f(P.a[(size_t)m * H + c]);
       }
     }
     __syncthreads();
     block_rms_inv(lin, K, M, H, P.eps, red, inv);
+#pragma unroll 1
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
       const float w = bf2f(P.w[c]);
-#pragma unroll
       for (int m = 0; m < M; ++m) lin[(size_t)m * K + c] = bfr(w * bfr(lin[(size_t)m * K + c] * inv[m]));
     }
     __syncthreads();
     block_rms_inv(lin + H, K, M, H, P.eps, red, inv);
+#pragma unroll 1
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
       const float w = bf2f(P.w2[c]);
-#pragma unroll
       for (int m = 0; m < M; ++m) lin[(size_t)m * K + H + c] = bfr(w * bfr(lin[(size_t)m * K + H + c] * inv[m]));
     }
+  }
+}
+
+// The add + norm prologue's global operands, fetched into registers before the weight prefetch
+// starts: a thread owns up to kAddNormGroups groups of 4 consecutive elements of every row
+// (K <= 4 * kAddNormGroups * blockDim.x is checked at launch).
+constexpr int kAddNormGroups = 2;
+template <int M>
+struct AddNormIn {
+  uint2 w[kAddNormGroups], a[M][kAddNormGroups], b[M][kAddNormGroups];
+  ORN_D void load(const Prologue& P) {
+#pragma unroll
+    for (int g = 0; g < kAddNormGroups; ++g) {
+      const int c = 4 * (threadIdx.x + g * blockDim.x);
+      if (c < P.K) {
+        w[g] = __ldg(reinterpret_cast<const uint2*>(P.w + c));
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          a[m][g] = __ldg(reinterpret_cast<const uint2*>(P.a + (size_t)m * P.K + c));
+          if (P.b != nullptr) b[m][g] = __ldg(reinterpret_cast<const uint2*>(P.b + (size_t)m * P.K + c));
+        }
+      }
+    }
+  }
+};
+
+// scratch: red[M*32 + M] floats.  Every loop walks (row m, 4-element group) so
+// that no index needs a division and global traffic is at least 64-bit.
+template <int M>
+ORN_D void run_prologue(const Prologue& P, const AddNormIn<M>& in, float* lin, float* red) {
+  const int K = P.K;
+  float* inv = red + M * 32;
+  if (P.mode == PRO_ADDNORM) {
+#pragma unroll
+    for (int g = 0; g < kAddNormGroups; ++g) {
+      const int c0 = 4 * (threadIdx.x + g * blockDim.x);
+      if (c0 < K) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const uint2 av = in.a[m][g];
+          float v[4] = {bf_lo(av.x), bf_hi(av.x), bf_lo(av.y), bf_hi(av.y)};
+          if (P.b != nullptr) {
+            const uint2 bv = in.b[m][g];
+            v[0] = bfr(v[0] + bf_lo(bv.x)); v[1] = bfr(v[1] + bf_hi(bv.x));
+            v[2] = bfr(v[2] + bf_lo(bv.y)); v[3] = bfr(v[3] + bf_hi(bv.y));
+          }
+          *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) = make_float4(v[0], v[1], v[2], v[3]);
+          if (P.sum_out != nullptr && blockIdx.x == 0) {
+            uint2 o;
+            o.x = (uint32_t)f2bf(v[0]) | ((uint32_t)f2bf(v[1]) << 16);
+            o.y = (uint32_t)f2bf(v[2]) | ((uint32_t)f2bf(v[3]) << 16);
+            *reinterpret_cast<uint2*>(P.sum_out + (size_t)m * K + c0) = o;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    block_rms_inv(lin, K, M, K, P.eps, red, inv);
+#pragma unroll
+    for (int g = 0; g < kAddNormGroups; ++g) {
+      const int c0 = 4 * (threadIdx.x + g * blockDim.x);
+      if (c0 < K) {
+        const uint2 ww = in.w[g];
+        const float wv[4] = {bf_lo(ww.x), bf_hi(ww.x), bf_lo(ww.y), bf_hi(ww.y)};
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          float4 v = *reinterpret_cast<const float4*>(lin + (size_t)m * K + c0);
+          const float iv = inv[m];
+          v.x = bfr(wv[0] * bfr(v.x * iv)); v.y = bfr(wv[1] * bfr(v.y * iv));
+          v.z = bfr(wv[2] * bfr(v.z * iv)); v.w = bfr(wv[3] * bfr(v.w * iv));
+          *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) = v;
+        }
+      }
+    }
+  } else {
+    prologue_other(P, M, lin, red);
   }
   __syncthreads();
   if (P.norm_out != nullptr && blockIdx.x == 0) {
 #pragma unroll
     for (int m = 0; m < M; ++m)
+#pragma unroll 1
       for (int c = threadIdx.x; c < K; c += blockDim.x) P.norm_out[(size_t)m * K + c] = f2bf(lin[(size_t)m * K + c]);
   }
 }
@@ -637,77 +649,85 @@ struct RowJob {
   LinDev lin2;   // EPI_SWIGLU: the "up" matrix paired with lin ("gate")
   bf16_t* out;   // [M][O]
   int epi;       // EPI_STORE | EPI_SWIGLU
-  int tasks;     // row pairs of the job
-  int units;     // lane units per row
-  int nchunk;    // streamed chunks per row
-  uint32_t rb0, rb1;  // bytes per row of the two streams
+  int tiles;     // row tiles of the job
 };
 struct RowJobs {
   RowJob job[4];
   int njobs;
+  int total;       // tiles of all jobs
   int kinds_mask;  // bit k set when some job has weights of kind k
 };
 
-constexpr int kRowsPerTask = 2;  // consecutive weight rows a warp takes per task
+// rows per tile of a format inside a launch whose rows have K weights (class KC)
+template <int KC>
+ORN_D int rows_of(int kind) {
+  return kind == ORN_A8 ? tile_rows(ORN_A8, KC) : kind == ORN_Q4K ? tile_rows(ORN_Q4K, KC)
+         : kind == ORN_Q6K ? tile_rows(ORN_Q6K, KC) : tile_rows(ORN_BF16, KC);
+}
 
-// a warp's position in its task sequence: row pairs gw, gw+GW, ... of the
-// concatenated jobs, each in `nchunk` chunks; no divisions
-struct Cursor {
-  int j, t, c;  // job, task (row pair) within the job, chunk
-  ORN_D bool valid(const RowJobs& J) const { return j < J.njobs; }
-  ORN_D void settle(const RowJobs& J) {
-    while (j < J.njobs && t >= J.job[j].tasks) { t -= J.job[j].tasks; ++j; }
+// dot of one staged tile for the format of L (only formats in MASK are compiled in)
+template <int M, int MASK, int KC>
+ORN_D void tile_dot_masked(const uint8_t* buf, const LinDev& L, const XStage* X, int lane, float* acc) {
+  if ((MASK & (1 << ORN_A8)) && L.kind == ORN_A8)
+    tile_dot<ORN_A8, M, tile_rows(ORN_A8, KC)>(buf, L, X[ORN_A8], 0, lane, acc);
+  else if ((MASK & (1 << ORN_Q4K)) && L.kind == ORN_Q4K)
+    tile_dot<ORN_Q4K, M, tile_rows(ORN_Q4K, KC)>(buf, L, X[ORN_Q4K], 0, lane, acc);
+  else if ((MASK & (1 << ORN_Q6K)) && L.kind == ORN_Q6K)
+    tile_dot<ORN_Q6K, M, tile_rows(ORN_Q6K, KC)>(buf, L, X[ORN_Q6K], 0, lane, acc);
+  else if ((MASK & (1 << ORN_BF16)) && L.kind == ORN_BF16)
+    tile_dot<ORN_BF16, M, tile_rows(ORN_BF16, KC)>(buf, L, X[ORN_BF16], 0, lane, acc);
+}
+
+__device__ __noinline__ float swiglu_bf_call(float g, float u) { return orn_swiglu_bf(g, u); }
+
+// butterfly + store of a finished tile: R x M sums (and the paired "up" sums for SwiGLU)
+template <int M, int R>
+ORN_D void tile_store(float* acc, float* up, bool swiglu, int lane, bf16_t* out, int O, int row0, int nvalid) {
+  constexpr int MP = pad_m(M), V = R * MP;
+  int which;
+  float v = rs_butterfly<V>(acc, lane, which);
+  if (swiglu) {
+    int w2;
+    const float u = rs_butterfly<V>(up, lane, w2);
+    v = swiglu_bf_call(bfr(v), bfr(u));
   }
+  const int r = which / MP, m = which % MP;
+  if ((lane & (32 / V - 1)) == 0 && r < nvalid && m < M) out[(size_t)m * O + row0 + r] = f2bf(v);
+}
+template <int M, int MASK, int KC>
+ORN_D void tile_store_masked(int kind, float* acc, float* up, bool swiglu, int lane, bf16_t* out, int O, int row0,
+                             int nvalid) {
+  if ((MASK & (1 << ORN_A8)) && kind == ORN_A8)
+    tile_store<M, tile_rows(ORN_A8, KC)>(acc, up, swiglu, lane, out, O, row0, nvalid);
+  else if ((MASK & (1 << ORN_Q4K)) && kind == ORN_Q4K)
+    tile_store<M, tile_rows(ORN_Q4K, KC)>(acc, up, swiglu, lane, out, O, row0, nvalid);
+  else if ((MASK & (1 << ORN_Q6K)) && kind == ORN_Q6K)
+    tile_store<M, tile_rows(ORN_Q6K, KC)>(acc, up, swiglu, lane, out, O, row0, nvalid);
+  else if ((MASK & (1 << ORN_BF16)) && kind == ORN_BF16)
+    tile_store<M, tile_rows(ORN_BF16, KC)>(acc, up, swiglu, lane, out, O, row0, nvalid);
+}
+
+// position of a warp in its slot sequence: tile g of the concatenated jobs (stepping by GW),
+// resolved to (job j, tile t); SwiGLU tiles take two slots (sub 0: gate rows, sub 1: up rows)
+struct Cursor {
+  int g, j, t, sub;
+  ORN_D void locate(const RowJobs& J) {
+    j = 0;
+    t = g;
+    while (j < J.njobs && t >= J.job[j].tiles) { t -= J.job[j].tiles; ++j; }
+  }
+  ORN_D bool valid(const RowJobs& J) const { return g < J.total; }
   ORN_D void advance(const RowJobs& J, int GW) {
-    if (++c == J.job[j].nchunk) {
-      c = 0;
-      t += GW;
-      settle(J);
-    }
+    if (J.job[j].epi == EPI_SWIGLU && sub == 0) { sub = 1; return; }
+    sub = 0;
+    g += GW;
+    if (g < J.total) locate(J);
   }
 };
 
-ORN_D int job_chunk_units(const RowJob& job, int c) {
-  const int u = job.units - 32 * kChunkSteps * c;
-  return u > 32 * kChunkSteps ? 32 * kChunkSteps : u;
-}
+constexpr int kMaxAcc = 32;  // R * pad(M) never exceeds this
 
-// lane 0: request chunk c of rows [row, row+n) of matrix L into a slot at byte
-// offset `off`, laid out [n x stream 0][n x stream 1].  Whole rows (nchunk == 1)
-// are contiguous in HBM and travel as one copy per stream.
-ORN_D void job_copy_tile(const Ring& R, int slot, uint32_t off, const RowJob& job, const LinDev& L, int row, int n,
-                         int c, uint32_t b0, uint32_t b1) {
-  const uint32_t bar = R.bar0 + 8 * slot;
-  const uint32_t dst = R.buf0 + slot * R.slot_bytes + off;
-  if (job.nchunk == 1) {
-    bulk_g2s(dst, L.w + (int64_t)row * job.rb0, n * b0, bar);
-    if (b1) bulk_g2s(dst + kRowsPerTask * b0, L.s + (int64_t)row * job.rb1, n * b1, bar);
-  } else {
-    for (int r = 0; r < n; ++r) {
-      bulk_g2s(dst + r * b0, L.w + (int64_t)(row + r) * job.rb0 + (int64_t)c * kChunkSteps * step_bytes0(L.kind), b0, bar);
-      if (b1)
-        bulk_g2s(dst + kRowsPerTask * b0 + r * b1,
-                 L.s + (int64_t)(row + r) * job.rb1 + (int64_t)c * kChunkSteps * step_bytes1(L.kind), b1, bar);
-    }
-  }
-}
-
-// tile dot for the formats present in MASK only (keeps the kernel small)
-template <int M, int MASK>
-ORN_D void tile_dot_masked(const uint8_t* buf, uint32_t b0, uint32_t b1, const LinDev& L, int64_t row, int nvalid, int c,
-                           const XStage* X, int lane, float (&acc)[kRowsPerTask][M]) {
-  const uint8_t* p1 = buf + kRowsPerTask * b0;
-  if ((MASK & (1 << ORN_A8)) && L.kind == ORN_A8)
-    warp_chunk_dot_rows<ORN_A8, M, kRowsPerTask>(buf, b0, p1, b1, L, row, nvalid, c, X[ORN_A8], 0, lane, acc);
-  else if ((MASK & (1 << ORN_Q4K)) && L.kind == ORN_Q4K)
-    warp_chunk_dot_rows<ORN_Q4K, M, kRowsPerTask>(buf, b0, p1, b1, L, row, nvalid, c, X[ORN_Q4K], 0, lane, acc);
-  else if ((MASK & (1 << ORN_Q6K)) && L.kind == ORN_Q6K)
-    warp_chunk_dot_rows<ORN_Q6K, M, kRowsPerTask>(buf, b0, p1, b1, L, row, nvalid, c, X[ORN_Q6K], 0, lane, acc);
-  else if ((MASK & (1 << ORN_BF16)) && L.kind == ORN_BF16)
-    warp_chunk_dot_rows<ORN_BF16, M, kRowsPerTask>(buf, b0, p1, b1, L, row, nvalid, c, X[ORN_BF16], 0, lane, acc);
-}
-
-template <int M, int MASK>
+template <int M, int MASK, int KC>
 __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJobs J, uint32_t slot_bytes, int depth,
                                                                 uint32_t ring_off, int* err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -715,100 +735,81 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
   const int lane = threadIdx.x & 31;
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int GW = gridDim.x * (blockDim.x >> 5);
-  // The weights do not depend on the activations: the rings are set up and the
-  // first `depth` tiles of every warp requested before the prologue runs, so
-  // that HBM is busy while the CTA rebuilds its input.
-  DBG(0);
+  // The weights do not depend on the activations, so the kernel is launched as a programmatic
+  // dependent: barriers and the first `depth` tiles of every warp are requested while the
+  // previous kernel is still draining; only then does it wait for that kernel's results and
+  // rebuild its input while HBM is busy.
+  pdl_trigger();
   Ring R;
   ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
-  __syncthreads();
-  DBG(1);
-  Cursor pc{0, gw, 0}, cc{0, gw, 0};
-  pc.settle(J);
-  cc.settle(J);
+  __syncwarp();
+  Cursor pc{gw, 0, 0, 0}, cc{gw, 0, 0, 0};
+  if (pc.valid(J)) { pc.locate(J); cc = pc; }
   int pslot = 0;
   auto issue = [&]() {  // all lanes keep the cursor; lane 0 issues
     const RowJob& job = J.job[pc.j];
     if (lane == 0) {
-      const int u = job_chunk_units(job, pc.c);
-      const uint32_t b0 = units_bytes0(job.lin.kind, u), b1 = units_bytes1(job.lin.kind, u);
-      const int row = pc.t * kRowsPerTask;
-      const int n = min(kRowsPerTask, job.lin.O - row);
-      mbar_expect_tx(R.bar0 + 8 * pslot, (job.epi == EPI_SWIGLU ? 2 : 1) * n * (b0 + b1));
-      job_copy_tile(R, pslot, 0, job, job.lin, row, n, pc.c, b0, b1);
-      if (job.epi == EPI_SWIGLU) job_copy_tile(R, pslot, kRowsPerTask * (b0 + b1), job, job.lin2, row, n, pc.c, b0, b1);
+      const LinDev& L = pc.sub ? job.lin2 : job.lin;
+      const int rows = rows_of<KC>(L.kind);
+      const int row = pc.t * rows;
+      const int n = min(rows, L.O - row);
+      ring_fill(R, pslot, L.w + (size_t)row * L.rec, n * L.rec);
     }
     pc.advance(J, GW);
     if (++pslot == depth) pslot = 0;
   };
   for (int i = 0; i < depth && pc.valid(J); ++i) issue();
-  DBG(2);
+  pdl_wait();  // everything below reads what earlier kernels wrote
+  AddNormIn<M> pin;
+  if (P.mode == PRO_ADDNORM) pin.load(P);
 
   // stages, then the prologue's scratch
   float* next = smem;
   XStage X[4];
+  constexpr int mask = MASK;
 #pragma unroll
   for (int k = 0; k < 4; ++k)
-    if (MASK & (1 << k)) next = stage_carve(next, k, M, P.K, X[k]);
+    if (mask & (1 << k)) next = stage_carve(next, k, M, P.K, X[k]);
   float* lin = smem + (((next - smem) + 31) & ~31);
   float* red = lin + (size_t)M * P.K;
-  run_prologue<M>(P, lin, red);
-  DBG(3);
-  if (MASK & (1 << ORN_Q4K)) stage_fill<ORN_Q4K>(lin, P.K, X[ORN_Q4K]);
-  if (MASK & (1 << ORN_Q6K)) stage_fill<ORN_Q6K>(lin, P.K, X[ORN_Q6K]);
-  if (MASK & (1 << ORN_A8)) stage_fill<ORN_A8>(lin, P.K, X[ORN_A8]);
-  if (MASK & (1 << ORN_BF16)) stage_fill<ORN_BF16>(lin, P.K, X[ORN_BF16]);
+  run_prologue<M>(P, pin, lin, red);
+  if (mask & (1 << ORN_Q4K)) stage_fill<ORN_Q4K>(lin, P.K, X[ORN_Q4K]);
+  if (mask & (1 << ORN_Q6K)) stage_fill<ORN_Q6K>(lin, P.K, X[ORN_Q6K]);
+  if (mask & (1 << ORN_A8)) stage_fill<ORN_A8>(lin, P.K, X[ORN_A8]);
+  if (mask & (1 << ORN_BF16)) stage_fill<ORN_BF16>(lin, P.K, X[ORN_BF16]);
   __syncthreads();
-  DBG(4);
 
-  float acc[kRowsPerTask][M], up[kRowsPerTask][M];
+  float acc[kMaxAcc], up[kMaxAcc];
   int slot = 0;
   uint32_t parity = 0;
-  int dbg_n = 0;
   while (cc.valid(J)) {
     if (!ring_wait(R, slot, parity)) return;
-    if (dbg_n < 8) { DBG(5 + 2 * dbg_n); }
     const RowJob& job = J.job[cc.j];
     const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
-    const int cu = job_chunk_units(job, cc.c);
-    const uint32_t b0 = units_bytes0(job.lin.kind, cu), b1 = units_bytes1(job.lin.kind, cu);
-    const int row = cc.t * kRowsPerTask;
-    const int nvalid = min(kRowsPerTask, job.lin.O - row);
-    if (cc.c == 0) {
+    const bool swiglu = job.epi == EPI_SWIGLU;
+    if (cc.sub == 0) {
 #pragma unroll
-      for (int r = 0; r < kRowsPerTask; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) { acc[r][m] = 0.f; up[r][m] = 0.f; }
+      for (int i = 0; i < kMaxAcc; ++i) { acc[i] = 0.f; up[i] = 0.f; }
+      tile_dot_masked<M, MASK, KC>(buf, job.lin, X, lane, acc);
+    } else {
+      tile_dot_masked<M, MASK, KC>(buf, job.lin2, X, lane, up);
     }
-    if (dbg_n == 0) { DBG(20); }
-    tile_dot_masked<M, MASK>(buf, b0, b1, job.lin, row, nvalid, cc.c, X, lane, acc);
-    if (dbg_n == 0) { DBG(21); }
-    if (job.epi == EPI_SWIGLU)
-      tile_dot_masked<M, MASK>(buf + kRowsPerTask * (b0 + b1), b0, b1, job.lin2, row, nvalid, cc.c, X, lane, up);
-    if (dbg_n == 0) { DBG(22); }
-    if (cc.c == job.nchunk - 1) {
-#pragma unroll
-      for (int r = 0; r < kRowsPerTask; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          float v = warp_sum(acc[r][m]);
-          if (job.epi == EPI_SWIGLU) v = orn_swiglu_bf(bfr(v), bfr(warp_sum(up[r][m])));
-          if (lane == 0 && r < nvalid) job.out[(size_t)m * job.lin.O + row + r] = f2bf(v);
-        }
-    }
-    if (dbg_n == 0) { DBG(23); }
     __syncwarp();
+    const bool last = !swiglu || cc.sub == 1;
+    const int kind = job.lin.kind, O = job.lin.O, t = cc.t;
+    bf16_t* out = job.out;
     if (pc.valid(J)) {
       if (lane == 0) fence_proxy_async();
       issue();  // refills the slot just consumed
     }
-    if (dbg_n == 0) { DBG(24); }
+    if (last) {
+      const int rows = rows_of<KC>(kind);
+      const int row0 = t * rows;
+      tile_store_masked<M, MASK, KC>(kind, acc, up, swiglu, lane, out, O, row0, min(rows, O - row0));
+    }
     cc.advance(J, GW);
     if (++slot == depth) { slot = 0; parity ^= 1; }
-    if (dbg_n < 8) { DBG(6 + 2 * dbg_n); }
-    ++dbg_n;
   }
-  DBG(30);
 }
 
 // ---------------------------------------------------------------------------
@@ -821,12 +822,12 @@ struct MoeUpParams {
   uint32_t* inds;        // [M][k] out (CTA 0)
   bf16_t* scores;        // [M][k] out (CTA 0)
   bf16_t* act;           // [M*k][I] out
-  int E, k, H, I;
+  int M, E, k, H, I;
 };
 
 // softmax (mlx softmax.h:10-99, float accumulate) then router_top_k
 // (kernels/moe.metal:568-614) for one token by one warp; results to shared
-ORN_D void warp_softmax_topk(const bf16_t* logits, int n, int k, float* probs /*[n] smem*/,
+__device__ __noinline__ void warp_softmax_topk(const bf16_t* logits, int n, int k, float* probs /*[n] smem*/,
                              float* red /*[32] smem*/, uint32_t* inds, float* scores, int lane) {
   float mx = -INFINITY;
   for (int i = lane; i < n; i += 32) mx = fmaxf(mx, bf2f(logits[i]));
@@ -842,7 +843,7 @@ ORN_D void warp_softmax_topk(const bf16_t* logits, int n, int k, float* probs /*
     for (int i = 0; i < 4; ++i) {
       const int idx = 4 * vt + i;
       if (idx < n) {
-        const float e = orn_expf(bf2f(logits[idx]) - mx);
+        const float e = expf_call(bf2f(logits[idx]) - mx);
         probs[idx] = e;
         acc = acc + e;
       }
@@ -885,25 +886,53 @@ ORN_D void warp_softmax_topk(const bf16_t* logits, int n, int k, float* probs /*
   __syncwarp();
 }
 
-template <int KIND, int M>
-__global__ void __launch_bounds__(kFusedThreads, 1) k_moe_up(MoeUpParams P, uint32_t slot_bytes, int depth, int* err) {
+
+template <int KIND, int KC>
+__global__ void __launch_bounds__(kFusedThreads, 1) k_moe_up(MoeUpParams P, uint32_t slot_bytes, int depth,
+                                                             uint32_t ring_off, int* err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* smem = reinterpret_cast<float*>(smem_raw);
+  constexpr int RT = tile_rows(KIND, KC);
+  const int M = P.M;
   XStage X;
   float* next = stage_carve(smem, KIND, M, P.H, X);
   uint32_t* inds = reinterpret_cast<uint32_t*>(next);  // [M][k], lives through the kernel
   next += M * P.k;
-  uint8_t* region = reinterpret_cast<uint8_t*>(smem) + ((((uint8_t*)next - (uint8_t*)smem) + 127) & ~(size_t)127);
-  float* lin = reinterpret_cast<float*>(region);       // [M][H]
+  float* lin = smem + (((next - smem) + 31) & ~31);    // [M][H]
   float* probs = lin + (size_t)M * P.H;                // [M][E]
   float* red = probs + (size_t)M * P.E;                // [M][32]
   float* scores = red + M * 32;                        // [M][k]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_trigger();
+  Ring R;
+  ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
+  pdl_wait();  // the routing (and so the first weight tile) depends on the previous kernel's logits
   if (warp < M)
     warp_softmax_topk(P.logits + (size_t)warp * P.E, P.E, P.k, probs + (size_t)warp * P.E, red + warp * 32,
                       inds + warp * P.k, scores + warp * P.k, lane);
-  for (int i = threadIdx.x; i < M * P.H; i += blockDim.x) lin[i] = bf2f(P.x[i]);
+  for (int i = threadIdx.x * 4; i < M * P.H; i += blockDim.x * 4) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.x + i));
+    *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+  }
   __syncthreads();
+  // task g = (routed row mj, tile t of the expert's I output rows): two slots, gate rows then up rows
+  const int gw = blockIdx.x * (blockDim.x >> 5) + warp, GW = gridDim.x * (blockDim.x >> 5);
+  const int ntile = (P.I + RT - 1) / RT;
+  const int total = M * P.k * ntile;
+  const RecGeom geo = rec_geom(KIND, P.H);
+  int pg = gw, psub = 0, pslot = 0;
+  auto issue = [&]() {
+    if (lane == 0) {
+      const int mj = pg / ntile, t = pg - mj * ntile;
+      const int o = t * RT;
+      const int n = min(RT, P.I - o);
+      const size_t row = (size_t)inds[mj] * P.I + o;
+      ring_fill(R, pslot, (psub ? P.up.w : P.gate.w) + row * geo.rec, n * geo.rec);
+    }
+    if (psub == 0) psub = 1; else { psub = 0; pg += GW; }
+    if (++pslot == depth) pslot = 0;
+  };
+  for (int i = 0; i < depth && pg < total; ++i) issue();
   if (blockIdx.x == 0)
     for (int i = threadIdx.x; i < M * P.k; i += blockDim.x) {
       P.inds[i] = inds[i];
@@ -911,101 +940,30 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_moe_up(MoeUpParams P, uint
     }
   stage_fill<KIND>(lin, P.H, X);
   __syncthreads();
-  Ring R;
-  ring_setup(R, region, slot_bytes, depth, err);
-  __syncthreads();
-  // task sequence of a warp: (mj, op) = routed row mj, pair op of consecutive expert output rows, starting
-  // at flat index gw and stepping by GW, each in `nchunk` chunks; positions advance without divisions
-  constexpr int RT = kRowsPerTask;
-  const int gw = blockIdx.x * (blockDim.x >> 5) + warp, GW = gridDim.x * (blockDim.x >> 5);
-  const int nmj = M * P.k;
-  const int npair = (P.I + RT - 1) / RT;
-  const int units = X.units;
-  const int nchunk = (units + 32 * kChunkSteps - 1) / (32 * kChunkSteps);
-  const uint32_t rb0 = units_bytes0(KIND, units), rb1 = units_bytes1(KIND, units);
-  struct Pos {
-    int mj, op, c;
-  };
-  auto settle = [&](Pos& q) {
-    while (q.mj < nmj && q.op >= npair) { q.op -= npair; ++q.mj; }
-  };
-  auto advance = [&](Pos& q) {
-    if (++q.c == nchunk) { q.c = 0; q.op += GW; settle(q); }
-  };
-  auto cunits = [&](int c) {
-    const int u = units - 32 * kChunkSteps * c;
-    return u > 32 * kChunkSteps ? 32 * kChunkSteps : u;
-  };
-  Pos pp{0, gw, 0}, cp{0, gw, 0};
-  settle(pp);
-  settle(cp);
-  int pslot = 0;
-  // slot layout: [gate: RT x stream 0][gate: RT x stream 1][up: RT x stream 0][up: RT x stream 1]
-  auto issue = [&]() {
-    if (lane == 0) {
-      const int o = pp.op * RT;
-      const int n = min(RT, P.I - o);
-      const int64_t row = (int64_t)inds[pp.mj] * P.I + o;
-      const int u = cunits(pp.c);
-      const uint32_t b0 = units_bytes0(KIND, u), b1 = units_bytes1(KIND, u);
-      const uint32_t bar = R.bar0 + 8 * pslot;
-      const uint32_t dst = R.buf0 + pslot * R.slot_bytes;
-      const uint32_t half = RT * (b0 + b1);
-      mbar_expect_tx(bar, 2 * n * (b0 + b1));
-      if (nchunk == 1) {
-        bulk_g2s(dst, P.gate.w + row * rb0, n * b0, bar);
-        if (b1) bulk_g2s(dst + RT * b0, P.gate.s + row * rb1, n * b1, bar);
-        bulk_g2s(dst + half, P.up.w + row * rb0, n * b0, bar);
-        if (b1) bulk_g2s(dst + half + RT * b0, P.up.s + row * rb1, n * b1, bar);
-      } else {
-        for (int r = 0; r < n; ++r) {
-          const int64_t o0 = (row + r) * rb0 + (int64_t)pp.c * kChunkSteps * step_bytes0(KIND);
-          const int64_t o1 = (row + r) * rb1 + (int64_t)pp.c * kChunkSteps * step_bytes1(KIND);
-          bulk_g2s(dst + r * b0, P.gate.w + o0, b0, bar);
-          if (b1) bulk_g2s(dst + RT * b0 + r * b1, P.gate.s + o1, b1, bar);
-          bulk_g2s(dst + half + r * b0, P.up.w + o0, b0, bar);
-          if (b1) bulk_g2s(dst + half + RT * b0 + r * b1, P.up.s + o1, b1, bar);
-        }
-      }
-    }
-    advance(pp);
-    if (++pslot == depth) pslot = 0;
-  };
-  for (int i = 0; i < depth && pp.mj < nmj; ++i) issue();
-  float g[RT][1], u[RT][1];
+  float g[RT], u[RT];
   int slot = 0;
   uint32_t parity = 0;
-  while (cp.mj < nmj) {
-    if (!ring_wait(R, slot, parity)) return;
-    int m = 0;
-    for (int t = P.k; t <= cp.mj; t += P.k) ++m;  // m = mj / k without a division
-    const int o = cp.op * RT;
-    const int nvalid = min(RT, P.I - o);
-    const int64_t row = (int64_t)inds[cp.mj] * P.I + o;
-    const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
-    const int cu = cunits(cp.c);
-    const uint32_t cb0 = units_bytes0(KIND, cu), cb1 = units_bytes1(KIND, cu);
-    const uint32_t half = RT * (cb0 + cb1);
-    if (cp.c == 0) {
+  for (int cg = gw; cg < total; cg += GW) {
+    const int mj = cg / ntile, t = cg - mj * ntile;
+    const int m = mj / P.k;
 #pragma unroll
-      for (int r = 0; r < RT; ++r) { g[r][0] = 0.f; u[r][0] = 0.f; }
-    }
-    warp_chunk_dot_rows<KIND, 1, RT>(buf, cb0, buf + RT * cb0, cb1, P.gate, row, nvalid, cp.c, X, m, lane, g);
-    warp_chunk_dot_rows<KIND, 1, RT>(buf + half, cb0, buf + half + RT * cb0, cb1, P.up, row, nvalid, cp.c, X, m, lane, u);
-    if (cp.c == nchunk - 1) {
+    for (int r = 0; r < RT; ++r) { g[r] = 0.f; u[r] = 0.f; }
 #pragma unroll
-      for (int r = 0; r < RT; ++r) {
-        const float gs = warp_sum(g[r][0]), us = warp_sum(u[r][0]);
-        if (lane == 0 && r < nvalid) P.act[(size_t)cp.mj * P.I + o + r] = f2bf(orn_swiglu_bf(bfr(gs), bfr(us)));
+    for (int sub = 0; sub < 2; ++sub) {
+      if (!ring_wait(R, slot, parity)) return;
+      tile_dot<KIND, 1, RT>(R.buf + (size_t)slot * slot_bytes, P.gate, X, m, lane, sub ? u : g);
+      __syncwarp();
+      if (pg < total) {
+        if (lane == 0) fence_proxy_async();
+        issue();
       }
+      if (++slot == depth) { slot = 0; parity ^= 1; }
     }
-    __syncwarp();
-    if (pp.mj < nmj) {
-      if (lane == 0) fence_proxy_async();
-      issue();
-    }
-    advance(cp);
-    if (++slot == depth) { slot = 0; parity ^= 1; }
+    int which, w2;
+    const float gs = rs_butterfly<RT>(g, lane, which);
+    const float us = rs_butterfly<RT>(u, lane, w2);
+    const int o = t * RT + which;
+    if ((lane & (32 / RT - 1)) == 0 && o < P.I) P.act[(size_t)mj * P.I + o] = f2bf(swiglu_bf_call(bfr(gs), bfr(us)));
   }
 }
 
@@ -1022,13 +980,21 @@ struct MoeDownParams {
   LinDev down;           // [E, H, I]
   LinDev sh_down;        // [1, H, SI]
   bf16_t* out;           // [M][H]
-  int k, H, I, SI, normalize;
+  int M, k, H, I, SI, normalize;
 };
 
-template <int KIND, int M>
-__global__ void __launch_bounds__(kFusedThreads, 1) k_moe_down(MoeDownParams P, uint32_t slot_bytes, int depth, int* err) {
+// Task = (token m, group of RT consecutive output columns).  Consecutive columns are consecutive
+// weight rows of one expert, so one bulk copy brings a group's rows of one routed expert.  Per
+// task the warp consumes the k routed tiles in ascending j (the combine's order) and then the
+// shared expert's tile.  After the butterfly each lane holds one column's sum, so the bf16
+// combine runs per lane without further exchange.
+template <int KIND, int KC>
+__global__ void __launch_bounds__(kFusedThreads, 1) k_moe_down(MoeDownParams P, uint32_t slot_bytes, int depth,
+                                                               uint32_t ring_off, int* err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* smem = reinterpret_cast<float*>(smem_raw);
+  constexpr int RT = tile_rows(KIND, KC);
+  const int M = P.M;
   const int rows = M * P.k;
   XStage X, XS;
   float* next = stage_carve(smem, KIND, rows, P.I, X);
@@ -1037,11 +1003,40 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_moe_down(MoeDownParams P, 
   float* gsig = wts + rows;                            // [M]
   uint32_t* inds = reinterpret_cast<uint32_t*>(gsig + M);
   next = reinterpret_cast<float*>(inds + rows);
-  uint8_t* region = reinterpret_cast<uint8_t*>(smem) + ((((uint8_t*)next - (uint8_t*)smem) + 127) & ~(size_t)127);
-  float* lin = reinterpret_cast<float*>(region);       // [rows][I] then [M][SI]
+  float* lin = smem + (((next - smem) + 31) & ~31);    // [rows][I] then [M][SI]
   float* lin2 = lin + (size_t)rows * P.I;
-  for (int i = threadIdx.x; i < rows * P.I; i += blockDim.x) lin[i] = bf2f(P.act[i]);
-  for (int i = threadIdx.x; i < M * P.SI; i += blockDim.x) lin2[i] = bf2f(P.sact[i]);
+  const int lane = threadIdx.x & 31;
+  pdl_trigger();
+  Ring R;
+  ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
+  pdl_wait();
+  if (threadIdx.x < rows) inds[threadIdx.x] = P.inds[threadIdx.x];
+  __syncthreads();
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), GW = gridDim.x * (blockDim.x >> 5);
+  const int ngroups = (P.H + RT - 1) / RT;
+  const int total = M * ngroups;
+  const RecGeom geo = rec_geom(KIND, P.I), sgeo = rec_geom(KIND, P.SI);
+  int pg = gw, pq = 0, pslot = 0;  // producer: task, tile within the task (k = the shared expert's)
+  auto issue = [&]() {
+    if (lane == 0) {
+      const int m = pg / ngroups, grp = pg - m * ngroups;
+      const int c0 = grp * RT;
+      const int n = min(RT, P.H - c0);
+      if (pq < P.k) ring_fill(R, pslot, P.down.w + ((size_t)inds[m * P.k + pq] * P.H + c0) * geo.rec, n * geo.rec);
+      else ring_fill(R, pslot, P.sh_down.w + (size_t)c0 * sgeo.rec, n * sgeo.rec);
+    }
+    if (++pq > P.k) { pq = 0; pg += GW; }
+    if (++pslot == depth) pslot = 0;
+  };
+  for (int i = 0; i < depth && pg < total; ++i) issue();
+  for (int i = threadIdx.x * 4; i < rows * P.I; i += blockDim.x * 4) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.act + i));
+    *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+  }
+  for (int i = threadIdx.x * 4; i < M * P.SI; i += blockDim.x * 4) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.sact + i));
+    *reinterpret_cast<float4*>(lin2 + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+  }
   if (threadIdx.x < M) {
     const int m = threadIdx.x;
     float denom = 0.f;
@@ -1050,105 +1045,42 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_moe_down(MoeDownParams P, 
     for (int j = 0; j < P.k; ++j) {
       const float sc = bf2f(P.scores[m * P.k + j]);
       wts[m * P.k + j] = P.normalize ? bfr(sc / denom) : sc;
-      inds[m * P.k + j] = P.inds[m * P.k + j];
     }
-    gsig[m] = orn_sigmoid_bf(bf2f(P.gs[m]));
+    gsig[m] = sigmoid_bf_call(bf2f(P.gs[m]));
   }
   __syncthreads();
   stage_fill<KIND>(lin, P.I, X);
   stage_fill<KIND>(lin2, P.SI, XS);
   __syncthreads();
-  Ring R;
-  ring_setup(R, region, slot_bytes, depth, err);
-  __syncthreads();
-  // A warp owns groups of kDownCols consecutive output columns (group gw,
-  // gw+GW, ...).  Consecutive columns are consecutive weight rows of one expert,
-  // so one pair of bulk copies brings a group's rows of one routed expert.  Per
-  // group the warp consumes the M*k routed tiles in (m, j) order and then the
-  // shared expert's tile.  Rows here are short (one chunk each, checked at launch).
-  const int lane = threadIdx.x & 31;
-  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), GW = gridDim.x * (blockDim.x >> 5);
-  const int ngroups = P.H / kDownCols;
-  const uint32_t b0 = units_bytes0(KIND, X.units), b1 = units_bytes1(KIND, X.units);      // routed row
-  const uint32_t sb0 = units_bytes0(KIND, XS.units), sb1 = units_bytes1(KIND, XS.units);  // shared row
-  struct Pos {
-    int g, q;
-  };
-  auto advance = [&](Pos& t) {
-    if (++t.q > rows) { t.q = 0; t.g += GW; }
-  };
-  Pos pp{gw, 0}, cp{gw, 0};
-  int pslot = 0;
-  auto issue = [&]() {
-    if (lane == 0) {
-      const uint32_t bar = R.bar0 + 8 * pslot;
-      const uint32_t dst = R.buf0 + pslot * R.slot_bytes;
-      const int c0 = pp.g * kDownCols;
-      if (pp.q < rows) {
-        const int64_t row = (int64_t)inds[pp.q] * P.H + c0;
-        mbar_expect_tx(bar, kDownCols * (b0 + b1));
-        bulk_g2s(dst, P.down.w + row * b0, kDownCols * b0, bar);
-        if (b1) bulk_g2s(dst + kDownCols * b0, P.down.s + row * b1, kDownCols * b1, bar);
-      } else {
-        mbar_expect_tx(bar, kDownCols * (sb0 + sb1));
-        bulk_g2s(dst, P.sh_down.w + (int64_t)c0 * sb0, kDownCols * sb0, bar);
-        if (sb1) bulk_g2s(dst + kDownCols * sb0, P.sh_down.s + (int64_t)c0 * sb1, kDownCols * sb1, bar);
-      }
-    }
-    advance(pp);
-    if (++pslot == depth) pslot = 0;
-  };
-  for (int i = 0; i < depth && pp.g < ngroups; ++i) issue();
-  float acc[kDownCols][M];
-#pragma unroll
-  for (int r = 0; r < kDownCols; ++r)
-#pragma unroll
-    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
   int slot = 0;
   uint32_t parity = 0;
-  while (cp.g < ngroups) {
-    if (!ring_wait(R, slot, parity)) return;
-    const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
-    const int c0 = cp.g * kDownCols;
-    if (cp.q < rows) {
-      const int64_t row = (int64_t)inds[cp.q] * P.H + c0;
-      const float w = wts[cp.q];
-      int m = 0;
-      for (int t = P.k; t <= cp.q; t += P.k) ++m;  // m = q / k without a division
-      float d[kDownCols][1];
+  for (int cg = gw; cg < total; cg += GW) {
+    const int m = cg / ngroups, grp = cg - m * ngroups;
+    const int c0 = grp * RT;
+    float acc = 0.f;  // this lane's column, combined so far
+    for (int q = 0; q <= P.k; ++q) {
+      if (!ring_wait(R, slot, parity)) return;
+      const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
+      float d[RT];
 #pragma unroll
-      for (int r = 0; r < kDownCols; ++r) d[r][0] = 0.f;
-      warp_chunk_dot_rows<KIND, 1, kDownCols>(buf, b0, buf + kDownCols * b0, b1, P.down, row, kDownCols, 0, X, cp.q, lane, d);
-#pragma unroll
-      for (int r = 0; r < kDownCols; ++r) {
-        const float weighted = bfr(bfr(warp_sum(d[r][0])) * w);
-#pragma unroll
-        for (int mm = 0; mm < M; ++mm)
-          if (mm == m) acc[r][mm] = bfr(weighted + acc[r][mm]);
+      for (int r = 0; r < RT; ++r) d[r] = 0.f;
+      if (q < P.k) tile_dot<KIND, 1, RT>(buf, P.down, X, m * P.k + q, lane, d);
+      else tile_dot<KIND, 1, RT>(buf, P.sh_down, XS, m, lane, d);
+      __syncwarp();
+      if (pg < total) {
+        if (lane == 0) fence_proxy_async();
+        issue();
       }
-    } else {
-      float sd[kDownCols][M];
-#pragma unroll
-      for (int r = 0; r < kDownCols; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) sd[r][m] = 0.f;
-      warp_chunk_dot_rows<KIND, M, kDownCols>(buf, sb0, buf + kDownCols * sb0, sb1, P.sh_down, c0, kDownCols, 0, XS, 0, lane, sd);
-#pragma unroll
-      for (int r = 0; r < kDownCols; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          const float v = warp_sum(sd[r][m]);
-          if (lane == 0) P.out[(size_t)m * P.H + c0 + r] = f2bf(acc[r][m] + bfr(gsig[m] * bfr(v)));
-          acc[r][m] = 0.f;
-        }
+      int which;
+      const float v = rs_butterfly<RT>(d, lane, which);
+      if (q < P.k) {
+        acc = bfr(bfr(bfr(v) * wts[m * P.k + q]) + acc);
+      } else {
+        const int c = c0 + which;
+        if ((lane & (32 / RT - 1)) == 0 && c < P.H) P.out[(size_t)m * P.H + c] = f2bf(acc + bfr(gsig[m] * bfr(v)));
+      }
+      if (++slot == depth) { slot = 0; parity ^= 1; }
     }
-    __syncwarp();
-    if (pp.g < ngroups) {
-      if (lane == 0) fence_proxy_async();
-      issue();
-    }
-    advance(cp);
-    if (++slot == depth) { slot = 0; parity ^= 1; }
   }
 }
 
@@ -1175,10 +1107,26 @@ constexpr int kGdnMaxT = 4;
 __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
   __shared__ float s_q[kGdnMaxT][128], s_k[kGdnMaxT][128], s_v[kGdnMaxT][kGdnRows];
   __shared__ float s_g[kGdnMaxT], s_beta[kGdnMaxT];
+  pdl_trigger();
+  pdl_wait();
   const int hv = blockIdx.y;
   const int hk = hv / (p.Hv / p.Hk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int key_dim = p.Hk * 128;
+  // the state rows do not depend on the front end: request them first so that the 2 MB of HBM
+  // reads per layer overlap the convolution and the norms
+  const int row = blockIdx.x * kGdnRows + (threadIdx.x >> 2);
+  const int lir = threadIdx.x & 3;
+  const size_t ssz = (size_t)p.Hv * 128 * 128;
+  const size_t off = ((size_t)hv * 128 + row) * 128 + lir * 32;
+  const int cur = *p.cur;
+  const float* sin = p.ring + (size_t)(cur % p.nring) * ssz + off;
+  float S[32];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 v4 = *reinterpret_cast<const float4*>(sin + 4 * i);
+    S[4 * i] = v4.x; S[4 * i + 1] = v4.y; S[4 * i + 2] = v4.z; S[4 * i + 3] = v4.w;
+  }
   // ---- front end (kernels/gdn_front.metal:65-190): warp 0 -> q head, warp 1 -> k head
   for (int t = 0; t < p.T; ++t) {
     const int c0 = (warp == 0 ? hk * 128 : key_dim + hk * 128) + 4 * lane;
@@ -1192,7 +1140,7 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
     float yv[4];
     float sum = 0.f;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) { yv[r] = orn_silu_bf(bfr(acc[r])); sum = fmaf(yv[r], yv[r], sum); }
+    for (int r = 0; r < 4; ++r) { yv[r] = silu_bf_call(bfr(acc[r])); sum = fmaf(yv[r], yv[r], sum); }
     sum = warp_sum(sum);
     const float inv = orn_rsqrtf(sum / 128.0f + p.eps);
     const float sc = warp == 0 ? p.q_scale : p.k_scale;
@@ -1201,37 +1149,25 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
     for (int r = 0; r < 4; ++r) dst[4 * lane + r] = bfr(sc * bfr(yv[r] * inv));
   }
   // value rows of this CTA and the per-head gates
-  const int row = blockIdx.x * kGdnRows + (threadIdx.x >> 2);
-  const int lir = threadIdx.x & 3;
   if (lir == 0) {
     const int c = 2 * key_dim + hv * 128 + row;
     for (int t = 0; t < p.T; ++t) {
       float acc = 0.f;
       for (int i = 0; i < p.Kc; ++i)
         acc = fmaf(bf2f(p.conv[(size_t)(t + i) * p.D + c]), bf2f(p.cw[(size_t)c * p.Kc + i]), acc);
-      s_v[t][threadIdx.x >> 2] = orn_silu_bf(bfr(acc));
+      s_v[t][threadIdx.x >> 2] = silu_bf_call(bfr(acc));
     }
   }
   if (threadIdx.x < p.T) {
     const int t = threadIdx.x;
     const size_t i = (size_t)t * p.Hv + hv;
-    const float sp = orn_softplus_bf(bfr(bf2f(p.a_in[i]) + bf2f(p.dt_bias[hv])));
-    const float decay = orn_expf(bf2f(p.a_log[hv]));
-    s_g[t] = orn_expf((-decay) * sp);
-    s_beta[t] = orn_sigmoid_bf(bf2f(p.b_in[i]));
+    const float sp = softplus_bf_call(bfr(bf2f(p.a_in[i]) + bf2f(p.dt_bias[hv])));
+    const float decay = expf_call(bf2f(p.a_log[hv]));
+    s_g[t] = expf_call((-decay) * sp);
+    s_beta[t] = sigmoid_bf_call(bf2f(p.b_in[i]));
   }
   __syncthreads();
   // ---- recurrence (kernels/gated_delta.metal:36-142)
-  const size_t ssz = (size_t)p.Hv * 128 * 128;
-  const size_t off = ((size_t)hv * 128 + row) * 128 + lir * 32;
-  const int cur = *p.cur;
-  const float* sin = p.ring + (size_t)(cur % p.nring) * ssz + off;
-  float S[32];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float4 v4 = *reinterpret_cast<const float4*>(sin + 4 * i);
-    S[4 * i] = v4.x; S[4 * i + 1] = v4.y; S[4 * i + 2] = v4.z; S[4 * i + 3] = v4.w;
-  }
   for (int t = 0; t < p.T; ++t) {
     const float* kf = s_k[t] + lir * 32;
     const float* qf = s_q[t] + lir * 32;
@@ -1327,10 +1263,10 @@ ORN_D void warp_norm_rope(const bf16_t* src, const bf16_t* w, float eps, int rop
   __syncwarp();
   const int half = rope_dims / 2;
   for (int i = lane; i < half; i += 32) {
-    const float inv_freq = orn_expf(-(float)i * lnb);
+    const float inv_freq = expf_call(-(float)i * lnb);
     const float ang = (float)position * inv_freq;
     float sn, cs;
-    orn_sincosf(ang, &sn, &cs);
+    sincosf_call(ang, &sn, &cs);
     const float x1 = dst[i], x2 = dst[i + half];
     const float t1 = x2 * sn, t2 = x2 * cs;
     dst[i] = bfr(fmaf(x1, cs, -t1));
@@ -1345,6 +1281,8 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
   __shared__ float s_q[HD];
   __shared__ float s_knew[kGdnMaxT][HD];
   __shared__ float s_max[32], s_sum[32], s_f[32];
+  pdl_trigger();
+  pdl_wait();
   const int h = blockIdx.x, r = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int group = p.Hq / p.Hkv;
@@ -1388,8 +1326,8 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
     for (int i = 0; i < 8; ++i) acc = fmaf(qs[i], kf[i], acc);
     const float score = warp_sum(acc);
     const float nm = fmaxf(mx, score);
-    const float factor = orn_expf(mx - nm);
-    const float e = orn_expf(score - nm);
+    const float factor = expf_call(mx - nm);
+    const float e = expf_call(score - nm);
     mx = nm;
     sm = fmaf(sm, factor, e);
 #pragma unroll
@@ -1401,7 +1339,7 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
   __syncthreads();
   if (warp == 0) {
     const float M = warp_max(s_max[lane]);
-    const float f = orn_expf(s_max[lane] - M);
+    const float f = expf_call(s_max[lane] - M);
     s_f[lane] = f;
     const float S = warp_sum(s_sum[lane] * f);
     if (lane == 0) s_sum[0] = S;
@@ -1418,7 +1356,7 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
       for (int i = 0; i < off; ++i) a[i] = a[i] + a[i + off];
     const float att = bfr(a[0] / s_sum[0]);
     const float gate = bf2f(p.qg[((size_t)r * p.Hq + h) * 2 * HD + HD + d]);
-    p.out[((size_t)r * p.Hq + h) * HD + d] = f2bf(orn_sigmoid_bf(gate) * att);
+    p.out[((size_t)r * p.Hq + h) * HD + d] = f2bf(sigmoid_bf_call(gate) * att);
   }
 }
 
@@ -1449,110 +1387,118 @@ int set_smem(orn_ctx* ctx, Kern kern, size_t bytes) {
   return ORN_OK;
 }
 
-// ring depth that fits beside `fixed` bytes of stages, and the dynamic shared
-// memory of the launch: max(prologue scratch, rings) shares one region
-int plan_smem(orn_ctx* ctx, size_t fixed, size_t scratch, uint32_t slot_bytes, int* depth, size_t* total) {
+// rings beside `fixed` bytes of stages and scratch: offset of the rings, their depth, the launch's
+// dynamic shared memory
+int plan_smem(orn_ctx* ctx, size_t fixed, uint32_t slot_bytes, int* depth, uint32_t* ring_off, size_t* total) {
   const int nwarps = kFusedThreads / 32;
   fixed = (fixed + 127) & ~(size_t)127;
   int d = 8;
   while (d > 1 && fixed + ring_bytes(nwarps, d, slot_bytes) > kSmemBudget) --d;
-  const size_t rb = ring_bytes(nwarps, d, slot_bytes);
   *depth = d;
-  *total = fixed + (rb > scratch ? rb : scratch) + 128;
+  *ring_off = (uint32_t)fixed;
+  *total = fixed + ring_bytes(nwarps, d, slot_bytes) + 128;
   if (*total > 227 * 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "fused kernel: rows too long for the shared-memory rings");
   return ORN_OK;
 }
 
-template <int M, int MASK>
+template <int M, int MASK, int KC>
 int launch_norm_gemv_mask(orn_ctx* ctx, cudaStream_t s, const Prologue& P, const RowJobs& J, uint32_t slot) {
   size_t fixed = 0;
   for (int k = 0; k < 4; ++k)
     if (MASK & (1 << k)) fixed += stage_floats(k, M, P.K) * sizeof(float);
-  // stages + prologue scratch stay live beside the rings (the rings are filled while the prologue runs)
-  fixed += ((size_t)M * P.K + M * 33 + 64) * sizeof(float);
   fixed = (fixed + 127) & ~(size_t)127;
+  fixed += ((size_t)M * P.K + M * 33 + 64) * sizeof(float);  // the prologue's row and its reduction scratch
   int depth;
+  uint32_t ring_off;
   size_t bytes;
-  int rc = plan_smem(ctx, fixed, 0, slot, &depth, &bytes);
+  int rc = plan_smem(ctx, fixed, slot, &depth, &ring_off, &bytes);
   if (rc != ORN_OK) return rc;
-  rc = set_smem(ctx, k_norm_gemv<M, MASK>, bytes);
+  rc = set_smem(ctx, k_norm_gemv<M, MASK, KC>, bytes);
   if (rc != ORN_OK) return rc;
-  k_norm_gemv<M, MASK><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, J, slot, depth, (uint32_t)fixed, ctx->dev_err);
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_norm_gemv<M, MASK, KC>, dim3(ctx->sm_count), dim3(kFusedThreads),
+                                           bytes, P, J, slot, depth, ring_off, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_norm_gemv", M, J.job[0].lin.kind, J.job[0].lin.O, P.K));
+}
+
+template <int M, int KC>
+int launch_norm_gemv_kc(orn_ctx* ctx, cudaStream_t s, const Prologue& P, const RowJobs& J, uint32_t slot) {
+  // one instantiation per set of formats present, so that a kernel carries only the code it runs
+  switch (J.kinds_mask) {
+    case 1: return launch_norm_gemv_mask<M, 1, KC>(ctx, s, P, J, slot);
+    case 2: return launch_norm_gemv_mask<M, 2, KC>(ctx, s, P, J, slot);
+    case 4: return launch_norm_gemv_mask<M, 4, KC>(ctx, s, P, J, slot);
+    case 8: return launch_norm_gemv_mask<M, 8, KC>(ctx, s, P, J, slot);
+    case 5: return launch_norm_gemv_mask<M, 5, KC>(ctx, s, P, J, slot);    // Q4_K + affine-8
+    case 12: return launch_norm_gemv_mask<M, 12, KC>(ctx, s, P, J, slot);  // affine-8 + bf16
+    case 9: return launch_norm_gemv_mask<M, 9, KC>(ctx, s, P, J, slot);    // Q4_K + bf16
+    case 6: return launch_norm_gemv_mask<M, 6, KC>(ctx, s, P, J, slot);    // Q6_K + affine-8
+    default: return launch_norm_gemv_mask<M, 15, KC>(ctx, s, P, J, slot);
+  }
 }
 
 template <int M>
 int launch_norm_gemv(orn_ctx* ctx, cudaStream_t s, const Prologue& P, RowJobs& J) {
   J.kinds_mask = 0;
+  J.total = 0;
   uint32_t slot = 0;
-  if (P.mode == PRO_ADDNORM && P.K > 4 * kFusedThreads)
+  if (P.mode == PRO_ADDNORM && P.K > 4 * kAddNormGroups * kFusedThreads)
     ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: hidden size above 2048 is not supported by the norm prologue");
+  if (P.K % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: K must be a multiple of 256");
+  const int kc = P.K > 2048 ? 2 : 1;  // rows of 512 weights or fewer run with the class-1 tile heights
   for (int j = 0; j < J.njobs; ++j) {
     RowJob& job = J.job[j];
     J.kinds_mask |= 1 << job.lin.kind;
     if (job.lin.K != P.K) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: weight K differs from the staged row");
-    if (job.lin.K % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: K must be a multiple of 256");
-    job.tasks = (job.lin.O + kRowsPerTask - 1) / kRowsPerTask;
-    job.units = kind_units(job.lin.kind, job.lin.K);
-    job.nchunk = row_chunks(job.lin.kind, job.lin.K);
-    job.rb0 = units_bytes0(job.lin.kind, job.units);
-    job.rb1 = units_bytes1(job.lin.kind, job.units);
-    uint32_t rb = kRowsPerTask * chunk_bytes_max(job.lin.kind, job.lin.K);
-    if (job.epi == EPI_SWIGLU) {
-      if (job.lin2.kind != job.lin.kind || job.lin2.K != job.lin.K || job.lin2.O != job.lin.O)
-        ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: gate and up projections must share format and shape");
-      rb *= 2;
-    }
-    slot = rb > slot ? rb : slot;
+    if (job.epi == EPI_SWIGLU &&
+        (job.lin2.kind != job.lin.kind || job.lin2.K != job.lin.K || job.lin2.O != job.lin.O))
+      ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: gate and up projections must share format and shape");
+    const int rows = tile_rows(job.lin.kind, kc);
+    job.tiles = (job.lin.O + rows - 1) / rows;
+    J.total += job.tiles;
+    const uint32_t bytes = (uint32_t)rows * job.lin.rec;
+    slot = bytes > slot ? bytes : slot;
   }
-  // one instantiation per set of formats present, so that a kernel carries only the code it runs
-  switch (J.kinds_mask) {
-    case 1: return launch_norm_gemv_mask<M, 1>(ctx, s, P, J, slot);
-    case 2: return launch_norm_gemv_mask<M, 2>(ctx, s, P, J, slot);
-    case 4: return launch_norm_gemv_mask<M, 4>(ctx, s, P, J, slot);
-    case 8: return launch_norm_gemv_mask<M, 8>(ctx, s, P, J, slot);
-    case 5: return launch_norm_gemv_mask<M, 5>(ctx, s, P, J, slot);    // Q4_K + affine-8
-    case 12: return launch_norm_gemv_mask<M, 12>(ctx, s, P, J, slot);  // affine-8 + bf16
-    case 9: return launch_norm_gemv_mask<M, 9>(ctx, s, P, J, slot);    // Q4_K + bf16
-    case 6: return launch_norm_gemv_mask<M, 6>(ctx, s, P, J, slot);    // Q6_K + affine-8
-    default: return launch_norm_gemv_mask<M, 15>(ctx, s, P, J, slot);
-  }
+  if (kc == 2) return launch_norm_gemv_kc<M, 2>(ctx, s, P, J, slot);
+  return launch_norm_gemv_kc<M, 1>(ctx, s, P, J, slot);
 }
 
-template <int KIND, int M>
+template <int KIND, int KC>
 int launch_moe_up_k(orn_ctx* ctx, cudaStream_t s, const MoeUpParams& P) {
-  if (P.H % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_up: hidden must be a multiple of 256");
-  const size_t fixed = stage_floats(KIND, M, P.H) * sizeof(float) + (size_t)M * P.k * 4;
-  const size_t scratch = ((size_t)M * P.H + (size_t)M * P.E + M * 32 + M * P.k + 8) * sizeof(float);
-  const uint32_t slot = 2 * kRowsPerTask * chunk_bytes_max(KIND, P.H);
+  const int M = P.M;
+  size_t fixed = stage_floats(KIND, M, P.H) * sizeof(float) + (size_t)M * P.k * 4;
+  fixed = (fixed + 127) & ~(size_t)127;
+  fixed += ((size_t)M * P.H + (size_t)M * P.E + M * 32 + M * P.k + 8) * sizeof(float);
+  const uint32_t slot = tile_rows(KIND, KC) * P.gate.rec;
   int depth;
+  uint32_t ring_off;
   size_t bytes;
-  int rc = plan_smem(ctx, fixed, scratch, slot, &depth, &bytes);
+  int rc = plan_smem(ctx, fixed, slot, &depth, &ring_off, &bytes);
   if (rc != ORN_OK) return rc;
-  rc = set_smem(ctx, k_moe_up<KIND, M>, bytes);
+  rc = set_smem(ctx, k_moe_up<KIND, KC>, bytes);
   if (rc != ORN_OK) return rc;
-  k_moe_up<KIND, M><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, slot, depth, ctx->dev_err);
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_moe_up<KIND, KC>, dim3(ctx->sm_count), dim3(kFusedThreads), bytes,
+                                           P, slot, depth, ring_off, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_moe_up", M, KIND, P.I, P.H));
 }
 
-template <int KIND, int M>
+template <int KIND, int KC>
 int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
-  if (P.I % 256 || P.SI % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: intermediate sizes must be multiples of 256");
+  const int M = P.M;
   const int rows = M * P.k;
-  const size_t fixed = (stage_floats(KIND, rows, P.I) + stage_floats(KIND, M, P.SI) + 2 * rows + M) * sizeof(float);
-  const size_t scratch = ((size_t)rows * P.I + (size_t)M * P.SI + 8) * sizeof(float);
-  if (row_chunks(KIND, P.I) != 1 || row_chunks(KIND, P.SI) != 1)
-    ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: intermediate size too long for one streamed chunk");
-  if (P.H % kDownCols) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: hidden must be even");
-  const uint32_t r0 = chunk_bytes_max(KIND, P.I), r1 = chunk_bytes_max(KIND, P.SI);
-  const uint32_t slot = kDownCols * (r0 > r1 ? r0 : r1);
+  size_t fixed = (stage_floats(KIND, rows, P.I) + stage_floats(KIND, M, P.SI) + 2 * rows + M) * sizeof(float);
+  fixed = (fixed + 127) & ~(size_t)127;
+  fixed += ((size_t)rows * P.I + (size_t)M * P.SI + 8) * sizeof(float);
+  const uint32_t r0 = tile_rows(KIND, KC) * P.down.rec, r1 = tile_rows(KIND, KC) * P.sh_down.rec;
+  const uint32_t slot = r0 > r1 ? r0 : r1;
   int depth;
+  uint32_t ring_off;
   size_t bytes;
-  int rc = plan_smem(ctx, fixed, scratch, slot, &depth, &bytes);
+  int rc = plan_smem(ctx, fixed, slot, &depth, &ring_off, &bytes);
   if (rc != ORN_OK) return rc;
-  rc = set_smem(ctx, k_moe_down<KIND, M>, bytes);
+  rc = set_smem(ctx, k_moe_down<KIND, KC>, bytes);
   if (rc != ORN_OK) return rc;
-  k_moe_down<KIND, M><<<ctx->sm_count, kFusedThreads, bytes, s>>>(P, slot, depth, ctx->dev_err);
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_moe_down<KIND, KC>, dim3(ctx->sm_count), dim3(kFusedThreads), bytes,
+                                           P, slot, depth, ring_off, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_moe_down", M, KIND, P.H, P.I));
 }
 
@@ -1563,7 +1509,7 @@ int f_norm_gemv(orn_ctx* ctx, cudaStream_t s, int M, const FusedPrologue& fp, co
   Prologue P;
   P.mode = fp.mode; P.K = fp.K; P.a = fp.a; P.b = fp.b; P.w = fp.w; P.w2 = fp.w2; P.sum_out = fp.sum_out;
   P.norm_out = fp.norm_out; P.ids = fp.ids; P.eps = fp.eps;
-  P.emb = fp.emb ? lin_dev(fp.emb) : LinDev{0, 0, 0, 0, nullptr, nullptr, nullptr};
+  P.emb = fp.emb ? lin_dev(fp.emb) : LinDev{0, 0, 0, 0, nullptr, nullptr, nullptr, 0};
   RowJobs J;
   J.njobs = njobs;
   for (int j = 0; j < njobs; ++j) {
@@ -1583,52 +1529,48 @@ int f_norm_gemv(orn_ctx* ctx, cudaStream_t s, int M, const FusedPrologue& fp, co
 
 int f_moe_up(orn_ctx* ctx, cudaStream_t s, int M, const bf16_t* logits, const bf16_t* x, const orn_linear* gate,
              const orn_linear* up, int k, uint32_t* inds, bf16_t* scores, bf16_t* act) {
-  if (gate->kind != up->kind) ORN_FAIL(ctx, ORN_ERR_ARG, "moe: gate and up experts must share a format");
+  if (gate->kind != up->kind || gate->K != up->K || gate->O != up->O)
+    ORN_FAIL(ctx, ORN_ERR_ARG, "moe: gate and up experts must share format and shape");
+  if (M < 1 || M > 4) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_up: 1..4 rows");
   MoeUpParams P;
   P.logits = logits; P.x = x; P.gate = lin_dev(gate); P.up = lin_dev(up); P.inds = inds; P.scores = scores;
-  P.act = act; P.E = gate->E; P.k = k; P.H = gate->K; P.I = gate->O;
+  P.act = act; P.M = M; P.E = gate->E; P.k = k; P.H = gate->K; P.I = gate->O;
   if (P.E > 512) ORN_FAIL(ctx, ORN_ERR_ARG, "moe: more than 512 experts");
-#define ORN_UP(KIND)                                                   \
-  switch (M) {                                                         \
-    case 1: return launch_moe_up_k<KIND, 1>(ctx, s, P);                \
-    case 2: return launch_moe_up_k<KIND, 2>(ctx, s, P);                \
-    case 3: return launch_moe_up_k<KIND, 3>(ctx, s, P);                \
-    case 4: return launch_moe_up_k<KIND, 4>(ctx, s, P);                \
-  }
+  if (P.H % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_up: hidden must be a multiple of 256");
+  if (P.H > 4096) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_up: hidden above 4096");
+#define ORN_UP(KIND) \
+  return P.H > 2048 ? launch_moe_up_k<KIND, 2>(ctx, s, P) : launch_moe_up_k<KIND, 1>(ctx, s, P)
   switch (gate->kind) {
-    case ORN_Q4K: ORN_UP(ORN_Q4K) break;
-    case ORN_Q6K: ORN_UP(ORN_Q6K) break;
-    case ORN_A8: ORN_UP(ORN_A8) break;
-    default: ORN_UP(ORN_BF16) break;
+    case ORN_Q4K: ORN_UP(ORN_Q4K);
+    case ORN_Q6K: ORN_UP(ORN_Q6K);
+    case ORN_A8: ORN_UP(ORN_A8);
+    default: ORN_UP(ORN_BF16);
   }
 #undef ORN_UP
-  ORN_FAIL(ctx, ORN_ERR_ARG, "moe_up: 1..4 rows");
 }
 
 int f_moe_down(orn_ctx* ctx, cudaStream_t s, int M, const bf16_t* act, const bf16_t* sact, const uint32_t* inds,
                const bf16_t* scores, const bf16_t* gs, const orn_linear* down, const orn_linear* sh_down, int k,
                int normalize, bf16_t* out) {
   if (down->kind != sh_down->kind) ORN_FAIL(ctx, ORN_ERR_ARG, "moe: routed and shared down projections must share a format");
+  if (M < 1 || M > 4) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: 1..4 rows");
   MoeDownParams P;
   P.act = act; P.sact = sact; P.inds = inds; P.scores = scores; P.gs = gs; P.down = lin_dev(down);
-  P.sh_down = lin_dev(sh_down); P.out = out; P.k = k; P.H = down->O; P.I = down->K; P.SI = sh_down->K;
+  P.sh_down = lin_dev(sh_down); P.out = out; P.M = M; P.k = k; P.H = down->O; P.I = down->K; P.SI = sh_down->K;
   P.normalize = normalize;
   if (k > 8) ORN_FAIL(ctx, ORN_ERR_ARG, "moe: top_k above 8");
-#define ORN_DN(KIND)                                                   \
-  switch (M) {                                                         \
-    case 1: return launch_moe_down_k<KIND, 1>(ctx, s, P);              \
-    case 2: return launch_moe_down_k<KIND, 2>(ctx, s, P);              \
-    case 3: return launch_moe_down_k<KIND, 3>(ctx, s, P);              \
-    case 4: return launch_moe_down_k<KIND, 4>(ctx, s, P);              \
-  }
+  if (P.I % 256 || P.SI % 256) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: intermediate sizes must be multiples of 256");
+  const int big = P.I > P.SI ? P.I : P.SI;
+  if (big > 2048) ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: intermediate size above 2048");
+#define ORN_DN(KIND) \
+  return big > 512 ? launch_moe_down_k<KIND, 1>(ctx, s, P) : launch_moe_down_k<KIND, 0>(ctx, s, P)
   switch (down->kind) {
-    case ORN_Q4K: ORN_DN(ORN_Q4K) break;
-    case ORN_Q6K: ORN_DN(ORN_Q6K) break;
-    case ORN_A8: ORN_DN(ORN_A8) break;
-    default: ORN_DN(ORN_BF16) break;
+    case ORN_Q4K: ORN_DN(ORN_Q4K);
+    case ORN_Q6K: ORN_DN(ORN_Q6K);
+    case ORN_A8: ORN_DN(ORN_A8);
+    default: ORN_DN(ORN_BF16);
   }
 #undef ORN_DN
-  ORN_FAIL(ctx, ORN_ERR_ARG, "moe_down: 1..4 rows");
 }
 
 int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, const bf16_t* a, const bf16_t* b,
@@ -1645,7 +1587,7 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
   p.k_scale = bfr(inv_scale);
   p.eps = eps;
   dim3 grid(128 / kGdnRows, Hv);
-  k_gdn<<<grid, kGdnRows * 4, 0, s>>>(p);
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_gdn, grid, dim3(kGdnRows * 4), 0, p));
   return orn_launch_check(ctx, "k_gdn");
 }
 
@@ -1660,6 +1602,6 @@ int f_attn(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, const bf16_t* k, cons
   p.scale = 1.0f / sqrtf((float)hd);
   p.eps = eps;
   dim3 grid(Hq, T);
-  k_attn<<<grid, 1024, 0, s>>>(p);
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_attn, grid, dim3(1024), 0, p));
   return orn_launch_check(ctx, "k_attn");
 }

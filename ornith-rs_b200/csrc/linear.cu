@@ -52,10 +52,9 @@ struct Fmt<ORN_Q4K> {
     r.slo = s0; r.shi = s1;
   }
   ORN_D static void load_w(const LinDev& L, int64_t row, int u, W& w) {
-    int nb = L.K >> 8;
     int blk = u >> 3, j = u & 7;
-    w.q = ldg128_stream(L.w + (row * nb + blk) * 128 + 16 * j);
-    w.meta = ldg128(L.s + (row * nb + blk) * 16);
+    w.q = ldg128_stream(L.w + row * L.rec + blk * 128 + 16 * j);
+    w.meta = ldg128(L.s + row * L.rec + blk * 16);
   }
   ORN_D static float fold(const W& w, const X& x, int u, float acc) {
     int g = (u & 7) >> 1;
@@ -103,21 +102,20 @@ struct Fmt<ORN_Q6K> {
     }
   }
   ORN_D static void load_w(const LinDev& L, int64_t row, int u, W& w) {
-    int nb = L.K >> 8;
     int blk = u >> 4, j = u & 15, half = j >> 3, l0 = 4 * (j & 7);
-    const uint8_t* base = L.w + (row * nb + blk) * 192;
+    const uint8_t* base = L.w + row * L.rec + blk * 192;
     w.qa = ldg32_stream(base + 64 * half + l0);
     w.qb = ldg32_stream(base + 64 * half + 32 + l0);
     w.qh = ldg32_stream(base + 128 + 32 * half + l0);
     // scales sc[8*half + is + {0,2,4,6}], is = l0/16: read the 8 bytes of this
     // half as two words and pick bytes is, is+2 | is+4, is+6
-    const uint8_t* sp = L.s + (row * nb + blk) * 16 + 8 * half;
+    const uint8_t* sp = L.s + row * L.rec + blk * 16 + 8 * half;
     uint2 s8 = __ldg(reinterpret_cast<const uint2*>(sp));
     int is = l0 >> 4;
     uint32_t lo = s8.x >> (8 * is), hi = s8.y >> (8 * is);
     w.sc4 = (lo & 0xff) | (((lo >> 16) & 0xff) << 8) | ((hi & 0xff) << 16) |
             (((hi >> 16) & 0xff) << 24);
-    w.d = h2f(__ldg(reinterpret_cast<const uint16_t*>(L.b) + row * nb + blk));
+    w.d = h2f(__ldg(reinterpret_cast<const uint16_t*>(L.b + row * L.rec) + blk));
   }
   ORN_D static float fold(const W& w, const X& x, int, float acc) {
     uint32_t q1 = (w.qa & 0x0F0F0F0Fu) | ((w.qh & 0x03030303u) << 4);
@@ -158,8 +156,8 @@ struct Fmt<ORN_A8> {
     r.sum = s;
   }
   ORN_D static void load_w(const LinDev& L, int64_t row, int u, W& w) {
-    w.q = ldg128_stream(L.w + row * L.K + 16 * u);
-    w.sb = __ldg(reinterpret_cast<const uint32_t*>(L.s) + row * (L.K >> 6) + (u >> 2));
+    w.q = ldg128_stream(L.w + row * L.rec + 16 * u);
+    w.sb = __ldg(reinterpret_cast<const uint32_t*>(L.s + row * L.rec) + (u >> 2));
   }
   ORN_D static float fold(const W& w, const X& x, int, float acc) {
     const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
@@ -184,7 +182,7 @@ struct Fmt<ORN_BF16> {
   struct W { uint4 q; };
   ORN_D static void load_x(const bf16_t* x, int u, X& r) { widen8(ldg128(x + 8 * u), r.v); }
   ORN_D static void load_w(const LinDev& L, int64_t row, int u, W& w) {
-    w.q = ldg128_stream(L.w + (row * L.K + 8 * u) * 2);
+    w.q = ldg128_stream(L.w + row * L.rec + 16 * u);
   }
   ORN_D static float fold(const W& w, const X& x, int, float acc) {
     float f[8];
@@ -349,9 +347,11 @@ __global__ void q4k_dequant_kernel(LinDev L, int e, float* out) {
   int64_t nblocks = (int64_t)L.O * (L.K >> 8);
   int64_t ib = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (ib >= nblocks) return;
-  int64_t gb = (int64_t)e * nblocks + ib;
-  const uint8_t* q = L.w + gb * 128;
-  uint4 meta = ldg128(L.s + gb * 16);
+  const int nb = L.K >> 8;
+  const int64_t row = (int64_t)e * L.O + ib / nb;
+  const int blk = (int)(ib % nb);
+  const uint8_t* q = L.w + row * L.rec + blk * 128;
+  uint4 meta = ldg128(L.s + row * L.rec + blk * 16);
   float d = h2f((uint16_t)(meta.x & 0xffff)), dmin = h2f((uint16_t)(meta.x >> 16));
   float* y = out + ib * 256;
   for (int g = 0; g < 4; ++g) {
@@ -371,11 +371,13 @@ __global__ void q6k_dequant_kernel(LinDev L, int e, float* out) {
   int64_t nblocks = (int64_t)L.O * (L.K >> 8);
   int64_t ib = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (ib >= nblocks) return;
-  int64_t gb = (int64_t)e * nblocks + ib;
-  const uint8_t* ql = L.w + gb * 192;
+  const int nb = L.K >> 8;
+  const int64_t row = (int64_t)e * L.O + ib / nb;
+  const int blk = (int)(ib % nb);
+  const uint8_t* ql = L.w + row * L.rec + blk * 192;
   const uint8_t* qh = ql + 128;
-  const int8_t* sc = reinterpret_cast<const int8_t*>(L.s) + gb * 16;
-  float d = h2f(reinterpret_cast<const uint16_t*>(L.b)[gb]);
+  const int8_t* sc = reinterpret_cast<const int8_t*>(L.s + row * L.rec) + blk * 16;
+  float d = h2f(reinterpret_cast<const uint16_t*>(L.b + row * L.rec)[blk]);
   float* y = out + ib * 256;
   for (int n = 0; n < 2; ++n) {
     for (int l = 0; l < 32; ++l) {
@@ -399,8 +401,9 @@ __global__ void embedding_a8_kernel(LinDev L, const uint32_t* ids, bf16_t* out) 
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= L.K) return;
   int64_t row = ids[t];
-  uint32_t sb = reinterpret_cast<const uint32_t*>(L.s)[row * (L.K >> 6) + (i >> 6)];
-  float q = (float)L.w[row * L.K + i];
+  if (row >= L.O) row = L.O - 1;  // an id outside the table must not fault
+  uint32_t sb = reinterpret_cast<const uint32_t*>(L.s + row * L.rec)[i >> 6];
+  float q = (float)L.w[row * L.rec + i];
   out[(int64_t)t * L.K + i] = f2bf(fmaf(bf_lo(sb), q, bf_hi(sb)));
 }
 }  // namespace
@@ -434,105 +437,112 @@ void linear_artifact_sizes(int kind, int E, int O, int K, size_t* w, size_t* s, 
     default: *w = rows * K * 2; *s = 0; *b = 0; break;
   }
 }
-void linear_alloc_sizes(int kind, int E, int O, int K, size_t* w, size_t* s, size_t* b) {
-  size_t rows = (size_t)E * O;
-  switch (kind) {
-    case ORN_Q4K: *w = rows * (K / 2); *s = rows * (K / 256) * 16; *b = 0; break;
-    case ORN_Q6K: *w = rows * (K / 256) * 192; *s = rows * (K / 256) * 16; *b = rows * (K / 256) * 2; break;
-    case ORN_A8: *w = rows * K; *s = rows * (K / 64) * 4; *b = 0; break;
-    default: *w = rows * K * 2; *s = 0; *b = 0; break;
+namespace {
+// stream `off` of every row record <- / -> a dense [rows][row_bytes] tensor (row_bytes even)
+__global__ void rows_scatter_kernel(const uint8_t* dense, size_t row_bytes, uint8_t* recs, size_t rec, size_t off) {
+  const size_t r = blockIdx.x;
+  const uint16_t* s = reinterpret_cast<const uint16_t*>(dense + r * row_bytes);
+  uint16_t* d = reinterpret_cast<uint16_t*>(recs + r * rec + off);
+  for (size_t i = threadIdx.x; i < row_bytes / 2; i += blockDim.x) d[i] = s[i];
+}
+__global__ void rows_gather_kernel(const uint8_t* recs, size_t rec, size_t off, size_t row_bytes, uint8_t* dense) {
+  const size_t r = blockIdx.x;
+  const uint16_t* s = reinterpret_cast<const uint16_t*>(recs + r * rec + off);
+  uint16_t* d = reinterpret_cast<uint16_t*>(dense + r * row_bytes);
+  for (size_t i = threadIdx.x; i < row_bytes / 2; i += blockDim.x) d[i] = s[i];
+}
+// Q4_K: {dm[4], scales[12]} <-> one 16-byte header per block inside the record
+__global__ void q4k_pack_meta(const uint8_t* scales, const uint8_t* dm, int64_t nblocks, int nb, uint8_t* s1, size_t rec) {
+  int64_t ib = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (ib >= nblocks) return;
+  uint8_t* meta = s1 + (ib / nb) * rec + (ib % nb) * 16;
+  for (int i = 0; i < 4; ++i) meta[i] = dm[ib * 4 + i];
+  for (int i = 0; i < 12; ++i) meta[4 + i] = scales[ib * 12 + i];
+}
+__global__ void q4k_unpack_meta(const uint8_t* s1, size_t rec, int64_t nblocks, int nb, uint8_t* scales, uint8_t* dm) {
+  int64_t ib = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (ib >= nblocks) return;
+  const uint8_t* meta = s1 + (ib / nb) * rec + (ib % nb) * 16;
+  for (int i = 0; i < 4; ++i) dm[ib * 4 + i] = meta[i];
+  for (int i = 0; i < 12; ++i) scales[ib * 12 + i] = meta[4 + i];
+}
+// A8: scales bf16 + biases bf16 <-> u32 {scale, bias} inside the record
+__global__ void a8_pack_sb(const uint16_t* s, const uint16_t* b, int64_t n, int ng, uint8_t* s1, size_t rec) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < n) reinterpret_cast<uint32_t*>(s1 + (i / ng) * rec)[i % ng] = (uint32_t)s[i] | ((uint32_t)b[i] << 16);
+}
+__global__ void a8_unpack_sb(const uint8_t* s1, size_t rec, int64_t n, int ng, uint16_t* s, uint16_t* b) {
+  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < n) {
+    const uint32_t v = reinterpret_cast<const uint32_t*>(s1 + (i / ng) * rec)[i % ng];
+    s[i] = (uint16_t)(v & 0xffff);
+    b[i] = (uint16_t)(v >> 16);
   }
 }
-
-namespace {
-// Q4_K: {dm[4], scales[12]} -> one 16-byte record per block
-__global__ void q4k_pack_meta(const uint8_t* scales, const uint8_t* dm, int64_t nblocks, uint8_t* meta) {
-  int64_t ib = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (ib >= nblocks) return;
-  for (int i = 0; i < 4; ++i) meta[ib * 16 + i] = dm[ib * 4 + i];
-  for (int i = 0; i < 12; ++i) meta[ib * 16 + 4 + i] = scales[ib * 12 + i];
-}
-__global__ void q4k_unpack_meta(const uint8_t* meta, int64_t nblocks, uint8_t* scales, uint8_t* dm) {
-  int64_t ib = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (ib >= nblocks) return;
-  for (int i = 0; i < 4; ++i) dm[ib * 4 + i] = meta[ib * 16 + i];
-  for (int i = 0; i < 12; ++i) scales[ib * 12 + i] = meta[ib * 16 + 4 + i];
-}
-// A8: scales bf16 + biases bf16 -> u32 {scale, bias}
-__global__ void a8_pack_sb(const uint16_t* s, const uint16_t* b, int64_t n, uint32_t* sb) {
-  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (i < n) sb[i] = (uint32_t)s[i] | ((uint32_t)b[i] << 16);
-}
-__global__ void a8_unpack_sb(const uint32_t* sb, int64_t n, uint16_t* s, uint16_t* b) {
-  int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-  if (i < n) { s[i] = (uint16_t)(sb[i] & 0xffff); b[i] = (uint16_t)(sb[i] >> 16); }
-}
-__global__ void gather_rows_kernel(const uint8_t* src, const uint32_t* ids, int n, size_t row_bytes,
-                                   uint8_t* dst) {
-  // row_bytes is a multiple of 4 for every stream
-  int r = blockIdx.x;
-  const uint32_t* s = reinterpret_cast<const uint32_t*>(src + (size_t)ids[r] * row_bytes);
-  uint32_t* d = reinterpret_cast<uint32_t*>(dst + (size_t)r * row_bytes);
-  for (size_t i = threadIdx.x; i < row_bytes / 4; i += blockDim.x) d[i] = s[i];
+__global__ void gather_records_kernel(const uint8_t* src, const uint32_t* ids, size_t rec, uint8_t* dst) {
+  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)ids[blockIdx.x] * rec);
+  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)blockIdx.x * rec);
+  for (size_t i = threadIdx.x; i < rec / 16; i += blockDim.x) d[i] = s[i];
 }
 }  // namespace
 
-// dw/ds/db: device copies of the artifact tensors
-int k_linear_pack(orn_ctx* ctx, cudaStream_t st, orn_linear* L, const uint8_t* dw,
-                  const uint8_t* ds, const uint8_t* db) {
-  size_t aw, as, ab;
-  linear_artifact_sizes(L->kind, L->E, L->O, L->K, &aw, &as, &ab);
-  if (dw != L->w) ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(L->w, dw, aw, cudaMemcpyDeviceToDevice, st));
+// dw/ds/db: device copies of the artifact tensors -> row records
+int k_linear_pack(orn_ctx* ctx, cudaStream_t st, orn_linear* L, const uint8_t* dw, const uint8_t* ds,
+                  const uint8_t* db) {
+  const RecGeom g = rec_geom(L->kind, L->K);
+  const size_t rows = (size_t)L->E * L->O;
+  rows_scatter_kernel<<<(unsigned)rows, 128, 0, st>>>(dw, g.b0, L->w, g.rec, 0);
+  int rc = orn_launch_check(ctx, "rows_scatter");
+  if (rc != ORN_OK) return rc;
   if (L->kind == ORN_Q4K) {
-    int64_t nb = (int64_t)L->E * L->O * (L->K / 256);
-    q4k_pack_meta<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(ds, db, nb, L->s);
+    const int nb = L->K / 256;
+    const int64_t n = (int64_t)rows * nb;
+    q4k_pack_meta<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ds, db, n, nb, L->s, g.rec);
     return orn_launch_check(ctx, "q4k_pack_meta");
   }
   if (L->kind == ORN_Q6K) {
-    ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(L->s, ds, as, cudaMemcpyDeviceToDevice, st));
-    ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(L->b, db, ab, cudaMemcpyDeviceToDevice, st));
-    return ORN_OK;
+    rows_scatter_kernel<<<(unsigned)rows, 64, 0, st>>>(ds, g.b1, L->w, g.rec, g.b0);
+    rows_scatter_kernel<<<(unsigned)rows, 32, 0, st>>>(db, g.b2, L->w, g.rec, g.b0 + g.b1);
+    return orn_launch_check(ctx, "rows_scatter");
   }
   if (L->kind == ORN_A8) {
-    int64_t n = (int64_t)L->E * L->O * (L->K / 64);
-    a8_pack_sb<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const uint16_t*)ds, (const uint16_t*)db,
-                                                             n, (uint32_t*)L->s);
+    const int ng = L->K / 64;
+    const int64_t n = (int64_t)rows * ng;
+    a8_pack_sb<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const uint16_t*)ds, (const uint16_t*)db, n, ng, L->s, g.rec);
     return orn_launch_check(ctx, "a8_pack_sb");
   }
   return ORN_OK;
 }
 
-int k_linear_unpack(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, uint8_t* dw, uint8_t* ds,
-                    uint8_t* db) {
-  size_t aw, as, ab;
-  linear_artifact_sizes(L->kind, L->E, L->O, L->K, &aw, &as, &ab);
-  if (dw != nullptr) ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(dw, L->w, aw, cudaMemcpyDeviceToDevice, st));
+int k_linear_unpack(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, uint8_t* dw, uint8_t* ds, uint8_t* db) {
+  const RecGeom g = rec_geom(L->kind, L->K);
+  const size_t rows = (size_t)L->E * L->O;
+  rows_gather_kernel<<<(unsigned)rows, 128, 0, st>>>(L->w, g.rec, 0, g.b0, dw);
+  int rc = orn_launch_check(ctx, "rows_gather");
+  if (rc != ORN_OK) return rc;
   if (L->kind == ORN_Q4K) {
-    int64_t nb = (int64_t)L->E * L->O * (L->K / 256);
-    q4k_unpack_meta<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(L->s, nb, ds, db);
+    const int nb = L->K / 256;
+    const int64_t n = (int64_t)rows * nb;
+    q4k_unpack_meta<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(L->s, g.rec, n, nb, ds, db);
     return orn_launch_check(ctx, "q4k_unpack_meta");
   }
   if (L->kind == ORN_Q6K) {
-    ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(ds, L->s, as, cudaMemcpyDeviceToDevice, st));
-    ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(db, L->b, ab, cudaMemcpyDeviceToDevice, st));
-    return ORN_OK;
+    rows_gather_kernel<<<(unsigned)rows, 64, 0, st>>>(L->w, g.rec, g.b0, g.b1, ds);
+    rows_gather_kernel<<<(unsigned)rows, 32, 0, st>>>(L->w, g.rec, g.b0 + g.b1, g.b2, db);
+    return orn_launch_check(ctx, "rows_gather");
   }
   if (L->kind == ORN_A8) {
-    int64_t n = (int64_t)L->E * L->O * (L->K / 64);
-    a8_unpack_sb<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const uint32_t*)L->s, n,
-                                                               (uint16_t*)ds, (uint16_t*)db);
+    const int ng = L->K / 64;
+    const int64_t n = (int64_t)rows * ng;
+    a8_unpack_sb<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(L->s, g.rec, n, ng, (uint16_t*)ds, (uint16_t*)db);
     return orn_launch_check(ctx, "a8_unpack_sb");
   }
   return ORN_OK;
 }
 
-int k_linear_gather_rows(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const uint32_t* ids,
-                         int n, orn_linear* out) {
-  size_t w, s, b;
-  linear_alloc_sizes(L->kind, 1, 1, L->K, &w, &s, &b);
-  gather_rows_kernel<<<n, 256, 0, st>>>(L->w, ids, n, w, out->w);
-  if (s) gather_rows_kernel<<<n, 64, 0, st>>>(L->s, ids, n, s, out->s);
-  if (b) gather_rows_kernel<<<n, 32, 0, st>>>(L->b, ids, n, b, out->b);
+int k_linear_gather_rows(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const uint32_t* ids, int n,
+                         orn_linear* out) {
+  gather_records_kernel<<<n, 128, 0, st>>>(L->w, ids, L->rec, out->w);
   return orn_launch_check(ctx, "gather_rows");
 }
 
@@ -590,7 +600,10 @@ __global__ void random_q4k_kernel(LinDev L, uint64_t seed, float std) {
     sc[j] = d > 0.f ? (uint8_t)fminf(63.f, fmaxf(0.f, rintf(scale[j] / d))) : 0;
     m[j] = dm > 0.f ? (uint8_t)fminf(63.f, fmaxf(0.f, rintf(mn[j] / dm))) : 0;
   }
-  uint8_t* meta = const_cast<uint8_t*>(L.s) + ib * 16;
+  const int nbr = L.K >> 8;
+  const int64_t rrow = ib / nbr;
+  const int rblk = (int)(ib % nbr);
+  uint8_t* meta = const_cast<uint8_t*>(L.s) + rrow * L.rec + rblk * 16;
   meta[0] = dh & 0xff; meta[1] = dh >> 8; meta[2] = dmh & 0xff; meta[3] = dmh >> 8;
   uint8_t* p = meta + 4;
   for (int i = 0; i < 12; ++i) p[i] = 0;
@@ -600,7 +613,7 @@ __global__ void random_q4k_kernel(LinDev L, uint64_t seed, float std) {
     p[j - 4] |= (sc[j] >> 4) << 6;
     p[j] |= (m[j] >> 4) << 6;
   }
-  uint8_t* q = const_cast<uint8_t*>(L.w) + ib * 128;
+  uint8_t* q = const_cast<uint8_t*>(L.w) + rrow * L.rec + rblk * 128;
   for (int g = 0; g < 4; ++g) {
     float ds0 = d * sc[2 * g], ms0 = dm * m[2 * g], ds1 = d * sc[2 * g + 1], ms1 = dm * m[2 * g + 1];
     for (int l = 0; l < 32; ++l) {
@@ -631,10 +644,13 @@ __global__ void random_q6k_kernel(LinDev L, uint64_t seed, float std) {
   int8_t sc[16];
   for (int j = 0; j < 16; ++j)
     sc[j] = d > 0.f ? (int8_t)fminf(127.f, fmaxf(1.f, rintf(sub[j] / d))) : 0;
-  int8_t* sp = reinterpret_cast<int8_t*>(const_cast<uint8_t*>(L.s)) + ib * 16;
+  const int nbr = L.K >> 8;
+  const int64_t rrow = ib / nbr;
+  const int rblk = (int)(ib % nbr);
+  int8_t* sp = reinterpret_cast<int8_t*>(const_cast<uint8_t*>(L.s) + rrow * L.rec) + rblk * 16;
   for (int j = 0; j < 16; ++j) sp[j] = sc[j];
-  reinterpret_cast<uint16_t*>(const_cast<uint8_t*>(L.b))[ib] = dh;
-  uint8_t* ql = const_cast<uint8_t*>(L.w) + ib * 192;
+  reinterpret_cast<uint16_t*>(const_cast<uint8_t*>(L.b) + rrow * L.rec)[rblk] = dh;
+  uint8_t* ql = const_cast<uint8_t*>(L.w) + rrow * L.rec + rblk * 192;
   uint8_t* qh = ql + 128;
   for (int i = 0; i < 128; ++i) ql[i] = 0;
   for (int i = 0; i < 64; ++i) qh[i] = 0;
@@ -664,8 +680,11 @@ __global__ void random_a8_kernel(LinDev L, uint64_t seed, float std) {
   float scale = fmaxf((hi - lo) / 255.0f, 1e-8f);
   bf16_t sb = f2bf(scale), bb = f2bf(lo);
   float s = bf2f(sb), b = bf2f(bb);
-  reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(L.s))[ig] = (uint32_t)sb | ((uint32_t)bb << 16);
-  uint8_t* q = const_cast<uint8_t*>(L.w) + ig * 64;
+  const int ngr = L.K >> 6;
+  const int64_t rrow = ig / ngr;
+  const int rgrp = (int)(ig % ngr);
+  reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(L.s) + rrow * L.rec)[rgrp] = (uint32_t)sb | ((uint32_t)bb << 16);
+  uint8_t* q = const_cast<uint8_t*>(L.w) + rrow * L.rec + rgrp * 64;
   for (int i = 0; i < 64; ++i) {
     float v = std * approx_normal(seed, ig * 64 + i);
     q[i] = (uint8_t)fminf(255.f, fmaxf(0.f, rintf((v - b) / s)));

@@ -833,7 +833,7 @@ int32_t orn_model_config(const orn_model* m, orn_config* out) {
 size_t orn_model_weight_bytes(const orn_model* m) {
   size_t total = 0;
   if (!m) return 0;
-  for (auto& kv : m->lins) total += kv.second->w_bytes + kv.second->s_bytes + kv.second->b_bytes;
+  for (auto& kv : m->lins) total += kv.second->w_bytes;
   for (auto& kv : m->tensors) total += kv.second.n * 2;
   return total;
 }

@@ -48,6 +48,13 @@ typedef uint16_t bf16_t;
 
 ORN_HD float bf2f(bf16_t h) { return orn_u2f(((uint32_t)h) << 16); }
 ORN_HD bf16_t f2bf(float f) {
+#ifdef __CUDA_ARCH__
+  // one instruction on the device; equal to the integer form below for every input that is not
+  // a NaN (a NaN comes back as the canonical quiet NaN instead of keeping its payload)
+  unsigned short r;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
+  return r;
+#endif
   uint32_t u = orn_f2u(f);
   if ((u & 0x7fffffffu) > 0x7f800000u) return (bf16_t)((u >> 16) | 0x40);  // NaN
   u += 0x7fffu + ((u >> 16) & 1u);
@@ -59,6 +66,11 @@ ORN_HD float bfr(float f) { return bf2f(f2bf(f)); }
 // IEEE half -> float, subnormals included (k-quant super-scales at the 1e-3
 // scale of the synthetic artifacts are often subnormal halves).
 ORN_HD float h2f(uint16_t h) {
+#ifdef __CUDA_ARCH__
+  float r;  // the hardware conversion is exact for every half, subnormals included
+  asm("cvt.f32.f16 %0, %1;" : "=f"(r) : "h"(h));
+  return r;
+#endif
   uint32_t s = ((uint32_t)(h & 0x8000u)) << 16;
   uint32_t e = (h >> 10) & 0x1fu;
   uint32_t m = h & 0x3ffu;
@@ -199,6 +211,10 @@ ORN_HD float orn_softplus_bf(float x /* bf16 value */) {
 // ---------------------------------------------------------------------------
 // Butterfly sum over the 32 lanes: xor 16, 8, 4, 2, 1.  Every lane ends with
 // the same value; the CPU restatement folds a 32-entry array the same way.
+// programmatic dependent launch: let the next kernel of the stream start / wait for the previous ones
+ORN_D void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+ORN_D void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 ORN_D float warp_sum(float v) {
   v = v + __shfl_xor_sync(0xffffffffu, v, 16);
   v = v + __shfl_xor_sync(0xffffffffu, v, 8);

@@ -20,26 +20,46 @@ struct orn_ctx {
   cudaEvent_t t0 = nullptr, t1 = nullptr;  // orn_timer_start / orn_timer_stop
   int* dev_err = nullptr;  // set by a kernel whose bounded wait ran out
   struct orn_ktime* kt = nullptr;  // per-kernel device times when ORN_KTIME=1 (eager launches only)
+  bool pdl = true;  // launch the fused kernels as programmatic dependents (ORN_NO_PDL=1 turns it off)
 };
 
 // Records an event after the launch just made and attributes the device time
 // since the previous mark to `what` (api.cu).
 void orn_ktime_mark(orn_ctx* ctx, const char* what);
 
-// Device-resident weight matrix [E, O, K].
-//   Q4_K: w = nibble bytes [E,O,K/2]; s = 16-byte records [E,O,K/256] =
-//         {d f16, dmin f16, scales[12]} so one aligned 128-bit load brings a
-//         block's whole header; b unused.
-//   Q6_K: w = ql|qh bytes [E,O,K/256*192]; s = int8 scales [E,O,K/256,16];
-//         b = d f16 [E,O,K/256].
-//   A8  : w = codes [E,O,K]; s = u32 records [E,O,K/64] = {scale bf16, bias bf16}.
-//   BF16: w = bf16 [E,O,K].
+// Device-resident weight matrix [E, O, K] as ROW RECORDS: every weight row is
+// one contiguous, 16-byte aligned record
+//   [stream 0: codes][stream 1: scales / headers][stream 2: Q6_K super-scales][pad]
+// so that one bulk copy brings everything a consecutive run of rows needs.
+//   Q4_K: nibble bytes K/2 | one 16-byte header {d f16, dmin f16, scales[12]} per block
+//   Q6_K: ql|qh 192 bytes per block | int8 scales 16 per block | d f16 per block
+//   A8  : codes K | u32 {scale bf16, bias bf16} per 64 weights
+//   BF16: bf16 K
+// w points at row 0's record; s and b point at its streams 1 and 2 (same
+// allocation), so row r's streams are w + r*rec, s + r*rec, b + r*rec.
+struct RecGeom {
+  uint32_t b0, b1, b2, rec;
+};
+__host__ __device__ inline RecGeom rec_geom(int kind, int K) {
+  RecGeom g;
+  const uint32_t nb = (uint32_t)K >> 8;
+  switch (kind) {
+    case ORN_Q4K: g.b0 = (uint32_t)K / 2; g.b1 = nb * 16; g.b2 = 0; break;
+    case ORN_Q6K: g.b0 = nb * 192; g.b1 = nb * 16; g.b2 = nb * 2; break;
+    case ORN_A8: g.b0 = (uint32_t)K; g.b1 = ((uint32_t)K >> 6) * 4; g.b2 = 0; break;
+    default: g.b0 = 2u * (uint32_t)K; g.b1 = 0; g.b2 = 0; break;
+  }
+  g.rec = (g.b0 + g.b1 + g.b2 + 15u) & ~15u;
+  return g;
+}
+
 struct orn_linear {
   int kind = 0, E = 1, O = 0, K = 0;
-  uint8_t* w = nullptr;
-  uint8_t* s = nullptr;
-  uint8_t* b = nullptr;
-  size_t w_bytes = 0, s_bytes = 0, b_bytes = 0;  // device sizes
+  uint8_t* w = nullptr;  // the allocation: E*O records
+  uint8_t* s = nullptr;  // w + b0
+  uint8_t* b = nullptr;  // w + b0 + b1
+  uint32_t rec = 0;      // bytes per row record
+  size_t w_bytes = 0;    // device size of the allocation
   bool owns = true;
 };
 
@@ -49,9 +69,10 @@ struct LinDev {
   const uint8_t* w;
   const uint8_t* s;
   const uint8_t* b;
+  uint32_t rec;
 };
 static inline LinDev lin_dev(const orn_linear* l) {
-  return LinDev{l->kind, l->E, l->O, l->K, l->w, l->s, l->b};
+  return LinDev{l->kind, l->E, l->O, l->K, l->w, l->s, l->b, l->rec};
 }
 
 #define ORN_CHECK_CUDA(ctx, call)                                              \
@@ -80,6 +101,32 @@ static inline int orn_launch_check(orn_ctx* ctx, const char* what) {
   return ORN_OK;
 }
 
+// Launch `kern` so that it may begin while the previous kernel of the stream is still draining
+// (programmatic dependent launch).  Such a kernel runs its set-up and its weight prefetch at
+// once and executes griddepcontrol.wait before it touches anything an earlier kernel wrote or
+// still reads.  Without the attribute the same kernel runs as an ordinary launch (the wait
+// returns immediately).
+template <typename... KArgs, typename... Args>
+inline cudaError_t orn_launch_dependent(orn_ctx* ctx, cudaStream_t s, void (*kern)(KArgs...), dim3 grid, dim3 block,
+                                        size_t smem, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  // In a captured graph plain kernel-to-kernel edges replay faster than programmatic ones
+  // (measured: the decode cycle's graph is 7 % slower with them), so the attribute is used for
+  // eager launches only.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing(s, &cap);
+  at[0].val.programmaticStreamSerializationAllowed = (ctx->pdl && cap == cudaStreamCaptureStatusNone) ? 1 : 0;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // ---- kernel launchers (each returns ORN_OK or an error, work on s) ---------
 // linear.cu
 int k_gemv(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, int M, void* y,
@@ -98,7 +145,6 @@ int k_linear_gather_rows(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, cons
                          int n, orn_linear* out);
 int k_fill_bf16(orn_ctx* ctx, cudaStream_t s, bf16_t* p, size_t n, uint64_t seed, float mean,
                 float std);
-void linear_alloc_sizes(int kind, int E, int O, int K, size_t* w, size_t* s, size_t* b);
 void linear_artifact_sizes(int kind, int E, int O, int K, size_t* w, size_t* s, size_t* b);
 
 // ops.cu

@@ -26,19 +26,16 @@ ORN_D void widen8(const uint4& v, float* f) {
 }
 
 // kernels/q4k.metal:43-56 (get_scale_min_k4) on the 12 scale bytes held as
-// three words (bytes 0-3, 4-7, 8-11)
+// three words (bytes 0-3, 4-7, 8-11).  Branch-free: neighbouring lanes ask for
+// different sub-blocks, so a branch on j would run both sides one after the other.
 ORN_D void q4k_scale_min(int j, uint32_t s0, uint32_t s1, uint32_t s2, float* sc, float* mn) {
-  if (j < 4) {
-    uint32_t q_j = (s0 >> (8 * j)) & 0xff;
-    uint32_t q_j4 = (s1 >> (8 * j)) & 0xff;
-    *sc = (float)(q_j & 63);
-    *mn = (float)(q_j4 & 63);
-  } else {
-    int jj = j - 4;
-    uint32_t a = (s2 >> (8 * jj)) & 0xff;   // q[j+4]
-    uint32_t lo = (s0 >> (8 * jj)) & 0xff;  // q[j-4]
-    uint32_t hi = (s1 >> (8 * jj)) & 0xff;  // q[j]
-    *sc = (float)((a & 0xF) | ((lo >> 6) << 4));
-    *mn = (float)((a >> 4) | ((hi >> 6) << 4));
-  }
+  const int sh = 8 * (j & 3);
+  const uint32_t a = (s0 >> sh) & 0xff;  // q[j & 3]
+  const uint32_t b = (s1 >> sh) & 0xff;  // q[(j & 3) + 4]
+  const uint32_t c = (s2 >> sh) & 0xff;  // q[(j & 3) + 8]
+  const bool low = j < 4;
+  const uint32_t scv = low ? (a & 63) : ((c & 0xF) | ((a >> 6) << 4));
+  const uint32_t mnv = low ? (b & 63) : ((c >> 4) | ((b >> 6) << 4));
+  *sc = (float)scv;
+  *mn = (float)mnv;
 }
