@@ -224,6 +224,24 @@ def kernel_roofline(pkg, ctx, model, cfg, iters=20):
             "traffic": NCU_TRAFFIC_BYTES, "launch_us": per * 1e3, "algorithmic_bytes": alg, "launches_timed": n}
 
 
+def reduce_max_over_ranks(values, dist, device):
+    """Element-wise maximum of `values` over all ranks (the slowest rank times the job).
+    `dist` is torch.distributed after init_process_group, or None for one process."""
+    if dist is None:
+        return list(values)
+    import torch
+    t = torch.tensor(list(values), dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def whole_job_rates(world, steps, gen_tokens, dev_ms, wall_s):
+    """Replica per GPU (weak scaling): every rank generates steps x gen_tokens tokens; the job's
+    rate is all ranks' tokens over the slowest rank's time.  Returns (device-timed, end-to-end)."""
+    total_tokens = world * steps * gen_tokens
+    return total_tokens / (dev_ms * 1e-3), total_tokens / wall_s
+
+
 def ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -279,14 +297,8 @@ def ours(args):
     clocks = sampler.stop()
     assert toks == ar
 
-    if dist is not None:
-        import torch
-        t = torch.tensor([dev_ms, walls], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, walls = t.tolist()
-    total_tokens = world * args.steps * GEN_TOKENS
-    value = total_tokens / (dev_ms * 1e-3)
-    e2e = total_tokens / walls
+    dev_ms, walls = reduce_max_over_ranks([dev_ms, walls], dist, "cuda")
+    value, e2e = whole_job_rates(world, args.steps, GEN_TOKENS, dev_ms, walls)
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()

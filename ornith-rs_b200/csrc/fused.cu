@@ -37,6 +37,7 @@ __device__ __noinline__ float sigmoid_f32_call(float x) { return orn_sigmoid_f32
 __device__ __noinline__ float softplus_bf_call(float x) { return orn_softplus_bf(x); }
 __device__ __noinline__ void sincosf_call(float a, float* sn, float* cs) { orn_sincosf(a, sn, cs); }
 
+constexpr int kMoeThreads = 256;    // 16 warps with half-height tiles measured no faster than 8
 constexpr int kFusedThreads = 256;  // one CTA per SM: 8 warps (up to 255 registers each), each with its own weight ring
 
 // ---------------------------------------------------------------------------
@@ -287,6 +288,13 @@ constexpr uint32_t kWaitLimit = 1u << 14;  // try_wait rounds before giving up (
 constexpr int kSlotMax = 9216;
 __host__ __device__ constexpr int k_class(int K) { return K <= 512 ? 0 : K <= 2048 ? 1 : 2; }
 __host__ __device__ constexpr int tile_rows(int kind, int kc) {
+  return kind == ORN_A8    ? (kc == 0 ? 8 : kc == 1 ? 4 : 2)
+         : kind == ORN_Q4K ? (kc == 0 ? 8 : 2)
+         : kind == ORN_Q6K ? (kc == 2 ? 2 : 4)
+                           : (kc == 0 ? 8 : kc == 1 ? 2 : 1);
+}
+// rows per tile in the expert kernels
+__host__ __device__ constexpr int moe_rows(int kind, int kc) {
   return kind == ORN_A8    ? (kc == 0 ? 8 : kc == 1 ? 4 : 2)
          : kind == ORN_Q4K ? (kc == 0 ? 8 : 4)
          : kind == ORN_Q6K ? (kc == 2 ? 2 : 4)
@@ -888,11 +896,11 @@ __device__ __noinline__ void warp_softmax_topk(const bf16_t* logits, int n, int 
 
 
 template <int KIND, int KC>
-__global__ void __launch_bounds__(kFusedThreads, 1) k_moe_up(MoeUpParams P, uint32_t slot_bytes, int depth,
+__global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32_t slot_bytes, int depth,
                                                              uint32_t ring_off, int* err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* smem = reinterpret_cast<float*>(smem_raw);
-  constexpr int RT = tile_rows(KIND, KC);
+  constexpr int RT = moe_rows(KIND, KC);
   const int M = P.M;
   XStage X;
   float* next = stage_carve(smem, KIND, M, P.H, X);
@@ -989,11 +997,11 @@ struct MoeDownParams {
 // shared expert's tile.  After the butterfly each lane holds one column's sum, so the bf16
 // combine runs per lane without further exchange.
 template <int KIND, int KC>
-__global__ void __launch_bounds__(kFusedThreads, 1) k_moe_down(MoeDownParams P, uint32_t slot_bytes, int depth,
+__global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, uint32_t slot_bytes, int depth,
                                                                uint32_t ring_off, int* err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* smem = reinterpret_cast<float*>(smem_raw);
-  constexpr int RT = tile_rows(KIND, KC);
+  constexpr int RT = moe_rows(KIND, KC);
   const int M = P.M;
   const int rows = M * P.k;
   XStage X, XS;
@@ -1389,8 +1397,7 @@ int set_smem(orn_ctx* ctx, Kern kern, size_t bytes) {
 
 // rings beside `fixed` bytes of stages and scratch: offset of the rings, their depth, the launch's
 // dynamic shared memory
-int plan_smem(orn_ctx* ctx, size_t fixed, uint32_t slot_bytes, int* depth, uint32_t* ring_off, size_t* total) {
-  const int nwarps = kFusedThreads / 32;
+int plan_smem(orn_ctx* ctx, size_t fixed, uint32_t slot_bytes, int nwarps, int* depth, uint32_t* ring_off, size_t* total) {
   fixed = (fixed + 127) & ~(size_t)127;
   int d = 8;
   while (d > 1 && fixed + ring_bytes(nwarps, d, slot_bytes) > kSmemBudget) --d;
@@ -1411,7 +1418,7 @@ int launch_norm_gemv_mask(orn_ctx* ctx, cudaStream_t s, const Prologue& P, const
   int depth;
   uint32_t ring_off;
   size_t bytes;
-  int rc = plan_smem(ctx, fixed, slot, &depth, &ring_off, &bytes);
+  int rc = plan_smem(ctx, fixed, slot, kFusedThreads / 32, &depth, &ring_off, &bytes);
   if (rc != ORN_OK) return rc;
   rc = set_smem(ctx, k_norm_gemv<M, MASK, KC>, bytes);
   if (rc != ORN_OK) return rc;
@@ -1468,15 +1475,15 @@ int launch_moe_up_k(orn_ctx* ctx, cudaStream_t s, const MoeUpParams& P) {
   size_t fixed = stage_floats(KIND, M, P.H) * sizeof(float) + (size_t)M * P.k * 4;
   fixed = (fixed + 127) & ~(size_t)127;
   fixed += ((size_t)M * P.H + (size_t)M * P.E + M * 32 + M * P.k + 8) * sizeof(float);
-  const uint32_t slot = tile_rows(KIND, KC) * P.gate.rec;
+  const uint32_t slot = moe_rows(KIND, KC) * P.gate.rec;
   int depth;
   uint32_t ring_off;
   size_t bytes;
-  int rc = plan_smem(ctx, fixed, slot, &depth, &ring_off, &bytes);
+  int rc = plan_smem(ctx, fixed, slot, kMoeThreads / 32, &depth, &ring_off, &bytes);
   if (rc != ORN_OK) return rc;
   rc = set_smem(ctx, k_moe_up<KIND, KC>, bytes);
   if (rc != ORN_OK) return rc;
-  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_moe_up<KIND, KC>, dim3(ctx->sm_count), dim3(kFusedThreads), bytes,
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_moe_up<KIND, KC>, dim3(ctx->sm_count), dim3(kMoeThreads), bytes,
                                            P, slot, depth, ring_off, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_moe_up", M, KIND, P.I, P.H));
 }
@@ -1488,16 +1495,16 @@ int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
   size_t fixed = (stage_floats(KIND, rows, P.I) + stage_floats(KIND, M, P.SI) + 2 * rows + M) * sizeof(float);
   fixed = (fixed + 127) & ~(size_t)127;
   fixed += ((size_t)rows * P.I + (size_t)M * P.SI + 8) * sizeof(float);
-  const uint32_t r0 = tile_rows(KIND, KC) * P.down.rec, r1 = tile_rows(KIND, KC) * P.sh_down.rec;
+  const uint32_t r0 = moe_rows(KIND, KC) * P.down.rec, r1 = moe_rows(KIND, KC) * P.sh_down.rec;
   const uint32_t slot = r0 > r1 ? r0 : r1;
   int depth;
   uint32_t ring_off;
   size_t bytes;
-  int rc = plan_smem(ctx, fixed, slot, &depth, &ring_off, &bytes);
+  int rc = plan_smem(ctx, fixed, slot, kMoeThreads / 32, &depth, &ring_off, &bytes);
   if (rc != ORN_OK) return rc;
   rc = set_smem(ctx, k_moe_down<KIND, KC>, bytes);
   if (rc != ORN_OK) return rc;
-  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_moe_down<KIND, KC>, dim3(ctx->sm_count), dim3(kFusedThreads), bytes,
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_moe_down<KIND, KC>, dim3(ctx->sm_count), dim3(kMoeThreads), bytes,
                                            P, slot, depth, ring_off, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_moe_down", M, KIND, P.H, P.I));
 }

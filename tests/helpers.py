@@ -243,3 +243,104 @@ def upload_model(pkg, ctx, cfg, weights):
         else:
             m.set_tensor(name, w)
     return m
+
+
+# ---------------------------------------------------------------------------
+# a seeded artifact on disk in the reference's layout (src/safetensors.rs:189-308,
+# src/weights.rs:179-279, tools/forge_q4k.py:40-48): config.json, sharded
+# safetensors with an index, the MTP sidecar with numbered experts, FR-Spec ids
+# ---------------------------------------------------------------------------
+def _st_write(path, tensors):
+    """tensors: name -> (dtype string, shape, bytes)."""
+    import json
+    header, off, blobs = {}, 0, []
+    for name, (dt, shape, raw) in tensors.items():
+        header[name] = {"dtype": dt, "shape": [int(x) for x in shape], "data_offsets": [off, off + len(raw)]}
+        off += len(raw)
+        blobs.append(raw)
+    hj = json.dumps(header).encode()
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(len(hj).to_bytes(8, "little"))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+def _module_tensors(name, W):
+    """The artifact tensors of one weight module."""
+    import orn_oracle as orc
+    lead = [W.E] if W.E > 1 else []
+    raw = lambda a: np.ascontiguousarray(a).tobytes()
+    nb = W.K // 256
+    if W.kind == orc.Q4K:
+        return {name + ".weight": ("U32", lead + [W.O, W.K // 8], raw(W.w)),
+                name + ".scales": ("U8", lead + [W.O, nb, 12], raw(W.s)),
+                name + ".dm": ("F16", lead + [W.O, nb, 2], raw(W.b))}
+    if W.kind == orc.Q6K:
+        return {name + ".weight": ("U32", lead + [W.O, 3 * W.K // 16], raw(W.w)),
+                name + ".scales": ("I8", lead + [W.O, nb, 16], raw(W.s)),
+                name + ".dm": ("F16", lead + [W.O, nb, 1], raw(W.b))}
+    if W.kind == orc.A8:
+        return {name + ".weight": ("U32", lead + [W.O, W.K // 4], raw(W.w)),
+                name + ".scales": ("BF16", lead + [W.O, W.K // 64], raw(W.s)),
+                name + ".biases": ("BF16", lead + [W.O, W.K // 64], raw(W.b))}
+    return None
+
+
+def write_artifact(directory, cfg, W, frspec_ids=None):
+    """Writes the tiny model as the reference stores a model on disk; returns the directory."""
+    import json
+    import os
+    import orn_oracle as orc
+    os.makedirs(os.path.join(directory, "mtp"), exist_ok=True)
+    text = {"hidden_size": cfg.hidden, "num_hidden_layers": cfg.n_layers, "num_attention_heads": cfg.n_heads,
+            "num_key_value_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
+            "full_attention_interval": cfg.full_attn_interval,
+            "rope_parameters": {"rope_theta": cfg.rope_theta, "partial_rotary_factor": cfg.rope_dims / cfg.head_dim},
+            "linear_num_key_heads": cfg.gdn_k_heads, "linear_num_value_heads": cfg.gdn_v_heads,
+            "linear_key_head_dim": cfg.gdn_head_dim, "linear_value_head_dim": cfg.gdn_head_dim,
+            "linear_conv_kernel_dim": cfg.gdn_conv_kernel, "num_experts": cfg.n_experts,
+            "num_experts_per_tok": cfg.top_k, "moe_intermediate_size": cfg.expert_inter,
+            "shared_expert_intermediate_size": cfg.shared_inter, "norm_topk_prob": bool(cfg.norm_topk_prob),
+            "vocab_size": cfg.vocab, "rms_norm_eps": cfg.rms_eps}
+    with open(os.path.join(directory, "config.json"), "w") as f:
+        json.dump({"model_type": "qwen3_5_moe", "text_config": text,
+                   "mlx_lm_extra_tensors": {"mtp_file": "mtp/weights.safetensors"}}, f)
+    trunk, side = {}, {}
+    for name, w in W.items():
+        is_mtp = name.startswith("mtp.")
+        dst = side if is_mtp else trunk
+        full = name if is_mtp else ("language_model.lm_head" if name == "lm_head" else "language_model.model." + name)
+        if isinstance(w, orc.Weights):
+            mod = full[:-len(".weight")] if full.endswith(".weight") else full
+            t = _module_tensors(mod, w)
+            if t is not None:
+                dst.update(t)
+            elif w.E > 1:  # bf16 experts of the MTP head: numbered, one matrix each (src/weights.rs:237-279)
+                proj = mod.rsplit(".", 1)[1]
+                base = mod[:-len("switch_mlp." + proj)] + "experts."
+                per = w.w.reshape(w.E, w.O, w.K)
+                for e in range(w.E):
+                    dst["%s%d.%s.weight" % (base, e, proj)] = ("BF16", [w.O, w.K], per[e].tobytes())
+            else:
+                dst[mod + ".weight"] = ("BF16", [w.O, w.K], np.ascontiguousarray(w.w).tobytes())
+        else:
+            dst[full] = ("BF16", list(np.shape(w)), np.ascontiguousarray(w).tobytes())
+    # two shards + index, as a published artifact has
+    names = sorted(trunk)
+    half = len(names) // 2
+    shards = {"model-00001-of-00002.safetensors": names[:half], "model-00002-of-00002.safetensors": names[half:]}
+    weight_map = {}
+    for fn, ns in shards.items():
+        _st_write(os.path.join(directory, fn), {n: trunk[n] for n in ns})
+        weight_map.update({n: fn for n in ns})
+    with open(os.path.join(directory, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {}, "weight_map": weight_map}, f)
+    _st_write(os.path.join(directory, "mtp", "weights.safetensors"), side)
+    if frspec_ids is not None:  # u32 count then the ids, little endian (src/frspec.rs:67-148)
+        ids = np.ascontiguousarray(frspec_ids, np.uint32)
+        with open(os.path.join(directory, "ids.bin"), "wb") as f:
+            f.write(np.uint32(len(ids)).tobytes())
+            f.write(ids.tobytes())
+    return directory

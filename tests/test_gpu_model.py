@@ -117,6 +117,41 @@ def test_mtp_depth2_and_frspec(pkg, ctx, tiny):
         gm.set_frspec(np.array([cfg.vocab], np.uint32))
 
 
+def test_load_from_safetensors_artifact(pkg, ctx, tiny, tmp_path):
+    """orn_model_load (config.json, sharded safetensors + index, MTP sidecar with numbered experts) and
+    orn_frspec_load give the same model as uploading the tensors one by one."""
+    cfg, W, om, gm = tiny
+    rng = np.random.default_rng(3)
+    ids = np.sort(rng.choice(cfg.vocab, 256, replace=False)).astype(np.uint32)
+    d = hp.write_artifact(str(tmp_path / "artifact"), cfg, W, frspec_ids=ids)
+    lm = pkg.TextModel.load(ctx, d, max_ctx=cfg.max_ctx)
+    for f in ("hidden", "n_layers", "n_heads", "n_kv_heads", "head_dim", "rope_dims", "gdn_k_heads", "gdn_v_heads",
+              "n_experts", "top_k", "expert_inter", "shared_inter", "vocab", "full_attn_interval", "norm_topk_prob"):
+        assert getattr(lm.cfg, f) == getattr(cfg, f), f
+    prompt = np.array([11, 4, 1300, 77, 5], np.uint32)
+    ref = om.generate(prompt, 12)
+    c = lm.make_cache()
+    assert pkg.generate_step(lm, c, prompt, 12) == ref
+    c.reset()
+    got, st = pkg.generate_step_mtp(lm, c, prompt, 2, 12)
+    rref, rst = om.generate_mtp(prompt, 2, 12)
+    assert got == ref == rref and (st.cycles, st.accepted) == (rst.cycles, rst.accepted)
+    # FR-Spec ids file: the pruned head drafts the same as the oracle's
+    om.set_frspec(hp.gather_rows_weights(W["lm_head"], ids), ids)
+    lm.load_frspec(d + "/ids.bin")
+    c.reset()
+    got, st = pkg.generate_step_mtp(lm, c, prompt, 1, 12, frspec=True)
+    rref, rst = om.generate_mtp(prompt, 1, 12, frspec=True)
+    assert got == ref == rref and (st.cycles, st.accepted) == (rst.cycles, rst.accepted)
+    c.free()
+    lm.free()
+    # a missing shard is an error code with a message, not a crash
+    import os
+    os.remove(d + "/model-00002-of-00002.safetensors")
+    with pytest.raises(pkg.OrnError):
+        pkg.TextModel.load(ctx, d, max_ctx=cfg.max_ctx)
+
+
 def test_full_size_layers_mtp_equals_autoregressive(pkg, ctx):
     """Real layer dimensions (hidden 2048, 256 experts top-8, 16/2 heads, vocab
     248320) at 4 layers, random-init on the GPU: speculative output is
