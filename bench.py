@@ -33,8 +33,8 @@ PROMPT_LEN, GEN_TOKENS, FORCE_P, SEED = 51, 200, 0.5, 20240611
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the kernel above, from the ncu
-# capture summarised in profiles/ (None until a capture of the current kernel exists)
-NCU_TRAFFIC_BYTES = None
+# capture summarised in profiles/
+NCU_TRAFFIC_BYTES = 28.59e6  # profiles/fused_kernels_ncu_profile_step_4layer.md: 27.04 MB read + 1.55 MB written
 
 
 def peaks():
@@ -285,10 +285,11 @@ def ours(args):
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
-    dev_ms, walls, launches, cycles, accepted = 0.0, 0.0, 0, 0, 0
+    dev_ms, walls, launches, cycles, accepted, prefill_ms = 0.0, 0.0, 0, 0, 0, 0.0
     for _ in range(args.steps):
         toks, st, prof, wall = one()
         dev_ms += prof.total_ms
+        prefill_ms += prof.prefill_ms
         walls += wall
         launches += prof.kernel_launches
         cycles += st.cycles
@@ -320,13 +321,15 @@ def ours(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations, f32 accumulate",
         "data": "synthetic (random-init weights, random prompt ids)",
         "config": {"workload": "BASELINE config 4: 40-layer 35B-A3B, Q4_K/Q6_K experts + affine-8 dense + bf16 MTP head, "
-                               "51-token prompt, 200 greedy tokens, MTP depth 1, forced-draft p=%.2f" % FORCE_P,
+                               "51-token prompt, 200 greedy tokens, MTP depth 1, forced-draft p=%.2f; value = decode loop "
+                               "(200 tokens) on the device, e2e = the whole call on the host clock including the "
+                               "prompt upload, the 51-token prefill and the per-cycle readback" % FORCE_P,
                    "l2_policy": "weights read per step (2.7 GB) exceed L2 (126 MB)", "parallelism": "replica per GPU"},
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": PROMPT_LEN * 4,
                 "d2h_bytes_per_step": int(16 * cycles / args.steps) + 4},
         "gpu_launches": launches, "clocks": clocks, "roofline": roof, "step_roofline": step_roof,
         "acceptance": accepted / max(cycles, 1), "tokens_per_cycle": args.steps * GEN_TOKENS / max(cycles, 1),
-        "mtp_equals_autoregressive": True,
+        "mtp_equals_autoregressive": True, "prefill_ms_per_step": prefill_ms / args.steps,
     }
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_arm(pkg, ctx)

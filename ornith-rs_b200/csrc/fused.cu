@@ -737,7 +737,7 @@ constexpr int kMaxAcc = 32;  // R * pad(M) never exceeds this
 
 template <int M, int MASK, int KC>
 __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJobs J, uint32_t slot_bytes, int depth,
-                                                                uint32_t ring_off, int* err) {
+                                                                uint32_t ring_off, int late, int* err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* smem = reinterpret_cast<float*>(smem_raw);
   const int lane = threadIdx.x & 31;
@@ -747,10 +747,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
   // dependent: barriers and the first `depth` tiles of every warp are requested while the
   // previous kernel is still draining; only then does it wait for that kernel's results and
   // rebuild its input while HBM is busy.
+  // (`late`: wide windows whose staged rows leave too little room run the rings over the
+  // prologue's scratch instead, so their first tiles can only be requested after the staging.)
   pdl_trigger();
   Ring R;
-  ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
-  __syncwarp();
+  if (!late) {
+    ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
+    __syncwarp();
+  }
   Cursor pc{gw, 0, 0, 0}, cc{gw, 0, 0, 0};
   if (pc.valid(J)) { pc.locate(J); cc = pc; }
   int pslot = 0;
@@ -766,7 +770,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
     pc.advance(J, GW);
     if (++pslot == depth) pslot = 0;
   };
-  for (int i = 0; i < depth && pc.valid(J); ++i) issue();
+  if (!late)
+    for (int i = 0; i < depth && pc.valid(J); ++i) issue();
   pdl_wait();  // everything below reads what earlier kernels wrote
   AddNormIn<M> pin;
   if (P.mode == PRO_ADDNORM) pin.load(P);
@@ -786,6 +791,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
   if (mask & (1 << ORN_A8)) stage_fill<ORN_A8>(lin, P.K, X[ORN_A8]);
   if (mask & (1 << ORN_BF16)) stage_fill<ORN_BF16>(lin, P.K, X[ORN_BF16]);
   __syncthreads();
+  if (late) {
+    ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
+    __syncwarp();
+    for (int i = 0; i < depth && pc.valid(J); ++i) issue();
+  }
 
   float acc[kMaxAcc], up[kMaxAcc];
   int slot = 0;
@@ -1414,16 +1424,24 @@ int launch_norm_gemv_mask(orn_ctx* ctx, cudaStream_t s, const Prologue& P, const
   for (int k = 0; k < 4; ++k)
     if (MASK & (1 << k)) fixed += stage_floats(k, M, P.K) * sizeof(float);
   fixed = (fixed + 127) & ~(size_t)127;
-  fixed += ((size_t)M * P.K + M * 33 + 64) * sizeof(float);  // the prologue's row and its reduction scratch
-  int depth;
+  const size_t stages = fixed;
+  const size_t scratch = ((size_t)M * P.K + M * 33 + 64) * sizeof(float);  // the prologue's row and its reduction scratch
+  fixed += scratch;
+  int depth, late = 0;
   uint32_t ring_off;
   size_t bytes;
   int rc = plan_smem(ctx, fixed, slot, kFusedThreads / 32, &depth, &ring_off, &bytes);
+  if (rc != ORN_OK || depth < 2) {
+    // too little room for two slots per warp beside the scratch: run the rings over it
+    rc = plan_smem(ctx, stages, slot, kFusedThreads / 32, &depth, &ring_off, &bytes);
+    if (bytes < stages + scratch + 256) bytes = stages + scratch + 256;
+    late = 1;
+  }
   if (rc != ORN_OK) return rc;
   rc = set_smem(ctx, k_norm_gemv<M, MASK, KC>, bytes);
   if (rc != ORN_OK) return rc;
   ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_norm_gemv<M, MASK, KC>, dim3(ctx->sm_count), dim3(kFusedThreads),
-                                           bytes, P, J, slot, depth, ring_off, ctx->dev_err));
+                                           bytes, P, J, slot, depth, ring_off, late, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_norm_gemv", M, J.job[0].lin.kind, J.job[0].lin.O, P.K));
 }
 

@@ -553,8 +553,8 @@ int forward_greedy_dev(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int
 int upload_ids(orn_model* m, const uint32_t* host_ids, int T) {
   ORN_CHECK_CUDA(m->ctx, cudaMemcpyAsync(m->ws.ids, host_ids, sizeof(uint32_t) * (size_t)T,
                                          cudaMemcpyHostToDevice, m->ctx->stream));
-  // the caller's buffer may be pageable and short-lived
-  ORN_CHECK_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+  // A copy from pageable memory is staged before the call returns and a pinned buffer of the
+  // caller outlives the generate call, which drains the stream before it returns: no wait here.
   return ORN_OK;
 }
 
@@ -681,7 +681,7 @@ int ar_body(orn_model* m, orn_cache* c) {
 // Run a step body eagerly the first time a shape is seen, capture it into a CUDA
 // graph the second time and replay it afterwards.  The host-side bookkeeping the
 // body does (positions, counters) is repeated by hand on a replay.
-int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar*/, int want, bool use_frspec) {
+int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar, 2 prefill rows*/, int want, bool use_frspec) {
   orn_ctx* ctx = m->ctx;
   cudaStream_t s = ctx->stream;
   const int key = kind * 64 + want * 2 + (use_frspec ? 1 : 0);
@@ -696,16 +696,22 @@ int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar*/, int want, b
     ORN_CHECK_CUDA(ctx, cudaGraphLaunch(g.exec, s));
     ctx->launches += g.launches;
     if (kind == 0) { c->h_mtp_pos += want; c->cap_T = n_rows; }
-    else { c->h_pos += 1; c->h_cur += 1; }
+    else if (kind == 1) { c->h_pos += 1; c->h_cur += 1; }
+    else { c->h_pos += n_rows; c->h_cur += 1; }
     return ORN_OK;
   }
+  auto body = [&]() {
+    if (kind == 0) return cycle_body(m, c, want, use_frspec);
+    if (kind == 1) return ar_body(m, c);
+    return forward_dev(m, c, m->ws.ids, n_rows, false, nullptr, nullptr);  // a window of prompt rows
+  };
   if (g.seen == 0 || no_graph || !use_fused()) {
     g.seen += 1;
-    return kind == 0 ? cycle_body(m, c, want, use_frspec) : ar_body(m, c);
+    return body();
   }
   const int64_t l0 = ctx->launches;
   ORN_CHECK_CUDA(ctx, cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-  int rc = kind == 0 ? cycle_body(m, c, want, use_frspec) : ar_body(m, c);
+  int rc = body();
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(s, &graph);
   if (rc != ORN_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
@@ -732,7 +738,7 @@ int prefill(orn_model* m, orn_cache* cc, const uint32_t* prompt, int n, int pref
     while (off < chunk) {
       int t = std::min(kMaxRows, chunk - off);
       CK(upload_ids(m, prompt + done + off, t));
-      CK(forward_dev(m, cc, m->ws.ids, t, false, nullptr, nullptr));
+      CK(run_step(m, cc, 2, t - 1, false));  // the same rows as forward_dev, replayed as a graph
       off += t;
     }
     CK(orn_sync(m->ctx));  // the reference drains the queue after each chunk (generate.rs:128-131)
