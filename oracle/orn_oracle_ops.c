@@ -94,8 +94,10 @@ void orc_q6k_dequantize(const uint8_t* w, const int8_t* scales, const uint16_t* 
  * cut into units of U consecutive storage elements (Q4_K: 16 bytes = 32
  * weights; Q6_K: 4 bytes of ql, 4 of ql+32, 4 of qh = 16 weights; affine-8:
  * 16 bytes = 16 weights; bf16: 8 weights).  Unit u belongs to lane u mod 32;
- * a lane folds its units in ascending order into one float; the 32 lane
- * values are folded by the xor-16,8,4,2,1 butterfly.  The activation row is
+ * a lane folds its units in ascending order into one float (inside a unit the
+ * products accumulate in two fma chains, even and odd elements, whose sum is
+ * the unit's dot product); the 32 lane values are folded by the xor-16,8,4,2,1
+ * butterfly.  The activation row is
  * bfloat16 widened to float. */
 
 /* kernels/q4k.metal:158-221: y += d * sum_sub sc*(sum q x) - dmin * sum_sub m*(sum x) */
@@ -105,13 +107,15 @@ static float q4k_unit(const uint8_t* qs_row, const uint8_t* sc_row, const uint16
   const uint8_t* b = qs_row + blk * 128 + 32 * g + 16 * h;
   const float* xl = x + blk * 256 + 64 * g + 16 * h;
   const float* xh = xl + 32;
-  float lo = 0.f, hi = 0.f, sxl = 0.f, sxh = 0.f;
+  /* products accumulate in two chains per sum, even and odd elements, added at the end */
+  float lo2[2] = {0.f, 0.f}, hi2[2] = {0.f, 0.f}, sxl = 0.f, sxh = 0.f;
   for (int i = 0; i < 16; ++i) {
-    lo = fmaf(xl[i], (float)(b[i] & 0xF), lo);
-    hi = fmaf(xh[i], (float)(b[i] >> 4), hi);
+    lo2[i & 1] = fmaf(xl[i], (float)(b[i] & 0xF), lo2[i & 1]);
+    hi2[i & 1] = fmaf(xh[i], (float)(b[i] >> 4), hi2[i & 1]);
     sxl = sxl + xl[i];
     sxh = sxh + xh[i];
   }
+  const float lo = lo2[0] + lo2[1], hi = hi2[0] + hi2[1];
   uint8_t s1, m1, s2, m2;
   orc_q4k_scale_min(2 * g, sc_row + blk * 12, &s1, &m1);
   orc_q4k_scale_min(2 * g + 1, sc_row + blk * 12, &s2, &m2);
@@ -133,17 +137,19 @@ static float q6k_unit(const uint8_t* w_row, const int8_t* sc_row, const uint16_t
   const uint8_t* qh = w_row + blk * 192 + 128 + 32 * half + l0;
   const int8_t* sc = sc_row + blk * 16 + 8 * half + l0 / 16;
   const float* xx = x + blk * 256 + 128 * half + l0;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  /* two chains per quadrant sum (even and odd elements), added at the end */
+  float p0[2] = {0.f, 0.f}, p1[2] = {0.f, 0.f}, p2[2] = {0.f, 0.f}, p3[2] = {0.f, 0.f};
   for (int i = 0; i < 4; ++i) {
     int q1 = (int)((ql[i] & 0xF) | ((qh[i] & 3) << 4)) - 32;
     int q2 = (int)((ql[i + 32] & 0xF) | (((qh[i] >> 2) & 3) << 4)) - 32;
     int q3 = (int)((ql[i] >> 4) | (((qh[i] >> 4) & 3) << 4)) - 32;
     int q4 = (int)((ql[i + 32] >> 4) | (((qh[i] >> 6) & 3) << 4)) - 32;
-    s0 = fmaf(xx[i], (float)q1, s0);
-    s1 = fmaf(xx[i + 32], (float)q2, s1);
-    s2 = fmaf(xx[i + 64], (float)q3, s2);
-    s3 = fmaf(xx[i + 96], (float)q4, s3);
+    p0[i & 1] = fmaf(xx[i], (float)q1, p0[i & 1]);
+    p1[i & 1] = fmaf(xx[i + 32], (float)q2, p1[i & 1]);
+    p2[i & 1] = fmaf(xx[i + 64], (float)q3, p2[i & 1]);
+    p3[i & 1] = fmaf(xx[i + 96], (float)q4, p3[i & 1]);
   }
+  const float s0 = p0[0] + p0[1], s1 = p1[0] + p1[1], s2 = p2[0] + p2[1], s3 = p3[0] + p3[1];
   float t = (float)sc[0] * s0;
   t = fmaf((float)sc[2], s1, t);
   t = fmaf((float)sc[4], s2, t);
@@ -157,11 +163,12 @@ static float a8_unit(const uint8_t* w_row, const bf16* s_row, const bf16* b_row,
                      const float* x, float acc) {
   const uint8_t* q = w_row + 16 * u;
   const float* xx = x + 16 * u;
-  float s1 = 0.f, s2 = 0.f;
+  float p[2] = {0.f, 0.f}, s2 = 0.f; /* products: even and odd chains, added at the end */
   for (int i = 0; i < 16; ++i) {
-    s1 = fmaf(xx[i], (float)q[i], s1);
+    p[i & 1] = fmaf(xx[i], (float)q[i], p[i & 1]);
     s2 = s2 + xx[i];
   }
+  const float s1 = p[0] + p[1];
   acc = fmaf(o_bf2f(s_row[u >> 2]), s1, acc);
   acc = fmaf(o_bf2f(b_row[u >> 2]), s2, acc);
   return acc;
@@ -169,8 +176,9 @@ static float a8_unit(const uint8_t* w_row, const bf16* s_row, const bf16* b_row,
 
 /* mlx gemv.h (bf16 weights, float accumulate) via src/ops/matmul.rs:334-437 */
 static float bf_unit(const bf16* w_row, int u, const float* x, float acc) {
-  for (int i = 0; i < 8; ++i) acc = fmaf(x[8 * u + i], o_bf2f(w_row[8 * u + i]), acc);
-  return acc;
+  float p[2] = {0.f, 0.f}; /* the unit's products: even and odd chains; their sum joins the lane's total */
+  for (int i = 0; i < 8; ++i) p[i & 1] = fmaf(x[8 * u + i], o_bf2f(w_row[8 * u + i]), p[i & 1]);
+  return acc + (p[0] + p[1]);
 }
 
 float orc_row_dot(const orc_lin* L, int e, int o, const float* x) {

@@ -138,15 +138,14 @@ template <> struct WU<ORN_A8> {
   }
   ORN_D static float fold(const W& w, const float* x, const float* sm, int, float acc) {
     const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
-    float s1 = 0.f;
+    const uint64_t nm = pk2(-8388608.0f, -8388608.0f);
+    uint64_t s2 = pk2(0.f, 0.f);  // (even chain, odd chain)
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      s1 = fmaf(x[4 * k + 0], byte_f<0>(qw[k]), s1);
-      s1 = fmaf(x[4 * k + 1], byte_f<1>(qw[k]), s1);
-      s1 = fmaf(x[4 * k + 2], byte_f<2>(qw[k]), s1);
-      s1 = fmaf(x[4 * k + 3], byte_f<3>(qw[k]), s1);
+      s2 = ffma2(pk2(x[4 * k + 0], x[4 * k + 1]), byte2_f<0>(qw[k], nm), s2);
+      s2 = ffma2(pk2(x[4 * k + 2], x[4 * k + 3]), byte2_f<2>(qw[k], nm), s2);
     }
-    acc = fmaf(bf_lo(w.sb), s1, acc);
+    acc = fmaf(bf_lo(w.sb), pk2_sum(s2), acc);
     acc = fmaf(bf_hi(w.sb), sm[0], acc);
     return acc;
   }
@@ -162,19 +161,17 @@ template <> struct WU<ORN_Q4K> {
   ORN_D static float fold(const W& w, const float* x, const float* sm, int u, float acc) {
     const int g = (u & 7) >> 1;
     const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
-    float lo = 0.f, hi = 0.f;
+    const uint64_t nm = pk2(-8388608.0f, -8388608.0f);
+    uint64_t lo2 = pk2(0.f, 0.f), hi2 = pk2(0.f, 0.f);  // (even chain, odd chain) of the two sub-blocks
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const uint32_t l4 = qw[k] & 0x0F0F0F0Fu, h4 = (qw[k] >> 4) & 0x0F0F0F0Fu;
-      lo = fmaf(x[4 * k + 0], byte_f<0>(l4), lo);
-      lo = fmaf(x[4 * k + 1], byte_f<1>(l4), lo);
-      lo = fmaf(x[4 * k + 2], byte_f<2>(l4), lo);
-      lo = fmaf(x[4 * k + 3], byte_f<3>(l4), lo);
-      hi = fmaf(x[16 + 4 * k + 0], byte_f<0>(h4), hi);
-      hi = fmaf(x[16 + 4 * k + 1], byte_f<1>(h4), hi);
-      hi = fmaf(x[16 + 4 * k + 2], byte_f<2>(h4), hi);
-      hi = fmaf(x[16 + 4 * k + 3], byte_f<3>(h4), hi);
+      lo2 = ffma2(pk2(x[4 * k + 0], x[4 * k + 1]), byte2_f<0>(l4, nm), lo2);
+      lo2 = ffma2(pk2(x[4 * k + 2], x[4 * k + 3]), byte2_f<2>(l4, nm), lo2);
+      hi2 = ffma2(pk2(x[16 + 4 * k + 0], x[16 + 4 * k + 1]), byte2_f<0>(h4, nm), hi2);
+      hi2 = ffma2(pk2(x[16 + 4 * k + 2], x[16 + 4 * k + 3]), byte2_f<2>(h4, nm), hi2);
     }
+    const float lo = pk2_sum(lo2), hi = pk2_sum(hi2);
     const float d = h2f((uint16_t)(w.meta.x & 0xffff)), dmin = h2f((uint16_t)(w.meta.x >> 16));
     float s1, m1, s2, m2;
     q4k_scale_min(2 * g, w.meta.y, w.meta.z, w.meta.w, &s1, &m1);
@@ -209,15 +206,17 @@ template <> struct WU<ORN_Q6K> {
     const uint32_t q2 = (w.qb & 0x0F0F0F0Fu) | ((w.qh & 0x0C0C0C0Cu) << 2);
     const uint32_t q3 = ((w.qa >> 4) & 0x0F0F0F0Fu) | (w.qh & 0x30303030u);
     const uint32_t q4 = ((w.qb >> 4) & 0x0F0F0F0Fu) | ((w.qh & 0xC0C0C0C0u) >> 2);
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    s0 = fmaf(x[0], byte_m32_f<0>(q1), s0); s0 = fmaf(x[1], byte_m32_f<1>(q1), s0);
-    s0 = fmaf(x[2], byte_m32_f<2>(q1), s0); s0 = fmaf(x[3], byte_m32_f<3>(q1), s0);
-    s1 = fmaf(x[4], byte_m32_f<0>(q2), s1); s1 = fmaf(x[5], byte_m32_f<1>(q2), s1);
-    s1 = fmaf(x[6], byte_m32_f<2>(q2), s1); s1 = fmaf(x[7], byte_m32_f<3>(q2), s1);
-    s2 = fmaf(x[8], byte_m32_f<0>(q3), s2); s2 = fmaf(x[9], byte_m32_f<1>(q3), s2);
-    s2 = fmaf(x[10], byte_m32_f<2>(q3), s2); s2 = fmaf(x[11], byte_m32_f<3>(q3), s2);
-    s3 = fmaf(x[12], byte_m32_f<0>(q4), s3); s3 = fmaf(x[13], byte_m32_f<1>(q4), s3);
-    s3 = fmaf(x[14], byte_m32_f<2>(q4), s3); s3 = fmaf(x[15], byte_m32_f<3>(q4), s3);
+    const uint64_t nm = pk2(-8388640.0f, -8388640.0f);  // -(2^23 + 32)
+    const uint64_t z = pk2(0.f, 0.f);
+    uint64_t p0 = ffma2(pk2(x[0], x[1]), byte2_f<0>(q1, nm), z);
+    p0 = ffma2(pk2(x[2], x[3]), byte2_f<2>(q1, nm), p0);
+    uint64_t p1 = ffma2(pk2(x[4], x[5]), byte2_f<0>(q2, nm), z);
+    p1 = ffma2(pk2(x[6], x[7]), byte2_f<2>(q2, nm), p1);
+    uint64_t p2 = ffma2(pk2(x[8], x[9]), byte2_f<0>(q3, nm), z);
+    p2 = ffma2(pk2(x[10], x[11]), byte2_f<2>(q3, nm), p2);
+    uint64_t p3 = ffma2(pk2(x[12], x[13]), byte2_f<0>(q4, nm), z);
+    p3 = ffma2(pk2(x[14], x[15]), byte2_f<2>(q4, nm), p3);
+    const float s0 = pk2_sum(p0), s1 = pk2_sum(p1), s2 = pk2_sum(p2), s3 = pk2_sum(p3);
     const float c0 = (float)(int8_t)(w.sc4 & 0xff), c1 = (float)(int8_t)((w.sc4 >> 8) & 0xff);
     const float c2 = (float)(int8_t)((w.sc4 >> 16) & 0xff), c3 = (float)(int8_t)(w.sc4 >> 24);
     float t = c0 * s0;
@@ -236,9 +235,10 @@ template <> struct WU<ORN_BF16> {
   ORN_D static float fold(const W& w, const float* x, const float*, int, float acc) {
     float f[8];
     widen8(w.q, f);
+    uint64_t s2 = pk2(0.f, 0.f);  // the unit's (even chain, odd chain); their sum joins the lane's total
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc = fmaf(x[i], f[i], acc);
-    return acc;
+    for (int i = 0; i < 8; i += 2) s2 = ffma2(pk2(x[i], x[i + 1]), pk2(f[i], f[i + 1]), s2);
+    return acc + pk2_sum(s2);
   }
 };
 

@@ -14,7 +14,9 @@
 // belongs to lane u mod 32, so consecutive lanes read consecutive 16-byte
 // pieces of the row (fully coalesced 128-bit loads).  Dequantisation happens in
 // registers; a lane folds its units in ascending order into one float per
-// (row, activation row); lanes are folded by the xor-16..1 shuffle butterfly.
+// (row, activation row), the products of a unit in two fma chains (even and odd
+// elements: the two halves of a packed fma.rn.f32x2 in the fused kernels);
+// lanes are folded by the xor-16..1 shuffle butterfly.
 // The M activation rows of a verify window share each weight load and each get
 // exactly the arithmetic a single row gets, so a row's bits do not depend on M
 // (the property src/ops/invariant.rs:78-116 asks for).
@@ -59,19 +61,21 @@ struct Fmt<ORN_Q4K> {
   ORN_D static float fold(const W& w, const X& x, int u, float acc) {
     int g = (u & 7) >> 1;
     const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
-    float lo = 0.f, hi = 0.f;
+    // two chains per sum (even / odd elements), added at the end
+    float le = 0.f, lod = 0.f, he = 0.f, hod = 0.f;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       uint32_t l4 = qw[k] & 0x0F0F0F0Fu, h4 = (qw[k] >> 4) & 0x0F0F0F0Fu;
-      lo = fmaf(x.lo[4 * k + 0], byte_f<0>(l4), lo);
-      lo = fmaf(x.lo[4 * k + 1], byte_f<1>(l4), lo);
-      lo = fmaf(x.lo[4 * k + 2], byte_f<2>(l4), lo);
-      lo = fmaf(x.lo[4 * k + 3], byte_f<3>(l4), lo);
-      hi = fmaf(x.hi[4 * k + 0], byte_f<0>(h4), hi);
-      hi = fmaf(x.hi[4 * k + 1], byte_f<1>(h4), hi);
-      hi = fmaf(x.hi[4 * k + 2], byte_f<2>(h4), hi);
-      hi = fmaf(x.hi[4 * k + 3], byte_f<3>(h4), hi);
+      le = fmaf(x.lo[4 * k + 0], byte_f<0>(l4), le);
+      lod = fmaf(x.lo[4 * k + 1], byte_f<1>(l4), lod);
+      le = fmaf(x.lo[4 * k + 2], byte_f<2>(l4), le);
+      lod = fmaf(x.lo[4 * k + 3], byte_f<3>(l4), lod);
+      he = fmaf(x.hi[4 * k + 0], byte_f<0>(h4), he);
+      hod = fmaf(x.hi[4 * k + 1], byte_f<1>(h4), hod);
+      he = fmaf(x.hi[4 * k + 2], byte_f<2>(h4), he);
+      hod = fmaf(x.hi[4 * k + 3], byte_f<3>(h4), hod);
     }
+    const float lo = le + lod, hi = he + hod;
     float d = h2f((uint16_t)(w.meta.x & 0xffff)), dmin = h2f((uint16_t)(w.meta.x >> 16));
     float s1, m1, s2, m2;
     q4k_scale_min(2 * g, w.meta.y, w.meta.z, w.meta.w, &s1, &m1);
@@ -122,15 +126,16 @@ struct Fmt<ORN_Q6K> {
     uint32_t q2 = (w.qb & 0x0F0F0F0Fu) | ((w.qh & 0x0C0C0C0Cu) << 2);
     uint32_t q3 = ((w.qa >> 4) & 0x0F0F0F0Fu) | (w.qh & 0x30303030u);
     uint32_t q4 = ((w.qb >> 4) & 0x0F0F0F0Fu) | ((w.qh & 0xC0C0C0C0u) >> 2);
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    s0 = fmaf(x.v[0][0], byte_m32_f<0>(q1), s0); s0 = fmaf(x.v[0][1], byte_m32_f<1>(q1), s0);
-    s0 = fmaf(x.v[0][2], byte_m32_f<2>(q1), s0); s0 = fmaf(x.v[0][3], byte_m32_f<3>(q1), s0);
-    s1 = fmaf(x.v[1][0], byte_m32_f<0>(q2), s1); s1 = fmaf(x.v[1][1], byte_m32_f<1>(q2), s1);
-    s1 = fmaf(x.v[1][2], byte_m32_f<2>(q2), s1); s1 = fmaf(x.v[1][3], byte_m32_f<3>(q2), s1);
-    s2 = fmaf(x.v[2][0], byte_m32_f<0>(q3), s2); s2 = fmaf(x.v[2][1], byte_m32_f<1>(q3), s2);
-    s2 = fmaf(x.v[2][2], byte_m32_f<2>(q3), s2); s2 = fmaf(x.v[2][3], byte_m32_f<3>(q3), s2);
-    s3 = fmaf(x.v[3][0], byte_m32_f<0>(q4), s3); s3 = fmaf(x.v[3][1], byte_m32_f<1>(q4), s3);
-    s3 = fmaf(x.v[3][2], byte_m32_f<2>(q4), s3); s3 = fmaf(x.v[3][3], byte_m32_f<3>(q4), s3);
+    // two chains per quadrant sum (even / odd elements), added at the end
+    float e0 = fmaf(x.v[0][0], byte_m32_f<0>(q1), 0.f), o0 = fmaf(x.v[0][1], byte_m32_f<1>(q1), 0.f);
+    e0 = fmaf(x.v[0][2], byte_m32_f<2>(q1), e0); o0 = fmaf(x.v[0][3], byte_m32_f<3>(q1), o0);
+    float e1 = fmaf(x.v[1][0], byte_m32_f<0>(q2), 0.f), o1 = fmaf(x.v[1][1], byte_m32_f<1>(q2), 0.f);
+    e1 = fmaf(x.v[1][2], byte_m32_f<2>(q2), e1); o1 = fmaf(x.v[1][3], byte_m32_f<3>(q2), o1);
+    float e2 = fmaf(x.v[2][0], byte_m32_f<0>(q3), 0.f), o2 = fmaf(x.v[2][1], byte_m32_f<1>(q3), 0.f);
+    e2 = fmaf(x.v[2][2], byte_m32_f<2>(q3), e2); o2 = fmaf(x.v[2][3], byte_m32_f<3>(q3), o2);
+    float e3 = fmaf(x.v[3][0], byte_m32_f<0>(q4), 0.f), o3 = fmaf(x.v[3][1], byte_m32_f<1>(q4), 0.f);
+    e3 = fmaf(x.v[3][2], byte_m32_f<2>(q4), e3); o3 = fmaf(x.v[3][3], byte_m32_f<3>(q4), o3);
+    const float s0 = e0 + o0, s1 = e1 + o1, s2 = e2 + o2, s3 = e3 + o3;
     float c0 = (float)(int8_t)(w.sc4 & 0xff), c1 = (float)(int8_t)((w.sc4 >> 8) & 0xff);
     float c2 = (float)(int8_t)((w.sc4 >> 16) & 0xff), c3 = (float)(int8_t)(w.sc4 >> 24);
     float t = c0 * s0;
@@ -161,14 +166,15 @@ struct Fmt<ORN_A8> {
   }
   ORN_D static float fold(const W& w, const X& x, int, float acc) {
     const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
-    float s1 = 0.f;
+    float se = 0.f, so = 0.f;  // even / odd chains, added at the end
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      s1 = fmaf(x.v[4 * k + 0], byte_f<0>(qw[k]), s1);
-      s1 = fmaf(x.v[4 * k + 1], byte_f<1>(qw[k]), s1);
-      s1 = fmaf(x.v[4 * k + 2], byte_f<2>(qw[k]), s1);
-      s1 = fmaf(x.v[4 * k + 3], byte_f<3>(qw[k]), s1);
+      se = fmaf(x.v[4 * k + 0], byte_f<0>(qw[k]), se);
+      so = fmaf(x.v[4 * k + 1], byte_f<1>(qw[k]), so);
+      se = fmaf(x.v[4 * k + 2], byte_f<2>(qw[k]), se);
+      so = fmaf(x.v[4 * k + 3], byte_f<3>(qw[k]), so);
     }
+    const float s1 = se + so;
     acc = fmaf(bf_lo(w.sb), s1, acc);
     acc = fmaf(bf_hi(w.sb), x.sum, acc);
     return acc;
@@ -187,9 +193,10 @@ struct Fmt<ORN_BF16> {
   ORN_D static float fold(const W& w, const X& x, int, float acc) {
     float f[8];
     widen8(w.q, f);
+    float se = 0.f, so = 0.f;  // the unit's even / odd chains; their sum joins the lane's total
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc = fmaf(x.v[i], f[i], acc);
-    return acc;
+    for (int i = 0; i < 8; i += 2) { se = fmaf(x.v[i], f[i], se); so = fmaf(x.v[i + 1], f[i + 1], so); }
+    return acc + (se + so);
   }
 };
 

@@ -14,6 +14,38 @@ template <int I>
 ORN_D float byte_m32_f(uint32_t w) {
   return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 + I)) - 8388640.0f;
 }
+// ---- packed pairs of floats: fma.rn.f32x2 / add.rn.f32x2 do two IEEE operations per issue slot.
+// A unit's products accumulate in two chains (even and odd elements), which is what one packed
+// fma over (x[2i], x[2i+1]) x (q[2i], q[2i+1]) + (even, odd) computes.
+ORN_D uint64_t pk2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+ORN_D float pk2_sum(uint64_t v) {  // even chain + odd chain
+  float a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+  return a + b;
+}
+ORN_D uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+ORN_D uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// float(byte I of w), float(byte I+1 of w), each minus `bias` (given as the packed pair of
+// -(2^23 + bias)): exact
+template <int I>
+ORN_D uint64_t byte2_f(uint32_t w, uint64_t neg_magic) {
+  const float f0 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 + I));
+  const float f1 = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 + I + 1));
+  return fadd2(pk2(f0, f1), neg_magic);
+}
+
 ORN_D float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
 ORN_D float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
