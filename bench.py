@@ -131,8 +131,12 @@ def cpu_arm(pkg, ctx, max_seconds=15.0):
     sizes) plus the MTP head and the full lm_head, MTP depth-1 cycles with the
     same forced-draft rule; the per-cycle layer time is scaled by 10 to the 40
     layers."""
+    threads = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(threads)  # torchrun sets it to 1 for its workers
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import orn_oracle as orc
+    orc.lib().orc_set_threads(threads)
+    threads = orc.lib().orc_get_threads()
 
     cfg4 = pkg.qwen35_config(max_ctx=128, n_layers=4)
     gm = pkg.TextModel(ctx, cfg4)
@@ -140,7 +144,6 @@ def cpu_arm(pkg, ctx, max_seconds=15.0):
     gm.make_cache().free()  # resolves the weight table
     om = orc.export_gpu_model(gm)
     gm.free()
-    threads = os.cpu_count() or 1
     rng = np.random.default_rng(SEED)
     ids = rng.integers(0, cfg4.vocab, 2).astype(np.uint32)
     cache = om.new_cache()

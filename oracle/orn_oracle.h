@@ -135,6 +135,10 @@ int orc_generate_mtp(const orc_model* m, orc_cache* c, const uint32_t* prompt, i
                      int depth, int max_tokens, int policy, int use_frspec,
                      const orc_force* force, uint32_t* out, orc_mtp_stats* stats);
 
+/* OpenMP threads used by the row loops */
+void orc_set_threads(int n);
+int orc_get_threads(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -675,3 +675,13 @@ uint32_t orc_greedy_token(const bf16* logits, int V, int normalize) {
   }
   return bi;
 }
+
+/* number of OpenMP threads of the row loops (a launcher may have set OMP_NUM_THREADS=1) */
+#ifdef _OPENMP
+#include <omp.h>
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int orc_get_threads(void) { return omp_get_max_threads(); }
+#else
+void orc_set_threads(int n) { (void)n; }
+int orc_get_threads(void) { return 1; }
+#endif
