@@ -115,6 +115,35 @@ __device__ __noinline__ void stage_fill(const float* lin, int stride, const XSta
     }
   }
 }
+// The same by the threads tid of nthreads only (a subset of the CTA may stage while other warps
+// do something else); no sync inside.
+template <int KIND>
+__device__ __noinline__ void stage_fill_part(const float* lin, int stride, const XStage& X, int tid, int nthreads) {
+  constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
+  const int padded = X.S * 32;
+#pragma unroll 1
+  for (int m = 0; m < X.rows; ++m) {
+    const float* src = lin + (size_t)m * stride;
+    float4* dst = reinterpret_cast<float4*>(X.xs) + (size_t)m * padded * P;
+#pragma unroll 1
+    for (int u = tid; u < padded; u += nthreads) {
+      const int lane = u & 31, s = u >> 5;
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (u < X.units) v = *reinterpret_cast<const float4*>(src + src_index<KIND>(u, p));
+        dst[(s * P + p) * 32 + lane] = v;
+        if (NS == 1 || (NS == 2 && p < 4)) { s0 = s0 + v.x; s0 = s0 + v.y; s0 = s0 + v.z; s0 = s0 + v.w; }
+        if (NS == 2 && p >= 4) { s1 = s1 + v.x; s1 = s1 + v.y; s1 = s1 + v.z; s1 = s1 + v.w; }
+      }
+      if (u < X.units) {
+        if (NS == 1) X.sums[(size_t)m * X.units + u] = s0;
+        if (NS == 2) { X.sums[((size_t)m * X.units + u) * 2] = s0; X.sums[((size_t)m * X.units + u) * 2 + 1] = s1; }
+      }
+    }
+  }
+}
 ORN_D void stage_fill_kind(int kind, const float* lin, int stride, const XStage& X) {
   switch (kind) {
     case ORN_A8: stage_fill<ORN_A8>(lin, stride, X); break;
@@ -925,12 +954,18 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32
   Ring R;
   ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
   pdl_wait();  // the routing (and so the first weight tile) depends on the previous kernel's logits
+  // the first M warps route their token while the other warps stage x: one barrier for both
   if (warp < M)
     warp_softmax_topk(P.logits + (size_t)warp * P.E, P.E, P.k, probs + (size_t)warp * P.E, red + warp * 32,
                       inds + warp * P.k, scores + warp * P.k, lane);
-  for (int i = threadIdx.x * 4; i < M * P.H; i += blockDim.x * 4) {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.x + i));
-    *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+  else {
+    const int tid = threadIdx.x - 32 * M, nt = blockDim.x - 32 * M;
+    for (int i = tid * 4; i < M * P.H; i += nt * 4) {
+      const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.x + i));
+      *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nt) : "memory");  // the staging warps only
+    stage_fill_part<KIND>(lin, P.H, X, tid, nt);
   }
   __syncthreads();
   // task g = (routed row mj, tile t of the expert's I output rows): two slots, gate rows then up rows
@@ -956,8 +991,6 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32
       P.inds[i] = inds[i];
       P.scores[i] = f2bf(scores[i]);
     }
-  stage_fill<KIND>(lin, P.H, X);
-  __syncthreads();
   float g[RT], u[RT];
   int slot = 0;
   uint32_t parity = 0;
@@ -1047,6 +1080,15 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, ui
     if (++pslot == depth) pslot = 0;
   };
   for (int i = 0; i < depth && pg < total; ++i) issue();
+  if (threadIdx.x < rows) {  // thread (m, j): the normalised score of routed expert j of token m
+    const int m = threadIdx.x / P.k, j = threadIdx.x - m * P.k;
+    float denom = 0.f;
+    if (P.normalize)
+      for (int jj = 0; jj < P.k; ++jj) denom = bfr(bf2f(P.scores[m * P.k + jj]) + denom);
+    const float sc = bf2f(P.scores[m * P.k + j]);
+    wts[threadIdx.x] = P.normalize ? bfr(sc / denom) : sc;
+    if (j == 0) gsig[m] = sigmoid_bf_call(bf2f(P.gs[m]));
+  }
   for (int i = threadIdx.x * 4; i < rows * P.I; i += blockDim.x * 4) {
     const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.act + i));
     *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
@@ -1054,17 +1096,6 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, ui
   for (int i = threadIdx.x * 4; i < M * P.SI; i += blockDim.x * 4) {
     const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.sact + i));
     *reinterpret_cast<float4*>(lin2 + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
-  }
-  if (threadIdx.x < M) {
-    const int m = threadIdx.x;
-    float denom = 0.f;
-    if (P.normalize)
-      for (int j = 0; j < P.k; ++j) denom = bfr(bf2f(P.scores[m * P.k + j]) + denom);
-    for (int j = 0; j < P.k; ++j) {
-      const float sc = bf2f(P.scores[m * P.k + j]);
-      wts[m * P.k + j] = P.normalize ? bfr(sc / denom) : sc;
-    }
-    gsig[m] = sigmoid_bf_call(bf2f(P.gs[m]));
   }
   __syncthreads();
   stage_fill<KIND>(lin, P.I, X);
