@@ -903,28 +903,32 @@ __device__ __noinline__ void warp_softmax_topk(const bf16_t* logits, int n, int 
   __syncwarp();
   for (int i = lane; i < n; i += 32) probs[i] = bfr(probs[i] * inv);
   __syncwarp();
+  // k rounds of argmax: largest value, ties to the larger index.  The probabilities are
+  // non-negative bfloat16 values, so their float bits order like the values and have 16 free low
+  // bits: (bits | index) + 1 is a key whose unsigned maximum is exactly that rule, and one
+  // hardware warp reduction per round finds it (0 marks entries that are absent, taken, or NaN;
+  // with nothing left the round yields index 0, as the comparison form does).
   constexpr int kMaxPerLane = 16;
-  float v[kMaxPerLane];
-  int held = 0;
+  uint32_t key[kMaxPerLane];
 #pragma unroll
   for (int s = 0; s < kMaxPerLane; ++s) {
     const int i = lane + 32 * s;
-    v[s] = -INFINITY;
-    if (i < n) { v[s] = probs[i]; held = s + 1; }
+    key[s] = 0;
+    if (i < n) {
+      const float p = probs[i];
+      const uint32_t bits = __float_as_uint(p);
+      if (p == p && (int)bits >= 0) key[s] = (bits | (uint32_t)i) + 1u;
+    }
   }
   for (int r = 0; r < k; ++r) {
-    float best = -INFINITY;
-    uint32_t besti = 0;
+    uint32_t best = 0;
 #pragma unroll
-    for (int s = 0; s < kMaxPerLane; ++s) {
-      const uint32_t i = lane + 32 * s;
-      if (s < held && (v[s] > best || (v[s] == best && i > besti))) { best = v[s]; besti = i; }
-    }
-    const float m = warp_max(best);
-    const uint32_t mi = warp_max_u32(best == m ? besti + 1 : 0u) - 1;
+    for (int s = 0; s < kMaxPerLane; ++s) best = key[s] > best ? key[s] : best;
+    const uint32_t m = __reduce_max_sync(0xffffffffu, best);
+    const uint32_t mi = m ? ((m - 1u) & 0xffffu) : 0u;
 #pragma unroll
     for (int s = 0; s < kMaxPerLane; ++s)
-      if ((mi & 31) == (uint32_t)lane && (mi >> 5) == (uint32_t)s) v[s] = -INFINITY;
+      if (m != 0 && key[s] == m) key[s] = 0;
     if (lane == 0) {
       inds[k - 1 - r] = mi;
       scores[k - 1 - r] = probs[mi];
