@@ -92,7 +92,9 @@ int32_t orn_ctx_create(int32_t device, orn_ctx** out) {
     return ORN_ERR_ALLOC;
   }
   const char* np = getenv("ORN_NO_PDL");
-  if (np && np[0] == '1') c->pdl = false;
+  const char* pg = getenv("ORN_PDL_MASK");
+  if (pg) c->pdl_mask = atoi(pg);
+  if (np && np[0] == '1') c->pdl_mask = 0;
   const char* kt = getenv("ORN_KTIME");
   if (kt && kt[0] == '1') c->kt = new orn_ktime();
   *out = c;

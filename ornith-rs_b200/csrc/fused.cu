@@ -1475,7 +1475,7 @@ int launch_norm_gemv_mask(orn_ctx* ctx, cudaStream_t s, const Prologue& P, const
   if (rc != ORN_OK) return rc;
   rc = set_smem(ctx, k_norm_gemv<M, MASK, KC>, bytes);
   if (rc != ORN_OK) return rc;
-  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_norm_gemv<M, MASK, KC>, dim3(ctx->sm_count), dim3(kFusedThreads),
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 0, k_norm_gemv<M, MASK, KC>, dim3(ctx->sm_count), dim3(kFusedThreads),
                                            bytes, P, J, slot, depth, ring_off, late, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_norm_gemv", M, J.job[0].lin.kind, J.job[0].lin.O, P.K));
 }
@@ -1536,7 +1536,7 @@ int launch_moe_up_k(orn_ctx* ctx, cudaStream_t s, const MoeUpParams& P) {
   if (rc != ORN_OK) return rc;
   rc = set_smem(ctx, k_moe_up<KIND, KC>, bytes);
   if (rc != ORN_OK) return rc;
-  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_moe_up<KIND, KC>, dim3(ctx->sm_count), dim3(kMoeThreads), bytes,
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 1, k_moe_up<KIND, KC>, dim3(ctx->sm_count), dim3(kMoeThreads), bytes,
                                            P, slot, depth, ring_off, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_moe_up", M, KIND, P.I, P.H));
 }
@@ -1557,7 +1557,7 @@ int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
   if (rc != ORN_OK) return rc;
   rc = set_smem(ctx, k_moe_down<KIND, KC>, bytes);
   if (rc != ORN_OK) return rc;
-  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_moe_down<KIND, KC>, dim3(ctx->sm_count), dim3(kMoeThreads), bytes,
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 2, k_moe_down<KIND, KC>, dim3(ctx->sm_count), dim3(kMoeThreads), bytes,
                                            P, slot, depth, ring_off, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_moe_down", M, KIND, P.H, P.I));
 }
@@ -1647,7 +1647,7 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
   p.k_scale = bfr(inv_scale);
   p.eps = eps;
   dim3 grid(128 / kGdnRows, Hv);
-  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_gdn, grid, dim3(kGdnRows * 4), 0, p));
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn, grid, dim3(kGdnRows * 4), 0, p));
   return orn_launch_check(ctx, "k_gdn");
 }
 
@@ -1662,6 +1662,6 @@ int f_attn(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, const bf16_t* k, cons
   p.scale = 1.0f / sqrtf((float)hd);
   p.eps = eps;
   dim3 grid(Hq, T);
-  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, k_attn, grid, dim3(1024), 0, p));
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 4, k_attn, grid, dim3(1024), 0, p));
   return orn_launch_check(ctx, "k_attn");
 }

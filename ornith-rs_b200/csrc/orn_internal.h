@@ -20,7 +20,11 @@ struct orn_ctx {
   cudaEvent_t t0 = nullptr, t1 = nullptr;  // orn_timer_start / orn_timer_stop
   int* dev_err = nullptr;  // set by a kernel whose bounded wait ran out
   struct orn_ktime* kt = nullptr;  // per-kernel device times when ORN_KTIME=1 (eager launches only)
-  bool pdl = true;  // launch the fused kernels as programmatic dependents (ORN_NO_PDL=1 turns it off)
+  // Kernel classes launched as programmatic dependents (bit 0 norm + mat-vec, 1 expert up, 2 expert
+  // down, 3 gated-delta, 4 attention).  Measured on the replayed decode graph: bit 0 alone +3 %,
+  // adding the expert kernels nothing or worse, the gated-delta kernel -8 %.  ORN_PDL_MASK overrides,
+  // ORN_NO_PDL=1 clears it.
+  int pdl_mask = 1;
 };
 
 // Records an event after the launch just made and attributes the device time
@@ -107,8 +111,8 @@ static inline int orn_launch_check(orn_ctx* ctx, const char* what) {
 // still reads.  Without the attribute the same kernel runs as an ordinary launch (the wait
 // returns immediately).
 template <typename... KArgs, typename... Args>
-inline cudaError_t orn_launch_dependent(orn_ctx* ctx, cudaStream_t s, void (*kern)(KArgs...), dim3 grid, dim3 block,
-                                        size_t smem, Args... args) {
+inline cudaError_t orn_launch_dependent(orn_ctx* ctx, cudaStream_t s, int cls, void (*kern)(KArgs...), dim3 grid,
+                                        dim3 block, size_t smem, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -116,12 +120,7 @@ inline cudaError_t orn_launch_dependent(orn_ctx* ctx, cudaStream_t s, void (*ker
   cfg.stream = s;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  // In a captured graph plain kernel-to-kernel edges replay faster than programmatic ones
-  // (measured: the decode cycle's graph is 7 % slower with them), so the attribute is used for
-  // eager launches only.
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  cudaStreamIsCapturing(s, &cap);
-  at[0].val.programmaticStreamSerializationAllowed = (ctx->pdl && cap == cudaStreamCaptureStatusNone) ? 1 : 0;
+  at[0].val.programmaticStreamSerializationAllowed = (ctx->pdl_mask >> cls) & 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
