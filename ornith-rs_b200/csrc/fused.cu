@@ -799,11 +799,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
     pc.advance(J, GW);
     if (++pslot == depth) pslot = 0;
   };
+  int primed = 0;
   if (!late)
-    for (int i = 0; i < depth && pc.valid(J); ++i) issue();
+    for (; primed < 1 && pc.valid(J); ++primed) issue();  // one tile per warp ahead of the wait ...
   pdl_wait();  // everything below reads what earlier kernels wrote
   AddNormIn<M> pin;
   if (P.mode == PRO_ADDNORM) pin.load(P);
+  if (!late)
+    for (; primed < depth && pc.valid(J); ++primed) issue();  // ... the rest behind the prologue's own loads
 
   // stages, then the prologue's scratch
   float* next = smem;
