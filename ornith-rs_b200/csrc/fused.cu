@@ -1068,6 +1068,15 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, ui
   Ring R;
   ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
   pdl_wait();
+  // first batch of the routed activations into registers, so that their latency overlaps the
+  // routing table's and the first weight requests
+  constexpr int kPre = 4;
+  uint2 pre[kPre];
+#pragma unroll
+  for (int j = 0; j < kPre; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < rows * P.I) pre[j] = __ldg(reinterpret_cast<const uint2*>(P.act + i));
+  }
   if (threadIdx.x < rows) inds[threadIdx.x] = P.inds[threadIdx.x];
   __syncthreads();
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), GW = gridDim.x * (blockDim.x >> 5);
@@ -1096,7 +1105,12 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, ui
     wts[threadIdx.x] = P.normalize ? bfr(sc / denom) : sc;
     if (j == 0) gsig[m] = sigmoid_bf_call(bf2f(P.gs[m]));
   }
-  for (int i = threadIdx.x * 4; i < rows * P.I; i += blockDim.x * 4) {
+#pragma unroll
+  for (int j = 0; j < kPre; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < rows * P.I) *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(pre[j].x), bf_hi(pre[j].x), bf_lo(pre[j].y), bf_hi(pre[j].y));
+  }
+  for (int i = (threadIdx.x + kPre * blockDim.x) * 4; i < rows * P.I; i += blockDim.x * 4) {
     const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.act + i));
     *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
   }
