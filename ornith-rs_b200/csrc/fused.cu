@@ -329,6 +329,13 @@ __host__ __device__ constexpr int moe_rows(int kind, int kc) {
          : kind == ORN_Q6K ? (kc == 2 ? 2 : 4)
                            : (kc == 0 ? 8 : kc == 1 ? 2 : 1);
 }
+// rows of a tile in the expert up kernel: half of them gate rows, half their up rows
+__host__ __device__ constexpr int up_rows(int kind, int kc) {
+  return kind == ORN_A8    ? (kc <= 1 ? 4 : 2)
+         : kind == ORN_Q4K ? (kc <= 1 ? 8 : 4)
+         : kind == ORN_Q6K ? (kc <= 1 ? 4 : 2)
+                           : 2;
+}
 __host__ __device__ constexpr int pad_m(int M) { return M == 3 ? 4 : M; }
 
 struct Ring {
@@ -345,6 +352,14 @@ ORN_D void ring_fill(const Ring& R, int slot, const uint8_t* src, uint32_t bytes
   const uint32_t bar = R.bar0 + 8 * slot;
   mbar_expect_tx(bar, bytes);
   bulk_g2s(R.buf0 + slot * R.slot_bytes, src, bytes, bar);
+}
+// lane 0: two bulk copies into one slot (a gate tile at offset 0 and its up tile at `off1`)
+ORN_D void ring_fill2(const Ring& R, int slot, const uint8_t* src0, const uint8_t* src1, uint32_t bytes, uint32_t off1) {
+  const uint32_t bar = R.bar0 + 8 * slot;
+  const uint32_t dst = R.buf0 + slot * R.slot_bytes;
+  mbar_expect_tx(bar, 2 * bytes);
+  bulk_g2s(dst, src0, bytes, bar);
+  bulk_g2s(dst + off1, src1, bytes, bar);
 }
 // all lanes: wait for a slot; false after the bounded wait ran out
 ORN_D bool ring_wait(const Ring& R, int slot, uint32_t parity) {
@@ -717,37 +732,38 @@ ORN_D void tile_dot_masked(const uint8_t* buf, const LinDev& L, const XStage* X,
 
 __device__ __noinline__ float swiglu_bf_call(float g, float u) { return orn_swiglu_bf(g, u); }
 
-// butterfly + store of a finished tile: R x M sums (and the paired "up" sums for SwiGLU)
+// butterfly + store of a finished tile of R x M sums.  A SwiGLU tile holds R/2 gate rows followed
+// by their R/2 up rows: after the butterfly the up sums sit 16 lanes above the gate sums.
 template <int M, int R>
-ORN_D void tile_store(float* acc, float* up, bool swiglu, int lane, bf16_t* out, int O, int row0, int nvalid) {
+ORN_D void tile_store(float* acc, bool swiglu, int lane, bf16_t* out, int O, int row0, int nvalid) {
   constexpr int MP = pad_m(M), V = R * MP;
   int which;
   float v = rs_butterfly<V>(acc, lane, which);
+  bool writer = (lane & (32 / V - 1)) == 0;
   if (swiglu) {
-    int w2;
-    const float u = rs_butterfly<V>(up, lane, w2);
+    const float u = __shfl_down_sync(0xffffffffu, v, 16);
     v = swiglu_bf_call(bfr(v), bfr(u));
+    writer = writer && lane < 16;
   }
   const int r = which / MP, m = which % MP;
-  if ((lane & (32 / V - 1)) == 0 && r < nvalid && m < M) out[(size_t)m * O + row0 + r] = f2bf(v);
+  if (writer && r < nvalid && m < M) out[(size_t)m * O + row0 + r] = f2bf(v);
 }
 template <int M, int MASK, int KC>
-ORN_D void tile_store_masked(int kind, float* acc, float* up, bool swiglu, int lane, bf16_t* out, int O, int row0,
-                             int nvalid) {
+ORN_D void tile_store_masked(int kind, float* acc, bool swiglu, int lane, bf16_t* out, int O, int row0, int nvalid) {
   if ((MASK & (1 << ORN_A8)) && kind == ORN_A8)
-    tile_store<M, tile_rows(ORN_A8, KC)>(acc, up, swiglu, lane, out, O, row0, nvalid);
+    tile_store<M, tile_rows(ORN_A8, KC)>(acc, swiglu, lane, out, O, row0, nvalid);
   else if ((MASK & (1 << ORN_Q4K)) && kind == ORN_Q4K)
-    tile_store<M, tile_rows(ORN_Q4K, KC)>(acc, up, swiglu, lane, out, O, row0, nvalid);
+    tile_store<M, tile_rows(ORN_Q4K, KC)>(acc, swiglu, lane, out, O, row0, nvalid);
   else if ((MASK & (1 << ORN_Q6K)) && kind == ORN_Q6K)
-    tile_store<M, tile_rows(ORN_Q6K, KC)>(acc, up, swiglu, lane, out, O, row0, nvalid);
+    tile_store<M, tile_rows(ORN_Q6K, KC)>(acc, swiglu, lane, out, O, row0, nvalid);
   else if ((MASK & (1 << ORN_BF16)) && kind == ORN_BF16)
-    tile_store<M, tile_rows(ORN_BF16, KC)>(acc, up, swiglu, lane, out, O, row0, nvalid);
+    tile_store<M, tile_rows(ORN_BF16, KC)>(acc, swiglu, lane, out, O, row0, nvalid);
 }
 
-// position of a warp in its slot sequence: tile g of the concatenated jobs (stepping by GW),
-// resolved to (job j, tile t); SwiGLU tiles take two slots (sub 0: gate rows, sub 1: up rows)
+// position of a warp in its tile sequence: tile g of the concatenated jobs (stepping by GW),
+// resolved to (job j, tile t).  A SwiGLU job's tile is rows/2 gate rows and their up rows.
 struct Cursor {
-  int g, j, t, sub;
+  int g, j, t;
   ORN_D void locate(const RowJobs& J) {
     j = 0;
     t = g;
@@ -755,8 +771,6 @@ struct Cursor {
   }
   ORN_D bool valid(const RowJobs& J) const { return g < J.total; }
   ORN_D void advance(const RowJobs& J, int GW) {
-    if (J.job[j].epi == EPI_SWIGLU && sub == 0) { sub = 1; return; }
-    sub = 0;
     g += GW;
     if (g < J.total) locate(J);
   }
@@ -784,17 +798,24 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
     ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
     __syncwarp();
   }
-  Cursor pc{gw, 0, 0, 0}, cc{gw, 0, 0, 0};
+  Cursor pc{gw, 0, 0}, cc{gw, 0, 0};
   if (pc.valid(J)) { pc.locate(J); cc = pc; }
   int pslot = 0;
   auto issue = [&]() {  // all lanes keep the cursor; lane 0 issues
     const RowJob& job = J.job[pc.j];
     if (lane == 0) {
-      const LinDev& L = pc.sub ? job.lin2 : job.lin;
+      const LinDev& L = job.lin;
       const int rows = rows_of<KC>(L.kind);
-      const int row = pc.t * rows;
-      const int n = min(rows, L.O - row);
-      ring_fill(R, pslot, L.w + (size_t)row * L.rec, n * L.rec);
+      if (job.epi == EPI_SWIGLU) {
+        const int half = rows >> 1;
+        const int row = pc.t * half;
+        const int n = min(half, L.O - row);
+        ring_fill2(R, pslot, L.w + (size_t)row * L.rec, job.lin2.w + (size_t)row * L.rec, n * L.rec, half * L.rec);
+      } else {
+        const int row = pc.t * rows;
+        const int n = min(rows, L.O - row);
+        ring_fill(R, pslot, L.w + (size_t)row * L.rec, n * L.rec);
+      }
     }
     pc.advance(J, GW);
     if (++pslot == depth) pslot = 0;
@@ -829,34 +850,27 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
     for (int i = 0; i < depth && pc.valid(J); ++i) issue();
   }
 
-  float acc[kMaxAcc], up[kMaxAcc];
+  float acc[kMaxAcc];
   int slot = 0;
   uint32_t parity = 0;
   while (cc.valid(J)) {
     if (!ring_wait(R, slot, parity)) return;
     const RowJob& job = J.job[cc.j];
     const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
-    const bool swiglu = job.epi == EPI_SWIGLU;
-    if (cc.sub == 0) {
 #pragma unroll
-      for (int i = 0; i < kMaxAcc; ++i) { acc[i] = 0.f; up[i] = 0.f; }
-      tile_dot_masked<M, MASK, KC>(buf, job.lin, X, lane, acc);
-    } else {
-      tile_dot_masked<M, MASK, KC>(buf, job.lin2, X, lane, up);
-    }
+    for (int i = 0; i < kMaxAcc; ++i) acc[i] = 0.f;
+    tile_dot_masked<M, MASK, KC>(buf, job.lin, X, lane, acc);
     __syncwarp();
-    const bool last = !swiglu || cc.sub == 1;
+    const bool swiglu = job.epi == EPI_SWIGLU;
     const int kind = job.lin.kind, O = job.lin.O, t = cc.t;
     bf16_t* out = job.out;
     if (pc.valid(J)) {
       if (lane == 0) fence_proxy_async();
       issue();  // refills the slot just consumed
     }
-    if (last) {
-      const int rows = rows_of<KC>(kind);
-      const int row0 = t * rows;
-      tile_store_masked<M, MASK, KC>(kind, acc, up, swiglu, lane, out, O, row0, min(rows, O - row0));
-    }
+    const int rows = swiglu ? rows_of<KC>(kind) >> 1 : rows_of<KC>(kind);
+    const int row0 = t * rows;
+    tile_store_masked<M, MASK, KC>(kind, acc, swiglu, lane, out, O, row0, min(rows, O - row0));
     cc.advance(J, GW);
     if (++slot == depth) { slot = 0; parity ^= 1; }
   }
@@ -946,7 +960,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32
                                                              uint32_t ring_off, int* err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* smem = reinterpret_cast<float*>(smem_raw);
-  constexpr int RT = moe_rows(KIND, KC);
+  constexpr int RT = up_rows(KIND, KC);
   const int M = P.M;
   XStage X;
   float* next = stage_carve(smem, KIND, M, P.H, X);
@@ -975,21 +989,23 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32
     stage_fill_part<KIND>(lin, P.H, X, tid, nt);
   }
   __syncthreads();
-  // task g = (routed row mj, tile t of the expert's I output rows): two slots, gate rows then up rows
+  // task g = (routed row mj, tile t): RT/2 consecutive output rows of the expert's gate matrix and the
+  // same rows of its up matrix in one slot, one dot over the RT staged rows, one butterfly
+  constexpr int HALF = RT / 2;
   const int gw = blockIdx.x * (blockDim.x >> 5) + warp, GW = gridDim.x * (blockDim.x >> 5);
-  const int ntile = (P.I + RT - 1) / RT;
+  const int ntile = (P.I + HALF - 1) / HALF;
   const int total = M * P.k * ntile;
   const RecGeom geo = rec_geom(KIND, P.H);
-  int pg = gw, psub = 0, pslot = 0;
+  int pg = gw, pslot = 0;
   auto issue = [&]() {
     if (lane == 0) {
       const int mj = pg / ntile, t = pg - mj * ntile;
-      const int o = t * RT;
-      const int n = min(RT, P.I - o);
+      const int o = t * HALF;
+      const int n = min(HALF, P.I - o);
       const size_t row = (size_t)inds[mj] * P.I + o;
-      ring_fill(R, pslot, (psub ? P.up.w : P.gate.w) + row * geo.rec, n * geo.rec);
+      ring_fill2(R, pslot, P.gate.w + row * geo.rec, P.up.w + row * geo.rec, n * geo.rec, HALF * geo.rec);
     }
-    if (psub == 0) psub = 1; else { psub = 0; pg += GW; }
+    pg += GW;
     if (++pslot == depth) pslot = 0;
   };
   for (int i = 0; i < depth && pg < total; ++i) issue();
@@ -998,30 +1014,28 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32
       P.inds[i] = inds[i];
       P.scores[i] = f2bf(scores[i]);
     }
-  float g[RT], u[RT];
+  float gu[RT];
   int slot = 0;
   uint32_t parity = 0;
   for (int cg = gw; cg < total; cg += GW) {
     const int mj = cg / ntile, t = cg - mj * ntile;
     const int m = mj / P.k;
 #pragma unroll
-    for (int r = 0; r < RT; ++r) { g[r] = 0.f; u[r] = 0.f; }
-#pragma unroll
-    for (int sub = 0; sub < 2; ++sub) {
-      if (!ring_wait(R, slot, parity)) return;
-      tile_dot<KIND, 1, RT>(R.buf + (size_t)slot * slot_bytes, P.gate, X, m, lane, sub ? u : g);
-      __syncwarp();
-      if (pg < total) {
-        if (lane == 0) fence_proxy_async();
-        issue();
-      }
-      if (++slot == depth) { slot = 0; parity ^= 1; }
+    for (int r = 0; r < RT; ++r) gu[r] = 0.f;
+    if (!ring_wait(R, slot, parity)) return;
+    tile_dot<KIND, 1, RT>(R.buf + (size_t)slot * slot_bytes, P.gate, X, m, lane, gu);
+    __syncwarp();
+    if (pg < total) {
+      if (lane == 0) fence_proxy_async();
+      issue();
     }
-    int which, w2;
-    const float gs = rs_butterfly<RT>(g, lane, which);
-    const float us = rs_butterfly<RT>(u, lane, w2);
-    const int o = t * RT + which;
-    if ((lane & (32 / RT - 1)) == 0 && o < P.I) P.act[(size_t)mj * P.I + o] = f2bf(swiglu_bf_call(bfr(gs), bfr(us)));
+    if (++slot == depth) { slot = 0; parity ^= 1; }
+    int which;
+    const float gs = rs_butterfly<RT>(gu, lane, which);  // gate sums in lanes 0..15, up sums 16 lanes above
+    const float us = __shfl_down_sync(0xffffffffu, gs, 16);
+    const int o = t * HALF + which;
+    if (lane < 16 && (lane & (32 / RT - 1)) == 0 && o < P.I)
+      P.act[(size_t)mj * P.I + o] = f2bf(swiglu_bf_call(bfr(gs), bfr(us)));
   }
 }
 
@@ -1530,7 +1544,10 @@ int launch_norm_gemv(orn_ctx* ctx, cudaStream_t s, const Prologue& P, RowJobs& J
         (job.lin2.kind != job.lin.kind || job.lin2.K != job.lin.K || job.lin2.O != job.lin.O))
       ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: gate and up projections must share format and shape");
     const int rows = tile_rows(job.lin.kind, kc);
-    job.tiles = (job.lin.O + rows - 1) / rows;
+    if (job.epi == EPI_SWIGLU && rows < 2)
+      ORN_FAIL(ctx, ORN_ERR_ARG, "fused gemv: rows too long for a gate/up tile pair");
+    const int per_tile = job.epi == EPI_SWIGLU ? rows / 2 : rows;
+    job.tiles = (job.lin.O + per_tile - 1) / per_tile;
     J.total += job.tiles;
     const uint32_t bytes = (uint32_t)rows * job.lin.rec;
     slot = bytes > slot ? bytes : slot;
@@ -1545,7 +1562,7 @@ int launch_moe_up_k(orn_ctx* ctx, cudaStream_t s, const MoeUpParams& P) {
   size_t fixed = stage_floats(KIND, M, P.H) * sizeof(float) + (size_t)M * P.k * 4;
   fixed = (fixed + 127) & ~(size_t)127;
   fixed += ((size_t)M * P.H + (size_t)M * P.E + M * 32 + M * P.k + 8) * sizeof(float);
-  const uint32_t slot = moe_rows(KIND, KC) * P.gate.rec;
+  const uint32_t slot = up_rows(KIND, KC) * P.gate.rec;
   int depth;
   uint32_t ring_off;
   size_t bytes;
