@@ -86,7 +86,9 @@ int32_t orn_ctx_create(int32_t device, orn_ctx** out) {
   }
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) c->sm_count = prop.multiProcessorCount;
-  if (cudaMalloc((void**)&c->dev_err, sizeof(int)) != cudaSuccess || cudaMemset(c->dev_err, 0, sizeof(int)) != cudaSuccess) {
+  // [0] the error flag of bounded waits; [64 ..) arrival counters of the gated-delta kernel's heads
+  if (cudaMalloc((void**)&c->dev_err, 1024 * sizeof(int)) != cudaSuccess ||
+      cudaMemset(c->dev_err, 0, 1024 * sizeof(int)) != cudaSuccess) {
     cudaStreamDestroy(c->stream);
     delete c;
     return ORN_ERR_ALLOC;

@@ -1148,8 +1148,8 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, ui
       float d[RT];
 #pragma unroll
       for (int r = 0; r < RT; ++r) d[r] = 0.f;
-      if (q < P.k) tile_dot<KIND, 1, RT>(buf, P.down, X, m * P.k + q, lane, d);
-      else tile_dot<KIND, 1, RT>(buf, P.sh_down, XS, m, lane, d);
+      const bool routed = q < P.k;  // one copy of the dot serves the routed and the shared tile
+      tile_dot<KIND, 1, RT>(buf, routed ? P.down : P.sh_down, routed ? X : XS, routed ? m * P.k + q : m, lane, d);
       __syncwarp();
       if (pg < total) {
         if (lane == 0) fence_proxy_async();
@@ -1183,6 +1183,13 @@ struct GdnParams {
   bf16_t* y;            // [T][Hv][128]
   int T, S, Kc, D, Hk, Hv, nring, final_only;
   float q_scale, k_scale, eps;
+  // optional epilogue: rms_norm_gated of the outputs (kernels/ornith_norm.metal:119-185) by the
+  // last CTA of each head to finish; null `gated_out` leaves y as the only output
+  const bf16_t* z;          // [T][Hv*128] gate rows
+  const bf16_t* norm_w;     // [128]
+  bf16_t* gated_out;        // [T][Hv*128]
+  unsigned int* arrivals;   // [Hv], zero between launches
+  float norm_eps;
 };
 
 constexpr int kGdnRows = 16;
@@ -1295,6 +1302,47 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
       for (int i = 0; i < 8; ++i)
         *reinterpret_cast<float4*>(sout + 4 * i) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
     }
+  }
+  if (p.gated_out == nullptr) return;
+  // The 128 / kGdnRows CTAs of a head each wrote their rows of y.  The last of them to get here
+  // normalises the head (one warp per window row, the arithmetic of the stand-alone
+  // rms_norm_gated) and resets the head's counter for the next launch.
+  __shared__ unsigned int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(p.arrivals + hv, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1u : 0u;
+    if (s_last) atomicExch(p.arrivals + hv, 0u);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const uint2 wv = __ldg(reinterpret_cast<const uint2*>(p.norm_w + 4 * lane));
+  const float wf[4] = {bf_lo(wv.x), bf_hi(wv.x), bf_lo(wv.y), bf_hi(wv.y)};
+  for (int t = warp; t < p.T; t += (blockDim.x >> 5)) {
+    const size_t base = ((size_t)t * p.Hv + hv) * 128 + 4 * lane;
+    const uint2 a2 = __ldcg(reinterpret_cast<const uint2*>(p.y + base));  // written by other CTAs: read through L2
+    const uint2 z2 = __ldg(reinterpret_cast<const uint2*>(p.z + base));
+    const float xv[4] = {bf_lo(a2.x), bf_hi(a2.x), bf_lo(a2.y), bf_hi(a2.y)};
+    const float gz[4] = {bf_lo(z2.x), bf_hi(z2.x), bf_lo(z2.y), bf_hi(z2.y)};
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc = fmaf(xv[i], xv[i], acc);
+    acc = warp_sum(acc);
+    const float iv = orn_rsqrtf(acc / 128.0f + p.norm_eps);
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float normed = bfr(wf[i] * bfr(xv[i] * iv));
+      float g = gz[i];
+      g = g * sigmoid_f32_call(g);
+      o[i] = f2bf(g * normed);
+    }
+    uint2 ov;
+    ov.x = o[0] | (o[1] << 16);
+    ov.y = o[2] | (o[3] << 16);
+    *reinterpret_cast<uint2*>(p.gated_out + base) = ov;
   }
 }
 
@@ -1669,7 +1717,8 @@ int f_moe_down(orn_ctx* ctx, cudaStream_t s, int M, const bf16_t* act, const bf1
 
 int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, const bf16_t* a, const bf16_t* b,
           const bf16_t* a_log, const bf16_t* dt_bias, float* ring, int nring, const int* cur, int final_only, int T,
-          int Hk, int Hv, int Kc, float eps, bf16_t* y) {
+          int Hk, int Hv, int Kc, float eps, bf16_t* y, const bf16_t* z, const bf16_t* norm_w, float norm_eps,
+          bf16_t* gated_out) {
   if (T > kGdnMaxT) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gdn: at most 4 rows");
   if (!final_only && T + 1 > nring) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gdn: window wider than the state ring");
   GdnParams p;
@@ -1680,6 +1729,9 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
   p.q_scale = bfr(inv_scale * inv_scale);
   p.k_scale = bfr(inv_scale);
   p.eps = eps;
+  p.z = z; p.norm_w = norm_w; p.gated_out = gated_out; p.norm_eps = norm_eps;
+  p.arrivals = reinterpret_cast<unsigned int*>(ctx->dev_err) + 64;
+  if (gated_out != nullptr && Hv > 512) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gdn: more than 512 value heads");
   dim3 grid(128 / kGdnRows, Hv);
   ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn, grid, dim3(kGdnRows * 4), 0, p));
   return orn_launch_check(ctx, "k_gdn");

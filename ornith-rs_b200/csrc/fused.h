@@ -36,7 +36,8 @@ int f_moe_down(orn_ctx* ctx, cudaStream_t s, int M, const bf16_t* act, const bf1
                int normalize, bf16_t* out);
 int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, const bf16_t* a, const bf16_t* b,
           const bf16_t* a_log, const bf16_t* dt_bias, float* ring, int nring, const int* cur, int final_only, int T,
-          int Hk, int Hv, int Kc, float eps, bf16_t* y);
+          int Hk, int Hv, int Kc, float eps, bf16_t* y, const bf16_t* z, const bf16_t* norm_w, float norm_eps,
+          bf16_t* gated_out /* nullable: rms_norm_gated(y, z) per head, by the last CTA of the head */);
 int f_attn(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, const bf16_t* k, const bf16_t* v, const bf16_t* q_norm,
            const bf16_t* k_norm, bf16_t* kc, bf16_t* vc, const int* pos, int T, int Hq, int Hkv, int hd, int cap,
            int rope_dims, float lnb, float eps, bf16_t* out);

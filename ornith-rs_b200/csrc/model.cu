@@ -479,9 +479,10 @@ int trunk_layers(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int T, bo
       jobs[3].lin = ly.in_a; jobs[3].out = w.aa;
       CK(f_norm_gemv(ctx, s, T, fp, jobs, 4));
       CK(f_gdn(ctx, s, conv, ly.conv_w, w.aa, w.bb, ly.a_log, ly.dt_bias, cc->ring[i], kRing, cc->cur,
-               capture ? 0 : 1, T, c.gdn_k_heads, c.gdn_v_heads, c.gdn_conv_kernel, 1e-6f, w.gy));
-      FusedPrologue gp;
-      gp.mode = PRO_GATED; gp.K = VD; gp.a = w.gy; gp.b = w.z; gp.w = ly.gdn_norm; gp.eps = c.rms_eps;
+               capture ? 0 : 1, T, c.gdn_k_heads, c.gdn_v_heads, c.gdn_conv_kernel, 1e-6f, w.gy, w.z, ly.gdn_norm,
+               c.rms_eps, w.ggated));
+      FusedPrologue gp;  // the gated norm is already applied: the projection only loads its rows
+      gp.mode = PRO_PLAIN; gp.K = VD; gp.a = w.ggated;
       FusedJob oj;
       oj.lin = ly.out_proj; oj.out = w.r;
       CK(f_norm_gemv(ctx, s, T, gp, &oj, 1));
