@@ -86,63 +86,42 @@ ORN_D float* stage_carve(float* base, int kind, int rows, int K, XStage& X) {
   return X.sums + (size_t)rows * X.units * kind_ns(kind);
 }
 
-// lin: [rows][K] floats (row stride `stride`) -> stage; block-wide, no sync
-// inside.  A thread owns whole units: it moves the unit's P pieces to their
-// permuted places and, for the formats that need it, adds the unit's elements
-// in ascending order into the staged sum.
-template <int KIND>
-__device__ __noinline__ void stage_fill(const float* lin, int stride, const XStage& X) {
-  constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
-  const int padded = X.S * 32;  // unit slots per row, including the empty tail
-  for (int m = 0; m < X.rows; ++m) {
-    const float* src = lin + (size_t)m * stride;
-    float4* dst = reinterpret_cast<float4*>(X.xs) + (size_t)m * padded * P;
-    for (int u = threadIdx.x; u < padded; u += blockDim.x) {
-      const int lane = u & 31, s = u >> 5;
-      float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-      for (int p = 0; p < P; ++p) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (u < X.units) v = *reinterpret_cast<const float4*>(src + src_index<KIND>(u, p));
-        dst[(s * P + p) * 32 + lane] = v;
-        if (NS == 1 || (NS == 2 && p < 4)) { s0 = s0 + v.x; s0 = s0 + v.y; s0 = s0 + v.z; s0 = s0 + v.w; }
-        if (NS == 2 && p >= 4) { s1 = s1 + v.x; s1 = s1 + v.y; s1 = s1 + v.z; s1 = s1 + v.w; }
-      }
-      if (u < X.units) {
-        if (NS == 1) X.sums[(size_t)m * X.units + u] = s0;
-        if (NS == 2) { X.sums[((size_t)m * X.units + u) * 2] = s0; X.sums[((size_t)m * X.units + u) * 2 + 1] = s1; }
-      }
-    }
-  }
-}
-// The same by the threads tid of nthreads only (a subset of the CTA may stage while other warps
-// do something else); no sync inside.
+// lin: [rows][K] floats (row stride `stride`) -> stage, by the threads tid of nthreads (a subset of
+// the CTA may stage while other warps do something else); no sync inside.  A thread owns whole
+// units of any row (rows x unit slots are one flat index space, so short rows keep every thread
+// busy): it moves the unit's P pieces to their permuted places and, for the formats that need it,
+// adds the unit's elements in ascending order into the staged sum.
 template <int KIND>
 __device__ __noinline__ void stage_fill_part(const float* lin, int stride, const XStage& X, int tid, int nthreads) {
   constexpr int P = Lay<KIND>::P, NS = Lay<KIND>::NS;
-  const int padded = X.S * 32;
+  const int padded = X.S * 32;  // unit slots per row, including the empty tail
+  const int total = X.rows * padded;
 #pragma unroll 1
-  for (int m = 0; m < X.rows; ++m) {
+  for (int idx = tid; idx < total; idx += nthreads) {
+    const int m = idx / padded, u = idx - m * padded;
     const float* src = lin + (size_t)m * stride;
     float4* dst = reinterpret_cast<float4*>(X.xs) + (size_t)m * padded * P;
-#pragma unroll 1
-    for (int u = tid; u < padded; u += nthreads) {
-      const int lane = u & 31, s = u >> 5;
-      float s0 = 0.f, s1 = 0.f;
+    const int lane = u & 31, s = u >> 5;
+    float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int p = 0; p < P; ++p) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (u < X.units) v = *reinterpret_cast<const float4*>(src + src_index<KIND>(u, p));
-        dst[(s * P + p) * 32 + lane] = v;
-        if (NS == 1 || (NS == 2 && p < 4)) { s0 = s0 + v.x; s0 = s0 + v.y; s0 = s0 + v.z; s0 = s0 + v.w; }
-        if (NS == 2 && p >= 4) { s1 = s1 + v.x; s1 = s1 + v.y; s1 = s1 + v.z; s1 = s1 + v.w; }
-      }
-      if (u < X.units) {
-        if (NS == 1) X.sums[(size_t)m * X.units + u] = s0;
-        if (NS == 2) { X.sums[((size_t)m * X.units + u) * 2] = s0; X.sums[((size_t)m * X.units + u) * 2 + 1] = s1; }
-      }
+    for (int p = 0; p < P; ++p) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (u < X.units) v = *reinterpret_cast<const float4*>(src + src_index<KIND>(u, p));
+      dst[(s * P + p) * 32 + lane] = v;
+      if (NS == 1 || (NS == 2 && p < 4)) { s0 = s0 + v.x; s0 = s0 + v.y; s0 = s0 + v.z; s0 = s0 + v.w; }
+      if (NS == 2 && p >= 4) { s1 = s1 + v.x; s1 = s1 + v.y; s1 = s1 + v.z; s1 = s1 + v.w; }
+    }
+    if (u < X.units) {
+      if (NS == 1) X.sums[(size_t)m * X.units + u] = s0;
+      if (NS == 2) { X.sums[((size_t)m * X.units + u) * 2] = s0; X.sums[((size_t)m * X.units + u) * 2 + 1] = s1; }
     }
   }
+}
+
+// the same by every thread of the CTA
+template <int KIND>
+__device__ __noinline__ void stage_fill(const float* lin, int stride, const XStage& X) {
+  stage_fill_part<KIND>(lin, stride, X, threadIdx.x, blockDim.x);
 }
 ORN_D void stage_fill_kind(int kind, const float* lin, int stride, const XStage& X) {
   switch (kind) {
@@ -1109,7 +1088,10 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, ui
     if (++pq > P.k) { pq = 0; pg += GW; }
     if (++pslot == depth) pslot = 0;
   };
-  for (int i = 0; i < depth && pg < total; ++i) issue();
+  // two tiles per warp now, the rest once the activations are staged: a full ring of requests
+  // would hold every warp at the copy engine (about 50 cycles per request) before it can stage
+  int primed = 0;
+  for (; primed < 2 && primed < depth && pg < total; ++primed) issue();
   if (threadIdx.x < rows) {  // thread (m, j): the normalised score of routed expert j of token m
     const int m = threadIdx.x / P.k, j = threadIdx.x - m * P.k;
     float denom = 0.f;
@@ -1136,6 +1118,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, ui
   stage_fill<KIND>(lin, P.I, X);
   stage_fill<KIND>(lin2, P.SI, XS);
   __syncthreads();
+  for (; primed < depth && pg < total; ++primed) issue();
   int slot = 0;
   uint32_t parity = 0;
   for (int cg = gw; cg < total; cg += GW) {
