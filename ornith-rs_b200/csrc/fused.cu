@@ -619,20 +619,26 @@ ORN_D void run_prologue(const Prologue& P, const AddNormIn<M>& in, float* lin, f
   const int K = P.K;
   float* inv = red + M * 32;
   if (P.mode == PRO_ADDNORM) {
+    // A thread's 4-element groups are exactly the virtual threads of the RMS statistic (group g of
+    // thread t = virtual thread t + g * blockDim), so the sums of squares come straight from the
+    // registers: warp butterflies here, one barrier, the second-level butterfly, one barrier.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float hv[M][kAddNormGroups][4];
 #pragma unroll
     for (int g = 0; g < kAddNormGroups; ++g) {
       const int c0 = 4 * (threadIdx.x + g * blockDim.x);
-      if (c0 < K) {
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
+      for (int m = 0; m < M; ++m) {
+        float* v = hv[m][g];
+        v[0] = v[1] = v[2] = v[3] = 0.f;
+        if (c0 < K) {
           const uint2 av = in.a[m][g];
-          float v[4] = {bf_lo(av.x), bf_hi(av.x), bf_lo(av.y), bf_hi(av.y)};
+          v[0] = bf_lo(av.x); v[1] = bf_hi(av.x); v[2] = bf_lo(av.y); v[3] = bf_hi(av.y);
           if (P.b != nullptr) {
             const uint2 bv = in.b[m][g];
             v[0] = bfr(v[0] + bf_lo(bv.x)); v[1] = bfr(v[1] + bf_hi(bv.x));
             v[2] = bfr(v[2] + bf_lo(bv.y)); v[3] = bfr(v[3] + bf_hi(bv.y));
           }
-          *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) = make_float4(v[0], v[1], v[2], v[3]);
           if (P.sum_out != nullptr && blockIdx.x == 0) {
             uint2 o;
             o.x = (uint32_t)f2bf(v[0]) | ((uint32_t)f2bf(v[1]) << 16);
@@ -640,10 +646,25 @@ ORN_D void run_prologue(const Prologue& P, const AddNormIn<M>& in, float* lin, f
             *reinterpret_cast<uint2*>(P.sum_out + (size_t)m * K + c0) = o;
           }
         }
+        float acc = 0.f;  // a virtual thread past the row contributes an exact zero
+        acc = fmaf(v[0], v[0], acc);
+        acc = fmaf(v[1], v[1], acc);
+        acc = fmaf(v[2], v[2], acc);
+        acc = fmaf(v[3], v[3], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) red[m * 32 + warp + g * nw] = acc;  // virtual warp (t + g * blockDim) / 32
       }
     }
+    // virtual warps nobody owns (the CTA has kAddNormGroups * nw <= 32 of them) are zero
+    if (warp == 0 && lane >= kAddNormGroups * nw)
+#pragma unroll
+      for (int m = 0; m < M; ++m) red[m * 32 + lane] = 0.f;
     __syncthreads();
-    block_rms_inv(lin, K, M, K, P.eps, red, inv);
+    if (warp < M) {
+      const float total = warp_sum(red[warp * 32 + lane]);
+      if (lane == 0) inv[warp] = orn_rsqrtf(total / (float)K + P.eps);
+    }
+    __syncthreads();
 #pragma unroll
     for (int g = 0; g < kAddNormGroups; ++g) {
       const int c0 = 4 * (threadIdx.x + g * blockDim.x);
@@ -652,11 +673,11 @@ ORN_D void run_prologue(const Prologue& P, const AddNormIn<M>& in, float* lin, f
         const float wv[4] = {bf_lo(ww.x), bf_hi(ww.x), bf_lo(ww.y), bf_hi(ww.y)};
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          float4 v = *reinterpret_cast<const float4*>(lin + (size_t)m * K + c0);
+          const float* v = hv[m][g];
           const float iv = inv[m];
-          v.x = bfr(wv[0] * bfr(v.x * iv)); v.y = bfr(wv[1] * bfr(v.y * iv));
-          v.z = bfr(wv[2] * bfr(v.z * iv)); v.w = bfr(wv[3] * bfr(v.w * iv));
-          *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) = v;
+          *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) =
+              make_float4(bfr(wv[0] * bfr(v[0] * iv)), bfr(wv[1] * bfr(v[1] * iv)), bfr(wv[2] * bfr(v[2] * iv)),
+                          bfr(wv[3] * bfr(v[3] * iv)));
         }
       }
     }
