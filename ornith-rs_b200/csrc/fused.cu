@@ -31,6 +31,11 @@ namespace {
 // Out-of-line copies of the elementary functions: these kernels run each piece of code once or
 // twice per launch, so instruction-cache misses cost more than calls do.
 __device__ __noinline__ float expf_call(float x) { return orn_expf(x); }
+// four at once: the evaluations interleave in the pipelines instead of running one after another
+__device__ __noinline__ void expf4_call(float* v) {
+  const float a = orn_expf(v[0]), b = orn_expf(v[1]), c = orn_expf(v[2]), d = orn_expf(v[3]);
+  v[0] = a; v[1] = b; v[2] = c; v[3] = d;
+}
 __device__ __noinline__ float silu_bf_call(float x) { return orn_silu_bf(x); }
 __device__ __noinline__ float sigmoid_bf_call(float x) { return orn_sigmoid_bf(x); }
 __device__ __noinline__ float sigmoid_f32_call(float x) { return orn_sigmoid_f32(x); }
@@ -893,27 +898,57 @@ struct MoeUpParams {
 // (kernels/moe.metal:568-614) for one token by one warp; results to shared
 __device__ __noinline__ void warp_softmax_topk(const bf16_t* logits, int n, int k, float* probs /*[n] smem*/,
                              float* red /*[32] smem*/, uint32_t* inds, float* scores, int lane) {
-  float mx = -INFINITY;
-  for (int i = lane; i < n; i += 32) mx = fmaxf(mx, bf2f(logits[i]));
-  mx = warp_max(mx);
+  // the lane's logits (4 consecutive per virtual warp, up to 512 in all) come in with one round of
+  // loads; the maximum and the exponentials then work from registers
+  constexpr int kMaxVW = 4;
   const int nvt = (n + 3) / 4;
   const int nvw = (nvt + 31) / 32;
-  red[lane] = 0.f;
-  __syncwarp();
-  for (int vw = 0; vw < nvw; ++vw) {
-    const int vt = vw * 32 + lane;
-    float acc = 0.f;
+  float xv[kMaxVW][4];
+  const bool vec = (n & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 7) == 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int idx = 4 * vt + i;
-      if (idx < n) {
-        const float e = expf_call(bf2f(logits[idx]) - mx);
-        probs[idx] = e;
-        acc = acc + e;
+  for (int vw = 0; vw < kMaxVW; ++vw) {
+    const int base = 4 * (vw * 32 + lane);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) xv[vw][i] = -INFINITY;
+    if (vw < nvw) {
+      if (vec && base < n) {
+        const uint2 r = __ldg(reinterpret_cast<const uint2*>(logits + base));
+        xv[vw][0] = bf_lo(r.x); xv[vw][1] = bf_hi(r.x); xv[vw][2] = bf_lo(r.y); xv[vw][3] = bf_hi(r.y);
+      } else if (!vec) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (base + i < n) xv[vw][i] = bf2f(logits[base + i]);
       }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) red[vw] = acc;
+  }
+  float mx = -INFINITY;
+#pragma unroll
+  for (int vw = 0; vw < kMaxVW; ++vw)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mx = fmaxf(mx, xv[vw][i]);
+  mx = warp_max(mx);
+  red[lane] = 0.f;
+  __syncwarp();
+#pragma unroll
+  for (int vw = 0; vw < kMaxVW; ++vw) {
+    if (vw < nvw) {
+      const int vt = vw * 32 + lane;
+      float ev[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ev[i] = xv[vw][i] - mx;  // absent entries are -inf - mx: their exp is not used
+      expf4_call(ev);
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = 4 * vt + i;
+        if (idx < n) {
+          probs[idx] = ev[i];
+          acc = acc + ev[i];
+        }
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) red[vw] = acc;
+    }
   }
   __syncwarp();
   const float inv = 1.0f / warp_sum(red[lane]);
