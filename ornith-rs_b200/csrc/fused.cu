@@ -186,9 +186,21 @@ template <> struct WU<ORN_Q4K> {
     }
     const float lo = pk2_sum(lo2), hi = pk2_sum(hi2);
     const float d = h2f((uint16_t)(w.meta.x & 0xffff)), dmin = h2f((uint16_t)(w.meta.x >> 16));
-    float s1, m1, s2, m2;
-    q4k_scale_min(2 * g, w.meta.y, w.meta.z, w.meta.w, &s1, &m1);
-    q4k_scale_min(2 * g + 1, w.meta.y, w.meta.z, w.meta.w, &s2, &m2);
+    // get_scale_min_k4 (kernels/q4k.metal:43-56) for the sub-blocks 2g and 2g+1 at once: their
+    // bytes are neighbours in each of the three scale words, so both come out of 16-bit pieces
+    // (j < 4: sc = q[j] & 63, m = q[j+4] & 63; else sc = (q[j+4] & 15) | (q[j-4] >> 6 << 4),
+    // m = (q[j+4] >> 4) | (q[j] >> 6 << 4))
+    const int sh = (g & 1) * 16;
+    const uint32_t qa = (w.meta.y >> sh) & 0xffffu, qb = (w.meta.z >> sh) & 0xffffu, qc = (w.meta.w >> sh) & 0xffffu;
+    const bool low = g < 2;
+    const uint32_t sc2 = low ? (qa & 0x3f3fu) : ((qc & 0x0f0fu) | ((qa >> 2) & 0x3030u));
+    const uint32_t mn2 = low ? (qb & 0x3f3fu) : (((qc >> 4) & 0x0f0fu) | ((qb >> 2) & 0x3030u));
+    float s1, s2, m1, m2;
+    {
+      const uint64_t sp = byte2_f<0>(sc2, nm), mp = byte2_f<0>(mn2, nm);
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(s1), "=f"(s2) : "l"(sp));
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(m1), "=f"(m2) : "l"(mp));
+    }
     float t = s1 * lo;
     t = fmaf(s2, hi, t);
     float mt = m1 * sm[0];
