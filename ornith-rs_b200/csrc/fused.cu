@@ -221,9 +221,8 @@ template <> struct WU<ORN_Q6K> {
     w.qb = *reinterpret_cast<const uint32_t*>(base + 64 * half + 32 + l0);
     w.qh = *reinterpret_cast<const uint32_t*>(base + 128 + 32 * half + l0);
     const uint2 s8 = *reinterpret_cast<const uint2*>(rec + off1 + blk * 16 + 8 * half);
-    const int is = l0 >> 4;
-    const uint32_t lo = s8.x >> (8 * is), hi = s8.y >> (8 * is);
-    w.sc4 = (lo & 0xff) | (((lo >> 16) & 0xff) << 8) | ((hi & 0xff) << 16) | (((hi >> 16) & 0xff) << 24);
+    // scales sc[is + 0, 2, 4, 6] of this half: bytes is, is+2 of either word, one byte permute
+    w.sc4 = __byte_perm(s8.x, s8.y, (l0 >> 4) ? 0x7531u : 0x6420u);
     w.d = h2f(*reinterpret_cast<const uint16_t*>(rec + off2 + 2 * blk));
   }
   ORN_D static float fold(const W& w, const float* x, const float*, int, float acc) {
@@ -242,8 +241,15 @@ template <> struct WU<ORN_Q6K> {
     uint64_t p3 = ffma2(pk2(x[12], x[13]), byte2_f<0>(q4, nm), z);
     p3 = ffma2(pk2(x[14], x[15]), byte2_f<2>(q4, nm), p3);
     const float s0 = pk2_sum(p0), s1 = pk2_sum(p1), s2 = pk2_sum(p2), s3 = pk2_sum(p3);
-    const float c0 = (float)(int8_t)(w.sc4 & 0xff), c1 = (float)(int8_t)((w.sc4 >> 8) & 0xff);
-    const float c2 = (float)(int8_t)((w.sc4 >> 16) & 0xff), c3 = (float)(int8_t)(w.sc4 >> 24);
+    // four int8 scales -> float: b ^ 0x80 is b + 128 as an unsigned byte, then the exact byte -> float form
+    float c0, c1, c2, c3;
+    {
+      const uint32_t ub = w.sc4 ^ 0x80808080u;
+      const uint64_t nb = pk2(-8388736.0f, -8388736.0f);  // -(2^23 + 128)
+      const uint64_t c01 = byte2_f<0>(ub, nb), c23 = byte2_f<2>(ub, nb);
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(c0), "=f"(c1) : "l"(c01));
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(c2), "=f"(c3) : "l"(c23));
+    }
     float t = c0 * s0;
     t = fmaf(c1, s1, t);
     t = fmaf(c2, s2, t);
