@@ -342,6 +342,100 @@ def ours(args):
         dist.destroy_process_group()
 
 
+def ep_layer(args):
+    """Second workload (`--workload ep-layer`): one MoE decode layer in expert-parallel form at
+    BASELINE config 5's decode width (64 sequences x verify width 2 = 128 rows in all, split evenly
+    over the ranks; experts 256/N per rank; dispatch and return all-to-all over NCCL).  The total
+    work is fixed, so scaling is strong.  `checksum` is a sum over every output element of every
+    rank: it must be the same number at every N (the block's bits do not depend on N)."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = load_pkg()
+    from ornith_rs_b200 import ep
+    ctx = pkg.Context(local)
+    H, E, I, k, ROWS = 2048, 256, 512, 8, 128
+    assert ROWS % world == 0 and E % world == 0
+    R = ROWS // world
+    kinds = {"gate": (pkg.A8, 1, E, H), "sw_gate": (pkg.Q4K, E, I, H), "sw_up": (pkg.Q4K, E, I, H),
+             "sw_down": (pkg.Q6K, E, H, I), "sh_gate": (pkg.Q4K, 1, I, H), "sh_up": (pkg.Q4K, 1, I, H),
+             "sh_down": (pkg.Q6K, 1, H, I), "sh_egate": (pkg.A8, 1, 1, H)}
+    L = {}
+    for i, (name, (kind, e, o, kk)) in enumerate(kinds.items()):
+        full = pkg.Linear.random(ctx, kind, e, o, kk, SEED + i)     # the same tensor on every rank
+        if name.startswith("sw_") and world > 1:
+            L[name] = ep.shard_experts(ctx, full, rank, world)
+            full.free()
+        else:
+            L[name] = full
+    ops = ep.CudaOps(ctx, L, k, 1)
+    comm = ep.DistComm(dist) if dist is not None else ep.SelfComm()
+    block = ep.EpMoeBlock(ops, comm, E)
+    rng = np.random.default_rng(SEED)
+    x_all = (rng.standard_normal((ROWS, H)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    x_host = torch.from_numpy(x_all[rank * R:(rank + 1) * R].view(np.int16).copy()).pin_memory()
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    x_dev = x_host.to(ops.device)
+    for _ in range(args.warmup):
+        y = block.forward(x_dev)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    l0 = ctx.launches()
+    ctx.timer_start()
+    for _ in range(args.steps):
+        y = block.forward(x_dev)
+    dev_ms = ctx.timer_stop()
+    launches = ctx.launches() - l0
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        with ops.run():
+            xd = x_host.to(ops.device, non_blocking=True)
+        y_host = block.forward(xd).cpu()
+    barrier()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    check = torch.tensor([int(y_host.to(torch.int64).bitwise_and(0xffff).sum())], dtype=torch.int64, device=ops.device)
+    if dist is not None:
+        dist.all_reduce(check)
+    dev_ms, wall = reduce_max_over_ranks([dev_ms, wall], dist, "cuda")
+    if rank == 0:
+        rows = ROWS * args.steps
+        print(json.dumps({
+            "metric": "ep_moe_layer_rows_per_s", "value": rows / (dev_ms * 1e-3), "unit": "rows/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 activations, f32 accumulate",
+            "data": "synthetic (random-init weights, N(0,1) rows)",
+            "config": {"workload": "one expert-parallel MoE decode layer: 128 rows (BASELINE config 5: 64 sequences x "
+                                   "width 2), hidden 2048, 256 experts top-8 (Q4_K gate/up, Q6_K down) split %d per rank, "
+                                   "shared expert + router replicated; all-gather of routing, dispatch and return "
+                                   "all-to-all (NCCL)" % (E // world),
+                       "l2_policy": "routed weights read per step (about 1 GB over all ranks) exceed L2",
+                       "parallelism": "ep%d" % world},
+            "e2e": {"value": rows / wall, "unit": "rows/s", "h2d_bytes_per_step": R * H * 2,
+                    "d2h_bytes_per_step": R * H * 2 + R * k * 4},
+            "gpu_launches": launches, "clocks": clocks, "checksum": int(check.item()),
+        }))
+    # the context (and its stream) stays open until the process ends: torch buffers that were used
+    # on that stream are still alive here, and freeing them after the stream is gone is an error
+    ctx.sync()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def reference(args):
     """The reference's own CPU statement of the path (its Metal path cannot run
     on Linux): the C restatement under oracle/, all host threads."""
@@ -377,11 +471,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--gen-tokens", type=int, default=200, help="tokens per generation (profiling runs use fewer)")
     ap.add_argument("--prompt-len", type=int, default=51)
+    ap.add_argument("--workload", default="decode", choices=["decode", "ep-layer"],
+                    help="decode: the MTP depth-1 decode loop (the headline); ep-layer: one expert-parallel MoE layer")
     args = ap.parse_args()
     global GEN_TOKENS, PROMPT_LEN
     GEN_TOKENS, PROMPT_LEN = args.gen_tokens, args.prompt_len
     if args.impl == "reference":
         reference(args)
+    elif args.workload == "ep-layer":
+        ep_layer(args)
     else:
         ours(args)
 

@@ -66,6 +66,14 @@ int32_t orn_ctx_create(int32_t device, orn_ctx** out);
 int32_t orn_ctx_destroy(orn_ctx* ctx);
 int32_t orn_sync(orn_ctx* ctx);                        /* Context::sync */
 const char* orn_last_error(orn_ctx* ctx);
+/* The context's queue (metal::Context's one command queue, src/metal/mod.rs:433-519) as a
+ * cudaStream_t: every entry point enqueues on it in call order.  A caller that interleaves its
+ * own device work (an expert-parallel exchange between two ops, say) enqueues that work on this
+ * stream instead of synchronising. */
+int32_t orn_ctx_stream(orn_ctx* ctx, void** stream_out);
+/* kernels this context has launched so far (the per-dispatch count of the reference's
+ * ORNITH_PROF report, src/metal/mod.rs:197-284) */
+int32_t orn_ctx_launches(orn_ctx* ctx, int64_t* count_out);
 int32_t orn_alloc(orn_ctx* ctx, size_t nbytes, void** dev_out);   /* Context::alloc */
 int32_t orn_free(orn_ctx* ctx, void* dev);
 int32_t orn_memset(orn_ctx* ctx, void* dev, int32_t byte, size_t nbytes);

@@ -49,6 +49,7 @@ class Context:
     """orn_ctx: one device, one stream (the reference's metal::Context)."""
 
     def __init__(self, device=0):
+        self.device = device
         self._lib = lib()
         h = C.c_void_p()
         rc = self._lib.orn_ctx_create(device, C.byref(h))
@@ -88,6 +89,11 @@ class Context:
         if arr.nbytes:
             self.check(self._lib.orn_upload(self.h, b.ptr, arr.ctypes.data, arr.nbytes), "orn_upload")
         return b
+
+    def launches(self):
+        n = C.c_int64()
+        self.check(self._lib.orn_ctx_launches(self.h, C.byref(n)), "orn_ctx_launches")
+        return n.value
 
     def timer_start(self):
         self.check(self._lib.orn_timer_start(self.h), "orn_timer_start")

@@ -60,6 +60,8 @@ SIGNATURES = {
     "orn_last_error": (C.c_char_p, [vp]),
     "orn_alloc": (i32, [vp, sz, c_void_pp]),
     "orn_free": (i32, [vp, vp]),
+    "orn_ctx_stream": (i32, [vp, C.POINTER(vp)]),
+    "orn_ctx_launches": (i32, [vp, C.POINTER(C.c_int64)]),
     "orn_memset": (i32, [vp, vp, i32, sz]),
     "orn_upload": (i32, [vp, vp, vp, sz]),
     "orn_download": (i32, [vp, vp, vp, sz]),

@@ -169,6 +169,18 @@ int32_t orn_free(orn_ctx* ctx, void* dev) {
   return ORN_OK;
 }
 
+int32_t orn_ctx_stream(orn_ctx* ctx, void** stream_out) {
+  if (!ctx || !stream_out) return ORN_ERR_ARG;
+  *stream_out = (void*)ctx->stream;
+  return ORN_OK;
+}
+
+int32_t orn_ctx_launches(orn_ctx* ctx, int64_t* count_out) {
+  if (!ctx || !count_out) return ORN_ERR_ARG;
+  *count_out = (int64_t)ctx->launches;
+  return ORN_OK;
+}
+
 int32_t orn_memset(orn_ctx* ctx, void* dev, int32_t byte, size_t nbytes) {
   if (!ctx || !dev) return ORN_ERR_ARG;
   ORN_CHECK_CUDA(ctx, cudaMemsetAsync(dev, byte, nbytes, ctx->stream));
