@@ -254,6 +254,7 @@ def ours(args):
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local)
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep NCCL's banner off stdout
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_pkg()
     ctx = pkg.Context(local)
@@ -356,6 +357,7 @@ def ep_layer(args):
     dist = None
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep NCCL's banner off stdout
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_pkg()
     from ornith_rs_b200 import ep
@@ -402,9 +404,8 @@ def ep_layer(args):
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        with ops.run():
-            xd = x_host.to(ops.device, non_blocking=True)
-        y_host = block.forward(xd).cpu()
+        with ops.run():   # upload, block and readback all on the context's stream
+            y_host = block.forward(x_host.to(ops.device, non_blocking=True)).cpu()
     barrier()
     wall = time.perf_counter() - t0
     clocks = sampler.stop()

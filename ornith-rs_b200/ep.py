@@ -110,12 +110,22 @@ class CudaOps:
         self.stream = torch.cuda.ExternalStream(sp.value, device=self.device)
         self.H = weights["gate"].K
         self.E = weights["gate"].O
+        self._iota = {}
 
     # -- helpers
     def empty(self, shape, dtype=None):
         return self.torch.empty(shape, dtype=dtype or self.torch.int16, device=self.device)
 
     def _gemv(self, lin, x, rows):
+        """y[rows, O] = x W^T for a replicated matrix.  Up to 4 rows go through `orn_gemv`; more rows
+        go through ONE gather launch with every row on "expert" 0 (the same one-row dot, so the same
+        bits) instead of a launch per group of 4."""
+        if rows > 4:
+            if rows not in self._iota:
+                self._iota[rows] = (self.torch.arange(rows, dtype=self.torch.int32, device=self.device),
+                                    self.torch.zeros(rows, dtype=self.torch.int32, device=self.device))
+            ident, zeros = self._iota[rows]
+            return self._gather(lin, x, ident, zeros, rows)
         y = self.empty((rows, lin.O))
         if rows:
             self.ctx.check(self.lib.orn_gemv(self.ctx.h, lin.h, x.data_ptr(), rows, y.data_ptr(), 0), "orn_gemv")
@@ -243,7 +253,13 @@ class EpMoeBlock:
         return self.ops.index_rows(self.x, self.p.send_rows)
 
     def compute(self, received):
-        return self.ops.experts(received, self.p.lhs, self.p.rhs)
+        # pairs of one expert run next to each other (their weight reads meet in L2); the outputs go
+        # back into the plan's return order
+        order = np.argsort(self.p.rhs, kind="stable")
+        inverse = np.empty_like(order)
+        inverse[order] = np.arange(len(order))
+        y = self.ops.experts(received, self.p.lhs[order], self.p.rhs[order])
+        return self.ops.index_rows(y, inverse)
 
     def finish(self, returned):
         y = self.ops.index_rows(returned, self.p.home_index)
