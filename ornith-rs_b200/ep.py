@@ -43,17 +43,10 @@ class Plan:
                  "home_index")
 
 
-def _pairs(inds_src, dest, experts_per_rank):
-    """Pairs (row, slot) of one source rank whose expert lives on `dest`, in (row, slot) order,
-    and the distinct rows among them (ascending)."""
-    owner = inds_src // experts_per_rank
-    rows, slots = np.nonzero(owner == dest)          # row-major: ascending row, then slot
-    uniq = np.unique(rows)
-    return rows, slots, uniq
-
-
 def make_plan(all_inds, rank, n_experts):
-    """all_inds: integer array [N, R, k] of every rank's routing indices (global expert ids)."""
+    """all_inds: integer array [N, R, k] of every rank's routing indices (global expert ids).
+    Pairs are ordered by (row, slot) inside every (source, owner) group, rows ascending inside
+    every (source, destination) group."""
     all_inds = np.asarray(all_inds).astype(np.int64)
     N, R, k = all_inds.shape
     if n_experts % N:
@@ -61,33 +54,27 @@ def make_plan(all_inds, rank, n_experts):
     if all_inds.size and (all_inds.min() < 0 or all_inds.max() >= n_experts):
         raise ValueError("routing index out of range")
     per = n_experts // N
+    owner = all_inds // per                                       # [N, R, k]
     p = Plan()
-    # what this rank sends (as home) and gets back
-    send_rows, send_counts, back_counts = [], [], []
-    home_index = np.empty(R * k, np.int64)
-    off = 0
-    for d in range(N):
-        rows, slots, uniq = _pairs(all_inds[rank], d, per)
-        send_rows.append(uniq)
-        send_counts.append(len(uniq))
-        back_counts.append(len(rows))
-        home_index[rows * k + slots] = off + np.arange(len(rows))
-        off += len(rows)
-    p.send_rows = np.concatenate(send_rows).astype(np.int64) if N else np.zeros(0, np.int64)
-    p.send_counts, p.back_counts, p.home_index = send_counts, back_counts, home_index
-    # what this rank receives and computes (as owner)
-    lhs, rhs, recv_counts, pair_counts = [], [], [], []
-    base = 0
-    for s in range(N):
-        rows, slots, uniq = _pairs(all_inds[s], rank, per)
-        recv_counts.append(len(uniq))
-        pair_counts.append(len(rows))
-        lhs.append(base + np.searchsorted(uniq, rows))
-        rhs.append(all_inds[s][rows, slots] - rank * per)
-        base += len(uniq)
-    p.lhs = np.concatenate(lhs).astype(np.uint32)
-    p.rhs = np.concatenate(rhs).astype(np.uint32)
-    p.recv_counts, p.pair_counts = recv_counts, pair_counts
+    # home side: this rank's pairs grouped by owner; a row goes once to every owner it needs
+    mine = owner[rank].reshape(-1)                                # row-major (row, slot)
+    by_owner = np.argsort(mine, kind="stable")
+    p.home_index = np.empty(R * k, np.int64)
+    p.home_index[by_owner] = np.arange(R * k)
+    p.back_counts = np.bincount(mine, minlength=N).tolist()
+    need = np.zeros((N, R), bool)
+    need[mine, np.repeat(np.arange(R), k)] = True
+    p.send_rows = np.nonzero(need)[1].astype(np.int64)            # owner-major, rows ascending
+    p.send_counts = need.sum(1).tolist()
+    # owner side: the pairs of every source whose expert lives here, source-major
+    here = owner == rank
+    src, row, slot = np.nonzero(here)
+    p.pair_counts = np.bincount(src, minlength=N).tolist()
+    arrive = here.any(2)                                          # [N, R]: rows that arrive, in buffer order
+    p.recv_counts = arrive.sum(1).tolist()
+    position = np.cumsum(arrive.reshape(-1)) - 1
+    p.lhs = position[src * R + row].astype(np.uint32)
+    p.rhs = (all_inds[src, row, slot] - rank * per).astype(np.uint32)
     return p
 
 
@@ -121,10 +108,7 @@ class CudaOps:
         go through ONE gather launch with every row on "expert" 0 (the same one-row dot, so the same
         bits) instead of a launch per group of 4."""
         if rows > 4:
-            if rows not in self._iota:
-                self._iota[rows] = (self.torch.arange(rows, dtype=self.torch.int32, device=self.device),
-                                    self.torch.zeros(rows, dtype=self.torch.int32, device=self.device))
-            ident, zeros = self._iota[rows]
+            ident, zeros = self._iota_pair(rows)
             return self._gather(lin, x, ident, zeros, rows)
         y = self.empty((rows, lin.O))
         if rows:
@@ -163,16 +147,27 @@ class CudaOps:
         act = self._swiglu(self._gemv(self.w["sh_gate"], x, R), self._gemv(self.w["sh_up"], x, R))
         return self._gemv(self.w["sh_down"], act, R), self._gemv(self.w["sh_egate"], x, R)
 
+    def stage_indices(self, arrays):
+        """All index vectors of one block in one host-to-device copy (int32 views of one buffer)."""
+        sizes = [len(a) for a in arrays.values()]
+        packed = np.concatenate([np.asarray(a).astype(np.int32) for a in arrays.values()]) if sum(sizes) else \
+            np.zeros(0, np.int32)
+        dev = self.torch.from_numpy(packed).to(self.device)
+        return dict(zip(arrays.keys(), self.torch.split(dev, sizes)))
+
+    def _iota_pair(self, rows):
+        if rows not in self._iota:
+            self._iota[rows] = (self.torch.arange(rows, dtype=self.torch.int32, device=self.device),
+                                self.torch.zeros(rows, dtype=self.torch.int32, device=self.device))
+        return self._iota[rows]
+
     def experts(self, x, lhs, rhs):
         """x [U, H] received rows; pair p = expert rhs[p] applied to x[lhs[p]] -> [P, H]."""
         P = int(lhs.shape[0])
-        lhs_d = self.torch.from_numpy(lhs.astype(np.int32)).to(self.device, non_blocking=False)
-        rhs_d = self.torch.from_numpy(rhs.astype(np.int32)).to(self.device, non_blocking=False)
-        ident = self.torch.arange(P, dtype=self.torch.int32, device=self.device)
-        g = self._gather(self.w["sw_gate"], x, lhs_d, rhs_d, P)
-        u = self._gather(self.w["sw_up"], x, lhs_d, rhs_d, P)
+        g = self._gather(self.w["sw_gate"], x, lhs, rhs, P)
+        u = self._gather(self.w["sw_up"], x, lhs, rhs, P)
         act = self._swiglu(g, u)
-        return self._gather(self.w["sw_down"], act, ident, rhs_d, P)
+        return self._gather(self.w["sw_down"], act, self._iota_pair(P)[0], rhs, P)
 
     def combine(self, scores, y, gs, sy):
         R = scores.shape[0]
@@ -183,7 +178,7 @@ class CudaOps:
         return out
 
     def index_rows(self, x, idx):
-        return x.index_select(0, self.torch.from_numpy(np.asarray(idx, np.int64)).to(self.device))
+        return x.index_select(0, idx)
 
     def to_host(self, t):
         return t.cpu().numpy()   # waits for the context's stream
@@ -246,23 +241,25 @@ class EpMoeBlock:
         return self.inds
 
     def plan(self, all_inds_host):
-        self.p = make_plan(all_inds_host, self.comm.rank, self.E)
-        return self.p
-
-    def dispatch_buffer(self):
-        return self.ops.index_rows(self.x, self.p.send_rows)
-
-    def compute(self, received):
-        # pairs of one expert run next to each other (their weight reads meet in L2); the outputs go
-        # back into the plan's return order
-        order = np.argsort(self.p.rhs, kind="stable")
+        self.p = p = make_plan(all_inds_host, self.comm.rank, self.E)
+        # pairs of one expert run next to each other (their weight reads meet in L2); `inverse`
+        # puts the outputs back into the plan's return order
+        order = np.argsort(p.rhs, kind="stable")
         inverse = np.empty_like(order)
         inverse[order] = np.arange(len(order))
-        y = self.ops.experts(received, self.p.lhs[order], self.p.rhs[order])
-        return self.ops.index_rows(y, inverse)
+        self.ix = self.ops.stage_indices({"send_rows": p.send_rows, "lhs": p.lhs[order], "rhs": p.rhs[order],
+                                          "inverse": inverse, "home_index": p.home_index})
+        return p
+
+    def dispatch_buffer(self):
+        return self.ops.index_rows(self.x, self.ix["send_rows"])
+
+    def compute(self, received):
+        y = self.ops.experts(received, self.ix["lhs"], self.ix["rhs"])
+        return self.ops.index_rows(y, self.ix["inverse"])
 
     def finish(self, returned):
-        y = self.ops.index_rows(returned, self.p.home_index)
+        y = self.ops.index_rows(returned, self.ix["home_index"])
         sy, gs = self.ops.shared(self.x)
         return self.ops.combine(self.scores, y, gs, sy)
 

@@ -77,6 +77,7 @@ class OracleOps:
         if P == 0:
             return torch.zeros((0, self.H), dtype=torch.int16)
         xs = _u16(x)
+        lhs, rhs = np.asarray(lhs, np.uint32), np.asarray(rhs, np.uint32)
         g = orc.gather_gemv(self.w["sw_gate"], xs, lhs, rhs)
         u = orc.gather_gemv(self.w["sw_up"], xs, lhs, rhs)
         act = orc.swiglu(g, u).reshape(P, -1)
@@ -85,6 +86,9 @@ class OracleOps:
     def combine(self, scores, y, gs, sy):
         R = scores.shape[0]
         return _t(orc.moe_combine(_u16(scores), _u16(y), _u16(gs), _u16(sy), R, self.k, self.H, self.norm))
+
+    def stage_indices(self, arrays):
+        return {n: np.asarray(a) for n, a in arrays.items()}
 
     def index_rows(self, x, idx):
         return x.index_select(0, torch.from_numpy(np.asarray(idx, np.int64)))
