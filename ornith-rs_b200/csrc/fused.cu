@@ -1252,6 +1252,7 @@ struct GdnParams {
 constexpr int kGdnRows = 16;
 constexpr int kGdnMaxT = 4;
 
+template <bool TAPS4>  // TAPS4: the convolution has 4 taps (every Qwen3.5 artifact); else any width
 __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
   __shared__ float s_q[kGdnMaxT][128], s_k[kGdnMaxT][128], s_v[kGdnMaxT][kGdnRows];
   __shared__ float s_g[kGdnMaxT], s_beta[kGdnMaxT];
@@ -1276,6 +1277,71 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
     S[4 * i] = v4.x; S[4 * i + 1] = v4.y; S[4 * i + 2] = v4.z; S[4 * i + 3] = v4.w;
   }
   // ---- front end (kernels/gdn_front.metal:65-190): warp 0 -> q head, warp 1 -> k head
+  if constexpr (TAPS4) {
+    // Every global read of the front end is requested here, before any arithmetic, so that the
+    // latencies overlap each other and the state rows': the T + 3 window rows of the lane's four
+    // q / k channels, their taps, the window of the value channel, the gate inputs.
+    constexpr int NR = kGdnMaxT + 3;
+    const int c0 = (warp == 0 ? hk * 128 : key_dim + hk * 128) + 4 * lane;
+    const int cv = 2 * key_dim + hv * 128 + row;
+    uint2 xr[NR], wr[4], vw = make_uint2(0u, 0u);
+    bf16_t vr[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      xr[i] = make_uint2(0u, 0u);
+      vr[i] = 0;
+      if (i < p.T + 3) {
+        xr[i] = *reinterpret_cast<const uint2*>(p.conv + (size_t)i * p.D + c0);
+        if (lir == 0) vr[i] = p.conv[(size_t)i * p.D + cv];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) wr[r] = *reinterpret_cast<const uint2*>(p.cw + (size_t)(c0 + r) * 4);
+    if (lir == 0) vw = *reinterpret_cast<const uint2*>(p.cw + (size_t)cv * 4);
+    float ga = 0.f, gb = 0.f, gdt = 0.f, gal = 0.f;
+    if (threadIdx.x < p.T) {
+      const size_t i = (size_t)threadIdx.x * p.Hv + hv;
+      ga = bf2f(p.a_in[i]); gb = bf2f(p.b_in[i]); gdt = bf2f(p.dt_bias[hv]); gal = bf2f(p.a_log[hv]);
+    }
+    const float sc = warp == 0 ? p.q_scale : p.k_scale;
+    const float vtap[4] = {bf_lo(vw.x), bf_hi(vw.x), bf_lo(vw.y), bf_hi(vw.y)};
+#pragma unroll 1
+    for (int t = 0; t < p.T; ++t) {  // the window slides through the registers: rows t .. t+3 sit in [0..3]
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float xs[4] = {bf_lo(xr[i].x), bf_hi(xr[i].x), bf_lo(xr[i].y), bf_hi(xr[i].y)};
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float tap = i == 0 ? bf_lo(wr[r].x) : i == 1 ? bf_hi(wr[r].x) : i == 2 ? bf_lo(wr[r].y) : bf_hi(wr[r].y);
+          acc[r] = fmaf(xs[r], tap, acc[r]);
+        }
+      }
+      float yv[4];
+      float sum = 0.f;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) { yv[r] = silu_bf_call(bfr(acc[r])); sum = fmaf(yv[r], yv[r], sum); }
+      sum = warp_sum(sum);
+      const float inv = orn_rsqrtf(sum / 128.0f + p.eps);
+      float* dst = warp == 0 ? s_q[t] : s_k[t];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) dst[4 * lane + r] = bfr(sc * bfr(yv[r] * inv));
+      if (lir == 0) {  // the value channel of this thread's state row
+        float av = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) av = fmaf(bf2f(vr[i]), vtap[i], av);
+        s_v[t][threadIdx.x >> 2] = silu_bf_call(bfr(av));
+      }
+#pragma unroll
+      for (int i = 0; i + 1 < NR; ++i) { xr[i] = xr[i + 1]; vr[i] = vr[i + 1]; }
+    }
+    if (threadIdx.x < p.T) {
+      const float sp = softplus_bf_call(bfr(ga + gdt));
+      const float decay = expf_call(gal);
+      s_g[threadIdx.x] = expf_call((-decay) * sp);
+      s_beta[threadIdx.x] = sigmoid_bf_call(gb);
+    }
+  } else {
   for (int t = 0; t < p.T; ++t) {
     const int c0 = (warp == 0 ? hk * 128 : key_dim + hk * 128) + 4 * lane;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1313,6 +1379,7 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
     const float decay = expf_call(bf2f(p.a_log[hv]));
     s_g[t] = expf_call((-decay) * sp);
     s_beta[t] = sigmoid_bf_call(bf2f(p.b_in[i]));
+  }
   }
   __syncthreads();
   // ---- recurrence (kernels/gated_delta.metal:36-142)
@@ -1790,7 +1857,8 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
   p.arrivals = reinterpret_cast<unsigned int*>(ctx->dev_err) + 64;
   if (gated_out != nullptr && Hv > 512) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gdn: more than 512 value heads");
   dim3 grid(128 / kGdnRows, Hv);
-  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn, grid, dim3(kGdnRows * 4), 0, p));
+  if (Kc == 4) ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<true>, grid, dim3(kGdnRows * 4), 0, p));
+  else ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<false>, grid, dim3(kGdnRows * 4), 0, p));
   return orn_launch_check(ctx, "k_gdn");
 }
 
