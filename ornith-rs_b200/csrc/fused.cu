@@ -1257,7 +1257,6 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
   __shared__ float s_q[kGdnMaxT][128], s_k[kGdnMaxT][128], s_v[kGdnMaxT][kGdnRows];
   __shared__ float s_g[kGdnMaxT], s_beta[kGdnMaxT];
   pdl_trigger();
-  pdl_wait();
   const int hv = blockIdx.y;
   const int hk = hv / (p.Hv / p.Hk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1276,6 +1275,10 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
     const float4 v4 = *reinterpret_cast<const float4*>(sin + 4 * i);
     S[4 * i] = v4.x; S[4 * i + 1] = v4.y; S[4 * i + 2] = v4.z; S[4 * i + 3] = v4.w;
   }
+  // The state and the ring position were written by an earlier step (a graph launch, a copy or a
+  // host read lies in between), not by the kernel this one may overlap: only what follows reads
+  // the previous kernel's output.
+  pdl_wait();
   // ---- front end (kernels/gdn_front.metal:65-190): warp 0 -> q head, warp 1 -> k head
   if constexpr (TAPS4) {
     // Every global read of the front end is requested here, before any arithmetic, so that the
@@ -1857,8 +1860,18 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
   p.arrivals = reinterpret_cast<unsigned int*>(ctx->dev_err) + 64;
   if (gated_out != nullptr && Hv > 512) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gdn: more than 512 value heads");
   dim3 grid(128 / kGdnRows, Hv);
-  if (Kc == 4) ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<true>, grid, dim3(kGdnRows * 4), 0, p));
-  else ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<false>, grid, dim3(kGdnRows * 4), 0, p));
+  // Unused dynamic shared memory caps the kernel at two CTAs per SM.  As a programmatic dependent
+  // its CTAs become resident while the previous kernel drains, and without the cap the first SMs
+  // to come free would take sixteen CTAs each instead of the grid spreading over the whole part.
+  const size_t pad = 100 * 1024;
+  static bool granted = false;  // the kernel also has static shared memory: ask for the pad, not for the maximum
+  if (!granted) {
+    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_gdn<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pad));
+    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_gdn<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pad));
+    granted = true;
+  }
+  if (Kc == 4) ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<true>, grid, dim3(kGdnRows * 4), pad, p));
+  else ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<false>, grid, dim3(kGdnRows * 4), pad, p));
   return orn_launch_check(ctx, "k_gdn");
 }
 

@@ -21,10 +21,11 @@ struct orn_ctx {
   int* dev_err = nullptr;  // set by a kernel whose bounded wait ran out
   struct orn_ktime* kt = nullptr;  // per-kernel device times when ORN_KTIME=1 (eager launches only)
   // Kernel classes launched as programmatic dependents (bit 0 norm + mat-vec, 1 expert up, 2 expert
-  // down, 3 gated-delta, 4 attention).  Measured on the replayed decode graph: bit 0 alone +3 %,
-  // adding the expert kernels nothing or worse, the gated-delta kernel -8 %.  ORN_PDL_MASK overrides,
-  // ORN_NO_PDL=1 clears it.
-  int pdl_mask = 1;
+  // down, 3 gated-delta, 4 attention).  Measured on the replayed decode graph: bit 0 alone +3 %;
+  // the gated-delta kernel +0.6 % once it is capped at two CTAs per SM (uncapped -8 %: its small
+  // CTAs pile onto the first SMs the previous kernel leaves); expert up and attention +0.3 %;
+  // expert down -4 %, so it stays a plain launch.  ORN_PDL_MASK overrides, ORN_NO_PDL=1 clears it.
+  int pdl_mask = 27;
 };
 
 // Records an event after the launch just made and attributes the device time
