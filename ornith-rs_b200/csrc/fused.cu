@@ -1569,17 +1569,31 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) { qs[i] = s_q[8 * lane + i] * p.scale; o[i] = 0.f; }
   float mx = -INFINITY, sm = 0.f;
+  // a warp's next cache row is requested before the current one is folded in: the loop body has
+  // out-of-line calls, so without this every iteration would pay a full memory round trip
+  uint4 kr = make_uint4(0u, 0u, 0u, 0u), vr = kr;
+  auto fetch = [&](int n, uint4& kq, uint4& vq) {
+    if (n >= pos) {
+      vq = ldg128(p.v + ((size_t)(n - pos) * p.Hkv + kvh) * HD + 8 * lane);
+    } else {
+      const size_t rowoff = ((size_t)kvh * p.cap + n) * HD + 8 * lane;
+      kq = *reinterpret_cast<const uint4*>(p.kc + rowoff);
+      vq = *reinterpret_cast<const uint4*>(p.vc + rowoff);
+    }
+  };
+  if (warp < L) fetch(warp, kr, vr);
   for (int n = warp; n < L; n += 32) {
+    uint4 kn = kr, vn = vr;
+    if (n + 32 < L) fetch(n + 32, kn, vn);
     float kf[8], vf[8];
     if (n >= pos) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) kf[i] = s_knew[n - pos][8 * lane + i];
-      widen8(ldg128(p.v + ((size_t)(n - pos) * p.Hkv + kvh) * HD + 8 * lane), vf);
     } else {
-      const size_t rowoff = ((size_t)kvh * p.cap + n) * HD + 8 * lane;
-      widen8(*reinterpret_cast<const uint4*>(p.kc + rowoff), kf);
-      widen8(*reinterpret_cast<const uint4*>(p.vc + rowoff), vf);
+      widen8(kr, kf);
     }
+    widen8(vr, vf);
+    kr = kn; vr = vn;
     float acc = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc = fmaf(qs[i], kf[i], acc);
