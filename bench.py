@@ -254,7 +254,6 @@ def ours(args):
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local)
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep NCCL's banner off stdout
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_pkg()
     ctx = pkg.Context(local)
@@ -337,7 +336,7 @@ def ours(args):
     }
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_arm(pkg, ctx)
-    print(json.dumps(line))
+    emit(line)
     ctx.close()
     if dist is not None:
         dist.destroy_process_group()
@@ -357,7 +356,6 @@ def ep_layer(args):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep NCCL's banner off stdout
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_pkg()
     from ornith_rs_b200 import ep
@@ -415,7 +413,7 @@ def ep_layer(args):
     dev_ms, wall = reduce_max_over_ranks([dev_ms, wall], dist, "cuda")
     if rank == 0:
         rows = ROWS * args.steps
-        print(json.dumps({
+        emit({
             "metric": "ep_moe_layer_rows_per_s", "value": rows / (dev_ms * 1e-3), "unit": "rows/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 activations, f32 accumulate",
@@ -429,7 +427,7 @@ def ep_layer(args):
             "e2e": {"value": rows / wall, "unit": "rows/s", "h2d_bytes_per_step": R * H * 2,
                     "d2h_bytes_per_step": R * H * 2 + R * k * 4},
             "gpu_launches": launches, "clocks": clocks, "checksum": int(check.item()),
-        }))
+        })
     # the context (and its stream) stays open until the process ends: torch buffers that were used
     # on that stream are still alive here, and freeing them after the stream is gone is an error
     ctx.sync()
@@ -447,7 +445,7 @@ def reference(args):
     try:
         ctx = pkg.Context(0)
     except Exception as e:  # the weights of the sample are generated on the GPU
-        print(json.dumps({"impl": "reference", "unavailable": "no CUDA device to generate the sample weights: %s" % e}))
+        emit({"impl": "reference", "unavailable": "no CUDA device to generate the sample weights: %s" % e})
         return
     cb = cpu_arm(pkg, ctx, max_seconds=max(10.0, 8.0 * args.steps))
     line = {
@@ -459,11 +457,30 @@ def reference(args):
         "cpu_baseline": cb,
         "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
     ctx.close()
 
 
+_RESULT_FD = None
+
+
+def emit(line):
+    """The one JSON line, on the process's original stdout."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    # Libraries write banners to stdout (NCCL prints its version there): from here on file
+    # descriptor 1 is stderr, and only `emit` writes to the original stdout.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
