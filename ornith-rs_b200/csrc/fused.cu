@@ -1109,13 +1109,17 @@ struct MoeDownParams {
 };
 
 // Task = (token m, group of RT consecutive output columns).  Consecutive columns are consecutive
-// weight rows of one expert, so one bulk copy brings a group's rows of one routed expert.  Per
-// task the warp consumes the k routed tiles in ascending j (the combine's order) and then the
-// shared expert's tile.  After the butterfly each lane holds one column's sum, so the bf16
-// combine runs per lane without further exchange.
+// weight rows of one expert, so one bulk copy brings a group's rows of one routed expert.  A task
+// belongs to a PAIR of warps: the even warp takes the first half of the routed experts, the odd
+// warp the second half and the shared expert, so the serial chain of tiles per warp is half as
+// long and 16 warps hide each other's latencies.  After the butterfly each lane holds one column's
+// sum; the even warp runs its part of the bf16 combine (ascending j) and hands the running value
+// to the odd warp through shared memory, which adds its own terms in order and stores.
+constexpr int kDownThreads = 512;
+
 template <int KIND, int KC>
-__global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, uint32_t slot_bytes, int depth,
-                                                               uint32_t ring_off, int* err) {
+__global__ void __launch_bounds__(kDownThreads, 1) k_moe_down(MoeDownParams P, uint32_t slot_bytes, int depth,
+                                                                uint32_t ring_off, int* err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* smem = reinterpret_cast<float*>(smem_raw);
   constexpr int RT = moe_rows(KIND, KC);
@@ -1126,54 +1130,73 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, ui
   next = stage_carve(next, KIND, M, P.SI, XS);
   float* wts = next;                                   // [M][k] normalised scores
   float* gsig = wts + rows;                            // [M]
-  uint32_t* inds = reinterpret_cast<uint32_t*>(gsig + M);
+  float* xch = gsig + M;                               // [2][pairs][32] running combine values
+  uint32_t* inds = reinterpret_cast<uint32_t*>(xch + 2 * (kDownThreads / 64) * 32);
   next = reinterpret_cast<float*>(inds + rows);
   float* lin = smem + (((next - smem) + 31) & ~31);    // [rows][I] then [M][SI]
   float* lin2 = lin + (size_t)rows * P.I;
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_trigger();
   Ring R;
   ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
   pdl_wait();
-  // first batch of the routed activations into registers, so that their latency overlaps the
-  // routing table's and the first weight requests
+  // the first batch of routed activations and the shared expert's into registers, so that their
+  // latency overlaps the routing table's and the first weight requests
   constexpr int kPre = 4;
-  uint2 pre[kPre];
+  uint2 pre[kPre], spre = make_uint2(0u, 0u);
 #pragma unroll
   for (int j = 0; j < kPre; ++j) {
     const int i = (threadIdx.x + j * blockDim.x) * 4;
     if (i < rows * P.I) pre[j] = __ldg(reinterpret_cast<const uint2*>(P.act + i));
   }
-  if (threadIdx.x < rows) inds[threadIdx.x] = P.inds[threadIdx.x];
+  if (threadIdx.x * 4 < M * P.SI) spre = __ldg(reinterpret_cast<const uint2*>(P.sact + threadIdx.x * 4));
+  float sc_mine = 0.f, gs_mine = 0.f;
+  if (threadIdx.x < rows) {
+    inds[threadIdx.x] = P.inds[threadIdx.x];
+    sc_mine = bf2f(P.scores[threadIdx.x]);
+    if (threadIdx.x < M) gs_mine = bf2f(P.gs[threadIdx.x]);
+    wts[threadIdx.x] = sc_mine;  // raw scores first: the denominators below read all k of a token
+  }
   __syncthreads();
-  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), GW = gridDim.x * (blockDim.x >> 5);
+  // warp pair `gp` walks the tasks; this warp's tiles of a task are q = 0 .. nt-1
+  const int h = warp & 1, pair = warp >> 1, npairs = blockDim.x >> 6;
+  const int gp = blockIdx.x * npairs + pair, GP = gridDim.x * npairs;
   const int ngroups = (P.H + RT - 1) / RT;
   const int total = M * ngroups;
+  const int k0 = P.k >> 1;
+  const int nt = h ? P.k - k0 + 1 : k0;  // the odd warp's last tile is the shared expert's
   const RecGeom geo = rec_geom(KIND, P.I), sgeo = rec_geom(KIND, P.SI);
-  int pg = gw, pq = 0, pslot = 0;  // producer: task, tile within the task (k = the shared expert's)
-  auto issue = [&]() {
-    if (lane == 0) {
-      const int m = pg / ngroups, grp = pg - m * ngroups;
-      const int c0 = grp * RT;
-      const int n = min(RT, P.H - c0);
-      if (pq < P.k) ring_fill(R, pslot, P.down.w + ((size_t)inds[m * P.k + pq] * P.H + c0) * geo.rec, n * geo.rec);
-      else ring_fill(R, pslot, P.sh_down.w + (size_t)c0 * sgeo.rec, n * sgeo.rec);
-    }
-    if (++pq > P.k) { pq = 0; pg += GW; }
+  int pg = gp, pq = 0, pslot = 0;  // producer: task, tile within the task
+  auto fill = [&](int task, int q, int slot) {  // one lane: request tile q of `task` into `slot`
+    const int m = task / ngroups, grp = task - m * ngroups;
+    const int c0 = grp * RT;
+    const int n = min(RT, P.H - c0);
+    const int j = (h ? k0 : 0) + q;
+    if (j < P.k) ring_fill(R, slot, P.down.w + ((size_t)inds[m * P.k + j] * P.H + c0) * geo.rec, n * geo.rec);
+    else ring_fill(R, slot, P.sh_down.w + (size_t)c0 * sgeo.rec, n * sgeo.rec);
+  };
+  // the first `depth` tiles of the warp are requested by as many lanes at once (a request costs
+  // one lane some hundred cycles of address arithmetic and copy-engine hand-over)
+  if (nt > 0 && pg < total) {
+    const int ahead = min(depth, nt * ((total - pg + GP - 1) / GP));
+    if (lane < ahead) fill(pg + (lane / nt) * GP, lane % nt, lane);
+    pg += (ahead / nt) * GP;
+    pq = ahead % nt;
+    pslot = ahead == depth ? 0 : ahead;
+  }
+  auto issue = [&]() {  // steady state: lane 0 refills the slot just consumed
+    if (lane == 0) fill(pg, pq, pslot);
+    if (++pq == nt) { pq = 0; pg += GP; }
     if (++pslot == depth) pslot = 0;
   };
-  // two tiles per warp now, the rest once the activations are staged: a full ring of requests
-  // would hold every warp at the copy engine (about 50 cycles per request) before it can stage
-  int primed = 0;
-  for (; primed < 2 && primed < depth && pg < total; ++primed) issue();
   if (threadIdx.x < rows) {  // thread (m, j): the normalised score of routed expert j of token m
-    const int m = threadIdx.x / P.k, j = threadIdx.x - m * P.k;
-    float denom = 0.f;
-    if (P.normalize)
-      for (int jj = 0; jj < P.k; ++jj) denom = bfr(bf2f(P.scores[m * P.k + jj]) + denom);
-    const float sc = bf2f(P.scores[m * P.k + j]);
-    wts[threadIdx.x] = P.normalize ? bfr(sc / denom) : sc;
-    if (j == 0) gsig[m] = sigmoid_bf_call(bf2f(P.gs[m]));
+    if (P.normalize) {
+      const int m = threadIdx.x / P.k;
+      float denom = 0.f;
+      for (int jj = 0; jj < P.k; ++jj) denom = bfr(wts[m * P.k + jj] + denom);
+      sc_mine = bfr(sc_mine / denom);
+    }
+    if (threadIdx.x < M) gsig[threadIdx.x] = sigmoid_bf_call(gs_mine);
   }
 #pragma unroll
   for (int j = 0; j < kPre; ++j) {
@@ -1184,43 +1207,59 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_down(MoeDownParams P, ui
     const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.act + i));
     *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
   }
-  for (int i = threadIdx.x * 4; i < M * P.SI; i += blockDim.x * 4) {
+  if (threadIdx.x * 4 < M * P.SI)
+    *reinterpret_cast<float4*>(lin2 + threadIdx.x * 4) = make_float4(bf_lo(spre.x), bf_hi(spre.x), bf_lo(spre.y), bf_hi(spre.y));
+  for (int i = (threadIdx.x + blockDim.x) * 4; i < M * P.SI; i += blockDim.x * 4) {
     const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.sact + i));
     *reinterpret_cast<float4*>(lin2 + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
   }
-  __syncthreads();
+  __syncthreads();  // every thread has read the raw scores: the normalised ones may replace them
+  if (threadIdx.x < rows) wts[threadIdx.x] = sc_mine;
   stage_fill<KIND>(lin, P.I, X);
   stage_fill<KIND>(lin2, P.SI, XS);
   __syncthreads();
-  for (; primed < depth && pg < total; ++primed) issue();
-  int slot = 0;
+  int slot = 0, round = 0;
   uint32_t parity = 0;
-  for (int cg = gw; cg < total; cg += GW) {
+  bool ok = true;  // a wait that ran out: no more waits or stores, but the pair's barriers are kept
+  for (int cg = gp; cg < total; cg += GP, ++round) {
     const int m = cg / ngroups, grp = cg - m * ngroups;
     const int c0 = grp * RT;
-    float acc = 0.f;  // this lane's column, combined so far
-    for (int q = 0; q <= P.k; ++q) {
-      if (!ring_wait(R, slot, parity)) return;
+    float acc = 0.f;                               // even warp: the running combine value
+    float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;  // odd warp: its routed terms, newest in t3
+    float sh = 0.f;
+    int which = 0;
+    for (int q = 0; q < nt; ++q) {
+      ok = ok && ring_wait(R, slot, parity);
       const uint8_t* buf = R.buf + (size_t)slot * slot_bytes;
       float d[RT];
 #pragma unroll
       for (int r = 0; r < RT; ++r) d[r] = 0.f;
-      const bool routed = q < P.k;  // one copy of the dot serves the routed and the shared tile
-      tile_dot<KIND, 1, RT>(buf, routed ? P.down : P.sh_down, routed ? X : XS, routed ? m * P.k + q : m, lane, d);
+      const int j = (h ? k0 : 0) + q;
+      const bool routed = j < P.k;  // one copy of the dot serves the routed and the shared tile
+      if (ok) tile_dot<KIND, 1, RT>(buf, routed ? P.down : P.sh_down, routed ? X : XS, routed ? m * P.k + j : m, lane, d);
       __syncwarp();
-      if (pg < total) {
+      if (pg < total && ok) {
         if (lane == 0) fence_proxy_async();
         issue();
       }
-      int which;
       const float v = rs_butterfly<RT>(d, lane, which);
-      if (q < P.k) {
-        acc = bfr(bfr(bfr(v) * wts[m * P.k + q]) + acc);
-      } else {
-        const int c = c0 + which;
-        if ((lane & (32 / RT - 1)) == 0 && c < P.H) P.out[(size_t)m * P.H + c] = f2bf(acc + bfr(gsig[m] * bfr(v)));
-      }
+      if (!routed) sh = bfr(gsig[m] * bfr(v));
+      else if (h == 0) acc = bfr(bfr(bfr(v) * wts[m * P.k + j]) + acc);
+      else { t0 = t1; t1 = t2; t2 = t3; t3 = bfr(bfr(v) * wts[m * P.k + j]); }
       if (++slot == depth) { slot = 0; parity ^= 1; }
+    }
+    float* cell = xch + ((size_t)(round & 1) * npairs + pair) * 32 + lane;
+    if (h == 0) *cell = acc;
+    asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");  // the two warps of the pair
+    if (h == 1) {
+      acc = *cell;
+      const int mine = nt - 1;  // routed terms of this warp, oldest first
+      if (mine >= 4) acc = bfr(t0 + acc);
+      if (mine >= 3) acc = bfr(t1 + acc);
+      if (mine >= 2) acc = bfr(t2 + acc);
+      if (mine >= 1) acc = bfr(t3 + acc);
+      const int c = c0 + which;
+      if (ok && (lane & (32 / RT - 1)) == 0 && c < P.H) P.out[(size_t)m * P.H + c] = f2bf(acc + sh);
     }
   }
 }
@@ -1768,7 +1807,7 @@ template <int KIND, int KC>
 int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
   const int M = P.M;
   const int rows = M * P.k;
-  size_t fixed = (stage_floats(KIND, rows, P.I) + stage_floats(KIND, M, P.SI) + 2 * rows + M) * sizeof(float);
+  size_t fixed = (stage_floats(KIND, rows, P.I) + stage_floats(KIND, M, P.SI) + 2 * rows + M + 2 * (kDownThreads / 64) * 32) * sizeof(float);
   fixed = (fixed + 127) & ~(size_t)127;
   fixed += ((size_t)rows * P.I + (size_t)M * P.SI + 8) * sizeof(float);
   const uint32_t r0 = moe_rows(KIND, KC) * P.down.rec, r1 = moe_rows(KIND, KC) * P.sh_down.rec;
@@ -1776,11 +1815,11 @@ int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
   int depth;
   uint32_t ring_off;
   size_t bytes;
-  int rc = plan_smem(ctx, fixed, slot, kMoeThreads / 32, &depth, &ring_off, &bytes);
+  int rc = plan_smem(ctx, fixed, slot, kDownThreads / 32, &depth, &ring_off, &bytes);
   if (rc != ORN_OK) return rc;
   rc = set_smem(ctx, k_moe_down<KIND, KC>, bytes);
   if (rc != ORN_OK) return rc;
-  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 2, k_moe_down<KIND, KC>, dim3(ctx->sm_count), dim3(kMoeThreads), bytes,
+  ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 2, k_moe_down<KIND, KC>, dim3(ctx->sm_count), dim3(kDownThreads), bytes,
                                            P, slot, depth, ring_off, ctx->dev_err));
   return orn_launch_check(ctx, launch_label(ctx, "k_moe_down", M, KIND, P.H, P.I));
 }
