@@ -91,6 +91,42 @@ ORN_D float* stage_carve(float* base, int kind, int rows, int K, XStage& X) {
   return X.sums + (size_t)rows * X.units * kind_ns(kind);
 }
 
+// The staged place of the four consecutive activations x[k .. k+3] (k a multiple of 4) of row m:
+// the inverse of src_index.  Formats without per-unit sums can be staged piece by piece straight
+// from the registers a thread loaded them into, with no linear copy of the row in between.
+template <int KIND> ORN_D void unit_of(int k, int& u, int& p);
+template <> ORN_D void unit_of<ORN_A8>(int k, int& u, int& p) { u = k >> 4; p = (k & 15) >> 2; }
+template <> ORN_D void unit_of<ORN_BF16>(int k, int& u, int& p) { u = k >> 3; p = (k & 7) >> 2; }
+template <> ORN_D void unit_of<ORN_Q6K>(int k, int& u, int& p) {
+  const int r = k & 255, r2 = r & 127;
+  u = (k >> 8) * 16 + (r >> 7) * 8 + ((r2 & 31) >> 2);
+  p = r2 >> 5;
+}
+template <> ORN_D void unit_of<ORN_Q4K>(int k, int& u, int& p) {
+  const int r = k & 255, r2 = r & 63, r3 = r2 & 31;
+  u = (k >> 8) * 8 + (r >> 6) * 2 + (r3 >> 4);
+  p = (r2 >> 5) * 4 + ((r3 & 15) >> 2);
+}
+template <int KIND>
+ORN_D void stage_piece(const XStage& X, int m, int k, float4 v) {
+  constexpr int P = Lay<KIND>::P;
+  int u, p;
+  unit_of<KIND>(k, u, p);
+  reinterpret_cast<float4*>(X.xs)[((size_t)(m * X.S + (u >> 5)) * P + p) * 32 + (u & 31)] = v;
+}
+// zero the unit slots behind the last unit of every row (rows whose unit count is not a multiple of 32)
+template <int KIND>
+ORN_D void stage_zero_tail(const XStage& X) {
+  constexpr int P = Lay<KIND>::P;
+  const int tail = X.S * 32 - X.units;
+  if (tail == 0) return;
+  for (int idx = threadIdx.x; idx < X.rows * tail * P; idx += blockDim.x) {
+    const int m = idx / (tail * P), rem = idx - m * tail * P;
+    const int u = X.units + rem / P, p = rem % P;
+    reinterpret_cast<float4*>(X.xs)[((size_t)(m * X.S + (u >> 5)) * P + p) * 32 + (u & 31)] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
 // lin: [rows][K] floats (row stride `stride`) -> stage, by the threads tid of nthreads (a subset of
 // the CTA may stage while other warps do something else); no sync inside.  A thread owns whole
 // units of any row (rows x unit slots are one flat index space, so short rows keep every thread
@@ -1128,12 +1164,14 @@ __global__ void __launch_bounds__(kDownThreads, 1) k_moe_down(MoeDownParams P, u
   XStage X, XS;
   float* next = stage_carve(smem, KIND, rows, P.I, X);
   next = stage_carve(next, KIND, M, P.SI, XS);
+  constexpr bool kDirect = Lay<KIND>::NS == 0;       // staged straight from registers (no per-unit sums)
   float* wts = next;                                   // [M][k] normalised scores
-  float* gsig = wts + rows;                            // [M]
+  float* raw = wts + rows;                             // [M][k] the router's scores
+  float* gsig = raw + rows;                            // [M]
   float* xch = gsig + M;                               // [2][pairs][32] running combine values
   uint32_t* inds = reinterpret_cast<uint32_t*>(xch + 2 * (kDownThreads / 64) * 32);
   next = reinterpret_cast<float*>(inds + rows);
-  float* lin = smem + (((next - smem) + 31) & ~31);    // [rows][I] then [M][SI]
+  float* lin = smem + (((next - smem) + 31) & ~31);    // [rows][I] then [M][SI], only when !kDirect
   float* lin2 = lin + (size_t)rows * P.I;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_trigger();
@@ -1155,7 +1193,7 @@ __global__ void __launch_bounds__(kDownThreads, 1) k_moe_down(MoeDownParams P, u
     inds[threadIdx.x] = P.inds[threadIdx.x];
     sc_mine = bf2f(P.scores[threadIdx.x]);
     if (threadIdx.x < M) gs_mine = bf2f(P.gs[threadIdx.x]);
-    wts[threadIdx.x] = sc_mine;  // raw scores first: the denominators below read all k of a token
+    raw[threadIdx.x] = sc_mine;  // the denominators below read all k of a token
   }
   __syncthreads();
   // warp pair `gp` walks the tasks; this warp's tiles of a task are q = 0 .. nt-1
@@ -1193,30 +1231,41 @@ __global__ void __launch_bounds__(kDownThreads, 1) k_moe_down(MoeDownParams P, u
     if (P.normalize) {
       const int m = threadIdx.x / P.k;
       float denom = 0.f;
-      for (int jj = 0; jj < P.k; ++jj) denom = bfr(wts[m * P.k + jj] + denom);
+      for (int jj = 0; jj < P.k; ++jj) denom = bfr(raw[m * P.k + jj] + denom);
       sc_mine = bfr(sc_mine / denom);
     }
+    wts[threadIdx.x] = sc_mine;
     if (threadIdx.x < M) gsig[threadIdx.x] = sigmoid_bf_call(gs_mine);
   }
+  // widen a loaded piece and put it where the dot will read it (or into the linear copy)
+  auto place = [&](bool shared_row, int i, uint2 v) {
+    const float4 f = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+    if (kDirect) {
+      const int K = shared_row ? P.SI : P.I;
+      const int m = i / K;
+      stage_piece<KIND>(shared_row ? XS : X, m, i - m * K, f);
+    } else {
+      *reinterpret_cast<float4*>((shared_row ? lin2 : lin) + i) = f;
+    }
+  };
 #pragma unroll
   for (int j = 0; j < kPre; ++j) {
     const int i = (threadIdx.x + j * blockDim.x) * 4;
-    if (i < rows * P.I) *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(pre[j].x), bf_hi(pre[j].x), bf_lo(pre[j].y), bf_hi(pre[j].y));
+    if (i < rows * P.I) place(false, i, pre[j]);
   }
-  for (int i = (threadIdx.x + kPre * blockDim.x) * 4; i < rows * P.I; i += blockDim.x * 4) {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.act + i));
-    *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+  for (int i = (threadIdx.x + kPre * blockDim.x) * 4; i < rows * P.I; i += blockDim.x * 4)
+    place(false, i, __ldg(reinterpret_cast<const uint2*>(P.act + i)));
+  if (threadIdx.x * 4 < M * P.SI) place(true, threadIdx.x * 4, spre);
+  for (int i = (threadIdx.x + blockDim.x) * 4; i < M * P.SI; i += blockDim.x * 4)
+    place(true, i, __ldg(reinterpret_cast<const uint2*>(P.sact + i)));
+  if (kDirect) {
+    stage_zero_tail<KIND>(X);
+    stage_zero_tail<KIND>(XS);
+  } else {
+    __syncthreads();
+    stage_fill<KIND>(lin, P.I, X);
+    stage_fill<KIND>(lin2, P.SI, XS);
   }
-  if (threadIdx.x * 4 < M * P.SI)
-    *reinterpret_cast<float4*>(lin2 + threadIdx.x * 4) = make_float4(bf_lo(spre.x), bf_hi(spre.x), bf_lo(spre.y), bf_hi(spre.y));
-  for (int i = (threadIdx.x + blockDim.x) * 4; i < M * P.SI; i += blockDim.x * 4) {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.sact + i));
-    *reinterpret_cast<float4*>(lin2 + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
-  }
-  __syncthreads();  // every thread has read the raw scores: the normalised ones may replace them
-  if (threadIdx.x < rows) wts[threadIdx.x] = sc_mine;
-  stage_fill<KIND>(lin, P.I, X);
-  stage_fill<KIND>(lin2, P.SI, XS);
   __syncthreads();
   int slot = 0, round = 0;
   uint32_t parity = 0;
@@ -1807,9 +1856,10 @@ template <int KIND, int KC>
 int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
   const int M = P.M;
   const int rows = M * P.k;
-  size_t fixed = (stage_floats(KIND, rows, P.I) + stage_floats(KIND, M, P.SI) + 2 * rows + M + 2 * (kDownThreads / 64) * 32) * sizeof(float);
+  size_t fixed = (stage_floats(KIND, rows, P.I) + stage_floats(KIND, M, P.SI) + 3 * rows + M + 2 * (kDownThreads / 64) * 32) * sizeof(float);
   fixed = (fixed + 127) & ~(size_t)127;
-  fixed += ((size_t)rows * P.I + (size_t)M * P.SI + 8) * sizeof(float);
+  if (kind_ns(KIND) != 0)  // formats with per-unit sums stage through a linear copy of the rows
+    fixed += ((size_t)rows * P.I + (size_t)M * P.SI + 8) * sizeof(float);
   const uint32_t r0 = moe_rows(KIND, KC) * P.down.rec, r1 = moe_rows(KIND, KC) * P.sh_down.rec;
   const uint32_t slot = r0 > r1 ? r0 : r1;
   int depth;
