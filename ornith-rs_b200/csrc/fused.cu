@@ -673,8 +673,10 @@ struct AddNormIn {
 
 // scratch: red[M*32 + M] floats.  Every loop walks (row m, 4-element group) so
 // that no index needs a division and global traffic is at least 64-bit.
-template <int M>
-ORN_D void run_prologue(const Prologue& P, const AddNormIn<M>& in, float* lin, float* red) {
+// PRO_ADDNORM leaves the normalised rows in the stages X (pieces go from the registers to their
+// staged places, unit sums by a 4-lane chain); the other modes leave them in `lin` for stage_fill.
+template <int M, int MASK>
+ORN_D void run_prologue(const Prologue& P, const AddNormIn<M>& in, float* lin, float* red, const XStage* X) {
   const int K = P.K;
   float* inv = red + M * 32;
   if (P.mode == PRO_ADDNORM) {
@@ -734,21 +736,54 @@ ORN_D void run_prologue(const Prologue& P, const AddNormIn<M>& in, float* lin, f
         for (int m = 0; m < M; ++m) {
           const float* v = hv[m][g];
           const float iv = inv[m];
-          *reinterpret_cast<float4*>(lin + (size_t)m * K + c0) =
-              make_float4(bfr(wv[0] * bfr(v[0] * iv)), bfr(wv[1] * bfr(v[1] * iv)), bfr(wv[2] * bfr(v[2] * iv)),
-                          bfr(wv[3] * bfr(v[3] * iv)));
+          const float4 f = make_float4(bfr(wv[0] * bfr(v[0] * iv)), bfr(wv[1] * bfr(v[1] * iv)),
+                                       bfr(wv[2] * bfr(v[2] * iv)), bfr(wv[3] * bfr(v[3] * iv)));
+          if (MASK & (1 << ORN_Q4K)) stage_piece<ORN_Q4K>(X[ORN_Q4K], m, c0, f);
+          if (MASK & (1 << ORN_Q6K)) stage_piece<ORN_Q6K>(X[ORN_Q6K], m, c0, f);
+          if (MASK & (1 << ORN_A8)) stage_piece<ORN_A8>(X[ORN_A8], m, c0, f);
+          if (MASK & (1 << ORN_BF16)) stage_piece<ORN_BF16>(X[ORN_BF16], m, c0, f);
+          if (P.norm_out != nullptr && blockIdx.x == 0) {
+            uint2 o;
+            o.x = (uint32_t)f2bf(f.x) | ((uint32_t)f2bf(f.y) << 16);
+            o.y = (uint32_t)f2bf(f.z) | ((uint32_t)f2bf(f.w) << 16);
+            *reinterpret_cast<uint2*>(P.norm_out + (size_t)m * K + c0) = o;
+          }
+          if (MASK & ((1 << ORN_A8) | (1 << ORN_Q4K))) {
+            // The 16 activations of an aligned run (four lanes' pieces) are one unit of the 8-bit
+            // format and half a unit of Q4_K: their sum, added in ascending order from zero, passes
+            // from lane to lane (c0 < K holds for whole warps: K is a multiple of 256).
+            float run = 0.f;
+#pragma unroll
+            for (int step = 0; step < 4; ++step) {
+              if ((lane & 3) == step) { run = run + f.x; run = run + f.y; run = run + f.z; run = run + f.w; }
+              const float up = __shfl_up_sync(0xffffffffu, run, 1);
+              if ((lane & 3) == step + 1) run = up;
+            }
+            if ((lane & 3) == 3) {
+              if (MASK & (1 << ORN_A8)) X[ORN_A8].sums[(size_t)m * X[ORN_A8].units + (c0 >> 4)] = run;
+              if (MASK & (1 << ORN_Q4K)) {
+                int u, pp;
+                unit_of<ORN_Q4K>(c0, u, pp);
+                X[ORN_Q4K].sums[((size_t)m * X[ORN_Q4K].units + u) * 2 + (pp >> 2)] = run;
+              }
+            }
+          }
         }
       }
     }
+    if (MASK & (1 << ORN_Q4K)) stage_zero_tail<ORN_Q4K>(X[ORN_Q4K]);
+    if (MASK & (1 << ORN_Q6K)) stage_zero_tail<ORN_Q6K>(X[ORN_Q6K]);
+    if (MASK & (1 << ORN_A8)) stage_zero_tail<ORN_A8>(X[ORN_A8]);
+    if (MASK & (1 << ORN_BF16)) stage_zero_tail<ORN_BF16>(X[ORN_BF16]);
   } else {
     prologue_other(P, M, lin, red);
-  }
-  __syncthreads();
-  if (P.norm_out != nullptr && blockIdx.x == 0) {
+    __syncthreads();
+    if (P.norm_out != nullptr && blockIdx.x == 0) {
 #pragma unroll
-    for (int m = 0; m < M; ++m)
+      for (int m = 0; m < M; ++m)
 #pragma unroll 1
-      for (int c = threadIdx.x; c < K; c += blockDim.x) P.norm_out[(size_t)m * K + c] = f2bf(lin[(size_t)m * K + c]);
+        for (int c = threadIdx.x; c < K; c += blockDim.x) P.norm_out[(size_t)m * K + c] = f2bf(lin[(size_t)m * K + c]);
+    }
   }
 }
 
@@ -897,11 +932,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
     if (mask & (1 << k)) next = stage_carve(next, k, M, P.K, X[k]);
   float* lin = smem + (((next - smem) + 31) & ~31);
   float* red = lin + (size_t)M * P.K;
-  run_prologue<M>(P, pin, lin, red);
-  if (mask & (1 << ORN_Q4K)) stage_fill<ORN_Q4K>(lin, P.K, X[ORN_Q4K]);
-  if (mask & (1 << ORN_Q6K)) stage_fill<ORN_Q6K>(lin, P.K, X[ORN_Q6K]);
-  if (mask & (1 << ORN_A8)) stage_fill<ORN_A8>(lin, P.K, X[ORN_A8]);
-  if (mask & (1 << ORN_BF16)) stage_fill<ORN_BF16>(lin, P.K, X[ORN_BF16]);
+  run_prologue<M, MASK>(P, pin, lin, red, X);
+  if (P.mode != PRO_ADDNORM) {
+    if (mask & (1 << ORN_Q4K)) stage_fill<ORN_Q4K>(lin, P.K, X[ORN_Q4K]);
+    if (mask & (1 << ORN_Q6K)) stage_fill<ORN_Q6K>(lin, P.K, X[ORN_Q6K]);
+    if (mask & (1 << ORN_A8)) stage_fill<ORN_A8>(lin, P.K, X[ORN_A8]);
+    if (mask & (1 << ORN_BF16)) stage_fill<ORN_BF16>(lin, P.K, X[ORN_BF16]);
+  }
   __syncthreads();
   if (late) {
     ring_setup(R, smem_raw + ring_off, slot_bytes, depth, err);
@@ -1069,13 +1106,38 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32
     warp_softmax_topk(P.logits + (size_t)warp * P.E, P.E, P.k, probs + (size_t)warp * P.E, red + warp * 32,
                       inds + warp * P.k, scores + warp * P.k, lane);
   else {
+    // pieces of four activations go from the load straight to their staged places; the sum of an
+    // aligned run of 16 (a unit of the 8-bit format, half a unit of Q4_K) passes along four lanes
+    // in ascending order.  M * H / 4 pieces over whole warps: every round is warp-uniform.
     const int tid = threadIdx.x - 32 * M, nt = blockDim.x - 32 * M;
     for (int i = tid * 4; i < M * P.H; i += nt * 4) {
       const uint2 v = __ldg(reinterpret_cast<const uint2*>(P.x + i));
-      *reinterpret_cast<float4*>(lin + i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+      const float4 f = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+      const int m = i / P.H, k = i - m * P.H;
+      stage_piece<KIND>(X, m, k, f);
+      if (Lay<KIND>::NS > 0) {
+        float run = 0.f;
+#pragma unroll
+        for (int step = 0; step < 4; ++step) {
+          if ((lane & 3) == step) { run = run + f.x; run = run + f.y; run = run + f.z; run = run + f.w; }
+          const float up = __shfl_up_sync(0xffffffffu, run, 1);
+          if ((lane & 3) == step + 1) run = up;
+        }
+        if ((lane & 3) == 3) {
+          int u, pp;
+          unit_of<KIND>(k, u, pp);
+          if (Lay<KIND>::NS == 1) X.sums[(size_t)m * X.units + u] = run;
+          else X.sums[((size_t)m * X.units + u) * 2 + (pp >> 2)] = run;
+        }
+      }
     }
-    asm volatile("bar.sync 1, %0;" ::"r"(nt) : "memory");  // the staging warps only
-    stage_fill_part<KIND>(lin, P.H, X, tid, nt);
+    const int tail = X.S * 32 - X.units;  // empty unit slots behind a row's last unit
+    for (int idx = tid; idx < M * tail * Lay<KIND>::P; idx += nt) {
+      const int m = idx / (tail * Lay<KIND>::P), rem = idx - m * tail * Lay<KIND>::P;
+      const int u = X.units + rem / Lay<KIND>::P, pc = rem % Lay<KIND>::P;
+      reinterpret_cast<float4*>(X.xs)[((size_t)(m * X.S + (u >> 5)) * Lay<KIND>::P + pc) * 32 + (u & 31)] =
+          make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
   __syncthreads();
   // task g = (routed row mj, tile t): RT/2 consecutive output rows of the expert's gate matrix and the
