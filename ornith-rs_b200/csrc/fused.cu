@@ -42,7 +42,7 @@ __device__ __noinline__ float sigmoid_f32_call(float x) { return orn_sigmoid_f32
 __device__ __noinline__ float softplus_bf_call(float x) { return orn_softplus_bf(x); }
 __device__ __noinline__ void sincosf_call(float a, float* sn, float* cs) { orn_sincosf(a, sn, cs); }
 
-constexpr int kMoeThreads = 256;    // 16 warps with half-height tiles measured no faster than 8
+constexpr int kMoeThreads = 512;    // expert up kernel: 16 warps, at verify width each has at most one tile
 constexpr int kFusedThreads = 256;  // one CTA per SM: 8 warps (up to 255 registers each), each with its own weight ring
 
 // ---------------------------------------------------------------------------
@@ -878,7 +878,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
   extern __shared__ __align__(128) uint8_t smem_raw[];
   float* smem = reinterpret_cast<float*>(smem_raw);
   const int lane = threadIdx.x & 31;
-  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // a launch with fewer tiles than warps gives warp w of CTA b the tiles w * CTAs + b, so that it
+  // still spreads over every SM; otherwise a CTA's warps take neighbouring tiles
+  const int gw = J.total >= (int)(gridDim.x * (blockDim.x >> 5)) ? blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)
+                                                                  : (threadIdx.x >> 5) * gridDim.x + blockIdx.x;
   const int GW = gridDim.x * (blockDim.x >> 5);
   // The weights do not depend on the activations, so the kernel is launched as a programmatic
   // dependent: barriers and the first `depth` tiles of every warp are requested while the
@@ -1143,7 +1146,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32
   // task g = (routed row mj, tile t): RT/2 consecutive output rows of the expert's gate matrix and the
   // same rows of its up matrix in one slot, one dot over the RT staged rows, one butterfly
   constexpr int HALF = RT / 2;
-  const int gw = blockIdx.x * (blockDim.x >> 5) + warp, GW = gridDim.x * (blockDim.x >> 5);
+  const int gw = warp * gridDim.x + blockIdx.x, GW = gridDim.x * (blockDim.x >> 5);  // few tiles still reach every SM
   const int ntile = (P.I + HALF - 1) / HALF;
   const int total = M * P.k * ntile;
   const RecGeom geo = rec_geom(KIND, P.H);
@@ -1260,7 +1263,7 @@ __global__ void __launch_bounds__(kDownThreads, 1) k_moe_down(MoeDownParams P, u
   __syncthreads();
   // warp pair `gp` walks the tasks; this warp's tiles of a task are q = 0 .. nt-1
   const int h = warp & 1, pair = warp >> 1, npairs = blockDim.x >> 6;
-  const int gp = blockIdx.x * npairs + pair, GP = gridDim.x * npairs;
+  const int gp = pair * gridDim.x + blockIdx.x, GP = gridDim.x * npairs;  // few tasks still reach every SM
   const int ngroups = (P.H + RT - 1) / RT;
   const int total = M * ngroups;
   const int k0 = P.k >> 1;
