@@ -990,11 +990,13 @@ struct MoeUpParams {
 
 // softmax (mlx softmax.h:10-99, float accumulate) then router_top_k
 // (kernels/moe.metal:568-614) for one token by one warp; results to shared
-__device__ __noinline__ void warp_softmax_topk(const bf16_t* logits, int n, int k, float* probs /*[n] smem*/,
+// kMaxVW virtual warps of 128 logits (so n <= 128 * kMaxVW); the 256-expert instantiation carries
+// half the code of the 512-expert one, and this code runs once per CTA from cold instruction caches
+template <int kMaxVW>
+__device__ __noinline__ void warp_softmax_topk_n(const bf16_t* logits, int n, int k, float* probs /*[n] smem*/,
                              float* red /*[32] smem*/, uint32_t* inds, float* scores, int lane) {
-  // the lane's logits (4 consecutive per virtual warp, up to 512 in all) come in with one round of
-  // loads; the maximum and the exponentials then work from registers
-  constexpr int kMaxVW = 4;
+  // the lane's logits (4 consecutive per virtual warp) come in with one round of loads; the
+  // maximum and the exponentials then work from registers
   const int nvt = (n + 3) / 4;
   const int nvw = (nvt + 31) / 32;
   float xv[kMaxVW][4];
@@ -1054,7 +1056,7 @@ __device__ __noinline__ void warp_softmax_topk(const bf16_t* logits, int n, int 
   // bits: (bits | index) + 1 is a key whose unsigned maximum is exactly that rule, and one
   // hardware warp reduction per round finds it (0 marks entries that are absent, taken, or NaN;
   // with nothing left the round yields index 0, as the comparison form does).
-  constexpr int kMaxPerLane = 16;
+  constexpr int kMaxPerLane = 4 * kMaxVW;
   uint32_t key[kMaxPerLane];
 #pragma unroll
   for (int s = 0; s < kMaxPerLane; ++s) {
@@ -1082,7 +1084,11 @@ __device__ __noinline__ void warp_softmax_topk(const bf16_t* logits, int n, int 
   }
   __syncwarp();
 }
-
+ORN_D void warp_softmax_topk(const bf16_t* logits, int n, int k, float* probs, float* red, uint32_t* inds,
+                             float* scores, int lane) {
+  if (n <= 256) warp_softmax_topk_n<2>(logits, n, k, probs, red, inds, scores, lane);
+  else warp_softmax_topk_n<4>(logits, n, k, probs, red, inds, scores, lane);
+}
 
 template <int KIND, int KC>
 __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32_t slot_bytes, int depth,
