@@ -775,6 +775,53 @@ ORN_D void run_prologue(const Prologue& P, const AddNormIn<M>& in, float* lin, f
     if (MASK & (1 << ORN_Q6K)) stage_zero_tail<ORN_Q6K>(X[ORN_Q6K]);
     if (MASK & (1 << ORN_A8)) stage_zero_tail<ORN_A8>(X[ORN_A8]);
     if (MASK & (1 << ORN_BF16)) stage_zero_tail<ORN_BF16>(X[ORN_BF16]);
+  } else if (P.mode == PRO_PLAIN) {
+    // rows as they are: pieces go from the loads (a batch of four per thread in flight) to their
+    // staged places, unit sums as above.  M * K / 4 pieces over whole warps: rounds are warp-uniform.
+    constexpr int kBatch = 4;
+    const int lane = threadIdx.x & 31;
+    const int step = blockDim.x * 4;
+#pragma unroll 1
+    for (int base = threadIdx.x * 4; base < M * K; base += kBatch * step) {
+      uint2 av[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j)
+        if (base + j * step < M * K) av[j] = __ldg(reinterpret_cast<const uint2*>(P.a + base + j * step));
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int c = base + j * step;
+        if (c < M * K) {
+          const float4 f = make_float4(bf_lo(av[j].x), bf_hi(av[j].x), bf_lo(av[j].y), bf_hi(av[j].y));
+          const int m = c / K, k = c - m * K;
+          if (MASK & (1 << ORN_Q4K)) stage_piece<ORN_Q4K>(X[ORN_Q4K], m, k, f);
+          if (MASK & (1 << ORN_Q6K)) stage_piece<ORN_Q6K>(X[ORN_Q6K], m, k, f);
+          if (MASK & (1 << ORN_A8)) stage_piece<ORN_A8>(X[ORN_A8], m, k, f);
+          if (MASK & (1 << ORN_BF16)) stage_piece<ORN_BF16>(X[ORN_BF16], m, k, f);
+          if (P.norm_out != nullptr && blockIdx.x == 0) *reinterpret_cast<uint2*>(P.norm_out + c) = av[j];
+          if (MASK & ((1 << ORN_A8) | (1 << ORN_Q4K))) {
+            float run = 0.f;
+#pragma unroll
+            for (int st = 0; st < 4; ++st) {
+              if ((lane & 3) == st) { run = run + f.x; run = run + f.y; run = run + f.z; run = run + f.w; }
+              const float up = __shfl_up_sync(0xffffffffu, run, 1);
+              if ((lane & 3) == st + 1) run = up;
+            }
+            if ((lane & 3) == 3) {
+              if (MASK & (1 << ORN_A8)) X[ORN_A8].sums[(size_t)m * X[ORN_A8].units + (k >> 4)] = run;
+              if (MASK & (1 << ORN_Q4K)) {
+                int u, pp;
+                unit_of<ORN_Q4K>(k, u, pp);
+                X[ORN_Q4K].sums[((size_t)m * X[ORN_Q4K].units + u) * 2 + (pp >> 2)] = run;
+              }
+            }
+          }
+        }
+      }
+    }
+    if (MASK & (1 << ORN_Q4K)) stage_zero_tail<ORN_Q4K>(X[ORN_Q4K]);
+    if (MASK & (1 << ORN_Q6K)) stage_zero_tail<ORN_Q6K>(X[ORN_Q6K]);
+    if (MASK & (1 << ORN_A8)) stage_zero_tail<ORN_A8>(X[ORN_A8]);
+    if (MASK & (1 << ORN_BF16)) stage_zero_tail<ORN_BF16>(X[ORN_BF16]);
   } else {
     prologue_other(P, M, lin, red);
     __syncthreads();
@@ -936,7 +983,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
   float* lin = smem + (((next - smem) + 31) & ~31);
   float* red = lin + (size_t)M * P.K;
   run_prologue<M, MASK>(P, pin, lin, red, X);
-  if (P.mode != PRO_ADDNORM) {
+  if (P.mode != PRO_ADDNORM && P.mode != PRO_PLAIN) {
     if (mask & (1 << ORN_Q4K)) stage_fill<ORN_Q4K>(lin, P.K, X[ORN_Q4K]);
     if (mask & (1 << ORN_Q6K)) stage_fill<ORN_Q6K>(lin, P.K, X[ORN_Q6K]);
     if (mask & (1 << ORN_A8)) stage_fill<ORN_A8>(lin, P.K, X[ORN_A8]);
