@@ -1458,8 +1458,15 @@ struct GdnParams {
 constexpr int kGdnRows = 16;
 constexpr int kGdnMaxT = 4;
 
+// CTA = (head hv, block of kGdnRows state rows).  Threads 0 .. 4*kGdnRows-1 own the state (a row's
+// 128 floats over 4 lanes) and run the recurrence; the front end is spread over one warp per
+// (q or k, window token), one warp for the block's value rows and one for the gates, so that its
+// out-of-line calls run side by side: 2 T + 2 warps in all.
+constexpr int kGdnStateThreads = kGdnRows * 4;
+__host__ __device__ constexpr int gdn_threads(int T) { return 32 * (2 * T + 2); }
+
 template <bool TAPS4>  // TAPS4: the convolution has 4 taps (every Qwen3.5 artifact); else any width
-__global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
+__global__ void __launch_bounds__(gdn_threads(kGdnMaxT)) k_gdn(GdnParams p) {
   __shared__ float s_q[kGdnMaxT][128], s_k[kGdnMaxT][128], s_v[kGdnMaxT][kGdnRows];
   __shared__ float s_g[kGdnMaxT], s_beta[kGdnMaxT];
   pdl_trigger();
@@ -1467,55 +1474,40 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
   const int hk = hv / (p.Hv / p.Hk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int key_dim = p.Hk * 128;
+  const bool owner = threadIdx.x < kGdnStateThreads;
   // the state rows do not depend on the front end: request them first so that the 2 MB of HBM
   // reads per layer overlap the convolution and the norms
-  const int row = blockIdx.x * kGdnRows + (threadIdx.x >> 2);
+  const int row = blockIdx.x * kGdnRows + ((threadIdx.x >> 2) & (kGdnRows - 1));
   const int lir = threadIdx.x & 3;
   const size_t ssz = (size_t)p.Hv * 128 * 128;
   const size_t off = ((size_t)hv * 128 + row) * 128 + lir * 32;
   const int cur = *p.cur;
   const float* sin = p.ring + (size_t)(cur % p.nring) * ssz + off;
   float S[32];
+  if (owner) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float4 v4 = *reinterpret_cast<const float4*>(sin + 4 * i);
-    S[4 * i] = v4.x; S[4 * i + 1] = v4.y; S[4 * i + 2] = v4.z; S[4 * i + 3] = v4.w;
+    for (int i = 0; i < 8; ++i) {
+      const float4 v4 = *reinterpret_cast<const float4*>(sin + 4 * i);
+      S[4 * i] = v4.x; S[4 * i + 1] = v4.y; S[4 * i + 2] = v4.z; S[4 * i + 3] = v4.w;
+    }
   }
   // The state and the ring position were written by an earlier step (a graph launch, a copy or a
   // host read lies in between), not by the kernel this one may overlap: only what follows reads
   // the previous kernel's output.
   pdl_wait();
-  // ---- front end (kernels/gdn_front.metal:65-190): warp 0 -> q head, warp 1 -> k head
+  // ---- front end (kernels/gdn_front.metal:65-190)
   if constexpr (TAPS4) {
-    // Every global read of the front end is requested here, before any arithmetic, so that the
-    // latencies overlap each other and the state rows': the T + 3 window rows of the lane's four
-    // q / k channels, their taps, the window of the value channel, the gate inputs.
-    constexpr int NR = kGdnMaxT + 3;
-    const int c0 = (warp == 0 ? hk * 128 : key_dim + hk * 128) + 4 * lane;
-    const int cv = 2 * key_dim + hv * 128 + row;
-    uint2 xr[NR], wr[4], vw = make_uint2(0u, 0u);
-    bf16_t vr[NR];
+    if (warp < 2 * p.T) {
+      // q (even warps) or k (odd warps) head of window token t: the four window rows and the taps
+      // of the lane's four channels are requested together
+      const int t = warp >> 1;
+      const bool isk = (warp & 1) != 0;
+      const int c0 = (isk ? key_dim + hk * 128 : hk * 128) + 4 * lane;
+      uint2 xr[4], wr[4];
 #pragma unroll
-    for (int i = 0; i < NR; ++i) {
-      xr[i] = make_uint2(0u, 0u);
-      vr[i] = 0;
-      if (i < p.T + 3) {
-        xr[i] = *reinterpret_cast<const uint2*>(p.conv + (size_t)i * p.D + c0);
-        if (lir == 0) vr[i] = p.conv[(size_t)i * p.D + cv];
-      }
-    }
+      for (int i = 0; i < 4; ++i) xr[i] = *reinterpret_cast<const uint2*>(p.conv + (size_t)(t + i) * p.D + c0);
 #pragma unroll
-    for (int r = 0; r < 4; ++r) wr[r] = *reinterpret_cast<const uint2*>(p.cw + (size_t)(c0 + r) * 4);
-    if (lir == 0) vw = *reinterpret_cast<const uint2*>(p.cw + (size_t)cv * 4);
-    float ga = 0.f, gb = 0.f, gdt = 0.f, gal = 0.f;
-    if (threadIdx.x < p.T) {
-      const size_t i = (size_t)threadIdx.x * p.Hv + hv;
-      ga = bf2f(p.a_in[i]); gb = bf2f(p.b_in[i]); gdt = bf2f(p.dt_bias[hv]); gal = bf2f(p.a_log[hv]);
-    }
-    const float sc = warp == 0 ? p.q_scale : p.k_scale;
-    const float vtap[4] = {bf_lo(vw.x), bf_hi(vw.x), bf_lo(vw.y), bf_hi(vw.y)};
-#pragma unroll 1
-    for (int t = 0; t < p.T; ++t) {  // the window slides through the registers: rows t .. t+3 sit in [0..3]
+      for (int r = 0; r < 4; ++r) wr[r] = *reinterpret_cast<const uint2*>(p.cw + (size_t)(c0 + r) * 4);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -1532,25 +1524,36 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
       for (int r = 0; r < 4; ++r) { yv[r] = silu_bf_call(bfr(acc[r])); sum = fmaf(yv[r], yv[r], sum); }
       sum = warp_sum(sum);
       const float inv = orn_rsqrtf(sum / 128.0f + p.eps);
-      float* dst = warp == 0 ? s_q[t] : s_k[t];
+      const float sc = isk ? p.k_scale : p.q_scale;
+      float* dst = isk ? s_k[t] : s_q[t];
 #pragma unroll
       for (int r = 0; r < 4; ++r) dst[4 * lane + r] = bfr(sc * bfr(yv[r] * inv));
-      if (lir == 0) {  // the value channel of this thread's state row
+    } else if (warp == 2 * p.T) {
+      // the block's value channels: item = (state row r, window token t)
+#pragma unroll 1
+      for (int idx = lane; idx < kGdnRows * p.T; idx += 32) {
+        const int r = idx & (kGdnRows - 1), t = idx / kGdnRows;
+        const int cv = 2 * key_dim + hv * 128 + blockIdx.x * kGdnRows + r;
+        bf16_t vr[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) vr[i] = p.conv[(size_t)(t + i) * p.D + cv];
+        const uint2 vw = *reinterpret_cast<const uint2*>(p.cw + (size_t)cv * 4);
+        const float vtap[4] = {bf_lo(vw.x), bf_hi(vw.x), bf_lo(vw.y), bf_hi(vw.y)};
         float av = 0.f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) av = fmaf(bf2f(vr[i]), vtap[i], av);
-        s_v[t][threadIdx.x >> 2] = silu_bf_call(bfr(av));
+        s_v[t][r] = silu_bf_call(bfr(av));
       }
-#pragma unroll
-      for (int i = 0; i + 1 < NR; ++i) { xr[i] = xr[i + 1]; vr[i] = vr[i + 1]; }
-    }
-    if (threadIdx.x < p.T) {
+    } else if (lane < p.T) {
+      // the head's gates of window token `lane`
+      const size_t i = (size_t)lane * p.Hv + hv;
+      const float ga = bf2f(p.a_in[i]), gb = bf2f(p.b_in[i]), gdt = bf2f(p.dt_bias[hv]), gal = bf2f(p.a_log[hv]);
       const float sp = softplus_bf_call(bfr(ga + gdt));
       const float decay = expf_call(gal);
-      s_g[threadIdx.x] = expf_call((-decay) * sp);
-      s_beta[threadIdx.x] = sigmoid_bf_call(gb);
+      s_g[lane] = expf_call((-decay) * sp);
+      s_beta[lane] = sigmoid_bf_call(gb);
     }
-  } else {
+  } else if (warp < 2) {  // any number of taps: warp 0 -> q, warp 1 -> k, then value rows and gates
   for (int t = 0; t < p.T; ++t) {
     const int c0 = (warp == 0 ? hk * 128 : key_dim + hk * 128) + 4 * lane;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1589,9 +1592,10 @@ __global__ void __launch_bounds__(kGdnRows * 4) k_gdn(GdnParams p) {
     s_g[t] = expf_call((-decay) * sp);
     s_beta[t] = sigmoid_bf_call(bf2f(p.b_in[i]));
   }
-  }
+    }
   __syncthreads();
-  // ---- recurrence (kernels/gated_delta.metal:36-142)
+  // ---- recurrence (kernels/gated_delta.metal:36-142), by the threads that own the state
+  if (owner)
   for (int t = 0; t < p.T; ++t) {
     const float* kf = s_k[t] + lir * 32;
     const float* qf = s_q[t] + lir * 32;
@@ -2081,6 +2085,7 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
   p.arrivals = reinterpret_cast<unsigned int*>(ctx->dev_err) + 64;
   if (gated_out != nullptr && Hv > 512) ORN_FAIL(ctx, ORN_ERR_ARG, "fused gdn: more than 512 value heads");
   dim3 grid(128 / kGdnRows, Hv);
+  const dim3 block(gdn_threads(T));
   // Unused dynamic shared memory caps the kernel at two CTAs per SM.  As a programmatic dependent
   // its CTAs become resident while the previous kernel drains, and without the cap the first SMs
   // to come free would take sixteen CTAs each instead of the grid spreading over the whole part.
@@ -2091,8 +2096,8 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
     ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_gdn<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pad));
     granted = true;
   }
-  if (Kc == 4) ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<true>, grid, dim3(kGdnRows * 4), pad, p));
-  else ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<false>, grid, dim3(kGdnRows * 4), pad, p));
+  if (Kc == 4) ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<true>, grid, block, pad, p));
+  else ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<false>, grid, block, pad, p));
   return orn_launch_check(ctx, "k_gdn");
 }
 
