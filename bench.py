@@ -34,7 +34,7 @@ PROMPT_LEN, GEN_TOKENS, FORCE_P, SEED = 51, 200, 0.5, 20240611
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the kernel above, from the ncu
 # capture summarised in profiles/
-NCU_TRAFFIC_BYTES = 28.61e6  # profiles/fused_kernels_ncu_profile_step_4layer.md: 27.06 MB read + 1.55 MB written
+NCU_TRAFFIC_BYTES = 28.60e6  # profiles/fused_kernels_ncu_profile_step_4layer.md: 27.06 MB read + 1.54 MB written
 
 
 def peaks():
