@@ -980,8 +980,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_norm_gemv(Prologue P, RowJ
 #pragma unroll
   for (int k = 0; k < 4; ++k)
     if (mask & (1 << k)) next = stage_carve(next, k, M, P.K, X[k]);
+  // the add + norm and the plain prologue stage from registers: they need the reduction scratch
+  // only, no linear copy of the rows (the launch sizes shared memory accordingly)
   float* lin = smem + (((next - smem) + 31) & ~31);
-  float* red = lin + (size_t)M * P.K;
+  float* red = (P.mode == PRO_ADDNORM || P.mode == PRO_PLAIN) ? lin : lin + (size_t)M * P.K;
   run_prologue<M, MASK>(P, pin, lin, red, X);
   if (P.mode != PRO_ADDNORM && P.mode != PRO_PLAIN) {
     if (mask & (1 << ORN_Q4K)) stage_fill<ORN_Q4K>(lin, P.K, X[ORN_Q4K]);
@@ -1890,7 +1892,8 @@ int launch_norm_gemv_mask(orn_ctx* ctx, cudaStream_t s, const Prologue& P, const
     if (MASK & (1 << k)) fixed += stage_floats(k, M, P.K) * sizeof(float);
   fixed = (fixed + 127) & ~(size_t)127;
   const size_t stages = fixed;
-  const size_t scratch = ((size_t)M * P.K + M * 33 + 64) * sizeof(float);  // the prologue's row and its reduction scratch
+  const bool direct = P.mode == PRO_ADDNORM || P.mode == PRO_PLAIN;  // staged from registers: no linear copy of the rows
+  const size_t scratch = ((direct ? 0 : (size_t)M * P.K) + M * 33 + 64) * sizeof(float);
   fixed += scratch;
   int depth, late = 0;
   uint32_t ring_off;
