@@ -32,9 +32,13 @@ METRIC = "MTP-depth-1 decode tok/s (35B-A3B k-quant, batch 1)"
 PROMPT_LEN, GEN_TOKENS, FORCE_P, SEED = 51, 200, 0.5, 20240611
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the kernel above, from the ncu
-# capture summarised in profiles/
-NCU_TRAFFIC_BYTES = 28.60e6  # profiles/fused_kernels_ncu_profile_step_4layer.md: 27.06 MB read + 1.54 MB written
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under
+# profiles/ (4-layer full-width model: the kernels and their matrices are those of the 40-layer run)
+NCU_TRAFFIC_BYTES = {
+    "k_norm_gemv M=2 kind=2 8192x2048": 28.60e6,   # add + norm + in_proj: 27.06 MB read + 1.54 MB written
+    "k_moe_up M=2 kind=0 512x2048": 18.81e6,
+    "k_moe_down M=2 kind=1 2048x512": 15.07e6,
+}
 
 
 def peaks():
@@ -125,54 +129,179 @@ def draft_bytes(cfg, head_rows):
             + (cfg.top_k + 1) * expert + head_rows * H * 1.0625)
 
 
-def cpu_arm(pkg, ctx, max_seconds=15.0):
-    """The reference's scalar CPU path (the C restatement under oracle/) timed on
-    this host.  Sample: one 3:1 period of the stack (4 of 40 layers, real layer
-    sizes) plus the MTP head and the full lm_head, MTP depth-1 cycles with the
-    same forced-draft rule; the per-cycle layer time is scaled by 10 to the 40
-    layers."""
+def sample_weights_cpu(cfg, seed):
+    """Seeded weights of a full-width model in the benchmark's mix, made on the host with numpy
+    (name -> oracle Weights / bf16 tensor).  Raw fields are drawn so that the dequantised weights
+    are zero-mean with a standard deviation near 0.02, like the GPU-side random-init: the sample
+    only has to move the same bytes through the same arithmetic as the real layers."""
+    import orn_oracle as orc
+    rng = np.random.default_rng(seed)
+    bfv = lambda v: np.uint16(np.float32(v).view(np.uint32) >> 16)
+    to_bf = lambda a: (np.ascontiguousarray(a, np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+    def a8(E, O, K):
+        q = rng.integers(0, 256, (E * O, K), dtype=np.uint8)
+        g = E * O * (K // 64)
+        return orc.Weights(orc.A8, E, O, K, q, np.full(g, bfv(0.07 / 255), np.uint16), np.full(g, bfv(-0.035), np.uint16))
+
+    def q4(E, O, K):
+        n = E * O * (K // 256)
+        qs = rng.integers(0, 256, (n, 128), dtype=np.uint8)
+        sc = rng.integers(4, 9, (n, 8), dtype=np.uint8)           # 6-bit scales 4..8
+        mn = np.rint(7.5 * sc).astype(np.uint8)                   # mins that centre the 0..15 codes
+        scales = np.zeros((n, 12), np.uint8)
+        for j in range(4):
+            scales[:, j] = sc[:, j] & 63
+            scales[:, j + 4] = mn[:, j] & 63
+        for j in range(4, 8):
+            scales[:, j + 4] = (sc[:, j] & 0xF) | ((mn[:, j] & 0xF) << 4)
+            scales[:, j - 4] |= (sc[:, j] >> 4) << 6
+            scales[:, j] |= (mn[:, j] >> 4) << 6
+        dm = np.full((n, 2), np.float16(7.2e-4)).view(np.uint16)
+        return orc.Weights(orc.Q4K, E, O, K, qs, scales, dm)
+
+    def q6(E, O, K):
+        n = E * O * (K // 256)
+        w = rng.integers(0, 256, (n, 192), dtype=np.uint8)
+        sc = rng.integers(20, 41, (n, 16)).astype(np.int8).view(np.uint8)
+        d = np.full(n, np.float16(3.6e-5)).view(np.uint16)
+        return orc.Weights(orc.Q6K, E, O, K, w, sc, d)
+
+    def bf(E, O, K):
+        # random sign, magnitudes spread over [2^-7, 2^-5): bfloat16 bit patterns straight from the generator
+        r = rng.integers(0, 1024, (E * O, K), dtype=np.uint16)
+        return orc.Weights(orc.BF16, E, O, K, ((r >> 9) << 15) | (np.uint16(0x3C00) + (r & 511)))
+
+    H, V = cfg.hidden, cfg.vocab
+    D = 2 * cfg.gdn_k_heads * 128 + cfg.gdn_v_heads * 128
+    VD, QD, KVD = cfg.gdn_v_heads * 128, cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    W = {}
+    ten = lambda name, n, mean, std: W.__setitem__(name, to_bf(mean + std * rng.standard_normal(n).astype(np.float32)))
+
+    def moe(p, dense):
+        f4, f6, f8 = (bf, bf, bf) if dense else (q4, q6, a8)
+        W[p + "gate"] = f8(1, cfg.n_experts, H)
+        W[p + "switch_mlp.gate_proj"] = f4(cfg.n_experts, cfg.expert_inter, H)
+        W[p + "switch_mlp.up_proj"] = f4(cfg.n_experts, cfg.expert_inter, H)
+        W[p + "switch_mlp.down_proj"] = f6(cfg.n_experts, H, cfg.expert_inter)
+        W[p + "shared_expert.gate_proj"] = f4(1, cfg.shared_inter, H)
+        W[p + "shared_expert.up_proj"] = f4(1, cfg.shared_inter, H)
+        W[p + "shared_expert.down_proj"] = f6(1, H, cfg.shared_inter)
+        W[p + "shared_expert_gate"] = f8(1, 1, H)
+
+    W["embed_tokens"] = a8(1, V, H)
+    W["lm_head"] = a8(1, V, H)
+    ten("norm.weight", H, 1.0, 0.05)
+    for i in range(cfg.n_layers):
+        lp = "layers.%d." % i
+        ten(lp + "input_layernorm.weight", H, 1.0, 0.05)
+        ten(lp + "post_attention_layernorm.weight", H, 1.0, 0.05)
+        if (i + 1) % cfg.full_attn_interval != 0:
+            a = lp + "linear_attn."
+            W[a + "in_proj_qkv"], W[a + "in_proj_z"], W[a + "out_proj"] = a8(1, D, H), a8(1, VD, H), a8(1, H, VD)
+            W[a + "in_proj_a.weight"], W[a + "in_proj_b.weight"] = bf(1, cfg.gdn_v_heads, H), bf(1, cfg.gdn_v_heads, H)
+            ten(a + "conv1d.weight", D * cfg.gdn_conv_kernel, 0.0, 0.2)
+            ten(a + "dt_bias", cfg.gdn_v_heads, 0.0, 0.3)
+            ten(a + "A_log", cfg.gdn_v_heads, 0.0, 0.3)
+            ten(a + "norm.weight", 128, 1.0, 0.05)
+        else:
+            a = lp + "self_attn."
+            W[a + "q_proj"], W[a + "k_proj"] = a8(1, 2 * QD, H), a8(1, KVD, H)
+            W[a + "v_proj"], W[a + "o_proj"] = a8(1, KVD, H), a8(1, H, QD)
+            ten(a + "q_norm.weight", cfg.head_dim, 1.0, 0.05)
+            ten(a + "k_norm.weight", cfg.head_dim, 1.0, 0.05)
+        moe(lp + "mlp.", False)
+    lp = "mtp.layers.0."
+    ten("mtp.pre_fc_norm_embedding.weight", H, 1.0, 0.05)
+    ten("mtp.pre_fc_norm_hidden.weight", H, 1.0, 0.05)
+    W["mtp.fc.weight"] = bf(1, H, 2 * H)
+    ten("mtp.norm.weight", H, 1.0, 0.05)
+    ten(lp + "input_layernorm.weight", H, 1.0, 0.05)
+    ten(lp + "post_attention_layernorm.weight", H, 1.0, 0.05)
+    W[lp + "self_attn.q_proj.weight"], W[lp + "self_attn.k_proj.weight"] = bf(1, 2 * QD, H), bf(1, KVD, H)
+    W[lp + "self_attn.v_proj.weight"], W[lp + "self_attn.o_proj.weight"] = bf(1, KVD, H), bf(1, H, QD)
+    ten(lp + "self_attn.q_norm.weight", cfg.head_dim, 1.0, 0.05)
+    ten(lp + "self_attn.k_norm.weight", cfg.head_dim, 1.0, 0.05)
+    moe(lp + "mlp.", True)
+    return W
+
+
+class _Cfg:
+    """The benchmark model's dimensions as a plain object (the CPU arm builds no CUDA context)."""
+
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def qwen35_dims(n_layers, max_ctx):
+    return _Cfg(hidden=2048, n_layers=n_layers, full_attn_interval=4, n_heads=16, n_kv_heads=2, head_dim=256,
+                rope_dims=64, rope_theta=1e7, gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128, gdn_conv_kernel=4,
+                n_experts=256, top_k=8, expert_inter=512, shared_inter=512, norm_topk_prob=1, vocab=248320,
+                rms_eps=1e-6, max_ctx=max_ctx)
+
+
+def cpu_arm(max_seconds=15.0):
+    """The reference's scalar CPU path (the C restatement under oracle/) timed on this host's
+    cores; no GPU and no product library involved.  Sample: a 4-layer full-width model (one 3:1
+    period of the stack, real layer sizes, full vocabulary, MTP head), weights made on the host.
+    Measured: (a) whole MTP depth-1 cycles of that model with the benchmark's forced-draft rule
+    (draft level, 2-row verify window through 4 layers, lm_head + greedy for both rows, accept and
+    rewind); (b) the 2-row window through its 4 layers alone.  The 40-layer cycle is (a) + 9 x (b):
+    the only extrapolation is the layer count."""
     threads = os.cpu_count() or 1
     os.environ["OMP_NUM_THREADS"] = str(threads)  # torchrun sets it to 1 for its workers
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import orn_oracle as orc
     orc.lib().orc_set_threads(threads)
     threads = orc.lib().orc_get_threads()
-
-    cfg4 = pkg.qwen35_config(max_ctx=128, n_layers=4)
-    gm = pkg.TextModel(ctx, cfg4)
-    gm.init_random(SEED)
-    gm.make_cache().free()  # resolves the weight table
-    om = orc.export_gpu_model(gm)
-    gm.free()
+    cfg4 = qwen35_dims(4, 160)
+    t_make = time.perf_counter()
+    om = orc.Model(cfg4, sample_weights_cpu(cfg4, SEED))
+    t_make = time.perf_counter() - t_make
     rng = np.random.default_rng(SEED)
-    ids = rng.integers(0, cfg4.vocab, 2).astype(np.uint32)
-    cache = om.new_cache()
-    om.forward(cache, ids[:1])  # warm
-    t_layers, t_head, n = 0.0, 0.0, 0
-    t_start = time.perf_counter()
-    while n < 3 or time.perf_counter() - t_start < max_seconds:
+    prompt = rng.integers(0, cfg4.vocab, 4).astype(np.uint32)
+
+    def measure(budget_s, gen):
+        """-> (seconds per cycle of the 4-layer model, tokens per cycle, seconds per 2-row 4-layer window)"""
+        ar = om.generate(prompt, gen)
         t0 = time.perf_counter()
-        h = om.forward(cache, ids)                      # a 2-row verify window through 4 layers
-        t1 = time.perf_counter()
-        om.head_greedy(h, 2)                            # lm_head + greedy for both rows
-        t2 = time.perf_counter()
-        t_layers += t1 - t0
-        t_head += t2 - t1
-        n += 1
-        if n % 40 == 0:  # stay inside the sample model's 128-token context
-            om.free_cache(cache)
-            cache = om.new_cache()
-    om.free_cache(cache)
+        toks, st = om.generate_mtp(prompt, 1, gen, policy=1, force=(ar, FORCE_P, SEED))
+        t_gen = time.perf_counter() - t0
+        assert toks == ar
+        # the prompt's prefill and first step are inside t_gen; take them out with a zero-token run
+        t0 = time.perf_counter()
+        om.generate(prompt, 1)
+        t_pre = time.perf_counter() - t0
+        cyc = max(st.cycles, 1)
+        cache = om.new_cache()
+        om.forward(cache, prompt[:2])
+        n, t_lay = 0, 0.0
+        while n < 2 or t_lay < budget_s * 0.25:
+            t0 = time.perf_counter()
+            om.forward(cache, prompt[:2])
+            t_lay += time.perf_counter() - t0
+            n += 1
+        om.free_cache(cache)
+        return max(t_gen - t_pre, 1e-9) / cyc, gen / cyc, t_lay / n
+
+    t_start = time.perf_counter()
+    c4, tpc, l4 = measure(max_seconds, 24)
+    value = tpc / (c4 + 9.0 * l4)
+    t_multi = time.perf_counter() - t_start
+    # the single-thread figure of the same sample (shorter: a scalar core is ~cores x slower)
+    orc.lib().orc_set_threads(1)
+    t1 = time.perf_counter()
+    c4s, tpcs, l4s = measure(max_seconds * 0.3, 3)
+    single = tpcs / (c4s + 9.0 * l4s)
+    t_single = time.perf_counter() - t1
+    orc.lib().orc_set_threads(threads)
     om.free()
-    verify_s = 10.0 * t_layers / n + t_head / n
-    # draft level: MTP head is one attention layer with bf16 weights + lm_head row: bounded by head time / 2
-    draft_s = t_head / n / 2 + (t_layers / n) / 4
-    tok_per_cycle = 1.0 + FORCE_P
-    value = tok_per_cycle / (verify_s + draft_s)
-    return {"value": value, "unit": "tok/s", "cores": threads, "kind": "port",
-            "sample": "%d verify windows (T=2) through 4 of 40 layers + full lm_head on the C oracle with "
-                      "OpenMP over rows; layer time x10, draft level estimated from the same parts; "
-                      "%.1f s of CPU work" % (n, time.perf_counter() - t_start)}
+    return {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "single_thread_value": single,
+            "sample": "C oracle, OpenMP over rows: MTP depth-1 cycles (draft level + 2-row verify + lm_head + accept) of a "
+                      "4-layer full-width model timed whole (%.3f s per cycle, %.2f tokens per cycle), plus the 2-row "
+                      "window through its 4 layers (%.3f s); 40-layer cycle = cycle + 9 x window: extrapolated from 4 "
+                      "of 40 layers; %.1f s of CPU work at %d threads, %.1f s at 1 thread; weights made on the host in "
+                      "%.1f s" % (c4, tpc, l4, t_multi, threads, t_single, t_make)}
 
 
 FMT_BYTES = {0: 144.0 / 256, 1: 210.0 / 256, 2: 1.0625, 3: 2.0}  # Q4_K, Q6_K, affine-8 g64, bf16 bytes per weight
@@ -224,7 +353,88 @@ def kernel_roofline(pkg, ctx, model, cfg, iters=20):
     ach = alg / (per * 1e-3) / 1e9
     return {"bound": "hbm", "kernel": "k_norm_gemv<M=2> add+rms_norm + in_proj_{qkv,z,a,b} [12352x2048]",
             "achieved": ach, "peak": peak, "peak_source": which, "unit": "GB/s", "frac": ach / peak,
-            "traffic": NCU_TRAFFIC_BYTES, "launch_us": per * 1e3, "algorithmic_bytes": alg, "launches_timed": n}
+            "traffic": NCU_TRAFFIC_BYTES["k_norm_gemv M=2 kind=2 8192x2048"], "launch_us": per * 1e3, "algorithmic_bytes": alg, "launches_timed": n}
+
+
+def label_bytes(cfg, label):
+    """Algorithmic bytes of one launch with this per-kernel label (kernel, rows M, first job's
+    format and shape), or None for bookkeeping kernels.  Expert kernels: expected distinct experts
+    of M rows x their format size; the add + norm + mat-vec launches: all jobs of that launch."""
+    H, E, k, I = cfg.hidden, cfg.n_experts, cfg.top_k, cfg.expert_inter
+    parts = label.split()
+    if len(parts) != 4 or not parts[1].startswith("M="):
+        return None
+    kern, M, kind, shape = parts[0], int(parts[1][2:]), int(parts[2][5:]), parts[3]
+    O, K = (int(v) for v in shape.split("x"))
+    fb = FMT_BYTES[kind]
+    distinct = E * (1.0 - (1.0 - k / E) ** M)
+    act = lambda rows, n: rows * n * 2
+    if kern == "k_moe_up":
+        return distinct * 2 * O * K * fb + act(M, K) + act(M * k, O) + M * E * 2
+    if kern == "k_moe_down":
+        return (distinct + 1) * O * K * fb + act(M * k + M, K) + act(M, O)
+    if kern == "k_norm_gemv":
+        VD, QD, KVD = cfg.gdn_v_heads * 128, cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+        D = 2 * cfg.gdn_k_heads * 128 + VD
+        rows = O
+        extra = 0.0
+        if (O, K) == (D, H):                     # in_proj qkv + z (+ the two bf16 gate rows)
+            rows += VD
+            extra = 2 * cfg.gdn_v_heads * K * 2.0
+        elif (O, K) == (2 * QD, H):              # q + k + v
+            rows += 2 * KVD
+        elif (O, K) == (E, H):                   # router + shared gate/up (Q4_K or bf16) + shared-expert gate row
+            sh = 2 * cfg.shared_inter * K * (FMT_BYTES[0] if kind == 2 else 2.0)
+            extra = sh + K * fb
+        return rows * K * fb + extra + act(2 * M, K) + act(M, rows)
+    return None
+
+
+def kernel_table(pkg, ctx, model, cache, prompt, ar, cfg, cycle_ms):
+    """Per-kernel device times of one whole generation, live (CUDA events on the launching stream
+    after every launch, eager launches): for every kernel label its launches, average time, share
+    of the decode loop, algorithmic bytes and the fraction of the measured HBM peak it reaches.
+    Eager event-to-event times include the gap between launches, so fractions read low."""
+    peak, _ = peaks()
+    cache.reset()
+    ctx.ktime_begin()
+    toks, st = pkg.generate_step_mtp(model, cache, prompt, 1, GEN_TOKENS, force=(ar, FORCE_P, SEED))
+    table = ctx.ktime_end()
+    assert toks == ar
+    table = {l: v for l, v in table.items() if " M=4 " not in l and " M=3 " not in l}  # prompt windows are not the decode loop
+    rows, total = [], sum(ms for _, ms in table.values())
+    for label, (n, ms) in table.items():
+        b = label_bytes(cfg, label)
+        us = 1e3 * ms / n
+        rows.append({"kernel": label, "launches": n, "launch_us": us, "share": ms / total,
+                     "bytes": b, "frac": None if b is None else b / (us * 1e-6) / 1e9 / peak})
+    rows.sort(key=lambda r: -r["share"])
+    return rows
+
+
+def oracle_check(pkg, ctx):
+    """The decode loop's integers against the CPU oracle on a 4-layer full-width model (the
+    oracle is the checker here): emitted ids and accepted count at the benchmark's p."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import orn_oracle as orc
+    cfg4 = pkg.qwen35_config(max_ctx=96, n_layers=4)
+    gm = pkg.TextModel(ctx, cfg4)
+    gm.init_random(SEED)
+    gm.make_cache().free()
+    om = orc.export_gpu_model(gm)
+    prompt = np.random.default_rng(SEED).integers(0, cfg4.vocab, 6).astype(np.uint32)
+    n = 16
+    ar = om.generate(prompt, n)
+    ref, rst = om.generate_mtp(prompt, 1, n, policy=1, force=(ar, FORCE_P, SEED))
+    c = gm.make_cache()
+    got, gst = pkg.generate_step_mtp(gm, c, prompt, 1, n, force=(ar, FORCE_P, SEED))
+    ok = got == ref == ar and (gst.cycles, gst.drafted, gst.accepted) == (rst.cycles, rst.drafted, rst.accepted)
+    c.free()
+    gm.free()
+    om.free()
+    assert ok, "decode loop differs from the CPU oracle on the 4-layer full-width sample"
+    return {"model": "4 full-width layers + MTP head + full vocabulary", "tokens": n, "p": FORCE_P,
+            "cycles": gst.cycles, "accepted": gst.accepted, "oracle_accepted": rst.accepted, "equal": True}
 
 
 def reduce_max_over_ranks(values, dist, device):
@@ -257,7 +467,7 @@ def ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_pkg()
     ctx = pkg.Context(local)
-    cfg = pkg.qwen35_config(max_ctx=512)
+    cfg = pkg.qwen35_config(max_ctx=512, n_layers=args.n_layers)
     model = pkg.TextModel(ctx, cfg)
     model.init_random(SEED)
     cache = model.make_cache()
@@ -307,8 +517,16 @@ def ours(args):
         if dist is not None:
             dist.destroy_process_group()
         return
-    roof = kernel_roofline(pkg, ctx, model, cfg)
     peak, which = peaks()
+    iso = kernel_roofline(pkg, ctx, model, cfg)
+    kt = kernel_table(pkg, ctx, model, cache, prompt, ar, cfg, dev_ms / max(cycles, 1))
+    # the roofline object names the kernel with the largest share of the decode loop
+    top = next(r for r in kt if r["bytes"] is not None)
+    roof = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["frac"] * peak, "peak": peak, "peak_source": which,
+            "unit": "GB/s", "frac": top["frac"], "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
+            "launch_us": top["launch_us"], "algorithmic_bytes": top["bytes"], "launches_timed": top["launches"],
+            "share_of_decode_loop": top["share"],
+            "timing": "CUDA events on the launching stream after every launch of one whole generation (eager)"}
     vb, db = step_bytes(cfg, 2), draft_bytes(cfg, cfg.vocab)
     cyc_s = dev_ms * 1e-3 / max(cycles, 1)
     step_roof = {"bytes_per_cycle": vb + db, "verify_bytes": vb, "draft_bytes": db,
@@ -331,11 +549,13 @@ def ours(args):
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": PROMPT_LEN * 4,
                 "d2h_bytes_per_step": int(16 * cycles / args.steps) + 4},
         "gpu_launches": launches, "clocks": clocks, "roofline": roof, "step_roofline": step_roof,
+        "kernels": kt[:12], "isolated_in_proj_launch": iso,
         "acceptance": accepted / max(cycles, 1), "tokens_per_cycle": args.steps * GEN_TOKENS / max(cycles, 1),
         "mtp_equals_autoregressive": True, "prefill_ms_per_step": prefill_ms / args.steps,
     }
     if world == 1 and not args.no_cpu:
-        line["cpu_baseline"] = cpu_arm(pkg, ctx)
+        line["oracle_check"] = oracle_check(pkg, ctx)
+        line["cpu_baseline"] = cpu_arm()
     emit(line)
     ctx.close()
     if dist is not None:
@@ -436,29 +656,24 @@ def ep_layer(args):
 
 
 def reference(args):
-    """The reference's own CPU statement of the path (its Metal path cannot run
-    on Linux): the C restatement under oracle/, all host threads."""
+    """The reference's own CPU statement of the path (its Metal path cannot run on Linux): the C
+    restatement under oracle/, all host threads.  Builds no CUDA context and loads no product
+    library: the sample's weights are made on the host."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    pkg = load_pkg()
-    try:
-        ctx = pkg.Context(0)
-    except Exception as e:  # the weights of the sample are generated on the GPU
-        emit({"impl": "reference", "unavailable": "no CUDA device to generate the sample weights: %s" % e})
-        return
-    cb = cpu_arm(pkg, ctx, max_seconds=max(10.0, 8.0 * args.steps))
+    cb = cpu_arm(max_seconds=max(10.0, 6.0 * args.steps))
     line = {
         "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": GEN_TOKENS / cb["value"] * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": GEN_TOKENS / cb["value"] * 1e3, "ms_per_step_is": "extrapolated from the bounded sample",
+        "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 activations, f32 accumulate", "data": "synthetic",
         "config": {"workload": "BASELINE config 4 (bounded sample, see cpu_baseline.sample)"},
         "cpu_baseline": cb,
         "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     emit(line)
-    ctx.close()
 
 
 _RESULT_FD = None
@@ -489,6 +704,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--gen-tokens", type=int, default=200, help="tokens per generation (profiling runs use fewer)")
     ap.add_argument("--prompt-len", type=int, default=51)
+    ap.add_argument("--n-layers", type=int, default=40, help="fewer layers at the full layer sizes (profiling runs)")
     ap.add_argument("--workload", default="decode", choices=["decode", "ep-layer"],
                     help="decode: the MTP depth-1 decode loop (the headline); ep-layer: one expert-parallel MoE layer")
     args = ap.parse_args()

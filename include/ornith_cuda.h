@@ -80,6 +80,24 @@ int32_t orn_memset(orn_ctx* ctx, void* dev, int32_t byte, size_t nbytes);
 int32_t orn_upload(orn_ctx* ctx, void* dev, const void* host, size_t nbytes);   /* Array::from_slice */
 int32_t orn_download(orn_ctx* ctx, void* host, const void* dev, size_t nbytes); /* Array::to_vec (syncs) */
 
+/* Per-kernel device time on demand (the reference's ORNITH_PROF per-dispatch report,
+ * src/metal/mod.rs:197-284).  Between begin and end every launch of this context is followed by a
+ * CUDA event on its stream and the generation loops launch eagerly instead of replaying graphs; the
+ * time between two events is charged to the later kernel.  end writes one line per kernel label,
+ * "label<TAB>launches<TAB>total milliseconds", as a NUL-terminated string.  ORN_KTIME=1 in the
+ * environment does the same for a whole context and prints the table when it is destroyed. */
+int32_t orn_ctx_ktime_begin(orn_ctx* ctx);
+int32_t orn_ctx_ktime_end(orn_ctx* ctx, char* host_buf, size_t nbytes);
+
+/* Test hook for the library's only device-side failure report (no reference counterpart: Metal
+ * command buffers report errors through their completion handler, src/metal/mod.rs:612-646).
+ * Every streaming kernel waits for its own asynchronous copies with a bounded number of tries and,
+ * if they run out, sets a flag that the next orn_sync turns into ORN_ERR_TIMEOUT.  This call queues
+ * a one-warp kernel that waits `rounds` (1..64) tries for a copy that was never requested, so the
+ * give-up path runs with nothing in flight; the following orn_sync returns ORN_ERR_TIMEOUT once and
+ * the context stays usable. */
+int32_t orn_debug_wait_probe(orn_ctx* ctx, uint32_t rounds);
+
 /* device-side stopwatch on the context's stream (CUDA events; the reference's
  * ORNITH_PROF GPUStart/GPUEnd sums, src/metal/mod.rs:197-284) */
 int32_t orn_timer_start(orn_ctx* ctx);

@@ -103,6 +103,20 @@ class Context:
         self.check(self._lib.orn_timer_stop(self.h, C.byref(ms)), "orn_timer_stop")
         return ms.value
 
+    def ktime_begin(self):
+        """Per-kernel device times from here on (eager launches, an event after each)."""
+        self.check(self._lib.orn_ctx_ktime_begin(self.h), "orn_ctx_ktime_begin")
+
+    def ktime_end(self):
+        """-> {label: (launches, total_ms)} since ktime_begin."""
+        buf = C.create_string_buffer(1 << 16)
+        self.check(self._lib.orn_ctx_ktime_end(self.h, buf, len(buf)), "orn_ctx_ktime_end")
+        out = {}
+        for line in buf.value.decode().splitlines():
+            name, n, ms = line.split("\t")
+            out[name] = (int(n), float(ms))
+        return out
+
     def close(self):
         if self.h:
             self._lib.orn_ctx_destroy(self.h)

@@ -70,6 +70,9 @@ SIGNATURES = {
     "orn_linear_export": (i32, [vp, vp, vp, vp, vp]),
     "orn_linear_sizes": (i32, [vp, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]),
     "orn_linear_info": (i32, [vp] + [C.POINTER(i32)] * 4),
+    "orn_debug_wait_probe": (i32, [vp, C.c_uint32]),
+    "orn_ctx_ktime_begin": (i32, [vp]),
+    "orn_ctx_ktime_end": (i32, [vp, C.c_char_p, sz]),
     "orn_timer_start": (i32, [vp]),
     "orn_timer_stop": (i32, [vp, C.POINTER(f32)]),
     "orn_linear_destroy": (i32, [vp, vp]),

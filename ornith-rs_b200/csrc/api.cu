@@ -128,6 +128,39 @@ int32_t orn_sync(orn_ctx* ctx) {
   return ORN_OK;
 }
 
+int32_t orn_ctx_ktime_begin(orn_ctx* ctx) {
+  if (!ctx) return ORN_ERR_ARG;
+  ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->kt) ktime_flush(ctx);
+  else ctx->kt = new orn_ktime();
+  ctx->kt->agg.clear();
+  return ORN_OK;
+}
+
+int32_t orn_ctx_ktime_end(orn_ctx* ctx, char* host_buf, size_t nbytes) {
+  if (!ctx || !host_buf || nbytes < 2) return ORN_ERR_ARG;
+  if (!ctx->kt) ORN_FAIL(ctx, ORN_ERR_STATE, "ktime_end without ktime_begin");
+  ktime_flush(ctx);
+  std::string out;
+  char line[192];
+  for (auto& kv : ctx->kt->agg) {
+    snprintf(line, sizeof line, "%s\t%ld\t%.6f\n", kv.first.c_str(), kv.second.second, kv.second.first);
+    out += line;
+  }
+  for (cudaEvent_t e : ctx->kt->ev) cudaEventDestroy(e);
+  delete ctx->kt;
+  ctx->kt = nullptr;
+  if (out.size() + 1 > nbytes) ORN_FAIL(ctx, ORN_ERR_ARG, "ktime_end: buffer too small");
+  memcpy(host_buf, out.c_str(), out.size() + 1);
+  return ORN_OK;
+}
+
+int32_t orn_debug_wait_probe(orn_ctx* ctx, uint32_t rounds) {
+  if (!ctx) return ORN_ERR_ARG;
+  if (rounds < 1 || rounds > 64) ORN_FAIL(ctx, ORN_ERR_ARG, "wait probe: 1..64 rounds");
+  return f_wait_probe(ctx, ctx->stream, rounds, ctx->dev_err + 32);
+}
+
 int32_t orn_timer_start(orn_ctx* ctx) {
   if (!ctx) return ORN_ERR_ARG;
   if (!ctx->t0) {

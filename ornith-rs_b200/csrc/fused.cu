@@ -19,8 +19,10 @@
 // (src/ops/gdn.rs:191-413), Attention::forward (src/model/qwen3_5.rs:430-474).
 #include <algorithm>
 #include <cstdio>
+#include <mutex>
 #include <set>
 #include <string>
+#include <utility>
 
 #include "orn_internal.h"
 #include "orn_quant.cuh"
@@ -383,6 +385,7 @@ struct Ring {
   uint32_t slot_bytes;
   int depth;
   int* err;
+  uint32_t limit;      // try_wait rounds before a wait gives up
 };
 
 // lane 0: one bulk copy of `bytes` (a multiple of 16) into a slot
@@ -402,7 +405,7 @@ ORN_D void ring_fill2(const Ring& R, int slot, const uint8_t* src0, const uint8_
 // all lanes: wait for a slot; false after the bounded wait ran out
 ORN_D bool ring_wait(const Ring& R, int slot, uint32_t parity) {
   const uint32_t bar = R.bar0 + 8 * slot;
-  for (uint32_t it = 0; it < kWaitLimit; ++it)
+  for (uint32_t it = 0; it < R.limit; ++it)
     if (mbar_try_wait(bar, parity)) return true;
   if ((threadIdx.x & 31) == 0) atomicExch(R.err, 1);
   return false;
@@ -420,6 +423,7 @@ ORN_D void ring_setup(Ring& R, uint8_t* base, uint32_t slot_bytes, int depth, in
   R.slot_bytes = slot_bytes;
   R.depth = depth;
   R.err = err;
+  R.limit = kWaitLimit;
   if (lane == 0)
     for (int i = 0; i < depth; ++i) mbar_init(R.bar0 + 8 * i, 1);
   fence_mbar_init();
@@ -1851,24 +1855,32 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
 constexpr size_t kSmemBudget = 220 * 1024;
 
 // launch label for the per-kernel time report (ORN_KTIME=1): kernel, rows, first job's shape
+std::mutex g_grant_mu;  // guards the label pool below and the table of shared-memory grants
 const char* launch_label(orn_ctx* ctx, const char* kern, int M, int kind, int O, int K) {
   if (!ctx->kt) return kern;
   static std::set<std::string> pool;
+  std::lock_guard<std::mutex> lock(g_grant_mu);
   char buf[96];
   snprintf(buf, sizeof buf, "%s M=%d kind=%d %dx%d", kern, M, kind, O, K);
   return pool.insert(buf).first->c_str();
 }
 
-// raise a kernel's dynamic shared-memory limit once (per kernel, per process)
+// raise a kernel's dynamic shared-memory limit once per (device, kernel): the attribute belongs to
+// the kernel's image on one device, and contexts of several devices (or host threads) share this table
+std::set<std::pair<int, const void*>> g_granted;  // (device, kernel address); instantiations share a type
+template <typename Kern>
+int grant_smem(orn_ctx* ctx, Kern kern, size_t bytes) {
+  const std::pair<int, const void*> key(ctx->device, reinterpret_cast<const void*>(kern));
+  std::lock_guard<std::mutex> lock(g_grant_mu);
+  if (g_granted.count(key)) return ORN_OK;
+  ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  g_granted.insert(key);
+  return ORN_OK;
+}
 template <typename Kern>
 int set_smem(orn_ctx* ctx, Kern kern, size_t bytes) {
-  static std::map<const void*, bool> granted;  // keyed by kernel address (instantiations share a type)
   if (bytes > 227 * 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "fused kernel: staged activations exceed shared memory");
-  const void* key = reinterpret_cast<const void*>(kern);
-  if (bytes > 48 * 1024 && !granted[key]) {
-    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    granted[key] = true;
-  }
+  if (bytes > 48 * 1024) return grant_smem(ctx, kern, 227 * 1024);
   return ORN_OK;
 }
 
@@ -1999,6 +2011,19 @@ int launch_moe_down_k(orn_ctx* ctx, cudaStream_t s, const MoeDownParams& P) {
   return orn_launch_check(ctx, launch_label(ctx, "k_moe_down", M, KIND, P.H, P.I));
 }
 
+
+// Probe of the give-up path: one warp sets up a ring like every streaming kernel, requests no copy
+// at all and waits on the empty slot with a short limit.  Nothing is in flight when the wait runs
+// out, so the kernel simply records the failure (as the streaming kernels do) and returns.
+__global__ void k_wait_probe(uint32_t rounds, int* err, int* waited_out) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  Ring R;
+  ring_setup(R, smem_raw, 128, 1, err);
+  R.limit = rounds;
+  __syncwarp();
+  const bool ok = ring_wait(R, 0, 0);
+  if ((threadIdx.x & 31) == 0) *waited_out = ok ? 1 : 0;
+}
 }  // namespace
 
 int f_norm_gemv(orn_ctx* ctx, cudaStream_t s, int M, const FusedPrologue& fp, const FusedJob* jobs, int njobs) {
@@ -2093,11 +2118,10 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
   // its CTAs become resident while the previous kernel drains, and without the cap the first SMs
   // to come free would take sixteen CTAs each instead of the grid spreading over the whole part.
   const size_t pad = 100 * 1024;
-  static bool granted = false;  // the kernel also has static shared memory: ask for the pad, not for the maximum
-  if (!granted) {
-    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_gdn<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pad));
-    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_gdn<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pad));
-    granted = true;
+  // the kernel also has static shared memory: ask for the pad, not for the maximum
+  {
+    int rc = Kc == 4 ? grant_smem(ctx, k_gdn<true>, pad) : grant_smem(ctx, k_gdn<false>, pad);
+    if (rc != ORN_OK) return rc;
   }
   if (Kc == 4) ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<true>, grid, block, pad, p));
   else ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 3, k_gdn<false>, grid, block, pad, p));
@@ -2117,4 +2141,9 @@ int f_attn(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, const bf16_t* k, cons
   dim3 grid(Hq, T);
   ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 4, k_attn, grid, dim3(1024), 0, p));
   return orn_launch_check(ctx, "k_attn");
+}
+
+int f_wait_probe(orn_ctx* ctx, cudaStream_t s, uint32_t rounds, int* dev_waited) {
+  k_wait_probe<<<1, 32, ring_bytes(1, 1, 128) + 128, s>>>(rounds, ctx->dev_err, dev_waited);
+  return orn_launch_check(ctx, "k_wait_probe");
 }

@@ -121,6 +121,7 @@ struct orn_model {
   orn_linear* fr_head = nullptr;
   uint32_t* fr_ids = nullptr;  // device
   int fr_n = 0;
+  int fr_gen = 0;  // bumped whenever the FR-Spec head is replaced: graphs that drafted through the old one are stale
   bool finalized = false;
   Workspace ws{};
   std::vector<void*> ws_allocs;
@@ -146,6 +147,7 @@ struct orn_cache {
     cudaGraphExec_t exec = nullptr;
     int seen = 0;
     int64_t launches = 0;
+    int fr_gen = 0;  // orn_model::fr_gen at capture time (FR-Spec graphs hold the pruned head's addresses)
   };
   std::map<int, StepGraph> graphs;
   uint32_t* mailbox_h = nullptr;  // pinned
@@ -692,8 +694,15 @@ int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar, 2 prefill row
   if (kind == 0 && c->h_mtp_pos + want > m->cfg.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "mtp: context exceeds max_ctx");
   static int no_graph = -1;
   if (no_graph < 0) { const char* e = getenv("ORN_NO_GRAPH"); no_graph = (e && e[0] == '1') ? 1 : 0; }
-  if (ctx->kt) no_graph = 1;  // per-kernel times need eager launches
-  if (g.exec != nullptr) {
+  const bool eager = no_graph || ctx->kt != nullptr;  // per-kernel times need eager launches
+  if (g.exec != nullptr && use_frspec && g.fr_gen != m->fr_gen) {
+    // the pruned head was replaced since this graph was captured: its kernel arguments point at
+    // freed memory.  Drop it; the shape is run eagerly once and captured again.
+    ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(s));
+    cudaGraphExecDestroy(g.exec);
+    g = orn_cache::StepGraph();
+  }
+  if (g.exec != nullptr && !eager) {
     ORN_CHECK_CUDA(ctx, cudaGraphLaunch(g.exec, s));
     ctx->launches += g.launches;
     if (kind == 0) { c->h_mtp_pos += want; c->cap_T = n_rows; }
@@ -706,7 +715,7 @@ int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar, 2 prefill row
     if (kind == 1) return ar_body(m, c);
     return forward_dev(m, c, m->ws.ids, n_rows, false, nullptr, nullptr);  // a window of prompt rows
   };
-  if (g.seen == 0 || no_graph || !use_fused()) {
+  if (g.seen == 0 || eager || !use_fused() || g.exec != nullptr) {
     g.seen += 1;
     return body();
   }
@@ -721,6 +730,7 @@ int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar, 2 prefill row
   cudaGraphDestroy(graph);
   if (e != cudaSuccess) { g.exec = nullptr; ORN_FAIL(ctx, ORN_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e)); }
   g.launches = ctx->launches - l0;
+  g.fr_gen = m->fr_gen;
   // the capture recorded the work without running it; the host bookkeeping it did stands
   ORN_CHECK_CUDA(ctx, cudaGraphLaunch(g.exec, s));
   return ORN_OK;
@@ -941,6 +951,8 @@ int32_t orn_frspec_set(orn_model* m, const uint32_t* host_ids, int32_t n) {
     if (seen[host_ids[i]]) ORN_FAIL(m->ctx, ORN_ERR_ARG, "frspec: duplicate id");
     seen[host_ids[i]] = 1;
   }
+  ORN_CHECK_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));  // nothing may still read the old head
+  m->fr_gen += 1;
   if (m->fr_head) { orn_linear_destroy(m->ctx, m->fr_head); m->fr_head = nullptr; }
   cudaFree(m->fr_ids); m->fr_ids = nullptr;
   CK(orn_linear_gather_rows(m->ctx, m->lm_head, host_ids, n, &m->fr_head));
@@ -1274,7 +1286,28 @@ int32_t orn_moe_block(orn_ctx* ctx, const orn_linear* gate, const orn_linear* sw
   moe.gate = (orn_linear*)gate; moe.sw_gate = (orn_linear*)sw_gate; moe.sw_up = (orn_linear*)sw_up;
   moe.sw_down = (orn_linear*)sw_down; moe.sh_gate = (orn_linear*)sh_gate; moe.sh_up = (orn_linear*)sh_up;
   moe.sh_down = (orn_linear*)sh_down; moe.sh_egate = (orn_linear*)sh_egate;
-  if (rc == ORN_OK) rc = moe_block(&shell, moe, dev_x, T, dev_out, dev_inds_out);
+  // the route the model takes (three persistent kernels) whenever the shapes allow it; the
+  // one-kernel-per-op sequence under ORN_UNFUSED=1 and for shapes outside the fused kernels' limits
+  const bool fused = use_fused() && cfg.hidden % 256 == 0 && cfg.hidden <= 4096 && cfg.n_experts <= 512 && top_k <= 8 &&
+                     cfg.expert_inter % 256 == 0 && cfg.shared_inter % 256 == 0 && cfg.expert_inter <= 2048 &&
+                     cfg.shared_inter <= 2048 && sw_gate->kind == sw_up->kind && sw_down->kind == sh_down->kind &&
+                     sh_gate->kind == sh_up->kind && sh_gate->K == cfg.hidden && sh_up->O == cfg.shared_inter &&
+                     sh_up->K == cfg.hidden;
+  if (rc == ORN_OK && fused) {
+    FusedPrologue fp;
+    fp.mode = PRO_PLAIN; fp.K = cfg.hidden; fp.a = dev_x;
+    FusedJob jobs[3];
+    jobs[0].lin = gate; jobs[0].out = w.gates;
+    jobs[1].lin = sh_gate; jobs[1].lin2 = sh_up; jobs[1].out = w.sact; jobs[1].epi = EPI_SWIGLU;
+    jobs[2].lin = sh_egate; jobs[2].out = w.gs;
+    uint32_t* inds = dev_inds_out ? dev_inds_out : w.inds;
+    rc = f_norm_gemv(ctx, ctx->stream, T, fp, jobs, 3);
+    if (rc == ORN_OK) rc = f_moe_up(ctx, ctx->stream, T, w.gates, dev_x, sw_gate, sw_up, top_k, inds, w.scores, w.eact);
+    if (rc == ORN_OK)
+      rc = f_moe_down(ctx, ctx->stream, T, w.eact, w.sact, inds, w.scores, w.gs, sw_down, sh_down, top_k, norm_topk, dev_out);
+  } else if (rc == ORN_OK) {
+    rc = moe_block(&shell, moe, dev_x, T, dev_out, dev_inds_out);
+  }
   if (rc == ORN_OK) rc = orn_sync(ctx);
   else cudaStreamSynchronize(ctx->stream);
   for (void* p : shell.ws_allocs) cudaFree(p);

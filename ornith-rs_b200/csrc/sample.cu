@@ -10,6 +10,8 @@
 // bf(max - lse); so one pass produces per-1024-logit chunk (max, sum), and a
 // second, single-CTA pass merges the chunks in ascending order and scans only
 // the first chunk whose maximum reaches the winning lp value.
+#include <atomic>
+
 #include "orn_internal.h"
 
 namespace {
@@ -133,9 +135,10 @@ int k_greedy(orn_ctx* ctx, cudaStream_t s, const bf16_t* logits, int T, int V, i
 // allocator on every call.  Some callers must not touch the allocator at all: a
 // decode loop that runs with the allocator's device-wide lock held elsewhere
 // (another thread loading weights), a host thread whose latency budget cannot
-// absorb an allocation that may synchronise the whole device, or code that has
-// already begun recording work on its stream and may no longer call routines
-// that allocate.  For them the same two kernels run on a fixed scratch array
+// absorb an allocation that may synchronise the whole device, or code that is
+// about to record work on its stream (the first call on a device looks the
+// array's address up and must come before any stream capture begins; later
+// calls only launch the two kernels).  For them the same two kernels run on a fixed scratch array
 // that lives in the module's global memory.
 //
 // The array is sized for the largest decode window and vocabulary the engine
@@ -154,8 +157,10 @@ constexpr int kStaticGreedyMaxT = 4;
 constexpr int kStaticGreedyMaxV = 262144;
 constexpr size_t kStaticGreedyFloats = (size_t)kStaticGreedyMaxT * 2 * (kStaticGreedyMaxV / 1024);
 constexpr int kMaxDevices = 64;
-float* g_static_scratch_ptr[kMaxDevices];   // device address of the array, per device
-bool g_static_scratch_ready[kMaxDevices];
+// Device address of the array per device; null = not looked up yet.  Published with release /
+// read with acquire, so a second host thread on the same device never sees a half-made entry
+// (two threads that race on the first call both look the address up and store the same value).
+std::atomic<float*> g_static_scratch_ptr[kMaxDevices];
 }  // namespace
 
 static __device__ __align__(256) float g_greedy_static_scratch[kStaticGreedyFloats];
@@ -169,15 +174,21 @@ extern "C" int32_t orn_greedy_static(orn_ctx* ctx, const uint16_t* logits, int32
              "use orn_greedy for larger inputs");
   const int dev = ctx->device;
   if (dev < 0 || dev >= kMaxDevices) ORN_FAIL(ctx, ORN_ERR_ARG, "orn_greedy_static: device index above 63");
-  if (!g_static_scratch_ready[dev]) {
+  float* scratch = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // one-time set-up per device, with that device current: ask the runtime where this
-    // device's copy of the array lives (the array's name is not a device address on the host)
+    // device's copy of the array lives (the array's name is not a device address on the host).
+    // The calling thread's current device is put back afterwards.
+    int prev = -1;
+    ORN_CHECK_CUDA(ctx, cudaGetDevice(&prev));
     ORN_CHECK_CUDA(ctx, cudaSetDevice(dev));
     float* p = nullptr;
-    ORN_CHECK_CUDA(ctx, cudaGetSymbolAddress((void**)&p, g_greedy_static_scratch));
+    const cudaError_t e = cudaGetSymbolAddress((void**)&p, g_greedy_static_scratch);
+    if (prev >= 0 && prev != dev) cudaSetDevice(prev);
+    if (e != cudaSuccess) ORN_FAIL(ctx, ORN_ERR_CUDA, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
     if (p == nullptr) ORN_FAIL(ctx, ORN_ERR_CUDA, "orn_greedy_static: no device address for the scratch array");
-    g_static_scratch_ptr[dev] = p;
-    g_static_scratch_ready[dev] = true;
+    g_static_scratch_ptr[dev].store(p, std::memory_order_release);
+    scratch = p;
   }
-  return k_greedy(ctx, ctx->stream, (const bf16_t*)logits, T, V, normalize, tokens, g_static_scratch_ptr[dev]);
+  return k_greedy(ctx, ctx->stream, (const bf16_t*)logits, T, V, normalize, tokens, scratch);
 }
