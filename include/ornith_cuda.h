@@ -145,6 +145,20 @@ int32_t orn_gemv(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x, int
 int32_t orn_gather_gemv(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x,
                         const uint32_t* dev_lhs, const uint32_t* dev_rhs, int32_t rows,
                         uint16_t* dev_y);
+/* Linear::matmul at prompt width -> kquant::qmm_t (src/ops/kquant.rs:783-812, kernels/kquant_mm.h:
+ * 88-360) / quantized_matmul / matmul above the row limit (kquant.rs:MM_ROW_LIMIT = 16):
+ * y[M,O] = x[M,K] W^T on the tensor cores, weights dequantised to bfloat16 tile by tile, float32
+ * accumulation, bfloat16 out (float32 when out_f32 != 0).  Any M >= 1 is accepted; the result agrees with orn_gemv to rounding,
+ * not bit for bit (the reference exempts this path from row invariance, src/generate.rs:99).
+ * K must be a multiple of 64. */
+int32_t orn_gemm(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x, int32_t M,
+                 void* dev_y, int32_t out_f32);
+/* Linear::gather_matmul at prompt width -> kquant::gather_qmm_t (kquant.rs:905-972): row r =
+ * W[rhs[r]] . x[lhs[r]].  Rows are counting-sorted by expert on the device (moe.rs:463-508), each
+ * expert's rows multiply its matrix once, results land in row order.  Synchronises. */
+int32_t orn_gather_gemm(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x,
+                        const uint32_t* dev_lhs, const uint32_t* dev_rhs, int32_t rows,
+                        void* dev_y, int32_t out_f32);
 /* ops::embedding (src/ops/embedding.rs:18-47) for the affine-8 table */
 int32_t orn_embedding(orn_ctx* ctx, const orn_linear* table, const uint32_t* dev_ids, int32_t T,
                       uint16_t* dev_out);

@@ -211,6 +211,18 @@ class Linear:
         self.ctx.check(self.ctx._lib.orn_gemv(self.ctx.h, self.h, _p(x), M, y.ptr, int(out_f32)), "orn_gemv")
         return y
 
+    def matmul_wide(self, x, M, out_f32=False):
+        """Linear::matmul at prompt width (tensor cores; agrees with matmul to rounding)."""
+        y = self.ctx.empty((M, self.O), np.float32 if out_f32 else np.uint16)
+        self.ctx.check(self.ctx._lib.orn_gemm(self.ctx.h, self.h, _p(x), M, y.ptr, int(out_f32)), "orn_gemm")
+        return y
+
+    def gather_matmul_wide(self, x, lhs, rhs, rows, out_f32=False):
+        y = self.ctx.empty((rows, self.O), np.float32 if out_f32 else np.uint16)
+        self.ctx.check(self.ctx._lib.orn_gather_gemm(self.ctx.h, self.h, _p(x), _p(lhs), _p(rhs), rows, y.ptr,
+                                                     int(out_f32)), "orn_gather_gemm")
+        return y
+
     def gather_matmul(self, x, lhs, rhs, rows):
         y = self.ctx.empty((rows, self.O), np.uint16)
         self.ctx.check(self.ctx._lib.orn_gather_gemv(self.ctx.h, self.h, _p(x), _p(lhs), _p(rhs), rows, y.ptr),

@@ -394,6 +394,35 @@ int32_t orn_gather_gemv(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev
   return k_gather_gemv(ctx, ctx->stream, lin, dev_x, dev_lhs, dev_rhs, rows, dev_y);
 }
 
+int32_t orn_gemm(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x, int32_t M, void* dev_y, int32_t out_f32) {
+  if (!ctx || !lin || !dev_x || !dev_y || M < 1) return ORN_ERR_ARG;
+  return f_qgemm(ctx, ctx->stream, lin, dev_x, M, dev_y, lin->O, nullptr, nullptr, out_f32);
+}
+
+int32_t orn_gather_gemm(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x, const uint32_t* dev_lhs,
+                        const uint32_t* dev_rhs, int32_t rows, void* dev_y, int32_t out_f32) {
+  if (!ctx || !lin || !dev_x || !dev_lhs || !dev_rhs || !dev_y || rows < 1) return ORN_ERR_ARG;
+  // sort the rows by expert, gather their inputs, run the grouped product, results back in row order
+  cudaStream_t s = ctx->stream;
+  const size_t seg_b = ((size_t)(2 * lin->E + 2) * sizeof(int) + 255) & ~(size_t)255;
+  const size_t perm_b = ((size_t)rows * sizeof(uint32_t) + 255) & ~(size_t)255;
+  const size_t xs_b = ((size_t)rows * lin->K * sizeof(bf16_t) + 255) & ~(size_t)255;
+  const size_t sc_b = qgemm_scratch_bytes(rows, lin->E, lin->O);
+  uint8_t* buf = nullptr;
+  CK(orn_alloc(ctx, seg_b + perm_b + xs_b + sc_b, (void**)&buf));
+  int* seg = reinterpret_cast<int*>(buf);
+  uint32_t* perm = reinterpret_cast<uint32_t*>(buf + seg_b);
+  bf16_t* xs = reinterpret_cast<bf16_t*>(buf + seg_b + perm_b);
+  int rc = f_route_sort(ctx, s, dev_rhs, rows, lin->E, seg, seg + lin->E + 1, perm);
+  if (rc == ORN_OK) rc = f_gather_rows(ctx, s, dev_x, dev_lhs, perm, rows, lin->K, xs);
+  QGemmGroup g{seg, perm, 0};
+  if (rc == ORN_OK) rc = f_qgemm(ctx, s, lin, xs, rows, dev_y, lin->O, &g, buf + seg_b + perm_b + xs_b, out_f32);
+  if (rc == ORN_OK) rc = orn_sync(ctx);
+  else cudaStreamSynchronize(s);
+  cudaFree(buf);
+  return rc;
+}
+
 int32_t orn_embedding(orn_ctx* ctx, const orn_linear* table, const uint32_t* dev_ids, int32_t T,
                       uint16_t* dev_out) {
   if (!ctx || !table || !dev_ids || !dev_out || T < 1) return ORN_ERR_ARG;

@@ -44,3 +44,16 @@ int f_attn(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, const bf16_t* k, cons
 // one warp waits, with a limit of `rounds` tries, for a copy that was never requested: sets the
 // context's device error flag; *dev_waited receives 0
 int f_wait_probe(orn_ctx* ctx, cudaStream_t s, uint32_t rounds, int* dev_waited);
+
+// ---- gemm.cu: the wide (>= 16 rows) mat-mul on the tensor cores
+struct QGemmGroup {
+  const int* seg;           // device [E + 1]: expert e owns sorted rows seg[e] .. seg[e+1]-1
+  const uint32_t* row_map;  // device [rows] or null: output row of sorted row p
+  int bn_hint;              // > 0: expected rows per expert (picks the token-tile width)
+};
+size_t qgemm_scratch_bytes(int rows, int E, int O);
+int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, int rows, void* y, int ldy,
+            const QGemmGroup* grp /*nullable: dense*/, void* scratch /*grouped only*/, int out_f32 = 0);
+int f_route_sort(orn_ctx* ctx, cudaStream_t s, const uint32_t* rhs, int rows, int E, int* seg, int* cursor, uint32_t* perm);
+int f_gather_rows(orn_ctx* ctx, cudaStream_t s, const bf16_t* x, const uint32_t* lhs /*nullable*/, const uint32_t* perm,
+                  int rows, int K, bf16_t* xs);

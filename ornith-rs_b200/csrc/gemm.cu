@@ -1,0 +1,618 @@
+// Wide mat-mul on the 5th-generation tensor cores: y[rows, O] = x[rows, K] W^T for rows >= 16,
+// with W in any of the library's weight formats.
+//
+// Replaces kquant::qmm_t / gather_qmm_t (src/ops/kquant.rs:783-812,905-972, kernels/kquant_mm.h:
+// 88-360: a tile of weights is dequantised into threadgroup memory and multiplied by simdgroup
+// matrices) and the prompt-width side of quantized_matmul / matmul (src/ops/quantized.rs:249-333,
+// src/ops/matmul.rs:486-526).  The reference exempts this path from row invariance
+// (src/generate.rs:99): a prompt row computed here does not carry the bits of the one-row
+// mat-vec, it agrees with it to rounding (weights are rounded to bfloat16 once, products are
+// accumulated in float32 by the tensor core).
+//
+// Shape of the kernel.  The contraction runs with the WEIGHTS as the A operand and the TOKENS as
+// the B operand, D[feature, token] = sum_k W[feature, k] x[token, k]: the tensor core's M is always
+// a full 128 features, its N is the token-tile width BN (16..256), so a launch with few tokens per
+// expert (a routed prompt chunk, a batched decode step) wastes no tensor-core work on padding.
+//   - a CTA owns (feature tile of 128, up to NT token tiles) and keeps NT accumulators of
+//     128 x BN float32 in tensor memory (NT * BN <= 512 columns);
+//   - per block of 64 weights along K: one warp's elected lane brings the NT token tiles
+//     [BN, 64] bf16 with TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, this GPU's memory, no
+//     multicast); four warps dequantise the 128 x 64 weight tile from the row records in HBM
+//     straight into shared memory in the same swizzled K-major layout (one thread per feature
+//     row: Q4_K / Q6_K / affine-8 / bf16 -> bf16); another elected lane issues 4 * NT
+//     tcgen05.mma (128 x BN x 16, kind::f16, bf16 inputs, f32 accumulate) and commits the stage
+//     back to the producers;
+//   - the four dequantising warps then read the accumulators (tcgen05.ld, one TMEM lane = one
+//     feature per thread), round to bfloat16 and store y[token, feature].
+// Stages are a ring guarded by mbarriers; every wait is bounded and reports through the context's
+// device error flag, and the CTA frees its tensor memory on every path.
+//
+// The grouped form serves rows sorted by expert (counting_sort + switch_glu_rows,
+// src/ops/moe.rs:283-314,463-508): a small plan kernel turns the experts' row ranges into work
+// items (expert, first row, rows, feature tile) and persistent CTAs walk that list.
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+#include <set>
+#include <string>
+#include <utility>
+
+#include "fused.h"
+#include "orn_internal.h"
+#include "orn_quant.cuh"
+
+namespace {
+
+constexpr int BM = 128;            // features per tile: the tensor core's M
+constexpr int BK = 64;             // weights per K block: one 128-byte swizzle row of bf16
+constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2..5: dequantise + epilogue
+constexpr int kDqWarps = 4;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kWTileBytes = BM * BK * 2;
+constexpr int kMaxStages = 4;
+constexpr uint32_t kGemmWaitLimit = 1u << 16;  // try_wait rounds (each may sleep kGemmHintNs)
+constexpr uint32_t kGemmHintNs = 20000;
+
+struct GemmParams {
+  LinDev W;
+  const int4* items;   // grouped: {expert, first row, rows, feature tile}; null = dense
+  const int* n_items;  // grouped: device count
+  int dense_items;     // dense: feature tiles x token groups
+  int rows;            // rows of x (dense) / of the sorted row space (grouped)
+  int O, K;
+  bf16_t* y;
+  float* y_f32;              // non-null: float32 output instead of bfloat16
+  int ldy;                   // elements between output rows
+  const uint32_t* row_map;   // nullable: output row of sorted row p
+  int BN, NT, stages, f_tiles;
+  uint32_t stage_bytes;
+  int* err;
+};
+
+ORN_D uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+ORN_D void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+ORN_D void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+ORN_D void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+ORN_D bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(kGemmHintNs)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait: false (and the error flag set) when the phase never completes
+ORN_D bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
+  for (uint32_t it = 0; it < kGemmWaitLimit; ++it)
+    if (mbar_try(bar, parity)) return true;
+  atomicExch(err, 1);
+  return false;
+}
+ORN_D void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+ORN_D void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+ORN_D void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+ORN_D void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+ORN_D void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, 128 x N x 16, bf16 in, f32 out
+ORN_D void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// shared-memory operand descriptor: K-major, 128-byte swizzle, rows of 128 bytes, groups of 8 rows
+// 1024 bytes apart (start >> 4 | LBO 1 | SBO 64 | version 1 | layout SWIZZLE_128B)
+ORN_D uint64_t smem_desc(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+ORN_D void tmem_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+}
+ORN_D void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+ORN_D void st_chunk(uint32_t row_addr, int rsw, int c, uint32_t a, uint32_t b, uint32_t cc, uint32_t d) {
+  // 16-byte chunk c of a 128-byte row, at its swizzled place (chunk index xor row mod 8)
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)((c ^ rsw) << 4)), "r"(a), "r"(b),
+               "r"(cc), "r"(d)
+               : "memory");
+}
+ORN_D uint32_t pack_bf2(float lo, float hi) { return (uint32_t)f2bf(lo) | ((uint32_t)f2bf(hi) << 16); }
+
+// One feature row, K block kb (64 weights): dequantise to bfloat16 and store the row's 128 bytes.
+template <int KIND>
+ORN_D void dequant_row(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw);
+
+template <>
+ORN_D void dequant_row<ORN_BF16>(const uint8_t* rec, const RecGeom&, int kb, uint32_t row_addr, int rsw) {
+  const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 128);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint4 v = __ldg(src + c);
+    st_chunk(row_addr, rsw, c, v.x, v.y, v.z, v.w);
+  }
+}
+
+// affine 8-bit, group 64: w = scale * q + bias (one fma, as the embedding lookup computes it)
+template <>
+ORN_D void dequant_row<ORN_A8>(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw) {
+  const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 64);
+  const uint32_t sb = __ldg(reinterpret_cast<const uint32_t*>(rec + g.b0) + kb);
+  const float sc = bf_lo(sb), bi = bf_hi(sb);
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    const uint4 q = __ldg(src + h);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o[2 * i] = pack_bf2(fmaf(sc, byte_f<0>(w[i]), bi), fmaf(sc, byte_f<1>(w[i]), bi));
+      o[2 * i + 1] = pack_bf2(fmaf(sc, byte_f<2>(w[i]), bi), fmaf(sc, byte_f<3>(w[i]), bi));
+    }
+    st_chunk(row_addr, rsw, 2 * h, o[0], o[1], o[2], o[3]);
+    st_chunk(row_addr, rsw, 2 * h + 1, o[4], o[5], o[6], o[7]);
+  }
+}
+
+// Q4_K (kernels/q4k.metal:43-96): 64 weights = 32 code bytes; low nibbles are sub-block 2i, high
+// nibbles sub-block 2i+1; w = (d * sc) * q - (dmin * m)
+template <>
+ORN_D void dequant_row<ORN_Q4K>(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw) {
+  const int b = kb >> 2, i4 = kb & 3;
+  const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(rec + g.b0 + (size_t)b * 16));
+  const float d = h2f((uint16_t)(hdr.x & 0xffff)), dmin = h2f((uint16_t)(hdr.x >> 16));
+  float sc0, m0, sc1, m1;
+  q4k_scale_min(2 * i4, hdr.y, hdr.z, hdr.w, &sc0, &m0);
+  q4k_scale_min(2 * i4 + 1, hdr.y, hdr.z, hdr.w, &sc1, &m1);
+  const float a0 = d * sc0, b0 = dmin * m0, a1 = d * sc1, b1 = dmin * m1;
+  const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)b * 128 + i4 * 32);
+  const uint4 qa = __ldg(src), qb = __ldg(src + 1);
+  const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {  // 8 code bytes -> chunk c (low nibbles) and chunk c + 4 (high nibbles)
+    uint32_t lo[4], hi[4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t l4 = w[2 * c + j] & 0x0F0F0F0Fu, h4 = (w[2 * c + j] >> 4) & 0x0F0F0F0Fu;
+      lo[2 * j] = pack_bf2(a0 * byte_f<0>(l4) - b0, a0 * byte_f<1>(l4) - b0);
+      lo[2 * j + 1] = pack_bf2(a0 * byte_f<2>(l4) - b0, a0 * byte_f<3>(l4) - b0);
+      hi[2 * j] = pack_bf2(a1 * byte_f<0>(h4) - b1, a1 * byte_f<1>(h4) - b1);
+      hi[2 * j + 1] = pack_bf2(a1 * byte_f<2>(h4) - b1, a1 * byte_f<3>(h4) - b1);
+    }
+    st_chunk(row_addr, rsw, c, lo[0], lo[1], lo[2], lo[3]);
+    st_chunk(row_addr, rsw, c + 4, hi[0], hi[1], hi[2], hi[3]);
+  }
+}
+
+// Q6_K (kernels/q6k.metal:47-77): per 128 weights, byte l of ql / qh gives q1 (weight l), q2 (l + 32),
+// q3 (l + 64), q4 (l + 96); a K block of 64 is (q1, q2) or (q3, q4) of one half; w = (d * sc) * (q - 32)
+template <>
+ORN_D void dequant_row<ORN_Q6K>(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw) {
+  const int b = kb >> 2, half = (kb >> 1) & 1, hi = kb & 1;
+  const uint8_t* base = rec + (size_t)b * 192;
+  const uint4* ql = reinterpret_cast<const uint4*>(base + 64 * half);
+  const uint4* qh = reinterpret_cast<const uint4*>(base + 128 + 32 * half);
+  const int8_t* sc = reinterpret_cast<const int8_t*>(rec + g.b0 + (size_t)b * 16 + 8 * half) + 4 * hi;
+  const float d = h2f(__ldg(reinterpret_cast<const uint16_t*>(rec + g.b0 + g.b1) + b));
+  // scales of elements 0..15, 16..31 (first code set) and 32..47, 48..63 (second code set)
+  const float s00 = d * (float)sc[0], s01 = d * (float)sc[1], s10 = d * (float)sc[2], s11 = d * (float)sc[3];
+  const uint4 h0 = __ldg(qh), h1 = __ldg(qh + 1);
+  const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+  for (int set = 0; set < 2; ++set) {  // set 0: ql bytes 0..31 (q1 / q3), set 1: ql bytes 32..63 (q2 / q4)
+    const uint4 l0 = __ldg(ql + 2 * set), l1 = __ldg(ql + 2 * set + 1);
+    const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+    const int hs = 2 * set + 4 * hi;  // bit position of this code set's two high bits in qh
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float s = set == 0 ? (c < 2 ? s00 : s01) : (c < 2 ? s10 : s11);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t low = hi ? ((lw[2 * c + j] >> 4) & 0x0F0F0F0Fu) : (lw[2 * c + j] & 0x0F0F0F0Fu);
+        const uint32_t q = low | (((hw[2 * c + j] >> hs) & 0x03030303u) << 4);
+        o[2 * j] = pack_bf2(s * byte_m32_f<0>(q), s * byte_m32_f<1>(q));
+        o[2 * j + 1] = pack_bf2(s * byte_m32_f<2>(q), s * byte_m32_f<3>(q));
+      }
+      st_chunk(row_addr, rsw, 4 * set + c, o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+ORN_D void zero_row(uint32_t row_addr) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) st_chunk(row_addr, 0, c, 0u, 0u, 0u, 0u);
+}
+
+struct Item {
+  int e, tok0, ntok, ft;
+};
+ORN_D bool get_item(const GemmParams& P, int w, int n_items, Item& it) {
+  if (w >= n_items) return false;
+  if (P.items != nullptr) {
+    const int4 v = P.items[w];
+    it.e = v.x; it.tok0 = v.y; it.ntok = v.z; it.ft = v.w;
+  } else {
+    const int g = w / P.f_tiles;
+    it.e = 0;
+    it.ft = w - g * P.f_tiles;
+    it.tok0 = g * P.NT * P.BN;
+    it.ntok = min(P.NT * P.BN, P.rows - it.tok0);
+  }
+  return true;
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant__ CUtensorMap xmap, GemmParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t s_bar[2 * kMaxStages + 2];
+  __shared__ uint32_t s_tmem;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem0 = (smem_addr(smem_raw) + 1023u) & ~1023u;  // swizzled tiles want 1024-byte alignment
+  const int S = P.stages;
+  const uint32_t bar_full = smem_addr(&s_bar[0]), bar_empty = smem_addr(&s_bar[kMaxStages]);
+  const uint32_t bar_acc_full = smem_addr(&s_bar[2 * kMaxStages]), bar_acc_empty = smem_addr(&s_bar[2 * kMaxStages + 1]);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(bar_full + 8 * i, 1 + kDqWarps);  // the TMA producer's expect_tx arrival + one per dequantising warp
+      mbar_init(bar_empty + 8 * i, 1);            // the MMA warp's commit
+    }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, kDqWarps);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  __syncwarp();
+  if (warp == 0) {  // tensor memory: all 512 columns (one CTA per SM: the launch's shared memory sees to that)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&s_tmem)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+  const int n_items = P.items != nullptr ? *P.n_items : P.dense_items;
+  const int KB = P.K / BK;
+  const uint32_t x_tile_bytes = (uint32_t)P.BN * 128u;
+
+  if (warp == 0) {
+    // ---- TMA producer: the token tiles of every stage
+    if (lane == 0) {
+      uint32_t it = 0;
+      Item w;
+      for (int wi = blockIdx.x; get_item(P, wi, n_items, w); wi += gridDim.x) {
+        const int nt = (w.ntok + P.BN - 1) / P.BN;
+        bool ok = true;
+        for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, P.err);
+          if (!ok) break;
+          mbar_expect_tx(bar_full + 8 * s, (uint32_t)nt * x_tile_bytes);
+          const uint32_t dst = smem0 + s * P.stage_bytes + kWTileBytes;
+          for (int t = 0; t < nt; ++t)
+            tma_load_2d(dst + t * x_tile_bytes, &xmap, kb * BK, w.tok0 + t * P.BN, bar_full + 8 * s);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(P.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      uint32_t it = 0, acc_ph = 0;
+      Item w;
+      for (int wi = blockIdx.x; get_item(P, wi, n_items, w); wi += gridDim.x) {
+        const int nt = (w.ntok + P.BN - 1) / P.BN;
+        bool ok = mbar_wait(bar_acc_empty, acc_ph ^ 1u, P.err);  // the previous item's accumulators were read
+        tc_fence_after();
+        for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          ok = mbar_wait(bar_full + 8 * s, ph, P.err);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t wa = smem0 + s * P.stage_bytes, xa = wa + kWTileBytes;
+          for (int t = 0; t < nt; ++t)
+#pragma unroll
+            for (int j = 0; j < BK / 16; ++j)
+              tc_mma(tmem + (uint32_t)(t * P.BN), smem_desc(wa + j * 32), smem_desc(xa + t * x_tile_bytes + j * 32), idesc,
+                     (kb > 0 || j > 0) ? 1u : 0u);
+          tc_commit(bar_empty + 8 * s);  // the stage is free once these MMAs have read it
+        }
+        if (!ok) break;
+        tc_commit(bar_acc_full);
+        acc_ph ^= 1u;
+      }
+    }
+  } else {
+    // ---- dequantising warps, then the epilogue of the item
+    const int r = threadIdx.x - 64;  // feature row of the tile this thread dequantises
+    const int q = warp & 3;          // TMEM lane quadrant this warp may read
+    const RecGeom geo = rec_geom(KIND, P.K);
+    uint32_t it = 0, acc_ph = 0;
+    Item w;
+    bool ok = true;
+    for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
+      const int f = w.ft * BM + r;
+      const uint8_t* rec = P.W.w + ((size_t)w.e * P.O + min(f, P.O - 1)) * geo.rec;
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
+        ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, P.err);
+        if (!ok) break;
+        const uint32_t row_addr = smem0 + s * P.stage_bytes + (uint32_t)r * 128u;
+        if (f < P.O) dequant_row<KIND>(rec, geo, kb, row_addr, r & 7);
+        else zero_row(row_addr);
+        fence_async_smem();  // the tensor core reads these bytes through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_full + 8 * s);
+      }
+      if (!ok) break;
+      ok = mbar_wait(bar_acc_full, acc_ph, P.err);
+      if (!ok) break;
+      acc_ph ^= 1u;
+      tc_fence_after();
+      const int fo = w.ft * BM + q * 32 + lane;  // TMEM lane = feature
+      const int nt = (w.ntok + P.BN - 1) / P.BN;
+      for (int t = 0; t < nt; ++t) {
+        for (int c0 = 0; c0 < P.BN; c0 += 16) {
+          if (t * P.BN + c0 >= w.ntok) break;  // warp-uniform
+          uint32_t v[16];
+          tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * P.BN + c0), v);
+          tmem_ld_wait();
+          if (fo < P.O) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int tok = t * P.BN + c0 + j;
+              if (tok < w.ntok) {
+                const size_t orow = P.row_map != nullptr ? P.row_map[w.tok0 + tok] : (size_t)(w.tok0 + tok);
+                if (P.y_f32 != nullptr) P.y_f32[orow * P.ldy + fo] = __uint_as_float(v[j]);
+                else P.y[orow * P.ldy + fo] = f2bf(__uint_as_float(v[j]));
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- grouped form: plan and row movement --------------------------------------------------------
+// counts[e] = rows routed to expert e (block-wide histogram), then seg[e] = exclusive scan
+__global__ void k_route_count(const uint32_t* rhs, int rows, int E, int* seg /*[E+1]*/, int* cursor /*[E]*/) {
+  extern __shared__ int s_cnt[];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) s_cnt[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+    const uint32_t e = rhs[i];
+    if (e < (uint32_t)E) atomicAdd(&s_cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      seg[e] = acc;
+      cursor[e] = acc;
+      acc += s_cnt[e];
+    }
+    seg[E] = acc;
+  }
+}
+// stable placement: sorted position of row i = seg[e] + (number of earlier rows with the same expert).
+// One warp per expert scans the routing table in order, so the order inside an expert is the
+// original order (counting_sort, src/ops/moe.rs:463-508).
+__global__ void k_route_place(const uint32_t* rhs, int rows, int E, const int* seg, uint32_t* perm /*[rows]: sorted -> original*/) {
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (e >= E) return;
+  int pos = seg[e];
+  for (int base = 0; base < rows; base += 32) {
+    const int i = base + lane;
+    const bool mine = i < rows && rhs[i] == (uint32_t)e;
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (mine) perm[pos + __popc(m & ((1u << lane) - 1u))] = (uint32_t)i;
+    pos += __popc(m);
+  }
+}
+// xs[p] = x[lhs[perm[p]]] (rows of K bf16)
+__global__ void k_gather_rows(const bf16_t* x, const uint32_t* lhs, const uint32_t* perm, int rows, int K, bf16_t* xs) {
+  const int p = blockIdx.x;
+  if (p >= rows) return;
+  const uint32_t o = perm[p];
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(lhs ? lhs[o] : o) * K);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)p * K);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+}
+// work items of the grouped launch: expert e's rows in groups of `span`, every feature tile
+__global__ void k_plan_items(const int* seg, int E, int span, int f_tiles, int4* items, int* n_items, int max_items) {
+  __shared__ int s_off[1025];
+  const int e = threadIdx.x;
+  int mine = 0;
+  if (e < E) mine = ((seg[e + 1] - seg[e] + span - 1) / span) * f_tiles;
+  s_off[e + 1] = mine;
+  if (e == 0) s_off[0] = 0;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i <= (int)blockDim.x; ++i) s_off[i] += s_off[i - 1];
+    *n_items = min(s_off[blockDim.x], max_items);
+  }
+  __syncthreads();
+  if (e < E) {
+    int at = s_off[e];
+    const int first = seg[e], n = seg[e + 1] - seg[e];
+    for (int g = 0; g * span < n; ++g)
+      for (int ft = 0; ft < f_tiles; ++ft, ++at)
+        if (at < max_items) items[at] = make_int4(e, first + g * span, min(span, n - g * span), ft);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+std::mutex g_gemm_mu;
+std::set<std::pair<int, int>> g_gemm_granted;  // (device, format): shared-memory limit raised
+
+template <int KIND>
+int launch_qgemm(orn_ctx* ctx, cudaStream_t s, const CUtensorMap& map, const GemmParams& P, int grid, size_t smem) {
+  {
+    std::lock_guard<std::mutex> lock(g_gemm_mu);
+    if (!g_gemm_granted.count({ctx->device, KIND})) {
+      ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_qgemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));  // + static barriers
+      g_gemm_granted.insert({ctx->device, KIND});
+    }
+  }
+  k_qgemm<KIND><<<grid, kGemmThreads, smem, s>>>(map, P);
+  return orn_launch_check(ctx, "k_qgemm");
+}
+
+}  // namespace
+
+// device scratch of the grouped form: the item count, then the work items (an expert contributes
+// one item per feature tile and started group of rows; groups hold at least 128 rows)
+size_t qgemm_scratch_bytes(int rows, int E, int O) {
+  const int f_tiles = (O + BM - 1) / BM;
+  const size_t max_items = (size_t)f_tiles * ((size_t)E + rows / 128 + 1);
+  return 256 + max_items * sizeof(int4);
+}
+
+// y[rows, O] (row stride ldy) = x[rows, K] W^T.  grp != null: rows are sorted by expert, expert e
+// owns rows seg[e] .. seg[e+1]-1 (device array of E + 1 ints) and multiplies by W[e]; row p of the
+// result goes to output row row_map[p] when row_map is given.  scratch: qgemm_scratch_bytes() of
+// device memory for the grouped form.
+int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, int rows, void* y, int ldy,
+            const QGemmGroup* grp, void* scratch, int out_f32) {
+  if (rows < 1) return ORN_OK;
+  if (L->K % BK) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: K must be a multiple of 64");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: x must be 16-byte aligned");
+  if (grp == nullptr && L->E != 1) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: a routed weight goes through the grouped form");
+  EncodeTiledFn enc = encode_tiled();
+  if (enc == nullptr) ORN_FAIL(ctx, ORN_ERR_CUDA, "gemm: the driver has no cuTensorMapEncodeTiled");
+  GemmParams P;
+  P.W = lin_dev(L);
+  P.O = L->O; P.K = L->K; P.rows = rows; P.ldy = ldy; P.err = ctx->dev_err;
+  P.y = out_f32 ? nullptr : reinterpret_cast<bf16_t*>(y);
+  P.y_f32 = out_f32 ? reinterpret_cast<float*>(y) : nullptr;
+  P.row_map = grp ? grp->row_map : nullptr;
+  P.f_tiles = (L->O + BM - 1) / BM;
+  // token-tile width: wide tiles when there are many tokens per weight tile, narrow ones otherwise
+  int per = grp ? (rows + L->E - 1) / L->E : rows;  // expected tokens per weight tile
+  if (grp && grp->bn_hint > 0) per = grp->bn_hint;
+  int BN = per >= 256 ? 256 : ((per + 15) / 16) * 16;
+  if (BN < 16) BN = 16;
+  P.BN = BN;
+  P.NT = (int)kTmemCols / BN;
+  if (grp == nullptr) P.NT = std::min(P.NT, (rows + BN - 1) / BN);
+  if (P.NT > 8) P.NT = 8;
+  P.stage_bytes = kWTileBytes + (uint32_t)P.NT * BN * 128u;
+  P.stages = (int)std::min<size_t>(kMaxStages, (200 * 1024) / P.stage_bytes);
+  if (P.stages < 2) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: stage does not fit twice into shared memory");
+  // One CTA per SM is part of the kernel's contract (it takes all of tensor memory): pad the
+  // launch's shared memory above half of the SM's.
+  size_t smem = 1024 + (size_t)P.stages * P.stage_bytes;
+  if (smem < 120 * 1024) smem = 120 * 1024;
+  CUtensorMap map;
+  {
+    const cuuint64_t gdim[2] = {(cuuint64_t)L->K, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)L->K * 2};
+    const cuuint32_t box[2] = {BK, (cuuint32_t)BN};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16_t*>(x), gdim, gstride, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) ORN_FAIL(ctx, ORN_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed with " + std::to_string((int)r));
+  }
+  int grid;
+  if (grp == nullptr) {
+    P.items = nullptr; P.n_items = nullptr;
+    const int groups = (rows + P.NT * BN - 1) / (P.NT * BN);
+    P.dense_items = P.f_tiles * groups;
+    grid = std::min(P.dense_items, ctx->sm_count);
+  } else {
+    if (L->E > 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: more than 1024 experts");
+    if (scratch == nullptr) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: the grouped form needs scratch");
+    int* n_items = reinterpret_cast<int*>(scratch);
+    int4* items = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(scratch) + 256);
+    const int max_items = (int)((qgemm_scratch_bytes(rows, L->E, L->O) - 256) / sizeof(int4));
+    int threads = 32;
+    while (threads < L->E) threads <<= 1;
+    k_plan_items<<<1, threads, 0, s>>>(grp->seg, L->E, P.NT * BN, P.f_tiles, items, n_items, max_items);
+    int rc = orn_launch_check(ctx, "k_plan_items");
+    if (rc != ORN_OK) return rc;
+    P.items = items; P.n_items = n_items; P.dense_items = 0;
+    grid = ctx->sm_count;
+  }
+  switch (L->kind) {
+    case ORN_Q4K: return launch_qgemm<ORN_Q4K>(ctx, s, map, P, grid, smem);
+    case ORN_Q6K: return launch_qgemm<ORN_Q6K>(ctx, s, map, P, grid, smem);
+    case ORN_A8: return launch_qgemm<ORN_A8>(ctx, s, map, P, grid, smem);
+    case ORN_BF16: return launch_qgemm<ORN_BF16>(ctx, s, map, P, grid, smem);
+  }
+  ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: unknown weight format");
+}
+
+// rows sorted by expert: seg[E+1] and perm[rows] (sorted position -> original row)
+int f_route_sort(orn_ctx* ctx, cudaStream_t s, const uint32_t* rhs, int rows, int E, int* seg, int* cursor, uint32_t* perm) {
+  if (E > 4096) ORN_FAIL(ctx, ORN_ERR_ARG, "route sort: more than 4096 experts");
+  k_route_count<<<1, 1024, E * sizeof(int), s>>>(rhs, rows, E, seg, cursor);
+  int rc = orn_launch_check(ctx, "k_route_count");
+  if (rc != ORN_OK) return rc;
+  k_route_place<<<(E + 7) / 8, 256, 0, s>>>(rhs, rows, E, seg, perm);
+  return orn_launch_check(ctx, "k_route_place");
+}
+
+int f_gather_rows(orn_ctx* ctx, cudaStream_t s, const bf16_t* x, const uint32_t* lhs, const uint32_t* perm, int rows, int K,
+                  bf16_t* xs) {
+  if (K % 8) ORN_FAIL(ctx, ORN_ERR_ARG, "gather rows: K must be a multiple of 8");
+  k_gather_rows<<<rows, 128, 0, s>>>(x, lhs, perm, rows, K, xs);
+  return orn_launch_check(ctx, "k_gather_rows");
+}
