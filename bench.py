@@ -470,7 +470,7 @@ def ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_pkg()
     ctx = pkg.Context(local)
-    cfg = pkg.qwen35_config(max_ctx=512, n_layers=args.n_layers)
+    cfg = pkg.qwen35_config(max_ctx=max(512, PROMPT_LEN + GEN_TOKENS + 64), n_layers=args.n_layers)
     model = pkg.TextModel(ctx, cfg)
     model.init_random(SEED)
     cache = model.make_cache()

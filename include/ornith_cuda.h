@@ -272,6 +272,13 @@ int32_t orn_cache_offset(const orn_cache* c);
 /* TextModel::forward_hidden: T <= 4 rows per call; dev_normed [T,H] */
 int32_t orn_forward(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_t T,
                     uint16_t* dev_normed, uint16_t* dev_pre_norm /*nullable*/);
+/* generate::prefill (src/generate.rs:90-136) over all n tokens: chunks of prefill_step rows
+ * (the reference's default is 2048).  A chunk of 16 rows or more runs every projection as one wide
+ * product on the tensor cores (orn_gemm / orn_gather_gemm), experts grouped by a counting sort;
+ * shorter chunks run as row-invariant windows of up to 4 rows.  The caches advance by n.
+ * dev_normed (nullable) receives the n hidden rows after the final norm, [n, hidden]. */
+int32_t orn_prefill(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_t n,
+                    int32_t prefill_step, uint16_t* dev_normed /*nullable*/);
 /* forward_capture + TrunkCapture::rewind(keep) (qwen3_5.rs:190-229,324-348) */
 int32_t orn_forward_capture(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_t T,
                             uint16_t* dev_normed);

@@ -312,6 +312,15 @@ class TextModel:
         self.ctx.check(rc, "orn_forward")
         return out
 
+    def prefill(self, cache, ids, prefill_step=2048, want_hidden=False):
+        """generate::prefill over all ids; chunks of 16 rows or more run on the tensor cores.
+        want_hidden: returns the post-norm hidden rows [n, hidden] (device)."""
+        ids = np.ascontiguousarray(ids, np.uint32)
+        out = self.ctx.empty((len(ids), self.cfg.hidden), np.uint16) if want_hidden else None
+        self.ctx.check(self.ctx._lib.orn_prefill(self.h, cache.h, ids.ctypes.data, len(ids), prefill_step, _p(out)),
+                       "orn_prefill")
+        return out
+
     def head_greedy(self, hidden, T, want_logits=False):
         toks = np.zeros(T, np.uint32)
         logits = self.ctx.empty((T, self.cfg.vocab), np.uint16) if want_logits else None

@@ -117,6 +117,7 @@ SIGNATURES = {
     "orn_cache_offset": (i32, [vp]),
     "orn_forward": (i32, [vp, vp, vp, i32, vp, vp]),
     "orn_forward_capture": (i32, [vp, vp, vp, i32, vp]),
+    "orn_prefill": (i32, [vp, vp, vp, i32, i32, vp]),
     "orn_cache_rewind": (i32, [vp, i32]),
     "orn_head_greedy": (i32, [vp, vp, i32, vp, vp]),
     "orn_generate_step": (i32, [vp, vp, vp, i32, i32, i32, TOKEN_CB, vp]),

@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <cstring>
 #include <memory>
+#include <type_traits>
 
 #include "fused.h"
 #include "orn_internal.h"
@@ -65,6 +66,22 @@ struct Workspace {
   float* greedy_scratch;
   uint32_t *ids, *window, *targets, *local, *mailbox;
   bf16_t *vh, *hrow, *dh, *memb, *me, *mh, *mjoined, *mx;
+};
+
+// activation scratch of the prompt path: one chunk of up to `cap` rows through the layers
+struct WideWs {
+  int cap = 0;
+  std::vector<void*> allocs;
+  uint32_t *ids = nullptr, *lhs = nullptr, *perm = nullptr, *inds = nullptr;
+  uint32_t *ident = nullptr, *sorted_e = nullptr, *perm_inv = nullptr;  // ORN_WIDE_EXACT only
+  int* seg = nullptr;
+  void* gemm_scratch = nullptr;
+  bf16_t *x, *n, *r, *h, *n2, *mo;
+  bf16_t *cb, *z, *a, *b, *gq, *gk, *gv, *beta, *gy, *gated;
+  float* gg;
+  bf16_t *qg, *aq, *agate, *ak, *av, *att, *agated;
+  bf16_t *gates, *probs, *scores, *sg, *su, *sact, *sy, *gs;
+  bf16_t *xs, *eg, *eu, *eact, *ey;
 };
 
 __global__ void iota_div_kernel(uint32_t* lhs, uint32_t* ident, int n, int k) {
@@ -128,6 +145,7 @@ struct orn_model {
   orn_prof prof{};
   cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
   float lnb = 0.f;  // ln(theta) / (rope_dims/2)
+  WideWs wide{};    // prompt-chunk scratch, allocated on first use
 };
 
 struct orn_cache {
@@ -736,20 +754,230 @@ int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar, 2 prefill row
   return ORN_OK;
 }
 
+// ------------------------------------------------------------------ prompt chunks on the tensor cores
+bool use_wide_prefill() {
+  // ORN_NO_WIDE_PREFILL=1 sends every prompt through the row-invariant 4-row windows
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ORN_NO_WIDE_PREFILL");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+// ORN_WIDE_EXACT=1 keeps the chunked prompt path but computes every product with the row-invariant
+// mat-vec kernels (groups of four rows; routed rows one by one): the chunk plumbing (conv windows,
+// KV append, causal attention over the chunk, the T-step recurrence, the expert sort) then has to
+// reproduce the 4-row windows bit for bit, which is how the tests check it
+bool wide_exact() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ORN_WIDE_EXACT");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+// y[T, O] = x[T, K] W^T for a prompt chunk
+int wide_mm(orn_model* m, const orn_linear* L, const bf16_t* x, int T, bf16_t* y) {
+  orn_ctx* ctx = m->ctx;
+  if (!wide_exact()) return f_qgemm(ctx, ctx->stream, L, x, T, y, L->O, nullptr, nullptr);
+  for (int r = 0; r < T; r += kMaxRows) {
+    const int n = std::min(kMaxRows, T - r);
+    CK(k_gemv(ctx, ctx->stream, L, x + (size_t)r * L->K, n, y + (size_t)r * L->O, 0));
+  }
+  return ORN_OK;
+}
+constexpr int kWideMinRows = 16;    // below this the mat-vec windows win (kquant.rs MM_ROW_LIMIT)
+constexpr int kWideMaxRows = 2048;  // the reference's prefill chunk (generate.rs:25)
+
+int wide_reserve(orn_model* m, int rows) {
+  WideWs& w = m->wide;
+  if (w.cap >= rows) return ORN_OK;
+  for (void* p : w.allocs) cudaFree(p);
+  w.allocs.clear();
+  w.cap = 0;
+  const orn_config& c = m->cfg;
+  const size_t R = rows, H = c.hidden, D = conv_dim(c), VD = (size_t)c.gdn_v_heads * c.gdn_head_dim;
+  const size_t KD = (size_t)c.gdn_k_heads * c.gdn_head_dim, QD = (size_t)c.n_heads * c.head_dim;
+  const size_t KVD = (size_t)c.n_kv_heads * c.head_dim, E = c.n_experts, I = c.expert_inter, SI = c.shared_inter, k = c.top_k;
+  const size_t S = c.gdn_conv_kernel - 1;
+  int rc = ORN_OK;
+  auto A = [&](auto** p, size_t n) {
+    if (rc != ORN_OK) return;
+    void* d = nullptr;
+    rc = orn_alloc(m->ctx, sizeof(**p) * (n ? n : 1), &d);
+    if (rc == ORN_OK) { w.allocs.push_back(d); *p = (std::remove_reference_t<decltype(**p)>*)d; }
+  };
+  A(&w.ids, R); A(&w.lhs, R * k); A(&w.perm, R * k); A(&w.inds, R * k); A(&w.seg, 2 * E + 4);
+  A(&w.ident, R * k); A(&w.sorted_e, R * k); A(&w.perm_inv, R * k);
+  A(&w.x, R * H); A(&w.n, R * H); A(&w.r, R * H); A(&w.h, R * H); A(&w.n2, R * H); A(&w.mo, R * H);
+  A(&w.cb, (S + R) * D); A(&w.z, R * VD); A(&w.a, R * c.gdn_v_heads); A(&w.b, R * c.gdn_v_heads);
+  A(&w.gq, R * KD); A(&w.gk, R * KD); A(&w.gv, R * VD); A(&w.beta, R * c.gdn_v_heads); A(&w.gg, R * c.gdn_v_heads);
+  A(&w.gy, R * VD); A(&w.gated, R * VD);
+  A(&w.qg, R * 2 * QD); A(&w.aq, R * QD); A(&w.agate, R * QD); A(&w.ak, R * KVD); A(&w.av, R * KVD);
+  A(&w.att, R * QD); A(&w.agated, R * QD);
+  A(&w.gates, R * E); A(&w.probs, R * E); A(&w.scores, R * k); A(&w.sg, R * SI); A(&w.su, R * SI); A(&w.sact, R * SI);
+  A(&w.sy, R * H); A(&w.gs, R);
+  A(&w.xs, R * k * H); A(&w.eg, R * k * I); A(&w.eu, R * k * I); A(&w.eact, R * k * I); A(&w.ey, R * k * H);
+  if (rc == ORN_OK) {
+    const size_t big = std::max(qgemm_scratch_bytes((int)(R * k), (int)E, (int)H), qgemm_scratch_bytes((int)(R * k), (int)E, (int)I));
+    rc = orn_alloc(m->ctx, big, &w.gemm_scratch);
+    if (rc == ORN_OK) w.allocs.push_back(w.gemm_scratch);
+  }
+  if (rc != ORN_OK) {
+    for (void* p : w.allocs) cudaFree(p);
+    w.allocs.clear();
+    return rc;
+  }
+  const int n = rows * c.top_k;
+  iota_div_kernel<<<(n + 255) / 256, 256, 0, m->ctx->stream>>>(w.lhs, w.ident, n, c.top_k);
+  CK(orn_launch_check(m->ctx, "iota_div"));
+  w.cap = rows;
+  return ORN_OK;
+}
+
+// sorted_e[p] = expert of sorted row p; perm_inv[original row] = its sorted position
+__global__ void perm_tables_kernel(const uint32_t* perm, const uint32_t* inds, int rows, uint32_t* sorted_e, uint32_t* perm_inv) {
+  int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p < rows) {
+    const uint32_t o = perm[p];
+    sorted_e[p] = inds[o];
+    perm_inv[o] = (uint32_t)p;
+  }
+}
+__global__ void copy_u4_kernel(const uint4* src, uint4* dst, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[i];
+}
+
+// sparse_moe_block on a chunk (moe.rs:662-741 with the sorted expert path of :283-314,463-508):
+// rows are counting-sorted by expert, an expert's matrices are read once for all its rows
+int moe_block_wide(orn_model* m, const Moe& moe, const bf16_t* x, int T, bf16_t* out) {
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  WideWs& w = m->wide;
+  const orn_config& c = m->cfg;
+  const int rows = T * c.top_k, H = c.hidden, I = c.expert_inter, SI = c.shared_inter, E = c.n_experts;
+  CK(wide_mm(m, moe.gate, x, T, w.gates));
+  CK(wide_mm(m, moe.sh_gate, x, T, w.sg));
+  CK(wide_mm(m, moe.sh_up, x, T, w.su));
+  CK(wide_mm(m, moe.sh_egate, x, T, w.gs));
+  CK(k_softmax_precise(ctx, s, w.gates, T, E, w.probs));
+  CK(k_swiglu(ctx, s, w.sg, w.su, T * SI, w.sact));
+  CK(k_router_topk(ctx, s, w.probs, T, E, c.top_k, w.inds, w.scores));
+  CK(wide_mm(m, moe.sh_down, w.sact, T, w.sy));
+  CK(f_route_sort(ctx, s, w.inds, rows, E, w.seg, w.seg + E + 1, w.perm));
+  CK(f_gather_rows(ctx, s, x, w.lhs, w.perm, rows, H, w.xs));
+  if (wide_exact()) {
+    perm_tables_kernel<<<(rows + 255) / 256, 256, 0, s>>>(w.perm, w.inds, rows, w.sorted_e, w.perm_inv);
+    CK(orn_launch_check(ctx, "perm_tables"));
+  }
+  if (wide_exact()) {
+    // the routed rows through the row-invariant gather mat-vec, in sorted order like the products below
+    CK(k_gather_gemv(ctx, s, moe.sw_gate, w.xs, w.ident, w.sorted_e, rows, w.eg));
+    CK(k_gather_gemv(ctx, s, moe.sw_up, w.xs, w.ident, w.sorted_e, rows, w.eu));
+    CK(k_swiglu(ctx, s, w.eg, w.eu, rows * I, w.eact));
+    CK(k_gather_gemv(ctx, s, moe.sw_down, w.eact, w.perm_inv, w.inds, rows, w.ey));
+  } else {
+    QGemmGroup sorted{w.seg, nullptr, 0}, back{w.seg, w.perm, 0};
+    CK(f_qgemm(ctx, s, moe.sw_gate, w.xs, rows, w.eg, I, &sorted, w.gemm_scratch));
+    CK(f_qgemm(ctx, s, moe.sw_up, w.xs, rows, w.eu, I, &sorted, w.gemm_scratch));
+    CK(k_swiglu(ctx, s, w.eg, w.eu, rows * I, w.eact));
+    CK(f_qgemm(ctx, s, moe.sw_down, w.eact, rows, w.ey, H, &back, w.gemm_scratch));  // rows back in (token, slot) order
+  }
+  CK(k_moe_combine(ctx, s, w.scores, w.ey, w.gs, w.sy, T, c.top_k, H, c.norm_topk_prob, out));
+  return ORN_OK;
+}
+
+// One prompt chunk of T rows (ids on the device in wide.ids) through the trunk: the layer
+// sequence of TextModel::forward_hidden (qwen3_5.rs:578-695) with every projection as one wide
+// product.  Only the caches matter (generate::prefill discards the hidden rows, generate.rs:90-136).
+int prefill_wide(orn_model* m, orn_cache* cc, int T, bf16_t* normed_out /*nullable: [T, H] rows after the final norm*/) {
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  WideWs& w = m->wide;
+  const orn_config& c = m->cfg;
+  const int H = c.hidden, S = c.gdn_conv_kernel - 1, D = conv_dim(c);
+  const int VD = c.gdn_v_heads * c.gdn_head_dim, QD = c.n_heads * c.head_dim, KVD = c.n_kv_heads * c.head_dim;
+  const int Hq = c.n_heads, Hkv = c.n_kv_heads, hd = c.head_dim;
+  if (cc->h_pos + T > c.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "forward: context exceeds max_ctx");
+  CK(k_embedding(ctx, s, m->embed, w.ids, T, w.x));
+  CK(k_rms_norm(ctx, s, w.x, m->layers[0].input_ln, T, H, c.rms_eps, w.n));
+  for (int i = 0; i < c.n_layers; ++i) {
+    const Layer& ly = m->layers[i];
+    if (ly.linear) {
+      // conv window of the chunk: the cached rows, then this chunk's qkv rows (written by the product)
+      const size_t n16 = (size_t)S * D / 8;
+      copy_u4_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, s>>>(reinterpret_cast<const uint4*>(cc->conv[i]),
+                                                                 reinterpret_cast<uint4*>(w.cb), n16);
+      CK(orn_launch_check(ctx, "copy_u4"));
+      bf16_t* qkv = w.cb + (size_t)S * D;
+      CK(wide_mm(m, ly.in_qkv, w.n, T, qkv));
+      CK(wide_mm(m, ly.in_z, w.n, T, w.z));
+      CK(wide_mm(m, ly.in_b, w.n, T, w.b));
+      CK(wide_mm(m, ly.in_a, w.n, T, w.a));
+      CK(k_gdn_front(ctx, s, w.cb, qkv, ly.conv_w, w.a, w.b, ly.a_log, ly.dt_bias, T, c.gdn_k_heads, c.gdn_v_heads,
+                     c.gdn_head_dim, c.gdn_conv_kernel, 1e-6f, cc->conv[i], w.gq, w.gk, w.gv, w.beta, w.gg, nullptr));
+      CK(k_gated_delta_ring(ctx, s, w.gq, w.gk, w.gv, w.gg, w.beta, cc->ring[i], kRing, cc->cur, 1, T, c.gdn_k_heads,
+                            c.gdn_v_heads, w.gy));
+      CK(k_rms_norm_gated(ctx, s, w.gy, ly.gdn_norm, w.z, T * c.gdn_v_heads, c.gdn_head_dim, c.rms_eps, w.gated));
+      CK(wide_mm(m, ly.out_proj, w.gated, T, w.r));
+    } else {
+      CK(wide_mm(m, ly.q_proj, w.n, T, w.qg));
+      CK(wide_mm(m, ly.k_proj, w.n, T, w.ak));
+      CK(wide_mm(m, ly.v_proj, w.n, T, w.av));
+      CK(k_split_qgate(ctx, s, w.qg, T, Hq, hd, w.aq, w.agate));
+      CK(k_rms_norm(ctx, s, w.aq, ly.q_norm, T * Hq, hd, c.rms_eps, w.aq));
+      CK(k_rms_norm(ctx, s, w.ak, ly.k_norm, T * Hkv, hd, c.rms_eps, w.ak));
+      CK(k_rope(ctx, s, w.aq, T, Hq, hd, c.rope_dims, m->lnb, cc->pos, 0));
+      CK(k_rope(ctx, s, w.ak, T, Hkv, hd, c.rope_dims, m->lnb, cc->pos, 0));
+      CK(k_kv_append(ctx, s, w.ak, w.av, T, Hkv, hd, c.max_ctx, cc->pos, 0, cc->kc[i], cc->vc[i]));
+      CK(k_sdpa_decode(ctx, s, w.aq, cc->kc[i], cc->vc[i], T, Hq, Hkv, hd, c.max_ctx, cc->pos, 0, 1.0f / sqrtf((float)hd),
+                       w.att));
+      CK(k_sigmoid_gate(ctx, s, w.agate, w.att, T * Hq * hd, 1, w.agated));
+      CK(wide_mm(m, ly.o_proj, w.agated, T, w.r));
+    }
+    CK(k_add_rms_norm(ctx, s, w.x, w.r, ly.post_ln, T, H, c.rms_eps, w.h, w.n2));
+    CK(moe_block_wide(m, ly.moe, w.n2, T, w.mo));
+    if (i + 1 < c.n_layers) CK(k_add_rms_norm(ctx, s, w.h, w.mo, m->layers[i + 1].input_ln, T, H, c.rms_eps, w.x, w.n));
+  }
+  if (normed_out != nullptr) CK(k_add_rms_norm(ctx, s, w.h, w.mo, m->norm, T, H, c.rms_eps, w.x, normed_out));
+  // bookkeeping of a call that keeps only its final state: the conv windows were written in place
+  add_int_kernel<<<1, 1, 0, s>>>(cc->pos, T);
+  CK(orn_launch_check(ctx, "add_int"));
+  add_int_kernel<<<1, 1, 0, s>>>(cc->cur, 1);
+  CK(orn_launch_check(ctx, "add_int"));
+  cc->h_pos += T;
+  cc->h_cur += 1;
+  return ORN_OK;
+}
+
 // generate::prefill (src/generate.rs:90-136): everything but the last prompt
 // token.  Rows are computed with one-row arithmetic, so the chunk width (the
 // reference's prefill_step) cannot change the result; chunks are cut to the
 // widest window a forward call takes.
-int prefill(orn_model* m, orn_cache* cc, const uint32_t* prompt, int n, int prefill_step, int* done_out) {
+int prefill(orn_model* m, orn_cache* cc, const uint32_t* prompt, int n, int prefill_step, int* done_out,
+            bf16_t* normed_out = nullptr, int keep_last = 1) {
   int done = 0;
   int step = prefill_step < 1 ? 1 : prefill_step;
-  while (n - done > 1) {
-    int chunk = std::min(step, n - done - 1);
+  while (n - done > keep_last) {
+    int chunk = std::min(step, n - done - keep_last);
     int off = 0;
+    if (chunk >= kWideMinRows && use_wide_prefill() && use_fused()) {
+      // a chunk wide enough for the tensor cores (the reference's tile path, kquant.rs:783-812)
+      chunk = std::min(chunk, kWideMaxRows);
+      CK(wide_reserve(m, chunk));
+      ORN_CHECK_CUDA(m->ctx, cudaMemcpyAsync(m->wide.ids, prompt + done, sizeof(uint32_t) * (size_t)chunk,
+                                             cudaMemcpyHostToDevice, m->ctx->stream));
+      CK(prefill_wide(m, cc, chunk, normed_out ? normed_out + (size_t)done * m->cfg.hidden : nullptr));
+      off = chunk;
+    }
     while (off < chunk) {
       int t = std::min(kMaxRows, chunk - off);
       CK(upload_ids(m, prompt + done + off, t));
-      CK(run_step(m, cc, 2, t - 1, false));  // the same rows as forward_dev, replayed as a graph
+      if (normed_out != nullptr)
+        CK(forward_dev(m, cc, m->ws.ids, t, false, normed_out + (size_t)(done + off) * m->cfg.hidden, nullptr));
+      else
+        CK(run_step(m, cc, 2, t - 1, false));  // the same rows as forward_dev, replayed as a graph
       off += t;
     }
     CK(orn_sync(m->ctx));  // the reference drains the queue after each chunk (generate.rs:128-131)
@@ -792,6 +1020,7 @@ int32_t orn_model_destroy(orn_model* m) {
   for (auto& kv : m->lins) orn_linear_destroy(m->ctx, kv.second);
   for (auto& kv : m->tensors) cudaFree(kv.second.p);
   for (void* p : m->ws_allocs) cudaFree(p);
+  for (void* p : m->wide.allocs) cudaFree(p);
   if (m->fr_head) orn_linear_destroy(m->ctx, m->fr_head);
   cudaFree(m->fr_ids);
   for (int i = 0; i < 4; ++i)
@@ -1073,6 +1302,15 @@ int32_t orn_forward_capture(orn_model* m, orn_cache* c, const uint32_t* host_ids
   if (T < 1 || T > kMaxRows) ORN_FAIL(m->ctx, ORN_ERR_ARG, "forward_capture: 1..4 rows per call");
   CK(upload_ids(m, host_ids, T));
   return forward_dev(m, c, m->ws.ids, T, true, dev_normed, nullptr);
+}
+
+int32_t orn_prefill(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_t n, int32_t prefill_step,
+                    uint16_t* dev_normed) {
+  if (!m || !c || !host_ids || n < 1) return ORN_ERR_ARG;
+  CK(finalize(m));
+  int done = 0;
+  CK(prefill(m, c, host_ids, n, prefill_step, &done, dev_normed, 0));
+  return orn_sync(m->ctx);
 }
 
 int32_t orn_cache_rewind(orn_cache* c, int32_t keep) {

@@ -43,6 +43,11 @@ def main():
     c.reset()
     h = [gm.forward(c, prompt[a:b]).numpy() for a, b in [(0, 1), (1, 3), (3, 7)]]
     out["tiny_hidden_sha"] = sha(np.concatenate(h))
+    # a 45-token prompt through orn_prefill (one chunk; which arithmetic it uses is the parent's choice)
+    c.reset()
+    long_ids = np.random.default_rng(4).integers(0, cfg.vocab, 45).astype(np.uint32)
+    out["tiny_prefill_sha"] = sha(gm.prefill(c, long_ids, prefill_step=2048, want_hidden=True).numpy())
+    out["tiny_after_prefill"] = sha(gm.forward(c, prompt[:2]).numpy())   # the caches it left behind
     c.free()
     gm.free()
     # full-width layers, random-init on the device
@@ -71,6 +76,10 @@ def main():
     ctx.check(ctx._lib.orn_moe_block(ctx.h, *[l.h for l in L], ctx.upload(x).ptr, 2, cfg.top_k, 1, y.ptr, inds.ptr),
               "moe_block")
     out["moe_sha"] = sha(y.numpy()) + sha(inds.numpy())
+    c.reset()
+    long_ids = rng.integers(0, cfg.vocab, 70).astype(np.uint32)
+    out["full_prefill_sha"] = sha(gm.prefill(c, long_ids, prefill_step=2048, want_hidden=True).numpy())
+    out["full_after_prefill"] = sha(gm.forward(c, prompt[:3]).numpy())
     c.free()
     gm.free()
     ctx.close()

@@ -111,7 +111,8 @@ def test_config2_moe_layer_256_experts_fused(pkg, ctx, T):
 
 def _run_worker(env_over):
     env = dict(os.environ)
-    for k in ("ORN_UNFUSED", "ORN_NO_GRAPH", "ORN_NO_PDL", "ORN_PDL_MASK", "ORN_KTIME"):
+    for k in ("ORN_UNFUSED", "ORN_NO_GRAPH", "ORN_NO_PDL", "ORN_PDL_MASK", "ORN_KTIME", "ORN_WIDE_EXACT",
+              "ORN_NO_WIDE_PREFILL"):
         env.pop(k, None)
     env.update(env_over)
     r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "env_worker.py")], env=env, capture_output=True,
@@ -134,6 +135,21 @@ def test_control_paths_give_identical_bits():
             assert got[key] == base[key], (over, key)
     unfused = _run_worker({"ORN_UNFUSED": "1"})
     assert unfused["launches"] > 3 * base["launches"]  # really another path: one launch per op
+
+
+def test_chunked_prompt_path_is_exact_with_exact_products():
+    """The chunked prompt path (conv window of the chunk, KV append of T rows, causal attention
+    over the chunk, the T-step recurrence, experts sorted by a counting sort and rows scattered
+    back) with its products computed by the row-invariant mat-vecs (ORN_WIDE_EXACT=1) reproduces
+    the 4-row windows (ORN_NO_WIDE_PREFILL=1) bit for bit: hidden rows of the prompt and the hidden
+    rows of a window decoded on top of the caches it left.  With the tensor-core products the same
+    path differs from it by rounding only (tests/test_gpu_prefill.py)."""
+    narrow = _run_worker({"ORN_NO_WIDE_PREFILL": "1"})
+    exact = _run_worker({"ORN_WIDE_EXACT": "1"})
+    for key in ("tiny_prefill_sha", "tiny_after_prefill", "full_prefill_sha", "full_after_prefill"):
+        assert exact[key] == narrow[key], key
+    tensor = _run_worker({})
+    assert tensor["tiny_prefill_sha"] != narrow["tiny_prefill_sha"]   # really another arithmetic
 
 
 def test_bounded_wait_gives_up_and_the_context_survives(pkg, ctx):
