@@ -43,6 +43,9 @@ extern "C" {
 #define ORN_Q6K 1  /* ggml Q6_K, three tensors: ql|qh / scales / d     */
 #define ORN_A8 2   /* mlx affine, 8 bits, group 64: codes/scales/biases */
 #define ORN_BF16 3 /* dense bfloat16                                    */
+#define ORN_A4 4   /* mlx affine, 4 bits, group 32 (src/ops/quantized.rs:249-278, QuantMode::Affine;
+                      the shared-expert modules of the published q6k-full artifact,
+                      tools/forge_q4k.py:131-152): codes/scales/biases       */
 
 typedef struct orn_ctx orn_ctx;
 typedef struct orn_linear orn_linear;
@@ -109,9 +112,13 @@ int32_t orn_timer_stop(orn_ctx* ctx, float* ms_out); /* synchronises */
  *   Q6_K: w = ql|qh bytes [E,O,K/256*192], s = i8 [E,O,K/256,16], b = d f16 [E,O,K/256]
  *   A8  : w = codes u8 [E,O,K], s = scales bf16 [E,O,K/64], b = biases bf16 [E,O,K/64]
  *   BF16: w = bf16 [E,O,K]
+ *   A4  : w = codes, 8 per u32, lowest nibble first [E,O,K/8 words], s = scales bf16 [E,O,K/32],
+ *         b = biases bf16 [E,O,K/32]
  * The library copies them into its own HBM layout (16-byte-aligned streams).
  * Shape rules follow KMatrix::new: K % 256 == 0 for k-quants, K % 64 == 0 for
- * A8, K % 8 == 0 for BF16; violations return ORN_ERR_ARG. */
+ * A8, K % 32 == 0 for A4, K % 8 == 0 for BF16; violations return ORN_ERR_ARG.
+ * A4 matrices run through the per-op kernels and the wide product; a model that holds one outside
+ * its MoE blocks runs unfused, a MoE block that holds one runs its block unfused. */
 int32_t orn_linear_create(orn_ctx* ctx, int32_t kind, int32_t E, int32_t O, int32_t K,
                           const void* host_w, const void* host_s, const void* host_b,
                           orn_linear** out);
@@ -273,7 +280,7 @@ int32_t orn_cache_offset(const orn_cache* c);
 int32_t orn_forward(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_t T,
                     uint16_t* dev_normed, uint16_t* dev_pre_norm /*nullable*/);
 /* generate::prefill (src/generate.rs:90-136) over all n tokens: chunks of prefill_step rows
- * (the reference's default is 2048).  A chunk of 16 rows or more runs every projection as one wide
+ * (the reference's default is 2048).  A chunk of 64 rows or more runs every projection as one wide
  * product on the tensor cores (orn_gemm / orn_gather_gemm), experts grouped by a counting sort;
  * shorter chunks run as row-invariant windows of up to 4 rows.  The caches advance by n.
  * dev_normed (nullable) receives the n hidden rows after the final norm, [n, hidden]. */

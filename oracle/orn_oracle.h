@@ -9,7 +9,7 @@
 extern "C" {
 #endif
 
-enum { ORC_Q4K = 0, ORC_Q6K = 1, ORC_A8 = 2, ORC_BF16 = 3 };
+enum { ORC_Q4K = 0, ORC_Q6K = 1, ORC_A8 = 2, ORC_BF16 = 3, ORC_A4 = 4 };
 
 /* One (optionally expert-stacked) weight matrix [E, O, K] in host memory, in
  * the reference's artifact layout (src/ops/kquant.rs:13-29, weights.rs:132-227):

@@ -12,7 +12,7 @@ import numpy as np
 ORACLE_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(ORACLE_DIR, "liborn_oracle.so")
 
-Q4K, Q6K, A8, BF16 = 0, 1, 2, 3
+Q4K, Q6K, A8, BF16, A4 = 0, 1, 2, 3, 4
 
 
 class Lin(C.Structure):

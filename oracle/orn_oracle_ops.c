@@ -174,6 +174,26 @@ static float a8_unit(const uint8_t* w_row, const bf16* s_row, const bf16* b_row,
   return acc;
 }
 
+/* mlx quantized.h:756-822 (affine_qmv_fast) restated for 4 bits, group 32 (the mode of
+ * src/ops/quantized.rs:249-278 for the artifact's default modules): a unit is one group,
+ * byte b of its 16 code bytes holds weights 2b (low nibble) and 2b+1 (high nibble);
+ * y += scale * sum(x q) + bias * sum(x) */
+static float a4_unit(const uint8_t* w_row, const bf16* s_row, const bf16* b_row, int u,
+                     const float* x, float acc) {
+  const uint8_t* q = w_row + 16 * u;
+  const float* xx = x + 32 * u;
+  float p[2] = {0.f, 0.f}, s2 = 0.f; /* products: even and odd chains, added at the end */
+  for (int i = 0; i < 32; ++i) {
+    const float code = (float)((i & 1) ? (q[i >> 1] >> 4) : (q[i >> 1] & 0xF));
+    p[i & 1] = fmaf(xx[i], code, p[i & 1]);
+    s2 = s2 + xx[i];
+  }
+  const float s1 = p[0] + p[1];
+  acc = fmaf(o_bf2f(s_row[u]), s1, acc);
+  acc = fmaf(o_bf2f(b_row[u]), s2, acc);
+  return acc;
+}
+
 /* mlx gemv.h (bf16 weights, float accumulate) via src/ops/matmul.rs:334-437 */
 static float bf_unit(const bf16* w_row, int u, const float* x, float acc) {
   float p[2] = {0.f, 0.f}; /* the unit's products: even and odd chains; their sum joins the lane's total */
@@ -206,6 +226,12 @@ float orc_row_dot(const orc_lin* L, int e, int o, const float* x) {
       const bf16* s = (const bf16*)L->s + row * (K / 64);
       const bf16* b = (const bf16*)L->b + row * (K / 64);
       for (int u = 0; u < K / 16; ++u) lanes[u & 31] = a8_unit(q, s, b, u, x, lanes[u & 31]);
+    } break;
+    case ORC_A4: {
+      const uint8_t* q = (const uint8_t*)L->w + row * (K / 2);
+      const bf16* s = (const bf16*)L->s + row * (K / 32);
+      const bf16* b = (const bf16*)L->b + row * (K / 32);
+      for (int u = 0; u < K / 32; ++u) lanes[u & 31] = a4_unit(q, s, b, u, x, lanes[u & 31]);
     } break;
     default: {
       const bf16* w = (const bf16*)L->w + row * K;

@@ -16,11 +16,11 @@ import ctypes as C
 import numpy as np
 
 from . import _ffi
-from ._ffi import A8, BF16, POLICY_COMMITTED, POLICY_CYCLE, Q4K, Q6K, Config, ForceDraft, MtpStats, Prof
+from ._ffi import A4, A8, BF16, POLICY_COMMITTED, POLICY_CYCLE, Q4K, Q6K, Config, ForceDraft, MtpStats, Prof
 
 __all__ = [
     "Context", "DevBuf", "Linear", "TextModel", "Cache", "Config", "MtpStats", "OrnError",
-    "Q4K", "Q6K", "A8", "BF16", "POLICY_CYCLE", "POLICY_COMMITTED", "generate_step",
+    "Q4K", "Q6K", "A8", "BF16", "A4", "POLICY_CYCLE", "POLICY_COMMITTED", "generate_step",
     "generate_step_mtp", "qwen35_config", "lib",
 ]
 
@@ -313,7 +313,7 @@ class TextModel:
         return out
 
     def prefill(self, cache, ids, prefill_step=2048, want_hidden=False):
-        """generate::prefill over all ids; chunks of 16 rows or more run on the tensor cores.
+        """generate::prefill over all ids; chunks of 64 rows or more run on the tensor cores.
         want_hidden: returns the post-norm hidden rows [n, hidden] (device)."""
         ids = np.ascontiguousarray(ids, np.uint32)
         out = self.ctx.empty((len(ids), self.cfg.hidden), np.uint16) if want_hidden else None

@@ -9,7 +9,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("ORN_CUDA_LIB") or os.path.join(_HERE, "libornith_cuda.so")  # the override serves A/B timing of builds
 
-Q4K, Q6K, A8, BF16 = 0, 1, 2, 3
+Q4K, Q6K, A8, BF16, A4 = 0, 1, 2, 3, 4
 POLICY_CYCLE, POLICY_COMMITTED = 0, 1
 
 c_void_pp = C.POINTER(C.c_void_p)

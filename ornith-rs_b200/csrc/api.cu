@@ -242,7 +242,8 @@ static int check_linear_shape(orn_ctx* ctx, int kind, int E, int O, int K) {
     ORN_FAIL(ctx, ORN_ERR_ARG, "k-quant matrix: K must be a multiple of 256");
   if (kind == ORN_A8 && K % 64 != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "affine-8 matrix: K must be a multiple of 64");
   if (kind == ORN_BF16 && K % 8 != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "bf16 matrix: K must be a multiple of 8");
-  if (kind < ORN_Q4K || kind > ORN_BF16) ORN_FAIL(ctx, ORN_ERR_ARG, "linear: unknown kind");
+  if (kind == ORN_A4 && K % 32 != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "affine-4 matrix: K must be a multiple of 32");
+  if (kind < ORN_Q4K || kind > ORN_A4) ORN_FAIL(ctx, ORN_ERR_ARG, "linear: unknown kind");
   return ORN_OK;
 }
 

@@ -180,6 +180,28 @@ ORN_D void dequant_row<ORN_A8>(const uint8_t* rec, const RecGeom& g, int kb, uin
   }
 }
 
+// affine 4-bit, group 32: a K block is two groups; byte b holds weights 2b (low nibble), 2b+1 (high)
+template <>
+ORN_D void dequant_row<ORN_A4>(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw) {
+  const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 32);
+  const uint2 sb2 = __ldg(reinterpret_cast<const uint2*>(rec + g.b0) + kb);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t sb = h ? sb2.y : sb2.x;
+    const float sc = bf_lo(sb), bi = bf_hi(sb);
+    const uint4 q = __ldg(src + h);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // one word = 8 weights = one 16-byte chunk of bfloat16
+      const uint32_t l4 = w[c] & 0x0F0F0F0Fu, h4 = (w[c] >> 4) & 0x0F0F0F0Fu;
+      st_chunk(row_addr, rsw, 4 * h + c, pack_bf2(fmaf(sc, byte_f<0>(l4), bi), fmaf(sc, byte_f<0>(h4), bi)),
+               pack_bf2(fmaf(sc, byte_f<1>(l4), bi), fmaf(sc, byte_f<1>(h4), bi)),
+               pack_bf2(fmaf(sc, byte_f<2>(l4), bi), fmaf(sc, byte_f<2>(h4), bi)),
+               pack_bf2(fmaf(sc, byte_f<3>(l4), bi), fmaf(sc, byte_f<3>(h4), bi)));
+    }
+  }
+}
+
 // Q4_K (kernels/q4k.metal:43-96): 64 weights = 32 code bytes; low nibbles are sub-block 2i, high
 // nibbles sub-block 2i+1; w = (d * sc) * q - (dmin * m)
 template <>
@@ -596,6 +618,7 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
     case ORN_Q6K: return launch_qgemm<ORN_Q6K>(ctx, s, map, P, grid, smem);
     case ORN_A8: return launch_qgemm<ORN_A8>(ctx, s, map, P, grid, smem);
     case ORN_BF16: return launch_qgemm<ORN_BF16>(ctx, s, map, P, grid, smem);
+    case ORN_A4: return launch_qgemm<ORN_A4>(ctx, s, map, P, grid, smem);
   }
   ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: unknown weight format");
 }

@@ -181,6 +181,48 @@ struct Fmt<ORN_A8> {
   }
 };
 
+// mlx affine 4-bit, group 32 (quantized.h:756-822 at bits = 4): a unit is one group, 16 code bytes;
+// byte b holds weights 2b (low nibble) and 2b+1 (high nibble)
+template <>
+struct Fmt<ORN_A4> {
+  static constexpr int kWeightsPerUnit = 32;
+  struct X { float v[32]; float sum; };
+  struct W { uint4 q; uint32_t sb; };
+  ORN_D static void load_x(const bf16_t* x, int u, X& r) {
+    const bf16_t* p = x + 32 * u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) widen8(ldg128(p + 8 * i), r.v + 8 * i);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) s = s + r.v[i];
+    r.sum = s;
+  }
+  ORN_D static void load_w(const LinDev& L, int64_t row, int u, W& w) {
+    w.q = ldg128_stream(L.w + row * L.rec + 16 * u);
+    w.sb = __ldg(reinterpret_cast<const uint32_t*>(L.s + row * L.rec) + u);
+  }
+  ORN_D static float fold(const W& w, const X& x, int, float acc) {
+    const uint32_t qw[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
+    float se = 0.f, so = 0.f;  // even (low nibbles) / odd (high nibbles) chains, added at the end
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t l4 = qw[k] & 0x0F0F0F0Fu, h4 = (qw[k] >> 4) & 0x0F0F0F0Fu;
+      se = fmaf(x.v[8 * k + 0], byte_f<0>(l4), se);
+      so = fmaf(x.v[8 * k + 1], byte_f<0>(h4), so);
+      se = fmaf(x.v[8 * k + 2], byte_f<1>(l4), se);
+      so = fmaf(x.v[8 * k + 3], byte_f<1>(h4), so);
+      se = fmaf(x.v[8 * k + 4], byte_f<2>(l4), se);
+      so = fmaf(x.v[8 * k + 5], byte_f<2>(h4), so);
+      se = fmaf(x.v[8 * k + 6], byte_f<3>(l4), se);
+      so = fmaf(x.v[8 * k + 7], byte_f<3>(h4), so);
+    }
+    const float s1 = se + so;
+    acc = fmaf(bf_lo(w.sb), s1, acc);
+    acc = fmaf(bf_hi(w.sb), x.sum, acc);
+    return acc;
+  }
+};
+
 template <>
 struct Fmt<ORN_BF16> {
   static constexpr int kWeightsPerUnit = 8;
@@ -327,6 +369,7 @@ int k_gemv(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf16_t* x, 
       case ORN_Q4K: rc = dispatch_m<ORN_Q4K>(ctx, st, L, xs, mm, ys, out_f32); break;
       case ORN_Q6K: rc = dispatch_m<ORN_Q6K>(ctx, st, L, xs, mm, ys, out_f32); break;
       case ORN_A8: rc = dispatch_m<ORN_A8>(ctx, st, L, xs, mm, ys, out_f32); break;
+      case ORN_A4: rc = dispatch_m<ORN_A4>(ctx, st, L, xs, mm, ys, out_f32); break;
       default: rc = dispatch_m<ORN_BF16>(ctx, st, L, xs, mm, ys, out_f32); break;
     }
     if (rc != ORN_OK) return rc;
@@ -341,6 +384,7 @@ int k_gather_gemv(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf16
     case ORN_Q4K: return dispatch_gemv<ORN_Q4K, 1>(ctx, st, L, x, y, 0, lhs, rhs, rows);
     case ORN_Q6K: return dispatch_gemv<ORN_Q6K, 1>(ctx, st, L, x, y, 0, lhs, rhs, rows);
     case ORN_A8: return dispatch_gemv<ORN_A8, 1>(ctx, st, L, x, y, 0, lhs, rhs, rows);
+    case ORN_A4: return dispatch_gemv<ORN_A4, 1>(ctx, st, L, x, y, 0, lhs, rhs, rows);
     default: return dispatch_gemv<ORN_BF16, 1>(ctx, st, L, x, y, 0, lhs, rhs, rows);
   }
 }
@@ -441,6 +485,7 @@ void linear_artifact_sizes(int kind, int E, int O, int K, size_t* w, size_t* s, 
     case ORN_Q4K: *w = rows * (K / 2); *s = rows * (K / 256) * 12; *b = rows * (K / 256) * 4; break;
     case ORN_Q6K: *w = rows * (K / 256) * 192; *s = rows * (K / 256) * 16; *b = rows * (K / 256) * 2; break;
     case ORN_A8: *w = rows * K; *s = rows * (K / 64) * 2; *b = rows * (K / 64) * 2; break;
+    case ORN_A4: *w = rows * (K / 2); *s = rows * (K / 32) * 2; *b = rows * (K / 32) * 2; break;
     default: *w = rows * K * 2; *s = 0; *b = 0; break;
   }
 }
@@ -512,8 +557,8 @@ int k_linear_pack(orn_ctx* ctx, cudaStream_t st, orn_linear* L, const uint8_t* d
     rows_scatter_kernel<<<(unsigned)rows, 32, 0, st>>>(db, g.b2, L->w, g.rec, g.b0 + g.b1);
     return orn_launch_check(ctx, "rows_scatter");
   }
-  if (L->kind == ORN_A8) {
-    const int ng = L->K / 64;
+  if (L->kind == ORN_A8 || L->kind == ORN_A4) {
+    const int ng = L->kind == ORN_A8 ? L->K / 64 : L->K / 32;
     const int64_t n = (int64_t)rows * ng;
     a8_pack_sb<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const uint16_t*)ds, (const uint16_t*)db, n, ng, L->s, g.rec);
     return orn_launch_check(ctx, "a8_pack_sb");
@@ -538,8 +583,8 @@ int k_linear_unpack(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, uint8_t*
     rows_gather_kernel<<<(unsigned)rows, 32, 0, st>>>(L->w, g.rec, g.b0 + g.b1, g.b2, db);
     return orn_launch_check(ctx, "rows_gather");
   }
-  if (L->kind == ORN_A8) {
-    const int ng = L->K / 64;
+  if (L->kind == ORN_A8 || L->kind == ORN_A4) {
+    const int ng = L->kind == ORN_A8 ? L->K / 64 : L->K / 32;
     const int64_t n = (int64_t)rows * ng;
     a8_unpack_sb<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(L->s, g.rec, n, ng, (uint16_t*)ds, (uint16_t*)db);
     return orn_launch_check(ctx, "a8_unpack_sb");
@@ -697,6 +742,29 @@ __global__ void random_a8_kernel(LinDev L, uint64_t seed, float std) {
     q[i] = (uint8_t)fminf(255.f, fmaxf(0.f, rintf((v - b) / s)));
   }
 }
+__global__ void random_a4_kernel(LinDev L, uint64_t seed, float std) {
+  int64_t ngroups = (int64_t)L.E * L.O * (L.K >> 5);
+  int64_t ig = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (ig >= ngroups) return;
+  float lo = 1e30f, hi = -1e30f;
+  for (int i = 0; i < 32; ++i) {
+    float v = std * approx_normal(seed, ig * 32 + i);
+    lo = fminf(lo, v); hi = fmaxf(hi, v);
+  }
+  float scale = fmaxf((hi - lo) / 15.0f, 1e-8f);
+  bf16_t sb = f2bf(scale), bb = f2bf(lo);
+  float s = bf2f(sb), b = bf2f(bb);
+  const int ngr = L.K >> 5;
+  const int64_t rrow = ig / ngr;
+  const int rgrp = (int)(ig % ngr);
+  reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(L.s) + rrow * L.rec)[rgrp] = (uint32_t)sb | ((uint32_t)bb << 16);
+  uint8_t* q = const_cast<uint8_t*>(L.w) + rrow * L.rec + rgrp * 16;
+  for (int i = 0; i < 16; ++i) {
+    float v0 = std * approx_normal(seed, ig * 32 + 2 * i), v1 = std * approx_normal(seed, ig * 32 + 2 * i + 1);
+    int q0 = (int)fminf(15.f, fmaxf(0.f, rintf((v0 - b) / s))), q1 = (int)fminf(15.f, fmaxf(0.f, rintf((v1 - b) / s)));
+    q[i] = (uint8_t)(q0 | (q1 << 4));
+  }
+}
 }  // namespace
 
 int k_fill_bf16(orn_ctx* ctx, cudaStream_t st, bf16_t* p, size_t n, uint64_t seed, float mean,
@@ -716,6 +784,9 @@ int k_linear_random(orn_ctx* ctx, cudaStream_t st, orn_linear* L, uint64_t seed,
   } else if (L->kind == ORN_A8) {
     int64_t ng = (int64_t)L->E * L->O * (L->K / 64);
     random_a8_kernel<<<(unsigned)((ng + 127) / 128), 128, 0, st>>>(d, seed, std);
+  } else if (L->kind == ORN_A4) {
+    int64_t ng = (int64_t)L->E * L->O * (L->K / 32);
+    random_a4_kernel<<<(unsigned)((ng + 127) / 128), 128, 0, st>>>(d, seed, std);
   } else {
     return k_fill_bf16(ctx, st, (bf16_t*)L->w, (size_t)L->E * L->O * L->K, seed, 0.f, std);
   }

@@ -11,6 +11,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <cctype>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -112,11 +113,19 @@ struct JParser {
     else if (lit("false")) { v.type = JVal::Bool; v.b = false; }
     else if (lit("null")) { v.type = JVal::Null; }
     else {
+      // the header of a memory-mapped file is not NUL-terminated: parse from a bounded copy
+      char tmp[64];
+      size_t n = 0;
+      while (p + n < end && n + 1 < sizeof tmp && (isdigit((unsigned char)p[n]) || strchr("+-.eE", p[n]) != nullptr)) {
+        tmp[n] = p[n];
+        ++n;
+      }
+      tmp[n] = 0;
       char* e = nullptr;
       v.type = JVal::Num;
-      v.num = strtod(p, &e);
-      if (e == p || e > end) ok = false;
-      p = e;
+      v.num = strtod(tmp, &e);
+      if (e == tmp) ok = false;
+      p += (e - tmp);
     }
     return v;
   }
@@ -188,7 +197,12 @@ bool open_shard(const std::string& path, Store* st, std::string* err) {
     if (!dt || !sh || !off || off->arr.size() != 2) { *err = "bad tensor entry " + kv.first; return false; }
     TInfo ti;
     ti.dtype = dt->str;
-    for (auto& d : sh->arr) ti.shape.push_back((int64_t)d.num);
+    bool shape_ok = true;
+    for (auto& d : sh->arr) {
+      if (d.type != JVal::Num || d.num < 0 || d.num > 2147483647.0 || d.num != (double)(int64_t)d.num) shape_ok = false;
+      ti.shape.push_back((int64_t)d.num);
+    }
+    if (!shape_ok) { *err = "bad shape for " + kv.first; return false; }
     size_t a = (size_t)off->arr[0].num, b = (size_t)off->arr[1].num;
     if (a > b || b > data_size) { *err = "tensor out of bounds: " + kv.first; return false; }
     ti.data = data + a;
@@ -207,6 +221,16 @@ int64_t numel(const TInfo& t) {
   for (auto d : t.shape) n *= d;
   return n;
 }
+// bytes the declared dtype and shape ask for must be the bytes the file holds for the tensor
+bool bytes_match(const TInfo& t, size_t elem) { return !t.shape.empty() && numel(t) > 0 && (size_t)numel(t) * elem == t.nbytes; }
+
+// per-module quantisation of config.json (src/weights.rs:41-98): a default {group_size, bits, mode}
+// and overrides keyed by module path
+struct QSpec {
+  int group = 0, bits = 0;
+  std::string mode;  // "affine", "q4k", "q6k", "nvfp4", ...
+  bool present = false;
+};
 
 }  // namespace
 
@@ -262,6 +286,31 @@ extern "C" int32_t orn_model_load(orn_ctx* ctx, const char* dir_c, int32_t max_c
   if (missing) ORN_FAIL(ctx, ORN_ERR_IO, "config.json: missing " + missing_key);
   if (u("linear_value_head_dim") != c.gdn_head_dim) ORN_FAIL(ctx, ORN_ERR_ARG, "config.json: key and value head dims differ");
 
+  // ---- quantization block (src/weights.rs:49-79); absent in hand-made artifacts: formats then follow the tensors
+  QSpec qdef;
+  std::map<std::string, QSpec> qmods;
+  if (const JVal* q = cfgj.get("quantization")) {
+    if (q->type != JVal::Obj) ORN_FAIL(ctx, ORN_ERR_IO, "config.json: quantization is not an object");
+    const JVal* g = q->get("group_size");
+    const JVal* b = q->get("bits");
+    if (!g || !b || g->type != JVal::Num || b->type != JVal::Num) ORN_FAIL(ctx, ORN_ERR_IO, "config.json: quantization.group_size / bits");
+    qdef.group = (int)g->num; qdef.bits = (int)b->num; qdef.present = true;
+    const JVal* md = q->get("mode");
+    qdef.mode = (md && md->type == JVal::Str) ? md->str : "affine";  // older artifacts carry no mode (weights.rs:52-53)
+    for (auto& kv : q->obj) {
+      if (kv.second.type != JVal::Obj) continue;
+      QSpec sp = qdef;
+      if (const JVal* v = kv.second.get("group_size")) sp.group = (int)v->num;
+      if (const JVal* v = kv.second.get("bits")) sp.bits = (int)v->num;
+      if (const JVal* v = kv.second.get("mode")) if (v->type == JVal::Str) sp.mode = v->str;
+      qmods[kv.first] = sp;
+    }
+  }
+  auto spec_of = [&](const std::string& mod) -> QSpec {
+    auto it = qmods.find(mod);
+    return it == qmods.end() ? qdef : it->second;
+  };
+
   // ---- shards (src/safetensors.rs:296-308) and the MTP sidecar (mtp.rs:270-279)
   Store st;
   std::string err;
@@ -316,7 +365,8 @@ extern "C" int32_t orn_model_load(orn_ctx* ctx, const char* dir_c, int32_t max_c
       std::string proj = name.substr(dot + 1);  // gate_proj.weight
       if (stacked_done[proj]) continue;
       stacked_done[proj] = true;
-      if (ti.dtype != "BF16" || ti.shape.size() != 2) return fail(ORN_ERR_ARG, "mtp expert tensor is not 2-D bf16: " + name);
+      if (ti.dtype != "BF16" || ti.shape.size() != 2 || !bytes_match(ti, 2))
+        return fail(ORN_ERR_ARG, "mtp expert tensor is not 2-D bf16 of its declared size: " + name);
       const int O = (int)ti.shape[0], K = (int)ti.shape[1];
       std::vector<uint8_t> buf((size_t)c.n_experts * O * K * 2);
       for (int e = 0; e < c.n_experts; ++e) {
@@ -341,26 +391,43 @@ extern "C" int32_t orn_model_load(orn_ctx* ctx, const char* dir_c, int32_t max_c
         int kind;
         const TInfo* third;
         // leading expert axis, then [O, packed K]
-        if (ti.shape.size() < 2) return fail(ORN_ERR_ARG, "quantised weight is not a matrix: " + name);
+        if (ti.shape.size() < 2 || sc->second.shape.empty()) return fail(ORN_ERR_ARG, "quantised weight is not a matrix: " + name);
         const int E = ti.shape.size() == 3 ? (int)ti.shape[0] : 1;
         const int O = (int)ti.shape[ti.shape.size() - 2];
         const int64_t packed = ti.shape.back();  // u32 words per row
+        const int64_t scols = sc->second.shape.back();
+        if (packed <= 0 || scols <= 0 || O <= 0 || E <= 0) return fail(ORN_ERR_ARG, "empty quantised tensor: " + mod);
+        const QSpec sp = spec_of(mod);
         int K;
-        if (dmq != st.tensors.end()) {
+        const bool as_kquant = sp.present ? (sp.mode == "q4k" || sp.mode == "q6k") : dmq != st.tensors.end();
+        if (sp.present && sp.mode != "affine" && !as_kquant)
+          return fail(ORN_ERR_ARG, "quantization mode '" + sp.mode + "' is not on this path: " + mod);
+        if (as_kquant) {
+          // kquant_matrix (src/weights.rs:199-227): .weight/.scales/.dm, never .biases, super-blocks of 256
+          if (dmq == st.tensors.end() || bia != st.tensors.end())
+            return fail(ORN_ERR_ARG, "k-quant module must carry .dm and no .biases: " + mod);
+          if (sp.present && sp.group != 256) return fail(ORN_ERR_ARG, "k-quant group_size must be 256: " + mod);
           third = &dmq->second;
+          if (third->shape.empty()) return fail(ORN_ERR_ARG, "k-quant .dm has no shape: " + mod);
           const int64_t last = third->shape.back();
-          if (last == 2) { kind = ORN_Q4K; K = (int)(packed * 8); }
-          else if (last == 1) { kind = ORN_Q6K; K = (int)(packed * 16 / 3); }
-          else return fail(ORN_ERR_ARG, "k-quant .dm has an unknown width: " + mod);
-        } else if (bia != st.tensors.end()) {
-          third = &bia->second;
-          kind = ORN_A8;
-          K = (int)(packed * 4);
-          // 8 bits, group 64 is the only affine flavour on this path
-          if (sc->second.shape.back() * 64 != K)
-            return fail(ORN_ERR_ARG, "affine module is not 8-bit group-64 (unsupported on this path): " + mod);
+          const bool q4 = sp.present ? sp.mode == "q4k" : last == 2;
+          if (q4 && last == 2) { kind = ORN_Q4K; K = (int)(packed * 8); }
+          else if (!q4 && last == 1) { kind = ORN_Q6K; K = (int)(packed * 16 / 3); }
+          else return fail(ORN_ERR_ARG, "k-quant .dm width does not match the module's mode: " + mod);
         } else {
-          return fail(ORN_ERR_ARG, "quantised module without .biases or .dm: " + mod);
+          // quant_matrix (src/weights.rs:132-172): mlx affine, bits and group size from config.json
+          if (bia == st.tensors.end() || dmq != st.tensors.end())
+            return fail(ORN_ERR_ARG, "affine module must carry .biases and no .dm: " + mod);
+          third = &bia->second;
+          int bits = sp.bits, group = sp.group;
+          if (!sp.present) {  // no quantization block: the 8-bit group-64 layout is the only one that can be assumed
+            bits = 8; group = 64;
+          }
+          if (bits == 8 && group == 64) kind = ORN_A8;
+          else if (bits == 4 && group == 32) kind = ORN_A4;
+          else return fail(ORN_ERR_ARG, "affine module is neither 8-bit group-64 nor 4-bit group-32 (unsupported on this path): " + mod);
+          K = (int)(packed * 32 / bits);
+          if (scols * group != K) return fail(ORN_ERR_ARG, "affine module's scales do not match its bits and group size: " + mod);
         }
         size_t aw, as, ab;
         linear_artifact_sizes(kind, E, O, K, &aw, &as, &ab);
@@ -373,6 +440,7 @@ extern "C" int32_t orn_model_load(orn_ctx* ctx, const char* dir_c, int32_t max_c
         continue;
       }
       if (ti.dtype == "BF16" && ti.shape.size() == 2) {
+        if (!bytes_match(ti, 2)) return fail(ORN_ERR_ARG, "tensor bytes do not match its shape: " + name);
         orn_linear* L = nullptr;
         rc = orn_linear_create(ctx, ORN_BF16, 1, (int)ti.shape[0], (int)ti.shape[1], ti.data, nullptr, nullptr, &L);
         if (rc != ORN_OK) { orn_model_destroy(m); return rc; }
@@ -383,6 +451,7 @@ extern "C" int32_t orn_model_load(orn_ctx* ctx, const char* dir_c, int32_t max_c
       }
     }
     if (ti.dtype == "BF16") {
+      if (!bytes_match(ti, 2)) return fail(ORN_ERR_ARG, "tensor bytes do not match its shape: " + name);
       rc = orn_model_set_tensor(m, name.c_str(), (const uint16_t*)ti.data, (size_t)numel(ti));
       if (rc != ORN_OK) { orn_model_destroy(m); return rc; }
     }

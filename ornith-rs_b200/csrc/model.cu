@@ -138,6 +138,7 @@ struct orn_model {
   orn_linear* fr_head = nullptr;
   uint32_t* fr_ids = nullptr;  // device
   int fr_n = 0;
+  bool fused_ok = true;  // false when a matrix outside the MoE blocks is in a format the fused kernels do not read
   int fr_gen = 0;  // bumped whenever the FR-Spec head is replaced: graphs that drafted through the old one are stale
   bool finalized = false;
   Workspace ws{};
@@ -317,6 +318,18 @@ int finalize(orn_model* m) {
     CK(load_moe(m, lp + "mlp.", h.moe));
     h.present = true;
   }
+  // formats outside the fused kernels' four: allowed anywhere, but only MoE blocks fall back one by one
+  m->fused_ok = m->embed->kind <= ORN_BF16 && m->lm_head->kind <= ORN_BF16;
+  for (const Layer& ly : m->layers) {
+    const orn_linear* mix[9] = {ly.in_qkv, ly.in_z, ly.in_a, ly.in_b, ly.out_proj, ly.q_proj, ly.k_proj, ly.v_proj, ly.o_proj};
+    for (const orn_linear* l : mix)
+      if (l != nullptr && l->kind > ORN_BF16) m->fused_ok = false;
+  }
+  if (m->mtp.present) {
+    const orn_linear* mix[5] = {m->mtp.fc, m->mtp.q_proj, m->mtp.k_proj, m->mtp.v_proj, m->mtp.o_proj};
+    for (const orn_linear* l : mix)
+      if (l->kind > ORN_BF16) m->fused_ok = false;
+  }
   m->lnb = (float)(std::log((double)c.rope_theta) / (double)(c.rope_dims / 2));
   CK(build_workspace(m));
   for (int i = 0; i < 4; ++i) ORN_CHECK_CUDA(m->ctx, cudaEventCreate(&m->ev[i]));
@@ -423,7 +436,7 @@ int commit(orn_cache* c, int keep, int ring_step) {
   return ORN_OK;
 }
 
-bool use_fused() {
+bool use_fused_env() {
   // ORN_UNFUSED=1 runs the one-kernel-per-op control path (same arithmetic)
   static int v = -1;
   if (v < 0) {
@@ -431,6 +444,14 @@ bool use_fused() {
     v = (e && e[0] == '1') ? 0 : 1;
   }
   return v == 1;
+}
+bool use_fused(const orn_model* m) { return use_fused_env() && m->fused_ok; }
+// the fused expert kernels read the four decode formats; gate/up share one, routed and shared down share one
+bool moe_fusable(const Moe& e) {
+  const orn_linear* all[8] = {e.gate, e.sw_gate, e.sw_up, e.sw_down, e.sh_gate, e.sh_up, e.sh_down, e.sh_egate};
+  for (const orn_linear* l : all)
+    if (l->kind > ORN_BF16) return false;
+  return e.sw_gate->kind == e.sw_up->kind && e.sh_gate->kind == e.sh_up->kind && e.sw_down->kind == e.sh_down->kind;
 }
 
 // MoE block from the pre-norm pair (a, b): h = bf(a+b) -> w.h, norm with `nw`,
@@ -440,6 +461,16 @@ int moe_fused(orn_model* m, const Moe& moe, const bf16_t* a, const bf16_t* b, co
   cudaStream_t s = ctx->stream;
   Workspace& w = m->ws;
   const orn_config& c = m->cfg;
+  if (!moe_fusable(moe)) {
+    // a block with a format outside the fused kernels (affine-4 shared experts of the published
+    // q6k-full mix, or routed and shared down projections in different formats): one kernel per op
+    if (b != nullptr) CK(k_add_rms_norm(ctx, s, a, b, nw, T, c.hidden, c.rms_eps, w.h, w.normed2));
+    else {
+      ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(w.h, a, sizeof(bf16_t) * (size_t)T * c.hidden, cudaMemcpyDeviceToDevice, s));
+      CK(k_rms_norm(ctx, s, a, nw, T, c.hidden, c.rms_eps, w.normed2));
+    }
+    return moe_block(m, moe, w.normed2, T, w.mo, nullptr);
+  }
   FusedPrologue fp;
   fp.mode = PRO_ADDNORM; fp.K = c.hidden; fp.a = a; fp.b = b; fp.w = nw; fp.sum_out = w.h; fp.norm_out = w.normed2;
   fp.eps = c.rms_eps;
@@ -465,7 +496,7 @@ int trunk_layers(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int T, bo
   const int H = c.hidden;
   if (T < 1 || T > kMaxRows) ORN_FAIL(ctx, ORN_ERR_ARG, "forward: 1..4 rows per call");
   if (cc->h_pos + T > c.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "forward: context exceeds max_ctx");
-  if (!use_fused()) {
+  if (!use_fused(m)) {
     CK(k_embedding(ctx, s, m->embed, dev_ids, T, w.x));
     CK(k_rms_norm(ctx, s, w.x, m->layers[0].input_ln, T, H, c.rms_eps, w.normed));
     for (int i = 0; i < c.n_layers; ++i) {
@@ -536,7 +567,7 @@ int trunk_finish(orn_model* m, orn_cache* cc, int T, bool capture, bf16_t* norme
   Workspace& w = m->ws;
   const orn_config& c = m->cfg;
   const int H = c.hidden;
-  if (head != nullptr && use_fused()) {
+  if (head != nullptr && use_fused(m)) {
     FusedPrologue fp;
     fp.mode = PRO_ADDNORM; fp.K = H; fp.a = w.h; fp.b = w.mo; fp.w = m->norm; fp.sum_out = pre_norm_out;
     fp.norm_out = normed_out; fp.eps = c.rms_eps;
@@ -593,7 +624,7 @@ int mtp_step(orn_model* m, orn_cache* cc, const bf16_t* trunk_hidden, const uint
   const int H = c.hidden;
   if (!h.present) ORN_FAIL(ctx, ORN_ERR_STATE, "mtp: the model has no MTP head");
   if (cc->h_mtp_pos + T > c.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "mtp: context exceeds max_ctx");
-  if (!use_fused()) {
+  if (!use_fused(m)) {
     CK(k_embedding(ctx, s, m->embed, dev_ids, T, w.memb));
     CK(k_rms_norm(ctx, s, w.memb, h.pre_fc_norm_embedding, T, H, c.rms_eps, w.me));
     CK(k_rms_norm(ctx, s, trunk_hidden, h.pre_fc_norm_hidden, T, H, c.rms_eps, w.mh));
@@ -733,7 +764,7 @@ int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar, 2 prefill row
     if (kind == 1) return ar_body(m, c);
     return forward_dev(m, c, m->ws.ids, n_rows, false, nullptr, nullptr);  // a window of prompt rows
   };
-  if (g.seen == 0 || eager || !use_fused() || g.exec != nullptr) {
+  if (g.seen == 0 || eager || !use_fused(m) || g.exec != nullptr) {
     g.seen += 1;
     return body();
   }
@@ -786,7 +817,8 @@ int wide_mm(orn_model* m, const orn_linear* L, const bf16_t* x, int T, bf16_t* y
   }
   return ORN_OK;
 }
-constexpr int kWideMinRows = 16;    // below this the mat-vec windows win (kquant.rs MM_ROW_LIMIT)
+constexpr int kWideMinRows = 64;    // measured: below about 60 rows the 4-row mat-vec windows are faster (the
+                                    // reference's own crossover, kquant.rs MM_ROW_LIMIT, is 16 on its hardware)
 constexpr int kWideMaxRows = 2048;  // the reference's prefill chunk (generate.rs:25)
 
 int wide_reserve(orn_model* m, int rows) {
@@ -962,7 +994,7 @@ int prefill(orn_model* m, orn_cache* cc, const uint32_t* prompt, int n, int pref
   while (n - done > keep_last) {
     int chunk = std::min(step, n - done - keep_last);
     int off = 0;
-    if (chunk >= kWideMinRows && use_wide_prefill() && use_fused()) {
+    if (chunk >= kWideMinRows && use_wide_prefill() && use_fused_env()) {
       // a chunk wide enough for the tensor cores (the reference's tile path, kquant.rs:783-812)
       chunk = std::min(chunk, kWideMaxRows);
       CK(wide_reserve(m, chunk));
@@ -1526,10 +1558,12 @@ int32_t orn_moe_block(orn_ctx* ctx, const orn_linear* gate, const orn_linear* sw
   moe.sh_down = (orn_linear*)sh_down; moe.sh_egate = (orn_linear*)sh_egate;
   // the route the model takes (three persistent kernels) whenever the shapes allow it; the
   // one-kernel-per-op sequence under ORN_UNFUSED=1 and for shapes outside the fused kernels' limits
-  const bool fused = use_fused() && cfg.hidden % 256 == 0 && cfg.hidden <= 4096 && cfg.n_experts <= 512 && top_k <= 8 &&
+  const bool fused = use_fused_env() && cfg.hidden % 256 == 0 && cfg.hidden <= 4096 && cfg.n_experts <= 512 && top_k <= 8 &&
                      cfg.expert_inter % 256 == 0 && cfg.shared_inter % 256 == 0 && cfg.expert_inter <= 2048 &&
                      cfg.shared_inter <= 2048 && sw_gate->kind == sw_up->kind && sw_down->kind == sh_down->kind &&
-                     sh_gate->kind == sh_up->kind && sh_gate->K == cfg.hidden && sh_up->O == cfg.shared_inter &&
+                     sh_gate->kind == sh_up->kind && gate->kind <= ORN_BF16 && sw_gate->kind <= ORN_BF16 &&
+                     sw_down->kind <= ORN_BF16 && sh_gate->kind <= ORN_BF16 && sh_egate->kind <= ORN_BF16 &&
+                     sh_gate->K == cfg.hidden && sh_up->O == cfg.shared_inter &&
                      sh_up->K == cfg.hidden;
   if (rc == ORN_OK && fused) {
     FusedPrologue fp;

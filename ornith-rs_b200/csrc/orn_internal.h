@@ -39,6 +39,7 @@ void orn_ktime_mark(orn_ctx* ctx, const char* what);
 //   Q4_K: nibble bytes K/2 | one 16-byte header {d f16, dmin f16, scales[12]} per block
 //   Q6_K: ql|qh 192 bytes per block | int8 scales 16 per block | d f16 per block
 //   A8  : codes K | u32 {scale bf16, bias bf16} per 64 weights
+//   A4  : nibble codes K/2 | u32 {scale bf16, bias bf16} per 32 weights
 //   BF16: bf16 K
 // w points at row 0's record; s and b point at its streams 1 and 2 (same
 // allocation), so row r's streams are w + r*rec, s + r*rec, b + r*rec.
@@ -52,6 +53,7 @@ __host__ __device__ inline RecGeom rec_geom(int kind, int K) {
     case ORN_Q4K: g.b0 = (uint32_t)K / 2; g.b1 = nb * 16; g.b2 = 0; break;
     case ORN_Q6K: g.b0 = nb * 192; g.b1 = nb * 16; g.b2 = nb * 2; break;
     case ORN_A8: g.b0 = (uint32_t)K; g.b1 = ((uint32_t)K >> 6) * 4; g.b2 = 0; break;
+    case ORN_A4: g.b0 = (uint32_t)K / 2; g.b1 = ((uint32_t)K >> 5) * 4; g.b2 = 0; break;
     default: g.b0 = 2u * (uint32_t)K; g.b1 = 0; g.b2 = 0; break;
   }
   g.rec = (g.b0 + g.b1 + g.b2 + 15u) & ~15u;

@@ -43,9 +43,9 @@ def main():
     c.reset()
     h = [gm.forward(c, prompt[a:b]).numpy() for a, b in [(0, 1), (1, 3), (3, 7)]]
     out["tiny_hidden_sha"] = sha(np.concatenate(h))
-    # a 45-token prompt through orn_prefill (one chunk; which arithmetic it uses is the parent's choice)
+    # a 70-token prompt through orn_prefill (one chunk; which arithmetic it uses is the parent's choice)
     c.reset()
-    long_ids = np.random.default_rng(4).integers(0, cfg.vocab, 45).astype(np.uint32)
+    long_ids = np.random.default_rng(4).integers(0, cfg.vocab, 70).astype(np.uint32)
     out["tiny_prefill_sha"] = sha(gm.prefill(c, long_ids, prefill_step=2048, want_hidden=True).numpy())
     out["tiny_after_prefill"] = sha(gm.forward(c, prompt[:2]).numpy())   # the caches it left behind
     c.free()

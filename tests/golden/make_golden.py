@@ -54,9 +54,54 @@ def main(ref_root):
     np.savez_compressed(os.path.join(HERE, "a8_golden.npz"), w=wa, q=q.reshape(16, 256), scales=s.reshape(16, 4),
                         biases=b.reshape(16, 4), words=words, deq=deq)
 
+    # 3b. affine 4-bit group-32 quantise + pack (the artifact's default mode)
+    q4, s4, b4 = aq.quantize(wa, group_size=32, bits=4)
+    words4 = aq.pack(q4, 4, 256 // 8)
+    deq4 = (s4[:, None] * q4.astype(np.float32) + b4[:, None]).reshape(16, 256)
+    np.savez_compressed(os.path.join(HERE, "a4_golden.npz"), w=wa, q=q4.reshape(16, 256), scales=s4.reshape(16, 8),
+                        biases=b4.reshape(16, 8), words=words4, deq=deq4)
+
     # 4. bfloat16 rounding as the tool states it (ties to even)
     xs = rng.standard_normal(4096).astype(np.float32) * np.float32(10.0) ** rng.integers(-6, 6, 4096)
     np.savez_compressed(os.path.join(HERE, "bf16_golden.npz"), x=xs.astype(np.float32), r=aq.bf16(xs))
+    # 5. weight bytes one decode step reads, by the reference's own accounting tool run on
+    # header-only artifacts (tools/step_bytes.py reads shapes and dtypes, never the data)
+    import json
+    import re
+    import subprocess
+    import tempfile
+    sys.path.insert(0, os.path.dirname(HERE))
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(HERE)), "oracle"))
+    import helpers as hp
+
+    class Dims:
+        hidden, n_layers, full_attn_interval, n_heads, n_kv_heads, head_dim = 2048, 40, 4, 16, 2, 256
+        gdn_k_heads, gdn_v_heads, gdn_head_dim, gdn_conv_kernel = 16, 32, 128, 4
+        n_experts, top_k, expert_inter, shared_inter, vocab = 256, 8, 512, 512, 248320
+
+    out = {}
+    for mix in ("benchmark", "published"):
+        with tempfile.TemporaryDirectory() as tmp:
+            art = os.path.join(tmp, "art-" + mix)
+            os.makedirs(art)
+            inv = hp.artifact_inventory(Dims, mix)
+            header, off = {}, 0
+            size = {"BF16": 2, "F16": 2, "U32": 4, "U8": 1, "I8": 1}
+            for name, (dt, shape) in inv.items():
+                n = int(np.prod(shape)) * size[dt]
+                header[name] = {"dtype": dt, "shape": shape, "data_offsets": [off, off + n]}
+                off += n
+            hj = json.dumps(header).encode()
+            with open(os.path.join(art, "model.safetensors"), "wb") as f:
+                f.write(len(hj).to_bytes(8, "little") + hj)
+            json.dump({"weight_map": {n: "model.safetensors" for n in inv}}, open(os.path.join(art, "model.safetensors.index.json"), "w"))
+            json.dump({"text_config": {"num_experts": Dims.n_experts, "num_experts_per_tok": Dims.top_k, "vocab_size": Dims.vocab},
+                       "quantization": {"group_size": 32, "bits": 4, "mode": "affine"}}, open(os.path.join(art, "config.json"), "w"))
+            txt = subprocess.run([sys.executable, os.path.join(ref_root, "tools", "step_bytes.py"), art], capture_output=True,
+                                 text=True, check=True).stdout
+        groups = {m.group(1).strip(): float(m.group(2)) for m in re.finditer(r"^\s{4}(.+?)\s+([0-9.]+) GB", txt, flags=re.M)}
+        out[mix] = {"total_gb": groups.pop("TOTAL"), "groups_gb": groups}
+    json.dump(out, open(os.path.join(HERE, "step_bytes_golden.json"), "w"), indent=1)
     print("wrote fixtures to", HERE)
 
 

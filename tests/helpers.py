@@ -4,7 +4,7 @@ import numpy as np
 
 import orn_oracle as orc
 
-Q4K, Q6K, A8, BF16 = 0, 1, 2, 3
+Q4K, Q6K, A8, BF16, A4 = 0, 1, 2, 3, 4
 
 
 # ------------------------------------------------------------------ bfloat16
@@ -130,6 +130,35 @@ def quantize_a8(w):
     return q, sb, bb
 
 
+def quantize_affine(w, group, bits):
+    """mlx's affine_quantize as the reference's tools/aq.py:34-72 restates it (scale signed towards
+    the larger edge, the edge code exact, codes computed against the unrounded scale and bias,
+    Metal's round half away from zero), then bfloat16 scales and biases."""
+    f = np.float32
+    n_bins = f((1 << bits) - 1)
+    g = np.asarray(w, np.float32).reshape(-1, group)
+    w_min = g.min(1)
+    w_max = np.maximum(g.max(1), f(0))
+    scale = np.maximum((w_max - w_min) / n_bins, f(1e-7)).astype(np.float32)
+    side = np.abs(w_min) > np.abs(w_max)
+    scale = np.where(side, scale, -scale).astype(np.float32)
+    edge = np.where(side, w_min, w_max).astype(np.float32)
+    rnd = lambda x: (np.sign(x) * np.floor(np.abs(x) + f(0.5))).astype(np.float32)
+    q0 = rnd(edge / scale)
+    at_zero = q0 == f(0)
+    scale = np.where(at_zero, scale, edge / np.where(at_zero, f(1), q0)).astype(np.float32)
+    bias = np.where(at_zero, f(0), edge).astype(np.float32)
+    q = np.minimum(rnd((g - bias[:, None]) / scale[:, None]), n_bins)
+    return q.astype(np.uint8), f32_to_bf16(scale), f32_to_bf16(bias)
+
+
+def pack_nibbles(q):
+    """4-bit codes, eight per u32 with the lowest-order field first (tools/aq.py:78-93): byte b of
+    a row holds code 2b in its low nibble and code 2b+1 in its high nibble."""
+    q = np.asarray(q, np.uint8).reshape(-1, 2)
+    return (q[:, 0] | (q[:, 1] << 4)).astype(np.uint8)
+
+
 def make_weights(rng, kind, E, O, K, std=0.02):
     w = (rng.standard_normal((E * O, K)) * std).astype(np.float32)
     if kind == Q4K:
@@ -141,6 +170,9 @@ def make_weights(rng, kind, E, O, K, std=0.02):
     if kind == A8:
         q, s, b = quantize_a8(w)
         return orc.Weights(A8, E, O, K, q, s, b)
+    if kind == A4:
+        q, s, b = quantize_affine(w, 32, 4)
+        return orc.Weights(A4, E, O, K, pack_nibbles(q).reshape(E * O, K // 2), s, b)
     return orc.Weights(BF16, E, O, K, f32_to_bf16(w))
 
 
@@ -157,9 +189,15 @@ def tiny_config(cfg_cls, **over):
     return cfg_cls(**d)
 
 
-def tiny_model_weights(cfg, seed=0):
-    """name -> Weights | uint16 tensor, in the benchmark's quantisation mix."""
+def tiny_model_weights(cfg, seed=0, mix="benchmark"):
+    """name -> Weights | uint16 tensor.  mix "benchmark": expert gate/up Q4_K, expert down Q6_K,
+    everything else 8-bit affine, MTP head bf16.  mix "published": the module formats of the
+    reference's q6k-full artifact (tools/forge_q4k.py:131-152): gated-delta projections, lm_head and
+    routed experts Q4_K, attention projections and routers Q6_K, shared experts affine 4-bit group
+    32, embedding and shared-expert gate 8-bit affine."""
     rng = np.random.default_rng(seed)
+    pub = mix == "published"
+    LIN, ATT, HEAD = (Q4K, Q6K, Q4K) if pub else (A8, A8, A8)
     H = cfg.hidden
     D = 2 * cfg.gdn_k_heads * cfg.gdn_head_dim + cfg.gdn_v_heads * cfg.gdn_head_dim
     VD = cfg.gdn_v_heads * cfg.gdn_head_dim
@@ -171,17 +209,18 @@ def tiny_model_weights(cfg, seed=0):
 
     def moe(p, dense):
         q4, q6, a8 = (BF16, BF16, BF16) if dense else (Q4K, Q6K, A8)
-        W[p + "gate"] = make_weights(rng, a8, 1, cfg.n_experts, H)
+        router, down, sh = (a8, q6, None) if (dense or not pub) else (Q6K, Q4K, A4)
+        W[p + "gate"] = make_weights(rng, router, 1, cfg.n_experts, H)
         W[p + "switch_mlp.gate_proj"] = make_weights(rng, q4, cfg.n_experts, cfg.expert_inter, H)
         W[p + "switch_mlp.up_proj"] = make_weights(rng, q4, cfg.n_experts, cfg.expert_inter, H)
-        W[p + "switch_mlp.down_proj"] = make_weights(rng, q6, cfg.n_experts, H, cfg.expert_inter)
-        W[p + "shared_expert.gate_proj"] = make_weights(rng, q4, 1, cfg.shared_inter, H)
-        W[p + "shared_expert.up_proj"] = make_weights(rng, q4, 1, cfg.shared_inter, H)
-        W[p + "shared_expert.down_proj"] = make_weights(rng, q6, 1, H, cfg.shared_inter)
+        W[p + "switch_mlp.down_proj"] = make_weights(rng, down, cfg.n_experts, H, cfg.expert_inter)
+        W[p + "shared_expert.gate_proj"] = make_weights(rng, sh if sh is not None else q4, 1, cfg.shared_inter, H)
+        W[p + "shared_expert.up_proj"] = make_weights(rng, sh if sh is not None else q4, 1, cfg.shared_inter, H)
+        W[p + "shared_expert.down_proj"] = make_weights(rng, sh if sh is not None else q6, 1, H, cfg.shared_inter)
         W[p + "shared_expert_gate"] = make_weights(rng, a8, 1, 1, H)
 
     W["embed_tokens"] = make_weights(rng, A8, 1, cfg.vocab, H)
-    W["lm_head"] = make_weights(rng, A8, 1, cfg.vocab, H)
+    W["lm_head"] = make_weights(rng, HEAD, 1, cfg.vocab, H)
     ten("norm.weight", H, 1.0, 0.05)
     for i in range(cfg.n_layers):
         lp = "layers.%d." % i
@@ -189,21 +228,21 @@ def tiny_model_weights(cfg, seed=0):
         ten(lp + "post_attention_layernorm.weight", H, 1.0, 0.05)
         if (i + 1) % cfg.full_attn_interval != 0:
             a = lp + "linear_attn."
-            W[a + "in_proj_qkv"] = make_weights(rng, A8, 1, D, H)
-            W[a + "in_proj_z"] = make_weights(rng, A8, 1, VD, H)
+            W[a + "in_proj_qkv"] = make_weights(rng, LIN, 1, D, H)
+            W[a + "in_proj_z"] = make_weights(rng, LIN, 1, VD, H)
             W[a + "in_proj_a.weight"] = make_weights(rng, BF16, 1, cfg.gdn_v_heads, H)
             W[a + "in_proj_b.weight"] = make_weights(rng, BF16, 1, cfg.gdn_v_heads, H)
-            W[a + "out_proj"] = make_weights(rng, A8, 1, H, VD)
+            W[a + "out_proj"] = make_weights(rng, LIN, 1, H, VD)
             ten(a + "conv1d.weight", D * cfg.gdn_conv_kernel, 0.0, 0.2)
             ten(a + "dt_bias", cfg.gdn_v_heads, 0.0, 0.3)
             ten(a + "A_log", cfg.gdn_v_heads, 0.0, 0.3)
             ten(a + "norm.weight", cfg.gdn_head_dim, 1.0, 0.05)
         else:
             a = lp + "self_attn."
-            W[a + "q_proj"] = make_weights(rng, A8, 1, 2 * QD, H)
-            W[a + "k_proj"] = make_weights(rng, A8, 1, KVD, H)
-            W[a + "v_proj"] = make_weights(rng, A8, 1, KVD, H)
-            W[a + "o_proj"] = make_weights(rng, A8, 1, H, QD)
+            W[a + "q_proj"] = make_weights(rng, ATT, 1, 2 * QD, H)
+            W[a + "k_proj"] = make_weights(rng, ATT, 1, KVD, H)
+            W[a + "v_proj"] = make_weights(rng, ATT, 1, KVD, H)
+            W[a + "o_proj"] = make_weights(rng, ATT, 1, H, QD)
             ten(a + "q_norm.weight", cfg.head_dim, 1.0, 0.05)
             ten(a + "k_norm.weight", cfg.head_dim, 1.0, 0.05)
         moe(lp + "mlp.", False)
@@ -285,11 +324,21 @@ def _module_tensors(name, W):
         return {name + ".weight": ("U32", lead + [W.O, W.K // 4], raw(W.w)),
                 name + ".scales": ("BF16", lead + [W.O, W.K // 64], raw(W.s)),
                 name + ".biases": ("BF16", lead + [W.O, W.K // 64], raw(W.b))}
+    if W.kind == orc.A4:
+        return {name + ".weight": ("U32", lead + [W.O, W.K // 8], raw(W.w)),
+                name + ".scales": ("BF16", lead + [W.O, W.K // 32], raw(W.s)),
+                name + ".biases": ("BF16", lead + [W.O, W.K // 32], raw(W.b))}
     return None
 
 
-def write_artifact(directory, cfg, W, frspec_ids=None):
-    """Writes the tiny model as the reference stores a model on disk; returns the directory."""
+QUANT_SPEC = {0: {"mode": "q4k", "group_size": 256, "bits": 4}, 1: {"mode": "q6k", "group_size": 256, "bits": 6},
+              2: {"mode": "affine", "group_size": 64, "bits": 8}, 4: {"mode": "affine", "group_size": 32, "bits": 4}}
+
+
+def write_artifact(directory, cfg, W, frspec_ids=None, quant_block=False):
+    """Writes the tiny model as the reference stores a model on disk; returns the directory.
+    quant_block: config.json carries the per-module `quantization` table of a published artifact
+    (default affine 4-bit group 32, an override per module in another mode, src/weights.rs:49-79)."""
     import json
     import os
     import orn_oracle as orc
@@ -304,9 +353,18 @@ def write_artifact(directory, cfg, W, frspec_ids=None):
             "num_experts_per_tok": cfg.top_k, "moe_intermediate_size": cfg.expert_inter,
             "shared_expert_intermediate_size": cfg.shared_inter, "norm_topk_prob": bool(cfg.norm_topk_prob),
             "vocab_size": cfg.vocab, "rms_norm_eps": cfg.rms_eps}
+    top = {"model_type": "qwen3_5_moe", "text_config": text,
+           "mlx_lm_extra_tensors": {"mtp_file": "mtp/weights.safetensors"}}
+    if quant_block:
+        qb = {"group_size": 32, "bits": 4, "mode": "affine"}
+        for name, w in W.items():
+            if isinstance(w, orc.Weights) and w.kind in QUANT_SPEC and w.kind != orc.A4:
+                full = name if name.startswith("mtp.") else (
+                    "language_model.lm_head" if name == "lm_head" else "language_model.model." + name)
+                qb[full[:-len(".weight")] if full.endswith(".weight") else full] = QUANT_SPEC[w.kind]
+        top["quantization"] = qb
     with open(os.path.join(directory, "config.json"), "w") as f:
-        json.dump({"model_type": "qwen3_5_moe", "text_config": text,
-                   "mlx_lm_extra_tensors": {"mtp_file": "mtp/weights.safetensors"}}, f)
+        json.dump(top, f)
     trunk, side = {}, {}
     for name, w in W.items():
         is_mtp = name.startswith("mtp.")
@@ -344,3 +402,85 @@ def write_artifact(directory, cfg, W, frspec_ids=None):
             f.write(np.uint32(len(ids)).tobytes())
             f.write(ids.tobytes())
     return directory
+
+
+# ---------------------------------------------------------------------------
+# tensor inventory of a full-size artifact (names, dtypes, shapes; no data): what
+# tools/step_bytes.py of the reference reads from the safetensors headers
+# ---------------------------------------------------------------------------
+def artifact_inventory(cfg, mix):
+    """name -> (dtype, shape) of every trunk tensor.  mix "benchmark": BASELINE config 4 (expert
+    gate/up Q4_K, expert down Q6_K, the rest 8-bit affine group 64).  mix "published": the
+    reference's q6k-full artifact (tools/forge_q4k.py:24-35,131-152): layers 0..31 keep their routed
+    experts in Q4_K and their shared experts in affine 4-bit group 32, layers 32..39 hold both in
+    Q6_K; gated-delta projections and lm_head Q4_K; attention projections and routers Q6_K;
+    embedding and shared-expert gates 8-bit affine."""
+    H, V, E, I, SI = cfg.hidden, cfg.vocab, cfg.n_experts, cfg.expert_inter, cfg.shared_inter
+    D = 2 * cfg.gdn_k_heads * cfg.gdn_head_dim + cfg.gdn_v_heads * cfg.gdn_head_dim
+    VD, QD, KVD = cfg.gdn_v_heads * cfg.gdn_head_dim, cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    inv = {}
+
+    def mod(name, kind, O, K, lead=()):
+        lead = list(lead)
+        nb = K // 256
+        if kind == Q4K:
+            inv[name + ".weight"] = ("U32", lead + [O, K // 8])
+            inv[name + ".scales"] = ("U8", lead + [O, nb, 12])
+            inv[name + ".dm"] = ("F16", lead + [O, nb, 2])
+        elif kind == Q6K:
+            inv[name + ".weight"] = ("U32", lead + [O, 3 * K // 16])
+            inv[name + ".scales"] = ("I8", lead + [O, nb, 16])
+            inv[name + ".dm"] = ("F16", lead + [O, nb, 1])
+        elif kind in (A8, A4):
+            bits, group = (8, 64) if kind == A8 else (4, 32)
+            inv[name + ".weight"] = ("U32", lead + [O, K * bits // 32])
+            inv[name + ".scales"] = ("BF16", lead + [O, K // group])
+            inv[name + ".biases"] = ("BF16", lead + [O, K // group])
+        else:
+            inv[name + ".weight"] = ("BF16", lead + [O, K])
+
+    pub = mix == "published"
+    P = "language_model.model."
+    mod(P + "embed_tokens", A8, V, H)
+    mod("language_model.lm_head", Q4K if pub else A8, V, H)
+    inv[P + "norm.weight"] = ("BF16", [H])
+    for i in range(cfg.n_layers):
+        lp = P + "layers.%d." % i
+        inv[lp + "input_layernorm.weight"] = ("BF16", [H])
+        inv[lp + "post_attention_layernorm.weight"] = ("BF16", [H])
+        if (i + 1) % cfg.full_attn_interval != 0:
+            a = lp + "linear_attn."
+            lin = Q4K if pub else A8
+            mod(a + "in_proj_qkv", lin, D, H)
+            mod(a + "in_proj_z", lin, VD, H)
+            mod(a + "out_proj", lin, H, VD)
+            mod(a + "in_proj_a", BF16, cfg.gdn_v_heads, H)
+            mod(a + "in_proj_b", BF16, cfg.gdn_v_heads, H)
+            inv[a + "conv1d.weight"] = ("BF16", [D, cfg.gdn_conv_kernel, 1])
+            inv[a + "dt_bias"] = ("BF16", [cfg.gdn_v_heads])
+            inv[a + "A_log"] = ("BF16", [cfg.gdn_v_heads])
+            inv[a + "norm.weight"] = ("BF16", [cfg.gdn_head_dim])
+        else:
+            a = lp + "self_attn."
+            att = Q6K if pub else A8
+            mod(a + "q_proj", att, 2 * QD, H)
+            mod(a + "k_proj", att, KVD, H)
+            mod(a + "v_proj", att, KVD, H)
+            mod(a + "o_proj", att, H, QD)
+            inv[a + "q_norm.weight"] = ("BF16", [cfg.head_dim])
+            inv[a + "k_norm.weight"] = ("BF16", [cfg.head_dim])
+        m = lp + "mlp."
+        late = i >= 32   # the artifact's 8-bit side: layers 32..39
+        if pub:
+            router, gu, dn, sgu, sdn = Q6K, (Q6K if late else Q4K), (Q6K if late else Q4K), (Q6K if late else A4), (Q6K if late else A4)
+        else:
+            router, gu, dn, sgu, sdn = A8, Q4K, Q6K, Q4K, Q6K
+        mod(m + "gate", router, E, H)
+        mod(m + "switch_mlp.gate_proj", gu, I, H, (E,))
+        mod(m + "switch_mlp.up_proj", gu, I, H, (E,))
+        mod(m + "switch_mlp.down_proj", dn, H, I, (E,))
+        mod(m + "shared_expert.gate_proj", sgu, SI, H)
+        mod(m + "shared_expert.up_proj", sgu, SI, H)
+        mod(m + "shared_expert.down_proj", sdn, H, SI)
+        mod(m + "shared_expert_gate", A8, 1, H)
+    return inv

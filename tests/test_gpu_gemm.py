@@ -23,7 +23,7 @@ def lin_of(pkg, ctx, W):
     return pkg.Linear.from_numpy(ctx, W.kind, W.w, W.s, W.b, E=W.E, O=W.O, K=W.K)
 
 
-@pytest.mark.parametrize("kind", [orc.Q4K, orc.Q6K, orc.A8, orc.BF16])
+@pytest.mark.parametrize("kind", [orc.Q4K, orc.Q6K, orc.A8, orc.BF16, orc.A4])
 @pytest.mark.parametrize("M,O,K", [(16, 512, 2048), (100, 2048, 512), (300, 200, 1024), (37, 128, 256)])
 def test_gemm_matches_oracle_matvec(pkg, ctx, kind, M, O, K):
     """Row counts on and off the tile widths (16, 100, 300, 37: the reference's partial-tile

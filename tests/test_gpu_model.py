@@ -152,6 +152,72 @@ def test_load_from_safetensors_artifact(pkg, ctx, tiny, tmp_path):
         pkg.TextModel.load(ctx, d, max_ctx=cfg.max_ctx)
 
 
+def test_published_mix_loads_through_the_quantization_block(pkg, ctx, tmp_path):
+    """The module formats of the reference's q6k-full artifact (tools/forge_q4k.py:131-152): Q4_K
+    gated-delta projections, lm_head and routed experts (down included), Q6_K attention and
+    routers, affine 4-bit group-32 shared experts, 8-bit affine embedding and shared-expert gates.
+    config.json's `quantization` block names each module's mode (src/weights.rs:49-79,179-184): the
+    default is affine 4-bit group 32, every other module is an override.  The MoE blocks fall out
+    of the fused kernels' formats and run one kernel per op; tokens equal the oracle's."""
+    cfg = hp.tiny_config(pkg.Config)
+    W = hp.tiny_model_weights(cfg, seed=8, mix="published")
+    kinds = {w.kind for w in W.values() if isinstance(w, orc.Weights)}
+    assert kinds == {orc.Q4K, orc.Q6K, orc.A8, orc.A4, orc.BF16}
+    om = orc.Model(cfg, W)
+    d = hp.write_artifact(str(tmp_path / "published"), cfg, W, quant_block=True)
+    lm = pkg.TextModel.load(ctx, d, max_ctx=cfg.max_ctx)
+    assert lm.get_linear("layers.0.mlp.shared_expert.up_proj").kind == pkg.A4
+    assert lm.get_linear("layers.0.mlp.gate").kind == pkg.Q6K
+    assert lm.get_linear("layers.0.mlp.switch_mlp.down_proj").kind == pkg.Q4K
+    prompt = np.array([11, 4, 1300, 77, 5, 900], np.uint32)
+    ref = om.generate(prompt, 14)
+    c = lm.make_cache()
+    assert pkg.generate_step(lm, c, prompt, 14) == ref
+    c.reset()
+    got, st = pkg.generate_step_mtp(lm, c, prompt, 1, 14, force=(ref, 0.5, 2))
+    rref, rst = om.generate_mtp(prompt, 1, 14, force=(ref, 0.5, 2))
+    assert got == ref == rref and (st.cycles, st.accepted) == (rst.cycles, rst.accepted)
+    # a long prompt takes the wide path: every format through the tensor-core product
+    c.reset()
+    long_ids = np.random.default_rng(1).integers(0, cfg.vocab, 70).astype(np.uint32)
+    h = lm.prefill(c, long_ids, want_hidden=True).numpy()
+    assert c.offset == 70 and np.isfinite(hp.bf16_to_f32(h)).all()
+    c.free()
+    lm.free()
+    om.free()
+    # a module whose tensors disagree with the block is refused at load
+    import json
+    cj = json.load(open(d + "/config.json"))
+    cj["quantization"]["language_model.model.layers.0.mlp.gate"] = {"mode": "affine", "group_size": 64, "bits": 8}
+    json.dump(cj, open(d + "/config.json", "w"))
+    with pytest.raises(pkg.OrnError, match="affine module"):
+        pkg.TextModel.load(ctx, d, max_ctx=cfg.max_ctx)
+    cj["quantization"]["language_model.model.layers.0.mlp.gate"] = {"mode": "nvfp4", "group_size": 16, "bits": 4}
+    json.dump(cj, open(d + "/config.json", "w"))
+    with pytest.raises(pkg.OrnError, match="not on this path"):
+        pkg.TextModel.load(ctx, d, max_ctx=cfg.max_ctx)
+
+
+def test_truncated_tensor_is_refused(pkg, ctx, tmp_path):
+    """A safetensors header whose shape asks for more bytes than data_offsets hold is an error at
+    load, not a read past the mapping."""
+    import json
+    cfg = hp.tiny_config(pkg.Config)
+    W = hp.tiny_model_weights(cfg, seed=5)
+    d = hp.write_artifact(str(tmp_path / "trunc"), cfg, W)
+    path = d + "/model-00001-of-00002.safetensors"
+    raw = open(path, "rb").read()
+    n = int.from_bytes(raw[:8], "little")
+    hdr = json.loads(raw[8:8 + n])
+    name = next(k for k, v in hdr.items() if v["dtype"] == "BF16" and len(v["shape"]) == 1)
+    hdr[name]["shape"] = [hdr[name]["shape"][0] * 4]   # claims four times the bytes it has
+    hj = json.dumps(hdr).encode()
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    open(path, "wb").write(len(hj).to_bytes(8, "little") + hj + raw[8 + n:])
+    with pytest.raises(pkg.OrnError, match="do not match"):
+        pkg.TextModel.load(ctx, d, max_ctx=cfg.max_ctx)
+
+
 def test_full_size_layers_mtp_equals_autoregressive(pkg, ctx):
     """Real layer dimensions (hidden 2048, 256 experts top-8, 16/2 heads, vocab
     248320) at 4 layers, random-init on the GPU: speculative output is

@@ -35,7 +35,7 @@ def test_config1_q4k_matvec(pkg, ctx):
     assert np.median(hp.rel_err(y, r64)) < 1e-4
 
 
-@pytest.mark.parametrize("kind", [orc.Q4K, orc.Q6K, orc.A8, orc.BF16])
+@pytest.mark.parametrize("kind", [orc.Q4K, orc.Q6K, orc.A8, orc.BF16, orc.A4])
 @pytest.mark.parametrize("O,K", [(37, 512), (100, 2048), (256, 4096), (1, 2048), (64, 256)])
 def test_gemv_bit_exact_all_widths(pkg, ctx, kind, O, K):
     rng = np.random.default_rng(O * 7 + K + kind)
@@ -60,7 +60,8 @@ def test_gemv_bit_exact_all_widths(pkg, ctx, kind, O, K):
     L.free()
 
 
-@pytest.mark.parametrize("kind,O,K", [(orc.Q4K, 512, 2048), (orc.Q6K, 2048, 512), (orc.BF16, 64, 512), (orc.A8, 40, 256)])
+@pytest.mark.parametrize("kind,O,K", [(orc.Q4K, 512, 2048), (orc.Q6K, 2048, 512), (orc.BF16, 64, 512), (orc.A8, 40, 256),
+                                       (orc.A4, 48, 512)])
 def test_gather_gemv(pkg, ctx, kind, O, K):
     """Routed rows: 11 rows over 4 experts, unsorted (tools/dump_q4k.py:177-199 shapes)."""
     rng = np.random.default_rng(kind + 3)

@@ -1,4 +1,4 @@
-"""The prompt path: chunks of 16 rows or more run through the wide tensor-core products
+"""The prompt path: chunks of 64 rows or more run through the wide tensor-core products
 (orn_gemm / the grouped expert product), shorter chunks through the row-invariant 4-row windows.
 The reference exempts prefill from row invariance (src/generate.rs:99).  The chunk plumbing is
 checked bit for bit with exact products in tests/test_gpu_fullwidth.py; here the tensor-core
@@ -24,18 +24,18 @@ def row_errors(got, want):
 
 @pytest.mark.parametrize("interval,what", [(4, "gated-delta layer"), (1, "attention layer")])
 def test_one_layer_hidden_rows_within_rounding(pkg, ctx, interval, what):
-    """One layer (mixer + MoE) on 45 rows: the typical row differs from the row-invariant path by
+    """One layer (mixer + MoE) on 70 rows: the typical row differs from the row-invariant path by
     a couple of bfloat16 steps of its largest value (<= 2e-2); rows whose routing flipped may
     differ more and are few."""
     cfg = hp.tiny_config(pkg.Config, max_ctx=160, n_layers=1, full_attn_interval=interval)
     W = hp.tiny_model_weights(cfg, seed=5)
     gm = hp.upload_model(pkg, ctx, cfg, W)
-    ids = np.random.default_rng(4).integers(0, cfg.vocab, 45).astype(np.uint32)
+    ids = np.random.default_rng(4).integers(0, cfg.vocab, 70).astype(np.uint32)
     c = gm.make_cache()
     narrow = gm.prefill(c, ids, prefill_step=8, want_hidden=True).numpy()
     c.reset()
     wide = gm.prefill(c, ids, prefill_step=2048, want_hidden=True).numpy()
-    assert c.offset == 45
+    assert c.offset == 70
     rel, cos = row_errors(wide, narrow)
     assert np.median(rel) <= 2e-2, np.median(rel)
     assert (rel > 5e-2).mean() <= 0.1
@@ -50,24 +50,24 @@ def test_wide_prefill_and_generation_on_the_tiny_model(pkg, ctx):
     om = orc.Model(cfg, W)
     gm = hp.upload_model(pkg, ctx, cfg, W)
     rng = np.random.default_rng(4)
-    ids = rng.integers(0, cfg.vocab, 45).astype(np.uint32)
+    ids = rng.integers(0, cfg.vocab, 70).astype(np.uint32)
     oc = om.new_cache()
-    ref = np.concatenate([om.forward(oc, ids[a:a + 4]) for a in range(0, 45, 4)])
+    ref = np.concatenate([om.forward(oc, ids[a:a + 4]) for a in range(0, 70, 4)])
     om.free_cache(oc)
     c = gm.make_cache()
     narrow = gm.prefill(c, ids, prefill_step=8, want_hidden=True).numpy()   # 8-row chunks: 4-row windows
     assert np.array_equal(narrow, ref)                                       # the row-invariant path is the oracle's
-    for step in (2048, 16):   # one 45-row chunk; chunks of 16, 16 and 13 rows (the last one in windows)
+    for step in (2048, 64):   # one 70-row chunk; a 64-row chunk and a 6-row one (the last in windows)
         c.reset()
         wide = gm.prefill(c, ids, prefill_step=step, want_hidden=True).numpy()
-        assert c.offset == 45
+        assert c.offset == 70
         rel, cos = row_errors(wide, ref)
         assert np.median(cos) >= 0.97, (step, np.median(cos))
     # the decode loop on the caches a wide prefill left: speculative output equals the engine's own
     # autoregressive output, whatever the prompt arithmetic was
-    prompt = ids[:40]
+    prompt = ids[:66]
     c.reset()
-    ar = pkg.generate_step(gm, c, prompt, 24)                       # 39-row prompt chunk: wide
+    ar = pkg.generate_step(gm, c, prompt, 24)                       # 65-row prompt chunk: wide
     c.reset()
     got, st = pkg.generate_step_mtp(gm, c, prompt, 1, 24, force=(ar, 0.5, 3))
     assert got == ar
