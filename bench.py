@@ -441,6 +441,76 @@ def long_prefill(pkg, ctx, model, cache, cfg):
             "reference_published_s": 4.22, "reference_hardware": "Apple M4 Max (the reference's own figure, other hardware)"}
 
 
+EP_ROWS = 128  # BASELINE config 5's decode width: 64 sequences x verify width 2
+
+
+def ep_moe_layer(pkg, ctx, dist, rank, world, exact=False, steps=30, warmup=5):
+    """BASELINE config 5's per-layer exchange, run by every rank of the job: one expert-parallel
+    MoE decode layer through the library's own block (orn_ep_moe_block): 128 rows in all, split
+    evenly over the ranks; 256 experts top-8 (Q4_K gate/up, Q6_K down) split 256 / N per rank;
+    router, shared expert and its gate replicated.  The total work is fixed (strong scaling).
+    `checksum` sums every output element's bits over all ranks: the same number at every N, because
+    every product is the row-invariant mat-vec and the combine runs at the row's home."""
+    from ornith_rs_b200 import ep
+    H, E, I, k = 2048, 256, 512, 8
+    if EP_ROWS % world or E % world:
+        return None
+    Rr = EP_ROWS // world
+    kinds = {"gate": (pkg.A8, 1, E, H), "sw_gate": (pkg.Q4K, E, I, H), "sw_up": (pkg.Q4K, E, I, H),
+             "sw_down": (pkg.Q6K, E, H, I), "sh_gate": (pkg.Q4K, 1, I, H), "sh_up": (pkg.Q4K, 1, I, H),
+             "sh_down": (pkg.Q6K, 1, H, I), "sh_egate": (pkg.A8, 1, 1, H)}
+    L = {}
+    for i, (name, (kind, e, o, kk)) in enumerate(kinds.items()):
+        full = pkg.Linear.random(ctx, kind, e, o, kk, SEED + 100 + i)     # the same tensor on every rank
+        if name.startswith("sw_") and world > 1:
+            L[name] = ep.shard_experts(ctx, full, rank, world)
+            full.free()
+        else:
+            L[name] = full
+    uid = None
+    if world > 1:
+        box = [ep.LibEp.unique_id(ctx._lib) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        uid = box[0]
+    group = ep.LibEp(ctx, rank, world, uid, exact=exact)
+    rng = np.random.default_rng(SEED + 7)
+    x_all = (rng.standard_normal((EP_ROWS, H)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    x = ctx.upload(x_all[rank * Rr:(rank + 1) * Rr])
+    out = ctx.empty((Rr, H), np.uint16)
+    for _ in range(warmup):
+        group.moe_block(L, x, Rr, k, 1, out=out)
+    ctx.sync()
+    if dist is not None:
+        dist.barrier()
+    l0 = ctx.launches()
+    ctx.timer_start()
+    for _ in range(steps):
+        group.moe_block(L, x, Rr, k, 1, out=out)
+    ms = ctx.timer_stop() / steps
+    launches = (ctx.launches() - l0) // steps
+    check = int(out.numpy().astype(np.int64).sum())
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms, float(check)], dtype=torch.float64, device="cuda")
+        mx = t.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, check = float(mx[0]), int(t[1])
+    group.close()
+    for l in L.values():
+        l.free()
+    peak, which = peaks()
+    expert = 2 * I * H * 0.5625 + H * I * 0.8203125
+    per_gpu = (E // world) * expert + expert + E * H * 1.0625 + H * 1.0625 + 3 * Rr * H * 2
+    return {"rows": EP_ROWS, "rows_per_rank": Rr, "experts_per_rank": E // world, "ms_per_layer": ms,
+            "rows_per_s": EP_ROWS / (ms * 1e-3), "bytes_per_gpu": per_gpu, "frac": per_gpu / (ms * 1e-3) / 1e9 / peak,
+            "peak_source": which, "launches_per_layer": int(launches), "checksum": check,
+            "routed_experts": "grouped row-invariant mat-vec (bits of the single-GPU block)" if exact
+                              else "grouped tensor-core product (tcgen05), routing and combine row-invariant",
+            "collectives": "all-gather of routing indices and rows, all-to-all of fixed return blocks (NCCL, library stream)"
+                           if world > 1 else "none (one rank)"}
+
+
 def oracle_check(pkg, ctx):
     """The decode loop's integers against the CPU oracle on a 4-layer full-width model (the
     oracle is the checker here): emitted ids and accepted count at the benchmark's p."""
@@ -542,6 +612,9 @@ def ours(args):
 
     dev_ms, walls = reduce_max_over_ranks([dev_ms, walls], dist, "cuda")
     value, e2e = whole_job_rates(world, args.steps, GEN_TOKENS, dev_ms, walls)
+    epl = ep_moe_layer(pkg, ctx, dist, rank, world)   # every rank takes part
+    if epl is not None:
+        epl["row_invariant_variant"] = ep_moe_layer(pkg, ctx, dist, rank, world, exact=True)
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -579,7 +652,7 @@ def ours(args):
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": PROMPT_LEN * 4,
                 "d2h_bytes_per_step": int(16 * cycles / args.steps) + 4},
         "gpu_launches": launches, "clocks": clocks, "roofline": roof, "step_roofline": step_roof,
-        "kernels": kt[:12], "isolated_in_proj_launch": iso, "prefill_6621": lp,
+        "kernels": kt[:12], "isolated_in_proj_launch": iso, "prefill_6621": lp, "ep_moe_layer": epl,
         "acceptance": accepted / max(cycles, 1), "tokens_per_cycle": args.steps * GEN_TOKENS / max(cycles, 1),
         "mtp_equals_autoregressive": True, "prefill_ms_per_step": prefill_ms / args.steps,
     }

@@ -51,6 +51,7 @@ typedef struct orn_ctx orn_ctx;
 typedef struct orn_linear orn_linear;
 typedef struct orn_model orn_model;
 typedef struct orn_cache orn_cache;
+typedef struct orn_ep orn_ep;
 
 /* model dimensions (src/model/config.rs:9-158) */
 typedef struct {
@@ -211,6 +212,33 @@ int32_t orn_moe_block(orn_ctx* ctx, const orn_linear* gate, const orn_linear* sw
                       const orn_linear* sh_down, const orn_linear* sh_egate,
                       const uint16_t* dev_x, int32_t T, int32_t top_k, int32_t norm_topk,
                       uint16_t* dev_out, uint32_t* dev_inds_out /*nullable*/);
+
+/* ---- expert parallelism over the GPUs of one node (no counterpart in the reference, which is
+ * single-GPU, README.md:217-221; the block it distributes is sparse_moe_block, moe.rs:662-741,
+ * and the owner's work is the sorted expert path, moe.rs:283-314,463-508).  Experts are split
+ * evenly: expert e lives on rank e / (E / world).  One process per GPU; the collectives are NCCL
+ * calls on the context's stream (libnccl.so.2 is resolved at run time; world == 1 needs none).
+ * orn_ep_unique_id: rank 0 makes the 128-byte NCCL id, the caller carries it to the other ranks.
+ * orn_ep_init: collective over all ranks.  orn_ep_moe_block: collective; R rows per rank (the same
+ * R everywhere); gate, the shared expert and its gate are replicated, sw_* hold this rank's
+ * E / world experts.  Nothing is read back to the host inside the block.  Routing, the shared
+ * expert and the combine always run the row-invariant arithmetic at the row's home (routing
+ * indices equal the single-GPU block's bit for bit).  The routed experts run as grouped products on
+ * the tensor cores (a decode batch of many sequences is a dense contraction per expert; results
+ * agree with the single-GPU block to rounding), or, with ORN_EP_EXACT, through the grouped
+ * row-invariant mat-vec (every output bit equals the single-GPU block's).  Either way a row's
+ * result does not depend on which rows share its tile, so the output bits do not depend on world. */
+int32_t orn_ep_unique_id(uint8_t* id_out /*128 bytes*/);
+#define ORN_EP_EXACT 1 /* flags: routed experts through the row-invariant grouped mat-vec too */
+int32_t orn_ep_init(orn_ctx* ctx, const uint8_t* id /*128 bytes; NULL when world == 1*/, int32_t rank,
+                    int32_t world, int32_t flags, orn_ep** out);
+int32_t orn_ep_destroy(orn_ep* ep);
+int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* sw_gate,
+                         const orn_linear* sw_up, const orn_linear* sw_down,
+                         const orn_linear* sh_gate, const orn_linear* sh_up,
+                         const orn_linear* sh_down, const orn_linear* sh_egate,
+                         const uint16_t* dev_x, int32_t R, int32_t top_k, int32_t norm_topk,
+                         uint16_t* dev_out, uint32_t* dev_inds_out /*nullable*/);
 
 /* ---- gated delta net (src/ops/gdn.rs:191-413) */
 int32_t orn_gdn_front(orn_ctx* ctx, const uint16_t* dev_conv_state, const uint16_t* dev_qkv,

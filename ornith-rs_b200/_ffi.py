@@ -93,6 +93,10 @@ SIGNATURES = {
     "orn_router_topk": (i32, [vp, vp, i32, i32, i32, vp, vp]),
     "orn_moe_combine": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "orn_moe_block": (i32, [vp] + [vp] * 8 + [vp, i32, i32, i32, vp, vp]),
+    "orn_ep_unique_id": (i32, [vp]),
+    "orn_ep_init": (i32, [vp, vp, i32, i32, i32, c_void_pp]),
+    "orn_ep_destroy": (i32, [vp]),
+    "orn_ep_moe_block": (i32, [vp] + [vp] * 8 + [vp, i32, i32, i32, vp, vp]),
     "orn_gdn_front": (i32, [vp] + [vp] * 7 + [i32] * 5 + [f32] + [vp] * 6),
     "orn_gated_delta": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "orn_rope": (i32, [vp, vp, i32, i32, i32, i32, f32, i32]),

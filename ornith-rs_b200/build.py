@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libornith_cuda.so")
-SOURCES = ["api.cu", "linear.cu", "ops.cu", "gdn.cu", "attn.cu", "sample.cu", "model.cu", "loader.cu", "fused.cu", "gemm.cu"]
+SOURCES = ["api.cu", "linear.cu", "ops.cu", "gdn.cu", "attn.cu", "sample.cu", "model.cu", "loader.cu", "fused.cu", "gemm.cu", "ep.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -53,7 +53,7 @@ def build(verbose=False):
         with open(os.path.join(OBJ, "ptxas.log"), "a") as f:
             f.write(log)
     if (not os.path.exists(LIB)) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
-        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lcudart"]
+        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lcudart", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))

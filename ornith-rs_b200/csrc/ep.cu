@@ -1,0 +1,330 @@
+// Expert-parallel sparse MoE block: the 256 experts are split evenly over the ranks of one node
+// (expert e lives on rank e / (E / world)), token rows stay with the rank that owns their
+// sequence, and one layer costs two small collectives each way over NVLink (NCCL, stream-ordered
+// on the context's stream; no peer pointers, no multicast loads).
+//
+// The reference is single-GPU (README.md:217-221); what it has is the block this distributes,
+// sparse_moe_block (src/ops/moe.rs:662-741), and the building block an expert owner needs: rows
+// counting-sorted by expert and each expert run once over its rows (counting_sort +
+// switch_glu_rows, src/ops/moe.rs:283-314,463-508, kernels/moe.metal:329-462).
+//
+// One call, R local rows, nothing read back to the host in between:
+//   home   router mat-vec, precise softmax, top-k; shared expert and its gate
+//   all    all-gather of the [R, k] routing indices and of the [R, H] rows: every rank then holds
+//          the whole table and derives, on the device, which routes are its own
+//   owner  routes whose expert it owns, counting-sorted by expert; gate / up / SwiGLU / down with
+//          the grouped mat-vec (an expert's records are streamed once for all its rows, every
+//          row with the one-row arithmetic); results written straight into the return block of
+//          the row's home rank
+//   all    all-to-all of fixed-size return blocks [R * k, H] (slots a rank does not own are not
+//          read by the receiver, so no counts travel and no host round trip is needed)
+//   home   each route's row picked from its owner's block, moe_combine in the reference's
+//          ascending-slot bfloat16 order, shared expert added
+// Every product runs the row-invariant arithmetic of the single-GPU path and the combine runs at
+// home in the reference's order, so the output bits do not depend on the number of ranks.
+//
+// NCCL is resolved at run time (dlopen of libnccl.so.2: the copy already in the process when the
+// host program has one, else the system's), so the library has no link-time dependency on it and
+// a single-rank block needs no NCCL at all.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <type_traits>
+
+#include "fused.h"
+#include "orn_internal.h"
+
+namespace {
+
+struct NcclApi {
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*);
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+  ncclResult_t (*CommDestroy)(ncclComm_t);
+  ncclResult_t (*GroupStart)();
+  ncclResult_t (*GroupEnd)();
+  ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+  ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+  const char* (*GetErrorString)(ncclResult_t);
+};
+
+NcclApi* nccl_api(std::string* why) {
+  static NcclApi api;
+  static bool ok = false;
+  static std::string err;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (h == nullptr) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (h == nullptr) { err = std::string("cannot load libnccl.so.2: ") + dlerror(); return; }
+    bool all = true;
+    auto sym = [&](const char* n) { void* p = dlsym(h, n); if (!p) { all = false; err = std::string("libnccl lacks ") + n; } return p; };
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+    api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+    api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
+    api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
+    api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+    ok = all;
+  });
+  if (!ok && why) *why = err;
+  return ok ? &api : nullptr;
+}
+
+// routes of every rank -> this rank's local expert index, or "not mine"
+__global__ void ep_map_kernel(const uint32_t* all_inds, int routes, int base, int e_local, uint32_t* rhs_local) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= routes) return;
+  const int e = (int)all_inds[i] - base;
+  rhs_local[i] = (e >= 0 && e < e_local) ? (uint32_t)e : 0xFFFFFFFFu;
+}
+// lhs[i] = i / k: the row a route belongs to
+__global__ void ep_iota_kernel(uint32_t* lhs, int n, int k) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) lhs[i] = (uint32_t)(i / k);
+}
+// xs[p] = x[lhs[perm[p]]] for the p < *n_rows sorted rows this rank owns
+__global__ void ep_gather_kernel(const bf16_t* x, const uint32_t* lhs, const uint32_t* perm, const int* n_rows, int K,
+                                 bf16_t* xs) {
+  const int p = blockIdx.x;
+  if (p >= *n_rows) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)lhs[perm[p]] * K);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)p * K);
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+}
+// SwiGLU of the owned sorted rows only
+__global__ void ep_swiglu_kernel(const bf16_t* g, const bf16_t* u, const int* n_rows, int I, bf16_t* out) {
+  const size_t n = (size_t)(*n_rows) * I;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = f2bf(orn_swiglu_bf(bf2f(g[i]), bf2f(u[i])));
+}
+// home: route j's row comes from the block its owner sent
+__global__ void ep_select_kernel(const bf16_t* recv, const uint32_t* inds, int e_local, int blk_rows, int H, bf16_t* ey) {
+  const int j = blockIdx.x;
+  const int owner = (int)inds[j] / e_local;
+  const uint4* src = reinterpret_cast<const uint4*>(recv + ((size_t)owner * blk_rows + j) * H);
+  uint4* dst = reinterpret_cast<uint4*>(ey + (size_t)j * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+}  // namespace
+
+struct orn_ep {
+  orn_ctx* ctx = nullptr;
+  int rank = 0, world = 1;
+  bool exact = false;  // routed experts through the row-invariant grouped mat-vec instead of the tensor cores
+  void* gemm_scratch = nullptr;
+  ncclComm_t comm = nullptr;
+  // scratch for one shape (R, H, E, k, I, SI); rebuilt when a call asks for a larger one
+  size_t cap_key[6] = {0, 0, 0, 0, 0, 0};
+  std::vector<void*> allocs;
+  bf16_t *gates, *probs, *scores, *sg, *su, *sact, *sy, *gs, *all_x, *xs, *eg, *eu, *eact, *ret_send, *ret_recv, *ey;
+  uint32_t *inds, *all_inds, *rhs_local, *lhs, *perm;
+  int *seg, *seg1;
+};
+
+namespace {
+
+int ep_reserve(orn_ep* ep, int R, int H, int E, int k, int I, int SI) {
+  const size_t key[6] = {(size_t)R, (size_t)H, (size_t)E, (size_t)k, (size_t)I, (size_t)SI};
+  bool fits = true;
+  for (int i = 0; i < 6; ++i) fits = fits && key[i] == ep->cap_key[i];
+  if (fits) return ORN_OK;
+  orn_ctx* ctx = ep->ctx;
+  ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (void* p : ep->allocs) cudaFree(p);
+  ep->allocs.clear();
+  for (int i = 0; i < 6; ++i) ep->cap_key[i] = 0;
+  const size_t W = ep->world, G = W * R, routes = G * k, el = (size_t)E / W;
+  int rc = ORN_OK;
+  auto A = [&](auto** p, size_t n) {
+    if (rc != ORN_OK) return;
+    void* d = nullptr;
+    rc = orn_alloc(ctx, sizeof(**p) * (n ? n : 1), &d);
+    if (rc == ORN_OK) { ep->allocs.push_back(d); *p = (std::remove_reference_t<decltype(**p)>*)d; }
+  };
+  A(&ep->gates, (size_t)R * E); A(&ep->probs, (size_t)R * E); A(&ep->scores, (size_t)R * k); A(&ep->inds, (size_t)R * k);
+  A(&ep->sg, (size_t)R * SI); A(&ep->su, (size_t)R * SI); A(&ep->sact, (size_t)R * SI); A(&ep->sy, (size_t)R * H); A(&ep->gs, (size_t)R);
+  A(&ep->all_inds, routes); A(&ep->all_x, G * H); A(&ep->rhs_local, routes); A(&ep->lhs, routes); A(&ep->perm, routes);
+  A(&ep->seg, 2 * el + 4); A(&ep->seg1, (size_t)2);
+  A(&ep->xs, routes * H); A(&ep->eg, routes * I); A(&ep->eu, routes * I); A(&ep->eact, routes * I);
+  A(&ep->ret_send, routes * H); A(&ep->ret_recv, routes * H); A(&ep->ey, (size_t)R * k * H);
+  if (rc == ORN_OK) {
+    const size_t big = std::max(qgemm_scratch_bytes((int)routes, (int)el, H), qgemm_scratch_bytes((int)routes, (int)el, I));
+    rc = orn_alloc(ctx, big, &ep->gemm_scratch);
+    if (rc == ORN_OK) ep->allocs.push_back(ep->gemm_scratch);
+  }
+  if (rc != ORN_OK) {
+    for (void* p : ep->allocs) cudaFree(p);
+    ep->allocs.clear();
+    return rc;
+  }
+  const int seg1[2] = {0, R};
+  rc = orn_upload(ctx, ep->seg1, seg1, sizeof seg1);
+  if (rc != ORN_OK) return rc;
+  ep_iota_kernel<<<(unsigned)((routes + 255) / 256), 256, 0, ctx->stream>>>(ep->lhs, (int)routes, k);
+  rc = orn_launch_check(ctx, "ep_iota");
+  if (rc != ORN_OK) return rc;
+  for (int i = 0; i < 6; ++i) ep->cap_key[i] = key[i];
+  return ORN_OK;
+}
+
+#define EP_NCCL(ctx, api, call)                                                              \
+  do {                                                                                       \
+    ncclResult_t r__ = (call);                                                               \
+    if (r__ != ncclSuccess) {                                                                \
+      (ctx)->err = std::string(#call) + ": " + (api)->GetErrorString(r__);                   \
+      return ORN_ERR_CUDA;                                                                   \
+    }                                                                                        \
+  } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int32_t orn_ep_unique_id(uint8_t* id_out) {
+  if (!id_out) return ORN_ERR_ARG;
+  static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+  std::string why;
+  NcclApi* api = nccl_api(&why);
+  if (!api) return ORN_ERR_STATE;
+  ncclUniqueId id;
+  if (api->GetUniqueId(&id) != ncclSuccess) return ORN_ERR_CUDA;
+  memcpy(id_out, &id, sizeof id);
+  return ORN_OK;
+}
+
+int32_t orn_ep_init(orn_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world, int32_t flags, orn_ep** out) {
+  if (!ctx || !out || world < 1 || rank < 0 || rank >= world) return ORN_ERR_ARG;
+  *out = nullptr;
+  orn_ep* ep = new orn_ep();
+  ep->ctx = ctx; ep->rank = rank; ep->world = world;
+  ep->exact = (flags & ORN_EP_EXACT) != 0;
+  if (world > 1) {
+    if (!id) { delete ep; ORN_FAIL(ctx, ORN_ERR_ARG, "ep_init: more than one rank needs the unique id of rank 0"); }
+    std::string why;
+    NcclApi* api = nccl_api(&why);
+    if (!api) { delete ep; ORN_FAIL(ctx, ORN_ERR_STATE, "ep_init: " + why); }
+    ncclUniqueId uid;
+    memcpy(&uid, id, sizeof uid);
+    cudaSetDevice(ctx->device);
+    ncclResult_t r = api->CommInitRank(&ep->comm, world, uid, rank);
+    if (r != ncclSuccess) {
+      delete ep;
+      ORN_FAIL(ctx, ORN_ERR_CUDA, std::string("ncclCommInitRank: ") + api->GetErrorString(r));
+    }
+  }
+  *out = ep;
+  return ORN_OK;
+}
+
+int32_t orn_ep_destroy(orn_ep* ep) {
+  if (!ep) return ORN_OK;
+  cudaStreamSynchronize(ep->ctx->stream);
+  if (ep->comm) {
+    NcclApi* api = nccl_api(nullptr);
+    if (api) api->CommDestroy(ep->comm);
+  }
+  for (void* p : ep->allocs) cudaFree(p);
+  delete ep;
+  return ORN_OK;
+}
+
+int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* sw_gate, const orn_linear* sw_up,
+                         const orn_linear* sw_down, const orn_linear* sh_gate, const orn_linear* sh_up,
+                         const orn_linear* sh_down, const orn_linear* sh_egate, const uint16_t* dev_x, int32_t R,
+                         int32_t top_k, int32_t norm_topk, uint16_t* dev_out, uint32_t* dev_inds_out) {
+  if (!ep || !gate || !sw_gate || !sw_up || !sw_down || !sh_gate || !sh_up || !sh_down || !sh_egate || !dev_x || !dev_out)
+    return ORN_ERR_ARG;
+  orn_ctx* ctx = ep->ctx;
+  cudaStream_t s = ctx->stream;
+  const int W = ep->world, H = gate->K, E = gate->O, I = sw_gate->O, SI = sh_gate->O, k = top_k;
+  if (R < 1 || k < 1 || k > E) ORN_FAIL(ctx, ORN_ERR_ARG, "ep_moe_block: bad row count or top_k");
+  if (E % W) ORN_FAIL(ctx, ORN_ERR_ARG, "ep_moe_block: the experts do not split evenly over the ranks");
+  const int el = E / W;
+  if (sw_gate->E != el || sw_up->E != el || sw_down->E != el || sw_gate->K != H || sw_up->K != H || sw_up->O != I ||
+      sw_down->O != H || sw_down->K != I || sh_up->O != SI || sh_gate->K != H || sh_up->K != H || sh_down->O != H ||
+      sh_down->K != SI || sh_egate->O != 1 || sh_egate->K != H || H % 8)
+    ORN_FAIL(ctx, ORN_ERR_ARG, "ep_moe_block: inconsistent weight shapes (routed matrices hold this rank's E / world experts)");
+  int rc = ep_reserve(ep, R, H, E, k, I, SI);
+  if (rc != ORN_OK) return rc;
+  const int G = W * R, routes = G * k, blk = R * k;
+  NcclApi* api = W > 1 ? nccl_api(nullptr) : nullptr;
+  if (W > 1 && !api) ORN_FAIL(ctx, ORN_ERR_STATE, "ep_moe_block: NCCL is not loaded");
+#define EPCK(call) do { int rc__ = (call); if (rc__ != ORN_OK) return rc__; } while (0)
+  // ---- home: routing and the shared expert (one launch per matrix over all R rows)
+  uint32_t* inds = dev_inds_out ? dev_inds_out : ep->inds;
+  EPCK(k_grouped_gemv(ctx, s, gate, dev_x, ep->seg1, ep->gates, nullptr, R));
+  EPCK(k_softmax_precise(ctx, s, ep->gates, R, E, ep->probs));
+  EPCK(k_router_topk(ctx, s, ep->probs, R, E, k, inds, ep->scores));
+  // ---- every rank learns the whole routing table and the rows
+  const uint32_t* all_inds = inds;
+  const bf16_t* all_x = dev_x;
+  if (W > 1) {
+    EP_NCCL(ctx, api, api->GroupStart());
+    EP_NCCL(ctx, api, api->AllGather(inds, ep->all_inds, (size_t)R * k, ncclUint32, ep->comm, s));
+    EP_NCCL(ctx, api, api->AllGather(dev_x, ep->all_x, (size_t)R * H, ncclBfloat16, ep->comm, s));
+    EP_NCCL(ctx, api, api->GroupEnd());
+    ctx->launches += 2;
+    all_inds = ep->all_inds;
+    all_x = ep->all_x;
+  }
+  // the shared expert does not depend on the exchange: it runs while the gathered table lands
+  EPCK(k_grouped_gemv(ctx, s, sh_gate, dev_x, ep->seg1, ep->sg, nullptr, R));
+  EPCK(k_grouped_gemv(ctx, s, sh_up, dev_x, ep->seg1, ep->su, nullptr, R));
+  EPCK(k_grouped_gemv(ctx, s, sh_egate, dev_x, ep->seg1, ep->gs, nullptr, R));
+  EPCK(k_swiglu(ctx, s, ep->sg, ep->su, R * SI, ep->sact));
+  EPCK(k_grouped_gemv(ctx, s, sh_down, ep->sact, ep->seg1, ep->sy, nullptr, R));
+  // ---- owner: this rank's routes, sorted by expert
+  ep_map_kernel<<<(routes + 255) / 256, 256, 0, s>>>(all_inds, routes, ep->rank * el, el, ep->rhs_local);
+  EPCK(orn_launch_check(ctx, "ep_map"));
+  EPCK(f_route_sort(ctx, s, ep->rhs_local, routes, el, ep->seg, ep->seg + el + 1, ep->perm));
+  const int* n_owned = ep->seg + el;  // device: seg[el] = number of routes this rank owns
+  ep_gather_kernel<<<routes, 128, 0, s>>>(all_x, ep->lhs, ep->perm, n_owned, H, ep->xs);
+  EPCK(orn_launch_check(ctx, "ep_gather"));
+  // sorted row p is route perm[p] of the whole table = slot perm[p] of the return blocks laid end to end
+  bf16_t* ret = W > 1 ? ep->ret_send : ep->ey;
+  if (ep->exact) {
+    EPCK(k_grouped_gemv(ctx, s, sw_gate, ep->xs, ep->seg, ep->eg, nullptr, routes));
+    EPCK(k_grouped_gemv(ctx, s, sw_up, ep->xs, ep->seg, ep->eu, nullptr, routes));
+    ep_swiglu_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(ep->eg, ep->eu, n_owned, I, ep->eact);
+    EPCK(orn_launch_check(ctx, "ep_swiglu"));
+    EPCK(k_grouped_gemv(ctx, s, sw_down, ep->eact, ep->seg, ret, ep->perm, routes));
+  } else {
+    // a decode batch of many sequences is a dense contraction per expert: the grouped tensor-core
+    // product (an expert's records dequantised once per tile for all its rows)
+    const int hint = std::max(1, (routes / W) / el);
+    QGemmGroup sorted{ep->seg, nullptr, hint}, back{ep->seg, ep->perm, hint};
+    EPCK(f_qgemm(ctx, s, sw_gate, ep->xs, routes, ep->eg, I, &sorted, ep->gemm_scratch));
+    EPCK(f_qgemm(ctx, s, sw_up, ep->xs, routes, ep->eu, I, &sorted, ep->gemm_scratch));
+    ep_swiglu_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(ep->eg, ep->eu, n_owned, I, ep->eact);
+    EPCK(orn_launch_check(ctx, "ep_swiglu"));
+    EPCK(f_qgemm(ctx, s, sw_down, ep->eact, routes, ret, H, &back, ep->gemm_scratch));
+  }
+  // ---- the return: one fixed-size block per pair of ranks
+  if (W > 1) {
+    const size_t n = (size_t)blk * H;
+    EP_NCCL(ctx, api, api->GroupStart());
+    for (int d = 0; d < W; ++d) {
+      EP_NCCL(ctx, api, api->Send(ep->ret_send + (size_t)d * n, n, ncclBfloat16, d, ep->comm, s));
+      EP_NCCL(ctx, api, api->Recv(ep->ret_recv + (size_t)d * n, n, ncclBfloat16, d, ep->comm, s));
+    }
+    EP_NCCL(ctx, api, api->GroupEnd());
+    ctx->launches += 1;
+    ep_select_kernel<<<blk, 128, 0, s>>>(ep->ret_recv, inds, el, blk, H, ep->ey);
+    EPCK(orn_launch_check(ctx, "ep_select"));
+  }
+  // ---- home: combine in the reference's order
+  EPCK(k_moe_combine(ctx, s, ep->scores, ep->ey, ep->gs, ep->sy, R, k, H, norm_topk, dev_out));
+#undef EPCK
+  return ORN_OK;
+}
+
+}  // extern "C"

@@ -17,12 +17,12 @@
 //     128 x BN float32 in tensor memory (NT * BN <= 512 columns);
 //   - per block of 64 weights along K: one warp's elected lane brings the NT token tiles
 //     [BN, 64] bf16 with TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, this GPU's memory, no
-//     multicast); four warps dequantise the 128 x 64 weight tile from the row records in HBM
+//     multicast); eight warps dequantise the 128 x 64 weight tile from the row records in HBM
 //     straight into shared memory in the same swizzled K-major layout (one thread per feature
 //     row: Q4_K / Q6_K / affine-8 / bf16 -> bf16); another elected lane issues 4 * NT
 //     tcgen05.mma (128 x BN x 16, kind::f16, bf16 inputs, f32 accumulate) and commits the stage
 //     back to the producers;
-//   - the four dequantising warps then read the accumulators (tcgen05.ld, one TMEM lane = one
+//   - the eight dequantising warps then read the accumulators (tcgen05.ld, one TMEM lane = one
 //     feature per thread), round to bfloat16 and store y[token, feature].
 // Stages are a ring guarded by mbarriers; every wait is bounded and reports through the context's
 // device error flag, and the CTA frees its tensor memory on every path.
@@ -46,8 +46,8 @@ namespace {
 
 constexpr int BM = 128;            // features per tile: the tensor core's M
 constexpr int BK = 64;             // weights per K block: one 128-byte swizzle row of bf16
-constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2..5: dequantise + epilogue
-constexpr int kDqWarps = 4;
+constexpr int kGemmThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2..9: dequantise + epilogue
+constexpr int kDqWarps = 8;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWTileBytes = BM * BK * 2;
 constexpr int kMaxStages = 4;
@@ -143,133 +143,154 @@ ORN_D void st_chunk(uint32_t row_addr, int rsw, int c, uint32_t a, uint32_t b, u
                "r"(cc), "r"(d)
                : "memory");
 }
-ORN_D uint32_t pack_bf2(float lo, float hi) { return (uint32_t)f2bf(lo) | ((uint32_t)f2bf(hi) << 16); }
-
-// One feature row, K block kb (64 weights): dequantise to bfloat16 and store the row's 128 bytes.
-template <int KIND>
-ORN_D void dequant_row(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw);
-
-template <>
-ORN_D void dequant_row<ORN_BF16>(const uint8_t* rec, const RecGeom&, int kb, uint32_t row_addr, int rsw) {
-  const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 128);
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const uint4 v = __ldg(src + c);
-    st_chunk(row_addr, rsw, c, v.x, v.y, v.z, v.w);
-  }
+// two floats -> packed bfloat16x2, round to nearest even (lo in the low half)
+ORN_D uint32_t pack_bf2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
 }
+
+// A thread dequantises HALF of one feature row's K block: 32 weights -> 64 bytes of bfloat16 (chunks
+// 4*half .. 4*half+3 of the row).  The raw bytes of the next K block are requested (load) before
+// the current ones are converted (store), so the latency of the row records hides behind arithmetic.
+template <int KIND> struct Raw;
+
+template <> struct Raw<ORN_BF16> {
+  uint4 v[4];
+  ORN_D void load(const uint8_t* rec, const RecGeom&, int kb, int half) {
+    const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 128 + half * 64);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) v[c] = __ldg(src + c);
+  }
+  ORN_D void store(int, int half, uint32_t row_addr, int rsw) const {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) st_chunk(row_addr, rsw, 4 * half + c, v[c].x, v[c].y, v[c].z, v[c].w);
+  }
+};
 
 // affine 8-bit, group 64: w = scale * q + bias (one fma, as the embedding lookup computes it)
-template <>
-ORN_D void dequant_row<ORN_A8>(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw) {
-  const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 64);
-  const uint32_t sb = __ldg(reinterpret_cast<const uint32_t*>(rec + g.b0) + kb);
-  const float sc = bf_lo(sb), bi = bf_hi(sb);
-#pragma unroll
-  for (int h = 0; h < 4; ++h) {
-    const uint4 q = __ldg(src + h);
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    uint32_t o[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      o[2 * i] = pack_bf2(fmaf(sc, byte_f<0>(w[i]), bi), fmaf(sc, byte_f<1>(w[i]), bi));
-      o[2 * i + 1] = pack_bf2(fmaf(sc, byte_f<2>(w[i]), bi), fmaf(sc, byte_f<3>(w[i]), bi));
-    }
-    st_chunk(row_addr, rsw, 2 * h, o[0], o[1], o[2], o[3]);
-    st_chunk(row_addr, rsw, 2 * h + 1, o[4], o[5], o[6], o[7]);
+template <> struct Raw<ORN_A8> {
+  uint4 q[2];
+  uint32_t sb;
+  ORN_D void load(const uint8_t* rec, const RecGeom& g, int kb, int half) {
+    const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 64 + half * 32);
+    q[0] = __ldg(src); q[1] = __ldg(src + 1);
+    sb = __ldg(reinterpret_cast<const uint32_t*>(rec + g.b0) + kb);
   }
-}
-
-// affine 4-bit, group 32: a K block is two groups; byte b holds weights 2b (low nibble), 2b+1 (high)
-template <>
-ORN_D void dequant_row<ORN_A4>(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw) {
-  const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 32);
-  const uint2 sb2 = __ldg(reinterpret_cast<const uint2*>(rec + g.b0) + kb);
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const uint32_t sb = h ? sb2.y : sb2.x;
+  ORN_D void store(int, int half, uint32_t row_addr, int rsw) const {
     const float sc = bf_lo(sb), bi = bf_hi(sb);
-    const uint4 q = __ldg(src + h);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t w[4] = {q[h].x, q[h].y, q[h].z, q[h].w};
+      uint32_t o[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        o[2 * i] = pack_bf2(fmaf(sc, byte_f<0>(w[i]), bi), fmaf(sc, byte_f<1>(w[i]), bi));
+        o[2 * i + 1] = pack_bf2(fmaf(sc, byte_f<2>(w[i]), bi), fmaf(sc, byte_f<3>(w[i]), bi));
+      }
+      st_chunk(row_addr, rsw, 4 * half + 2 * h, o[0], o[1], o[2], o[3]);
+      st_chunk(row_addr, rsw, 4 * half + 2 * h + 1, o[4], o[5], o[6], o[7]);
+    }
+  }
+};
+
+// affine 4-bit, group 32: half a K block is one group; byte b holds weights 2b (low nibble), 2b+1 (high)
+template <> struct Raw<ORN_A4> {
+  uint4 q;
+  uint32_t sb;
+  ORN_D void load(const uint8_t* rec, const RecGeom& g, int kb, int half) {
+    q = __ldg(reinterpret_cast<const uint4*>(rec + (size_t)kb * 32 + half * 16));
+    sb = __ldg(reinterpret_cast<const uint32_t*>(rec + g.b0) + 2 * kb + half);
+  }
+  ORN_D void store(int, int half, uint32_t row_addr, int rsw) const {
+    const float sc = bf_lo(sb), bi = bf_hi(sb);
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
     for (int c = 0; c < 4; ++c) {  // one word = 8 weights = one 16-byte chunk of bfloat16
       const uint32_t l4 = w[c] & 0x0F0F0F0Fu, h4 = (w[c] >> 4) & 0x0F0F0F0Fu;
-      st_chunk(row_addr, rsw, 4 * h + c, pack_bf2(fmaf(sc, byte_f<0>(l4), bi), fmaf(sc, byte_f<0>(h4), bi)),
+      st_chunk(row_addr, rsw, 4 * half + c, pack_bf2(fmaf(sc, byte_f<0>(l4), bi), fmaf(sc, byte_f<0>(h4), bi)),
                pack_bf2(fmaf(sc, byte_f<1>(l4), bi), fmaf(sc, byte_f<1>(h4), bi)),
                pack_bf2(fmaf(sc, byte_f<2>(l4), bi), fmaf(sc, byte_f<2>(h4), bi)),
                pack_bf2(fmaf(sc, byte_f<3>(l4), bi), fmaf(sc, byte_f<3>(h4), bi)));
     }
   }
-}
+};
 
-// Q4_K (kernels/q4k.metal:43-96): 64 weights = 32 code bytes; low nibbles are sub-block 2i, high
-// nibbles sub-block 2i+1; w = (d * sc) * q - (dmin * m)
-template <>
-ORN_D void dequant_row<ORN_Q4K>(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw) {
-  const int b = kb >> 2, i4 = kb & 3;
-  const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(rec + g.b0 + (size_t)b * 16));
-  const float d = h2f((uint16_t)(hdr.x & 0xffff)), dmin = h2f((uint16_t)(hdr.x >> 16));
-  float sc0, m0, sc1, m1;
-  q4k_scale_min(2 * i4, hdr.y, hdr.z, hdr.w, &sc0, &m0);
-  q4k_scale_min(2 * i4 + 1, hdr.y, hdr.z, hdr.w, &sc1, &m1);
-  const float a0 = d * sc0, b0 = dmin * m0, a1 = d * sc1, b1 = dmin * m1;
-  const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)b * 128 + i4 * 32);
-  const uint4 qa = __ldg(src), qb = __ldg(src + 1);
-  const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {  // 8 code bytes -> chunk c (low nibbles) and chunk c + 4 (high nibbles)
-    uint32_t lo[4], hi[4];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const uint32_t l4 = w[2 * c + j] & 0x0F0F0F0Fu, h4 = (w[2 * c + j] >> 4) & 0x0F0F0F0Fu;
-      lo[2 * j] = pack_bf2(a0 * byte_f<0>(l4) - b0, a0 * byte_f<1>(l4) - b0);
-      lo[2 * j + 1] = pack_bf2(a0 * byte_f<2>(l4) - b0, a0 * byte_f<3>(l4) - b0);
-      hi[2 * j] = pack_bf2(a1 * byte_f<0>(h4) - b1, a1 * byte_f<1>(h4) - b1);
-      hi[2 * j + 1] = pack_bf2(a1 * byte_f<2>(h4) - b1, a1 * byte_f<3>(h4) - b1);
-    }
-    st_chunk(row_addr, rsw, c, lo[0], lo[1], lo[2], lo[3]);
-    st_chunk(row_addr, rsw, c + 4, hi[0], hi[1], hi[2], hi[3]);
+// Q4_K (kernels/q4k.metal:43-96): a K block is 32 code bytes; low nibbles are sub-block 2i (the first
+// half of the K block), high nibbles sub-block 2i+1 (the second half); w = (d * sc) * q - dmin * m,
+// evaluated as one fma per weight (this path agrees with the mat-vec to rounding, not bit for bit)
+template <> struct Raw<ORN_Q4K> {
+  uint4 qa, qb, hdr;
+  ORN_D void load(const uint8_t* rec, const RecGeom& g, int kb, int) {
+    const int b = kb >> 2, i4 = kb & 3;
+    const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)b * 128 + i4 * 32);
+    qa = __ldg(src); qb = __ldg(src + 1);
+    hdr = __ldg(reinterpret_cast<const uint4*>(rec + g.b0 + (size_t)b * 16));
   }
-}
-
-// Q6_K (kernels/q6k.metal:47-77): per 128 weights, byte l of ql / qh gives q1 (weight l), q2 (l + 32),
-// q3 (l + 64), q4 (l + 96); a K block of 64 is (q1, q2) or (q3, q4) of one half; w = (d * sc) * (q - 32)
-template <>
-ORN_D void dequant_row<ORN_Q6K>(const uint8_t* rec, const RecGeom& g, int kb, uint32_t row_addr, int rsw) {
-  const int b = kb >> 2, half = (kb >> 1) & 1, hi = kb & 1;
-  const uint8_t* base = rec + (size_t)b * 192;
-  const uint4* ql = reinterpret_cast<const uint4*>(base + 64 * half);
-  const uint4* qh = reinterpret_cast<const uint4*>(base + 128 + 32 * half);
-  const int8_t* sc = reinterpret_cast<const int8_t*>(rec + g.b0 + (size_t)b * 16 + 8 * half) + 4 * hi;
-  const float d = h2f(__ldg(reinterpret_cast<const uint16_t*>(rec + g.b0 + g.b1) + b));
-  // scales of elements 0..15, 16..31 (first code set) and 32..47, 48..63 (second code set)
-  const float s00 = d * (float)sc[0], s01 = d * (float)sc[1], s10 = d * (float)sc[2], s11 = d * (float)sc[3];
-  const uint4 h0 = __ldg(qh), h1 = __ldg(qh + 1);
-  const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+  ORN_D void store(int kb, int half, uint32_t row_addr, int rsw) const {
+    const float d = h2f((uint16_t)(hdr.x & 0xffff)), dmin = h2f((uint16_t)(hdr.x >> 16));
+    float sc, m;
+    q4k_scale_min(2 * (kb & 3) + half, hdr.y, hdr.z, hdr.w, &sc, &m);
+    const float a = d * sc, nb = -(dmin * m);
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const int sh = 4 * half;
 #pragma unroll
-  for (int set = 0; set < 2; ++set) {  // set 0: ql bytes 0..31 (q1 / q3), set 1: ql bytes 32..63 (q2 / q4)
-    const uint4 l0 = __ldg(ql + 2 * set), l1 = __ldg(ql + 2 * set + 1);
-    const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-    const int hs = 2 * set + 4 * hi;  // bit position of this code set's two high bits in qh
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const float s = set == 0 ? (c < 2 ? s00 : s01) : (c < 2 ? s10 : s11);
+    for (int c = 0; c < 4; ++c) {  // 8 code bytes -> one chunk of this half
       uint32_t o[4];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const uint32_t low = hi ? ((lw[2 * c + j] >> 4) & 0x0F0F0F0Fu) : (lw[2 * c + j] & 0x0F0F0F0Fu);
-        const uint32_t q = low | (((hw[2 * c + j] >> hs) & 0x03030303u) << 4);
-        o[2 * j] = pack_bf2(s * byte_m32_f<0>(q), s * byte_m32_f<1>(q));
-        o[2 * j + 1] = pack_bf2(s * byte_m32_f<2>(q), s * byte_m32_f<3>(q));
+        const uint32_t n4 = (w[2 * c + j] >> sh) & 0x0F0F0F0Fu;
+        o[2 * j] = pack_bf2(fmaf(a, byte_f<0>(n4), nb), fmaf(a, byte_f<1>(n4), nb));
+        o[2 * j + 1] = pack_bf2(fmaf(a, byte_f<2>(n4), nb), fmaf(a, byte_f<3>(n4), nb));
+      }
+      st_chunk(row_addr, rsw, 4 * half + c, o[0], o[1], o[2], o[3]);
+    }
+  }
+};
+
+// Q6_K (kernels/q6k.metal:47-77): per 128 weights, byte l of ql / qh gives q1 (weight l), q2 (l + 32),
+// q3 (l + 64), q4 (l + 96); a K block of 64 is (q1, q2) or (q3, q4) of one half-block, this thread's
+// half of it one of the two; w = (d * sc) * (q - 32)
+template <> struct Raw<ORN_Q6K> {
+  uint4 l0, l1, h0, h1;
+  uint32_t sc2;  // the two int8 sub-scales of this half (16 weights each)
+  uint16_t dh;
+  ORN_D void load(const uint8_t* rec, const RecGeom& g, int kb, int set) {
+    const int b = kb >> 2, half = (kb >> 1) & 1, hi = kb & 1;
+    const uint8_t* base = rec + (size_t)b * 192;
+    const uint4* ql = reinterpret_cast<const uint4*>(base + 64 * half + 32 * set);
+    const uint4* qh = reinterpret_cast<const uint4*>(base + 128 + 32 * half);
+    l0 = __ldg(ql); l1 = __ldg(ql + 1);
+    h0 = __ldg(qh); h1 = __ldg(qh + 1);
+    sc2 = __ldg(reinterpret_cast<const uint16_t*>(rec + g.b0 + (size_t)b * 16 + 8 * half + 4 * hi + 2 * set));
+    dh = __ldg(reinterpret_cast<const uint16_t*>(rec + g.b0 + g.b1) + b);
+  }
+  ORN_D void store(int kb, int set, uint32_t row_addr, int rsw) const {
+    const int hi = kb & 1;
+    const float d = h2f(dh);
+    const float s0 = d * (float)(int8_t)(sc2 & 0xff), s1 = d * (float)(int8_t)(sc2 >> 8);
+    const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+    const int hs = 2 * set + 4 * hi;  // bit position of this code set's two high bits in qh
+    const int ls = 4 * hi;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float sv = c < 2 ? s0 : s1;
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t q = ((lw[2 * c + j] >> ls) & 0x0F0F0F0Fu) | (((hw[2 * c + j] >> hs) & 0x03030303u) << 4);
+        o[2 * j] = pack_bf2(sv * byte_m32_f<0>(q), sv * byte_m32_f<1>(q));
+        o[2 * j + 1] = pack_bf2(sv * byte_m32_f<2>(q), sv * byte_m32_f<3>(q));
       }
       st_chunk(row_addr, rsw, 4 * set + c, o[0], o[1], o[2], o[3]);
     }
   }
-}
+};
 
-ORN_D void zero_row(uint32_t row_addr) {
+ORN_D void zero_half(uint32_t row_addr, int half) {
 #pragma unroll
-  for (int c = 0; c < 8; ++c) st_chunk(row_addr, 0, c, 0u, 0u, 0u, 0u);
+  for (int c = 0; c < 4; ++c) st_chunk(row_addr, 0, 4 * half + c, 0u, 0u, 0u, 0u);
 }
 
 struct Item {
@@ -376,26 +397,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
     }
   } else {
     // ---- dequantising warps, then the epilogue of the item
-    const int r = threadIdx.x - 64;  // feature row of the tile this thread dequantises
-    const int q = warp & 3;          // TMEM lane quadrant this warp may read
+    const int dq = threadIdx.x - 64;   // 0..255
+    const int r = dq & 127;            // feature row of the tile this thread dequantises
+    const int half = dq >> 7;          // which 32 of the K block's 64 weights
+    const int q = warp & 3;            // TMEM lane quadrant this warp may read
+    const int colhalf = (warp - 2) >> 2;  // the two warps of a quadrant split the 16-column groups
     const RecGeom geo = rec_geom(KIND, P.K);
     uint32_t it = 0, acc_ph = 0;
     Item w;
     bool ok = true;
     for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
       const int f = w.ft * BM + r;
+      const bool live = f < P.O;
       const uint8_t* rec = P.W.w + ((size_t)w.e * P.O + min(f, P.O - 1)) * geo.rec;
+      Raw<KIND> cur, nxt;
+      if (live) cur.load(rec, geo, 0, half);
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1u;
+        if (live && kb + 1 < KB) nxt.load(rec, geo, kb + 1, half);  // in flight while this block is converted
         ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, P.err);
         if (!ok) break;
         const uint32_t row_addr = smem0 + s * P.stage_bytes + (uint32_t)r * 128u;
-        if (f < P.O) dequant_row<KIND>(rec, geo, kb, row_addr, r & 7);
-        else zero_row(row_addr);
+        if (live) cur.store(kb, half, row_addr, r & 7);
+        else zero_half(row_addr, half);
         fence_async_smem();  // the tensor core reads these bytes through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_full + 8 * s);
+        cur = nxt;
       }
       if (!ok) break;
       ok = mbar_wait(bar_acc_full, acc_ph, P.err);
@@ -405,7 +434,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
       const int fo = w.ft * BM + q * 32 + lane;  // TMEM lane = feature
       const int nt = (w.ntok + P.BN - 1) / P.BN;
       for (int t = 0; t < nt; ++t) {
-        for (int c0 = 0; c0 < P.BN; c0 += 16) {
+        for (int c0 = 16 * colhalf; c0 < P.BN; c0 += 32) {
           if (t * P.BN + c0 >= w.ntok) break;  // warp-uniform
           uint32_t v[16];
           tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * P.BN + c0), v);

@@ -38,15 +38,27 @@ constexpr int kWarpsPerBlock = 4;
 template <int KIND>
 struct Fmt;
 
+// activation loads: from global memory through the read-only path, or from shared memory
+template <bool SH> ORN_D uint4 ldx128(const void* p) {
+  if constexpr (SH) return *reinterpret_cast<const uint4*>(p);
+  else return ldg128(p);
+}
+template <bool SH> ORN_D uint2 ldx64(const void* p) {
+  if constexpr (SH) return *reinterpret_cast<const uint2*>(p);
+  else return __ldg(reinterpret_cast<const uint2*>(p));
+}
+
 template <>
 struct Fmt<ORN_Q4K> {
   static constexpr int kWeightsPerUnit = 32;
   struct X { float lo[16], hi[16], slo, shi; };
   struct W { uint4 q; uint4 meta; };
-  ORN_D static void load_x(const bf16_t* x, int u, X& r) {
+  ORN_D static void load_x(const bf16_t* x, int u, X& r) { load_x_t<false>(x, u, r); }
+  template <bool SH>
+  ORN_D static void load_x_t(const bf16_t* x, int u, X& r) {
     int blk = u >> 3, j = u & 7, g = j >> 1, h = j & 1;
     const bf16_t* p = x + blk * 256 + 64 * g + 16 * h;
-    uint4 a = ldg128(p), b = ldg128(p + 8), c = ldg128(p + 32), d = ldg128(p + 40);
+    uint4 a = ldx128<SH>(p), b = ldx128<SH>(p + 8), c = ldx128<SH>(p + 32), d = ldx128<SH>(p + 40);
     widen8(a, r.lo); widen8(b, r.lo + 8); widen8(c, r.hi); widen8(d, r.hi + 8);
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -95,12 +107,14 @@ struct Fmt<ORN_Q6K> {
   static constexpr int kWeightsPerUnit = 16;
   struct X { float v[4][4]; };  // [quadrant][i]
   struct W { uint32_t qa, qb, qh; uint32_t sc4; float d; };
-  ORN_D static void load_x(const bf16_t* x, int u, X& r) {
+  ORN_D static void load_x(const bf16_t* x, int u, X& r) { load_x_t<false>(x, u, r); }
+  template <bool SH>
+  ORN_D static void load_x_t(const bf16_t* x, int u, X& r) {
     int blk = u >> 4, j = u & 15, half = j >> 3, l0 = 4 * (j & 7);
     const bf16_t* p = x + blk * 256 + 128 * half + l0;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      uint2 v = __ldg(reinterpret_cast<const uint2*>(p + 32 * c));
+      uint2 v = ldx64<SH>(p + 32 * c);
       r.v[c][0] = bf_lo(v.x); r.v[c][1] = bf_hi(v.x);
       r.v[c][2] = bf_lo(v.y); r.v[c][3] = bf_hi(v.y);
     }
@@ -151,9 +165,11 @@ struct Fmt<ORN_A8> {
   static constexpr int kWeightsPerUnit = 16;
   struct X { float v[16]; float sum; };
   struct W { uint4 q; uint32_t sb; };
-  ORN_D static void load_x(const bf16_t* x, int u, X& r) {
+  ORN_D static void load_x(const bf16_t* x, int u, X& r) { load_x_t<false>(x, u, r); }
+  template <bool SH>
+  ORN_D static void load_x_t(const bf16_t* x, int u, X& r) {
     const bf16_t* p = x + 16 * u;
-    uint4 a = ldg128(p), b = ldg128(p + 8);
+    uint4 a = ldx128<SH>(p), b = ldx128<SH>(p + 8);
     widen8(a, r.v); widen8(b, r.v + 8);
     float s = 0.f;
 #pragma unroll
@@ -188,10 +204,12 @@ struct Fmt<ORN_A4> {
   static constexpr int kWeightsPerUnit = 32;
   struct X { float v[32]; float sum; };
   struct W { uint4 q; uint32_t sb; };
-  ORN_D static void load_x(const bf16_t* x, int u, X& r) {
+  ORN_D static void load_x(const bf16_t* x, int u, X& r) { load_x_t<false>(x, u, r); }
+  template <bool SH>
+  ORN_D static void load_x_t(const bf16_t* x, int u, X& r) {
     const bf16_t* p = x + 32 * u;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) widen8(ldg128(p + 8 * i), r.v + 8 * i);
+    for (int i = 0; i < 4; ++i) widen8(ldx128<SH>(p + 8 * i), r.v + 8 * i);
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) s = s + r.v[i];
@@ -228,7 +246,9 @@ struct Fmt<ORN_BF16> {
   static constexpr int kWeightsPerUnit = 8;
   struct X { float v[8]; };
   struct W { uint4 q; };
-  ORN_D static void load_x(const bf16_t* x, int u, X& r) { widen8(ldg128(x + 8 * u), r.v); }
+  ORN_D static void load_x(const bf16_t* x, int u, X& r) { load_x_t<false>(x, u, r); }
+  template <bool SH>
+  ORN_D static void load_x_t(const bf16_t* x, int u, X& r) { widen8(ldx128<SH>(x + 8 * u), r.v); }
   ORN_D static void load_w(const LinDev& L, int64_t row, int u, W& w) {
     w.q = ldg128_stream(L.w + row * L.rec + 16 * u);
   }
@@ -386,6 +406,136 @@ int k_gather_gemv(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf16
     case ORN_A8: return dispatch_gemv<ORN_A8, 1>(ctx, st, L, x, y, 0, lhs, rhs, rows);
     case ORN_A4: return dispatch_gemv<ORN_A4, 1>(ctx, st, L, x, y, 0, lhs, rhs, rows);
     default: return dispatch_gemv<ORN_BF16, 1>(ctx, st, L, x, y, 0, lhs, rhs, rows);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// grouped mat-vec: rows sorted by expert (the sorted path of switch_glu_rows,
+// src/ops/moe.rs:283-314, after counting_sort, :463-508).  Expert e owns the
+// sorted rows seg[e] .. seg[e+1]-1; a warp takes R output rows of one expert and
+// walks that expert's activation rows in groups of four, so the expert's
+// records come from HBM once (later groups find them in L1/L2) and every row is
+// computed with exactly the one-row arithmetic of gemv_kernel: the result bits
+// do not depend on how the rows are grouped.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int kGroupThreads = 256;  // 8 warps
+constexpr int kGroupRows = 128;     // output rows of one expert a block owns
+constexpr int kGroupBatch = 4;      // activation rows staged per pass (the mat-vec's row limit)
+
+// One warp, R output rows starting at row0 of expert matrix rows `rowbase`, M staged activation
+// rows in shared memory: the arithmetic of gemv_kernel (units in ascending order per lane, the
+// xor butterfly), weights requested SU units ahead.
+template <int KIND, int M, int R, int SU>
+ORN_D void grouped_rows(const LinDev& L, int64_t rowbase, int row0, int row_end, const bf16_t* xsm, bf16_t* y,
+                        const uint32_t* row_map, int first, int lane) {
+  using F = Fmt<KIND>;
+  const int units = L.K / F::kWeightsPerUnit;
+  float acc[R][M];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+  for (int u0 = lane; u0 < units; u0 += 32 * SU) {
+    typename F::W w[SU][R];
+#pragma unroll
+    for (int su = 0; su < SU; ++su) {
+      const int u = u0 + 32 * su;
+      if (u < units) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          if (row0 + r < row_end) F::load_w(L, rowbase + r, u, w[su][r]);
+      }
+    }
+#pragma unroll
+    for (int su = 0; su < SU; ++su) {
+      const int u = u0 + 32 * su;
+      if (u < units) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          typename F::X xr;
+          F::template load_x_t<true>(xsm + (size_t)m * L.K, u, xr);
+#pragma unroll
+          for (int r = 0; r < R; ++r)
+            if (row0 + r < row_end) acc[r][m] = F::fold(w[su][r], xr, u, acc[r][m]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const float v = warp_sum(acc[r][m]);
+      if (lane == 0 && row0 + r < row_end) {
+        const int64_t orow = row_map != nullptr ? (int64_t)row_map[first + m] : (int64_t)(first + m);
+        y[orow * L.O + row0 + r] = f2bf(v);
+      }
+    }
+}
+
+// grid (ceil(O / kGroupRows), E): a block owns kGroupRows output rows of one expert; it stages up
+// to four of the expert's activation rows in shared memory per pass and streams its weight rows
+// once per pass (the first pass from HBM, later passes from L2)
+template <int KIND, int R, int SU>
+__global__ void __launch_bounds__(kGroupThreads)
+grouped_gemv_kernel(LinDev L, const bf16_t* __restrict__ xs, const int* __restrict__ seg, bf16_t* __restrict__ y,
+                    const uint32_t* __restrict__ row_map) {
+  extern __shared__ __align__(16) uint8_t gsm[];
+  bf16_t* xsm = reinterpret_cast<bf16_t*>(gsm);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = blockIdx.y;
+  const int first = seg[e], n = seg[e + 1] - first;
+  if (n <= 0) return;
+  const int chunk0 = blockIdx.x * kGroupRows;
+  const int row_end = min(L.O, chunk0 + kGroupRows);
+  // the expert's rows in passes of four; blockIdx.z takes every gridDim.z-th pass
+  for (int m0 = kGroupBatch * blockIdx.z; m0 < n; m0 += kGroupBatch * gridDim.z) {
+    const int M = min(kGroupBatch, n - m0);
+    __syncthreads();  // the previous pass has read its rows
+    const uint4* src = reinterpret_cast<const uint4*>(xs + (size_t)(first + m0) * L.K);
+    for (int i = threadIdx.x; i < M * L.K / 8; i += blockDim.x) reinterpret_cast<uint4*>(xsm)[i] = __ldg(src + i);
+    __syncthreads();
+    for (int row0 = chunk0 + warp * R; row0 < row_end; row0 += (kGroupThreads / 32) * R) {
+      const int64_t rowbase = (int64_t)e * L.O + row0;
+      switch (M) {
+        case 1: grouped_rows<KIND, 1, R, SU>(L, rowbase, row0, row_end, xsm, y, row_map, first + m0, lane); break;
+        case 2: grouped_rows<KIND, 2, R, SU>(L, rowbase, row0, row_end, xsm, y, row_map, first + m0, lane); break;
+        case 3: grouped_rows<KIND, 3, R, SU>(L, rowbase, row0, row_end, xsm, y, row_map, first + m0, lane); break;
+        default: grouped_rows<KIND, 4, R, SU>(L, rowbase, row0, row_end, xsm, y, row_map, first + m0, lane); break;
+      }
+    }
+  }
+}
+
+template <int KIND>
+int launch_grouped(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf16_t* xs, const int* seg, bf16_t* y,
+                   const uint32_t* row_map, int max_rows) {
+  const size_t smem = (size_t)kGroupBatch * L->K * sizeof(bf16_t);
+  if (smem > 48 * 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "grouped gemv: rows longer than 6144 weights");
+  // passes of four rows spread over blockIdx.z: all of them for one dense matrix over many rows,
+  // a few for routed experts (an expert with more rows than that loops)
+  int z = L->E == 1 ? (max_rows + kGroupBatch - 1) / kGroupBatch : 4;
+  if (z < 1) z = 1;
+  if (z > 64) z = 64;
+  dim3 grid((L->O + kGroupRows - 1) / kGroupRows, L->E, z);
+  const int units = L->K / Fmt<KIND>::kWeightsPerUnit;
+  if (units > 32) grouped_gemv_kernel<KIND, 2, 2><<<grid, kGroupThreads, smem, st>>>(lin_dev(L), xs, seg, y, row_map);
+  else grouped_gemv_kernel<KIND, 4, 1><<<grid, kGroupThreads, smem, st>>>(lin_dev(L), xs, seg, y, row_map);
+  return orn_launch_check(ctx, "grouped_gemv");
+}
+}  // namespace
+
+// y[row_map ? row_map[p] : p] = W[expert of sorted row p] . xs[p] for every sorted row p
+int k_grouped_gemv(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf16_t* xs, const int* seg, bf16_t* y,
+                   const uint32_t* row_map, int max_rows) {
+  if (L->E > 65535) ORN_FAIL(ctx, ORN_ERR_ARG, "grouped gemv: more than 65535 experts");
+  switch (L->kind) {
+    case ORN_Q4K: return launch_grouped<ORN_Q4K>(ctx, st, L, xs, seg, y, row_map, max_rows);
+    case ORN_Q6K: return launch_grouped<ORN_Q6K>(ctx, st, L, xs, seg, y, row_map, max_rows);
+    case ORN_A8: return launch_grouped<ORN_A8>(ctx, st, L, xs, seg, y, row_map, max_rows);
+    case ORN_A4: return launch_grouped<ORN_A4>(ctx, st, L, xs, seg, y, row_map, max_rows);
+    default: return launch_grouped<ORN_BF16>(ctx, st, L, xs, seg, y, row_map, max_rows);
   }
 }
 

@@ -135,6 +135,8 @@ int k_gemv(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, i
            int out_f32);
 int k_gather_gemv(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x,
                   const uint32_t* lhs, const uint32_t* rhs, int rows, bf16_t* y);
+int k_grouped_gemv(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* xs, const int* seg, bf16_t* y,
+                   const uint32_t* row_map /*nullable*/, int max_rows /*upper bound of the rows of one expert*/);
 int k_kq_dequantize(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, int e, float* out);
 int k_embedding(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const uint32_t* ids, int T,
                 bf16_t* out);

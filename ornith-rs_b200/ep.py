@@ -286,3 +286,52 @@ def shard_experts(ctx, lin, rank, world):
         step = a.size // lin.E
         parts.append(a[rank * per * step:(rank + 1) * per * step] if a.size else None)
     return Linear.from_numpy(ctx, lin.kind, parts[0], parts[1], parts[2], E=per, O=lin.O, K=lin.K)
+
+
+# --------------------------------------------------------------------------- the library's block
+class LibEp:
+    """orn_ep: the expert-parallel block inside the library (csrc/ep.cu).  The plan is derived on
+    the device from the all-gathered routing table, the collectives are NCCL calls the library
+    enqueues on the context's stream, the expert owner runs the grouped mat-vec: no torch in the
+    data path and no host read inside the block.  exact=True runs the routed experts through the
+    row-invariant grouped mat-vec (bit-identical to the single-GPU block) instead of the grouped
+    tensor-core product (identical routing, rows equal to rounding).  `uid` is the 128-byte id rank 0 got from
+    `LibEp.unique_id(lib)` and the caller carried to the other ranks; a world of one needs none."""
+
+    ORDER = ("gate", "sw_gate", "sw_up", "sw_down", "sh_gate", "sh_up", "sh_down", "sh_egate")
+
+    def __init__(self, ctx, rank=0, world=1, uid=None, exact=False):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        h = C.c_void_p()
+        buf = None
+        if world > 1:
+            if uid is None or len(uid) != 128:
+                raise ValueError("LibEp: world > 1 needs the 128-byte unique id made by rank 0")
+            buf = (C.c_uint8 * 128).from_buffer_copy(bytes(uid))
+        ctx.check(ctx._lib.orn_ep_init(ctx.h, buf, rank, world, 1 if exact else 0, C.byref(h)), "orn_ep_init")
+        self.h = h
+
+    @staticmethod
+    def unique_id(lib):
+        buf = (C.c_uint8 * 128)()
+        rc = lib.orn_ep_unique_id(buf)
+        if rc != 0:
+            raise RuntimeError("orn_ep_unique_id failed with status %d (is libnccl.so.2 loadable?)" % rc)
+        return bytes(buf)
+
+    def moe_block(self, lins, x, R, top_k, norm_topk=1, out=None, inds=None):
+        """lins: the eight Linear handles by name (sw_* hold this rank's experts); x: device rows
+        [R, H]; returns the device buffer of the output rows."""
+        H = lins["gate"].K
+        if out is None:
+            out = self.ctx.empty((R, H), np.uint16)
+        xp = x.ptr if hasattr(x, "ptr") else x
+        ip = None if inds is None else (inds.ptr if hasattr(inds, "ptr") else inds)
+        self.ctx.check(self.ctx._lib.orn_ep_moe_block(self.h, *[lins[n].h for n in self.ORDER], xp, R, top_k,
+                                                      int(bool(norm_topk)), out.ptr, ip), "orn_ep_moe_block")
+        return out
+
+    def close(self):
+        if self.h:
+            self.ctx._lib.orn_ep_destroy(self.h)
+            self.h = None

@@ -93,3 +93,64 @@ def test_two_gpus_over_nccl_equal_the_single_device_block(tmp_path):
     xs = [eh.rows_of(seed, r, R, H) for r in range(2)]
     for r, want in enumerate(eh.expected(ws, xs, k)):
         assert np.array_equal(np.load("%s.%d.npy" % (out, r)), want)
+
+
+# ---- the library's own block (csrc/ep.cu): plan on the device, NCCL inside the library -------------
+def test_library_block_world_of_one_equals_the_oracle(pkg, ctx, ep):
+    """BASELINE config 5's decode width on one rank: 128 rows (64 sequences x width 2), 256 experts
+    top-8, through orn_ep_moe_block: every expert's records streamed once for all its rows by the
+    grouped mat-vec, each row with the one-row arithmetic, so rows and routing indices equal the
+    oracle's single-device block bit for bit."""
+    H, E, I, k, R = 2048, 256, 512, 8, 128
+    ws = eh.layer_weights(21, H, E, I)
+    L = {n: pkg.Linear.from_numpy(ctx, w.kind, w.w, w.s, w.b, E=w.E, O=w.O, K=w.K) for n, w in ws.items()}
+    x = eh.rows_of(21, 0, R, H)
+    group = ep.LibEp(ctx, exact=True)
+    inds = ctx.empty((R, k), np.uint32)
+    l0 = ctx.launches()
+    y = group.moe_block(L, ctx.upload(x), R, k, 1, inds=inds)
+    ctx.sync()
+    assert ctx.launches() - l0 <= 20     # a fixed number of launches, whatever the row count
+    import orn_oracle as orc
+    import helpers as hp
+    want, want_inds = orc.moe_block(ws, x, R, k, 1)
+    assert np.array_equal(inds.numpy(), want_inds)
+    assert np.array_equal(y.numpy(), want)
+    # the default: routed experts on the tensor cores.  Routing stays bit-exact; rows agree to rounding
+    # (raw-field weights are of one sign, so the bound is the reference's own for its bfloat16 tile,
+    # 1/256 of the largest output, tests/q4k.rs:444-450, plus one bfloat16 step of the stored value)
+    fast = ep.LibEp(ctx)
+    inds2 = ctx.empty((R, k), np.uint32)
+    y2 = fast.moe_block(L, ctx.upload(x), R, k, 1, inds=inds2)
+    ctx.sync()
+    assert np.array_equal(inds2.numpy(), want_inds)
+    g, w = hp.bf16_to_f32(y2.numpy()).astype(np.float64), hp.bf16_to_f32(want).astype(np.float64)
+    assert np.all(np.abs(g - w) <= np.abs(w).max() / 256.0 + np.abs(w) * 2.0 ** -7)
+    fast.close()
+    # a second call on other rows reuses the scratch; ragged row counts work too
+    x2 = eh.rows_of(22, 0, 37, H)
+    y2 = group.moe_block(L, ctx.upload(x2), 37, k, 1)
+    ctx.sync()
+    assert np.array_equal(y2.numpy(), orc.moe_block(ws, x2, 37, k, 1)[0])
+    group.close()
+    for l in L.values():
+        l.free()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_library_block_two_gpus_equal_the_single_device_block(tmp_path):
+    H, E, I, k = (SHAPE[n] for n in "HEIk")
+    seed, R = 14, 10
+    port, out = _free_port(), str(tmp_path / "y")
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "ep_worker.py"), "lib-exact", out] +
+                                      [str(v) for v in (seed, R, H, E, I, k)], env=env))
+    for p in procs:
+        assert p.wait(timeout=600) == 0
+    ws = eh.layer_weights(seed, H, E, I)
+    xs = [eh.rows_of(seed, r, R, H) for r in range(2)]
+    for r, want in enumerate(eh.expected(ws, xs, k)):
+        assert np.array_equal(np.load("%s.%d.npy" % (out, r)), want)
