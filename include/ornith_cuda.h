@@ -223,7 +223,8 @@ int32_t orn_moe_block(orn_ctx* ctx, const orn_linear* gate, const orn_linear* sw
  * R everywhere); gate, the shared expert and its gate are replicated, sw_* hold this rank's
  * E / world experts.  Nothing is read back to the host inside the block.  Routing, the shared
  * expert and the combine always run the row-invariant arithmetic at the row's home (routing
- * indices equal the single-GPU block's bit for bit).  The routed experts run as grouped products on
+ * indices equal the single-GPU block's bit for bit).  The routed experts (and, from 16 rows per
+ * rank, the shared expert) run as products on
  * the tensor cores (a decode batch of many sequences is a dense contraction per expert; results
  * agree with the single-GPU block to rounding), or, with ORN_EP_EXACT, through the grouped
  * row-invariant mat-vec (every output bit equals the single-GPU block's).  Either way a row's

@@ -148,21 +148,39 @@ __global__ void __launch_bounds__(kRowsPerCta * 4) gated_delta_kernel(DeltaParam
     float4 v4 = *reinterpret_cast<const float4*>(sin + 4 * i);
     S[4 * i] = v4.x; S[4 * i + 1] = v4.y; S[4 * i + 2] = v4.z; S[4 * i + 3] = v4.w;
   }
-  for (int t = 0; t < p.T; ++t) {
+  // the inputs of step t + 1 are requested before step t's arithmetic: a long window (a prompt
+  // chunk) otherwise pays one memory round trip per token on top of the recurrence's own chain
+  struct StepIn {
+    uint4 kv[4], qv[4];
+    float g;
+    bf16_t beta, v;
+  };
+  auto fetch = [&](int t, StepIn& in) {
     const bf16_t* kp = p.k + ((size_t)t * p.Hk + hk) * 128 + lir * 32;
     const bf16_t* qp = p.q + ((size_t)t * p.Hk + hk) * 128 + lir * 32;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { in.kv[i] = ldg128(kp + 8 * i); in.qv[i] = ldg128(qp + 8 * i); }
+    in.g = p.g[(size_t)t * p.Hv + hv];
+    in.beta = p.beta[(size_t)t * p.Hv + hv];
+    in.v = p.v[((size_t)t * p.Hv + hv) * 128 + row];
+  };
+  StepIn now, nxt;
+  fetch(0, now);
+  for (int t = 0; t < p.T; ++t) {
+    if (t + 1 < p.T) fetch(t + 1, nxt);
     float kf[32], qf[32];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      uint4 kv = ldg128(kp + 8 * i), qv = ldg128(qp + 8 * i);
+      const uint4 kv = now.kv[i], qv = now.qv[i];
       kf[8 * i] = bf_lo(kv.x); kf[8 * i + 1] = bf_hi(kv.x); kf[8 * i + 2] = bf_lo(kv.y); kf[8 * i + 3] = bf_hi(kv.y);
       kf[8 * i + 4] = bf_lo(kv.z); kf[8 * i + 5] = bf_hi(kv.z); kf[8 * i + 6] = bf_lo(kv.w); kf[8 * i + 7] = bf_hi(kv.w);
       qf[8 * i] = bf_lo(qv.x); qf[8 * i + 1] = bf_hi(qv.x); qf[8 * i + 2] = bf_lo(qv.y); qf[8 * i + 3] = bf_hi(qv.y);
       qf[8 * i + 4] = bf_lo(qv.z); qf[8 * i + 5] = bf_hi(qv.z); qf[8 * i + 6] = bf_lo(qv.w); qf[8 * i + 7] = bf_hi(qv.w);
     }
-    const float gt = p.g[(size_t)t * p.Hv + hv];
-    const float bt = bf2f(p.beta[(size_t)t * p.Hv + hv]);
-    const float vt = bf2f(p.v[((size_t)t * p.Hv + hv) * 128 + row]);
+    const float gt = now.g;
+    const float bt = bf2f(now.beta);
+    const float vt = bf2f(now.v);
+    now = nxt;
     float part[8];
 #pragma unroll
     for (int pb = 0; pb < 8; ++pb) {

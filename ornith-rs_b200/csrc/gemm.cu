@@ -33,6 +33,8 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdio>
+#include <cstring>
 #include <mutex>
 #include <set>
 #include <string>
@@ -50,7 +52,8 @@ constexpr int kGemmThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2..9: dequ
 constexpr int kDqWarps = 8;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWTileBytes = BM * BK * 2;
-constexpr int kMaxStages = 4;
+constexpr int kMaxIn = 12;  // IN ring slots (raw weight boxes + token tiles)
+constexpr int kMaxW = 3;    // W ring slots (dequantised weight tile)
 constexpr uint32_t kGemmWaitLimit = 1u << 16;  // try_wait rounds (each may sleep kGemmHintNs)
 constexpr uint32_t kGemmHintNs = 20000;
 
@@ -65,7 +68,7 @@ struct GemmParams {
   float* y_f32;              // non-null: float32 output instead of bfloat16
   int ldy;                   // elements between output rows
   const uint32_t* row_map;   // nullable: output row of sorted row p
-  int BN, NT, stages, f_tiles;
+  int BN, NT, stages /*IN ring*/, w_stages /*W ring*/, f_tiles;
   uint32_t stage_bytes;
   int* err;
 };
@@ -137,6 +140,21 @@ ORN_D void tmem_ld16(uint32_t taddr, uint32_t* v) {
 }
 ORN_D void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+ORN_D uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+ORN_D uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+ORN_D uint32_t lds16(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
 ORN_D void st_chunk(uint32_t row_addr, int rsw, int c, uint32_t a, uint32_t b, uint32_t cc, uint32_t d) {
   // 16-byte chunk c of a 128-byte row, at its swizzled place (chunk index xor row mod 8)
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)((c ^ rsw) << 4)), "r"(a), "r"(b),
@@ -150,35 +168,49 @@ ORN_D uint32_t pack_bf2(float lo, float hi) {
   return r;
 }
 
-// A thread dequantises HALF of one feature row's K block: 32 weights -> 64 bytes of bfloat16 (chunks
-// 4*half .. 4*half+3 of the row).  The raw bytes of the next K block are requested (load) before
-// the current ones are converted (store), so the latency of the row records hides behind arithmetic.
-template <int KIND> struct Raw;
+// The raw bytes of a K block arrive by TMA as boxes of [128 rows x 16 / 32 / 64 bytes] cut out of
+// the row records (no swizzle: row r of a box is at r * box bytes).  A thread dequantises HALF of
+// one feature row's K block: 32 weights -> 64 bytes of bfloat16 (chunks 4*half .. 4*half+3 of the
+// row's 128 bytes in the swizzled MMA tile).
+//
+// Raw tile layout per format (byte offsets inside the stage's raw area) and the record offsets
+// (x coordinates, multiples of 16) the boxes are cut at, for K block kb (b = kb / 4):
+//   Q4_K  [0, 4096)      codes, box 32:   x = b*128 + (kb&3)*32
+//         [4096, 6144)   header, box 16:  x = b0 + b*16
+//   Q6_K  [0, 8192)      ql, box 64:      x = b*192 + 64*half128          (half128 = (kb>>1)&1)
+//         [8192, 12288)  qh, box 32:      x = b*192 + 128 + 32*half128
+//         [12288, 14336) scales, box 16:  x = b0 + b*16
+//         [14336, 16384) d, box 16:       x = b0 + b1 + ((2b) & ~15)
+//   A8    [0, 8192)      codes, box 64:   x = kb*64
+//         [8192, 10240)  {scale,bias}, box 16: x = b0 + ((4kb) & ~15)
+//   A4    [0, 4096)      codes, box 32:   x = kb*32
+//         [4096, 6144)   {scale,bias}, box 16: x = b0 + ((8kb) & ~15)
+//   BF16  none: the [128 x 64] bf16 box lands in the MMA tile itself (128-byte swizzle)
+template <int KIND> struct Fmt;
 
-template <> struct Raw<ORN_BF16> {
-  uint4 v[4];
-  ORN_D void load(const uint8_t* rec, const RecGeom&, int kb, int half) {
-    const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 128 + half * 64);
-#pragma unroll
-    for (int c = 0; c < 4; ++c) v[c] = __ldg(src + c);
+template <> struct Fmt<ORN_BF16> {
+  static constexpr uint32_t kRawBytes = 0;
+  ORN_D static void issue(const CUtensorMap*, const CUtensorMap*, const CUtensorMap*, const CUtensorMap* wsw, const RecGeom&,
+                          int kb, int row, uint32_t raw, uint32_t wtile, uint32_t bar) {
+    tma_load_2d(raw, wsw, kb * BK, row, bar);
   }
-  ORN_D void store(int, int half, uint32_t row_addr, int rsw) const {
-#pragma unroll
-    for (int c = 0; c < 4; ++c) st_chunk(row_addr, rsw, 4 * half + c, v[c].x, v[c].y, v[c].z, v[c].w);
-  }
+  static constexpr uint32_t kTxBytes = kWTileBytes;
+  ORN_D static void convert(uint32_t, int, int, int, uint32_t, const RecGeom&) {}
 };
 
 // affine 8-bit, group 64: w = scale * q + bias (one fma, as the embedding lookup computes it)
-template <> struct Raw<ORN_A8> {
-  uint4 q[2];
-  uint32_t sb;
-  ORN_D void load(const uint8_t* rec, const RecGeom& g, int kb, int half) {
-    const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)kb * 64 + half * 32);
-    q[0] = __ldg(src); q[1] = __ldg(src + 1);
-    sb = __ldg(reinterpret_cast<const uint32_t*>(rec + g.b0) + kb);
+template <> struct Fmt<ORN_A8> {
+  static constexpr uint32_t kRawBytes = 10240, kTxBytes = 8192 + 2048;
+  ORN_D static void issue(const CUtensorMap* m64, const CUtensorMap*, const CUtensorMap* m16, const CUtensorMap*, const RecGeom& g,
+                          int kb, int row, uint32_t raw, uint32_t, uint32_t bar) {
+    tma_load_2d(raw, m64, kb * 64, row, bar);
+    tma_load_2d(raw + 8192, m16, (int)g.b0 + ((4 * kb) & ~15), row, bar);
   }
-  ORN_D void store(int, int half, uint32_t row_addr, int rsw) const {
+  ORN_D static void convert(uint32_t raw, int r, int kb, int half, uint32_t row_addr, const RecGeom&) {
+    const uint4 q0 = lds128(raw + r * 64 + half * 32), q1 = lds128(raw + r * 64 + half * 32 + 16);
+    const uint32_t sb = lds32(raw + 8192 + r * 16 + ((4 * kb) & 15));
     const float sc = bf_lo(sb), bi = bf_hi(sb);
+    const uint4 q[2] = {q0, q1};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const uint32_t w[4] = {q[h].x, q[h].y, q[h].z, q[h].w};
@@ -188,27 +220,29 @@ template <> struct Raw<ORN_A8> {
         o[2 * i] = pack_bf2(fmaf(sc, byte_f<0>(w[i]), bi), fmaf(sc, byte_f<1>(w[i]), bi));
         o[2 * i + 1] = pack_bf2(fmaf(sc, byte_f<2>(w[i]), bi), fmaf(sc, byte_f<3>(w[i]), bi));
       }
-      st_chunk(row_addr, rsw, 4 * half + 2 * h, o[0], o[1], o[2], o[3]);
-      st_chunk(row_addr, rsw, 4 * half + 2 * h + 1, o[4], o[5], o[6], o[7]);
+      st_chunk(row_addr, r & 7, 4 * half + 2 * h, o[0], o[1], o[2], o[3]);
+      st_chunk(row_addr, r & 7, 4 * half + 2 * h + 1, o[4], o[5], o[6], o[7]);
     }
   }
 };
 
 // affine 4-bit, group 32: half a K block is one group; byte b holds weights 2b (low nibble), 2b+1 (high)
-template <> struct Raw<ORN_A4> {
-  uint4 q;
-  uint32_t sb;
-  ORN_D void load(const uint8_t* rec, const RecGeom& g, int kb, int half) {
-    q = __ldg(reinterpret_cast<const uint4*>(rec + (size_t)kb * 32 + half * 16));
-    sb = __ldg(reinterpret_cast<const uint32_t*>(rec + g.b0) + 2 * kb + half);
+template <> struct Fmt<ORN_A4> {
+  static constexpr uint32_t kRawBytes = 6144, kTxBytes = 4096 + 2048;
+  ORN_D static void issue(const CUtensorMap*, const CUtensorMap* m32, const CUtensorMap* m16, const CUtensorMap*, const RecGeom& g,
+                          int kb, int row, uint32_t raw, uint32_t, uint32_t bar) {
+    tma_load_2d(raw, m32, kb * 32, row, bar);
+    tma_load_2d(raw + 4096, m16, (int)g.b0 + ((8 * kb) & ~15), row, bar);
   }
-  ORN_D void store(int, int half, uint32_t row_addr, int rsw) const {
+  ORN_D static void convert(uint32_t raw, int r, int kb, int half, uint32_t row_addr, const RecGeom&) {
+    const uint4 q = lds128(raw + r * 32 + half * 16);
+    const uint32_t sb = lds32(raw + 4096 + r * 16 + ((8 * kb) & 15) + 4 * half);
     const float sc = bf_lo(sb), bi = bf_hi(sb);
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
     for (int c = 0; c < 4; ++c) {  // one word = 8 weights = one 16-byte chunk of bfloat16
       const uint32_t l4 = w[c] & 0x0F0F0F0Fu, h4 = (w[c] >> 4) & 0x0F0F0F0Fu;
-      st_chunk(row_addr, rsw, 4 * half + c, pack_bf2(fmaf(sc, byte_f<0>(l4), bi), fmaf(sc, byte_f<0>(h4), bi)),
+      st_chunk(row_addr, r & 7, 4 * half + c, pack_bf2(fmaf(sc, byte_f<0>(l4), bi), fmaf(sc, byte_f<0>(h4), bi)),
                pack_bf2(fmaf(sc, byte_f<1>(l4), bi), fmaf(sc, byte_f<1>(h4), bi)),
                pack_bf2(fmaf(sc, byte_f<2>(l4), bi), fmaf(sc, byte_f<2>(h4), bi)),
                pack_bf2(fmaf(sc, byte_f<3>(l4), bi), fmaf(sc, byte_f<3>(h4), bi)));
@@ -219,15 +253,15 @@ template <> struct Raw<ORN_A4> {
 // Q4_K (kernels/q4k.metal:43-96): a K block is 32 code bytes; low nibbles are sub-block 2i (the first
 // half of the K block), high nibbles sub-block 2i+1 (the second half); w = (d * sc) * q - dmin * m,
 // evaluated as one fma per weight (this path agrees with the mat-vec to rounding, not bit for bit)
-template <> struct Raw<ORN_Q4K> {
-  uint4 qa, qb, hdr;
-  ORN_D void load(const uint8_t* rec, const RecGeom& g, int kb, int) {
-    const int b = kb >> 2, i4 = kb & 3;
-    const uint4* src = reinterpret_cast<const uint4*>(rec + (size_t)b * 128 + i4 * 32);
-    qa = __ldg(src); qb = __ldg(src + 1);
-    hdr = __ldg(reinterpret_cast<const uint4*>(rec + g.b0 + (size_t)b * 16));
+template <> struct Fmt<ORN_Q4K> {
+  static constexpr uint32_t kRawBytes = 6144, kTxBytes = 4096 + 2048;
+  ORN_D static void issue(const CUtensorMap*, const CUtensorMap* m32, const CUtensorMap* m16, const CUtensorMap*, const RecGeom& g,
+                          int kb, int row, uint32_t raw, uint32_t, uint32_t bar) {
+    tma_load_2d(raw, m32, (kb >> 2) * 128 + (kb & 3) * 32, row, bar);
+    tma_load_2d(raw + 4096, m16, (int)g.b0 + (kb >> 2) * 16, row, bar);
   }
-  ORN_D void store(int kb, int half, uint32_t row_addr, int rsw) const {
+  ORN_D static void convert(uint32_t raw, int r, int kb, int half, uint32_t row_addr, const RecGeom&) {
+    const uint4 qa = lds128(raw + r * 32), qb = lds128(raw + r * 32 + 16), hdr = lds128(raw + 4096 + r * 16);
     const float d = h2f((uint16_t)(hdr.x & 0xffff)), dmin = h2f((uint16_t)(hdr.x >> 16));
     float sc, m;
     q4k_scale_min(2 * (kb & 3) + half, hdr.y, hdr.z, hdr.w, &sc, &m);
@@ -243,31 +277,30 @@ template <> struct Raw<ORN_Q4K> {
         o[2 * j] = pack_bf2(fmaf(a, byte_f<0>(n4), nb), fmaf(a, byte_f<1>(n4), nb));
         o[2 * j + 1] = pack_bf2(fmaf(a, byte_f<2>(n4), nb), fmaf(a, byte_f<3>(n4), nb));
       }
-      st_chunk(row_addr, rsw, 4 * half + c, o[0], o[1], o[2], o[3]);
+      st_chunk(row_addr, r & 7, 4 * half + c, o[0], o[1], o[2], o[3]);
     }
   }
 };
 
 // Q6_K (kernels/q6k.metal:47-77): per 128 weights, byte l of ql / qh gives q1 (weight l), q2 (l + 32),
 // q3 (l + 64), q4 (l + 96); a K block of 64 is (q1, q2) or (q3, q4) of one half-block, this thread's
-// half of it one of the two; w = (d * sc) * (q - 32)
-template <> struct Raw<ORN_Q6K> {
-  uint4 l0, l1, h0, h1;
-  uint32_t sc2;  // the two int8 sub-scales of this half (16 weights each)
-  uint16_t dh;
-  ORN_D void load(const uint8_t* rec, const RecGeom& g, int kb, int set) {
-    const int b = kb >> 2, half = (kb >> 1) & 1, hi = kb & 1;
-    const uint8_t* base = rec + (size_t)b * 192;
-    const uint4* ql = reinterpret_cast<const uint4*>(base + 64 * half + 32 * set);
-    const uint4* qh = reinterpret_cast<const uint4*>(base + 128 + 32 * half);
-    l0 = __ldg(ql); l1 = __ldg(ql + 1);
-    h0 = __ldg(qh); h1 = __ldg(qh + 1);
-    sc2 = __ldg(reinterpret_cast<const uint16_t*>(rec + g.b0 + (size_t)b * 16 + 8 * half + 4 * hi + 2 * set));
-    dh = __ldg(reinterpret_cast<const uint16_t*>(rec + g.b0 + g.b1) + b);
+// half of it one of the two code sets; w = (d * sc) * (q - 32)
+template <> struct Fmt<ORN_Q6K> {
+  static constexpr uint32_t kRawBytes = 16384, kTxBytes = 8192 + 4096 + 2048 + 2048;
+  ORN_D static void issue(const CUtensorMap* m64, const CUtensorMap* m32, const CUtensorMap* m16, const CUtensorMap*,
+                          const RecGeom& g, int kb, int row, uint32_t raw, uint32_t, uint32_t bar) {
+    const int b = kb >> 2, half128 = (kb >> 1) & 1;
+    tma_load_2d(raw, m64, b * 192 + 64 * half128, row, bar);
+    tma_load_2d(raw + 8192, m32, b * 192 + 128 + 32 * half128, row, bar);
+    tma_load_2d(raw + 12288, m16, (int)g.b0 + b * 16, row, bar);
+    tma_load_2d(raw + 14336, m16, (int)(g.b0 + g.b1) + ((2 * b) & ~15), row, bar);
   }
-  ORN_D void store(int kb, int set, uint32_t row_addr, int rsw) const {
-    const int hi = kb & 1;
-    const float d = h2f(dh);
+  ORN_D static void convert(uint32_t raw, int r, int kb, int set, uint32_t row_addr, const RecGeom&) {
+    const int b = kb >> 2, half128 = (kb >> 1) & 1, hi = kb & 1;
+    const uint4 l0 = lds128(raw + r * 64 + 32 * set), l1 = lds128(raw + r * 64 + 32 * set + 16);
+    const uint4 h0 = lds128(raw + 8192 + r * 32), h1 = lds128(raw + 8192 + r * 32 + 16);
+    const uint32_t sc2 = lds16(raw + 12288 + r * 16 + 8 * half128 + 4 * hi + 2 * set);
+    const float d = h2f((uint16_t)lds16(raw + 14336 + r * 16 + ((2 * b) & 15)));
     const float s0 = d * (float)(int8_t)(sc2 & 0xff), s1 = d * (float)(int8_t)(sc2 >> 8);
     const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
     const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
@@ -283,15 +316,10 @@ template <> struct Raw<ORN_Q6K> {
         o[2 * j] = pack_bf2(sv * byte_m32_f<0>(q), sv * byte_m32_f<1>(q));
         o[2 * j + 1] = pack_bf2(sv * byte_m32_f<2>(q), sv * byte_m32_f<3>(q));
       }
-      st_chunk(row_addr, rsw, 4 * set + c, o[0], o[1], o[2], o[3]);
+      st_chunk(row_addr, r & 7, 4 * set + c, o[0], o[1], o[2], o[3]);
     }
   }
 };
-
-ORN_D void zero_half(uint32_t row_addr, int half) {
-#pragma unroll
-  for (int c = 0; c < 4; ++c) st_chunk(row_addr, 0, 4 * half + c, 0u, 0u, 0u, 0u);
-}
 
 struct Item {
   int e, tok0, ntok, ft;
@@ -311,20 +339,45 @@ ORN_D bool get_item(const GemmParams& P, int w, int n_items, Item& it) {
   return true;
 }
 
+struct GemmMaps {
+  CUtensorMap x;    // tokens [rows, K] bf16, box [BN, 64], 128-byte swizzle
+  CUtensorMap w64;  // row records as bytes [E*O, rec], boxes [128, 64] / [128, 32] / [128, 16], no swizzle
+  CUtensorMap w32;
+  CUtensorMap w16;
+  CUtensorMap wsw;  // bf16 weights only: [E*O, K] bf16, box [128, 64], 128-byte swizzle
+};
+
+// Two rings per CTA.  The IN ring (deep: TMA latency is a few thousand cycles) holds what TMA brings
+// per K block: the raw weight boxes and the token tiles.  The W ring (two or three 16 KB slots) holds
+// the dequantised weight tile the MMAs read.  bf16 weights need no dequantisation: their box lands
+// swizzled in the IN ring and the MMAs read it there.
+//   landed[i]   TMA boxes of IN slot i arrived            (producer's expect_tx)
+//   full[w]     W slot w dequantised                       (one arrival per dequantising warp)
+//   in_free[i]  the MMAs that read IN slot i are done      (tcgen05.commit)
+//   w_free[w]   the MMAs that read W slot w are done       (tcgen05.commit)
 template <int KIND>
-__global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant__ CUtensorMap xmap, GemmParams P) {
+__global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant__ GemmMaps maps, GemmParams P) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t s_bar[2 * kMaxStages + 2];
+  __shared__ __align__(8) uint64_t s_bar[2 * kMaxIn + 2 * kMaxW + 2];
   __shared__ uint32_t s_tmem;
+  using F = Fmt<KIND>;
+  constexpr bool kDirect = KIND == ORN_BF16;  // the MMA reads the weight box where TMA put it
+  constexpr uint32_t kInRaw = kDirect ? kWTileBytes : F::kRawBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem0 = (smem_addr(smem_raw) + 1023u) & ~1023u;  // swizzled tiles want 1024-byte alignment
-  const int S = P.stages;
-  const uint32_t bar_full = smem_addr(&s_bar[0]), bar_empty = smem_addr(&s_bar[kMaxStages]);
-  const uint32_t bar_acc_full = smem_addr(&s_bar[2 * kMaxStages]), bar_acc_empty = smem_addr(&s_bar[2 * kMaxStages + 1]);
+  const int SI = P.stages, SW = P.w_stages;
+  const uint32_t in0 = smem0 + (uint32_t)SW * kWTileBytes;  // W ring first, then the IN ring
+  const uint32_t bar_landed = smem_addr(&s_bar[0]), bar_in_free = smem_addr(&s_bar[kMaxIn]);
+  const uint32_t bar_full = smem_addr(&s_bar[2 * kMaxIn]), bar_w_free = smem_addr(&s_bar[2 * kMaxIn + kMaxW]);
+  const uint32_t bar_acc_full = smem_addr(&s_bar[2 * kMaxIn + 2 * kMaxW]), bar_acc_empty = bar_acc_full + 8;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < S; ++i) {
-      mbar_init(bar_full + 8 * i, 1 + kDqWarps);  // the TMA producer's expect_tx arrival + one per dequantising warp
-      mbar_init(bar_empty + 8 * i, 1);            // the MMA warp's commit
+    for (int i = 0; i < SI; ++i) {
+      mbar_init(bar_landed + 8 * i, 1);
+      mbar_init(bar_in_free + 8 * i, 1);
+    }
+    for (int i = 0; i < SW; ++i) {
+      mbar_init(bar_full + 8 * i, kDqWarps);
+      mbar_init(bar_w_free + 8 * i, 1);
     }
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_empty, kDqWarps);
@@ -344,26 +397,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
   const int n_items = P.items != nullptr ? *P.n_items : P.dense_items;
   const int KB = P.K / BK;
   const uint32_t x_tile_bytes = (uint32_t)P.BN * 128u;
+  const RecGeom geo = rec_geom(KIND, P.K);
 
   if (warp == 0) {
-    // ---- TMA producer: the token tiles of every stage
+    // ---- TMA producer: the raw weight boxes and the token tiles of every K block
     if (lane == 0) {
       uint32_t it = 0;
       Item w;
-      for (int wi = blockIdx.x; get_item(P, wi, n_items, w); wi += gridDim.x) {
+      bool ok = true;
+      for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
         const int nt = (w.ntok + P.BN - 1) / P.BN;
-        bool ok = true;
-        for (int kb = 0; kb < KB && ok; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1u;
-          ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, P.err);
+        const int wrow = w.e * P.O + w.ft * BM;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int si = it % SI;
+          ok = mbar_wait(bar_in_free + 8 * si, ((it / SI) & 1u) ^ 1u, P.err);
           if (!ok) break;
-          mbar_expect_tx(bar_full + 8 * s, (uint32_t)nt * x_tile_bytes);
-          const uint32_t dst = smem0 + s * P.stage_bytes + kWTileBytes;
-          for (int t = 0; t < nt; ++t)
-            tma_load_2d(dst + t * x_tile_bytes, &xmap, kb * BK, w.tok0 + t * P.BN, bar_full + 8 * s);
+          const uint32_t bar = bar_landed + 8 * si, base = in0 + si * P.stage_bytes;
+          mbar_expect_tx(bar, (uint32_t)nt * x_tile_bytes + F::kTxBytes);
+          F::issue(&maps.w64, &maps.w32, &maps.w16, &maps.wsw, geo, kb, wrow, base, base, bar);
+          for (int t = 0; t < nt; ++t) tma_load_2d(base + kInRaw + t * x_tile_bytes, &maps.x, kb * BK, w.tok0 + t * P.BN, bar);
         }
-        if (!ok) break;
       }
     }
   } else if (warp == 1) {
@@ -372,23 +425,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(P.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       uint32_t it = 0, acc_ph = 0;
       Item w;
-      for (int wi = blockIdx.x; get_item(P, wi, n_items, w); wi += gridDim.x) {
+      bool ok = true;
+      for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
         const int nt = (w.ntok + P.BN - 1) / P.BN;
-        bool ok = mbar_wait(bar_acc_empty, acc_ph ^ 1u, P.err);  // the previous item's accumulators were read
+        ok = mbar_wait(bar_acc_empty, acc_ph ^ 1u, P.err);  // the previous item's accumulators were read
         tc_fence_after();
         for (int kb = 0; kb < KB && ok; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1u;
-          ok = mbar_wait(bar_full + 8 * s, ph, P.err);
+          const int si = it % SI, sw = it % SW;
+          ok = mbar_wait(bar_full + 8 * sw, (it / SW) & 1u, P.err);  // implies landed[si]: the dequantisers waited for it
           if (!ok) break;
           tc_fence_after();
-          const uint32_t wa = smem0 + s * P.stage_bytes, xa = wa + kWTileBytes;
+          const uint32_t inb = in0 + si * P.stage_bytes;
+          const uint32_t wa = kDirect ? inb : smem0 + sw * kWTileBytes, xa = inb + kInRaw;
           for (int t = 0; t < nt; ++t)
 #pragma unroll
             for (int j = 0; j < BK / 16; ++j)
               tc_mma(tmem + (uint32_t)(t * P.BN), smem_desc(wa + j * 32), smem_desc(xa + t * x_tile_bytes + j * 32), idesc,
                      (kb > 0 || j > 0) ? 1u : 0u);
-          tc_commit(bar_empty + 8 * s);  // the stage is free once these MMAs have read it
+          tc_commit(bar_in_free + 8 * si);  // both slots are free once these MMAs have read them
+          tc_commit(bar_w_free + 8 * sw);
         }
         if (!ok) break;
         tc_commit(bar_acc_full);
@@ -402,29 +457,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
     const int half = dq >> 7;          // which 32 of the K block's 64 weights
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
     const int colhalf = (warp - 2) >> 2;  // the two warps of a quadrant split the 16-column groups
-    const RecGeom geo = rec_geom(KIND, P.K);
     uint32_t it = 0, acc_ph = 0;
     Item w;
     bool ok = true;
     for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
-      const int f = w.ft * BM + r;
-      const bool live = f < P.O;
-      const uint8_t* rec = P.W.w + ((size_t)w.e * P.O + min(f, P.O - 1)) * geo.rec;
-      Raw<KIND> cur, nxt;
-      if (live) cur.load(rec, geo, 0, half);
       for (int kb = 0; kb < KB; ++kb, ++it) {
-        const int s = it % S;
-        const uint32_t ph = (it / S) & 1u;
-        if (live && kb + 1 < KB) nxt.load(rec, geo, kb + 1, half);  // in flight while this block is converted
-        ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, P.err);
+        const int si = it % SI, sw = it % SW;
+        ok = mbar_wait(bar_w_free + 8 * sw, ((it / SW) & 1u) ^ 1u, P.err) && mbar_wait(bar_landed + 8 * si, (it / SI) & 1u, P.err);
         if (!ok) break;
-        const uint32_t row_addr = smem0 + s * P.stage_bytes + (uint32_t)r * 128u;
-        if (live) cur.store(kb, half, row_addr, r & 7);
-        else zero_half(row_addr, half);
-        fence_async_smem();  // the tensor core reads these bytes through the async proxy
+        if (!kDirect) {
+          F::convert(in0 + si * P.stage_bytes, r, kb, half, smem0 + sw * kWTileBytes + (uint32_t)r * 128u, geo);
+          fence_async_smem();  // the tensor core reads these bytes through the async proxy
+        }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_full + 8 * s);
-        cur = nxt;
+        if (lane == 0) mbar_arrive(bar_full + 8 * sw);
       }
       if (!ok) break;
       ok = mbar_wait(bar_acc_full, acc_ph, P.err);
@@ -502,6 +548,15 @@ __global__ void k_route_place(const uint32_t* rhs, int rows, int E, const int* s
     pos += __popc(m);
   }
 }
+// the same placement for long tables, one thread per row: the slot inside an expert is taken from a
+// cursor, so the order inside an expert is arbitrary (every row's result is independent of its
+// neighbours, and results are stored by original row index)
+__global__ void k_route_place_atomic(const uint32_t* rhs, int rows, int E, int* cursor, uint32_t* perm) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows) return;
+  const uint32_t e = rhs[i];
+  if (e < (uint32_t)E) perm[atomicAdd(&cursor[e], 1)] = (uint32_t)i;
+}
 // xs[p] = x[lhs[perm[p]]] (rows of K bf16)
 __global__ void k_gather_rows(const bf16_t* x, const uint32_t* lhs, const uint32_t* perm, int rows, int K, bf16_t* xs) {
   const int p = blockIdx.x;
@@ -554,7 +609,7 @@ std::mutex g_gemm_mu;
 std::set<std::pair<int, int>> g_gemm_granted;  // (device, format): shared-memory limit raised
 
 template <int KIND>
-int launch_qgemm(orn_ctx* ctx, cudaStream_t s, const CUtensorMap& map, const GemmParams& P, int grid, size_t smem) {
+int launch_qgemm(orn_ctx* ctx, cudaStream_t s, const GemmMaps& maps, const GemmParams& P, int grid, size_t smem) {
   {
     std::lock_guard<std::mutex> lock(g_gemm_mu);
     if (!g_gemm_granted.count({ctx->device, KIND})) {
@@ -562,8 +617,24 @@ int launch_qgemm(orn_ctx* ctx, cudaStream_t s, const CUtensorMap& map, const Gem
       g_gemm_granted.insert({ctx->device, KIND});
     }
   }
-  k_qgemm<KIND><<<grid, kGemmThreads, smem, s>>>(map, P);
-  return orn_launch_check(ctx, "k_qgemm");
+  k_qgemm<KIND><<<grid, kGemmThreads, smem, s>>>(maps, P);
+  if (ctx->kt == nullptr) return orn_launch_check(ctx, "k_qgemm");
+  // per-kernel timing: one label per shape
+  static std::set<std::string> pool;
+  char buf[96];
+  snprintf(buf, sizeof buf, "k_qgemm kind=%d O=%d K=%d rows=%d %s", KIND, P.O, P.K, P.rows, P.items ? "grouped" : "dense");
+  std::lock_guard<std::mutex> lock(g_gemm_mu);
+  return orn_launch_check(ctx, pool.insert(buf).first->c_str());
+}
+
+uint32_t raw_bytes(int kind) {
+  switch (kind) {
+    case ORN_Q4K: return Fmt<ORN_Q4K>::kRawBytes;
+    case ORN_Q6K: return Fmt<ORN_Q6K>::kRawBytes;
+    case ORN_A8: return Fmt<ORN_A8>::kRawBytes;
+    case ORN_A4: return Fmt<ORN_A4>::kRawBytes;
+    default: return 0;
+  }
 }
 
 }  // namespace
@@ -581,7 +652,7 @@ size_t qgemm_scratch_bytes(int rows, int E, int O) {
 // result goes to output row row_map[p] when row_map is given.  scratch: qgemm_scratch_bytes() of
 // device memory for the grouped form.
 int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, int rows, void* y, int ldy,
-            const QGemmGroup* grp, void* scratch, int out_f32) {
+            const QGemmGroup* grp, void* scratch, int out_f32, int bn_force) {
   if (rows < 1) return ORN_OK;
   if (L->K % BK) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: K must be a multiple of 64");
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: x must be 16-byte aligned");
@@ -598,30 +669,55 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
   // token-tile width: wide tiles when there are many tokens per weight tile, narrow ones otherwise
   int per = grp ? (rows + L->E - 1) / L->E : rows;  // expected tokens per weight tile
   if (grp && grp->bn_hint > 0) per = grp->bn_hint;
-  int BN = per >= 256 ? 256 : ((per + 15) / 16) * 16;
+  int BN = per >= 128 ? 128 : ((per + 15) / 16) * 16;
   if (BN < 16) BN = 16;
+  if (bn_force > 0) BN = bn_force;  // a caller that wants one tile shape whatever the row count
   P.BN = BN;
+  // tokens per item: 256 for dense products over many rows (a weight tile is dequantised once for
+  // all of them; more would leave the IN ring too shallow to cover the TMA latency), a few tiles for
+  // routed rows (an expert with more rows than that takes several items)
   P.NT = (int)kTmemCols / BN;
-  if (grp == nullptr) P.NT = std::min(P.NT, (rows + BN - 1) / BN);
+  if (grp == nullptr) P.NT = std::min(std::min(P.NT, (rows + BN - 1) / BN), BN >= 128 ? 2 : 8);
+  else P.NT = std::min(P.NT, BN >= 64 ? 4 : 2);
   if (P.NT > 8) P.NT = 8;
-  P.stage_bytes = kWTileBytes + (uint32_t)P.NT * BN * 128u;
-  P.stages = (int)std::min<size_t>(kMaxStages, (200 * 1024) / P.stage_bytes);
+  // shared memory: the W ring, then as many IN slots as fit (TMA latency wants depth)
+  const uint32_t in_raw = L->kind == ORN_BF16 ? kWTileBytes : raw_bytes(L->kind);
+  P.stage_bytes = in_raw + (uint32_t)P.NT * BN * 128u;
+  P.w_stages = L->kind == ORN_BF16 ? 1 : kMaxW;
+  const size_t budget = 200 * 1024;
+  P.stages = (int)std::min<size_t>(kMaxIn, (budget - (size_t)P.w_stages * kWTileBytes) / P.stage_bytes);
+  if (P.stages < 2) {
+    P.w_stages = L->kind == ORN_BF16 ? 1 : 2;
+    P.stages = (int)std::min<size_t>(kMaxIn, (budget - (size_t)P.w_stages * kWTileBytes) / P.stage_bytes);
+  }
   if (P.stages < 2) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: stage does not fit twice into shared memory");
   // One CTA per SM is part of the kernel's contract (it takes all of tensor memory): pad the
   // launch's shared memory above half of the SM's.
-  size_t smem = 1024 + (size_t)P.stages * P.stage_bytes;
+  size_t smem = 1024 + (size_t)P.w_stages * kWTileBytes + (size_t)P.stages * P.stage_bytes;
   if (smem < 120 * 1024) smem = 120 * 1024;
-  CUtensorMap map;
-  {
-    const cuuint64_t gdim[2] = {(cuuint64_t)L->K, (cuuint64_t)rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)L->K * 2};
-    const cuuint32_t box[2] = {BK, (cuuint32_t)BN};
+  GemmMaps maps;
+  memset(&maps, 0, sizeof maps);
+  auto encode = [&](CUtensorMap* m, CUtensorMapDataType dt, void* base, uint64_t inner, uint64_t outer, uint64_t stride_bytes,
+                    uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) -> bool {
+    const cuuint64_t gdim[2] = {inner, outer};
+    const cuuint64_t gstride[1] = {stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16_t*>(x), gdim, gstride, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) ORN_FAIL(ctx, ORN_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed with " + std::to_string((int)r));
+    return enc(m, dt, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  };
+  bool ok = encode(&maps.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, const_cast<bf16_t*>(x), (uint64_t)L->K, (uint64_t)rows,
+                   (uint64_t)L->K * 2, BK, (uint32_t)BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  const uint64_t wrows = (uint64_t)L->E * L->O;
+  if (L->kind == ORN_BF16) {
+    ok = ok && encode(&maps.wsw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, L->w, (uint64_t)L->K, wrows, (uint64_t)L->rec, BK, BM,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    ok = ok && encode(&maps.w64, CU_TENSOR_MAP_DATA_TYPE_UINT8, L->w, (uint64_t)L->rec, wrows, (uint64_t)L->rec, 64, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+    ok = ok && encode(&maps.w32, CU_TENSOR_MAP_DATA_TYPE_UINT8, L->w, (uint64_t)L->rec, wrows, (uint64_t)L->rec, 32, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+    ok = ok && encode(&maps.w16, CU_TENSOR_MAP_DATA_TYPE_UINT8, L->w, (uint64_t)L->rec, wrows, (uint64_t)L->rec, 16, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
   }
+  if (!ok) ORN_FAIL(ctx, ORN_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed");
   int grid;
   if (grp == nullptr) {
     P.items = nullptr; P.n_items = nullptr;
@@ -643,11 +739,11 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
     grid = ctx->sm_count;
   }
   switch (L->kind) {
-    case ORN_Q4K: return launch_qgemm<ORN_Q4K>(ctx, s, map, P, grid, smem);
-    case ORN_Q6K: return launch_qgemm<ORN_Q6K>(ctx, s, map, P, grid, smem);
-    case ORN_A8: return launch_qgemm<ORN_A8>(ctx, s, map, P, grid, smem);
-    case ORN_BF16: return launch_qgemm<ORN_BF16>(ctx, s, map, P, grid, smem);
-    case ORN_A4: return launch_qgemm<ORN_A4>(ctx, s, map, P, grid, smem);
+    case ORN_Q4K: return launch_qgemm<ORN_Q4K>(ctx, s, maps, P, grid, smem);
+    case ORN_Q6K: return launch_qgemm<ORN_Q6K>(ctx, s, maps, P, grid, smem);
+    case ORN_A8: return launch_qgemm<ORN_A8>(ctx, s, maps, P, grid, smem);
+    case ORN_BF16: return launch_qgemm<ORN_BF16>(ctx, s, maps, P, grid, smem);
+    case ORN_A4: return launch_qgemm<ORN_A4>(ctx, s, maps, P, grid, smem);
   }
   ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: unknown weight format");
 }
@@ -658,7 +754,8 @@ int f_route_sort(orn_ctx* ctx, cudaStream_t s, const uint32_t* rhs, int rows, in
   k_route_count<<<1, 1024, E * sizeof(int), s>>>(rhs, rows, E, seg, cursor);
   int rc = orn_launch_check(ctx, "k_route_count");
   if (rc != ORN_OK) return rc;
-  k_route_place<<<(E + 7) / 8, 256, 0, s>>>(rhs, rows, E, seg, perm);
+  if (rows >= 4096) k_route_place_atomic<<<(rows + 255) / 256, 256, 0, s>>>(rhs, rows, E, cursor, perm);
+  else k_route_place<<<(E + 7) / 8, 256, 0, s>>>(rhs, rows, E, seg, perm);
   return orn_launch_check(ctx, "k_route_place");
 }
 
