@@ -364,6 +364,35 @@ typedef struct {
 } orn_prof;
 int32_t orn_get_prof(orn_model* m, orn_prof* out);
 
+/* ---- batched decode: B concurrent sequences, a verify window of T rows each (T = 2 for MTP
+ * depth 1), one pass over the weights per step.  No counterpart in the reference, which decodes one
+ * sequence (README.md:217-221); the layer sequence is TextModel::forward_capture
+ * (src/model/qwen3_5.rs:578-695) and the per-sequence acceptance is TrunkCapture::rewind
+ * (qwen3_5.rs:324-348).  Per sequence: a KV cache of `cap` positions per attention layer, a conv
+ * window and a ring of T_max + 1 recurrent states per gated-delta layer, a position.  Rows are
+ * sequence-major: row b * T + t is window row t of sequence b.  The MoE blocks run through
+ * orn_ep_moe_block on `ep` (NULL: this GPU alone); with a group of several ranks every rank steps
+ * its own B sequences and serves its E / world experts of every layer (views into the model's
+ * matrices, nothing is copied), so the call is collective.  From 16 rows the projections run on the
+ * tensor cores and attention as a split-KV pass over the caches; with ORN_BATCH_EXACT (or fewer
+ * rows) every product is the row-invariant mat-vec and the batched pass equals the single-sequence
+ * engine bit for bit.
+ * orn_batch_fill_random: benchmark set-up, every sequence as if ctx_len tokens had been decoded.
+ * orn_batch_forward: host_ids [B*T]; dev_normed (nullable) [B*T, hidden]; host_targets (nullable)
+ * receives the greedy token of every row (syncs).  orn_batch_commit: keep[b] in 1..T. */
+typedef struct orn_batch orn_batch;
+#define ORN_BATCH_EXACT 1 /* flags: row-invariant products at every row count */
+int32_t orn_batch_create(orn_model* m, int32_t B, int32_t T_max, int32_t cap, int32_t flags, orn_batch** out);
+int32_t orn_batch_destroy(orn_batch* bt);
+int32_t orn_batch_reset(orn_batch* bt);
+int32_t orn_batch_fill_random(orn_batch* bt, int32_t ctx_len, uint64_t seed);
+int32_t orn_batch_positions(orn_batch* bt, int32_t* host_pos /*[B]*/);
+int32_t orn_batch_forward(orn_batch* bt, orn_ep* ep /*nullable*/, const uint32_t* host_ids, int32_t T,
+                          uint16_t* dev_normed /*nullable*/, uint32_t* host_targets /*nullable*/);
+int32_t orn_batch_commit(orn_batch* bt, const int32_t* host_keep /*[B]*/);
+int32_t orn_ep_world(const orn_ep* ep);
+int32_t orn_ep_rank(const orn_ep* ep);
+
 /* host copies of the shared elementary functions, so that a checker can
  * compare them with its own restatement without a GPU */
 float orn_host_expf(float x);

@@ -339,6 +339,55 @@ class TextModel:
             self.h = None
 
 
+class Batch:
+    """orn_batch: B concurrent sequences stepping verify windows of up to t_max rows through the
+    whole trunk in one pass over the weights (csrc/batch.cu).  `ep` is an `ep.LibEp` group (None:
+    this GPU alone); with several ranks every rank holds its own B sequences and serves its share
+    of every layer's experts, and forward() is collective.  exact=True keeps every product on the
+    row-invariant mat-vec (bit-identical to the single-sequence engine)."""
+
+    def __init__(self, model, B, t_max=2, cap=256, exact=False):
+        self.model, self.ctx, self.B, self.t_max, self.cap = model, model.ctx, B, t_max, cap
+        h = C.c_void_p()
+        self.ctx.check(self.ctx._lib.orn_batch_create(model.h, B, t_max, cap, 1 if exact else 0, C.byref(h)),
+                       "orn_batch_create")
+        self.h = h
+
+    def reset(self):
+        self.ctx.check(self.ctx._lib.orn_batch_reset(self.h), "orn_batch_reset")
+
+    def fill_random(self, ctx_len, seed=1):
+        self.ctx.check(self.ctx._lib.orn_batch_fill_random(self.h, ctx_len, seed), "orn_batch_fill_random")
+
+    def positions(self):
+        out = np.zeros(self.B, np.int32)
+        self.ctx.check(self.ctx._lib.orn_batch_positions(self.h, out.ctypes.data), "orn_batch_positions")
+        return out
+
+    def forward(self, ids, ep=None, want_hidden=False, want_targets=True):
+        """ids [B, T] -> (greedy targets [B, T] or None, post-norm hidden rows [B*T, hidden] on the device or None)."""
+        ids = np.ascontiguousarray(ids, np.uint32)
+        if ids.ndim != 2 or ids.shape[0] != self.B:
+            raise ValueError("Batch.forward: ids must be [B, T]")
+        T = ids.shape[1]
+        hid = self.ctx.empty((self.B * T, self.model.cfg.hidden), np.uint16) if want_hidden else None
+        tg = np.zeros((self.B, T), np.uint32) if want_targets else None
+        self.ctx.check(self.ctx._lib.orn_batch_forward(self.h, None if ep is None else ep.h, ids.ctypes.data, T, _p(hid),
+                                                       None if tg is None else tg.ctypes.data), "orn_batch_forward")
+        return tg, hid
+
+    def commit(self, keep):
+        keep = np.ascontiguousarray(keep, np.int32)
+        if keep.shape != (self.B,):
+            raise ValueError("Batch.commit: one keep per sequence")
+        self.ctx.check(self.ctx._lib.orn_batch_commit(self.h, keep.ctypes.data), "orn_batch_commit")
+
+    def free(self):
+        if self.h:
+            self.ctx._lib.orn_batch_destroy(self.h)
+            self.h = None
+
+
 class Cache:
     """orn_cache: KvCache + GdnCache per layer and the MTP head's KvCache (src/model/cache.rs)."""
 

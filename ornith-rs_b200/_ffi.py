@@ -97,6 +97,15 @@ SIGNATURES = {
     "orn_ep_init": (i32, [vp, vp, i32, i32, i32, c_void_pp]),
     "orn_ep_destroy": (i32, [vp]),
     "orn_ep_moe_block": (i32, [vp] + [vp] * 8 + [vp, i32, i32, i32, vp, vp]),
+    "orn_ep_world": (i32, [vp]),
+    "orn_ep_rank": (i32, [vp]),
+    "orn_batch_create": (i32, [vp, i32, i32, i32, i32, c_void_pp]),
+    "orn_batch_destroy": (i32, [vp]),
+    "orn_batch_reset": (i32, [vp]),
+    "orn_batch_fill_random": (i32, [vp, i32, u64]),
+    "orn_batch_positions": (i32, [vp, vp]),
+    "orn_batch_forward": (i32, [vp, vp, vp, i32, vp, vp]),
+    "orn_batch_commit": (i32, [vp, vp]),
     "orn_gdn_front": (i32, [vp] + [vp] * 7 + [i32] * 5 + [f32] + [vp] * 6),
     "orn_gated_delta": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "orn_rope": (i32, [vp, vp, i32, i32, i32, i32, f32, i32]),

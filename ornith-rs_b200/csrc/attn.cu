@@ -23,17 +23,19 @@ ORN_D void widen8(const uint4& v, float* f) {
 }
 
 // x [T, H, hd] rotated in place on the first `dims` dims, pair (i, i+dims/2)
+// Tb > 0: the T rows are Tb-row windows of T / Tb sequences, dev_offset holds one position per sequence
 __global__ void rope_kernel(bf16_t* x, int T, int H, int hd, int dims, float lnb,
-                            const int* dev_offset, int offset_add) {
+                            const int* dev_offset, int offset_add, int Tb) {
   const int half = dims / 2;
   int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= T * H * half) return;
   const int i = idx % half;
   const int h = (idx / half) % H;
   const int t = idx / (half * H);
-  const int offset = (dev_offset ? *dev_offset : 0) + offset_add;
+  const int seq = Tb > 0 ? t / Tb : 0, tl = Tb > 0 ? t - seq * Tb : t;
+  const int offset = (dev_offset ? dev_offset[seq] : 0) + offset_add;
   const float inv_freq = orn_expf(-(float)i * lnb);
-  const float ang = (float)(offset + t) * inv_freq;
+  const float ang = (float)(offset + tl) * inv_freq;
   float sn, cs;
   orn_sincosf(ang, &sn, &cs);
   bf16_t* p = x + ((int64_t)t * H + h) * hd;
@@ -46,17 +48,18 @@ __global__ void rope_kernel(bf16_t* x, int T, int H, int hd, int dims, float lnb
 
 // k, v [T, Hkv, hd] -> caches [Hkv, cap, hd] at rows offset..offset+T-1
 __global__ void kv_append_kernel(const bf16_t* k, const bf16_t* v, int T, int Hkv, int hd, int cap,
-                                 const int* dev_offset, int offset_add, bf16_t* kc, bf16_t* vc) {
+                                 const int* dev_offset, int offset_add, bf16_t* kc, bf16_t* vc, int Tb) {
   int idx = blockIdx.x * blockDim.x + threadIdx.x;  // over T*Hkv*hd/8 16-byte pieces
   const int per = hd / 8;
   if (idx >= T * Hkv * per) return;
   const int c = idx % per;
   const int h = (idx / per) % Hkv;
   const int t = idx / (per * Hkv);
-  const int offset = (dev_offset ? *dev_offset : 0) + offset_add;
-  if (offset + t >= cap) return;
+  const int seq = Tb > 0 ? t / Tb : 0, tl = Tb > 0 ? t - seq * Tb : t;  // Tb > 0: a cache [Hkv, cap, hd] per sequence
+  const int offset = (dev_offset ? dev_offset[seq] : 0) + offset_add;
+  if (offset + tl >= cap) return;
   const int64_t src = (((int64_t)t * Hkv + h) * hd) / 8 + c;
-  const int64_t dst = (((int64_t)h * cap + offset + t) * hd) / 8 + c;
+  const int64_t dst = ((((int64_t)seq * Hkv + h) * cap + offset + tl) * hd) / 8 + c;
   reinterpret_cast<uint4*>(kc)[dst] = reinterpret_cast<const uint4*>(k)[src];
   reinterpret_cast<uint4*>(vc)[dst] = reinterpret_cast<const uint4*>(v)[src];
 }
@@ -65,15 +68,18 @@ __global__ void kv_append_kernel(const bf16_t* k, const bf16_t* v, int T, int Hk
 __global__ void __launch_bounds__(1024)
 sdpa_decode_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ kc,
                    const bf16_t* __restrict__ vc, int T, int Hq, int Hkv, int cap,
-                   const int* dev_offset, int offset_add, float scale, bf16_t* __restrict__ out) {
+                   const int* dev_offset, int offset_add, float scale, bf16_t* __restrict__ out, int Tb) {
   constexpr int HD = 256;
   __shared__ float s_o[32][HD];
   __shared__ float s_max[32], s_sum[32], s_f[32];
   const int h = blockIdx.x, r = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kvh = h / (Hq / Hkv);
-  const int offset = (dev_offset ? *dev_offset : 0) + offset_add;
-  int L = offset + r + 1;
+  const int seq = Tb > 0 ? r / Tb : 0, tl = Tb > 0 ? r - seq * Tb : r;  // Tb > 0: a cache and a position per sequence
+  const int offset = (dev_offset ? dev_offset[seq] : 0) + offset_add;
+  kc += (int64_t)seq * Hkv * cap * HD;
+  vc += (int64_t)seq * Hkv * cap * HD;
+  int L = offset + tl + 1;
   if (L > cap) L = cap;
   float qs[8], o[8];
   {
@@ -129,14 +135,14 @@ sdpa_decode_kernel(const bf16_t* __restrict__ q, const bf16_t* __restrict__ kc,
 int k_rope(orn_ctx* ctx, cudaStream_t s, bf16_t* x, int T, int H, int hd, int dims, float lnb,
            const int* dev_offset, int offset_add) {
   int n = T * H * (dims / 2);
-  rope_kernel<<<(n + 127) / 128, 128, 0, s>>>(x, T, H, hd, dims, lnb, dev_offset, offset_add);
+  rope_kernel<<<(n + 127) / 128, 128, 0, s>>>(x, T, H, hd, dims, lnb, dev_offset, offset_add, 0);
   return orn_launch_check(ctx, "rope");
 }
 
 int k_kv_append(orn_ctx* ctx, cudaStream_t s, const bf16_t* k, const bf16_t* v, int T, int Hkv,
                 int hd, int cap, const int* dev_offset, int offset_add, bf16_t* kc, bf16_t* vc) {
   int n = T * Hkv * (hd / 8);
-  kv_append_kernel<<<(n + 127) / 128, 128, 0, s>>>(k, v, T, Hkv, hd, cap, dev_offset, offset_add, kc, vc);
+  kv_append_kernel<<<(n + 127) / 128, 128, 0, s>>>(k, v, T, Hkv, hd, cap, dev_offset, offset_add, kc, vc, 0);
   return orn_launch_check(ctx, "kv_append");
 }
 
@@ -146,6 +152,27 @@ int k_sdpa_decode(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* k
   if (hd != 256) ORN_FAIL(ctx, ORN_ERR_ARG, "sdpa_decode: head_dim must be 256");
   if (Hq % Hkv != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "sdpa_decode: Hq % Hkv != 0");
   dim3 grid(Hq, T);
-  sdpa_decode_kernel<<<grid, 1024, 0, s>>>(q, kc, vc, T, Hq, Hkv, cap, dev_offset, offset_add, scale, out);
+  sdpa_decode_kernel<<<grid, 1024, 0, s>>>(q, kc, vc, T, Hq, Hkv, cap, dev_offset, offset_add, scale, out, 0);
+  return orn_launch_check(ctx, "sdpa_decode");
+}
+
+// ---- the same three ops over B sequences at once: rows are sequence-major ([B][Tb] windows), every
+// sequence has its own position pos[b] and its own caches [Hkv, cap, hd] laid end to end
+int k_rope_batched(orn_ctx* ctx, cudaStream_t s, bf16_t* x, int B, int Tb, int H, int hd, int dims, float lnb, const int* pos) {
+  const int n = B * Tb * H * (dims / 2);
+  rope_kernel<<<(n + 127) / 128, 128, 0, s>>>(x, B * Tb, H, hd, dims, lnb, pos, 0, Tb);
+  return orn_launch_check(ctx, "rope");
+}
+int k_kv_append_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* k, const bf16_t* v, int B, int Tb, int Hkv, int hd, int cap,
+                        const int* pos, bf16_t* kc, bf16_t* vc) {
+  const int n = B * Tb * Hkv * (hd / 8);
+  kv_append_kernel<<<(n + 127) / 128, 128, 0, s>>>(k, v, B * Tb, Hkv, hd, cap, pos, 0, kc, vc, Tb);
+  return orn_launch_check(ctx, "kv_append");
+}
+int k_sdpa_decode_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* kc, const bf16_t* vc, int B, int Tb,
+                          int Hq, int Hkv, int hd, int cap, const int* pos, float scale, bf16_t* out) {
+  if (hd != 256) ORN_FAIL(ctx, ORN_ERR_ARG, "sdpa_decode: head_dim must be 256");
+  dim3 grid(Hq, B * Tb);
+  sdpa_decode_kernel<<<grid, 1024, 0, s>>>(q, kc, vc, B * Tb, Hq, Hkv, cap, pos, 0, scale, out, Tb);
   return orn_launch_check(ctx, "sdpa_decode");
 }

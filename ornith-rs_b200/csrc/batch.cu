@@ -1,0 +1,513 @@
+// Batched decode: B concurrent sequences, each stepping a verify window of T rows (T = 2 for MTP
+// depth 1) through the whole trunk in one pass over the weights, the routed experts through the
+// expert-parallel block.
+//
+// The reference decodes one sequence (README.md:217-221); this is the same layer sequence
+// (TextModel::forward_capture, src/model/qwen3_5.rs:578-695, and TrunkCapture::rewind, :301-349)
+// over rows laid out sequence-major, [B][T].  What is per sequence stays per sequence: a KV cache
+// [Hkv, cap, 256] per attention layer, a conv window and a ring of T + 1 recurrent states per
+// gated-delta layer, a position and a ring cursor.  What is per row is batched: every projection is
+// one wide product over the B * T rows (tensor cores from 16 rows; the row-invariant mat-vec below
+// that or with ORN_WIDE_EXACT=1), the MoE block is orn_ep_moe_block over all rows (experts split
+// over the ranks of the node when the group has more than one), lm_head is one product and the
+// greedy targets of all rows come back together.  Acceptance is per sequence: commit(keep[b]) moves
+// position and ring cursor by keep[b] and shifts the conv window; nothing is copied for a rollback.
+//
+// With row-invariant products the batched pass reproduces the single-sequence engine bit for bit
+// (same kernels, a sequence index in their grids); that is how it is tested.  With the tensor-core
+// products it agrees to rounding, like the prompt path.
+//
+// Attention over long contexts: the row-invariant kernel walks a sequence's cache once per (query
+// head, row); the batched fast path walks it once per (KV head, 256-key chunk) for the G * T
+// queries that share it and merges the chunks in a second kernel (split-KV; 5.4 GB of cache per
+// step at 64 sequences x 4096 tokens is the largest HBM stream of the step after the experts).
+#include <algorithm>
+#include <cstring>
+#include <type_traits>
+
+#include "fused.h"
+#include "model_types.h"
+#include "orn_internal.h"
+
+#define CK(call)                     \
+  do {                               \
+    int rc__ = (call);               \
+    if (rc__ != ORN_OK) return rc__; \
+  } while (0)
+
+
+namespace {
+
+constexpr int kChunk = 256;  // keys per CTA of the split-KV attention
+constexpr int kPartStride = 264;  // floats per (query, chunk) partial: m, s, pad, o[256]
+
+ORN_D float bflo(uint32_t v) { return __uint_as_float(v << 16); }
+ORN_D float bfhi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+ORN_D void widen(const uint4& v, float* f) {
+  f[0] = bflo(v.x); f[1] = bfhi(v.x); f[2] = bflo(v.y); f[3] = bfhi(v.y);
+  f[4] = bflo(v.z); f[5] = bfhi(v.z); f[6] = bflo(v.w); f[7] = bfhi(v.w);
+}
+
+// rows of n elements: dst[map[r]] = src[r]
+__global__ void scatter_rows_kernel(const bf16_t* src, const uint32_t* map, int n, bf16_t* dst) {
+  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)blockIdx.x * n);
+  uint4* d = reinterpret_cast<uint4*>(dst + (size_t)map[blockIdx.x] * n);
+  for (int i = threadIdx.x; i < n / 8; i += blockDim.x) d[i] = s[i];
+}
+__global__ void conv_map_kernel(uint32_t* map, int B, int T, int rows_per_seq, int S) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < B * T) map[r] = (uint32_t)((r / T) * rows_per_seq + S + r % T);
+}
+// accept keep[b] rows of sequence b's window: position and ring cursor move, the conv windows of
+// every gated-delta layer shift so that their first S rows are the last S rows kept
+__global__ void commit_kernel(int* pos, int* cur, const int* keep, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) { pos[b] += keep[b]; cur[b] += keep[b]; }
+}
+__global__ void conv_shift_batched_kernel(bf16_t* const* bufs, const int* keep, int S, int D, int rows_per_seq) {
+  bf16_t* buf = bufs[blockIdx.y] + (size_t)blockIdx.z * rows_per_seq * D;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;  // over D/8 16-byte pieces
+  if (c >= D / 8) return;
+  const int k = keep[blockIdx.z];
+  uint4* p = reinterpret_cast<uint4*>(buf);
+  for (int j = 0; j < S; ++j) p[(size_t)j * (D / 8) + c] = p[(size_t)(j + k) * (D / 8) + c];
+}
+__global__ void fill_f32_kernel(float* p, size_t n, uint64_t seed, float std) {
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint64_t x = seed + i * 0x9e3779b97f4a7c15ull;
+  x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+  x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+  x ^= x >> 31;
+  const float u = ((float)(x >> 40) + 0.5f) * (1.0f / 16777216.0f) - 0.5f;  // uniform (-0.5, 0.5)
+  p[i] = std * 3.4641016f * u;
+}
+__global__ void set_ints_kernel(int* p, int n, int v) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = v;
+}
+
+// ---- split-KV attention over the caches of B sequences (fast path) ------------------------------
+// grid (chunks, Hkv, B), 8 warps.  NQ = G * Tb queries share this KV head: query j is head
+// kvh * G + j / Tb, window row j % Tb.  Warp w takes keys chunk*256 + w, + 8, ...; a lane holds 8 of
+// the 256 dims.  Per query an online softmax over the warp's keys, then the 8 warps' partials merge
+// through shared memory and the CTA writes one (max, sum, out[256]) per query.
+template <int NQ>
+__global__ void __launch_bounds__(256) battn_partial_kernel(const bf16_t* __restrict__ q /*[B*Tb, Hq, 256]*/,
+                                                            const bf16_t* __restrict__ kc, const bf16_t* __restrict__ vc,
+                                                            const int* __restrict__ pos, int Tb, int Hq, int Hkv, int cap,
+                                                            float scale, float* __restrict__ part, int nchunks) {
+  constexpr int HD = 256;
+  extern __shared__ __align__(16) float bsm[];
+  float* qs = bsm;                       // [NQ][256] scaled queries
+  float* red = bsm + NQ * HD;            // [8 warps][NQ][258]
+  const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = Hq / Hkv;
+  const int p0 = pos[b];
+  const int Lmax = min(cap, p0 + Tb);  // keys any row of the window may see
+  float* out = part + (((size_t)b * Hkv + kvh) * nchunks + chunk) * NQ * kPartStride;
+  if (chunk * kChunk >= Lmax) {  // nothing to do for this chunk: an empty partial
+    for (int j = threadIdx.x; j < NQ; j += blockDim.x) { out[(size_t)j * kPartStride] = -INFINITY; out[(size_t)j * kPartStride + 1] = 0.f; }
+    return;
+  }
+  for (int i = threadIdx.x; i < NQ * HD; i += blockDim.x) {
+    const int j = i / HD, d = i - j * HD;
+    const int h = kvh * G + j / Tb, tl = j % Tb;
+    qs[i] = bf2f(q[(((size_t)b * Tb + tl) * Hq + h) * HD + d]) * scale;
+  }
+  __syncthreads();
+  float m[NQ], s[NQ], o[NQ][8];
+#pragma unroll
+  for (int j = 0; j < NQ; ++j) {
+    m[j] = -INFINITY; s[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[j][i] = 0.f;
+  }
+  const size_t base = (((size_t)b * Hkv + kvh) * cap) * HD + 8 * lane;
+  const int kend = min(Lmax, (chunk + 1) * kChunk);
+  for (int n = chunk * kChunk + warp; n < kend; n += 8) {
+    float kf[8], vf[8];
+    widen(ldg128(kc + base + (size_t)n * HD), kf);
+    widen(ldg128(vc + base + (size_t)n * HD), vf);
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) {
+      if (n < p0 + (j % Tb) + 1) {  // causal inside the window (warp-uniform)
+        const float4 qa = *reinterpret_cast<const float4*>(qs + j * HD + 8 * lane);
+        const float4 qb = *reinterpret_cast<const float4*>(qs + j * HD + 8 * lane + 4);
+        float acc = qa.x * kf[0];
+        acc = fmaf(qa.y, kf[1], acc); acc = fmaf(qa.z, kf[2], acc); acc = fmaf(qa.w, kf[3], acc);
+        acc = fmaf(qb.x, kf[4], acc); acc = fmaf(qb.y, kf[5], acc); acc = fmaf(qb.z, kf[6], acc); acc = fmaf(qb.w, kf[7], acc);
+        const float sc = warp_sum(acc);
+        const float nm = fmaxf(m[j], sc);
+        const float f = orn_expf(m[j] - nm), e = orn_expf(sc - nm);
+        m[j] = nm;
+        s[j] = fmaf(s[j], f, e);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[j][i] = fmaf(o[j][i], f, e * vf[i]);
+      }
+    }
+  }
+  // the 8 warps' partials -> one per query
+#pragma unroll
+  for (int j = 0; j < NQ; ++j) {
+    float* r = red + ((size_t)warp * NQ + j) * 258;
+    if (lane == 0) { r[0] = m[j]; r[1] = s[j]; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[2 + 8 * lane + i] = o[j][i];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < NQ * HD; idx += blockDim.x) {
+    const int j = idx / HD, d = idx - j * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) M = fmaxf(M, red[((size_t)w * NQ + j) * 258]);
+    float S = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const float* r = red + ((size_t)w * NQ + j) * 258;
+      const float f = r[0] == -INFINITY ? 0.f : orn_expf(r[0] - M);
+      S = fmaf(r[1], f, S);
+      O = fmaf(r[2 + d], f, O);
+    }
+    float* dst = out + (size_t)j * kPartStride;
+    if (d == 0) { dst[0] = M; dst[1] = S; }
+    dst[8 + d] = O;
+  }
+}
+// grid (NQ, Hkv, B), 256 threads (one per dim): merge the chunks, apply the output gate
+__global__ void __launch_bounds__(256) battn_merge_kernel(const float* __restrict__ part, const bf16_t* __restrict__ qg /*[B*Tb, Hq, 512]: query | gate*/,
+                                                          int Tb, int Hq, int Hkv, int nchunks, int NQ, bf16_t* __restrict__ out /*[B*Tb, Hq*256]*/) {
+  constexpr int HD = 256;
+  const int j = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
+  const int G = Hq / Hkv, h = kvh * G + j / Tb, tl = j % Tb;
+  const float* p = part + (((size_t)b * Hkv + kvh) * nchunks) * NQ * kPartStride + (size_t)j * kPartStride;
+  float M = -INFINITY;
+  for (int c = 0; c < nchunks; ++c) M = fmaxf(M, p[(size_t)c * NQ * kPartStride]);
+  float S = 0.f, O = 0.f;
+  for (int c = 0; c < nchunks; ++c) {
+    const float* pc = p + (size_t)c * NQ * kPartStride;
+    const float f = pc[0] == -INFINITY ? 0.f : orn_expf(pc[0] - M);
+    S = fmaf(pc[1], f, S);
+    O = fmaf(pc[8 + d], f, O);
+  }
+  const float att = bfr(O / S);
+  const size_t row = (size_t)b * Tb + tl;
+  const float gate = bf2f(qg[(row * Hq + h) * 2 * HD + HD + d]);
+  out[(row * Hq + h) * HD + d] = f2bf(orn_sigmoid_bf(gate) * att);
+}
+
+template <int NQ>
+int launch_battn(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* kc, const bf16_t* vc, const int* pos, int B, int Tb,
+                 int Hq, int Hkv, int cap, float scale, float* part, int nchunks) {
+  const size_t smem = sizeof(float) * ((size_t)NQ * 256 + (size_t)8 * NQ * 258);
+  static bool granted[64] = {};
+  if (smem > 48 * 1024 && ctx->device < 64 && !granted[ctx->device]) {
+    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(battn_partial_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    granted[ctx->device] = true;
+  }
+  dim3 grid(nchunks, Hkv, B);
+  battn_partial_kernel<NQ><<<grid, 256, smem, s>>>(q, kc, vc, pos, Tb, Hq, Hkv, cap, scale, part, nchunks);
+  return orn_launch_check(ctx, "battn_partial");
+}
+
+}  // namespace
+
+struct orn_batch {
+  orn_model* m = nullptr;
+  orn_ep *own_ep = nullptr, *own_ep_exact = nullptr;  // one-rank groups for calls that pass none (made on first use)
+  int B = 0, Tmax = 0, cap = 0, nring = 0, conv_rows = 0;
+  bool exact = false;  // ORN_BATCH_EXACT or ORN_WIDE_EXACT=1: every product row-invariant
+  std::vector<bf16_t*> kc, vc, conv;  // per layer
+  std::vector<float*> ring;           // per layer: [B][nring][Hv,128,128]
+  bf16_t** conv_table = nullptr;
+  int n_gdn = 0;
+  int *pos = nullptr, *cur = nullptr, *keep = nullptr;  // device [B]
+  std::vector<int> h_pos;
+  std::vector<void*> allocs;
+  // activation scratch for R = B * Tmax rows
+  uint32_t *ids, *targets, *conv_map;
+  bf16_t *x, *n, *r, *h, *n2, *mo, *qkv, *z, *a, *b, *gq, *gk, *gv, *beta, *gy, *gated;
+  float* gg;
+  bf16_t *qg, *aq, *agate, *ak, *av, *att, *agated, *logits;
+  float *greedy_scratch, *part;
+  int part_chunks = 0;
+  int last_T = 0;
+  // this rank's slices of the routed experts when the group has several ranks (views, not copies)
+  int shard_rank = -1, shard_world = 0;
+  std::vector<orn_linear*> views;  // [layer][3]
+};
+
+namespace {
+
+int batch_mm(orn_batch* bt, const orn_linear* L, const bf16_t* x, int R, bf16_t* y) {
+  orn_ctx* ctx = bt->m->ctx;
+  if (R >= 16 && !bt->exact && L->K % 64 == 0) return f_qgemm(ctx, ctx->stream, L, x, R, y, L->O, nullptr, nullptr);
+  for (int r = 0; r < R; r += kMaxRows) {
+    const int n = std::min(kMaxRows, R - r);
+    CK(k_gemv(ctx, ctx->stream, L, x + (size_t)r * L->K, n, y + (size_t)r * L->O, 0));
+  }
+  return ORN_OK;
+}
+
+// views of this rank's E / world experts of every layer's routed matrices
+int ensure_shards(orn_batch* bt, int rank, int world) {
+  if (bt->shard_rank == rank && bt->shard_world == world) return ORN_OK;
+  for (orn_linear* v : bt->views) delete v;
+  bt->views.clear();
+  orn_model* m = bt->m;
+  if (m->cfg.n_experts % world) ORN_FAIL(m->ctx, ORN_ERR_ARG, "batch: the experts do not split evenly over the ranks");
+  const int el = m->cfg.n_experts / world;
+  for (const Layer& ly : m->layers) {
+    const orn_linear* full[3] = {ly.moe.sw_gate, ly.moe.sw_up, ly.moe.sw_down};
+    for (const orn_linear* f : full) {
+      orn_linear* v = new orn_linear(*f);
+      v->E = el;
+      const size_t off = (size_t)rank * el * f->O * f->rec;
+      v->w = f->w + off; v->s = f->s + off; v->b = f->b + off;
+      v->w_bytes = (size_t)el * f->O * f->rec;
+      v->owns = false;
+      bt->views.push_back(v);
+    }
+  }
+  bt->shard_rank = rank; bt->shard_world = world;
+  return ORN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t orn_batch_destroy(orn_batch* bt) {
+  if (!bt) return ORN_OK;
+  cudaStreamSynchronize(bt->m->ctx->stream);
+  for (void* p : bt->allocs) cudaFree(p);
+  for (orn_linear* v : bt->views) delete v;
+  if (bt->own_ep) orn_ep_destroy(bt->own_ep);
+  if (bt->own_ep_exact) orn_ep_destroy(bt->own_ep_exact);
+  delete bt;
+  return ORN_OK;
+}
+
+int32_t orn_batch_create(orn_model* m, int32_t B, int32_t T_max, int32_t cap, int32_t flags, orn_batch** out) {
+  if (!m || !out) return ORN_ERR_ARG;
+  *out = nullptr;
+  CK(orn_model_finalize(m));
+  orn_ctx* ctx = m->ctx;
+  const orn_config& c = m->cfg;
+  if (B < 1 || T_max < 1 || T_max > kMaxRows || cap < 8) ORN_FAIL(ctx, ORN_ERR_ARG, "batch_create: 1..4 rows per window, at least one sequence");
+  orn_batch* bt = new orn_batch();
+  bt->m = m; bt->B = B; bt->Tmax = T_max; bt->cap = cap; bt->nring = T_max + 1;
+  bt->exact = (flags & ORN_BATCH_EXACT) != 0 || orn_wide_exact();
+  const int S = c.gdn_conv_kernel - 1, D = orn_conv_dim(c);
+  bt->conv_rows = S + T_max;
+  bt->kc.assign(c.n_layers, nullptr); bt->vc.assign(c.n_layers, nullptr);
+  bt->conv.assign(c.n_layers, nullptr); bt->ring.assign(c.n_layers, nullptr);
+  bt->h_pos.assign(B, 0);
+  int rc = ORN_OK;
+  auto A = [&](auto** p, size_t n) {
+    if (rc != ORN_OK) return;
+    void* d = nullptr;
+    rc = orn_alloc(ctx, sizeof(**p) * (n ? n : 1), &d);
+    if (rc == ORN_OK) { bt->allocs.push_back(d); *p = (std::remove_reference_t<decltype(**p)>*)d; }
+  };
+  const size_t kvsz = (size_t)B * c.n_kv_heads * cap * c.head_dim;
+  const size_t ssz = (size_t)c.gdn_v_heads * 128 * 128;
+  std::vector<bf16_t*> table;
+  for (int i = 0; i < c.n_layers; ++i) {
+    if (m->layers[i].linear) {
+      A(&bt->conv[i], (size_t)B * bt->conv_rows * D);
+      A(&bt->ring[i], (size_t)B * bt->nring * ssz);
+      table.push_back(bt->conv[i]);
+    } else {
+      A(&bt->kc[i], kvsz);
+      A(&bt->vc[i], kvsz);
+    }
+  }
+  bt->n_gdn = (int)table.size();
+  const size_t R = (size_t)B * T_max, H = c.hidden, VD = (size_t)c.gdn_v_heads * c.gdn_head_dim;
+  const size_t KD = (size_t)c.gdn_k_heads * c.gdn_head_dim, QD = (size_t)c.n_heads * c.head_dim, KVD = (size_t)c.n_kv_heads * c.head_dim;
+  A(&bt->pos, (size_t)B); A(&bt->cur, (size_t)B); A(&bt->keep, (size_t)B);
+  A(&bt->ids, R); A(&bt->targets, R); A(&bt->conv_map, R);
+  A(&bt->x, R * H); A(&bt->n, R * H); A(&bt->r, R * H); A(&bt->h, R * H); A(&bt->n2, R * H); A(&bt->mo, R * H);
+  A(&bt->qkv, R * D); A(&bt->z, R * VD); A(&bt->a, R * c.gdn_v_heads); A(&bt->b, R * c.gdn_v_heads);
+  A(&bt->gq, R * KD); A(&bt->gk, R * KD); A(&bt->gv, R * VD); A(&bt->beta, R * c.gdn_v_heads); A(&bt->gg, R * c.gdn_v_heads);
+  A(&bt->gy, R * VD); A(&bt->gated, R * VD);
+  A(&bt->qg, R * 2 * QD); A(&bt->aq, R * QD); A(&bt->agate, R * QD); A(&bt->ak, R * KVD); A(&bt->av, R * KVD);
+  A(&bt->att, R * QD); A(&bt->agated, R * QD);
+  A(&bt->logits, R * (size_t)c.vocab);
+  A(&bt->greedy_scratch, greedy_scratch_floats((int)R, c.vocab));
+  bt->part_chunks = (cap + kChunk - 1) / kChunk;
+  A(&bt->part, (size_t)B * c.n_kv_heads * bt->part_chunks * 16 * kPartStride);
+  if (rc == ORN_OK && bt->n_gdn) {
+    A(&bt->conv_table, table.size());
+    if (rc == ORN_OK) rc = orn_upload(ctx, bt->conv_table, table.data(), sizeof(bf16_t*) * table.size());
+  }
+  if (rc != ORN_OK) { orn_batch_destroy(bt); return rc; }
+  *out = bt;
+  return orn_batch_reset(bt);
+}
+
+// make_cache for every sequence (cache.rs:160-181): zero conv windows and states, empty KV
+int32_t orn_batch_reset(orn_batch* bt) {
+  if (!bt) return ORN_ERR_ARG;
+  orn_model* m = bt->m;
+  const orn_config& c = m->cfg;
+  const size_t ssz = sizeof(float) * (size_t)c.gdn_v_heads * 128 * 128;
+  for (int i = 0; i < c.n_layers; ++i)
+    if (m->layers[i].linear) {
+      CK(orn_memset(m->ctx, bt->conv[i], 0, sizeof(bf16_t) * (size_t)bt->B * bt->conv_rows * orn_conv_dim(c)));
+      CK(orn_memset(m->ctx, bt->ring[i], 0, ssz * bt->nring * bt->B));
+    }
+  CK(orn_memset(m->ctx, bt->pos, 0, sizeof(int) * bt->B));
+  CK(orn_memset(m->ctx, bt->cur, 0, sizeof(int) * bt->B));
+  std::fill(bt->h_pos.begin(), bt->h_pos.end(), 0);
+  bt->last_T = 0;
+  return orn_sync(m->ctx);
+}
+
+// Benchmark set-up: every sequence as if it had decoded ctx_len tokens: seeded random KV rows, conv
+// windows and recurrent states (the traffic and arithmetic of a step do not depend on the values).
+int32_t orn_batch_fill_random(orn_batch* bt, int32_t ctx_len, uint64_t seed) {
+  if (!bt || ctx_len < 0 || ctx_len + bt->Tmax > bt->cap) return ORN_ERR_ARG;
+  orn_model* m = bt->m;
+  orn_ctx* ctx = m->ctx;
+  const orn_config& c = m->cfg;
+  const size_t kvsz = (size_t)bt->B * c.n_kv_heads * bt->cap * c.head_dim;
+  const size_t ssz = (size_t)c.gdn_v_heads * 128 * 128;
+  for (int i = 0; i < c.n_layers; ++i) {
+    if (m->layers[i].linear) {
+      CK(k_fill_bf16(ctx, ctx->stream, bt->conv[i], (size_t)bt->B * bt->conv_rows * orn_conv_dim(c), seed + 31 * i, 0.f, 0.5f));
+      const size_t n = (size_t)bt->B * bt->nring * ssz;
+      fill_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(bt->ring[i], n, seed + 77 * i, 0.05f);
+      CK(orn_launch_check(ctx, "fill_f32"));
+    } else {
+      CK(k_fill_bf16(ctx, ctx->stream, bt->kc[i], kvsz, seed + 13 * i, 0.f, 1.0f));
+      CK(k_fill_bf16(ctx, ctx->stream, bt->vc[i], kvsz, seed + 17 * i, 0.f, 1.0f));
+    }
+  }
+  set_ints_kernel<<<(bt->B + 127) / 128, 128, 0, ctx->stream>>>(bt->pos, bt->B, ctx_len);
+  CK(orn_launch_check(ctx, "set_ints"));
+  std::fill(bt->h_pos.begin(), bt->h_pos.end(), ctx_len);
+  return orn_sync(ctx);
+}
+
+int32_t orn_batch_positions(orn_batch* bt, int32_t* host_pos) {
+  if (!bt || !host_pos) return ORN_ERR_ARG;
+  for (int b = 0; b < bt->B; ++b) host_pos[b] = bt->h_pos[b];
+  return ORN_OK;
+}
+
+int32_t orn_batch_forward(orn_batch* bt, orn_ep* ep, const uint32_t* host_ids, int32_t T, uint16_t* dev_normed,
+                          uint32_t* host_targets) {
+  if (!bt || !host_ids) return ORN_ERR_ARG;
+  orn_model* m = bt->m;
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  const orn_config& c = m->cfg;
+  if (T < 1 || T > bt->Tmax) ORN_FAIL(ctx, ORN_ERR_ARG, "batch_forward: window wider than the batch was made for");
+  for (int b = 0; b < bt->B; ++b)
+    if (bt->h_pos[b] + T > bt->cap) ORN_FAIL(ctx, ORN_ERR_STATE, "batch_forward: a sequence would pass the cache capacity");
+  const int B = bt->B, R = B * T, H = c.hidden, S = c.gdn_conv_kernel - 1, D = orn_conv_dim(c);
+  const int Hq = c.n_heads, Hkv = c.n_kv_heads, hd = c.head_dim;
+  const bool exact = bt->exact || R < 16;
+  orn_ep* group = ep;
+  if (!group) {
+    orn_ep** own = exact ? &bt->own_ep_exact : &bt->own_ep;
+    if (!*own) CK(orn_ep_init(ctx, nullptr, 0, 1, exact ? ORN_EP_EXACT : 0, own));
+    group = *own;
+  }
+  const int world = orn_ep_world(group), rank = orn_ep_rank(group);
+  if (world > 1) CK(ensure_shards(bt, rank, world));
+  ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(bt->ids, host_ids, sizeof(uint32_t) * (size_t)R, cudaMemcpyHostToDevice, s));
+  conv_map_kernel<<<(R + 127) / 128, 128, 0, s>>>(bt->conv_map, B, T, bt->conv_rows, S);
+  CK(orn_launch_check(ctx, "conv_map"));
+  CK(k_embedding(ctx, s, m->embed, bt->ids, R, bt->x));
+  CK(k_rms_norm(ctx, s, bt->x, m->layers[0].input_ln, R, H, c.rms_eps, bt->n));
+  int max_pos = 0;
+  for (int b = 0; b < B; ++b) max_pos = std::max(max_pos, bt->h_pos[b]);
+  const int NQ = (Hq / Hkv) * T;
+  for (int i = 0; i < c.n_layers; ++i) {
+    const Layer& ly = m->layers[i];
+    if (ly.linear) {
+      CK(batch_mm(bt, ly.in_qkv, bt->n, R, bt->qkv));
+      scatter_rows_kernel<<<R, 128, 0, s>>>(bt->qkv, bt->conv_map, D, bt->conv[i]);  // row (b, t) -> window row S + t of sequence b
+      CK(orn_launch_check(ctx, "scatter_rows"));
+      CK(batch_mm(bt, ly.in_z, bt->n, R, bt->z));
+      CK(batch_mm(bt, ly.in_b, bt->n, R, bt->b));
+      CK(batch_mm(bt, ly.in_a, bt->n, R, bt->a));
+      CK(k_gdn_front_batched(ctx, s, bt->conv[i], (int64_t)bt->conv_rows * D, ly.conv_w, bt->a, bt->b, ly.a_log, ly.dt_bias, B, T,
+                             c.gdn_k_heads, c.gdn_v_heads, c.gdn_head_dim, c.gdn_conv_kernel, 1e-6f, bt->gq, bt->gk, bt->gv,
+                             bt->beta, bt->gg));
+      CK(k_gated_delta_batched(ctx, s, bt->gq, bt->gk, bt->gv, bt->gg, bt->beta, bt->ring[i], bt->nring, bt->cur, B, T,
+                               c.gdn_k_heads, c.gdn_v_heads, bt->gy));
+      CK(k_rms_norm_gated(ctx, s, bt->gy, ly.gdn_norm, bt->z, R * c.gdn_v_heads, c.gdn_head_dim, c.rms_eps, bt->gated));
+      CK(batch_mm(bt, ly.out_proj, bt->gated, R, bt->r));
+    } else {
+      CK(batch_mm(bt, ly.q_proj, bt->n, R, bt->qg));
+      CK(batch_mm(bt, ly.k_proj, bt->n, R, bt->ak));
+      CK(batch_mm(bt, ly.v_proj, bt->n, R, bt->av));
+      CK(k_split_qgate(ctx, s, bt->qg, R, Hq, hd, bt->aq, bt->agate));
+      CK(k_rms_norm(ctx, s, bt->aq, ly.q_norm, R * Hq, hd, c.rms_eps, bt->aq));
+      CK(k_rms_norm(ctx, s, bt->ak, ly.k_norm, R * Hkv, hd, c.rms_eps, bt->ak));
+      CK(k_rope_batched(ctx, s, bt->aq, B, T, Hq, hd, c.rope_dims, m->lnb, bt->pos));
+      CK(k_rope_batched(ctx, s, bt->ak, B, T, Hkv, hd, c.rope_dims, m->lnb, bt->pos));
+      CK(k_kv_append_batched(ctx, s, bt->ak, bt->av, B, T, Hkv, hd, bt->cap, bt->pos, bt->kc[i], bt->vc[i]));
+      const float scale = 1.0f / sqrtf((float)hd);
+      if (exact || hd != 256 || (NQ != 4 && NQ != 8 && NQ != 16)) {
+        CK(k_sdpa_decode_batched(ctx, s, bt->aq, bt->kc[i], bt->vc[i], B, T, Hq, Hkv, hd, bt->cap, bt->pos, scale, bt->att));
+        CK(k_sigmoid_gate(ctx, s, bt->agate, bt->att, R * Hq * hd, 1, bt->agated));
+      } else {
+        const int nchunks = std::min(bt->part_chunks, (max_pos + T + kChunk - 1) / kChunk);
+        int rc2;
+        if (NQ == 16) rc2 = launch_battn<16>(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks);
+        else if (NQ == 8) rc2 = launch_battn<8>(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks);
+        else rc2 = launch_battn<4>(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks);
+        CK(rc2);
+        dim3 grid(NQ, Hkv, B);
+        battn_merge_kernel<<<grid, 256, 0, s>>>(bt->part, bt->qg, T, Hq, Hkv, nchunks, NQ, bt->agated);
+        CK(orn_launch_check(ctx, "battn_merge"));
+      }
+      CK(batch_mm(bt, ly.o_proj, bt->agated, R, bt->r));
+    }
+    CK(k_add_rms_norm(ctx, s, bt->x, bt->r, ly.post_ln, R, H, c.rms_eps, bt->h, bt->n2));
+    const orn_linear* sg = world > 1 ? bt->views[3 * i] : ly.moe.sw_gate;
+    const orn_linear* su = world > 1 ? bt->views[3 * i + 1] : ly.moe.sw_up;
+    const orn_linear* sd = world > 1 ? bt->views[3 * i + 2] : ly.moe.sw_down;
+    CK(orn_ep_moe_block(group, ly.moe.gate, sg, su, sd, ly.moe.sh_gate, ly.moe.sh_up, ly.moe.sh_down, ly.moe.sh_egate, bt->n2, R,
+                        c.top_k, c.norm_topk_prob, bt->mo, nullptr));
+    const bf16_t* nw = i + 1 < c.n_layers ? m->layers[i + 1].input_ln : m->norm;
+    CK(k_add_rms_norm(ctx, s, bt->h, bt->mo, nw, R, H, c.rms_eps, bt->x, bt->n));
+  }
+  if (dev_normed) ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(dev_normed, bt->n, sizeof(bf16_t) * (size_t)R * H, cudaMemcpyDeviceToDevice, s));
+  CK(batch_mm(bt, m->lm_head, bt->n, R, bt->logits));
+  CK(k_greedy(ctx, s, bt->logits, R, c.vocab, 1, bt->targets, bt->greedy_scratch));
+  bt->last_T = T;
+  if (host_targets) return orn_download(ctx, host_targets, bt->targets, sizeof(uint32_t) * (size_t)R);
+  return ORN_OK;
+}
+
+// TrunkCapture::rewind per sequence (qwen3_5.rs:324-348): keep[b] in 1..T rows of the last window
+int32_t orn_batch_commit(orn_batch* bt, const int32_t* host_keep) {
+  if (!bt || !host_keep) return ORN_ERR_ARG;
+  orn_model* m = bt->m;
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  if (bt->last_T == 0) ORN_FAIL(ctx, ORN_ERR_STATE, "batch_commit: no window to commit");
+  for (int b = 0; b < bt->B; ++b)
+    if (host_keep[b] < 1 || host_keep[b] > bt->last_T) ORN_FAIL(ctx, ORN_ERR_ARG, "batch_commit: keep out of range");
+  ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(bt->keep, host_keep, sizeof(int) * bt->B, cudaMemcpyHostToDevice, s));
+  commit_kernel<<<(bt->B + 127) / 128, 128, 0, s>>>(bt->pos, bt->cur, bt->keep, bt->B);
+  CK(orn_launch_check(ctx, "batch_commit"));
+  if (bt->n_gdn > 0) {
+    const int S = m->cfg.gdn_conv_kernel - 1, D = orn_conv_dim(m->cfg);
+    dim3 grid((D / 8 + 127) / 128, bt->n_gdn, bt->B);
+    conv_shift_batched_kernel<<<grid, 128, 0, s>>>(bt->conv_table, bt->keep, S, D, bt->conv_rows);
+    CK(orn_launch_check(ctx, "conv_shift"));
+  }
+  for (int b = 0; b < bt->B; ++b) bt->h_pos[b] += host_keep[b];
+  bt->last_T = 0;
+  return ORN_OK;
+}
+
+}  // extern "C"

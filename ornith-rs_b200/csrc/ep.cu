@@ -225,6 +225,9 @@ int32_t orn_ep_init(orn_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
   return ORN_OK;
 }
 
+int32_t orn_ep_world(const orn_ep* ep) { return ep ? ep->world : 0; }
+int32_t orn_ep_rank(const orn_ep* ep) { return ep ? ep->rank : -1; }
+
 int32_t orn_ep_destroy(orn_ep* ep) {
   if (!ep) return ORN_OK;
   cudaStreamSynchronize(ep->ctx->stream);

@@ -39,6 +39,8 @@ struct FrontParams {
   float* g;                  // [T, Hv]
   int T, S, Kc, D, Dh, Hk, Hv;
   float q_scale, k_scale, eps;
+  int Tb;         // > 0: the T rows are Tb-row windows of T / Tb sequences ...
+  int64_t seq_stride;  // ... whose conv buffers [S + Tcap, D] lie seq_stride elements apart (qkv = rows S.. of each)
 };
 
 // one warp per (token, 128-channel head slot); lane owns 4 channels
@@ -50,9 +52,12 @@ __global__ void gdn_front_kernel(FrontParams p) {
   if (slot >= slots) return;
   const int c0 = slot * p.Dh + lane * 4;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int seq = p.Tb > 0 ? t / p.Tb : 0, tl = p.Tb > 0 ? t - seq * p.Tb : t;
+  const bf16_t* cs = p.conv_state + seq * p.seq_stride;
+  const bf16_t* qk = p.qkv + seq * p.seq_stride;
   for (int i = 0; i < p.Kc; ++i) {
-    const int j = t + i;
-    const bf16_t* src = (j < p.S) ? (p.conv_state + (int64_t)j * p.D) : (p.qkv + (int64_t)(j - p.S) * p.D);
+    const int j = tl + i;
+    const bf16_t* src = (j < p.S) ? (cs + (int64_t)j * p.D) : (qk + (int64_t)(j - p.S) * p.D);
     uint2 xv = *reinterpret_cast<const uint2*>(src + c0);
     float xs[4] = {bf_lo(xv.x), bf_hi(xv.x), bf_lo(xv.y), bf_hi(xv.y)};
 #pragma unroll
@@ -123,6 +128,7 @@ struct DeltaParams {
   int ring_final;      // ring mode: only the state after the last token is kept, in ring[(cur+1)%nring]
   bf16_t* y;           // [T, Hv, 128]
   int T, Hk, Hv;
+  int batched;         // ring mode over sequences: blockIdx.z = sequence, a ring and a cursor per sequence, T rows each
 };
 
 constexpr int kRowsPerCta = 16;
@@ -136,6 +142,12 @@ __global__ void __launch_bounds__(kRowsPerCta * 4) gated_delta_kernel(DeltaParam
   const size_t off = ((size_t)hv * 128 + row) * 128 + lir * 32;
   const float* sin;
   int cur = 0;
+  if (p.batched) {  // this sequence's rows, ring and cursor
+    const size_t z = blockIdx.z;
+    p.q += z * p.T * p.Hk * 128; p.k += z * p.T * p.Hk * 128; p.v += z * p.T * p.Hv * 128;
+    p.g += z * p.T * p.Hv; p.beta += z * p.T * p.Hv; p.y += z * p.T * p.Hv * 128;
+    p.ring += z * p.nring * ssz; p.cur += z;
+  }
   if (p.ring != nullptr) {
     cur = *p.cur;
     sin = p.ring + (size_t)(cur % p.nring) * ssz + off;
@@ -247,6 +259,7 @@ int k_gdn_front(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv_state, const bf
   p.dt_bias = dt_bias; p.conv_next = conv_next; p.conv_input = conv_input_keep;
   p.q = q; p.k = k; p.v = v; p.beta = beta; p.g = g;
   p.T = T; p.S = Kc - 1; p.Kc = Kc; p.D = 2 * Hk * Dh + Hv * Dh; p.Dh = Dh; p.Hk = Hk; p.Hv = Hv;
+  p.Tb = 0; p.seq_stride = 0;
   // powf(dk, -0.5) and its square, cast to bfloat16 (qwen3_5.rs:506,524-525)
   float inv_scale = 1.0f / sqrtf((float)Dh);
   p.q_scale = bfr(inv_scale * inv_scale);
@@ -258,9 +271,9 @@ int k_gdn_front(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv_state, const bf
   return orn_launch_check(ctx, "gdn_front");
 }
 
-static int launch_delta(orn_ctx* ctx, cudaStream_t s, DeltaParams& p) {
+static int launch_delta(orn_ctx* ctx, cudaStream_t s, DeltaParams& p, int B = 1) {
   if (p.Hv % p.Hk != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "gated_delta: Hv % Hk != 0");
-  dim3 grid(128 / kRowsPerCta, p.Hv);
+  dim3 grid(128 / kRowsPerCta, p.Hv, B);
   gated_delta_kernel<<<grid, kRowsPerCta * 4, 0, s>>>(p);
   return orn_launch_check(ctx, "gated_delta");
 }
@@ -271,6 +284,7 @@ int k_gated_delta(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* k
   DeltaParams p;
   p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.state = state; p.snaps = snaps;
   p.ring = nullptr; p.cur = nullptr; p.nring = 1; p.ring_final = 0; p.y = y; p.T = T; p.Hk = Hk; p.Hv = Hv;
+  p.batched = 0;
   return launch_delta(ctx, s, p);
 }
 
@@ -284,5 +298,39 @@ int k_gated_delta_ring(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16
   DeltaParams p;
   p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.state = nullptr; p.snaps = nullptr;
   p.ring = ring; p.cur = cur; p.nring = nring; p.ring_final = final_only; p.y = y; p.T = T; p.Hk = Hk; p.Hv = Hv;
+  p.batched = 0;
   return launch_delta(ctx, s, p);
+}
+
+// ---- B sequences at once: rows sequence-major ([B][Tb] windows); conv buffers [B][S + Tcap, D] with the
+// window's qkv rows already in place behind each sequence's S cached rows; state rings [B][nring][Hv,128,128]
+// with one cursor per sequence, the state after window row t written to slot (cur + 1 + t) % nring
+int k_gdn_front_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, int64_t seq_stride, const bf16_t* cw,
+                        const bf16_t* a, const bf16_t* b, const bf16_t* a_log, const bf16_t* dt_bias, int B, int Tb, int Hk,
+                        int Hv, int Dh, int Kc, float eps, bf16_t* q, bf16_t* k, bf16_t* v, bf16_t* beta, float* g) {
+  if (Dh != 128) ORN_FAIL(ctx, ORN_ERR_ARG, "gdn_front: head dim must be 128");
+  FrontParams p;
+  p.D = 2 * Hk * Dh + Hv * Dh;
+  p.conv_state = conv; p.qkv = conv + (int64_t)(Kc - 1) * p.D; p.cw = cw; p.a_in = a; p.b_in = b; p.a_log = a_log;
+  p.dt_bias = dt_bias; p.conv_next = nullptr; p.conv_input = nullptr;
+  p.q = q; p.k = k; p.v = v; p.beta = beta; p.g = g;
+  p.T = B * Tb; p.S = Kc - 1; p.Kc = Kc; p.Dh = Dh; p.Hk = Hk; p.Hv = Hv;
+  p.Tb = Tb; p.seq_stride = seq_stride;
+  const float inv_scale = 1.0f / sqrtf((float)Dh);
+  p.q_scale = bfr(inv_scale * inv_scale);
+  p.k_scale = bfr(inv_scale);
+  p.eps = eps;
+  const int slots = p.D / Dh;
+  dim3 grid((slots + 3) / 4, B * Tb);
+  gdn_front_kernel<<<grid, 128, 0, s>>>(p);
+  return orn_launch_check(ctx, "gdn_front");
+}
+int k_gated_delta_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* k, const bf16_t* v, const float* g,
+                          const bf16_t* beta, float* rings, int nring, const int* cur, int B, int Tb, int Hk, int Hv, bf16_t* y) {
+  if (Tb + 1 > nring) ORN_FAIL(ctx, ORN_ERR_ARG, "gated_delta: window wider than the ring");
+  DeltaParams p;
+  p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.state = nullptr; p.snaps = nullptr;
+  p.ring = rings; p.cur = cur; p.nring = nring; p.ring_final = 0; p.y = y; p.T = Tb; p.Hk = Hk; p.Hv = Hv;
+  p.batched = 1;
+  return launch_delta(ctx, s, p, B);
 }

@@ -187,7 +187,18 @@ int k_gated_delta_ring(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16
                        int nring, const int* cur, int final_only, int T, int Hk, int Hv,
                        bf16_t* y);
 
+int k_gdn_front_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, int64_t seq_stride, const bf16_t* cw,
+                        const bf16_t* a, const bf16_t* b, const bf16_t* a_log, const bf16_t* dt_bias, int B, int Tb, int Hk,
+                        int Hv, int Dh, int Kc, float eps, bf16_t* q, bf16_t* k, bf16_t* v, bf16_t* beta, float* g);
+int k_gated_delta_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* k, const bf16_t* v, const float* g,
+                          const bf16_t* beta, float* rings, int nring, const int* cur, int B, int Tb, int Hk, int Hv, bf16_t* y);
+
 // attn.cu
+int k_rope_batched(orn_ctx* ctx, cudaStream_t s, bf16_t* x, int B, int Tb, int H, int hd, int dims, float lnb, const int* pos);
+int k_kv_append_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* k, const bf16_t* v, int B, int Tb, int Hkv, int hd, int cap,
+                        const int* pos, bf16_t* kc, bf16_t* vc);
+int k_sdpa_decode_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* kc, const bf16_t* vc, int B, int Tb,
+                          int Hq, int Hkv, int hd, int cap, const int* pos, float scale, bf16_t* out);
 int k_rope(orn_ctx* ctx, cudaStream_t s, bf16_t* x, int T, int H, int hd, int dims, float lnb,
            const int* dev_offset, int offset_add);
 int k_kv_append(orn_ctx* ctx, cudaStream_t s, const bf16_t* k, const bf16_t* v, int T, int Hkv,

@@ -67,7 +67,7 @@ _C2RUST = {"int32_t": "i32", "uint32_t": "u32", "int64_t": "i64", "uint64_t": "u
            "uint16_t": "u16", "uint8_t": "u8", "void": "c_void", "char": "c_char", "orn_ctx": "OrnCtx",
            "orn_linear": "OrnLinear", "orn_model": "OrnModel", "orn_cache": "OrnCache", "orn_config": "OrnConfig",
            "orn_mtp_stats": "OrnMtpStats", "orn_force_draft": "OrnForceDraft", "orn_prof": "OrnProf",
-           "orn_token_cb": "OrnTokenCb", "orn_ep": "OrnEp"}
+           "orn_token_cb": "OrnTokenCb", "orn_ep": "OrnEp", "orn_batch": "OrnBatch"}
 
 
 def _rust_type(ctype):
