@@ -123,6 +123,91 @@ def step_bytes(cfg, T, with_state=True):
     return n_lin * (gdn + state) + n_att * att + cfg.n_layers * moe + head
 
 
+def batch_step_bytes(cfg, B, T, ctx_len, world):
+    """Algorithmic bytes ONE GPU moves for one batched verify step of B local sequences, T rows
+    each, at ctx_len cached positions: every dense weight once; this rank's E / world experts of
+    every layer once (B * T * top_k routes of the whole job touch every expert); per sequence the
+    KV cache of every attention layer once and the gated-delta state once in, T times out."""
+    one = step_bytes(cfg, 1, with_state=False)
+    H, k, E = cfg.hidden, cfg.top_k, cfg.n_experts
+    expert = 2 * cfg.expert_inter * H * 0.5625 + H * cfg.expert_inter * 0.8203125
+    dense = one - cfg.n_layers * E * (1.0 - (1.0 - k / E)) * expert       # step_bytes' routed term at T = 1
+    n_lin = sum(1 for i in range(cfg.n_layers) if (i + 1) % cfg.full_attn_interval)
+    n_att = cfg.n_layers - n_lin
+    kv = n_att * 2 * cfg.n_kv_heads * cfg.head_dim * 2 * ctx_len
+    state = n_lin * cfg.gdn_v_heads * 128 * 128 * 4 * (1 + T)
+    return dense + cfg.n_layers * (E // world) * expert + B * (kv + state)
+
+
+def ep_decode(pkg, ctx, dist, rank, world, model, cfg, steps=8, warmup=3, total_seqs=64, ctx_len=4096, T=2):
+    """BASELINE config 5: batched decode of the whole model, 64 sequences in all at 4096 cached
+    positions each, every sequence stepping a verify window of 2 rows (MTP depth 1) per pass over
+    the weights; sequences split evenly over the ranks (data parallel), the routed experts of every
+    layer split E / N per rank (expert parallel) through the library's own block.  Every rank runs
+    this.  A step = host ids in, trunk forward of B * 2 rows, lm_head, greedy targets of every row
+    back on the host, per-sequence acceptance (keep 1 or 2 at the benchmark's forced p) committed.
+    The MTP head's draft pass (one more attention + MoE layer and a second lm_head per cycle) is not
+    part of the batched engine; tokens/s counts accepted tokens per verify step."""
+    from ornith_rs_b200 import ep
+    if total_seqs % world or cfg.n_experts % world:
+        return None
+    B = total_seqs // world
+    group = None
+    if world > 1:
+        box = [ep.LibEp.unique_id(ctx._lib) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        group = ep.LibEp(ctx, rank, world, box[0])
+    bt = pkg.Batch(model, B, t_max=T, cap=ctx_len + T * (steps + warmup) + 8)
+    bt.fill_random(ctx_len, seed=SEED + rank)
+    rng = np.random.default_rng(SEED + 50 + rank)
+    ids = [rng.integers(0, cfg.vocab, (B, T)).astype(np.uint32) for _ in range(steps + warmup)]
+    keeps = [(1 + (rng.random(B) < FORCE_P)).astype(np.int32) for _ in range(steps + warmup)]
+
+    def step(i):
+        tg, _ = bt.forward(ids[i], ep=group)
+        bt.commit(keeps[i])
+        return tg
+
+    for i in range(warmup):
+        step(i)
+    ctx.sync()
+    if dist is not None:
+        dist.barrier()
+    l0 = ctx.launches()
+    t0 = time.perf_counter()
+    ctx.timer_start()
+    tokens = 0
+    for i in range(warmup, warmup + steps):
+        tg = step(i)
+        tokens += int(keeps[i].sum())
+    ms = ctx.timer_stop()
+    wall = time.perf_counter() - t0
+    launches = ctx.launches() - l0
+    check = int(tg.astype(np.int64).sum())
+    if dist is not None:
+        import torch
+        mx = torch.tensor([ms, wall], dtype=torch.float64, device="cuda")
+        sm = torch.tensor([float(tokens), float(check)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, wall, tokens, check = float(mx[0]), float(mx[1]), int(sm[0]), int(sm[1])
+    bt.free()
+    if group is not None:
+        group.close()
+    peak, which = peaks()
+    per_gpu = batch_step_bytes(cfg, B, T, ctx_len, world)
+    step_ms = ms / steps
+    return {"sequences": total_seqs, "sequences_per_rank": B, "rows_per_step": total_seqs * T, "context": ctx_len,
+            "experts_per_rank": cfg.n_experts // world, "layers": cfg.n_layers, "steps": steps, "ms_per_step": step_ms,
+            "tokens_per_s": tokens / (ms * 1e-3), "e2e_tokens_per_s": tokens / wall,
+            "tokens_per_step": tokens / steps, "bytes_per_gpu_per_step": per_gpu,
+            "frac": per_gpu / (step_ms * 1e-3) / 1e9 / peak, "peak_source": which,
+            "launches_per_step": int(launches // steps), "h2d_bytes_per_step": B * T * 4 + B * 4,
+            "d2h_bytes_per_step": B * T * 4, "targets_checksum": check,
+            "scope": "trunk verify step + lm_head + greedy + per-sequence commit; the MTP head's draft pass is not batched",
+            "parallelism": "dp%d over sequences x ep%d over experts" % (world, world)}
+
+
 def draft_bytes(cfg, head_rows):
     H = cfg.hidden
     QD, KVD = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
@@ -615,6 +700,7 @@ def ours(args):
     epl = ep_moe_layer(pkg, ctx, dist, rank, world)   # every rank takes part
     if epl is not None:
         epl["row_invariant_variant"] = ep_moe_layer(pkg, ctx, dist, rank, world, exact=True)
+    epd = ep_decode(pkg, ctx, dist, rank, world, model, cfg) if cfg.n_layers == 40 or args.ep_decode else None
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -652,7 +738,7 @@ def ours(args):
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": PROMPT_LEN * 4,
                 "d2h_bytes_per_step": int(16 * cycles / args.steps) + 4},
         "gpu_launches": launches, "clocks": clocks, "roofline": roof, "step_roofline": step_roof,
-        "kernels": kt[:12], "isolated_in_proj_launch": iso, "prefill_6621": lp, "ep_moe_layer": epl,
+        "kernels": kt[:12], "isolated_in_proj_launch": iso, "prefill_6621": lp, "ep_moe_layer": epl, "ep_decode": epd,
         "acceptance": accepted / max(cycles, 1), "tokens_per_cycle": args.steps * GEN_TOKENS / max(cycles, 1),
         "mtp_equals_autoregressive": True, "prefill_ms_per_step": prefill_ms / args.steps,
     }
@@ -808,6 +894,7 @@ def main():
     ap.add_argument("--gen-tokens", type=int, default=200, help="tokens per generation (profiling runs use fewer)")
     ap.add_argument("--prompt-len", type=int, default=51)
     ap.add_argument("--n-layers", type=int, default=40, help="fewer layers at the full layer sizes (profiling runs)")
+    ap.add_argument("--ep-decode", action="store_true", help="run the batched expert-parallel decode leg at any layer count")
     ap.add_argument("--workload", default="decode", choices=["decode", "ep-layer"],
                     help="decode: the MTP depth-1 decode loop (the headline); ep-layer: one expert-parallel MoE layer")
     args = ap.parse_args()

@@ -382,6 +382,7 @@ int32_t orn_get_prof(orn_model* m, orn_prof* out);
  * receives the greedy token of every row (syncs).  orn_batch_commit: keep[b] in 1..T. */
 typedef struct orn_batch orn_batch;
 #define ORN_BATCH_EXACT 1 /* flags: row-invariant products at every row count */
+#define ORN_BATCH_SPLIT_ATTN 2 /* flags: split-KV attention at every row count (isolates it for a checker) */
 int32_t orn_batch_create(orn_model* m, int32_t B, int32_t T_max, int32_t cap, int32_t flags, orn_batch** out);
 int32_t orn_batch_destroy(orn_batch* bt);
 int32_t orn_batch_reset(orn_batch* bt);

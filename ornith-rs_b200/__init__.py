@@ -346,10 +346,11 @@ class Batch:
     of every layer's experts, and forward() is collective.  exact=True keeps every product on the
     row-invariant mat-vec (bit-identical to the single-sequence engine)."""
 
-    def __init__(self, model, B, t_max=2, cap=256, exact=False):
+    def __init__(self, model, B, t_max=2, cap=256, exact=False, split_attn=False):
         self.model, self.ctx, self.B, self.t_max, self.cap = model, model.ctx, B, t_max, cap
         h = C.c_void_p()
-        self.ctx.check(self.ctx._lib.orn_batch_create(model.h, B, t_max, cap, 1 if exact else 0, C.byref(h)),
+        self.ctx.check(self.ctx._lib.orn_batch_create(model.h, B, t_max, cap, (1 if exact else 0) | (2 if split_attn else 0),
+                                                      C.byref(h)),
                        "orn_batch_create")
         self.h = h
 

@@ -38,7 +38,7 @@
 
 namespace {
 
-constexpr int kChunk = 256;  // keys per CTA of the split-KV attention
+constexpr int kMinChunk = 128, kMaxChunk = 512;  // keys per CTA of the split-KV attention
 constexpr int kPartStride = 264;  // floats per (query, chunk) partial: m, s, pad, o[256]
 
 ORN_D float bflo(uint32_t v) { return __uint_as_float(v << 16); }
@@ -88,93 +88,201 @@ __global__ void set_ints_kernel(int* p, int n, int v) {
 }
 
 // ---- split-KV attention over the caches of B sequences (fast path) ------------------------------
-// grid (chunks, Hkv, B), 8 warps.  NQ = G * Tb queries share this KV head: query j is head
-// kvh * G + j / Tb, window row j % Tb.  Warp w takes keys chunk*256 + w, + 8, ...; a lane holds 8 of
-// the 256 dims.  Per query an online softmax over the warp's keys, then the 8 warps' partials merge
-// through shared memory and the CTA writes one (max, sum, out[256]) per query.
-template <int NQ>
-__global__ void __launch_bounds__(256) battn_partial_kernel(const bf16_t* __restrict__ q /*[B*Tb, Hq, 256]*/,
-                                                            const bf16_t* __restrict__ kc, const bf16_t* __restrict__ vc,
-                                                            const int* __restrict__ pos, int Tb, int Hq, int Hkv, int cap,
-                                                            float scale, float* __restrict__ part, int nchunks) {
+// grid (chunks, Hkv, B), 4 warps.  The G * Tb <= 16 queries that share a KV head (query j is head
+// kvh * G + j / Tb, window row j % Tb) form the 16-row A operand of mma.sync.m16n8k16 (bf16 in, f32
+// out); a CTA owns `chunk` consecutive keys of one (sequence, KV head), its warps take 16-key tiles
+// round robin.  Per warp a private 3-stage cp.async pipeline brings a tile's K and V rows (16 x 512 B
+// each, rows padded to 528 B so that ldmatrix reads without bank conflicts) into shared memory;
+// rows at or beyond the sequence's length arrive as zeros.  Per tile: S = Q K^T (32 MMAs), online
+// softmax in the base-2 domain on the accumulator fragments, P (bf16) V (32 MMAs, V fragments through
+// ldmatrix.trans).  The warps' partials merge through shared memory and the CTA writes one
+// (max, sum, out[256]) per query; battn_merge_kernel folds the chunks.
+constexpr int kAttWarps = 4;
+constexpr int kAttRowB = 528;                        // bytes per staged row: 256 bf16 + 16 B pad
+constexpr int kAttTile = 16 * kAttRowB;              // one 16-key tile of K or of V
+constexpr int kAttStages = 3;
+constexpr int kAttWarpBytes = kAttStages * 2 * kAttTile;                   // 50688
+constexpr int kAttSmem = 16 * kAttRowB + kAttWarps * kAttWarpBytes;        // Q + the warps' pipelines
+static_assert(kAttWarpBytes >= 16 * 256 * 4 + 2 * 16 * 4, "a warp's partial must fit its pipeline memory");
+
+ORN_D void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+ORN_D void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+ORN_D void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+ORN_D void ldsm4(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+ORN_D void ldsm4t(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+ORN_D void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+ORN_D uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+ORN_D uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__global__ void __launch_bounds__(kAttWarps * 32) battn_partial_kernel(const bf16_t* __restrict__ q /*[B*Tb, Hq, 256]*/,
+                                                                       const bf16_t* __restrict__ kc, const bf16_t* __restrict__ vc,
+                                                                       const int* __restrict__ pos, int Tb, int Hq, int Hkv, int cap,
+                                                                       float scale, float* __restrict__ part, int nchunks, int chunk,
+                                                                       int NQ) {
   constexpr int HD = 256;
-  extern __shared__ __align__(16) float bsm[];
-  float* qs = bsm;                       // [NQ][256] scaled queries
-  float* red = bsm + NQ * HD;            // [8 warps][NQ][258]
-  const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  extern __shared__ __align__(128) uint8_t asm_[];
+  const int ci = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, qd = lane & 3;
   const int G = Hq / Hkv;
   const int p0 = pos[b];
   const int Lmax = min(cap, p0 + Tb);  // keys any row of the window may see
-  float* out = part + (((size_t)b * Hkv + kvh) * nchunks + chunk) * NQ * kPartStride;
-  if (chunk * kChunk >= Lmax) {  // nothing to do for this chunk: an empty partial
+  float* out = part + (((size_t)b * Hkv + kvh) * nchunks + ci) * NQ * kPartStride;
+  const int k0 = ci * chunk;
+  if (k0 >= Lmax) {  // nothing here for this sequence: an empty partial
     for (int j = threadIdx.x; j < NQ; j += blockDim.x) { out[(size_t)j * kPartStride] = -INFINITY; out[(size_t)j * kPartStride + 1] = 0.f; }
     return;
   }
-  for (int i = threadIdx.x; i < NQ * HD; i += blockDim.x) {
-    const int j = i / HD, d = i - j * HD;
-    const int h = kvh * G + j / Tb, tl = j % Tb;
-    qs[i] = bf2f(q[(((size_t)b * Tb + tl) * Hq + h) * HD + d]) * scale;
+  const int k1 = min(Lmax, k0 + chunk);
+  // the 16 query rows (zeros beyond NQ)
+  for (int i = threadIdx.x; i < 16 * 32; i += blockDim.x) {
+    const int j = i >> 5, piece = i & 31;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (j < NQ) {
+      const int h = kvh * G + j / Tb, tl = j % Tb;
+      v = ldg128(q + (((size_t)b * Tb + tl) * Hq + h) * HD + 8 * piece);
+    }
+    *reinterpret_cast<uint4*>(asm_ + j * kAttRowB + 16 * piece) = v;
   }
   __syncthreads();
-  float m[NQ], s[NQ], o[NQ][8];
+  uint8_t* mine = asm_ + 16 * kAttRowB + warp * kAttWarpBytes;
+  const uint32_t q_s = smem_u32(asm_), mine_s = smem_u32(mine);
+  const size_t base = (((size_t)b * Hkv + kvh) * cap) * HD;
+  const int ntiles = (k1 - k0 + 15) / 16;
+  const int my_tiles = ntiles > warp ? (ntiles - warp + kAttWarps - 1) / kAttWarps : 0;
+  auto issue = [&](int i) {  // this warp's i-th tile into stage i % kAttStages
+    if (i < my_tiles) {
+      const int n0 = k0 + 16 * (warp + kAttWarps * i);
+      const uint32_t dst = mine_s + (i % kAttStages) * 2 * kAttTile;
 #pragma unroll
-  for (int j = 0; j < NQ; ++j) {
-    m[j] = -INFINITY; s[j] = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[j][i] = 0.f;
-  }
-  const size_t base = (((size_t)b * Hkv + kvh) * cap) * HD + 8 * lane;
-  const int kend = min(Lmax, (chunk + 1) * kChunk);
-  for (int n = chunk * kChunk + warp; n < kend; n += 8) {
-    float kf[8], vf[8];
-    widen(ldg128(kc + base + (size_t)n * HD), kf);
-    widen(ldg128(vc + base + (size_t)n * HD), vf);
-#pragma unroll
-    for (int j = 0; j < NQ; ++j) {
-      if (n < p0 + (j % Tb) + 1) {  // causal inside the window (warp-uniform)
-        const float4 qa = *reinterpret_cast<const float4*>(qs + j * HD + 8 * lane);
-        const float4 qb = *reinterpret_cast<const float4*>(qs + j * HD + 8 * lane + 4);
-        float acc = qa.x * kf[0];
-        acc = fmaf(qa.y, kf[1], acc); acc = fmaf(qa.z, kf[2], acc); acc = fmaf(qa.w, kf[3], acc);
-        acc = fmaf(qb.x, kf[4], acc); acc = fmaf(qb.y, kf[5], acc); acc = fmaf(qb.z, kf[6], acc); acc = fmaf(qb.w, kf[7], acc);
-        const float sc = warp_sum(acc);
-        const float nm = fmaxf(m[j], sc);
-        const float f = orn_expf(m[j] - nm), e = orn_expf(sc - nm);
-        m[j] = nm;
-        s[j] = fmaf(s[j], f, e);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[j][i] = fmaf(o[j][i], f, e * vf[i]);
+      for (int it = 0; it < 16; ++it) {
+        const int p = it * 32 + lane, row = p >> 5, piece = p & 31;
+        const int n = n0 + row;
+        const int ok = n < Lmax ? 16 : 0;
+        const size_t src = base + (size_t)min(n, cap - 1) * HD + 8 * piece;
+        cp_async16(dst + row * kAttRowB + 16 * piece, kc + src, ok);
+        cp_async16(dst + kAttTile + row * kAttRowB + 16 * piece, vc + src, ok);
       }
     }
+    cp_async_commit();
+  };
+  float o[32][4];
+#pragma unroll
+  for (int nt = 0; nt < 32; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows g and g + 8, base-2 domain
+  const float sc2 = scale * 1.4426950408889634f;
+  const int lim0 = p0 + (g % Tb) + 1, lim1 = p0 + ((g + 8) % Tb) + 1;  // keys below these are visible to the row
+  // ldmatrix lane addresses: A (queries), B of Q K^T (keys x dims), B of P V (keys x dims, transposed)
+  const uint32_t a_off = ((lane & 7) + 8 * ((lane >> 3) & 1)) * kAttRowB + 16 * (lane >> 4);
+  const uint32_t k_off = ((lane & 7) + 8 * (lane >> 4)) * kAttRowB + 16 * ((lane >> 3) & 1);
+  const uint32_t v_off = ((lane & 7) + 8 * ((lane >> 3) & 1)) * kAttRowB + 16 * (lane >> 4);
+  issue(0);
+  issue(1);
+  for (int i = 0; i < my_tiles; ++i) {
+    issue(i + 2);
+    cp_async_wait<2>();
+    __syncwarp();
+    const uint32_t ks = mine_s + (i % kAttStages) * 2 * kAttTile, vs = ks + kAttTile;
+    const int n0 = k0 + 16 * (warp + kAttWarps * i);
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      uint32_t a[4], bk[4];
+      ldsm4(q_s + a_off + 32 * kk, a);
+      ldsm4(ks + k_off + 32 * kk, bk);
+      mma16816(s[0], a, bk[0], bk[1]);
+      mma16816(s[1], a, bk[2], bk[3]);
+    }
+    const bool all_visible = n0 + 16 <= p0 + 1;  // warp-uniform: no row of the window masks a key of this tile
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = n0 + 8 * nt + 2 * qd + (c & 1);
+        const float v = s[nt][c] * sc2;
+        s[nt][c] = (all_visible || key < (c < 2 ? lim0 : lim1)) ? v : -INFINITY;
+      }
+    float x0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+    float x1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+    x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, 1)); x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, 2));
+    x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, 1)); x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, 2));
+    const float n0m = fmaxf(m0, x0), n1m = fmaxf(m1, x1);
+    const float u0 = n0m == -INFINITY ? 0.f : n0m, u1 = n1m == -INFINITY ? 0.f : n1m;  // a row that has seen no key yet
+    const float c0 = exp2f(m0 - u0), c1 = exp2f(m1 - u1);
+    m0 = n0m; m1 = n1m;
+    float pr[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      pr[nt][0] = exp2f(s[nt][0] - u0); pr[nt][1] = exp2f(s[nt][1] - u0);
+      pr[nt][2] = exp2f(s[nt][2] - u1); pr[nt][3] = exp2f(s[nt][3] - u1);
+    }
+    l0 = l0 * c0 + (pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1]);
+    l1 = l1 * c1 + (pr[0][2] + pr[0][3] + pr[1][2] + pr[1][3]);
+    if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {
+#pragma unroll
+      for (int nt = 0; nt < 32; ++nt) { o[nt][0] *= c0; o[nt][1] *= c0; o[nt][2] *= c1; o[nt][3] *= c1; }
+    }
+    uint32_t pa[4] = {pack_bf16x2(pr[0][0], pr[0][1]), pack_bf16x2(pr[0][2], pr[0][3]), pack_bf16x2(pr[1][0], pr[1][1]),
+                      pack_bf16x2(pr[1][2], pr[1][3])};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      uint32_t bv[4];
+      ldsm4t(vs + v_off + 32 * j, bv);
+      mma16816(o[2 * j], pa, bv[0], bv[1]);
+      mma16816(o[2 * j + 1], pa, bv[2], bv[3]);
+    }
+    __syncwarp();  // the stage is refilled by the next iteration's issue
   }
-  // the 8 warps' partials -> one per query
+  cp_async_wait<0>();
+  __syncwarp();
+  // this warp's partial into its own pipeline memory: out[16][256] f32, then max[16], sum[16]
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  float* wo = reinterpret_cast<float*>(mine);
 #pragma unroll
-  for (int j = 0; j < NQ; ++j) {
-    float* r = red + ((size_t)warp * NQ + j) * 258;
-    if (lane == 0) { r[0] = m[j]; r[1] = s[j]; }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) r[2 + 8 * lane + i] = o[j][i];
+  for (int nt = 0; nt < 32; ++nt) {
+    *reinterpret_cast<float2*>(wo + g * HD + 8 * nt + 2 * qd) = make_float2(o[nt][0], o[nt][1]);
+    *reinterpret_cast<float2*>(wo + (g + 8) * HD + 8 * nt + 2 * qd) = make_float2(o[nt][2], o[nt][3]);
+  }
+  if (qd == 0) {
+    wo[16 * HD + g] = m0; wo[16 * HD + g + 8] = m1;
+    wo[16 * HD + 16 + g] = l0; wo[16 * HD + 16 + g + 8] = l1;
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < NQ * HD; idx += blockDim.x) {
     const int j = idx / HD, d = idx - j * HD;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) M = fmaxf(M, red[((size_t)w * NQ + j) * 258]);
+    for (int w = 0; w < kAttWarps; ++w) M = fmaxf(M, reinterpret_cast<const float*>(asm_ + 16 * kAttRowB + w * kAttWarpBytes)[16 * HD + j]);
     float S = 0.f, O = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      const float* r = red + ((size_t)w * NQ + j) * 258;
-      const float f = r[0] == -INFINITY ? 0.f : orn_expf(r[0] - M);
-      S = fmaf(r[1], f, S);
-      O = fmaf(r[2 + d], f, O);
+    for (int w = 0; w < kAttWarps; ++w) {
+      const float* r = reinterpret_cast<const float*>(asm_ + 16 * kAttRowB + w * kAttWarpBytes);
+      const float mw = r[16 * HD + j];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      S = fmaf(r[16 * HD + 16 + j], f, S);
+      O = fmaf(r[j * HD + d], f, O);
     }
     float* dst = out + (size_t)j * kPartStride;
-    if (d == 0) { dst[0] = M; dst[1] = S; }
+    if (d == 0) { dst[0] = M * 0.6931471805599453f; dst[1] = S; }  // the merge works in the natural-log domain
     dst[8 + d] = O;
   }
 }
+
 // grid (NQ, Hkv, B), 256 threads (one per dim): merge the chunks, apply the output gate
 __global__ void __launch_bounds__(256) battn_merge_kernel(const float* __restrict__ part, const bf16_t* __restrict__ qg /*[B*Tb, Hq, 512]: query | gate*/,
                                                           int Tb, int Hq, int Hkv, int nchunks, int NQ, bf16_t* __restrict__ out /*[B*Tb, Hq*256]*/) {
@@ -197,17 +305,15 @@ __global__ void __launch_bounds__(256) battn_merge_kernel(const float* __restric
   out[(row * Hq + h) * HD + d] = f2bf(orn_sigmoid_bf(gate) * att);
 }
 
-template <int NQ>
 int launch_battn(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* kc, const bf16_t* vc, const int* pos, int B, int Tb,
-                 int Hq, int Hkv, int cap, float scale, float* part, int nchunks) {
-  const size_t smem = sizeof(float) * ((size_t)NQ * 256 + (size_t)8 * NQ * 258);
+                 int Hq, int Hkv, int cap, float scale, float* part, int nchunks, int chunk, int NQ) {
   static bool granted[64] = {};
-  if (smem > 48 * 1024 && ctx->device < 64 && !granted[ctx->device]) {
-    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(battn_partial_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  if (ctx->device < 64 && !granted[ctx->device]) {
+    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(battn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttSmem));
     granted[ctx->device] = true;
   }
   dim3 grid(nchunks, Hkv, B);
-  battn_partial_kernel<NQ><<<grid, 256, smem, s>>>(q, kc, vc, pos, Tb, Hq, Hkv, cap, scale, part, nchunks);
+  battn_partial_kernel<<<grid, kAttWarps * 32, kAttSmem, s>>>(q, kc, vc, pos, Tb, Hq, Hkv, cap, scale, part, nchunks, chunk, NQ);
   return orn_launch_check(ctx, "battn_partial");
 }
 
@@ -218,6 +324,7 @@ struct orn_batch {
   orn_ep *own_ep = nullptr, *own_ep_exact = nullptr;  // one-rank groups for calls that pass none (made on first use)
   int B = 0, Tmax = 0, cap = 0, nring = 0, conv_rows = 0;
   bool exact = false;  // ORN_BATCH_EXACT or ORN_WIDE_EXACT=1: every product row-invariant
+  bool split_attn = false;  // ORN_BATCH_SPLIT_ATTN: the split-KV attention whatever the row count
   std::vector<bf16_t*> kc, vc, conv;  // per layer
   std::vector<float*> ring;           // per layer: [B][nring][Hv,128,128]
   bf16_t** conv_table = nullptr;
@@ -299,6 +406,7 @@ int32_t orn_batch_create(orn_model* m, int32_t B, int32_t T_max, int32_t cap, in
   orn_batch* bt = new orn_batch();
   bt->m = m; bt->B = B; bt->Tmax = T_max; bt->cap = cap; bt->nring = T_max + 1;
   bt->exact = (flags & ORN_BATCH_EXACT) != 0 || orn_wide_exact();
+  bt->split_attn = (flags & ORN_BATCH_SPLIT_ATTN) != 0;
   const int S = c.gdn_conv_kernel - 1, D = orn_conv_dim(c);
   bt->conv_rows = S + T_max;
   bt->kc.assign(c.n_layers, nullptr); bt->vc.assign(c.n_layers, nullptr);
@@ -337,7 +445,7 @@ int32_t orn_batch_create(orn_model* m, int32_t B, int32_t T_max, int32_t cap, in
   A(&bt->att, R * QD); A(&bt->agated, R * QD);
   A(&bt->logits, R * (size_t)c.vocab);
   A(&bt->greedy_scratch, greedy_scratch_floats((int)R, c.vocab));
-  bt->part_chunks = (cap + kChunk - 1) / kChunk;
+  bt->part_chunks = (cap + kMinChunk - 1) / kMinChunk;
   A(&bt->part, (size_t)B * c.n_kv_heads * bt->part_chunks * 16 * kPartStride);
   if (rc == ORN_OK && bt->n_gdn) {
     A(&bt->conv_table, table.size());
@@ -454,16 +562,16 @@ int32_t orn_batch_forward(orn_batch* bt, orn_ep* ep, const uint32_t* host_ids, i
       CK(k_rope_batched(ctx, s, bt->ak, B, T, Hkv, hd, c.rope_dims, m->lnb, bt->pos));
       CK(k_kv_append_batched(ctx, s, bt->ak, bt->av, B, T, Hkv, hd, bt->cap, bt->pos, bt->kc[i], bt->vc[i]));
       const float scale = 1.0f / sqrtf((float)hd);
-      if (exact || hd != 256 || (NQ != 4 && NQ != 8 && NQ != 16)) {
+      if ((exact && !bt->split_attn) || hd != 256 || NQ > 16) {
         CK(k_sdpa_decode_batched(ctx, s, bt->aq, bt->kc[i], bt->vc[i], B, T, Hq, Hkv, hd, bt->cap, bt->pos, scale, bt->att));
         CK(k_sigmoid_gate(ctx, s, bt->agate, bt->att, R * Hq * hd, 1, bt->agated));
       } else {
-        const int nchunks = std::min(bt->part_chunks, (max_pos + T + kChunk - 1) / kChunk);
-        int rc2;
-        if (NQ == 16) rc2 = launch_battn<16>(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks);
-        else if (NQ == 8) rc2 = launch_battn<8>(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks);
-        else rc2 = launch_battn<4>(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks);
-        CK(rc2);
+        // keys per CTA: about six CTAs per SM over the whole launch, 128..512, a multiple of 64
+        const int maxL = max_pos + T;
+        int chunk = (int)(((int64_t)maxL * B * Hkv / (ctx->sm_count * 6) + 63) / 64 * 64);
+        chunk = std::min(kMaxChunk, std::max(kMinChunk, chunk));
+        const int nchunks = (maxL + chunk - 1) / chunk;
+        CK(launch_battn(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks, chunk, NQ));
         dim3 grid(NQ, Hkv, B);
         battn_merge_kernel<<<grid, 256, 0, s>>>(bt->part, bt->qg, T, Hq, Hkv, nchunks, NQ, bt->agated);
         CK(orn_launch_check(ctx, "battn_merge"));
