@@ -261,6 +261,14 @@ int32_t orn_rope(orn_ctx* ctx, uint16_t* dev_x, int32_t T, int32_t H, int32_t hd
 int32_t orn_sdpa_decode(orn_ctx* ctx, const uint16_t* dev_q, const uint16_t* dev_kc,
                         const uint16_t* dev_vc, int32_t T, int32_t Hq, int32_t Hkv, int32_t hd,
                         int32_t cap, int32_t offset, float scale, uint16_t* dev_out);
+/* The prompt path's attention (the causal scaled_dot_product_attention of a chunk,
+ * src/model/qwen3_5.rs:430-470): the same contract as orn_sdpa_decode for any T, computed on the
+ * warp-level tensor cores with an online softmax (head_dim 256).  Agrees with orn_sdpa_decode to
+ * rounding, not bit for bit (the reference exempts the prompt path from row invariance,
+ * src/generate.rs:99). */
+int32_t orn_sdpa_prefill(orn_ctx* ctx, const uint16_t* dev_q, const uint16_t* dev_kc,
+                         const uint16_t* dev_vc, int32_t T, int32_t Hq, int32_t Hkv, int32_t hd,
+                         int32_t cap, int32_t offset, float scale, uint16_t* dev_out);
 
 /* ---- greedy sampling (src/ops/sample.rs:134-147,186-191) */
 int32_t orn_greedy(orn_ctx* ctx, const uint16_t* dev_logits, int32_t T, int32_t V,

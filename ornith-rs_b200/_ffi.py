@@ -110,6 +110,7 @@ SIGNATURES = {
     "orn_gated_delta": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "orn_rope": (i32, [vp, vp, i32, i32, i32, i32, f32, i32]),
     "orn_sdpa_decode": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
+    "orn_sdpa_prefill": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
     "orn_greedy": (i32, [vp, vp, i32, i32, i32, vp]),
     "orn_greedy_static": (i32, [vp, vp, i32, i32, i32, vp]),
     "orn_model_create": (i32, [vp, C.POINTER(Config), c_void_pp]),

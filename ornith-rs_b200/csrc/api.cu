@@ -516,6 +516,20 @@ int32_t orn_sdpa_decode(orn_ctx* ctx, const uint16_t* q, const uint16_t* kc, con
   return k_sdpa_decode(ctx, ctx->stream, q, kc, vc, T, Hq, Hkv, hd, cap, nullptr, offset, scale, out);
 }
 
+int32_t orn_sdpa_prefill(orn_ctx* ctx, const uint16_t* q, const uint16_t* kc, const uint16_t* vc,
+                         int32_t T, int32_t Hq, int32_t Hkv, int32_t hd, int32_t cap,
+                         int32_t offset, float scale, uint16_t* out) {
+  if (!ctx || !q || !kc || !vc || !out || T < 1 || offset < 0) return ORN_ERR_ARG;
+  if (offset + T > cap) ORN_FAIL(ctx, ORN_ERR_ARG, "sdpa_prefill: chunk exceeds the cache capacity");
+  int* pos = nullptr;
+  CK(orn_alloc(ctx, sizeof(int), (void**)&pos));
+  int rc = orn_upload(ctx, pos, &offset, sizeof(int));
+  if (rc == ORN_OK) rc = k_flash_prefill(ctx, ctx->stream, q, kc, vc, T, Hq, Hkv, hd, cap, pos, scale, out);
+  if (rc == ORN_OK) rc = orn_sync(ctx);
+  orn_free(ctx, pos);
+  return rc;
+}
+
 int32_t orn_greedy(orn_ctx* ctx, const uint16_t* logits, int32_t T, int32_t V, int32_t normalize,
                    uint32_t* tokens) {
   if (!ctx || !logits || !tokens || T < 1 || V < 1) return ORN_ERR_ARG;

@@ -27,6 +27,7 @@
 
 #include "fused.h"
 #include "model_types.h"
+#include "mma_bf16.cuh"
 #include "orn_internal.h"
 
 #define CK(call)                     \
@@ -104,30 +105,6 @@ constexpr int kAttStages = 3;
 constexpr int kAttWarpBytes = kAttStages * 2 * kAttTile;                   // 50688
 constexpr int kAttSmem = 16 * kAttRowB + kAttWarps * kAttWarpBytes;        // Q + the warps' pipelines
 static_assert(kAttWarpBytes >= 16 * 256 * 4 + 2 * 16 * 4, "a warp's partial must fit its pipeline memory");
-
-ORN_D void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-ORN_D void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-ORN_D void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-ORN_D void ldsm4(uint32_t addr, uint32_t* r) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-ORN_D void ldsm4t(uint32_t addr, uint32_t* r) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-ORN_D void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-ORN_D uint32_t pack_bf16x2(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-ORN_D uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __global__ void __launch_bounds__(kAttWarps * 32) battn_partial_kernel(const bf16_t* __restrict__ q /*[B*Tb, Hq, 256]*/,
                                                                        const bf16_t* __restrict__ kc, const bf16_t* __restrict__ vc,
@@ -307,11 +284,8 @@ __global__ void __launch_bounds__(256) battn_merge_kernel(const float* __restric
 
 int launch_battn(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* kc, const bf16_t* vc, const int* pos, int B, int Tb,
                  int Hq, int Hkv, int cap, float scale, float* part, int nchunks, int chunk, int NQ) {
-  static bool granted[64] = {};
-  if (ctx->device < 64 && !granted[ctx->device]) {
-    ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(battn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttSmem));
-    granted[ctx->device] = true;
-  }
+  int rc = orn_grant_smem(ctx, reinterpret_cast<const void*>(battn_partial_kernel), kAttSmem);
+  if (rc != ORN_OK) return rc;
   dim3 grid(nchunks, Hkv, B);
   battn_partial_kernel<<<grid, kAttWarps * 32, kAttSmem, s>>>(q, kc, vc, pos, Tb, Hq, Hkv, cap, scale, part, nchunks, chunk, NQ);
   return orn_launch_check(ctx, "battn_partial");

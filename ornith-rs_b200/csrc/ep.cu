@@ -283,14 +283,14 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
   EPCK(k_grouped_gemv(ctx, s, sh_egate, dev_x, ep->seg1, ep->gs, nullptr, R));
   const bool wide_shared = !ep->exact && R >= 16 && H % 64 == 0 && SI % 64 == 0;
   if (wide_shared) {  // like the routed experts: one dense contraction per matrix over all R rows
-    EPCK(f_qgemm(ctx, s, sh_gate, dev_x, R, ep->sg, SI, nullptr, nullptr, 0, 16));  // one tile shape at every world size
-    EPCK(f_qgemm(ctx, s, sh_up, dev_x, R, ep->su, SI, nullptr, nullptr, 0, 16));
+    EPCK(f_qgemm(ctx, s, sh_gate, dev_x, R, ep->sg, SI, nullptr, nullptr));  // a row's bits do not depend on the tile shape
+    EPCK(f_qgemm(ctx, s, sh_up, dev_x, R, ep->su, SI, nullptr, nullptr));
   } else {
     EPCK(k_grouped_gemv(ctx, s, sh_gate, dev_x, ep->seg1, ep->sg, nullptr, R));
     EPCK(k_grouped_gemv(ctx, s, sh_up, dev_x, ep->seg1, ep->su, nullptr, R));
   }
   EPCK(k_swiglu(ctx, s, ep->sg, ep->su, R * SI, ep->sact));
-  if (wide_shared) EPCK(f_qgemm(ctx, s, sh_down, ep->sact, R, ep->sy, H, nullptr, nullptr, 0, 16));
+  if (wide_shared) EPCK(f_qgemm(ctx, s, sh_down, ep->sact, R, ep->sy, H, nullptr, nullptr));
   else EPCK(k_grouped_gemv(ctx, s, sh_down, ep->sact, ep->seg1, ep->sy, nullptr, R));
   // ---- owner: this rank's routes, sorted by expert
   ep_map_kernel<<<(routes + 255) / 256, 256, 0, s>>>(all_inds, routes, ep->rank * el, el, ep->rhs_local);

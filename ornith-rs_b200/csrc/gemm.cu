@@ -70,6 +70,7 @@ struct GemmParams {
   const uint32_t* row_map;   // nullable: output row of sorted row p
   int BN, NT, stages /*IN ring*/, w_stages /*W ring*/, f_tiles;
   uint32_t stage_bytes;
+  uint32_t tmem_cols;  // power of two >= NT * BN (and >= 32): what the CTA takes of tensor memory
   int* err;
 };
 
@@ -385,8 +386,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
     fence_async_smem();
   }
   __syncwarp();
-  if (warp == 0) {  // tensor memory: all 512 columns (one CTA per SM: the launch's shared memory sees to that)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&s_tmem)), "r"(kTmemCols)
+  if (warp == 0) {  // tensor memory: the columns of one item's accumulators (two CTAs of a narrow launch share an SM)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&s_tmem)), "r"(P.tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -507,7 +508,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(P.tmem_cols) : "memory");
   }
 }
 
@@ -683,18 +684,36 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
   // shared memory: the W ring, then as many IN slots as fit (TMA latency wants depth)
   const uint32_t in_raw = L->kind == ORN_BF16 ? kWTileBytes : raw_bytes(L->kind);
   P.stage_bytes = in_raw + (uint32_t)P.NT * BN * 128u;
-  P.w_stages = L->kind == ORN_BF16 ? 1 : kMaxW;
-  const size_t budget = 200 * 1024;
-  P.stages = (int)std::min<size_t>(kMaxIn, (budget - (size_t)P.w_stages * kWTileBytes) / P.stage_bytes);
-  if (P.stages < 2) {
-    P.w_stages = L->kind == ORN_BF16 ? 1 : 2;
-    P.stages = (int)std::min<size_t>(kMaxIn, (budget - (size_t)P.w_stages * kWTileBytes) / P.stage_bytes);
+  P.tmem_cols = 32;
+  while ((int)P.tmem_cols < P.NT * BN) P.tmem_cols <<= 1;
+  // A launch of narrow items with more items than SMs runs two CTAs per SM (each with half the
+  // shared memory and its own accumulator columns): an item's K loop is a chain of short,
+  // latency-bound steps, and two chains per SM overlap.
+  const int est_items = P.f_tiles * (grp ? std::max(L->E, (rows + P.NT * BN - 1) / (P.NT * BN)) : (rows + P.NT * BN - 1) / (P.NT * BN));
+  int ctas = 1;
+  size_t smem = 0;
+  if (P.tmem_cols <= 256 && est_items > ctx->sm_count) {
+    const size_t budget2 = 108 * 1024;
+    const int ws = L->kind == ORN_BF16 ? 1 : 2;
+    const int st = (int)std::min<size_t>(kMaxIn, (budget2 - (size_t)ws * kWTileBytes) / P.stage_bytes);
+    if (st >= 3) {
+      ctas = 2; P.w_stages = ws; P.stages = st;
+      smem = 1024 + (size_t)ws * kWTileBytes + (size_t)st * P.stage_bytes;
+    }
   }
-  if (P.stages < 2) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: stage does not fit twice into shared memory");
-  // One CTA per SM is part of the kernel's contract (it takes all of tensor memory): pad the
-  // launch's shared memory above half of the SM's.
-  size_t smem = 1024 + (size_t)P.w_stages * kWTileBytes + (size_t)P.stages * P.stage_bytes;
-  if (smem < 120 * 1024) smem = 120 * 1024;
+  if (ctas == 1) {
+    P.w_stages = L->kind == ORN_BF16 ? 1 : kMaxW;
+    const size_t budget = 200 * 1024;
+    P.stages = (int)std::min<size_t>(kMaxIn, (budget - (size_t)P.w_stages * kWTileBytes) / P.stage_bytes);
+    if (P.stages < 2) {
+      P.w_stages = L->kind == ORN_BF16 ? 1 : 2;
+      P.stages = (int)std::min<size_t>(kMaxIn, (budget - (size_t)P.w_stages * kWTileBytes) / P.stage_bytes);
+    }
+    if (P.stages < 2) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: stage does not fit twice into shared memory");
+    // one CTA per SM (it may take all of tensor memory): pad the launch's shared memory above half of the SM's
+    smem = 1024 + (size_t)P.w_stages * kWTileBytes + (size_t)P.stages * P.stage_bytes;
+    if (smem < 120 * 1024) smem = 120 * 1024;
+  }
   GemmMaps maps;
   memset(&maps, 0, sizeof maps);
   auto encode = [&](CUtensorMap* m, CUtensorMapDataType dt, void* base, uint64_t inner, uint64_t outer, uint64_t stride_bytes,
@@ -723,7 +742,7 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
     P.items = nullptr; P.n_items = nullptr;
     const int groups = (rows + P.NT * BN - 1) / (P.NT * BN);
     P.dense_items = P.f_tiles * groups;
-    grid = std::min(P.dense_items, ctx->sm_count);
+    grid = std::min(P.dense_items, ctas * ctx->sm_count);
   } else {
     if (L->E > 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: more than 1024 experts");
     if (scratch == nullptr) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: the grouped form needs scratch");
@@ -736,7 +755,7 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
     int rc = orn_launch_check(ctx, "k_plan_items");
     if (rc != ORN_OK) return rc;
     P.items = items; P.n_items = n_items; P.dense_items = 0;
-    grid = ctx->sm_count;
+    grid = ctas * ctx->sm_count;
   }
   switch (L->kind) {
     case ORN_Q4K: return launch_qgemm<ORN_Q4K>(ctx, s, maps, P, grid, smem);

@@ -859,8 +859,11 @@ int prefill_wide(orn_model* m, orn_cache* cc, int T, bf16_t* normed_out /*nullab
       CK(k_rope(ctx, s, w.aq, T, Hq, hd, c.rope_dims, m->lnb, cc->pos, 0));
       CK(k_rope(ctx, s, w.ak, T, Hkv, hd, c.rope_dims, m->lnb, cc->pos, 0));
       CK(k_kv_append(ctx, s, w.ak, w.av, T, Hkv, hd, c.max_ctx, cc->pos, 0, cc->kc[i], cc->vc[i]));
-      CK(k_sdpa_decode(ctx, s, w.aq, cc->kc[i], cc->vc[i], T, Hq, Hkv, hd, c.max_ctx, cc->pos, 0, 1.0f / sqrtf((float)hd),
-                       w.att));
+      if (wide_exact() || hd != 256)  // the row-invariant kernel: one pass over the cache per (head, row)
+        CK(k_sdpa_decode(ctx, s, w.aq, cc->kc[i], cc->vc[i], T, Hq, Hkv, hd, c.max_ctx, cc->pos, 0, 1.0f / sqrtf((float)hd),
+                         w.att));
+      else
+        CK(k_flash_prefill(ctx, s, w.aq, cc->kc[i], cc->vc[i], T, Hq, Hkv, hd, c.max_ctx, cc->pos, 1.0f / sqrtf((float)hd), w.att));
       CK(k_sigmoid_gate(ctx, s, w.agate, w.att, T * Hq * hd, 1, w.agated));
       CK(wide_mm(m, ly.o_proj, w.agated, T, w.r));
     }

@@ -5,7 +5,10 @@
 #include <stdint.h>
 
 #include <map>
+#include <mutex>
+#include <set>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/ornith_cuda.h"
@@ -108,6 +111,23 @@ static inline int orn_launch_check(orn_ctx* ctx, const char* what) {
   return ORN_OK;
 }
 
+// Raises a kernel's dynamic shared-memory limit once per (device, kernel).  The attribute belongs to
+// the device's copy of the function, so the table is keyed by both and guarded for concurrent contexts.
+inline int orn_grant_smem(orn_ctx* ctx, const void* kern, size_t bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<int, const void*>> granted;
+  const std::pair<int, const void*> key(ctx->device, kern);
+  std::lock_guard<std::mutex> lock(mu);
+  if (granted.count(key)) return ORN_OK;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) {
+    ctx->err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e);
+    return ORN_ERR_CUDA;
+  }
+  granted.insert(key);
+  return ORN_OK;
+}
+
 // Launch `kern` so that it may begin while the previous kernel of the stream is still draining
 // (programmatic dependent launch).  Such a kernel runs its set-up and its weight prefetch at
 // once and executes griddepcontrol.wait before it touches anything an earlier kernel wrote or
@@ -199,6 +219,9 @@ int k_kv_append_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* k, const bf1
                         const int* pos, bf16_t* kc, bf16_t* vc);
 int k_sdpa_decode_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* kc, const bf16_t* vc, int B, int Tb,
                           int Hq, int Hkv, int hd, int cap, const int* pos, float scale, bf16_t* out);
+// flash.cu
+int k_flash_prefill(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* kc, const bf16_t* vc, int T, int Hq, int Hkv, int hd,
+                    int cap, const int* pos, float scale, bf16_t* out);
 int k_rope(orn_ctx* ctx, cudaStream_t s, bf16_t* x, int T, int H, int hd, int dims, float lnb,
            const int* dev_offset, int offset_add);
 int k_kv_append(orn_ctx* ctx, cudaStream_t s, const bf16_t* k, const bf16_t* v, int T, int Hkv,

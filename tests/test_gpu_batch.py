@@ -115,7 +115,7 @@ def test_batched_tensor_core_mode_agrees_with_exact_mode(pkg, ctx, ctx_len):
         cos, err = row_stats(outs[True][a], outs[False][b])
         assert np.median(cos) > 0.998, (ctx_len, a, np.sort(cos)[:4])
         assert np.median(err) < tol, (ctx_len, a, np.sort(err)[-4:])
-        assert np.mean(cos > 0.998) >= 0.75, (ctx_len, a, np.sort(cos)[:4])   # a flipped route moves its whole sequence
+        assert np.mean(cos > 0.995) >= 0.6, (ctx_len, a, np.sort(cos)[:4])   # a flipped route moves its whole sequence
     gm.free()
 
 

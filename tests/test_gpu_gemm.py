@@ -42,6 +42,25 @@ def test_gemm_matches_oracle_matvec(pkg, ctx, kind, M, O, K):
     L.free()
 
 
+@pytest.mark.parametrize("kind", [orc.Q4K, orc.Q6K, orc.A8, orc.BF16, orc.A4])
+def test_a_rows_product_does_not_depend_on_the_tile_shape(pkg, ctx, kind):
+    """The same row computed in a launch of 16, 48, 128 and 300 rows (token tiles of 16, 48, 128 and
+    128 columns) has the same bits: the K loop accumulates in the same order for every column, so
+    results do not depend on how many rows share a launch (what lets the expert-parallel block give
+    the same bits at every world size)."""
+    rng = np.random.default_rng(77 + kind)
+    O, K = 384, 1024
+    W = hp.make_weights(rng, kind, 1, O, K)
+    x = hp.f32_to_bf16(rng.standard_normal((300, K)).astype(np.float32))
+    L = lin_of(pkg, ctx, W)
+    dx = ctx.upload(x)
+    full = L.matmul_wide(dx, 300, out_f32=True).numpy()
+    for rows in (16, 48, 128):
+        part = L.matmul_wide(dx, rows, out_f32=True).numpy()
+        assert np.array_equal(part.view(np.uint32), full[:rows].view(np.uint32)), rows
+    L.free()
+
+
 def test_gemm_raw_field_q4k_config1_shape(pkg, ctx):
     """BASELINE config 1's matrix (raw-field Q4_K, N = 512, K = 2048) at prompt width.  Raw fields
     give weights of one sign (mean +0.2, magnitudes up to 1), so the outputs are small differences of

@@ -343,6 +343,31 @@ def test_sdpa_decode(pkg, ctx, T, Lk):
         assert np.array_equal(one.numpy()[0], got[r])
 
 
+@pytest.mark.parametrize("T,offset", [(64, 0), (100, 0), (37, 300), (200, 1000), (1, 5), (130, 31)])
+def test_sdpa_prefill_agrees_with_the_row_invariant_kernel(pkg, ctx, T, offset):
+    """The prompt path's tensor-core attention against orn_sdpa_decode (itself bit-equal to the
+    oracle above): same contract, another summation order and bf16 probabilities.  Tolerance: an
+    output is a convex combination of V entries (|v| up to about 4 here), so 2e-2 absolute is a few
+    bf16 steps of the largest term; the mean error is checked an order of magnitude tighter."""
+    rng = np.random.default_rng(T * 7 + offset)
+    Hq, Hkv, hd = 16, 2, 256
+    cap = offset + T + 9
+    q = bf(rng, (T, Hq, hd))
+    kc, vc = bf(rng, (Hkv, cap, hd)), bf(rng, (Hkv, cap, hd))
+    dq, dk, dv = ctx.upload(q), ctx.upload(kc), ctx.upload(vc)
+    want, got = ctx.empty((T, Hq, hd), np.uint16), ctx.empty((T, Hq, hd), np.uint16)
+    for r in range(0, T, 4):          # the row-invariant kernel takes windows of up to 4 rows
+        n = min(4, T - r)
+        ctx.check(ctx._lib.orn_sdpa_decode(ctx.h, dq.at(r * Hq * hd * 2), dk.ptr, dv.ptr, n, Hq, Hkv, hd, cap, offset + r,
+                                           1.0 / 16.0, want.at(r * Hq * hd * 2)), "sdpa")
+    ctx.check(ctx._lib.orn_sdpa_prefill(ctx.h, dq.ptr, dk.ptr, dv.ptr, T, Hq, Hkv, hd, cap, offset, 1.0 / 16.0, got.ptr),
+              "sdpa_prefill")
+    w, g = hp.bf16_to_f32(want.numpy()).astype(np.float64), hp.bf16_to_f32(got.numpy()).astype(np.float64)
+    assert np.isfinite(g).all()
+    assert np.abs(w - g).max() < 2e-2, np.abs(w - g).max()
+    assert np.abs(w - g).mean() < 2e-3, np.abs(w - g).mean()
+
+
 @pytest.mark.parametrize("V", [248320, 1000, 1024, 5000])
 def test_greedy(pkg, ctx, V):
     rng = np.random.default_rng(V)
