@@ -314,6 +314,15 @@ struct orn_batch {
   float *greedy_scratch, *part;
   int part_chunks = 0;
   int last_T = 0;
+  uint32_t *ids_h = nullptr, *targets_h = nullptr;  // pinned staging: a captured step copies from / to fixed host addresses
+  bf16_t* normed = nullptr;                          // the rows after the final norm of the last step
+  struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    int seen = 0;
+    int64_t launches = 0;
+    orn_ep* group = nullptr;
+  };
+  std::map<uint64_t, StepGraph> graphs;  // keyed by (rows per window, split-KV launch shape, arithmetic)
   // this rank's slices of the routed experts when the group has several ranks (views, not copies)
   int shard_rank = -1, shard_world = 0;
   std::vector<orn_linear*> views;  // [layer][3]
@@ -355,6 +364,77 @@ int ensure_shards(orn_batch* bt, int rank, int world) {
   return ORN_OK;
 }
 
+// the device work of one step: everything between the upload of the ids and the download of the
+// targets, with fixed addresses and launch shapes (so that it can be captured once and replayed)
+int batch_body(orn_batch* bt, orn_ep* group, int T, int chunk, int nchunks) {
+  orn_model* m = bt->m;
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  const orn_config& c = m->cfg;
+  const int B = bt->B, R = B * T, H = c.hidden, S = c.gdn_conv_kernel - 1, D = orn_conv_dim(c);
+  const int Hq = c.n_heads, Hkv = c.n_kv_heads, hd = c.head_dim;
+  const bool exact = bt->exact || R < 16;
+  const int world = orn_ep_world(group);
+  ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(bt->ids, bt->ids_h, sizeof(uint32_t) * (size_t)R, cudaMemcpyHostToDevice, s));
+  conv_map_kernel<<<(R + 127) / 128, 128, 0, s>>>(bt->conv_map, B, T, bt->conv_rows, S);
+  CK(orn_launch_check(ctx, "conv_map"));
+  CK(k_embedding(ctx, s, m->embed, bt->ids, R, bt->x));
+  CK(k_rms_norm(ctx, s, bt->x, m->layers[0].input_ln, R, H, c.rms_eps, bt->n));
+  const int NQ = (Hq / Hkv) * T;
+  for (int i = 0; i < c.n_layers; ++i) {
+    const Layer& ly = m->layers[i];
+    if (ly.linear) {
+      CK(batch_mm(bt, ly.in_qkv, bt->n, R, bt->qkv));
+      scatter_rows_kernel<<<R, 128, 0, s>>>(bt->qkv, bt->conv_map, D, bt->conv[i]);  // row (b, t) -> window row S + t of sequence b
+      CK(orn_launch_check(ctx, "scatter_rows"));
+      CK(batch_mm(bt, ly.in_z, bt->n, R, bt->z));
+      CK(batch_mm(bt, ly.in_b, bt->n, R, bt->b));
+      CK(batch_mm(bt, ly.in_a, bt->n, R, bt->a));
+      CK(k_gdn_front_batched(ctx, s, bt->conv[i], (int64_t)bt->conv_rows * D, ly.conv_w, bt->a, bt->b, ly.a_log, ly.dt_bias, B, T,
+                             c.gdn_k_heads, c.gdn_v_heads, c.gdn_head_dim, c.gdn_conv_kernel, 1e-6f, bt->gq, bt->gk, bt->gv,
+                             bt->beta, bt->gg));
+      CK(k_gated_delta_batched(ctx, s, bt->gq, bt->gk, bt->gv, bt->gg, bt->beta, bt->ring[i], bt->nring, bt->cur, B, T,
+                               c.gdn_k_heads, c.gdn_v_heads, bt->gy));
+      CK(k_rms_norm_gated(ctx, s, bt->gy, ly.gdn_norm, bt->z, R * c.gdn_v_heads, c.gdn_head_dim, c.rms_eps, bt->gated));
+      CK(batch_mm(bt, ly.out_proj, bt->gated, R, bt->r));
+    } else {
+      CK(batch_mm(bt, ly.q_proj, bt->n, R, bt->qg));
+      CK(batch_mm(bt, ly.k_proj, bt->n, R, bt->ak));
+      CK(batch_mm(bt, ly.v_proj, bt->n, R, bt->av));
+      CK(k_split_qgate(ctx, s, bt->qg, R, Hq, hd, bt->aq, bt->agate));
+      CK(k_rms_norm(ctx, s, bt->aq, ly.q_norm, R * Hq, hd, c.rms_eps, bt->aq));
+      CK(k_rms_norm(ctx, s, bt->ak, ly.k_norm, R * Hkv, hd, c.rms_eps, bt->ak));
+      CK(k_rope_batched(ctx, s, bt->aq, B, T, Hq, hd, c.rope_dims, m->lnb, bt->pos));
+      CK(k_rope_batched(ctx, s, bt->ak, B, T, Hkv, hd, c.rope_dims, m->lnb, bt->pos));
+      CK(k_kv_append_batched(ctx, s, bt->ak, bt->av, B, T, Hkv, hd, bt->cap, bt->pos, bt->kc[i], bt->vc[i]));
+      const float scale = 1.0f / sqrtf((float)hd);
+      if ((exact && !bt->split_attn) || hd != 256 || NQ > 16) {
+        CK(k_sdpa_decode_batched(ctx, s, bt->aq, bt->kc[i], bt->vc[i], B, T, Hq, Hkv, hd, bt->cap, bt->pos, scale, bt->att));
+        CK(k_sigmoid_gate(ctx, s, bt->agate, bt->att, R * Hq * hd, 1, bt->agated));
+      } else {
+        CK(launch_battn(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks, chunk, NQ));
+        dim3 grid(NQ, Hkv, B);
+        battn_merge_kernel<<<grid, 256, 0, s>>>(bt->part, bt->qg, T, Hq, Hkv, nchunks, NQ, bt->agated);
+        CK(orn_launch_check(ctx, "battn_merge"));
+      }
+      CK(batch_mm(bt, ly.o_proj, bt->agated, R, bt->r));
+    }
+    CK(k_add_rms_norm(ctx, s, bt->x, bt->r, ly.post_ln, R, H, c.rms_eps, bt->h, bt->n2));
+    const orn_linear* sg = world > 1 ? bt->views[3 * i] : ly.moe.sw_gate;
+    const orn_linear* su = world > 1 ? bt->views[3 * i + 1] : ly.moe.sw_up;
+    const orn_linear* sd = world > 1 ? bt->views[3 * i + 2] : ly.moe.sw_down;
+    CK(orn_ep_moe_block(group, ly.moe.gate, sg, su, sd, ly.moe.sh_gate, ly.moe.sh_up, ly.moe.sh_down, ly.moe.sh_egate, bt->n2, R,
+                        c.top_k, c.norm_topk_prob, bt->mo, nullptr));
+    const bf16_t* nw = i + 1 < c.n_layers ? m->layers[i + 1].input_ln : m->norm;
+    CK(k_add_rms_norm(ctx, s, bt->h, bt->mo, nw, R, H, c.rms_eps, bt->x, bt->n));
+  }
+  ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(bt->normed, bt->n, sizeof(bf16_t) * (size_t)R * H, cudaMemcpyDeviceToDevice, s));  // the head's input survives it
+  CK(batch_mm(bt, m->lm_head, bt->n, R, bt->logits));
+  CK(k_greedy(ctx, s, bt->logits, R, c.vocab, 1, bt->targets, bt->greedy_scratch));
+  ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(bt->targets_h, bt->targets, sizeof(uint32_t) * (size_t)R, cudaMemcpyDeviceToHost, s));
+  return ORN_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -362,7 +442,11 @@ extern "C" {
 int32_t orn_batch_destroy(orn_batch* bt) {
   if (!bt) return ORN_OK;
   cudaStreamSynchronize(bt->m->ctx->stream);
+  for (auto& kv : bt->graphs)
+    if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
   for (void* p : bt->allocs) cudaFree(p);
+  if (bt->ids_h) cudaFreeHost(bt->ids_h);
+  if (bt->targets_h) cudaFreeHost(bt->targets_h);
   for (orn_linear* v : bt->views) delete v;
   if (bt->own_ep) orn_ep_destroy(bt->own_ep);
   if (bt->own_ep_exact) orn_ep_destroy(bt->own_ep_exact);
@@ -418,6 +502,7 @@ int32_t orn_batch_create(orn_model* m, int32_t B, int32_t T_max, int32_t cap, in
   A(&bt->qg, R * 2 * QD); A(&bt->aq, R * QD); A(&bt->agate, R * QD); A(&bt->ak, R * KVD); A(&bt->av, R * KVD);
   A(&bt->att, R * QD); A(&bt->agated, R * QD);
   A(&bt->logits, R * (size_t)c.vocab);
+  A(&bt->normed, R * H);
   A(&bt->greedy_scratch, greedy_scratch_floats((int)R, c.vocab));
   bt->part_chunks = (cap + kMinChunk - 1) / kMinChunk;
   A(&bt->part, (size_t)B * c.n_kv_heads * bt->part_chunks * 16 * kPartStride);
@@ -426,6 +511,12 @@ int32_t orn_batch_create(orn_model* m, int32_t B, int32_t T_max, int32_t cap, in
     if (rc == ORN_OK) rc = orn_upload(ctx, bt->conv_table, table.data(), sizeof(bf16_t*) * table.size());
   }
   if (rc != ORN_OK) { orn_batch_destroy(bt); return rc; }
+  if (cudaMallocHost((void**)&bt->ids_h, sizeof(uint32_t) * R) != cudaSuccess ||
+      cudaMallocHost((void**)&bt->targets_h, sizeof(uint32_t) * R) != cudaSuccess) {
+    ctx->err = "batch_create: pinned staging";
+    orn_batch_destroy(bt);
+    return ORN_ERR_ALLOC;
+  }
   *out = bt;
   return orn_batch_reset(bt);
 }
@@ -490,8 +581,7 @@ int32_t orn_batch_forward(orn_batch* bt, orn_ep* ep, const uint32_t* host_ids, i
   if (T < 1 || T > bt->Tmax) ORN_FAIL(ctx, ORN_ERR_ARG, "batch_forward: window wider than the batch was made for");
   for (int b = 0; b < bt->B; ++b)
     if (bt->h_pos[b] + T > bt->cap) ORN_FAIL(ctx, ORN_ERR_STATE, "batch_forward: a sequence would pass the cache capacity");
-  const int B = bt->B, R = B * T, H = c.hidden, S = c.gdn_conv_kernel - 1, D = orn_conv_dim(c);
-  const int Hq = c.n_heads, Hkv = c.n_kv_heads, hd = c.head_dim;
+  const int B = bt->B, R = B * T;
   const bool exact = bt->exact || R < 16;
   orn_ep* group = ep;
   if (!group) {
@@ -501,71 +591,56 @@ int32_t orn_batch_forward(orn_batch* bt, orn_ep* ep, const uint32_t* host_ids, i
   }
   const int world = orn_ep_world(group), rank = orn_ep_rank(group);
   if (world > 1) CK(ensure_shards(bt, rank, world));
-  ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(bt->ids, host_ids, sizeof(uint32_t) * (size_t)R, cudaMemcpyHostToDevice, s));
-  conv_map_kernel<<<(R + 127) / 128, 128, 0, s>>>(bt->conv_map, B, T, bt->conv_rows, S);
-  CK(orn_launch_check(ctx, "conv_map"));
-  CK(k_embedding(ctx, s, m->embed, bt->ids, R, bt->x));
-  CK(k_rms_norm(ctx, s, bt->x, m->layers[0].input_ln, R, H, c.rms_eps, bt->n));
+  // keys per CTA of the split-KV attention: about six CTAs per SM over the whole launch, 128..512,
+  // a multiple of 64; the launch covers the longest sequence (shorter ones leave chunks empty)
   int max_pos = 0;
   for (int b = 0; b < B; ++b) max_pos = std::max(max_pos, bt->h_pos[b]);
-  const int NQ = (Hq / Hkv) * T;
-  for (int i = 0; i < c.n_layers; ++i) {
-    const Layer& ly = m->layers[i];
-    if (ly.linear) {
-      CK(batch_mm(bt, ly.in_qkv, bt->n, R, bt->qkv));
-      scatter_rows_kernel<<<R, 128, 0, s>>>(bt->qkv, bt->conv_map, D, bt->conv[i]);  // row (b, t) -> window row S + t of sequence b
-      CK(orn_launch_check(ctx, "scatter_rows"));
-      CK(batch_mm(bt, ly.in_z, bt->n, R, bt->z));
-      CK(batch_mm(bt, ly.in_b, bt->n, R, bt->b));
-      CK(batch_mm(bt, ly.in_a, bt->n, R, bt->a));
-      CK(k_gdn_front_batched(ctx, s, bt->conv[i], (int64_t)bt->conv_rows * D, ly.conv_w, bt->a, bt->b, ly.a_log, ly.dt_bias, B, T,
-                             c.gdn_k_heads, c.gdn_v_heads, c.gdn_head_dim, c.gdn_conv_kernel, 1e-6f, bt->gq, bt->gk, bt->gv,
-                             bt->beta, bt->gg));
-      CK(k_gated_delta_batched(ctx, s, bt->gq, bt->gk, bt->gv, bt->gg, bt->beta, bt->ring[i], bt->nring, bt->cur, B, T,
-                               c.gdn_k_heads, c.gdn_v_heads, bt->gy));
-      CK(k_rms_norm_gated(ctx, s, bt->gy, ly.gdn_norm, bt->z, R * c.gdn_v_heads, c.gdn_head_dim, c.rms_eps, bt->gated));
-      CK(batch_mm(bt, ly.out_proj, bt->gated, R, bt->r));
-    } else {
-      CK(batch_mm(bt, ly.q_proj, bt->n, R, bt->qg));
-      CK(batch_mm(bt, ly.k_proj, bt->n, R, bt->ak));
-      CK(batch_mm(bt, ly.v_proj, bt->n, R, bt->av));
-      CK(k_split_qgate(ctx, s, bt->qg, R, Hq, hd, bt->aq, bt->agate));
-      CK(k_rms_norm(ctx, s, bt->aq, ly.q_norm, R * Hq, hd, c.rms_eps, bt->aq));
-      CK(k_rms_norm(ctx, s, bt->ak, ly.k_norm, R * Hkv, hd, c.rms_eps, bt->ak));
-      CK(k_rope_batched(ctx, s, bt->aq, B, T, Hq, hd, c.rope_dims, m->lnb, bt->pos));
-      CK(k_rope_batched(ctx, s, bt->ak, B, T, Hkv, hd, c.rope_dims, m->lnb, bt->pos));
-      CK(k_kv_append_batched(ctx, s, bt->ak, bt->av, B, T, Hkv, hd, bt->cap, bt->pos, bt->kc[i], bt->vc[i]));
-      const float scale = 1.0f / sqrtf((float)hd);
-      if ((exact && !bt->split_attn) || hd != 256 || NQ > 16) {
-        CK(k_sdpa_decode_batched(ctx, s, bt->aq, bt->kc[i], bt->vc[i], B, T, Hq, Hkv, hd, bt->cap, bt->pos, scale, bt->att));
-        CK(k_sigmoid_gate(ctx, s, bt->agate, bt->att, R * Hq * hd, 1, bt->agated));
-      } else {
-        // keys per CTA: about six CTAs per SM over the whole launch, 128..512, a multiple of 64
-        const int maxL = max_pos + T;
-        int chunk = (int)(((int64_t)maxL * B * Hkv / (ctx->sm_count * 6) + 63) / 64 * 64);
-        chunk = std::min(kMaxChunk, std::max(kMinChunk, chunk));
-        const int nchunks = (maxL + chunk - 1) / chunk;
-        CK(launch_battn(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks, chunk, NQ));
-        dim3 grid(NQ, Hkv, B);
-        battn_merge_kernel<<<grid, 256, 0, s>>>(bt->part, bt->qg, T, Hq, Hkv, nchunks, NQ, bt->agated);
-        CK(orn_launch_check(ctx, "battn_merge"));
-      }
-      CK(batch_mm(bt, ly.o_proj, bt->agated, R, bt->r));
-    }
-    CK(k_add_rms_norm(ctx, s, bt->x, bt->r, ly.post_ln, R, H, c.rms_eps, bt->h, bt->n2));
-    const orn_linear* sg = world > 1 ? bt->views[3 * i] : ly.moe.sw_gate;
-    const orn_linear* su = world > 1 ? bt->views[3 * i + 1] : ly.moe.sw_up;
-    const orn_linear* sd = world > 1 ? bt->views[3 * i + 2] : ly.moe.sw_down;
-    CK(orn_ep_moe_block(group, ly.moe.gate, sg, su, sd, ly.moe.sh_gate, ly.moe.sh_up, ly.moe.sh_down, ly.moe.sh_egate, bt->n2, R,
-                        c.top_k, c.norm_topk_prob, bt->mo, nullptr));
-    const bf16_t* nw = i + 1 < c.n_layers ? m->layers[i + 1].input_ln : m->norm;
-    CK(k_add_rms_norm(ctx, s, bt->h, bt->mo, nw, R, H, c.rms_eps, bt->x, bt->n));
+  const int maxL = max_pos + T;
+  int chunk = (int)(((int64_t)maxL * B * c.n_kv_heads / (ctx->sm_count * 6) + 63) / 64 * 64);
+  chunk = std::min(kMaxChunk, std::max(kMinChunk, chunk));
+  const int nchunks = (maxL + chunk - 1) / chunk;
+  // the previous step's targets have been read (its download synchronised) before ids_h is rewritten
+  ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(s));
+  memcpy(bt->ids_h, host_ids, sizeof(uint32_t) * (size_t)R);
+  static int no_graph = -1;
+  if (no_graph < 0) { const char* e = getenv("ORN_NO_GRAPH"); no_graph = (e && e[0] == '1') ? 1 : 0; }
+  const bool eager = no_graph || ctx->kt != nullptr;
+  const uint64_t key = (uint64_t)T | ((uint64_t)nchunks << 8) | ((uint64_t)chunk << 28) | ((uint64_t)(exact ? 1 : 0) << 40);
+  orn_batch::StepGraph& g = bt->graphs[key];
+  if (g.exec != nullptr && g.group != group) {  // captured for another group: its collectives belong to that one
+    cudaGraphExecDestroy(g.exec);
+    g = orn_batch::StepGraph();
   }
-  if (dev_normed) ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(dev_normed, bt->n, sizeof(bf16_t) * (size_t)R * H, cudaMemcpyDeviceToDevice, s));
-  CK(batch_mm(bt, m->lm_head, bt->n, R, bt->logits));
-  CK(k_greedy(ctx, s, bt->logits, R, c.vocab, 1, bt->targets, bt->greedy_scratch));
+  int rc = ORN_OK;
+  if (g.exec != nullptr && !eager) {
+    ORN_CHECK_CUDA(ctx, cudaGraphLaunch(g.exec, s));
+    ctx->launches += g.launches;
+  } else if (g.seen == 0 || eager) {
+    g.seen += 1;  // the first step of a shape runs eagerly (scratch is allocated on first use); the second is captured
+    rc = batch_body(bt, group, T, chunk, nchunks);
+  } else {
+    const int64_t l0 = ctx->launches;
+    ORN_CHECK_CUDA(ctx, cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    rc = batch_body(bt, group, T, chunk, nchunks);
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(s, &graph);
+    if (rc != ORN_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (e != cudaSuccess) ORN_FAIL(ctx, ORN_ERR_CUDA, std::string("batch_forward: cudaStreamEndCapture: ") + cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&g.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { g.exec = nullptr; ORN_FAIL(ctx, ORN_ERR_CUDA, std::string("batch_forward: cudaGraphInstantiate: ") + cudaGetErrorString(e)); }
+    g.launches = ctx->launches - l0;
+    g.group = group;
+    ORN_CHECK_CUDA(ctx, cudaGraphLaunch(g.exec, s));
+  }
+  if (rc != ORN_OK) return rc;
   bt->last_T = T;
-  if (host_targets) return orn_download(ctx, host_targets, bt->targets, sizeof(uint32_t) * (size_t)R);
+  if (dev_normed)
+    ORN_CHECK_CUDA(ctx, cudaMemcpyAsync(dev_normed, bt->normed, sizeof(bf16_t) * (size_t)R * c.hidden, cudaMemcpyDeviceToDevice, s));
+  if (host_targets) {
+    CK(orn_sync(ctx));
+    memcpy(host_targets, bt->targets_h, sizeof(uint32_t) * (size_t)R);
+  }
   return ORN_OK;
 }
 

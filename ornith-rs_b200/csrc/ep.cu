@@ -30,6 +30,8 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <array>
+#include <map>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -116,63 +118,72 @@ __global__ void ep_select_kernel(const bf16_t* recv, const uint32_t* inds, int e
 
 }  // namespace
 
-struct orn_ep {
-  orn_ctx* ctx = nullptr;
-  int rank = 0, world = 1;
-  bool exact = false;  // routed experts through the row-invariant grouped mat-vec instead of the tensor cores
-  void* gemm_scratch = nullptr;
-  ncclComm_t comm = nullptr;
-  // scratch for one shape (R, H, E, k, I, SI); rebuilt when a call asks for a larger one
-  size_t cap_key[6] = {0, 0, 0, 0, 0, 0};
-  std::vector<void*> allocs;
+// scratch for one shape (R, H, E, k, I, SI)
+struct EpBufs {
   bf16_t *gates, *probs, *scores, *sg, *su, *sact, *sy, *gs, *all_x, *xs, *eg, *eu, *eact, *ret_send, *ret_recv, *ey;
   uint32_t *inds, *all_inds, *rhs_local, *lhs, *perm;
   int *seg, *seg1;
+  void* gemm_scratch;
+};
+struct EpSet {
+  EpBufs bufs{};
+  std::vector<void*> allocs;
+};
+struct orn_ep : EpBufs {
+  orn_ctx* ctx = nullptr;
+  int rank = 0, world = 1;
+  bool exact = false;  // routed experts through the row-invariant grouped mat-vec instead of the tensor cores
+  ncclComm_t comm = nullptr;
+  // One scratch set per shape a caller has used, kept until the group is destroyed: a caller may
+  // have captured a call into a CUDA graph, whose kernel arguments are these addresses.
+  std::map<std::array<size_t, 6>, EpSet> sets;
 };
 
 namespace {
 
 int ep_reserve(orn_ep* ep, int R, int H, int E, int k, int I, int SI) {
-  const size_t key[6] = {(size_t)R, (size_t)H, (size_t)E, (size_t)k, (size_t)I, (size_t)SI};
-  bool fits = true;
-  for (int i = 0; i < 6; ++i) fits = fits && key[i] == ep->cap_key[i];
-  if (fits) return ORN_OK;
+  const std::array<size_t, 6> key = {(size_t)R, (size_t)H, (size_t)E, (size_t)k, (size_t)I, (size_t)SI};
+  auto it = ep->sets.find(key);
+  if (it != ep->sets.end()) {
+    static_cast<EpBufs&>(*ep) = it->second.bufs;
+    return ORN_OK;
+  }
   orn_ctx* ctx = ep->ctx;
-  ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  for (void* p : ep->allocs) cudaFree(p);
-  ep->allocs.clear();
-  for (int i = 0; i < 6; ++i) ep->cap_key[i] = 0;
+  if (ep->sets.size() >= 64) ORN_FAIL(ctx, ORN_ERR_ALLOC, "ep: more than 64 distinct block shapes on one group");
   const size_t W = ep->world, G = W * R, routes = G * k, el = (size_t)E / W;
+  EpSet set;
+  EpBufs& b = set.bufs;
   int rc = ORN_OK;
   auto A = [&](auto** p, size_t n) {
     if (rc != ORN_OK) return;
     void* d = nullptr;
     rc = orn_alloc(ctx, sizeof(**p) * (n ? n : 1), &d);
-    if (rc == ORN_OK) { ep->allocs.push_back(d); *p = (std::remove_reference_t<decltype(**p)>*)d; }
+    if (rc == ORN_OK) { set.allocs.push_back(d); *p = (std::remove_reference_t<decltype(**p)>*)d; }
   };
-  A(&ep->gates, (size_t)R * E); A(&ep->probs, (size_t)R * E); A(&ep->scores, (size_t)R * k); A(&ep->inds, (size_t)R * k);
-  A(&ep->sg, (size_t)R * SI); A(&ep->su, (size_t)R * SI); A(&ep->sact, (size_t)R * SI); A(&ep->sy, (size_t)R * H); A(&ep->gs, (size_t)R);
-  A(&ep->all_inds, routes); A(&ep->all_x, G * H); A(&ep->rhs_local, routes); A(&ep->lhs, routes); A(&ep->perm, routes);
-  A(&ep->seg, 2 * el + 4); A(&ep->seg1, (size_t)2);
-  A(&ep->xs, routes * H); A(&ep->eg, routes * I); A(&ep->eu, routes * I); A(&ep->eact, routes * I);
-  A(&ep->ret_send, routes * H); A(&ep->ret_recv, routes * H); A(&ep->ey, (size_t)R * k * H);
+  A(&b.gates, (size_t)R * E); A(&b.probs, (size_t)R * E); A(&b.scores, (size_t)R * k); A(&b.inds, (size_t)R * k);
+  A(&b.sg, (size_t)R * SI); A(&b.su, (size_t)R * SI); A(&b.sact, (size_t)R * SI); A(&b.sy, (size_t)R * H); A(&b.gs, (size_t)R);
+  A(&b.all_inds, routes); A(&b.all_x, G * H); A(&b.rhs_local, routes); A(&b.lhs, routes); A(&b.perm, routes);
+  A(&b.seg, 2 * el + 4); A(&b.seg1, (size_t)2);
+  A(&b.xs, routes * H); A(&b.eg, routes * I); A(&b.eu, routes * I); A(&b.eact, routes * I);
+  A(&b.ret_send, routes * H); A(&b.ret_recv, routes * H); A(&b.ey, (size_t)R * k * H);
   if (rc == ORN_OK) {
     const size_t big = std::max(qgemm_scratch_bytes((int)routes, (int)el, H), qgemm_scratch_bytes((int)routes, (int)el, I));
-    rc = orn_alloc(ctx, big, &ep->gemm_scratch);
-    if (rc == ORN_OK) ep->allocs.push_back(ep->gemm_scratch);
-  }
-  if (rc != ORN_OK) {
-    for (void* p : ep->allocs) cudaFree(p);
-    ep->allocs.clear();
-    return rc;
+    rc = orn_alloc(ctx, big, &b.gemm_scratch);
+    if (rc == ORN_OK) set.allocs.push_back(b.gemm_scratch);
   }
   const int seg1[2] = {0, R};
-  rc = orn_upload(ctx, ep->seg1, seg1, sizeof seg1);
-  if (rc != ORN_OK) return rc;
-  ep_iota_kernel<<<(unsigned)((routes + 255) / 256), 256, 0, ctx->stream>>>(ep->lhs, (int)routes, k);
-  rc = orn_launch_check(ctx, "ep_iota");
-  if (rc != ORN_OK) return rc;
-  for (int i = 0; i < 6; ++i) ep->cap_key[i] = key[i];
+  if (rc == ORN_OK) rc = orn_upload(ctx, b.seg1, seg1, sizeof seg1);
+  if (rc == ORN_OK) {
+    ep_iota_kernel<<<(unsigned)((routes + 255) / 256), 256, 0, ctx->stream>>>(b.lhs, (int)routes, k);
+    rc = orn_launch_check(ctx, "ep_iota");
+  }
+  if (rc == ORN_OK) rc = orn_sync(ctx);
+  if (rc != ORN_OK) {
+    for (void* p : set.allocs) cudaFree(p);
+    return rc;
+  }
+  static_cast<EpBufs&>(*ep) = set.bufs;
+  ep->sets.emplace(key, std::move(set));
   return ORN_OK;
 }
 
@@ -235,7 +246,8 @@ int32_t orn_ep_destroy(orn_ep* ep) {
     NcclApi* api = nccl_api(nullptr);
     if (api) api->CommDestroy(ep->comm);
   }
-  for (void* p : ep->allocs) cudaFree(p);
+  for (auto& kv : ep->sets)
+    for (void* p : kv.second.allocs) cudaFree(p);
   delete ep;
   return ORN_OK;
 }
