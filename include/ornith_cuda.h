@@ -327,6 +327,14 @@ int32_t orn_prefill(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_
 int32_t orn_forward_capture(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_t T,
                             uint16_t* dev_normed);
 int32_t orn_cache_rewind(orn_cache* c, int32_t keep);
+/* MtpHead::forward (src/model/mtp.rs:150-262) for T <= 4 rows: dev_hidden [T, hidden] are the
+ * trunk's post-norm rows the tokens pair with; the head's own KV cache advances by T.  kv_only:
+ * only the cache rows are wanted (the Committed re-encode, src/mtp_generate.rs:292-301); otherwise
+ * host_draft (nullable) receives the raw-logit argmax of the last row. */
+int32_t orn_mtp_forward(orn_model* m, orn_cache* c, const uint16_t* dev_hidden, const uint32_t* host_ids,
+                        int32_t T, int32_t kv_only, uint32_t* host_draft /*nullable*/);
+int32_t orn_cache_mtp_offset(const orn_cache* c);
+int32_t orn_cache_set_mtp_offset(orn_cache* c, int32_t offset);
 /* lm_head + greedy_token for T hidden rows (generate.rs:139-150) */
 int32_t orn_head_greedy(orn_model* m, const uint16_t* dev_hidden, int32_t T,
                         uint32_t* host_tokens, uint16_t* dev_logits_out /*nullable*/);
@@ -399,6 +407,14 @@ int32_t orn_batch_positions(orn_batch* bt, int32_t* host_pos /*[B]*/);
 int32_t orn_batch_forward(orn_batch* bt, orn_ep* ep /*nullable*/, const uint32_t* host_ids, int32_t T,
                           uint16_t* dev_normed /*nullable*/, uint32_t* host_targets /*nullable*/);
 int32_t orn_batch_commit(orn_batch* bt, const int32_t* host_keep /*[B]*/);
+/* MtpHead::forward at depth 1 for every sequence (src/model/mtp.rs:150-262): host_primary [B] is the
+ * token each sequence feeds next, the hidden row it pairs with is the one the last commit kept;
+ * host_drafts [B] receives the raw-logit argmax.  The head has its own per-sequence KV cache; a
+ * commit of the 2-row window that follows re-encodes the accepted draft into it
+ * (HistoryPolicy::Committed, src/mtp_generate.rs:292-301).  One cycle = draft, forward of
+ * [primary, draft], commit(1 + accepted). */
+int32_t orn_batch_mtp_draft(orn_batch* bt, orn_ep* ep /*nullable*/, const uint32_t* host_primary,
+                            uint32_t* host_drafts);
 int32_t orn_ep_world(const orn_ep* ep);
 int32_t orn_ep_rank(const orn_ep* ep);
 

@@ -321,6 +321,14 @@ class TextModel:
                        "orn_prefill")
         return out
 
+    def mtp_forward(self, cache, hidden, ids, kv_only=False):
+        """MtpHead::forward for len(ids) rows; returns the draft (raw-logit argmax of the last row) or None."""
+        ids = np.ascontiguousarray(ids, np.uint32)
+        out = np.zeros(1, np.uint32)
+        self.ctx.check(self.ctx._lib.orn_mtp_forward(self.h, cache.h, _p(hidden), ids.ctypes.data, len(ids), int(bool(kv_only)),
+                                                     None if kv_only else out.ctypes.data), "orn_mtp_forward")
+        return None if kv_only else int(out[0])
+
     def head_greedy(self, hidden, T, want_logits=False):
         toks = np.zeros(T, np.uint32)
         logits = self.ctx.empty((T, self.cfg.vocab), np.uint16) if want_logits else None
@@ -376,6 +384,16 @@ class Batch:
         self.ctx.check(self.ctx._lib.orn_batch_forward(self.h, None if ep is None else ep.h, ids.ctypes.data, T, _p(hid),
                                                        None if tg is None else tg.ctypes.data), "orn_batch_forward")
         return tg, hid
+
+    def mtp_draft(self, primary, ep=None):
+        """One draft token per sequence from the MTP head (depth 1): primary [B] -> drafts [B]."""
+        primary = np.ascontiguousarray(primary, np.uint32)
+        if primary.shape != (self.B,):
+            raise ValueError("Batch.mtp_draft: one primary token per sequence")
+        out = np.zeros(self.B, np.uint32)
+        self.ctx.check(self.ctx._lib.orn_batch_mtp_draft(self.h, None if ep is None else ep.h, primary.ctypes.data,
+                                                         out.ctypes.data), "orn_batch_mtp_draft")
+        return out
 
     def commit(self, keep):
         keep = np.ascontiguousarray(keep, np.int32)

@@ -106,6 +106,7 @@ SIGNATURES = {
     "orn_batch_positions": (i32, [vp, vp]),
     "orn_batch_forward": (i32, [vp, vp, vp, i32, vp, vp]),
     "orn_batch_commit": (i32, [vp, vp]),
+    "orn_batch_mtp_draft": (i32, [vp, vp, vp, vp]),
     "orn_gdn_front": (i32, [vp] + [vp] * 7 + [i32] * 5 + [f32] + [vp] * 6),
     "orn_gated_delta": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "orn_rope": (i32, [vp, vp, i32, i32, i32, i32, f32, i32]),
@@ -133,6 +134,9 @@ SIGNATURES = {
     "orn_forward_capture": (i32, [vp, vp, vp, i32, vp]),
     "orn_prefill": (i32, [vp, vp, vp, i32, i32, vp]),
     "orn_cache_rewind": (i32, [vp, i32]),
+    "orn_mtp_forward": (i32, [vp, vp, vp, vp, i32, i32, vp]),
+    "orn_cache_mtp_offset": (i32, [vp]),
+    "orn_cache_set_mtp_offset": (i32, [vp, i32]),
     "orn_head_greedy": (i32, [vp, vp, i32, vp, vp]),
     "orn_generate_step": (i32, [vp, vp, vp, i32, i32, i32, TOKEN_CB, vp]),
     "orn_generate_step_mtp": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, i32, C.POINTER(ForceDraft),

@@ -313,6 +313,14 @@ struct orn_batch {
   bf16_t *qg, *aq, *agate, *ak, *av, *att, *agated, *logits;
   float *greedy_scratch, *part;
   int part_chunks = 0;
+  // the MTP head's per-sequence state (depth 1): its own KV cache and positions, the hidden row its next draft reads
+  bf16_t *mtp_kc = nullptr, *mtp_vc = nullptr, *hrow = nullptr, *hid0 = nullptr;
+  bf16_t *memb = nullptr, *me = nullptr, *mh = nullptr, *mjoined = nullptr, *mx = nullptr, *dhid = nullptr;
+  uint32_t *prim = nullptr, *tok1 = nullptr, *drafts = nullptr;
+  int* mtp_pos = nullptr;
+  std::vector<int> h_mtp_pos;
+  bool drafted = false;  // a draft was made for the window in flight: commit re-encodes what it accepts
+  std::vector<orn_linear*> mtp_views;  // this rank's slices of the MTP layer's experts
   int last_T = 0;
   uint32_t *ids_h = nullptr, *targets_h = nullptr;  // pinned staging: a captured step copies from / to fixed host addresses
   bf16_t* normed = nullptr;                          // the rows after the final norm of the last step
@@ -360,8 +368,100 @@ int ensure_shards(orn_batch* bt, int rank, int world) {
       bt->views.push_back(v);
     }
   }
+  for (orn_linear* v : bt->mtp_views) delete v;
+  bt->mtp_views.clear();
+  if (m->mtp.present) {
+    const orn_linear* full[3] = {m->mtp.moe.sw_gate, m->mtp.moe.sw_up, m->mtp.moe.sw_down};
+    for (const orn_linear* f : full) {
+      orn_linear* v = new orn_linear(*f);
+      v->E = el;
+      const size_t off = (size_t)rank * el * f->O * f->rec;
+      v->w = f->w + off; v->s = f->s + off; v->b = f->b + off;
+      v->w_bytes = (size_t)el * f->O * f->rec;
+      v->owns = false;
+      bt->mtp_views.push_back(v);
+    }
+  }
   bt->shard_rank = rank; bt->shard_world = world;
   return ORN_OK;
+}
+
+// the attention sub-block over bt->n for B * T rows (T rows per sequence at positions pos[b] ...):
+// projections, per-head norms, RoPE, KV append, attention, output gate, output projection -> bt->r.
+// kv_only: stop after the KV rows are in the cache (the MTP head's re-encode of accepted tokens)
+int batch_attention(orn_batch* bt, const orn_linear* q_proj, const orn_linear* k_proj, const orn_linear* v_proj,
+                    const orn_linear* o_proj, const bf16_t* q_norm, const bf16_t* k_norm, int T, const int* pos, bf16_t* kc,
+                    bf16_t* vc, bool exact, int chunk, int nchunks, bool kv_only) {
+  orn_model* m = bt->m;
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  const orn_config& c = m->cfg;
+  const int B = bt->B, R = B * T, Hq = c.n_heads, Hkv = c.n_kv_heads, hd = c.head_dim, NQ = (Hq / Hkv) * T;
+  CK(batch_mm(bt, k_proj, bt->n, R, bt->ak));
+  CK(batch_mm(bt, v_proj, bt->n, R, bt->av));
+  CK(k_rms_norm(ctx, s, bt->ak, k_norm, R * Hkv, hd, c.rms_eps, bt->ak));
+  CK(k_rope_batched(ctx, s, bt->ak, B, T, Hkv, hd, c.rope_dims, m->lnb, pos));
+  CK(k_kv_append_batched(ctx, s, bt->ak, bt->av, B, T, Hkv, hd, bt->cap, pos, kc, vc));
+  if (kv_only) return ORN_OK;
+  CK(batch_mm(bt, q_proj, bt->n, R, bt->qg));
+  CK(k_split_qgate(ctx, s, bt->qg, R, Hq, hd, bt->aq, bt->agate));
+  CK(k_rms_norm(ctx, s, bt->aq, q_norm, R * Hq, hd, c.rms_eps, bt->aq));
+  CK(k_rope_batched(ctx, s, bt->aq, B, T, Hq, hd, c.rope_dims, m->lnb, pos));
+  const float scale = 1.0f / sqrtf((float)hd);
+  if ((exact && !bt->split_attn) || hd != 256 || NQ > 16) {
+    CK(k_sdpa_decode_batched(ctx, s, bt->aq, kc, vc, B, T, Hq, Hkv, hd, bt->cap, pos, scale, bt->att));
+    CK(k_sigmoid_gate(ctx, s, bt->agate, bt->att, R * Hq * hd, 1, bt->agated));
+  } else {
+    CK(launch_battn(ctx, s, bt->aq, kc, vc, pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks, chunk, NQ));
+    dim3 grid(NQ, Hkv, B);
+    battn_merge_kernel<<<grid, 256, 0, s>>>(bt->part, bt->qg, T, Hq, Hkv, nchunks, NQ, bt->agated);
+    CK(orn_launch_check(ctx, "battn_merge"));
+  }
+  return batch_mm(bt, o_proj, bt->agated, R, bt->r);
+}
+
+// keys per CTA of the split-KV attention: about six CTAs per SM over the whole launch, 128..512, a
+// multiple of 64; the launch covers the longest sequence (shorter ones leave chunks empty)
+void split_shape(const orn_batch* bt, int maxL, int* chunk, int* nchunks) {
+  const orn_ctx* ctx = bt->m->ctx;
+  int ch = (int)(((int64_t)maxL * bt->B * bt->m->cfg.n_kv_heads / (ctx->sm_count * 6) + 63) / 64 * 64);
+  ch = std::min(kMaxChunk, std::max(kMinChunk, ch));
+  *chunk = ch;
+  *nchunks = (maxL + ch - 1) / ch;
+}
+
+// the MTP head's input for B rows: fc([norm(embed(ids)) | norm(hidden)]) -> bt->mx (MtpHead::hidden, mtp.rs:150-190)
+int mtp_join(orn_batch* bt, const uint32_t* dev_ids, const bf16_t* hidden) {
+  orn_model* m = bt->m;
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  const orn_config& c = m->cfg;
+  const Mtp& h = m->mtp;
+  const int B = bt->B, H = c.hidden;
+  CK(k_embedding(ctx, s, m->embed, dev_ids, B, bt->memb));
+  CK(k_rms_norm(ctx, s, bt->memb, h.pre_fc_norm_embedding, B, H, c.rms_eps, bt->me));
+  CK(k_rms_norm(ctx, s, hidden, h.pre_fc_norm_hidden, B, H, c.rms_eps, bt->mh));
+  CK(k_concat2(ctx, s, bt->me, bt->mh, B, H, bt->mjoined));
+  CK(batch_mm(bt, h.fc, bt->mjoined, B, bt->mx));
+  return k_rms_norm(ctx, s, bt->mx, h.input_ln, B, H, c.rms_eps, bt->n);
+}
+
+__global__ void gather_window_kernel(const uint32_t* ids, const bf16_t* normed, const int* keep, int T, int H, uint32_t* tok1,
+                                     bf16_t* hid0, bf16_t* hrow) {
+  // per sequence b: the window's second token, its first hidden row (the re-encode's inputs) and
+  // the hidden row of the last kept position (the next draft's input)
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0 && T > 1) tok1[b] = ids[b * T + 1];
+  const uint4* r0 = reinterpret_cast<const uint4*>(normed + (size_t)(b * T) * H);
+  const uint4* rk = reinterpret_cast<const uint4*>(normed + (size_t)(b * T + keep[b] - 1) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    reinterpret_cast<uint4*>(hid0 + (size_t)b * H)[i] = r0[i];
+    reinterpret_cast<uint4*>(hrow + (size_t)b * H)[i] = rk[i];
+  }
+}
+__global__ void mtp_advance_kernel(int* mtp_pos, const int* keep, int B, int base) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) mtp_pos[b] += base + (keep ? keep[b] - 1 : 0);
 }
 
 // the device work of one step: everything between the upload of the ids and the download of the
@@ -380,7 +480,6 @@ int batch_body(orn_batch* bt, orn_ep* group, int T, int chunk, int nchunks) {
   CK(orn_launch_check(ctx, "conv_map"));
   CK(k_embedding(ctx, s, m->embed, bt->ids, R, bt->x));
   CK(k_rms_norm(ctx, s, bt->x, m->layers[0].input_ln, R, H, c.rms_eps, bt->n));
-  const int NQ = (Hq / Hkv) * T;
   for (int i = 0; i < c.n_layers; ++i) {
     const Layer& ly = m->layers[i];
     if (ly.linear) {
@@ -398,26 +497,8 @@ int batch_body(orn_batch* bt, orn_ep* group, int T, int chunk, int nchunks) {
       CK(k_rms_norm_gated(ctx, s, bt->gy, ly.gdn_norm, bt->z, R * c.gdn_v_heads, c.gdn_head_dim, c.rms_eps, bt->gated));
       CK(batch_mm(bt, ly.out_proj, bt->gated, R, bt->r));
     } else {
-      CK(batch_mm(bt, ly.q_proj, bt->n, R, bt->qg));
-      CK(batch_mm(bt, ly.k_proj, bt->n, R, bt->ak));
-      CK(batch_mm(bt, ly.v_proj, bt->n, R, bt->av));
-      CK(k_split_qgate(ctx, s, bt->qg, R, Hq, hd, bt->aq, bt->agate));
-      CK(k_rms_norm(ctx, s, bt->aq, ly.q_norm, R * Hq, hd, c.rms_eps, bt->aq));
-      CK(k_rms_norm(ctx, s, bt->ak, ly.k_norm, R * Hkv, hd, c.rms_eps, bt->ak));
-      CK(k_rope_batched(ctx, s, bt->aq, B, T, Hq, hd, c.rope_dims, m->lnb, bt->pos));
-      CK(k_rope_batched(ctx, s, bt->ak, B, T, Hkv, hd, c.rope_dims, m->lnb, bt->pos));
-      CK(k_kv_append_batched(ctx, s, bt->ak, bt->av, B, T, Hkv, hd, bt->cap, bt->pos, bt->kc[i], bt->vc[i]));
-      const float scale = 1.0f / sqrtf((float)hd);
-      if ((exact && !bt->split_attn) || hd != 256 || NQ > 16) {
-        CK(k_sdpa_decode_batched(ctx, s, bt->aq, bt->kc[i], bt->vc[i], B, T, Hq, Hkv, hd, bt->cap, bt->pos, scale, bt->att));
-        CK(k_sigmoid_gate(ctx, s, bt->agate, bt->att, R * Hq * hd, 1, bt->agated));
-      } else {
-        CK(launch_battn(ctx, s, bt->aq, bt->kc[i], bt->vc[i], bt->pos, B, T, Hq, Hkv, bt->cap, scale, bt->part, nchunks, chunk, NQ));
-        dim3 grid(NQ, Hkv, B);
-        battn_merge_kernel<<<grid, 256, 0, s>>>(bt->part, bt->qg, T, Hq, Hkv, nchunks, NQ, bt->agated);
-        CK(orn_launch_check(ctx, "battn_merge"));
-      }
-      CK(batch_mm(bt, ly.o_proj, bt->agated, R, bt->r));
+      CK(batch_attention(bt, ly.q_proj, ly.k_proj, ly.v_proj, ly.o_proj, ly.q_norm, ly.k_norm, T, bt->pos, bt->kc[i], bt->vc[i], exact,
+                         chunk, nchunks, false));
     }
     CK(k_add_rms_norm(ctx, s, bt->x, bt->r, ly.post_ln, R, H, c.rms_eps, bt->h, bt->n2));
     const orn_linear* sg = world > 1 ? bt->views[3 * i] : ly.moe.sw_gate;
@@ -448,6 +529,7 @@ int32_t orn_batch_destroy(orn_batch* bt) {
   if (bt->ids_h) cudaFreeHost(bt->ids_h);
   if (bt->targets_h) cudaFreeHost(bt->targets_h);
   for (orn_linear* v : bt->views) delete v;
+  for (orn_linear* v : bt->mtp_views) delete v;
   if (bt->own_ep) orn_ep_destroy(bt->own_ep);
   if (bt->own_ep_exact) orn_ep_destroy(bt->own_ep_exact);
   delete bt;
@@ -470,6 +552,7 @@ int32_t orn_batch_create(orn_model* m, int32_t B, int32_t T_max, int32_t cap, in
   bt->kc.assign(c.n_layers, nullptr); bt->vc.assign(c.n_layers, nullptr);
   bt->conv.assign(c.n_layers, nullptr); bt->ring.assign(c.n_layers, nullptr);
   bt->h_pos.assign(B, 0);
+  bt->h_mtp_pos.assign(B, 0);
   int rc = ORN_OK;
   auto A = [&](auto** p, size_t n) {
     if (rc != ORN_OK) return;
@@ -503,6 +586,12 @@ int32_t orn_batch_create(orn_model* m, int32_t B, int32_t T_max, int32_t cap, in
   A(&bt->att, R * QD); A(&bt->agated, R * QD);
   A(&bt->logits, R * (size_t)c.vocab);
   A(&bt->normed, R * H);
+  if (m->mtp.present) {
+    A(&bt->mtp_kc, kvsz); A(&bt->mtp_vc, kvsz); A(&bt->hrow, (size_t)B * H); A(&bt->hid0, (size_t)B * H);
+    A(&bt->memb, (size_t)B * H); A(&bt->me, (size_t)B * H); A(&bt->mh, (size_t)B * H); A(&bt->mjoined, (size_t)2 * B * H);
+    A(&bt->mx, (size_t)B * H); A(&bt->dhid, (size_t)B * H); A(&bt->prim, (size_t)B); A(&bt->tok1, (size_t)B); A(&bt->drafts, (size_t)B);
+    A(&bt->mtp_pos, (size_t)B);
+  }
   A(&bt->greedy_scratch, greedy_scratch_floats((int)R, c.vocab));
   bt->part_chunks = (cap + kMinChunk - 1) / kMinChunk;
   A(&bt->part, (size_t)B * c.n_kv_heads * bt->part_chunks * 16 * kPartStride);
@@ -535,6 +624,12 @@ int32_t orn_batch_reset(orn_batch* bt) {
   CK(orn_memset(m->ctx, bt->pos, 0, sizeof(int) * bt->B));
   CK(orn_memset(m->ctx, bt->cur, 0, sizeof(int) * bt->B));
   std::fill(bt->h_pos.begin(), bt->h_pos.end(), 0);
+  if (bt->mtp_pos) {
+    CK(orn_memset(m->ctx, bt->mtp_pos, 0, sizeof(int) * bt->B));
+    CK(orn_memset(m->ctx, bt->hrow, 0, sizeof(bf16_t) * (size_t)bt->B * c.hidden));
+    std::fill(bt->h_mtp_pos.begin(), bt->h_mtp_pos.end(), 0);
+  }
+  bt->drafted = false;
   bt->last_T = 0;
   return orn_sync(m->ctx);
 }
@@ -562,6 +657,14 @@ int32_t orn_batch_fill_random(orn_batch* bt, int32_t ctx_len, uint64_t seed) {
   set_ints_kernel<<<(bt->B + 127) / 128, 128, 0, ctx->stream>>>(bt->pos, bt->B, ctx_len);
   CK(orn_launch_check(ctx, "set_ints"));
   std::fill(bt->h_pos.begin(), bt->h_pos.end(), ctx_len);
+  if (bt->mtp_pos) {  // the MTP head's cache as far along as the trunk's, a random hidden row to draft from
+    CK(k_fill_bf16(ctx, ctx->stream, bt->mtp_kc, kvsz, seed + 1001, 0.f, 1.0f));
+    CK(k_fill_bf16(ctx, ctx->stream, bt->mtp_vc, kvsz, seed + 1003, 0.f, 1.0f));
+    CK(k_fill_bf16(ctx, ctx->stream, bt->hrow, (size_t)bt->B * c.hidden, seed + 1005, 0.f, 1.0f));
+    set_ints_kernel<<<(bt->B + 127) / 128, 128, 0, ctx->stream>>>(bt->mtp_pos, bt->B, ctx_len);
+    CK(orn_launch_check(ctx, "set_ints"));
+    std::fill(bt->h_mtp_pos.begin(), bt->h_mtp_pos.end(), ctx_len);
+  }
   return orn_sync(ctx);
 }
 
@@ -591,14 +694,10 @@ int32_t orn_batch_forward(orn_batch* bt, orn_ep* ep, const uint32_t* host_ids, i
   }
   const int world = orn_ep_world(group), rank = orn_ep_rank(group);
   if (world > 1) CK(ensure_shards(bt, rank, world));
-  // keys per CTA of the split-KV attention: about six CTAs per SM over the whole launch, 128..512,
-  // a multiple of 64; the launch covers the longest sequence (shorter ones leave chunks empty)
   int max_pos = 0;
   for (int b = 0; b < B; ++b) max_pos = std::max(max_pos, bt->h_pos[b]);
-  const int maxL = max_pos + T;
-  int chunk = (int)(((int64_t)maxL * B * c.n_kv_heads / (ctx->sm_count * 6) + 63) / 64 * 64);
-  chunk = std::min(kMaxChunk, std::max(kMinChunk, chunk));
-  const int nchunks = (maxL + chunk - 1) / chunk;
+  int chunk, nchunks;
+  split_shape(bt, max_pos + T, &chunk, &nchunks);
   // the previous step's targets have been read (its download synchronised) before ids_h is rewritten
   ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(s));
   memcpy(bt->ids_h, host_ids, sizeof(uint32_t) * (size_t)R);
@@ -663,8 +762,76 @@ int32_t orn_batch_commit(orn_batch* bt, const int32_t* host_keep) {
     CK(orn_launch_check(ctx, "conv_shift"));
   }
   for (int b = 0; b < bt->B; ++b) bt->h_pos[b] += host_keep[b];
+  if (bt->mtp_pos) {
+    // the next draft reads the hidden row of the last kept position; a window that followed a draft
+    // re-encodes the accepted draft token into the MTP head's cache (HistoryPolicy::Committed,
+    // mtp_generate.rs:292-301): KV row at the head's next position from (window token 1, hidden row 0),
+    // computed for every sequence, kept (the position advanced) only where the draft was accepted
+    const int T = bt->last_T, H = m->cfg.hidden;
+    gather_window_kernel<<<bt->B, 128, 0, s>>>(bt->ids, bt->normed, bt->keep, T, H, bt->tok1, bt->hid0, bt->hrow);
+    CK(orn_launch_check(ctx, "gather_window"));
+    if (bt->drafted && T == 2) {
+      const Mtp& h = m->mtp;
+      const bool exact = bt->exact || bt->B < 16;
+      CK(mtp_join(bt, bt->tok1, bt->hid0));
+      CK(batch_attention(bt, h.q_proj, h.k_proj, h.v_proj, h.o_proj, h.q_norm, h.k_norm, 1, bt->mtp_pos, bt->mtp_kc, bt->mtp_vc, exact,
+                         0, 0, true));
+      mtp_advance_kernel<<<(bt->B + 127) / 128, 128, 0, s>>>(bt->mtp_pos, bt->keep, bt->B, 0);
+      CK(orn_launch_check(ctx, "mtp_advance"));
+      for (int b = 0; b < bt->B; ++b) bt->h_mtp_pos[b] += host_keep[b] - 1;
+    }
+  }
+  bt->drafted = false;
   bt->last_T = 0;
   return ORN_OK;
+}
+
+// MtpHead::forward at depth 1 for every sequence (mtp.rs:150-262; the draft chain of
+// mtp_generate.rs:99-135): from the token each sequence is about to feed (its primary) and the trunk's
+// hidden row at the position that produced it, the draft of the token after it (raw-logit argmax).
+int32_t orn_batch_mtp_draft(orn_batch* bt, orn_ep* ep, const uint32_t* host_primary, uint32_t* host_drafts) {
+  if (!bt || !host_primary || !host_drafts) return ORN_ERR_ARG;
+  orn_model* m = bt->m;
+  orn_ctx* ctx = m->ctx;
+  cudaStream_t s = ctx->stream;
+  const orn_config& c = m->cfg;
+  const Mtp& h = m->mtp;
+  if (!h.present || !bt->mtp_pos) ORN_FAIL(ctx, ORN_ERR_STATE, "batch_mtp_draft: the model has no MTP head");
+  if (bt->last_T != 0) ORN_FAIL(ctx, ORN_ERR_STATE, "batch_mtp_draft: a window is waiting for its commit");
+  const int B = bt->B, H = c.hidden;
+  for (int b = 0; b < B; ++b)
+    if (bt->h_mtp_pos[b] + 2 > bt->cap) ORN_FAIL(ctx, ORN_ERR_STATE, "batch_mtp_draft: a sequence would pass the cache capacity");
+  const bool exact = bt->exact || B < 16;
+  orn_ep* group = ep;
+  if (!group) {
+    orn_ep** own = exact ? &bt->own_ep_exact : &bt->own_ep;
+    if (!*own) CK(orn_ep_init(ctx, nullptr, 0, 1, exact ? ORN_EP_EXACT : 0, own));
+    group = *own;
+  }
+  const int world = orn_ep_world(group), rank = orn_ep_rank(group);
+  if (world > 1) CK(ensure_shards(bt, rank, world));
+  int max_pos = 0;
+  for (int b = 0; b < B; ++b) max_pos = std::max(max_pos, bt->h_mtp_pos[b]);
+  int chunk, nchunks;
+  split_shape(bt, max_pos + 1, &chunk, &nchunks);
+  CK(orn_upload(ctx, bt->prim, host_primary, sizeof(uint32_t) * (size_t)B));
+  CK(mtp_join(bt, bt->prim, bt->hrow));
+  CK(batch_attention(bt, h.q_proj, h.k_proj, h.v_proj, h.o_proj, h.q_norm, h.k_norm, 1, bt->mtp_pos, bt->mtp_kc, bt->mtp_vc, exact, chunk,
+                     nchunks, false));
+  CK(k_add_rms_norm(ctx, s, bt->mx, bt->r, h.post_ln, B, H, c.rms_eps, bt->h, bt->n2));
+  const orn_linear* sg = world > 1 ? bt->mtp_views[0] : h.moe.sw_gate;
+  const orn_linear* su = world > 1 ? bt->mtp_views[1] : h.moe.sw_up;
+  const orn_linear* sd = world > 1 ? bt->mtp_views[2] : h.moe.sw_down;
+  CK(orn_ep_moe_block(group, h.moe.gate, sg, su, sd, h.moe.sh_gate, h.moe.sh_up, h.moe.sh_down, h.moe.sh_egate, bt->n2, B, c.top_k,
+                      c.norm_topk_prob, bt->mo, nullptr));
+  CK(k_add_rms_norm(ctx, s, bt->h, bt->mo, h.norm, B, H, c.rms_eps, bt->x, bt->dhid));
+  CK(batch_mm(bt, m->lm_head, bt->dhid, B, bt->logits));
+  CK(k_greedy(ctx, s, bt->logits, B, c.vocab, 0, bt->drafts, bt->greedy_scratch));
+  mtp_advance_kernel<<<(B + 127) / 128, 128, 0, s>>>(bt->mtp_pos, nullptr, B, 1);
+  CK(orn_launch_check(ctx, "mtp_advance"));
+  for (int b = 0; b < B; ++b) bt->h_mtp_pos[b] += 1;
+  bt->drafted = true;
+  return orn_download(ctx, host_drafts, bt->drafts, sizeof(uint32_t) * (size_t)B);
 }
 
 }  // extern "C"

@@ -1417,6 +1417,28 @@ int32_t orn_generate_step_mtp(orn_model* m, orn_cache* c, const uint32_t* prompt
   return ORN_OK;
 }
 
+// MtpHead::forward for T rows (mtp.rs:150-262): the head's cache advances by T; the draft is the
+// raw-logit argmax of the last row
+int32_t orn_mtp_forward(orn_model* m, orn_cache* c, const uint16_t* dev_hidden, const uint32_t* host_ids, int32_t T,
+                        int32_t kv_only, uint32_t* host_draft) {
+  if (!m || !c || !dev_hidden || !host_ids || T < 1 || T > kMaxRows) return ORN_ERR_ARG;
+  CK(orn_model_finalize(m));
+  orn_ctx* ctx = m->ctx;
+  Workspace& w = m->ws;
+  CK(upload_ids(m, host_ids, T));
+  CK(mtp_step(m, c, dev_hidden, w.ids, T, kv_only ? nullptr : m->lm_head, w.dh, kv_only ? nullptr : w.dlogits, kv_only != 0));
+  if (!kv_only && host_draft) {
+    CK(k_greedy(ctx, ctx->stream, w.dlogits + (size_t)(T - 1) * m->lm_head->O, 1, m->lm_head->O, 0, w.local, w.greedy_scratch));
+    return orn_download(ctx, host_draft, w.local, sizeof(uint32_t));
+  }
+  return orn_sync(ctx);
+}
+int32_t orn_cache_mtp_offset(const orn_cache* c) { return c ? c->h_mtp_pos : -1; }
+int32_t orn_cache_set_mtp_offset(orn_cache* c, int32_t v) {
+  if (!c || v < 0) return ORN_ERR_ARG;
+  return set_mtp_pos(c, v);
+}
+
 int32_t orn_get_prof(orn_model* m, orn_prof* out) {
   if (!m || !out) return ORN_ERR_ARG;
   *out = m->prof;

@@ -143,3 +143,107 @@ def test_split_kv_attention_alone(pkg, ctx, ctx_len):
         assert np.median(err) < 0.01 and np.median(cos) > 0.9999, (i, err, cos)
         assert np.mean(cos > 0.9999) >= 0.8, (i, cos)
     gm.free()
+
+
+def splitmix64(x):
+    x = (x + 0x9e3779b97f4a7c15) & 0xFFFFFFFFFFFFFFFF
+    x = ((x ^ (x >> 30)) * 0xbf58476d1ce4e5b9) & 0xFFFFFFFFFFFFFFFF
+    x = ((x ^ (x >> 27)) * 0x94d049bb133111eb) & 0xFFFFFFFFFFFFFFFF
+    return x ^ (x >> 31)
+
+
+def forced(stream, p, seed, cycle, emitted):
+    """the harness's forced draft for generated position emitted + 1 in this cycle, or None (orn_generate_step_mtp)"""
+    if emitted + 1 >= len(stream):
+        return None
+    uni = (splitmix64(seed + cycle * 8) >> 40) / 16777216.0
+    return int(stream[emitted + 1]) if uni < p else None
+
+
+def test_batched_mtp_cycles_equal_the_single_sequence_engine(pkg, ctx):
+    """MTP depth-1 decode of three sequences in lockstep (draft, verify window [primary, draft],
+    per-sequence acceptance, Committed re-encode) against the single-sequence engine: the drafts and
+    targets of every cycle against an op-level cycle of the same calls (orn_mtp_forward,
+    orn_forward_capture, orn_cache_rewind), and the emitted tokens against orn_generate_step_mtp
+    (itself compared with the oracle elsewhere).  Forced drafts (p = 0.6) make both acceptance
+    outcomes occur; unforced cycles use the head's own draft."""
+    cfg = hp.tiny_config(pkg.Config)
+    W = hp.tiny_model_weights(cfg, seed=21)
+    gm = hp.upload_model(pkg, ctx, cfg, W)
+    rng = np.random.default_rng(17)
+    B, NP, CYC, P = 3, 7, 9, 0.6
+    prompts = rng.integers(0, cfg.vocab, (B, NP)).astype(np.uint32)
+    seeds = [5, 6, 7]
+    # the single-sequence engine: the autoregressive stream (the forced drafts come from it) and the MTP loop's output
+    cache = gm.make_cache()
+    ar, mtp = [], []
+    for b in range(B):
+        cache.reset()
+        ar.append(pkg.generate_step(gm, cache, prompts[b], 30))
+        cache.reset()
+        toks, _ = pkg.generate_step_mtp(gm, cache, prompts[b], 1, 30, force=(ar[b], P, seeds[b]))
+        assert toks == ar[b]
+        mtp.append(toks)
+    # the same cycles at op level on the single-sequence engine: drafts, targets, acceptance per cycle
+    single = []
+    for b in range(B):
+        cache.reset()
+        gm.forward(cache, prompts[b][:4])
+        gm.forward(cache, prompts[b][4:NP - 1])
+        h = gm.forward(cache, prompts[b][NP - 1:])
+        primary = int(gm.head_greedy(h, 1)[0])
+        hrow = ctx.upload(h.numpy()[0:1].copy())
+        ctx.check(ctx._lib.orn_cache_set_mtp_offset(cache.h, 0), "mtp offset")
+        emitted, log = 0, []
+        for cyc in range(CYC):
+            off = ctx._lib.orn_cache_mtp_offset(cache.h)
+            draft = gm.mtp_forward(cache, hrow, [primary])
+            f = forced(ar[b], P, seeds[b], cyc, emitted)
+            used = draft if f is None else f
+            vh = gm.forward(cache, np.array([primary, used], np.uint32), capture=True)
+            tg = gm.head_greedy(vh, 2)
+            k = 1 if int(tg[0]) == used else 0
+            cache.rewind(k + 1)
+            ctx.check(ctx._lib.orn_cache_set_mtp_offset(cache.h, off + 1), "mtp offset")
+            if k:
+                gm.mtp_forward(cache, vh, [used], kv_only=True)
+            hrow = ctx.upload(vh.numpy()[k:k + 1].copy())
+            log.append((draft, used, [int(t) for t in tg], k))
+            emitted += k + 1
+            primary = int(tg[k])
+        single.append(log)
+    cache.free()
+    # the batched engine, exact arithmetic
+    bt = pkg.Batch(gm, B, t_max=2, cap=96, exact=True)
+    for a in range(0, NP - 1, 2):
+        bt.forward(prompts[:, a:a + 2], want_targets=False)
+        bt.commit(np.full(B, 2, np.int32))
+    tg, _ = bt.forward(prompts[:, NP - 1:])
+    bt.commit(np.ones(B, np.int32))
+    primary = tg[:, 0].copy()
+    emitted = [0] * B
+    out = [[] for _ in range(B)]
+    for cyc in range(CYC):
+        drafts = bt.mtp_draft(primary)
+        used = drafts.copy()
+        for b in range(B):
+            f = forced(ar[b], P, seeds[b], cyc, emitted[b])
+            if f is not None:
+                used[b] = f
+        tg, _ = bt.forward(np.stack([primary, used], 1))
+        k = (tg[:, 0] == used).astype(np.int32)
+        bt.commit(k + 1)
+        for b in range(B):
+            want = single[b][cyc]
+            assert (int(drafts[b]), int(used[b]), [int(t) for t in tg[b]], int(k[b])) == want, (b, cyc)
+            out[b].append(int(primary[b]))
+            if k[b]:
+                out[b].append(int(used[b]))
+            emitted[b] += int(k[b]) + 1
+            primary[b] = tg[b, k[b]]
+    ks = [x[3] for log in single for x in log]
+    assert 0 < sum(ks) < len(ks)          # both acceptance outcomes occurred
+    for b in range(B):
+        assert out[b] == mtp[b][:len(out[b])], b
+    bt.free()
+    gm.free()
