@@ -124,8 +124,8 @@ def step_bytes(cfg, T, with_state=True):
 
 
 def batch_step_bytes(cfg, B, T, ctx_len, world):
-    """Algorithmic bytes ONE GPU moves for one batched verify step of B local sequences, T rows
-    each, at ctx_len cached positions: every dense weight once; this rank's E / world experts of
+    """Algorithmic bytes ONE GPU moves for one batched MTP cycle of B local sequences (draft pass of
+    one row, verify pass of T rows each) at ctx_len cached positions: every dense weight once; this rank's E / world experts of
     every layer once (B * T * top_k routes of the whole job touch every expert); per sequence the
     KV cache of every attention layer once and the gated-delta state once in, T times out."""
     one = step_bytes(cfg, 1, with_state=False)
@@ -136,7 +136,13 @@ def batch_step_bytes(cfg, B, T, ctx_len, world):
     n_att = cfg.n_layers - n_lin
     kv = n_att * 2 * cfg.n_kv_heads * cfg.head_dim * 2 * ctx_len
     state = n_lin * cfg.gdn_v_heads * 128 * 128 * 4 * (1 + T)
-    return dense + cfg.n_layers * (E // world) * expert + B * (kv + state)
+    # the draft pass: the bf16 MTP layer (join, attention, router, this rank's experts, shared expert),
+    # the lm_head a second time, the head's own KV cache once per sequence
+    QD, KVD = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    bf = lambda o, kk: o * kk * 2.0
+    mtp = (bf(H, 2 * H) + bf(2 * QD, H) + 2 * bf(KVD, H) + bf(H, QD) + bf(E, H) + ((E // world) + 1) * 3 * bf(cfg.expert_inter, H)
+           + cfg.vocab * H * 1.0625 + B * 2 * cfg.n_kv_heads * cfg.head_dim * 2 * ctx_len)
+    return dense + cfg.n_layers * (E // world) * expert + B * (kv + state) + mtp
 
 
 def ep_decode(pkg, ctx, dist, rank, world, model, cfg, steps=8, warmup=3, total_seqs=64, ctx_len=4096, T=2):
@@ -144,10 +150,12 @@ def ep_decode(pkg, ctx, dist, rank, world, model, cfg, steps=8, warmup=3, total_
     positions each, every sequence stepping a verify window of 2 rows (MTP depth 1) per pass over
     the weights; sequences split evenly over the ranks (data parallel), the routed experts of every
     layer split E / N per rank (expert parallel) through the library's own block.  Every rank runs
-    this.  A step = host ids in, trunk forward of B * 2 rows, lm_head, greedy targets of every row
-    back on the host, per-sequence acceptance (keep 1 or 2 at the benchmark's forced p) committed.
-    The MTP head's draft pass (one more attention + MoE layer and a second lm_head per cycle) is not
-    part of the batched engine; tokens/s counts accepted tokens per verify step."""
+    this.  A step = one MTP depth-1 cycle of every sequence: the MTP head's draft pass (B rows: its
+    attention layer over its own cache, its MoE block, lm_head, argmax; drafts back on the host), the
+    verify pass (B * 2 rows through the trunk, lm_head, greedy targets back on the host), per-sequence
+    acceptance and commit with the Committed re-encode.  Acceptance is the benchmark's forced pattern
+    (keep 2 with p, else 1) whatever the head drafted: random weights accept nothing by themselves,
+    and traffic and arithmetic do not depend on the outcome.  tokens/s counts kept tokens."""
     from ornith_rs_b200 import ep
     if total_seqs % world or cfg.n_experts % world:
         return None
@@ -163,9 +171,14 @@ def ep_decode(pkg, ctx, dist, rank, world, model, cfg, steps=8, warmup=3, total_
     ids = [rng.integers(0, cfg.vocab, (B, T)).astype(np.uint32) for _ in range(steps + warmup)]
     keeps = [(1 + (rng.random(B) < FORCE_P)).astype(np.int32) for _ in range(steps + warmup)]
 
+    primary = ids[0][:, 0].copy()
+
     def step(i):
-        tg, _ = bt.forward(ids[i], ep=group)
+        # one MTP depth-1 cycle per sequence: draft, verify window [primary, draft], acceptance, commit
+        drafts = bt.mtp_draft(primary, ep=group)
+        tg, _ = bt.forward(np.stack([primary, drafts], 1), ep=group)
         bt.commit(keeps[i])
+        primary[:] = tg[np.arange(B), keeps[i] - 1]
         return tg
 
     for i in range(warmup):
@@ -202,9 +215,9 @@ def ep_decode(pkg, ctx, dist, rank, world, model, cfg, steps=8, warmup=3, total_
             "tokens_per_s": tokens / (ms * 1e-3), "e2e_tokens_per_s": tokens / wall,
             "tokens_per_step": tokens / steps, "bytes_per_gpu_per_step": per_gpu,
             "frac": per_gpu / (step_ms * 1e-3) / 1e9 / peak, "peak_source": which,
-            "launches_per_step": int(launches // steps), "h2d_bytes_per_step": B * T * 4 + B * 4,
-            "d2h_bytes_per_step": B * T * 4, "targets_checksum": check,
-            "scope": "trunk verify step + lm_head + greedy + per-sequence commit; the MTP head's draft pass is not batched",
+            "launches_per_step": int(launches // steps), "h2d_bytes_per_step": B * 4 + B * T * 4 + B * 4,
+            "d2h_bytes_per_step": B * 4 + B * T * 4, "targets_checksum": check,
+            "scope": "MTP depth-1 cycle: draft pass + verify pass (trunk, lm_head, greedy) + per-sequence commit and re-encode",
             "parallelism": "dp%d over sequences x ep%d over experts" % (world, world)}
 
 
