@@ -111,6 +111,8 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
   if (ctx->t0) cudaEventDestroy(ctx->t0);
   if (ctx->t1) cudaEventDestroy(ctx->t1);
   cudaFree(ctx->dev_err);
+  cudaFree(ctx->split_partial);
+  cudaFree(ctx->split_arrivals);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return ORN_OK;

@@ -51,6 +51,9 @@ constexpr int BK = 64;             // weights per K block: one 128-byte swizzle 
 constexpr int kGemmThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2..9: dequantise + epilogue
 constexpr int kDqWarps = 8;
 constexpr uint32_t kTmemCols = 512;
+constexpr int kSplitMaxRows = 512;                      // dense products up to this many rows may split K
+constexpr size_t kSplitPartialBytes = (size_t)64 << 20;  // f32 partials of one launch
+constexpr size_t kSplitTiles = 4096;                     // arrival counters
 constexpr uint32_t kWTileBytes = BM * BK * 2;
 constexpr int kMaxIn = 12;  // IN ring slots (raw weight boxes + token tiles)
 constexpr int kMaxW = 3;    // W ring slots (dequantised weight tile)
@@ -71,6 +74,9 @@ struct GemmParams {
   int BN, NT, stages /*IN ring*/, w_stages /*W ring*/, f_tiles;
   uint32_t stage_bytes;
   uint32_t tmem_cols;  // power of two >= NT * BN (and >= 32): what the CTA takes of tensor memory
+  int splits;          // dense products over few rows: an item is one of `splits` ranges of the K blocks of a tile
+  float* partial;      // [tile][split][token][128 features] f32 partial sums of the split items
+  int* arrivals;       // [tile] how many splits of the tile have stored their partial (the last one reduces)
   int* err;
 };
 
@@ -324,18 +330,25 @@ template <> struct Fmt<ORN_Q6K> {
 
 struct Item {
   int e, tok0, ntok, ft;
+  int kb0, kb1;  // K blocks of this item
+  int tile, split;
 };
 ORN_D bool get_item(const GemmParams& P, int w, int n_items, Item& it) {
   if (w >= n_items) return false;
   if (P.items != nullptr) {
     const int4 v = P.items[w];
     it.e = v.x; it.tok0 = v.y; it.ntok = v.z; it.ft = v.w;
+    it.kb0 = 0; it.kb1 = P.K / BK; it.tile = w; it.split = 0;
   } else {
-    const int g = w / P.f_tiles;
+    const int tile = w / P.splits;
+    const int g = tile / P.f_tiles;
     it.e = 0;
-    it.ft = w - g * P.f_tiles;
+    it.ft = tile - g * P.f_tiles;
     it.tok0 = g * P.NT * P.BN;
     it.ntok = min(P.NT * P.BN, P.rows - it.tok0);
+    const int KB = P.K / BK, per = (KB + P.splits - 1) / P.splits;
+    it.tile = tile; it.split = w - tile * P.splits;
+    it.kb0 = it.split * per; it.kb1 = min(KB, it.kb0 + per);
   }
   return true;
 }
@@ -361,6 +374,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_bar[2 * kMaxIn + 2 * kMaxW + 2];
   __shared__ uint32_t s_tmem;
+  __shared__ int s_last;  // split-K: this CTA stored the last partial of its tile and reduces it
   using F = Fmt<KIND>;
   constexpr bool kDirect = KIND == ORN_BF16;  // the MMA reads the weight box where TMA put it
   constexpr uint32_t kInRaw = kDirect ? kWTileBytes : F::kRawBytes;
@@ -396,7 +410,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
   tc_fence_after();
   const uint32_t tmem = s_tmem;
   const int n_items = P.items != nullptr ? *P.n_items : P.dense_items;
-  const int KB = P.K / BK;
   const uint32_t x_tile_bytes = (uint32_t)P.BN * 128u;
   const RecGeom geo = rec_geom(KIND, P.K);
 
@@ -409,7 +422,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
       for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
         const int nt = (w.ntok + P.BN - 1) / P.BN;
         const int wrow = w.e * P.O + w.ft * BM;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int si = it % SI;
           ok = mbar_wait(bar_in_free + 8 * si, ((it / SI) & 1u) ^ 1u, P.err);
           if (!ok) break;
@@ -431,7 +444,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
         const int nt = (w.ntok + P.BN - 1) / P.BN;
         ok = mbar_wait(bar_acc_empty, acc_ph ^ 1u, P.err);  // the previous item's accumulators were read
         tc_fence_after();
-        for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it) {
           const int si = it % SI, sw = it % SW;
           ok = mbar_wait(bar_full + 8 * sw, (it / SW) & 1u, P.err);  // implies landed[si]: the dequantisers waited for it
           if (!ok) break;
@@ -442,7 +455,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
 #pragma unroll
             for (int j = 0; j < BK / 16; ++j)
               tc_mma(tmem + (uint32_t)(t * P.BN), smem_desc(wa + j * 32), smem_desc(xa + t * x_tile_bytes + j * 32), idesc,
-                     (kb > 0 || j > 0) ? 1u : 0u);
+                     (kb > w.kb0 || j > 0) ? 1u : 0u);
           tc_commit(bar_in_free + 8 * si);  // both slots are free once these MMAs have read them
           tc_commit(bar_w_free + 8 * sw);
         }
@@ -462,7 +475,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
     Item w;
     bool ok = true;
     for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
-      for (int kb = 0; kb < KB; ++kb, ++it) {
+      for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
         const int si = it % SI, sw = it % SW;
         ok = mbar_wait(bar_w_free + 8 * sw, ((it / SW) & 1u) ^ 1u, P.err) && mbar_wait(bar_landed + 8 * si, (it / SI) & 1u, P.err);
         if (!ok) break;
@@ -473,20 +486,43 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_full + 8 * sw);
       }
-      if (!ok) break;
-      ok = mbar_wait(bar_acc_full, acc_ph, P.err);
+      if (ok) ok = mbar_wait(bar_acc_full, acc_ph, P.err);
+      if (P.splits > 1) {
+        // the warps of a split item meet at named barriers below: they leave together or not at all
+        // (a warp whose bounded wait ran out still comes here, and its verdict is everybody's)
+        uint32_t all;
+        asm volatile(
+            "{\n"
+            ".reg .pred p, q;\n"
+            "setp.ne.u32 q, %1, 0;\n"
+            "barrier.red.and.pred p, 1, %2, q;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(all)
+            : "r"(ok ? 1u : 0u), "n"(kDqWarps * 32)
+            : "memory");
+        ok = all != 0;
+      }
       if (!ok) break;
       acc_ph ^= 1u;
       tc_fence_after();
       const int fo = w.ft * BM + q * 32 + lane;  // TMEM lane = feature
       const int nt = (w.ntok + P.BN - 1) / P.BN;
+      // split-K items store f32 partials [token][128 features] instead of results
+      float* part = P.splits > 1 ? P.partial + (size_t)(w.tile * P.splits + w.split) * (size_t)(P.NT * P.BN) * BM : nullptr;
       for (int t = 0; t < nt; ++t) {
         for (int c0 = 16 * colhalf; c0 < P.BN; c0 += 32) {
           if (t * P.BN + c0 >= w.ntok) break;  // warp-uniform
           uint32_t v[16];
           tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * P.BN + c0), v);
           tmem_ld_wait();
-          if (fo < P.O) {
+          if (part != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int tok = t * P.BN + c0 + j;
+              if (tok < w.ntok) part[(size_t)tok * BM + q * 32 + lane] = __uint_as_float(v[j]);
+            }
+          } else if (fo < P.O) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int tok = t * P.BN + c0 + j;
@@ -502,6 +538,52 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty);
+      if (part != nullptr) {
+        // the CTA that stores a tile's last partial adds the partials in split order (a fixed order:
+        // the result does not depend on which CTA comes last) and writes the tile
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kDqWarps * 32) : "memory");
+        if (dq == 0) s_last = atomicAdd(&P.arrivals[w.tile], 1) == P.splits - 1 ? 1 : 0;
+        asm volatile("bar.sync 1, %0;" ::"n"(kDqWarps * 32) : "memory");
+        if (s_last) {
+          __threadfence();
+          const float4* base = reinterpret_cast<const float4*>(P.partial + (size_t)w.tile * P.splits * (size_t)(P.NT * P.BN) * BM);
+          const size_t stride4 = (size_t)(P.NT * P.BN) * BM / 4;
+          const int n4 = w.ntok * (BM / 4);
+          constexpr int kU = 4;  // float4 pieces per thread and round: their loads are in flight together
+          for (int i0 = dq; i0 < n4; i0 += kU * kDqWarps * 32) {
+            float4 acc[kU];
+#pragma unroll
+            for (int u = 0; u < kU; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sp = 0; sp < P.splits; ++sp) {
+              float4 v[kU];
+#pragma unroll
+              for (int u = 0; u < kU; ++u) {
+                const int i = i0 + u * kDqWarps * 32;
+                v[u] = i < n4 ? __ldcg(base + sp * stride4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int u = 0; u < kU; ++u) { acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w; }
+            }
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+              const int i = i0 + u * kDqWarps * 32;
+              if (i >= n4) continue;
+              const int tok = i / (BM / 4), f = 4 * (i - tok * (BM / 4));
+              const int feat = w.ft * BM + f;
+              const size_t orow = (size_t)(w.tok0 + tok);
+              const float r4[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (feat + e < P.O) {
+                  if (P.y_f32 != nullptr) P.y_f32[orow * P.ldy + feat + e] = r4[e];
+                  else P.y[orow * P.ldy + feat + e] = f2bf(r4[e]);
+                }
+            }
+          }
+          if (dq == 0) P.arrivals[w.tile] = 0;  // ready for the next launch
+        }
+      }
     }
   }
   tc_fence_before();
@@ -686,10 +768,35 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
   P.stage_bytes = in_raw + (uint32_t)P.NT * BN * 128u;
   P.tmem_cols = 32;
   while ((int)P.tmem_cols < P.NT * BN) P.tmem_cols <<= 1;
+  // Dense products over few rows are one token group: the K loop of an item is a chain of short
+  // latency-bound steps (about 0.65 us per K block), so the blocks of a tile are split over several
+  // CTAs whose f32 partials the last of them adds in split order.  The number of splits depends on
+  // (O, K) only, never on the row count, so that a row's bits do not depend on how many rows share
+  // the launch.
+  P.splits = 1; P.partial = nullptr; P.arrivals = nullptr;
+  if (grp == nullptr && rows <= kSplitMaxRows && L->K / BK >= 8) {
+    const int tiles = P.f_tiles * ((rows + P.NT * BN - 1) / (P.NT * BN));
+    int sp = std::max(1, ctx->sm_count / tiles);                  // one round of items over the SMs
+    sp = std::min(sp, std::min(8, L->K / BK / 4));               // at least 4 K blocks per item
+    if (sp > 1) {                                                 // no split may be empty
+      const int KBn = L->K / BK, per = (KBn + sp - 1) / sp;
+      sp = (KBn + per - 1) / per;
+    }
+    const int groups = (rows + P.NT * BN - 1) / (P.NT * BN);
+    const size_t need = (size_t)P.f_tiles * groups * sp * (size_t)(P.NT * BN) * BM * sizeof(float);
+    if (sp > 1 && need <= kSplitPartialBytes && (size_t)P.f_tiles * groups <= kSplitTiles) {
+      if (ctx->split_partial == nullptr) {
+        ORN_CHECK_CUDA(ctx, cudaMalloc((void**)&ctx->split_partial, kSplitPartialBytes));
+        ORN_CHECK_CUDA(ctx, cudaMalloc((void**)&ctx->split_arrivals, kSplitTiles * sizeof(int)));
+        ORN_CHECK_CUDA(ctx, cudaMemset(ctx->split_arrivals, 0, kSplitTiles * sizeof(int)));
+      }
+      P.splits = sp; P.partial = ctx->split_partial; P.arrivals = ctx->split_arrivals;
+    }
+  }
   // A launch of narrow items with more items than SMs runs two CTAs per SM (each with half the
   // shared memory and its own accumulator columns): an item's K loop is a chain of short,
   // latency-bound steps, and two chains per SM overlap.
-  const int est_items = P.f_tiles * (grp ? std::max(L->E, (rows + P.NT * BN - 1) / (P.NT * BN)) : (rows + P.NT * BN - 1) / (P.NT * BN));
+  const int est_items = P.splits * P.f_tiles * (grp ? std::max(L->E, (rows + P.NT * BN - 1) / (P.NT * BN)) : (rows + P.NT * BN - 1) / (P.NT * BN));
   int ctas = 1;
   size_t smem = 0;
   if (P.tmem_cols <= 256 && est_items > ctx->sm_count) {
@@ -741,7 +848,7 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
   if (grp == nullptr) {
     P.items = nullptr; P.n_items = nullptr;
     const int groups = (rows + P.NT * BN - 1) / (P.NT * BN);
-    P.dense_items = P.f_tiles * groups;
+    P.dense_items = P.f_tiles * groups * P.splits;
     grid = std::min(P.dense_items, ctas * ctx->sm_count);
   } else {
     if (L->E > 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: more than 1024 experts");

@@ -29,6 +29,11 @@ struct orn_ctx {
   // CTAs pile onto the first SMs the previous kernel leaves); expert up and attention +0.3 %;
   // expert down -4 %, so it stays a plain launch.  ORN_PDL_MASK overrides, ORN_NO_PDL=1 clears it.
   int pdl_mask = 27;
+  // split-K scratch of the tensor-core product (gemm.cu): partial sums and per-tile arrival counters,
+  // allocated once at the first product that splits (never inside a stream capture: callers run a
+  // shape eagerly before they capture it)
+  float* split_partial = nullptr;
+  int* split_arrivals = nullptr;
 };
 
 // Records an event after the launch just made and attributes the device time
