@@ -48,8 +48,10 @@ namespace {
 
 constexpr int BM = 128;            // features per tile: the tensor core's M
 constexpr int BK = 64;             // weights per K block: one 128-byte swizzle row of bf16
-constexpr int kGemmThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2..9: dequantise + epilogue
-constexpr int kDqWarps = 8;
+// warp 0: TMA, warp 1: MMA, then DQW warps that dequantise and run the epilogue: 8 (two threads per
+// feature row of a tile) for launches with one or two CTAs per SM, 4 (one thread per row) for
+// launches of narrow items, where up to four small CTAs share an SM
+constexpr int gemm_threads(int dqw) { return 64 + 32 * dqw; }
 constexpr uint32_t kTmemCols = 512;
 constexpr int kSplitMaxRows = 512;                      // dense products up to this many rows may split K
 constexpr size_t kSplitPartialBytes = (size_t)64 << 20;  // f32 partials of one launch
@@ -369,8 +371,8 @@ struct GemmMaps {
 //   full[w]     W slot w dequantised                       (one arrival per dequantising warp)
 //   in_free[i]  the MMAs that read IN slot i are done      (tcgen05.commit)
 //   w_free[w]   the MMAs that read W slot w are done       (tcgen05.commit)
-template <int KIND>
-__global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant__ GemmMaps maps, GemmParams P) {
+template <int KIND, int DQW>
+__global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(const __grid_constant__ GemmMaps maps, GemmParams P) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_bar[2 * kMaxIn + 2 * kMaxW + 2];
   __shared__ uint32_t s_tmem;
@@ -391,11 +393,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
       mbar_init(bar_in_free + 8 * i, 1);
     }
     for (int i = 0; i < SW; ++i) {
-      mbar_init(bar_full + 8 * i, kDqWarps);
+      mbar_init(bar_full + 8 * i, DQW);
       mbar_init(bar_w_free + 8 * i, 1);
     }
     mbar_init(bar_acc_full, 1);
-    mbar_init(bar_acc_empty, kDqWarps);
+    mbar_init(bar_acc_empty, DQW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
   }
@@ -466,11 +468,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
     }
   } else {
     // ---- dequantising warps, then the epilogue of the item
-    const int dq = threadIdx.x - 64;   // 0..255
+    const int dq = threadIdx.x - 64;   // 0 .. 32 * DQW - 1
     const int r = dq & 127;            // feature row of the tile this thread dequantises
-    const int half = dq >> 7;          // which 32 of the K block's 64 weights
+    const int half = dq >> 7;          // DQW == 8: which 32 of the K block's 64 weights (DQW == 4: both)
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
-    const int colhalf = (warp - 2) >> 2;  // the two warps of a quadrant split the 16-column groups
+    const int colhalf = (warp - 2) >> 2;  // DQW == 8: the two warps of a quadrant split the 16-column groups
     uint32_t it = 0, acc_ph = 0;
     Item w;
     bool ok = true;
@@ -480,7 +482,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
         ok = mbar_wait(bar_w_free + 8 * sw, ((it / SW) & 1u) ^ 1u, P.err) && mbar_wait(bar_landed + 8 * si, (it / SI) & 1u, P.err);
         if (!ok) break;
         if (!kDirect) {
-          F::convert(in0 + si * P.stage_bytes, r, kb, half, smem0 + sw * kWTileBytes + (uint32_t)r * 128u, geo);
+          if (DQW == 8) {
+            F::convert(in0 + si * P.stage_bytes, r, kb, half, smem0 + sw * kWTileBytes + (uint32_t)r * 128u, geo);
+          } else {
+            F::convert(in0 + si * P.stage_bytes, r, kb, 0, smem0 + sw * kWTileBytes + (uint32_t)r * 128u, geo);
+            F::convert(in0 + si * P.stage_bytes, r, kb, 1, smem0 + sw * kWTileBytes + (uint32_t)r * 128u, geo);
+          }
           fence_async_smem();  // the tensor core reads these bytes through the async proxy
         }
         __syncwarp();
@@ -499,7 +506,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
             "selp.u32 %0, 1, 0, p;\n"
             "}\n"
             : "=r"(all)
-            : "r"(ok ? 1u : 0u), "n"(kDqWarps * 32)
+            : "r"(ok ? 1u : 0u), "n"(DQW * 32)
             : "memory");
         ok = all != 0;
       }
@@ -511,7 +518,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
       // split-K items store f32 partials [token][128 features] instead of results
       float* part = P.splits > 1 ? P.partial + (size_t)(w.tile * P.splits + w.split) * (size_t)(P.NT * P.BN) * BM : nullptr;
       for (int t = 0; t < nt; ++t) {
-        for (int c0 = 16 * colhalf; c0 < P.BN; c0 += 32) {
+        for (int c0 = 16 * colhalf; c0 < P.BN; c0 += (DQW == 8 ? 32 : 16)) {
           if (t * P.BN + c0 >= w.ntok) break;  // warp-uniform
           uint32_t v[16];
           tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * P.BN + c0), v);
@@ -542,16 +549,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
         // the CTA that stores a tile's last partial adds the partials in split order (a fixed order:
         // the result does not depend on which CTA comes last) and writes the tile
         __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(kDqWarps * 32) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(DQW * 32) : "memory");
         if (dq == 0) s_last = atomicAdd(&P.arrivals[w.tile], 1) == P.splits - 1 ? 1 : 0;
-        asm volatile("bar.sync 1, %0;" ::"n"(kDqWarps * 32) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(DQW * 32) : "memory");
         if (s_last) {
           __threadfence();
           const float4* base = reinterpret_cast<const float4*>(P.partial + (size_t)w.tile * P.splits * (size_t)(P.NT * P.BN) * BM);
           const size_t stride4 = (size_t)(P.NT * P.BN) * BM / 4;
           const int n4 = w.ntok * (BM / 4);
           constexpr int kU = 4;  // float4 pieces per thread and round: their loads are in flight together
-          for (int i0 = dq; i0 < n4; i0 += kU * kDqWarps * 32) {
+          for (int i0 = dq; i0 < n4; i0 += kU * DQW * 32) {
             float4 acc[kU];
 #pragma unroll
             for (int u = 0; u < kU; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -559,7 +566,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
               float4 v[kU];
 #pragma unroll
               for (int u = 0; u < kU; ++u) {
-                const int i = i0 + u * kDqWarps * 32;
+                const int i = i0 + u * DQW * 32;
                 v[u] = i < n4 ? __ldcg(base + sp * stride4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
               }
 #pragma unroll
@@ -567,7 +574,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) k_qgemm(const __grid_constant
             }
 #pragma unroll
             for (int u = 0; u < kU; ++u) {
-              const int i = i0 + u * kDqWarps * 32;
+              const int i = i0 + u * DQW * 32;
               if (i >= n4) continue;
               const int tok = i / (BM / 4), f = 4 * (i - tok * (BM / 4));
               const int feat = w.ft * BM + f;
@@ -689,18 +696,18 @@ EncodeTiledFn encode_tiled() {
 }
 
 std::mutex g_gemm_mu;
-std::set<std::pair<int, int>> g_gemm_granted;  // (device, format): shared-memory limit raised
+std::set<std::pair<int, int>> g_gemm_granted;  // (device, format and warp count): shared-memory limit raised
 
-template <int KIND>
+template <int KIND, int DQW>
 int launch_qgemm(orn_ctx* ctx, cudaStream_t s, const GemmMaps& maps, const GemmParams& P, int grid, size_t smem) {
   {
     std::lock_guard<std::mutex> lock(g_gemm_mu);
-    if (!g_gemm_granted.count({ctx->device, KIND})) {
-      ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_qgemm<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));  // + static barriers
-      g_gemm_granted.insert({ctx->device, KIND});
+    if (!g_gemm_granted.count({ctx->device, KIND * 16 + DQW})) {
+      ORN_CHECK_CUDA(ctx, cudaFuncSetAttribute(k_qgemm<KIND, DQW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));  // + static barriers
+      g_gemm_granted.insert({ctx->device, KIND * 16 + DQW});
     }
   }
-  k_qgemm<KIND><<<grid, kGemmThreads, smem, s>>>(maps, P);
+  k_qgemm<KIND, DQW><<<grid, gemm_threads(DQW), smem, s>>>(maps, P);
   if (ctx->kt == nullptr) return orn_launch_check(ctx, "k_qgemm");
   // per-kernel timing: one label per shape
   static std::set<std::string> pool;
@@ -797,9 +804,20 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
   // shared memory and its own accumulator columns): an item's K loop is a chain of short,
   // latency-bound steps, and two chains per SM overlap.
   const int est_items = P.splits * P.f_tiles * (grp ? std::max(L->E, (rows + P.NT * BN - 1) / (P.NT * BN)) : (rows + P.NT * BN - 1) / (P.NT * BN));
-  int ctas = 1;
+  int ctas = 1, dqw = 8;
   size_t smem = 0;
-  if (P.tmem_cols <= 256 && est_items > ctx->sm_count) {
+  // Launches of many narrow items (routed experts with a few rows each): small CTAs of 4 dequantising
+  // warps, two-slot rings, up to four per SM: an item's K loop is a latency chain, four chains overlap.
+  if (P.tmem_cols <= 128 && est_items > 2 * ctx->sm_count && P.splits == 1) {
+    const int ws = L->kind == ORN_BF16 ? 1 : 2;
+    const size_t need = 1024 + (size_t)ws * kWTileBytes + 2 * (size_t)P.stage_bytes;
+    const int fit = (int)((226 * 1024) / (need + 1024));  // + static shared memory and the allocation granule
+    if (fit >= 3) {
+      ctas = std::min(4, fit); dqw = 4; P.w_stages = ws; P.stages = 2;
+      smem = need;
+    }
+  }
+  if (ctas == 1 && P.tmem_cols <= 256 && est_items > ctx->sm_count) {
     const size_t budget2 = 108 * 1024;
     const int ws = L->kind == ORN_BF16 ? 1 : 2;
     const int st = (int)std::min<size_t>(kMaxIn, (budget2 - (size_t)ws * kWTileBytes) / P.stage_bytes);
@@ -864,12 +882,21 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
     P.items = items; P.n_items = n_items; P.dense_items = 0;
     grid = ctas * ctx->sm_count;
   }
+  if (dqw == 4) {
+    switch (L->kind) {
+      case ORN_Q4K: return launch_qgemm<ORN_Q4K, 4>(ctx, s, maps, P, grid, smem);
+      case ORN_Q6K: return launch_qgemm<ORN_Q6K, 4>(ctx, s, maps, P, grid, smem);
+      case ORN_A8: return launch_qgemm<ORN_A8, 4>(ctx, s, maps, P, grid, smem);
+      case ORN_BF16: return launch_qgemm<ORN_BF16, 4>(ctx, s, maps, P, grid, smem);
+      case ORN_A4: return launch_qgemm<ORN_A4, 4>(ctx, s, maps, P, grid, smem);
+    }
+  }
   switch (L->kind) {
-    case ORN_Q4K: return launch_qgemm<ORN_Q4K>(ctx, s, maps, P, grid, smem);
-    case ORN_Q6K: return launch_qgemm<ORN_Q6K>(ctx, s, maps, P, grid, smem);
-    case ORN_A8: return launch_qgemm<ORN_A8>(ctx, s, maps, P, grid, smem);
-    case ORN_BF16: return launch_qgemm<ORN_BF16>(ctx, s, maps, P, grid, smem);
-    case ORN_A4: return launch_qgemm<ORN_A4>(ctx, s, maps, P, grid, smem);
+    case ORN_Q4K: return launch_qgemm<ORN_Q4K, 8>(ctx, s, maps, P, grid, smem);
+    case ORN_Q6K: return launch_qgemm<ORN_Q6K, 8>(ctx, s, maps, P, grid, smem);
+    case ORN_A8: return launch_qgemm<ORN_A8, 8>(ctx, s, maps, P, grid, smem);
+    case ORN_BF16: return launch_qgemm<ORN_BF16, 8>(ctx, s, maps, P, grid, smem);
+    case ORN_A4: return launch_qgemm<ORN_A4, 8>(ctx, s, maps, P, grid, smem);
   }
   ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: unknown weight format");
 }

@@ -420,7 +420,7 @@ int k_gather_gemv(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf16
 // ---------------------------------------------------------------------------
 namespace {
 constexpr int kGroupThreads = 256;  // 8 warps
-constexpr int kGroupRows = 128;     // output rows of one expert a block owns
+constexpr int kGroupRows = 128;     // output rows of one expert a block owns (32 for one small dense matrix over many rows)
 constexpr int kGroupBatch = 4;      // activation rows staged per pass (the mat-vec's row limit)
 
 // One warp, R output rows starting at row0 of expert matrix rows `rowbase`, M staged activation
@@ -480,15 +480,15 @@ ORN_D void grouped_rows(const LinDev& L, int64_t rowbase, int row0, int row_end,
 template <int KIND, int R, int SU>
 __global__ void __launch_bounds__(kGroupThreads)
 grouped_gemv_kernel(LinDev L, const bf16_t* __restrict__ xs, const int* __restrict__ seg, bf16_t* __restrict__ y,
-                    const uint32_t* __restrict__ row_map) {
+                    const uint32_t* __restrict__ row_map, int rows_per_block) {
   extern __shared__ __align__(16) uint8_t gsm[];
   bf16_t* xsm = reinterpret_cast<bf16_t*>(gsm);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int e = blockIdx.y;
   const int first = seg[e], n = seg[e + 1] - first;
   if (n <= 0) return;
-  const int chunk0 = blockIdx.x * kGroupRows;
-  const int row_end = min(L.O, chunk0 + kGroupRows);
+  const int chunk0 = blockIdx.x * rows_per_block;
+  const int row_end = min(L.O, chunk0 + rows_per_block);
   // the expert's rows in passes of four; blockIdx.z takes every gridDim.z-th pass
   for (int m0 = kGroupBatch * blockIdx.z; m0 < n; m0 += kGroupBatch * gridDim.z) {
     const int M = min(kGroupBatch, n - m0);
@@ -518,10 +518,12 @@ int launch_grouped(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf1
   int z = L->E == 1 ? (max_rows + kGroupBatch - 1) / kGroupBatch : 4;
   if (z < 1) z = 1;
   if (z > 64) z = 64;
-  dim3 grid((L->O + kGroupRows - 1) / kGroupRows, L->E, z);
+  // one small dense matrix (a router) over many rows: narrower blocks so that the launch fills the part
+  const int rpb = (L->E == 1 && L->O <= 1024) ? 32 : kGroupRows;
+  dim3 grid((L->O + rpb - 1) / rpb, L->E, z);
   const int units = L->K / Fmt<KIND>::kWeightsPerUnit;
-  if (units > 32) grouped_gemv_kernel<KIND, 2, 2><<<grid, kGroupThreads, smem, st>>>(lin_dev(L), xs, seg, y, row_map);
-  else grouped_gemv_kernel<KIND, 4, 1><<<grid, kGroupThreads, smem, st>>>(lin_dev(L), xs, seg, y, row_map);
+  if (units > 32) grouped_gemv_kernel<KIND, 2, 2><<<grid, kGroupThreads, smem, st>>>(lin_dev(L), xs, seg, y, row_map, rpb);
+  else grouped_gemv_kernel<KIND, 4, 1><<<grid, kGroupThreads, smem, st>>>(lin_dev(L), xs, seg, y, row_map, rpb);
   return orn_launch_check(ctx, "grouped_gemv");
 }
 }  // namespace
