@@ -317,7 +317,7 @@ int32_t orn_cache_offset(const orn_cache* c);
 int32_t orn_forward(orn_model* m, orn_cache* c, const uint32_t* host_ids, int32_t T,
                     uint16_t* dev_normed, uint16_t* dev_pre_norm /*nullable*/);
 /* generate::prefill (src/generate.rs:90-136) over all n tokens: chunks of prefill_step rows
- * (the reference's default is 2048).  A chunk of 64 rows or more runs every projection as one wide
+ * (the reference's default is 2048; up to 8192 rows per chunk are taken whole).  A chunk of 64 rows or more runs every projection as one wide
  * product on the tensor cores (orn_gemm / orn_gather_gemm), experts grouped by a counting sort;
  * shorter chunks run as row-invariant windows of up to 4 rows.  The caches advance by n.
  * dev_normed (nullable) receives the n hidden rows after the final norm, [n, hidden]. */

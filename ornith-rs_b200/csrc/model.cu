@@ -715,7 +715,7 @@ int wide_mm(orn_model* m, const orn_linear* L, const bf16_t* x, int T, bf16_t* y
 }
 constexpr int kWideMinRows = 64;    // measured: below about 60 rows the 4-row mat-vec windows are faster (the
                                     // reference's own crossover, kquant.rs MM_ROW_LIMIT, is 16 on its hardware)
-constexpr int kWideMaxRows = 2048;  // the reference's prefill chunk (generate.rs:25)
+constexpr int kWideMaxRows = 8192;  // widest chunk of the wide path (the reference's default chunk is 2048, generate.rs:25)
 
 int wide_reserve(orn_model* m, int rows) {
   WideWs& w = m->wide;
