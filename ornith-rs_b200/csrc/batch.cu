@@ -348,6 +348,31 @@ int batch_mm(orn_batch* bt, const orn_linear* L, const bf16_t* x, int R, bf16_t*
   return ORN_OK;
 }
 
+// several projections of the same rows: consecutive matrices that share format and row length go
+// out as one tensor-core launch (their feature tiles form one tile space)
+int batch_mm_multi(orn_batch* bt, const orn_linear* const* Ls, bf16_t* const* ys, int n, const bf16_t* x, int R) {
+  orn_ctx* ctx = bt->m->ctx;
+  if (!(R >= 16 && !bt->exact)) {
+    for (int i = 0; i < n; ++i) CK(batch_mm(bt, Ls[i], x, R, ys[i]));
+    return ORN_OK;
+  }
+  int i = 0;
+  while (i < n) {
+    int j = i + 1;
+    while (j < n && j - i < 4 && Ls[j]->kind == Ls[i]->kind && Ls[j]->K == Ls[i]->K && Ls[i]->K % 64 == 0) ++j;
+    if (j - i == 1) {
+      CK(batch_mm(bt, Ls[i], x, R, ys[i]));
+    } else {
+      void* yv[4];
+      int ld[4];
+      for (int k = i; k < j; ++k) { yv[k - i] = ys[k]; ld[k - i] = Ls[k]->O; }
+      CK(f_qgemm_multi(ctx, ctx->stream, Ls + i, yv, ld, j - i, x, R));
+    }
+    i = j;
+  }
+  return ORN_OK;
+}
+
 // views of this rank's E / world experts of every layer's routed matrices
 int ensure_shards(orn_batch* bt, int rank, int world) {
   if (bt->shard_rank == rank && bt->shard_world == world) return ORN_OK;
@@ -397,13 +422,15 @@ int batch_attention(orn_batch* bt, const orn_linear* q_proj, const orn_linear* k
   cudaStream_t s = ctx->stream;
   const orn_config& c = m->cfg;
   const int B = bt->B, R = B * T, Hq = c.n_heads, Hkv = c.n_kv_heads, hd = c.head_dim, NQ = (Hq / Hkv) * T;
-  CK(batch_mm(bt, k_proj, bt->n, R, bt->ak));
-  CK(batch_mm(bt, v_proj, bt->n, R, bt->av));
+  {
+    const orn_linear* pl[3] = {k_proj, v_proj, q_proj};
+    bf16_t* py[3] = {bt->ak, bt->av, bt->qg};
+    CK(batch_mm_multi(bt, pl, py, kv_only ? 2 : 3, bt->n, R));
+  }
   CK(k_rms_norm(ctx, s, bt->ak, k_norm, R * Hkv, hd, c.rms_eps, bt->ak));
   CK(k_rope_batched(ctx, s, bt->ak, B, T, Hkv, hd, c.rope_dims, m->lnb, pos));
   CK(k_kv_append_batched(ctx, s, bt->ak, bt->av, B, T, Hkv, hd, bt->cap, pos, kc, vc));
   if (kv_only) return ORN_OK;
-  CK(batch_mm(bt, q_proj, bt->n, R, bt->qg));
   CK(k_split_qgate(ctx, s, bt->qg, R, Hq, hd, bt->aq, bt->agate));
   CK(k_rms_norm(ctx, s, bt->aq, q_norm, R * Hq, hd, c.rms_eps, bt->aq));
   CK(k_rope_batched(ctx, s, bt->aq, B, T, Hq, hd, c.rope_dims, m->lnb, pos));
@@ -483,12 +510,11 @@ int batch_body(orn_batch* bt, orn_ep* group, int T, int chunk, int nchunks) {
   for (int i = 0; i < c.n_layers; ++i) {
     const Layer& ly = m->layers[i];
     if (ly.linear) {
-      CK(batch_mm(bt, ly.in_qkv, bt->n, R, bt->qkv));
+      const orn_linear* pl[4] = {ly.in_qkv, ly.in_z, ly.in_b, ly.in_a};
+      bf16_t* py[4] = {bt->qkv, bt->z, bt->b, bt->a};
+      CK(batch_mm_multi(bt, pl, py, 4, bt->n, R));
       scatter_rows_kernel<<<R, 128, 0, s>>>(bt->qkv, bt->conv_map, D, bt->conv[i]);  // row (b, t) -> window row S + t of sequence b
       CK(orn_launch_check(ctx, "scatter_rows"));
-      CK(batch_mm(bt, ly.in_z, bt->n, R, bt->z));
-      CK(batch_mm(bt, ly.in_b, bt->n, R, bt->b));
-      CK(batch_mm(bt, ly.in_a, bt->n, R, bt->a));
       CK(k_gdn_front_batched(ctx, s, bt->conv[i], (int64_t)bt->conv_rows * D, ly.conv_w, bt->a, bt->b, ly.a_log, ly.dt_bias, B, T,
                              c.gdn_k_heads, c.gdn_v_heads, c.gdn_head_dim, c.gdn_conv_kernel, 1e-6f, bt->gq, bt->gk, bt->gv,
                              bt->beta, bt->gg));

@@ -295,8 +295,15 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
   EPCK(k_grouped_gemv(ctx, s, sh_egate, dev_x, ep->seg1, ep->gs, nullptr, R));
   const bool wide_shared = !ep->exact && R >= 16 && H % 64 == 0 && SI % 64 == 0;
   if (wide_shared) {  // like the routed experts: one dense contraction per matrix over all R rows
-    EPCK(f_qgemm(ctx, s, sh_gate, dev_x, R, ep->sg, SI, nullptr, nullptr));  // a row's bits do not depend on the tile shape
-    EPCK(f_qgemm(ctx, s, sh_up, dev_x, R, ep->su, SI, nullptr, nullptr));
+    if (sh_gate->kind == sh_up->kind && sh_gate->K == sh_up->K) {  // one launch for both (a row's bits do not depend on the tile shape)
+      const orn_linear* pl[2] = {sh_gate, sh_up};
+      void* py[2] = {ep->sg, ep->su};
+      const int ld[2] = {SI, SI};
+      EPCK(f_qgemm_multi(ctx, s, pl, py, ld, 2, dev_x, R));
+    } else {
+      EPCK(f_qgemm(ctx, s, sh_gate, dev_x, R, ep->sg, SI, nullptr, nullptr));
+      EPCK(f_qgemm(ctx, s, sh_up, dev_x, R, ep->su, SI, nullptr, nullptr));
+    }
   } else {
     EPCK(k_grouped_gemv(ctx, s, sh_gate, dev_x, ep->seg1, ep->sg, nullptr, R));
     EPCK(k_grouped_gemv(ctx, s, sh_up, dev_x, ep->seg1, ep->su, nullptr, R));

@@ -55,6 +55,10 @@ size_t qgemm_scratch_bytes(int rows, int E, int O);
 int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, int rows, void* y, int ldy,
             const QGemmGroup* grp /*nullable: dense*/, void* scratch /*grouped only*/, int out_f32 = 0,
             int bn_force = 0 /*> 0: token-tile width (multiple of 16, <= 256)*/);
+// up to four matrices of one format and row length over the same rows in one dense launch
+int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, void* const* ys, const int* ldys, int n,
+                  const bf16_t* x, int rows, const QGemmGroup* grp = nullptr, void* scratch = nullptr, int out_f32 = 0,
+                  int bn_force = 0);
 int f_route_sort(orn_ctx* ctx, cudaStream_t s, const uint32_t* rhs, int rows, int E, int* seg, int* cursor, uint32_t* perm);
 int f_gather_rows(orn_ctx* ctx, cudaStream_t s, const bf16_t* x, const uint32_t* lhs /*nullable*/, const uint32_t* perm,
                   int rows, int K, bf16_t* xs);

@@ -62,16 +62,21 @@ constexpr int kMaxW = 3;    // W ring slots (dequantised weight tile)
 constexpr uint32_t kGemmWaitLimit = 1u << 16;  // try_wait rounds (each may sleep kGemmHintNs)
 constexpr uint32_t kGemmHintNs = 20000;
 
+constexpr int kMaxJobs = 4;  // matrices of one dense launch (projections that share their input rows)
+struct GemmJob {
+  int O, tile0;        // output features; first feature tile of this matrix in the launch's tile space
+  int ldy;             // elements between output rows
+  bf16_t* y;
+  float* y_f32;        // non-null: float32 output instead of bfloat16
+};
 struct GemmParams {
-  LinDev W;
+  int njobs;
+  GemmJob job[kMaxJobs];
   const int4* items;   // grouped: {expert, first row, rows, feature tile}; null = dense
   const int* n_items;  // grouped: device count
   int dense_items;     // dense: feature tiles x token groups
   int rows;            // rows of x (dense) / of the sorted row space (grouped)
-  int O, K;
-  bf16_t* y;
-  float* y_f32;              // non-null: float32 output instead of bfloat16
-  int ldy;                   // elements between output rows
+  int K;
   const uint32_t* row_map;   // nullable: output row of sorted row p
   int BN, NT, stages /*IN ring*/, w_stages /*W ring*/, f_tiles;
   uint32_t stage_bytes;
@@ -334,18 +339,22 @@ struct Item {
   int e, tok0, ntok, ft;
   int kb0, kb1;  // K blocks of this item
   int tile, split;
+  int job;       // which matrix of the launch (ft counts inside it)
 };
 ORN_D bool get_item(const GemmParams& P, int w, int n_items, Item& it) {
   if (w >= n_items) return false;
   if (P.items != nullptr) {
     const int4 v = P.items[w];
     it.e = v.x; it.tok0 = v.y; it.ntok = v.z; it.ft = v.w;
-    it.kb0 = 0; it.kb1 = P.K / BK; it.tile = w; it.split = 0;
+    it.kb0 = 0; it.kb1 = P.K / BK; it.tile = w; it.split = 0; it.job = 0;
   } else {
     const int tile = w / P.splits;
     const int g = tile / P.f_tiles;
     it.e = 0;
     it.ft = tile - g * P.f_tiles;
+    it.job = 0;
+    while (it.job + 1 < P.njobs && it.ft >= P.job[it.job + 1].tile0) ++it.job;
+    it.ft -= P.job[it.job].tile0;
     it.tok0 = g * P.NT * P.BN;
     it.ntok = min(P.NT * P.BN, P.rows - it.tok0);
     const int KB = P.K / BK, per = (KB + P.splits - 1) / P.splits;
@@ -355,12 +364,15 @@ ORN_D bool get_item(const GemmParams& P, int w, int n_items, Item& it) {
   return true;
 }
 
-struct GemmMaps {
-  CUtensorMap x;    // tokens [rows, K] bf16, box [BN, 64], 128-byte swizzle
+struct WeightMaps {
   CUtensorMap w64;  // row records as bytes [E*O, rec], boxes [128, 64] / [128, 32] / [128, 16], no swizzle
   CUtensorMap w32;
   CUtensorMap w16;
   CUtensorMap wsw;  // bf16 weights only: [E*O, K] bf16, box [128, 64], 128-byte swizzle
+};
+struct GemmMaps {
+  CUtensorMap x;    // tokens [rows, K] bf16, box [BN, 64], 128-byte swizzle
+  WeightMaps w[kMaxJobs];
 };
 
 // Two rings per CTA.  The IN ring (deep: TMA latency is a few thousand cycles) holds what TMA brings
@@ -423,14 +435,15 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
       bool ok = true;
       for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
         const int nt = (w.ntok + P.BN - 1) / P.BN;
-        const int wrow = w.e * P.O + w.ft * BM;
+        const int wrow = w.e * P.job[w.job].O + w.ft * BM;
+        const WeightMaps& wm = maps.w[w.job];
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int si = it % SI;
           ok = mbar_wait(bar_in_free + 8 * si, ((it / SI) & 1u) ^ 1u, P.err);
           if (!ok) break;
           const uint32_t bar = bar_landed + 8 * si, base = in0 + si * P.stage_bytes;
           mbar_expect_tx(bar, (uint32_t)nt * x_tile_bytes + F::kTxBytes);
-          F::issue(&maps.w64, &maps.w32, &maps.w16, &maps.wsw, geo, kb, wrow, base, base, bar);
+          F::issue(&wm.w64, &wm.w32, &wm.w16, &wm.wsw, geo, kb, wrow, base, base, bar);
           for (int t = 0; t < nt; ++t) tma_load_2d(base + kInRaw + t * x_tile_bytes, &maps.x, kb * BK, w.tok0 + t * P.BN, bar);
         }
       }
@@ -513,6 +526,7 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
       if (!ok) break;
       acc_ph ^= 1u;
       tc_fence_after();
+      const GemmJob& J = P.job[w.job];
       const int fo = w.ft * BM + q * 32 + lane;  // TMEM lane = feature
       const int nt = (w.ntok + P.BN - 1) / P.BN;
       // split-K items store f32 partials [token][128 features] instead of results
@@ -529,14 +543,14 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
               const int tok = t * P.BN + c0 + j;
               if (tok < w.ntok) part[(size_t)tok * BM + q * 32 + lane] = __uint_as_float(v[j]);
             }
-          } else if (fo < P.O) {
+          } else if (fo < J.O) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int tok = t * P.BN + c0 + j;
               if (tok < w.ntok) {
                 const size_t orow = P.row_map != nullptr ? P.row_map[w.tok0 + tok] : (size_t)(w.tok0 + tok);
-                if (P.y_f32 != nullptr) P.y_f32[orow * P.ldy + fo] = __uint_as_float(v[j]);
-                else P.y[orow * P.ldy + fo] = f2bf(__uint_as_float(v[j]));
+                if (J.y_f32 != nullptr) J.y_f32[orow * J.ldy + fo] = __uint_as_float(v[j]);
+                else J.y[orow * J.ldy + fo] = f2bf(__uint_as_float(v[j]));
               }
             }
           }
@@ -582,9 +596,9 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
               const float r4[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
 #pragma unroll
               for (int e = 0; e < 4; ++e)
-                if (feat + e < P.O) {
-                  if (P.y_f32 != nullptr) P.y_f32[orow * P.ldy + feat + e] = r4[e];
-                  else P.y[orow * P.ldy + feat + e] = f2bf(r4[e]);
+                if (feat + e < J.O) {
+                  if (J.y_f32 != nullptr) J.y_f32[orow * J.ldy + feat + e] = r4[e];
+                  else J.y[orow * J.ldy + feat + e] = f2bf(r4[e]);
                 }
             }
           }
@@ -712,7 +726,7 @@ int launch_qgemm(orn_ctx* ctx, cudaStream_t s, const GemmMaps& maps, const GemmP
   // per-kernel timing: one label per shape
   static std::set<std::string> pool;
   char buf[96];
-  snprintf(buf, sizeof buf, "k_qgemm kind=%d O=%d K=%d rows=%d %s", KIND, P.O, P.K, P.rows, P.items ? "grouped" : "dense");
+  snprintf(buf, sizeof buf, "k_qgemm kind=%d O=%d%s K=%d rows=%d %s", KIND, P.job[0].O, P.njobs > 1 ? "+" : "", P.K, P.rows, P.items ? "grouped" : "dense");
   std::lock_guard<std::mutex> lock(g_gemm_mu);
   return orn_launch_check(ctx, pool.insert(buf).first->c_str());
 }
@@ -743,19 +757,37 @@ size_t qgemm_scratch_bytes(int rows, int E, int O) {
 // device memory for the grouped form.
 int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, int rows, void* y, int ldy,
             const QGemmGroup* grp, void* scratch, int out_f32, int bn_force) {
+  return f_qgemm_multi(ctx, s, &L, &y, &ldy, 1, x, rows, grp, scratch, out_f32, bn_force);
+}
+
+// Up to four matrices of one format and row length over the same rows in ONE launch (the projections
+// of a layer that share their input): their feature tiles form one tile space.  n == 1 is f_qgemm.
+int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, void* const* ys, const int* ldys, int n,
+                  const bf16_t* x, int rows, const QGemmGroup* grp, void* scratch, int out_f32, int bn_force) {
   if (rows < 1) return ORN_OK;
+  if (n < 1 || n > kMaxJobs) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: 1..4 matrices per launch");
+  if (grp != nullptr && n != 1) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: the grouped form takes one matrix");
+  const orn_linear* L = Ls[0];
+  for (int j = 1; j < n; ++j)
+    if (Ls[j]->kind != L->kind || Ls[j]->K != L->K || Ls[j]->E != 1)
+      ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: the matrices of one launch share format and row length");
   if (L->K % BK) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: K must be a multiple of 64");
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: x must be 16-byte aligned");
   if (grp == nullptr && L->E != 1) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: a routed weight goes through the grouped form");
   EncodeTiledFn enc = encode_tiled();
   if (enc == nullptr) ORN_FAIL(ctx, ORN_ERR_CUDA, "gemm: the driver has no cuTensorMapEncodeTiled");
   GemmParams P;
-  P.W = lin_dev(L);
-  P.O = L->O; P.K = L->K; P.rows = rows; P.ldy = ldy; P.err = ctx->dev_err;
-  P.y = out_f32 ? nullptr : reinterpret_cast<bf16_t*>(y);
-  P.y_f32 = out_f32 ? reinterpret_cast<float*>(y) : nullptr;
+  P.njobs = n;
+  P.f_tiles = 0;
+  for (int j = 0; j < n; ++j) {
+    GemmJob& J = P.job[j];
+    J.O = Ls[j]->O; J.tile0 = P.f_tiles; J.ldy = ldys[j];
+    J.y = out_f32 ? nullptr : reinterpret_cast<bf16_t*>(ys[j]);
+    J.y_f32 = out_f32 ? reinterpret_cast<float*>(ys[j]) : nullptr;
+    P.f_tiles += (Ls[j]->O + BM - 1) / BM;
+  }
+  P.K = L->K; P.rows = rows; P.err = ctx->dev_err;
   P.row_map = grp ? grp->row_map : nullptr;
-  P.f_tiles = (L->O + BM - 1) / BM;
   // token-tile width: wide tiles when there are many tokens per weight tile, narrow ones otherwise
   int per = grp ? (rows + L->E - 1) / L->E : rows;  // expected tokens per weight tile
   if (grp && grp->bn_hint > 0) per = grp->bn_hint;
@@ -852,14 +884,18 @@ int f_qgemm(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* x, 
   };
   bool ok = encode(&maps.x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, const_cast<bf16_t*>(x), (uint64_t)L->K, (uint64_t)rows,
                    (uint64_t)L->K * 2, BK, (uint32_t)BN, CU_TENSOR_MAP_SWIZZLE_128B);
-  const uint64_t wrows = (uint64_t)L->E * L->O;
-  if (L->kind == ORN_BF16) {
-    ok = ok && encode(&maps.wsw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, L->w, (uint64_t)L->K, wrows, (uint64_t)L->rec, BK, BM,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
-  } else {
-    ok = ok && encode(&maps.w64, CU_TENSOR_MAP_DATA_TYPE_UINT8, L->w, (uint64_t)L->rec, wrows, (uint64_t)L->rec, 64, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
-    ok = ok && encode(&maps.w32, CU_TENSOR_MAP_DATA_TYPE_UINT8, L->w, (uint64_t)L->rec, wrows, (uint64_t)L->rec, 32, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
-    ok = ok && encode(&maps.w16, CU_TENSOR_MAP_DATA_TYPE_UINT8, L->w, (uint64_t)L->rec, wrows, (uint64_t)L->rec, 16, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+  for (int j = 0; j < n; ++j) {
+    const orn_linear* Lj = Ls[j];
+    WeightMaps& wm = maps.w[j];
+    const uint64_t wrows = (uint64_t)Lj->E * Lj->O;
+    if (Lj->kind == ORN_BF16) {
+      ok = ok && encode(&wm.wsw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, Lj->w, (uint64_t)Lj->K, wrows, (uint64_t)Lj->rec, BK, BM,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+      ok = ok && encode(&wm.w64, CU_TENSOR_MAP_DATA_TYPE_UINT8, Lj->w, (uint64_t)Lj->rec, wrows, (uint64_t)Lj->rec, 64, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+      ok = ok && encode(&wm.w32, CU_TENSOR_MAP_DATA_TYPE_UINT8, Lj->w, (uint64_t)Lj->rec, wrows, (uint64_t)Lj->rec, 32, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+      ok = ok && encode(&wm.w16, CU_TENSOR_MAP_DATA_TYPE_UINT8, Lj->w, (uint64_t)Lj->rec, wrows, (uint64_t)Lj->rec, 16, BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+    }
   }
   if (!ok) ORN_FAIL(ctx, ORN_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed");
   int grid;
