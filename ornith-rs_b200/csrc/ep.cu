@@ -331,8 +331,15 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
     // product (an expert's records dequantised once per tile for all its rows)
     const int hint = std::max(1, (routes / W) / el);
     QGemmGroup sorted{ep->seg, nullptr, hint}, back{ep->seg, ep->perm, hint};
-    EPCK(f_qgemm(ctx, s, sw_gate, ep->xs, routes, ep->eg, I, &sorted, ep->gemm_scratch));
-    EPCK(f_qgemm(ctx, s, sw_up, ep->xs, routes, ep->eu, I, &sorted, ep->gemm_scratch));
+    if (sw_gate->kind == sw_up->kind) {  // gate and up of every expert in one launch (one plan, one tile space)
+      const orn_linear* pl[2] = {sw_gate, sw_up};
+      void* py[2] = {ep->eg, ep->eu};
+      const int ld[2] = {I, I};
+      EPCK(f_qgemm_multi(ctx, s, pl, py, ld, 2, ep->xs, routes, &sorted, ep->gemm_scratch));
+    } else {
+      EPCK(f_qgemm(ctx, s, sw_gate, ep->xs, routes, ep->eg, I, &sorted, ep->gemm_scratch));
+      EPCK(f_qgemm(ctx, s, sw_up, ep->xs, routes, ep->eu, I, &sorted, ep->gemm_scratch));
+    }
     ep_swiglu_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(ep->eg, ep->eu, n_owned, I, ep->eact);
     EPCK(orn_launch_check(ctx, "ep_swiglu"));
     EPCK(f_qgemm(ctx, s, sw_down, ep->eact, routes, ret, H, &back, ep->gemm_scratch));

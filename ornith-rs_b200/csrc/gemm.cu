@@ -347,6 +347,8 @@ ORN_D bool get_item(const GemmParams& P, int w, int n_items, Item& it) {
     const int4 v = P.items[w];
     it.e = v.x; it.tok0 = v.y; it.ntok = v.z; it.ft = v.w;
     it.kb0 = 0; it.kb1 = P.K / BK; it.tile = w; it.split = 0; it.job = 0;
+    while (it.job + 1 < P.njobs && it.ft >= P.job[it.job + 1].tile0) ++it.job;
+    it.ft -= P.job[it.job].tile0;
   } else {
     const int tile = w / P.splits;
     const int g = tile / P.f_tiles;
@@ -766,10 +768,9 @@ int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, voi
                   const bf16_t* x, int rows, const QGemmGroup* grp, void* scratch, int out_f32, int bn_force) {
   if (rows < 1) return ORN_OK;
   if (n < 1 || n > kMaxJobs) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: 1..4 matrices per launch");
-  if (grp != nullptr && n != 1) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: the grouped form takes one matrix");
   const orn_linear* L = Ls[0];
   for (int j = 1; j < n; ++j)
-    if (Ls[j]->kind != L->kind || Ls[j]->K != L->K || Ls[j]->E != 1)
+    if (Ls[j]->kind != L->kind || Ls[j]->K != L->K || Ls[j]->E != L->E)
       ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: the matrices of one launch share format and row length");
   if (L->K % BK) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: K must be a multiple of 64");
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: x must be 16-byte aligned");
@@ -909,7 +910,7 @@ int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, voi
     if (scratch == nullptr) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: the grouped form needs scratch");
     int* n_items = reinterpret_cast<int*>(scratch);
     int4* items = reinterpret_cast<int4*>(reinterpret_cast<uint8_t*>(scratch) + 256);
-    const int max_items = (int)((qgemm_scratch_bytes(rows, L->E, L->O) - 256) / sizeof(int4));
+    const int max_items = (int)((qgemm_scratch_bytes(rows, L->E, P.f_tiles * BM) - 256) / sizeof(int4));
     int threads = 32;
     while (threads < L->E) threads <<= 1;
     k_plan_items<<<1, threads, 0, s>>>(grp->seg, L->E, P.NT * BN, P.f_tiles, items, n_items, max_items);
