@@ -167,6 +167,11 @@ int32_t orn_gemm(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x, int
 int32_t orn_gather_gemm(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x,
                         const uint32_t* dev_lhs, const uint32_t* dev_rhs, int32_t rows,
                         void* dev_y, int32_t out_f32);
+/* Up to four matrices of one format and row length over the same M rows in ONE launch (the
+ * projections of a layer that share their input, e.g. q/k/v or the shared expert's gate and up):
+ * dev_ys[j] [M, O_j].  Same arithmetic contract as orn_gemm. */
+int32_t orn_gemm_multi(orn_ctx* ctx, const orn_linear* const* lins, int32_t n, const uint16_t* dev_x,
+                       int32_t M, void* const* dev_ys, int32_t out_f32);
 /* ops::embedding (src/ops/embedding.rs:18-47) for the affine-8 table */
 int32_t orn_embedding(orn_ctx* ctx, const orn_linear* table, const uint32_t* dev_ids, int32_t T,
                       uint16_t* dev_out);

@@ -81,6 +81,7 @@ SIGNATURES = {
     "orn_gemv": (i32, [vp, vp, vp, i32, vp, i32]),
     "orn_gather_gemv": (i32, [vp, vp, vp, vp, vp, i32, vp]),
     "orn_gemm": (i32, [vp, vp, vp, i32, vp, i32]),
+    "orn_gemm_multi": (i32, [vp, vp, i32, vp, i32, vp, i32]),
     "orn_gather_gemm": (i32, [vp, vp, vp, vp, vp, i32, vp, i32]),
     "orn_embedding": (i32, [vp, vp, vp, i32, vp]),
     "orn_rms_norm": (i32, [vp, vp, vp, i32, i32, f32, vp]),

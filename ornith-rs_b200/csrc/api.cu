@@ -402,6 +402,17 @@ int32_t orn_gemm(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x, int
   return f_qgemm(ctx, ctx->stream, lin, dev_x, M, dev_y, lin->O, nullptr, nullptr, out_f32);
 }
 
+int32_t orn_gemm_multi(orn_ctx* ctx, const orn_linear* const* lins, int32_t n, const uint16_t* x, int32_t M,
+                       void* const* ys, int32_t out_f32) {
+  if (!ctx || !lins || !x || !ys || M < 1 || n < 1 || n > 4) return ORN_ERR_ARG;
+  int ld[4];
+  for (int j = 0; j < n; ++j) {
+    if (!lins[j] || !ys[j]) return ORN_ERR_ARG;
+    ld[j] = lins[j]->O;
+  }
+  return f_qgemm_multi(ctx, ctx->stream, lins, ys, ld, n, x, M, nullptr, nullptr, out_f32, 0);
+}
+
 int32_t orn_gather_gemm(orn_ctx* ctx, const orn_linear* lin, const uint16_t* dev_x, const uint32_t* dev_lhs,
                         const uint32_t* dev_rhs, int32_t rows, void* dev_y, int32_t out_f32) {
   if (!ctx || !lin || !dev_x || !dev_lhs || !dev_rhs || !dev_y || rows < 1) return ORN_ERR_ARG;

@@ -61,6 +61,29 @@ def test_a_rows_product_does_not_depend_on_the_tile_shape(pkg, ctx, kind):
     L.free()
 
 
+@pytest.mark.parametrize("kind", [orc.Q4K, orc.A8, orc.BF16])
+def test_several_matrices_in_one_launch(pkg, ctx, kind):
+    """orn_gemm_multi: three projections of the same 100 rows (feature counts on and off the tile
+    height) in one launch, each against the oracle's mat-vec at the single product's tolerance."""
+    import ctypes as C
+    rng = np.random.default_rng(300 + kind)
+    K, M = 1024, 100
+    Os = (512, 96, 384)
+    Ws = [hp.make_weights(rng, kind, 1, O, K) for O in Os]
+    x = hp.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    Ls = [lin_of(pkg, ctx, W) for W in Ws]
+    dx = ctx.upload(x)
+    ys = [ctx.empty((M, O), np.float32) for O in Os]
+    lp = (C.c_void_p * 3)(*[l.h for l in Ls])
+    yp = (C.c_void_p * 3)(*[y.ptr for y in ys])
+    ctx.check(ctx._lib.orn_gemm_multi(ctx.h, lp, 3, dx.ptr, M, yp, 1), "orn_gemm_multi")
+    for W, y in zip(Ws, ys):
+        want = orc.gemv(W, x, M, f32=True)
+        assert max_rel(y.numpy(), want) <= TOL, (W.O, max_rel(y.numpy(), want))
+    for l in Ls:
+        l.free()
+
+
 def test_gemm_raw_field_q4k_config1_shape(pkg, ctx):
     """BASELINE config 1's matrix (raw-field Q4_K, N = 512, K = 2048) at prompt width.  Raw fields
     give weights of one sign (mean +0.2, magnitudes up to 1), so the outputs are small differences of

@@ -99,3 +99,37 @@ def test_wide_prefill_at_full_width(pkg, ctx):
     assert got == ar
     c.free()
     m.free()
+
+
+def test_chunks_wider_than_2048_rows(pkg, ctx):
+    """A 2600-token prompt as one chunk (prefill_step 4096), as 2048 + 552, and as 1000-row chunks: one
+    layer of each kind on the tiny model.  Chunking changes which rows share a product launch and how
+    the attention and the recurrence are cut, not what a row computes: the first chunk's rows of the
+    2048 + 552 run equal the single chunk's bit for bit where the layer is causal-local (the
+    gated-delta layer and everything per row), and all runs agree to rounding everywhere."""
+    rng = np.random.default_rng(6)
+    for interval in (4, 1):
+        cfg = hp.tiny_config(pkg.Config, max_ctx=2700, n_layers=1, full_attn_interval=interval)
+        gm = hp.upload_model(pkg, ctx, cfg, hp.tiny_model_weights(cfg, seed=8))
+        ids = rng.integers(0, cfg.vocab, 2600).astype(np.uint32)
+        c = gm.make_cache()
+        outs = {}
+        for step in (4096, 2048, 1000):
+            c.reset()
+            outs[step] = gm.prefill(c, ids, prefill_step=step, want_hidden=True).numpy()
+            assert c.offset == 2600
+        for step in (2048, 1000):
+            rel, cos = row_errors(outs[step], outs[4096])
+            assert np.median(cos) >= 0.999, (interval, step, np.median(cos))
+            assert np.median(rel) <= 2e-2, (interval, step, np.median(rel))
+        # the decode step continues from the caches of the one-chunk prompt
+        c.reset()
+        gm.prefill(c, ids, prefill_step=4096)
+        h1 = gm.forward(c, ids[:2]).numpy()
+        c.reset()
+        gm.prefill(c, ids, prefill_step=1000)
+        h2 = gm.forward(c, ids[:2]).numpy()
+        rel, cos = row_errors(h1, h2)
+        assert cos.min() >= 0.99, (interval, cos)
+        c.free()
+        gm.free()
