@@ -259,6 +259,13 @@ int32_t orn_gated_delta(orn_ctx* ctx, const uint16_t* dev_q, const uint16_t* dev
                         const uint16_t* dev_v, const float* dev_g, const uint16_t* dev_beta,
                         float* dev_state, int32_t T, int32_t Hk, int32_t Hv, uint16_t* dev_y,
                         float* dev_snaps /*nullable*/);
+/* The same recurrence over a prompt chunk in chunkwise form on the warp-level tensor cores (64-token
+ * chunks: the triangular system inside a chunk solved once, the state carried from chunk to chunk by
+ * bf16 products with f32 accumulation).  Same contract as orn_gated_delta without snapshots; agrees
+ * with it to rounding, not bit for bit (the prompt path, src/generate.rs:99). */
+int32_t orn_gated_delta_prefill(orn_ctx* ctx, const uint16_t* dev_q, const uint16_t* dev_k,
+                                const uint16_t* dev_v, const float* dev_g, const uint16_t* dev_beta,
+                                float* dev_state, int32_t T, int32_t Hk, int32_t Hv, uint16_t* dev_y);
 
 /* ---- attention (src/ops/rope.rs:23-89, src/ops/sdpa.rs:122-229) */
 int32_t orn_rope(orn_ctx* ctx, uint16_t* dev_x, int32_t T, int32_t H, int32_t hd, int32_t dims,

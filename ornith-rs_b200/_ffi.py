@@ -110,6 +110,7 @@ SIGNATURES = {
     "orn_batch_mtp_draft": (i32, [vp, vp, vp, vp]),
     "orn_gdn_front": (i32, [vp] + [vp] * 7 + [i32] * 5 + [f32] + [vp] * 6),
     "orn_gated_delta": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp]),
+    "orn_gated_delta_prefill": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "orn_rope": (i32, [vp, vp, i32, i32, i32, i32, f32, i32]),
     "orn_sdpa_decode": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
     "orn_sdpa_prefill": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libornith_cuda.so")
-SOURCES = ["api.cu", "linear.cu", "ops.cu", "gdn.cu", "attn.cu", "sample.cu", "model.cu", "loader.cu", "fused.cu", "gemm.cu", "ep.cu", "batch.cu", "flash.cu"]
+SOURCES = ["api.cu", "linear.cu", "ops.cu", "gdn.cu", "attn.cu", "sample.cu", "model.cu", "loader.cu", "fused.cu", "gemm.cu", "ep.cu", "batch.cu", "flash.cu", "gdn_chunk.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

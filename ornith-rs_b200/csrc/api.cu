@@ -515,6 +515,18 @@ int32_t orn_gated_delta(orn_ctx* ctx, const uint16_t* q, const uint16_t* k, cons
   return k_gated_delta(ctx, ctx->stream, q, k, v, g, beta, state, T, Hk, Hv, y, snaps);
 }
 
+int32_t orn_gated_delta_prefill(orn_ctx* ctx, const uint16_t* q, const uint16_t* k, const uint16_t* v,
+                                const float* g, const uint16_t* beta, float* state, int32_t T, int32_t Hk,
+                                int32_t Hv, uint16_t* y) {
+  if (!ctx || !q || !k || !v || !g || !beta || !state || !y || T < 1) return ORN_ERR_ARG;
+  void* scratch = nullptr;
+  CK(orn_alloc(ctx, gdn_chunk_scratch_bytes(T, Hv), &scratch));
+  int rc = k_gated_delta_chunked(ctx, ctx->stream, q, k, v, g, beta, state, nullptr, 1, nullptr, T, Hk, Hv, y, scratch);
+  if (rc == ORN_OK) rc = orn_sync(ctx);
+  orn_free(ctx, scratch);
+  return rc;
+}
+
 int32_t orn_rope(orn_ctx* ctx, uint16_t* x, int32_t T, int32_t H, int32_t hd, int32_t dims,
                  float theta, int32_t offset) {
   if (!ctx || !x || T < 1 || dims > hd || dims % 2) return ORN_ERR_ARG;

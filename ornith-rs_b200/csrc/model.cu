@@ -750,6 +750,8 @@ int wide_reserve(orn_model* m, int rows) {
     const size_t big = std::max(qgemm_scratch_bytes((int)(R * k), (int)E, (int)H), qgemm_scratch_bytes((int)(R * k), (int)E, (int)I));
     rc = orn_alloc(m->ctx, big, &w.gemm_scratch);
     if (rc == ORN_OK) w.allocs.push_back(w.gemm_scratch);
+    if (rc == ORN_OK) rc = orn_alloc(m->ctx, gdn_chunk_scratch_bytes(rows, c.gdn_v_heads), &w.gdn_scratch);
+    if (rc == ORN_OK) w.allocs.push_back(w.gdn_scratch);
   }
   if (rc != ORN_OK) {
     for (void* p : w.allocs) cudaFree(p);
@@ -845,8 +847,12 @@ int prefill_wide(orn_model* m, orn_cache* cc, int T, bf16_t* normed_out /*nullab
       CK(wide_mm(m, ly.in_a, w.n, T, w.a));
       CK(k_gdn_front(ctx, s, w.cb, qkv, ly.conv_w, w.a, w.b, ly.a_log, ly.dt_bias, T, c.gdn_k_heads, c.gdn_v_heads,
                      c.gdn_head_dim, c.gdn_conv_kernel, 1e-6f, cc->conv[i], w.gq, w.gk, w.gv, w.beta, w.gg, nullptr));
-      CK(k_gated_delta_ring(ctx, s, w.gq, w.gk, w.gv, w.gg, w.beta, cc->ring[i], kRing, cc->cur, 1, T, c.gdn_k_heads,
-                            c.gdn_v_heads, w.gy));
+      if (wide_exact())  // token by token, the decode path's arithmetic
+        CK(k_gated_delta_ring(ctx, s, w.gq, w.gk, w.gv, w.gg, w.beta, cc->ring[i], kRing, cc->cur, 1, T, c.gdn_k_heads,
+                              c.gdn_v_heads, w.gy));
+      else  // chunkwise on the tensor cores; the state after the chunk's last token goes to ring slot cur + 1
+        CK(k_gated_delta_chunked(ctx, s, w.gq, w.gk, w.gv, w.gg, w.beta, nullptr, cc->ring[i], kRing, cc->cur, T, c.gdn_k_heads,
+                                 c.gdn_v_heads, w.gy, w.gdn_scratch));
       CK(k_rms_norm_gated(ctx, s, w.gy, ly.gdn_norm, w.z, T * c.gdn_v_heads, c.gdn_head_dim, c.rms_eps, w.gated));
       CK(wide_mm(m, ly.out_proj, w.gated, T, w.r));
     } else {

@@ -63,6 +63,7 @@ struct WideWs {
   uint32_t *ident = nullptr, *sorted_e = nullptr, *perm_inv = nullptr;  // ORN_WIDE_EXACT only
   int* seg = nullptr;
   void* gemm_scratch = nullptr;
+  void* gdn_scratch = nullptr;  // per-chunk operands of the chunkwise gated-delta recurrence
   bf16_t *x, *n, *r, *h, *n2, *mo;
   bf16_t *cb, *z, *a, *b, *gq, *gk, *gv, *beta, *gy, *gated;
   float* gg;

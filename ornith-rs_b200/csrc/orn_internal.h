@@ -218,6 +218,12 @@ int k_gdn_front_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, int64_
 int k_gated_delta_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* k, const bf16_t* v, const float* g,
                           const bf16_t* beta, float* rings, int nring, const int* cur, int B, int Tb, int Hk, int Hv, bf16_t* y);
 
+// gdn_chunk.cu: the recurrence over a prompt chunk in chunkwise form on the tensor cores (to rounding)
+size_t gdn_chunk_scratch_bytes(int T, int Hv);
+int k_gated_delta_chunked(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const bf16_t* k, const bf16_t* v, const float* g,
+                          const bf16_t* beta, float* state, float* ring, int nring, const int* cur, int T, int Hk, int Hv,
+                          bf16_t* y, void* scratch);
+
 // attn.cu
 int k_rope_batched(orn_ctx* ctx, cudaStream_t s, bf16_t* x, int B, int Tb, int H, int hd, int dims, float lnb, const int* pos);
 int k_kv_append_batched(orn_ctx* ctx, cudaStream_t s, const bf16_t* k, const bf16_t* v, int B, int Tb, int Hkv, int hd, int cap,
