@@ -36,26 +36,30 @@ struct PrepParams {
   float* gc;           // [Hv][nchunks] e^{L_C}
 };
 
-// grid (nchunks, Hv), 256 threads
+// grid (nchunks, Hv), 256 threads.  K K^T and Q K^T of the chunk on mma.sync (the inputs are bf16 already),
+// decays and the triangular solve in f32.
+constexpr int kPrepTile = kC * kPitchK;  // a [64][128] bf16 tile in shared memory
+constexpr int kPrepSmem = 2 * kPrepTile + (2 * kC * 65 + 2 * kC) * (int)sizeof(float);
 __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(PrepParams p) {
-  extern __shared__ __align__(16) float psm[];
-  float* Ks = psm;                 // [64][129]
-  float* Qs = Ks + kC * 129;       // [64][129]
-  float* BA = Qs + kC * 129;       // [64][65]  beta_s A[s][r] (strictly lower)
-  float* Tm = BA + kC * 65;        // [64][65]
-  float* L = Tm + kC * 65;         // [64]
-  float* bt = L + kC;              // [64]
+  extern __shared__ __align__(128) uint8_t psm[];
+  uint8_t* Kb = psm;                                                    // [64][pitch 272] bf16
+  uint8_t* Qb = psm + kPrepTile;
+  float* BA = reinterpret_cast<float*>(psm + 2 * kPrepTile);            // [64][65]  beta_s A[s][r] (strictly lower)
+  float* Tm = BA + kC * 65;                                             // [64][65]
+  float* L = Tm + kC * 65;                                              // [64]
+  float* bt = L + kC;                                                   // [64]
   const int c = blockIdx.x, hv = blockIdx.y, hk = hv / (p.Hv / p.Hk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, qd = lane & 3;
   const int t0 = c * kC;
-  for (int i = threadIdx.x; i < kC * 128; i += blockDim.x) {
-    const int s = i >> 7, d = i & 127, t = t0 + s;
-    float kv = 0.f, qv = 0.f;
+  for (int i = threadIdx.x; i < kC * 16; i += blockDim.x) {  // 16-byte pieces of the chunk's k and q rows (zeros beyond T)
+    const int s = i >> 4, pc = i & 15, t = t0 + s;
+    uint4 kv = make_uint4(0, 0, 0, 0), qv = kv;
     if (t < p.T) {
-      kv = bf2f(p.k[((size_t)t * p.Hk + hk) * 128 + d]);
-      qv = bf2f(p.q[((size_t)t * p.Hk + hk) * 128 + d]);
+      kv = ldg128(p.k + ((size_t)t * p.Hk + hk) * 128 + 8 * pc);
+      qv = ldg128(p.q + ((size_t)t * p.Hk + hk) * 128 + 8 * pc);
     }
-    Ks[s * 129 + d] = kv;
-    Qs[s * 129 + d] = qv;
+    *reinterpret_cast<uint4*>(Kb + s * kPitchK + 16 * pc) = kv;
+    *reinterpret_cast<uint4*>(Qb + s * kPitchK + 16 * pc) = qv;
   }
   if (threadIdx.x < kC) {
     const int t = t0 + threadIdx.x;
@@ -70,38 +74,61 @@ __global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(PrepParams p) {
   __syncthreads();
   bf16_t* out = p.scratch + ((size_t)hv * p.nchunks + c) * kChunkElems;
   bf16_t* Kg = out, *Qg = out + kC * 128, *Kd = out + 2 * kC * 128, *To = out + 3 * kC * 128, *Po = To + kC * kC;
-  // the two 64 x 64 products over the 128 key dims, with their decays
-  for (int i = threadIdx.x; i < kC * kC; i += blockDim.x) {
-    const int s = i >> 6, r = i & 63;
-    float kk = 0.f, qk = 0.f;
-    if (r <= s) {
-#pragma unroll 8
-      for (int d = 0; d < 128; ++d) {
-        const float kr = Ks[r * 129 + d];
-        kk = fmaf(Ks[s * 129 + d], kr, kk);
-        qk = fmaf(Qs[s * 129 + d], kr, qk);
-      }
+  {
+    // warp = (row tile mt of 16 tokens s, column half nh of 32 tokens r): 4 n-tiles, two products
+    const int mt = warp & 3, nh = warp >> 2;
+    const uint32_t kb_s = smem_u32(Kb), qb_s = smem_u32(Qb);
+    const uint32_t a_off = (16 * mt + (lane & 7) + 8 * ((lane >> 3) & 1)) * kPitchK + 16 * (lane >> 4);
+    const uint32_t b_off = (32 * nh + (lane & 7) + 8 * (lane >> 4)) * kPitchK + 16 * ((lane >> 3) & 1);
+    float kk[4][4], qk[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) kk[nt][e] = qk[nt][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t ak[4], aq[4], b0[4], b1[4];
+      ldsm4(kb_s + a_off + 32 * ks, ak);
+      ldsm4(qb_s + a_off + 32 * ks, aq);
+      ldsm4(kb_s + b_off + 32 * ks, b0);                  // tokens r 32nh .. +15
+      ldsm4(kb_s + b_off + 16 * kPitchK + 32 * ks, b1);   // tokens r 32nh+16 .. +31
+      mma16816(kk[0], ak, b0[0], b0[1]); mma16816(kk[1], ak, b0[2], b0[3]);
+      mma16816(kk[2], ak, b1[0], b1[1]); mma16816(kk[3], ak, b1[2], b1[3]);
+      mma16816(qk[0], aq, b0[0], b0[1]); mma16816(qk[1], aq, b0[2], b0[3]);
+      mma16816(qk[2], aq, b1[0], b1[1]); mma16816(qk[3], aq, b1[2], b1[3]);
     }
-    const float dec = r <= s ? expf(L[s] - L[r]) : 0.f;
-    BA[s * 65 + r] = r < s ? bt[s] * dec * kk : 0.f;
-    Po[i] = f2bf(dec * qk);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int s = 16 * mt + g + 8 * (e >> 1), r = 32 * nh + 8 * nt + 2 * qd + (e & 1);
+        const float dec = r <= s ? expf(L[s] - L[r]) : 0.f;
+        BA[s * 65 + r] = r < s ? bt[s] * dec * kk[nt][e] : 0.f;
+        Po[s * kC + r] = f2bf(dec * qk[nt][e]);
+      }
   }
   for (int i = threadIdx.x; i < kC * 128; i += blockDim.x) {
     const int s = i >> 7, d = i & 127;
+    const float kv = bf2f(*reinterpret_cast<const bf16_t*>(Kb + s * kPitchK + 2 * d));
+    const float qv = bf2f(*reinterpret_cast<const bf16_t*>(Qb + s * kPitchK + 2 * d));
     const float e = expf(L[s]);
-    Kg[i] = f2bf(e * Ks[s * 129 + d]);
-    Qg[i] = f2bf(e * Qs[s * 129 + d]);
-    Kd[i] = f2bf(expf(L[kC - 1] - L[s]) * Ks[s * 129 + d]);
+    Kg[i] = f2bf(e * kv);
+    Qg[i] = f2bf(e * qv);
+    Kd[i] = f2bf(expf(L[kC - 1] - L[s]) * kv);
   }
   if (threadIdx.x == 0) p.gc[(size_t)hv * p.nchunks + c] = expf(L[kC - 1]);
   __syncthreads();
-  // T = (I + B A)^{-1} B by forward substitution, one thread per column
-  if (threadIdx.x < kC) {
-    const int col = threadIdx.x;
+  // T = (I + B A)^{-1} B by forward substitution.  Column `col` of T depends on column `col` only:
+  // four adjacent lanes share a column and split the sum over the earlier rows between them.
+  {
+    const int col = threadIdx.x >> 2, sub = threadIdx.x & 3;
     for (int s = 0; s < kC; ++s) {
-      float acc = s == col ? bt[s] : 0.f;
-      for (int r = col; r < s; ++r) acc = fmaf(-BA[s * 65 + r], Tm[r * 65 + col], acc);  // T[r][col] = 0 for r < col
-      Tm[s * 65 + col] = s >= col ? acc : 0.f;
+      float acc = 0.f;
+      for (int r = col + sub; r < s; r += 4) acc = fmaf(-BA[s * 65 + r], Tm[r * 65 + col], acc);  // T[r][col] = 0 for r < col
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      if (sub == 0) Tm[s * 65 + col] = s >= col ? acc + (s == col ? bt[s] : 0.f) : 0.f;
+      __syncwarp();
     }
   }
   __syncthreads();
@@ -319,7 +346,7 @@ int k_gated_delta_chunked(orn_ctx* ctx, cudaStream_t s, const bf16_t* q, const b
   pp.q = q; pp.k = k; pp.g = g; pp.beta = beta; pp.T = T; pp.Hk = Hk; pp.Hv = Hv; pp.nchunks = nchunks;
   pp.scratch = reinterpret_cast<bf16_t*>(scratch);
   pp.gc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + (((size_t)Hv * nchunks * kChunkElems * sizeof(bf16_t) + 255) & ~(size_t)255));
-  const size_t psmem = sizeof(float) * (2 * kC * 129 + 2 * kC * 65 + 2 * kC);
+  const size_t psmem = kPrepSmem;
   int rc = orn_grant_smem(ctx, reinterpret_cast<const void*>(gdn_chunk_prep_kernel), psmem);
   if (rc != ORN_OK) return rc;
   gdn_chunk_prep_kernel<<<dim3(nchunks, Hv), 256, psmem, s>>>(pp);
