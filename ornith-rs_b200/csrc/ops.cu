@@ -175,6 +175,43 @@ __global__ void moe_combine_kernel(const bf16_t* __restrict__ scores, const bf16
   out[(int64_t)t * dim + c] = f2bf(acc + gated);
 }
 
+// the same arithmetic per element, eight columns per thread (16-byte loads) for many rows
+__global__ void __launch_bounds__(128) moe_combine_wide_kernel(const bf16_t* __restrict__ scores, const bf16_t* __restrict__ y,
+                                                                const bf16_t* __restrict__ gate, const bf16_t* __restrict__ shared,
+                                                                int k, int dim, int normalize, bf16_t* __restrict__ out) {
+  const int t = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= dim) return;
+  const bf16_t* s = scores + (int64_t)t * k;
+  float denom = 0.f;
+  if (normalize)
+    for (int j = 0; j < k; ++j) denom = bfr(bf2f(s[j]) + denom);
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int j = 0; j < k; ++j) {
+    const float w = normalize ? bfr(bf2f(s[j]) / denom) : bf2f(s[j]);
+    const uint4 v = ldg128(y + ((int64_t)t * k + j) * dim + c);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      acc[2 * e] = bfr(bfr(__uint_as_float(u[e] << 16) * w) + acc[2 * e]);
+      acc[2 * e + 1] = bfr(bfr(__uint_as_float(u[e] & 0xffff0000u) * w) + acc[2 * e + 1]);
+    }
+  }
+  const float g = orn_sigmoid_bf(bf2f(gate[t]));
+  const uint4 sh = ldg128(shared + (int64_t)t * dim + c);
+  const uint32_t su[4] = {sh.x, sh.y, sh.z, sh.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float lo = acc[2 * e] + bfr(g * __uint_as_float(su[e] << 16));
+    const float hi = acc[2 * e + 1] + bfr(g * __uint_as_float(su[e] & 0xffff0000u));
+    o[e] = (uint32_t)f2bf(lo) | ((uint32_t)f2bf(hi) << 16);
+  }
+  *reinterpret_cast<uint4*>(out + (int64_t)t * dim + c) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // q_proj output [T, Hq, 2*hd] -> queries [T,Hq,hd], gate [T,Hq,hd]
 // (qwen3_5.rs:441-443 slice_inner x2)
 __global__ void split_qgate_kernel(const bf16_t* qg, int n /*T*Hq*/, int hd, bf16_t* q, bf16_t* gate) {
@@ -243,6 +280,12 @@ int k_router_topk(orn_ctx* ctx, cudaStream_t s, const bf16_t* gates, int rows, i
 int k_moe_combine(orn_ctx* ctx, cudaStream_t s, const bf16_t* scores, const bf16_t* y,
                   const bf16_t* gate, const bf16_t* shared, int T, int k, int dim, int normalize,
                   bf16_t* out) {
+  const bool aligned = dim % 8 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(shared) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (T >= 16 && aligned) {
+    dim3 wgrid((dim / 8 + 127) / 128, T);
+    moe_combine_wide_kernel<<<wgrid, 128, 0, s>>>(scores, y, gate, shared, k, dim, normalize, out);
+    return orn_launch_check(ctx, "moe_combine");
+  }
   dim3 grid((dim + 255) / 256, T);
   moe_combine_kernel<<<grid, 256, 0, s>>>(scores, y, gate, shared, k, dim, normalize, out);
   return orn_launch_check(ctx, "moe_combine");

@@ -177,7 +177,7 @@ def test_elementwise_every_bf16_input(pkg, ctx):
     assert np.array_equal(hp.bf16_to_f32(o.numpy())[fin][::97], host)
 
 
-@pytest.mark.parametrize("T", [1, 2, 7])
+@pytest.mark.parametrize("T", [1, 2, 7, 40])   # 40: the combine's eight-columns-per-thread form (16 rows and more)
 def test_router_softmax_topk_combine(pkg, ctx, T):
     rng = np.random.default_rng(T)
     n, k, dim = 256, 8, 2048
