@@ -112,6 +112,8 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
   if (ctx->t1) cudaEventDestroy(ctx->t1);
   cudaFree(ctx->dev_err);
   cudaFree(ctx->split_partial);
+  cudaFree(ctx->attn_partial);
+  cudaFree(ctx->attn_arrivals);
   cudaFree(ctx->split_arrivals);
   cudaStreamDestroy(ctx->stream);
   delete ctx;

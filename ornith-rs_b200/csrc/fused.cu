@@ -2128,9 +2128,130 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
   return orn_launch_check(ctx, "k_gdn");
 }
 
+// The same attention with the 32 key groups of a (head, row) spread over kAttnSplit CTAs of 8 warps:
+// at long contexts one CTA of 32 warps is bound by its own issue slots (every group walks L / 32 keys)
+// while most SMs idle.  A group's arithmetic is unchanged (group = key index mod 32, keys in ascending
+// order), the partials (max, sum, out[256]) of all 32 groups go through global memory, and the CTA that
+// stores the last of them runs the same merge: the result has the bits of the one-CTA kernel.
+constexpr int kAttnSplit = 4;
+constexpr int kAttnMaxHeads = 128;
+constexpr int kAttnPart = 260;  // floats per group partial: out[256], max, sum, pad
+__global__ void __launch_bounds__(256) k_attn_split(AttnParams p, float* part, int* arrivals) {
+  constexpr int HD = 256;
+  __shared__ float s_o[32][HD];
+  __shared__ float s_q[HD];
+  __shared__ float s_knew[kGdnMaxT][HD];
+  __shared__ float s_max[32], s_sum[32], s_f[32];
+  __shared__ int s_last;
+  pdl_trigger();
+  pdl_wait();
+  const int h = blockIdx.x, r = blockIdx.y, z = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grp = 8 * z + warp;  // this warp's key group
+  const int group = p.Hq / p.Hkv;
+  const int kvh = h / group;
+  const int pos = *p.pos;
+  if (warp == 0)
+    warp_norm_rope(p.qg + ((size_t)r * p.Hq + h) * 2 * HD, p.q_norm, p.eps, p.rope_dims, p.lnb, pos + r, s_q, nullptr, lane);
+  else if (warp <= p.T)
+    warp_norm_rope(p.k + ((size_t)(warp - 1) * p.Hkv + kvh) * HD, p.k_norm, p.eps, p.rope_dims, p.lnb, pos + warp - 1,
+                   s_knew[warp - 1], nullptr, lane);
+  __syncthreads();
+  if (r == 0 && (h % group) == 0 && z == 0) {
+    for (int i = threadIdx.x; i < p.T * HD; i += blockDim.x) {
+      const int t = i / HD, d = i - t * HD;
+      if (pos + t < p.cap) {
+        p.kc[((size_t)kvh * p.cap + pos + t) * HD + d] = f2bf(s_knew[t][d]);
+        p.vc[((size_t)kvh * p.cap + pos + t) * HD + d] = p.v[((size_t)t * p.Hkv + kvh) * HD + d];
+      }
+    }
+  }
+  int L = pos + r + 1;
+  if (L > p.cap) L = p.cap;
+  float qs[8], o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { qs[i] = s_q[8 * lane + i] * p.scale; o[i] = 0.f; }
+  float mx = -INFINITY, sm = 0.f;
+  uint4 kr = make_uint4(0u, 0u, 0u, 0u), vr = kr;
+  auto fetch = [&](int n, uint4& kq, uint4& vq) {
+    if (n >= pos) {
+      vq = ldg128(p.v + ((size_t)(n - pos) * p.Hkv + kvh) * HD + 8 * lane);
+    } else {
+      const size_t rowoff = ((size_t)kvh * p.cap + n) * HD + 8 * lane;
+      kq = *reinterpret_cast<const uint4*>(p.kc + rowoff);
+      vq = *reinterpret_cast<const uint4*>(p.vc + rowoff);
+    }
+  };
+  if (grp < L) fetch(grp, kr, vr);
+  for (int n = grp; n < L; n += 32) {
+    uint4 kn = kr, vn = vr;
+    if (n + 32 < L) fetch(n + 32, kn, vn);
+    float kf[8], vf[8];
+    if (n >= pos) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) kf[i] = s_knew[n - pos][8 * lane + i];
+    } else {
+      widen8(kr, kf);
+    }
+    widen8(vr, vf);
+    kr = kn; vr = vn;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = fmaf(qs[i], kf[i], acc);
+    const float score = warp_sum(acc);
+    const float nm = fmaxf(mx, score);
+    const float factor = expf_call(mx - nm);
+    const float e = expf_call(score - nm);
+    mx = nm;
+    sm = fmaf(sm, factor, e);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = fmaf(o[i], factor, e * vf[i]);
+  }
+  // this group's partial to global memory
+  float* mine = part + (((size_t)h * kGdnMaxT + r) * 32 + grp) * kAttnPart;
+  *reinterpret_cast<float4*>(mine + 8 * lane) = make_float4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<float4*>(mine + 8 * lane + 4) = make_float4(o[4], o[5], o[6], o[7]);
+  if (lane == 0) { mine[HD] = mx; mine[HD + 1] = sm; }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&arrivals[h * kGdnMaxT + r], 1) == kAttnSplit - 1 ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* all = part + ((size_t)h * kGdnMaxT + r) * 32 * kAttnPart;
+  for (int i = threadIdx.x; i < 32 * HD; i += blockDim.x) s_o[i / HD][i % HD] = __ldcg(all + (size_t)(i / HD) * kAttnPart + (i % HD));
+  if (threadIdx.x < 32) {
+    s_max[threadIdx.x] = __ldcg(all + (size_t)threadIdx.x * kAttnPart + HD);
+    s_sum[threadIdx.x] = __ldcg(all + (size_t)threadIdx.x * kAttnPart + HD + 1);
+  }
+  if (threadIdx.x == 0) arrivals[h * kGdnMaxT + r] = 0;  // ready for the next launch
+  __syncthreads();
+  if (warp == 0) {
+    const float M = warp_max(s_max[lane]);
+    const float f = expf_call(s_max[lane] - M);
+    s_f[lane] = f;
+    const float S = warp_sum(s_sum[lane] * f);
+    if (lane == 0) s_sum[0] = S;
+  }
+  __syncthreads();
+  {
+    const int d = threadIdx.x;
+    float a[32];
+#pragma unroll
+    for (int g = 0; g < 32; ++g) a[g] = s_o[g][d] * s_f[g];
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+      for (int i = 0; i < off; ++i) a[i] = a[i] + a[i + off];
+    const float att = bfr(a[0] / s_sum[0]);
+    const float gate = bf2f(p.qg[((size_t)r * p.Hq + h) * 2 * HD + HD + d]);
+    p.out[((size_t)r * p.Hq + h) * HD + d] = f2bf(sigmoid_bf_call(gate) * att);
+  }
+}
+
 int f_attn(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, const bf16_t* k, const bf16_t* v, const bf16_t* q_norm,
            const bf16_t* k_norm, bf16_t* kc, bf16_t* vc, const int* pos, int T, int Hq, int Hkv, int hd, int cap,
-           int rope_dims, float lnb, float eps, bf16_t* out) {
+           int rope_dims, float lnb, float eps, bf16_t* out, int long_context) {
   if (hd != 256) ORN_FAIL(ctx, ORN_ERR_ARG, "fused attention: head_dim must be 256");
   if (T > kGdnMaxT) ORN_FAIL(ctx, ORN_ERR_ARG, "fused attention: at most 4 rows");
   AttnParams p;
@@ -2138,6 +2259,17 @@ int f_attn(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, const bf16_t* k, cons
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.cap = cap; p.rope_dims = rope_dims; p.lnb = lnb;
   p.scale = 1.0f / sqrtf((float)hd);
   p.eps = eps;
+  if (long_context) {
+    if (ctx->attn_partial == nullptr) {  // first use: never inside a capture (a shape runs eagerly once before it is captured)
+      ORN_CHECK_CUDA(ctx, cudaMalloc((void**)&ctx->attn_partial, sizeof(float) * (size_t)kAttnMaxHeads * kGdnMaxT * 32 * kAttnPart));
+      ORN_CHECK_CUDA(ctx, cudaMalloc((void**)&ctx->attn_arrivals, sizeof(int) * kAttnMaxHeads * kGdnMaxT));
+      ORN_CHECK_CUDA(ctx, cudaMemset(ctx->attn_arrivals, 0, sizeof(int) * kAttnMaxHeads * kGdnMaxT));
+    }
+    if (Hq > kAttnMaxHeads) ORN_FAIL(ctx, ORN_ERR_ARG, "fused attention: more than 128 query heads");
+    dim3 sgrid(Hq, T, kAttnSplit);
+    ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 4, k_attn_split, sgrid, dim3(256), 0, p, ctx->attn_partial, ctx->attn_arrivals));
+    return orn_launch_check(ctx, "k_attn_split");
+  }
   dim3 grid(Hq, T);
   ORN_CHECK_CUDA(ctx, orn_launch_dependent(ctx, s, 4, k_attn, grid, dim3(1024), 0, p));
   return orn_launch_check(ctx, "k_attn");

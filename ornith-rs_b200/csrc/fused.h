@@ -40,7 +40,8 @@ int f_gdn(orn_ctx* ctx, cudaStream_t s, const bf16_t* conv, const bf16_t* cw, co
           bf16_t* gated_out /* nullable: rms_norm_gated(y, z) per head, by the last CTA of the head */);
 int f_attn(orn_ctx* ctx, cudaStream_t s, const bf16_t* qg, const bf16_t* k, const bf16_t* v, const bf16_t* q_norm,
            const bf16_t* k_norm, bf16_t* kc, bf16_t* vc, const int* pos, int T, int Hq, int Hkv, int hd, int cap,
-           int rope_dims, float lnb, float eps, bf16_t* out);
+           int rope_dims, float lnb, float eps, bf16_t* out,
+           int long_context = 0 /* the key groups of a (head, row) over four CTAs: same bits, for long caches */);
 // one warp waits, with a limit of `rounds` tries, for a copy that was never requested: sets the
 // context's device error flag; *dev_waited receives 0
 int f_wait_probe(orn_ctx* ctx, cudaStream_t s, uint32_t rounds, int* dev_waited);

@@ -384,6 +384,16 @@ int moe_fused(orn_model* m, const Moe& moe, const bf16_t* a, const bf16_t* b, co
 // The 40 layers.  On return the residual stream is bf(w.h + w.mo), not yet
 // added: the add belongs to whatever norm comes next (the final norm here, the
 // next layer's input norm inside the loop), as in add_rms_norm (norm.rs).
+// the reference switches its attention to a two-pass form from 1024 keys (src/ops/sdpa.rs:166-170); here the
+// fused kernel spreads a head's key groups over four CTAs from there (same bits)
+// (ORN_LONG_CONTEXT_KEYS moves the threshold, for measurements: 0 = never)
+constexpr int kLongContext = 1024;
+int long_context(int keys) {
+  static int thr = -1;
+  if (thr < 0) { const char* e = getenv("ORN_LONG_CONTEXT_KEYS"); thr = e ? atoi(e) : kLongContext; if (thr <= 0) thr = 1 << 30; }
+  return keys > thr ? 1 : 0;
+}
+
 int trunk_layers(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int T, bool capture) {
   orn_ctx* ctx = m->ctx;
   cudaStream_t s = ctx->stream;
@@ -440,7 +450,7 @@ int trunk_layers(orn_model* m, orn_cache* cc, const uint32_t* dev_ids, int T, bo
       jobs[2].lin = ly.v_proj; jobs[2].out = w.av;
       CK(f_norm_gemv(ctx, s, T, fp, jobs, 3));
       CK(f_attn(ctx, s, w.qg, w.ak, w.av, ly.q_norm, ly.k_norm, cc->kc[i], cc->vc[i], cc->pos, T, c.n_heads,
-                c.n_kv_heads, c.head_dim, c.max_ctx, c.rope_dims, m->lnb, c.rms_eps, w.agated));
+                c.n_kv_heads, c.head_dim, c.max_ctx, c.rope_dims, m->lnb, c.rms_eps, w.agated, long_context(cc->h_pos + T)));
       FusedPrologue gp;
       gp.mode = PRO_PLAIN; gp.K = QD; gp.a = w.agated;
       FusedJob oj;
@@ -551,7 +561,7 @@ int mtp_step(orn_model* m, orn_cache* cc, const bf16_t* trunk_hidden, const uint
     jobs[2].lin = h.v_proj; jobs[2].out = w.av;
     CK(f_norm_gemv(ctx, s, T, fp, jobs, 3));
     CK(f_attn(ctx, s, w.qg, w.ak, w.av, h.q_norm, h.k_norm, cc->mtp_kc, cc->mtp_vc, cc->mtp_pos, T, c.n_heads,
-              c.n_kv_heads, c.head_dim, c.max_ctx, c.rope_dims, m->lnb, c.rms_eps, w.agated));
+              c.n_kv_heads, c.head_dim, c.max_ctx, c.rope_dims, m->lnb, c.rms_eps, w.agated, long_context(cc->h_mtp_pos + T)));
     if (!kv_only) {
       FusedPrologue gp;
       gp.mode = PRO_PLAIN; gp.K = QD; gp.a = w.agated;
@@ -632,9 +642,12 @@ int ar_body(orn_model* m, orn_cache* c) {
 int run_step(orn_model* m, orn_cache* c, int kind /*0 cycle, 1 ar, 2 prefill rows*/, int want, bool use_frspec) {
   orn_ctx* ctx = m->ctx;
   cudaStream_t s = ctx->stream;
-  const int key = kind * 64 + want * 2 + (use_frspec ? 1 : 0);
-  orn_cache::StepGraph& g = c->graphs[key];
   const int n_rows = want + 1;
+  // the launch shape of the fused attention changes once a cache passes kLongContext keys (the key
+  // groups of a head spread over four CTAs): such steps are graphs of their own
+  const int key = kind * 64 + want * 2 + (use_frspec ? 1 : 0) + 4096 * long_context(c->h_pos + n_rows) +
+                  8192 * (kind == 0 ? long_context(c->h_mtp_pos + want) : 0);
+  orn_cache::StepGraph& g = c->graphs[key];
   if (c->h_pos + n_rows > m->cfg.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "forward: context exceeds max_ctx");
   if (kind == 0 && c->h_mtp_pos + want > m->cfg.max_ctx) ORN_FAIL(ctx, ORN_ERR_STATE, "mtp: context exceeds max_ctx");
   static int no_graph = -1;

@@ -32,6 +32,9 @@ struct orn_ctx {
   // split-K scratch of the tensor-core product (gemm.cu): partial sums and per-tile arrival counters,
   // allocated once at the first product that splits (never inside a stream capture: callers run a
   // shape eagerly before they capture it)
+  // group partials and arrival counters of the fused attention's long-context form (fused.cu)
+  float* attn_partial = nullptr;
+  int* attn_arrivals = nullptr;
   float* split_partial = nullptr;
   int* split_arrivals = nullptr;
 };
