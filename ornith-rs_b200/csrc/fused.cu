@@ -33,6 +33,14 @@ namespace {
 // Out-of-line copies of the elementary functions: these kernels run each piece of code once or
 // twice per launch, so instruction-cache misses cost more than calls do.
 __device__ __noinline__ float expf_call(float x) { return orn_expf(x); }
+// n / d for small n (n * d < 2^32) as one multiply: the task loops of the expert kernels divide on
+// every tile, on the warp's critical path, and a hardware-less integer division is a hundred cycles
+struct SmallDiv {
+  uint32_t mg;
+  int d;
+  ORN_D explicit SmallDiv(int dd) : mg(dd > 1 ? 0xFFFFFFFFu / (uint32_t)dd + 1u : 0u), d(dd) {}
+  ORN_D int operator()(int n) const { return d > 1 ? (int)__umulhi((uint32_t)n, mg) : n; }
+};
 // four at once: the evaluations interleave in the pipelines instead of running one after another
 __device__ __noinline__ void expf4_call(float* v) {
   const float a = orn_expf(v[0]), b = orn_expf(v[1]), c = orn_expf(v[2]), d = orn_expf(v[3]);
@@ -1208,11 +1216,12 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32
   const int gw = warp * gridDim.x + blockIdx.x, GW = gridDim.x * (blockDim.x >> 5);  // few tiles still reach every SM
   const int ntile = (P.I + HALF - 1) / HALF;
   const int total = M * P.k * ntile;
+  const SmallDiv by_ntile(ntile), by_k(P.k);
   const RecGeom geo = rec_geom(KIND, P.H);
   int pg = gw, pslot = 0;
   auto issue = [&]() {
     if (lane == 0) {
-      const int mj = pg / ntile, t = pg - mj * ntile;
+      const int mj = by_ntile(pg), t = pg - mj * ntile;
       const int o = t * HALF;
       const int n = min(HALF, P.I - o);
       const size_t row = (size_t)inds[mj] * P.I + o;
@@ -1231,8 +1240,8 @@ __global__ void __launch_bounds__(kMoeThreads, 1) k_moe_up(MoeUpParams P, uint32
   int slot = 0;
   uint32_t parity = 0;
   for (int cg = gw; cg < total; cg += GW) {
-    const int mj = cg / ntile, t = cg - mj * ntile;
-    const int m = mj / P.k;
+    const int mj = by_ntile(cg), t = cg - mj * ntile;
+    const int m = by_k(mj);
 #pragma unroll
     for (int r = 0; r < RT; ++r) gu[r] = 0.f;
     if (!ring_wait(R, slot, parity)) return;
@@ -1325,12 +1334,13 @@ __global__ void __launch_bounds__(kDownThreads, 1) k_moe_down(MoeDownParams P, u
   const int gp = pair * gridDim.x + blockIdx.x, GP = gridDim.x * npairs;  // few tasks still reach every SM
   const int ngroups = (P.H + RT - 1) / RT;
   const int total = M * ngroups;
+  const SmallDiv by_ngroups(ngroups);
   const int k0 = P.k >> 1;
   const int nt = h ? P.k - k0 + 1 : k0;  // the odd warp's last tile is the shared expert's
   const RecGeom geo = rec_geom(KIND, P.I), sgeo = rec_geom(KIND, P.SI);
   int pg = gp, pq = 0, pslot = 0;  // producer: task, tile within the task
   auto fill = [&](int task, int q, int slot) {  // one lane: request tile q of `task` into `slot`
-    const int m = task / ngroups, grp = task - m * ngroups;
+    const int m = by_ngroups(task), grp = task - m * ngroups;
     const int c0 = grp * RT;
     const int n = min(RT, P.H - c0);
     const int j = (h ? k0 : 0) + q;
@@ -1395,7 +1405,7 @@ __global__ void __launch_bounds__(kDownThreads, 1) k_moe_down(MoeDownParams P, u
   uint32_t parity = 0;
   bool ok = true;  // a wait that ran out: no more waits or stores, but the pair's barriers are kept
   for (int cg = gp; cg < total; cg += GP, ++round) {
-    const int m = cg / ngroups, grp = cg - m * ngroups;
+    const int m = by_ngroups(cg), grp = cg - m * ngroups;
     const int c0 = grp * RT;
     float acc = 0.f;                               // even warp: the running combine value
     float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;  // odd warp: its routed terms, newest in t3
@@ -1750,6 +1760,84 @@ ORN_D void warp_norm_rope(const bf16_t* src, const bf16_t* w, float eps, int rop
   __syncwarp();
 }
 
+// One key group's walk over the cache (keys grp, grp + 32, ... < L in ascending order): the online
+// softmax of kernels/sdpa.metal per key, unchanged.  Keys are taken KB at a time: their cache rows are
+// requested together, their dot products and butterflies run side by side, and only the (max, sum,
+// out) update of each key waits for the one before it, so a memory round trip and the shuffle latency
+// are paid once per KB keys.  The arithmetic of a key and the order of the keys are those of KB = 1.
+template <int KB>
+ORN_D void attn_walk(const AttnParams& p, const float (*s_knew)[256], const float* qs, int grp, int L, int pos, int kvh, int lane,
+                     float* o, float& mx, float& sm) {
+  constexpr int HD = 256;
+  uint4 kr[KB], vr[KB];
+  auto fetch_k = [&](int n, uint4& kq) {
+    if (n < pos) kq = *reinterpret_cast<const uint4*>(p.kc + ((size_t)kvh * p.cap + n) * HD + 8 * lane);
+  };
+  auto fetch_v = [&](int n, uint4& vq) {
+    if (n >= pos) vq = ldg128(p.v + ((size_t)(n - pos) * p.Hkv + kvh) * HD + 8 * lane);
+    else vq = *reinterpret_cast<const uint4*>(p.vc + ((size_t)kvh * p.cap + n) * HD + 8 * lane);
+  };
+  auto dot = [&](int n, const uint4& kq) {
+    float kf[8];
+    if (n >= pos) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) kf[i] = s_knew[n - pos][8 * lane + i];
+    } else {
+      widen8(kq, kf);
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = fmaf(qs[i], kf[i], acc);
+    return acc;
+  };
+  // one key folded in; expf inline: a call would make the warp wait for every cache row it has in flight
+  auto fold = [&](float score, const uint4& vq) {
+    float vf[8];
+    widen8(vq, vf);
+    const float nm = fmaxf(mx, score);
+    const float factor = orn_expf(mx - nm);
+    const float e = orn_expf(score - nm);
+    mx = nm;
+    sm = fmaf(sm, factor, e);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = fmaf(o[i], factor, e * vf[i]);
+  };
+#pragma unroll
+  for (int j = 0; j < KB; ++j) {
+    kr[j] = make_uint4(0u, 0u, 0u, 0u);
+    vr[j] = kr[j];
+    if (grp + 32 * j < L) { fetch_k(grp + 32 * j, kr[j]); fetch_v(grp + 32 * j, vr[j]); }
+  }
+  int n0 = grp;
+  // whole blocks: straight-line code, so the KB butterflies and the 2 KB exponentials overlap
+  for (; n0 + 32 * (KB - 1) < L; n0 += 32 * KB) {
+    float score[KB];
+    uint4 vcur[KB];
+#pragma unroll
+    for (int j = 0; j < KB; ++j) {
+      score[j] = dot(n0 + 32 * j, kr[j]);
+      vcur[j] = vr[j];
+    }
+#pragma unroll
+    for (int j = 0; j < KB; ++j) {  // the next block's rows while this block is folded in
+      const int n = n0 + 32 * (KB + j);
+      if (n < L) { fetch_k(n, kr[j]); fetch_v(n, vr[j]); }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+      for (int j = 0; j < KB; ++j) score[j] = score[j] + __shfl_xor_sync(0xffffffffu, score[j], off);
+#pragma unroll
+    for (int j = 0; j < KB; ++j) fold(score[j], vcur[j]);
+  }
+  // the keys of the last, partial block one by one (their rows are already here)
+#pragma unroll
+  for (int j = 0; j < KB - 1; ++j) {
+    const int n = n0 + 32 * j;
+    if (n < L) fold(warp_sum(dot(n, kr[j])), vr[j]);
+  }
+}
+
 __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
   constexpr int HD = 256;
   __shared__ float s_o[32][HD];
@@ -1785,43 +1873,7 @@ __global__ void __launch_bounds__(1024) k_attn(AttnParams p) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) { qs[i] = s_q[8 * lane + i] * p.scale; o[i] = 0.f; }
   float mx = -INFINITY, sm = 0.f;
-  // a warp's next cache row is requested before the current one is folded in: the loop body has
-  // out-of-line calls, so without this every iteration would pay a full memory round trip
-  uint4 kr = make_uint4(0u, 0u, 0u, 0u), vr = kr;
-  auto fetch = [&](int n, uint4& kq, uint4& vq) {
-    if (n >= pos) {
-      vq = ldg128(p.v + ((size_t)(n - pos) * p.Hkv + kvh) * HD + 8 * lane);
-    } else {
-      const size_t rowoff = ((size_t)kvh * p.cap + n) * HD + 8 * lane;
-      kq = *reinterpret_cast<const uint4*>(p.kc + rowoff);
-      vq = *reinterpret_cast<const uint4*>(p.vc + rowoff);
-    }
-  };
-  if (warp < L) fetch(warp, kr, vr);
-  for (int n = warp; n < L; n += 32) {
-    uint4 kn = kr, vn = vr;
-    if (n + 32 < L) fetch(n + 32, kn, vn);
-    float kf[8], vf[8];
-    if (n >= pos) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) kf[i] = s_knew[n - pos][8 * lane + i];
-    } else {
-      widen8(kr, kf);
-    }
-    widen8(vr, vf);
-    kr = kn; vr = vn;
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc = fmaf(qs[i], kf[i], acc);
-    const float score = warp_sum(acc);
-    const float nm = fmaxf(mx, score);
-    const float factor = expf_call(mx - nm);
-    const float e = expf_call(score - nm);
-    mx = nm;
-    sm = fmaf(sm, factor, e);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = fmaf(o[i], factor, e * vf[i]);
-  }
+  attn_walk<2>(p, s_knew, qs, warp, L, pos, kvh, lane, o, mx, sm);
   if (lane == 0) { s_max[warp] = mx; s_sum[warp] = sm; }
 #pragma unroll
   for (int i = 0; i < 8; ++i) s_o[warp][8 * lane + i] = o[i];
@@ -2172,41 +2224,7 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnParams p, float* part, i
 #pragma unroll
   for (int i = 0; i < 8; ++i) { qs[i] = s_q[8 * lane + i] * p.scale; o[i] = 0.f; }
   float mx = -INFINITY, sm = 0.f;
-  uint4 kr = make_uint4(0u, 0u, 0u, 0u), vr = kr;
-  auto fetch = [&](int n, uint4& kq, uint4& vq) {
-    if (n >= pos) {
-      vq = ldg128(p.v + ((size_t)(n - pos) * p.Hkv + kvh) * HD + 8 * lane);
-    } else {
-      const size_t rowoff = ((size_t)kvh * p.cap + n) * HD + 8 * lane;
-      kq = *reinterpret_cast<const uint4*>(p.kc + rowoff);
-      vq = *reinterpret_cast<const uint4*>(p.vc + rowoff);
-    }
-  };
-  if (grp < L) fetch(grp, kr, vr);
-  for (int n = grp; n < L; n += 32) {
-    uint4 kn = kr, vn = vr;
-    if (n + 32 < L) fetch(n + 32, kn, vn);
-    float kf[8], vf[8];
-    if (n >= pos) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) kf[i] = s_knew[n - pos][8 * lane + i];
-    } else {
-      widen8(kr, kf);
-    }
-    widen8(vr, vf);
-    kr = kn; vr = vn;
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc = fmaf(qs[i], kf[i], acc);
-    const float score = warp_sum(acc);
-    const float nm = fmaxf(mx, score);
-    const float factor = expf_call(mx - nm);
-    const float e = expf_call(score - nm);
-    mx = nm;
-    sm = fmaf(sm, factor, e);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = fmaf(o[i], factor, e * vf[i]);
-  }
+  attn_walk<8>(p, s_knew, qs, grp, L, pos, kvh, lane, o, mx, sm);
   // this group's partial to global memory
   float* mine = part + (((size_t)h * kGdnMaxT + r) * 32 + grp) * kAttnPart;
   *reinterpret_cast<float4*>(mine + 8 * lane) = make_float4(o[0], o[1], o[2], o[3]);

@@ -432,16 +432,17 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
   if (warp == 0) {
     // ---- TMA producer: the raw weight boxes and the token tiles of every K block
     if (lane == 0) {
-      uint32_t it = 0;
+      // ring positions are counted, not divided: an integer division is a hundred cycles of this one thread
+      int si = 0;
+      uint32_t si_ph = 0;
       Item w;
       bool ok = true;
       for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
         const int nt = (w.ntok + P.BN - 1) / P.BN;
         const int wrow = w.e * P.job[w.job].O + w.ft * BM;
         const WeightMaps& wm = maps.w[w.job];
-        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
-          const int si = it % SI;
-          ok = mbar_wait(bar_in_free + 8 * si, ((it / SI) & 1u) ^ 1u, P.err);
+        for (int kb = w.kb0; kb < w.kb1; ++kb, si = (si + 1 == SI ? 0 : si + 1), si_ph ^= (si == 0 ? 1u : 0u)) {
+          ok = mbar_wait(bar_in_free + 8 * si, si_ph ^ 1u, P.err);
           if (!ok) break;
           const uint32_t bar = bar_landed + 8 * si, base = in0 + si * P.stage_bytes;
           mbar_expect_tx(bar, (uint32_t)nt * x_tile_bytes + F::kTxBytes);
@@ -454,16 +455,17 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
     // ---- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(P.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      uint32_t it = 0, acc_ph = 0;
+      uint32_t acc_ph = 0, sw_ph = 0;
+      int si = 0, sw = 0;
       Item w;
       bool ok = true;
       for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
         const int nt = (w.ntok + P.BN - 1) / P.BN;
         ok = mbar_wait(bar_acc_empty, acc_ph ^ 1u, P.err);  // the previous item's accumulators were read
         tc_fence_after();
-        for (int kb = w.kb0; kb < w.kb1 && ok; ++kb, ++it) {
-          const int si = it % SI, sw = it % SW;
-          ok = mbar_wait(bar_full + 8 * sw, (it / SW) & 1u, P.err);  // implies landed[si]: the dequantisers waited for it
+        for (int kb = w.kb0; kb < w.kb1 && ok;
+             ++kb, si = (si + 1 == SI ? 0 : si + 1), sw = (sw + 1 == SW ? 0 : sw + 1), sw_ph ^= (sw == 0 ? 1u : 0u)) {
+          ok = mbar_wait(bar_full + 8 * sw, sw_ph, P.err);  // implies landed[si]: the dequantisers waited for it
           if (!ok) break;
           tc_fence_after();
           const uint32_t inb = in0 + si * P.stage_bytes;
@@ -488,13 +490,14 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
     const int half = dq >> 7;          // DQW == 8: which 32 of the K block's 64 weights (DQW == 4: both)
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
     const int colhalf = (warp - 2) >> 2;  // DQW == 8: the two warps of a quadrant split the 16-column groups
-    uint32_t it = 0, acc_ph = 0;
+    uint32_t acc_ph = 0, si_ph = 0, sw_ph = 0;
+    int si = 0, sw = 0;
     Item w;
     bool ok = true;
     for (int wi = blockIdx.x; ok && get_item(P, wi, n_items, w); wi += gridDim.x) {
-      for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
-        const int si = it % SI, sw = it % SW;
-        ok = mbar_wait(bar_w_free + 8 * sw, ((it / SW) & 1u) ^ 1u, P.err) && mbar_wait(bar_landed + 8 * si, (it / SI) & 1u, P.err);
+      for (int kb = w.kb0; kb < w.kb1; ++kb, si = (si + 1 == SI ? 0 : si + 1), si_ph ^= (si == 0 ? 1u : 0u),
+               sw = (sw + 1 == SW ? 0 : sw + 1), sw_ph ^= (sw == 0 ? 1u : 0u)) {
+        ok = mbar_wait(bar_w_free + 8 * sw, sw_ph ^ 1u, P.err) && mbar_wait(bar_landed + 8 * si, si_ph, P.err);
         if (!ok) break;
         if (!kDirect) {
           if (DQW == 8) {

@@ -385,9 +385,10 @@ int moe_fused(orn_model* m, const Moe& moe, const bf16_t* a, const bf16_t* b, co
 // added: the add belongs to whatever norm comes next (the final norm here, the
 // next layer's input norm inside the loop), as in add_rms_norm (norm.rs).
 // the reference switches its attention to a two-pass form from 1024 keys (src/ops/sdpa.rs:166-170); here the
-// fused kernel spreads a head's key groups over four CTAs from there (same bits)
+// fused kernel spreads a head's key groups over four CTAs (same bits) from 512 keys, where that form
+// starts to win on this part (23.9 -> 22.4 us per launch at 600 keys, 155 -> 74 us at 6600)
 // (ORN_LONG_CONTEXT_KEYS moves the threshold, for measurements: 0 = never)
-constexpr int kLongContext = 1024;
+constexpr int kLongContext = 512;
 int long_context(int keys) {
   static int thr = -1;
   if (thr < 0) { const char* e = getenv("ORN_LONG_CONTEXT_KEYS"); thr = e ? atoi(e) : kLongContext; if (thr <= 0) thr = 1 << 30; }

@@ -246,18 +246,18 @@ def test_full_size_layers_mtp_equals_autoregressive(pkg, ctx):
     m.free()
 
 
-def test_decode_past_1024_cached_keys_equals_the_oracle(pkg, ctx):
-    """From 1024 cached keys on the fused attention spreads the key groups of a head over four CTAs and
-    merges their partials in the last one: same arithmetic, same bits.  A 1015-token prompt through
+def test_decode_past_the_split_attention_threshold_equals_the_oracle(pkg, ctx):
+    """From 512 cached keys on the fused attention spreads the key groups of a head over four CTAs and
+    merges their partials in the last one: same arithmetic, same bits.  A 503-token prompt through
     the row-invariant windows, then 24 generated tokens (autoregressive and MTP depth 1 and 2, so
     that windows of 1, 2 and 3 rows cross the threshold): ids, acceptance counts and hidden rows against
     the oracle.  The MTP head's own cache stays short here; its long form is the same kernel."""
-    cfg = hp.tiny_config(pkg.Config, max_ctx=1100)
+    cfg = hp.tiny_config(pkg.Config, max_ctx=700)
     W = hp.tiny_model_weights(cfg, seed=15)
     om = orc.Model(cfg, W)
     gm = hp.upload_model(pkg, ctx, cfg, W)
     rng = np.random.default_rng(77)
-    prompt = rng.integers(0, cfg.vocab, 1015).astype(np.uint32)
+    prompt = rng.integers(0, cfg.vocab, 503).astype(np.uint32)
     ar = om.generate(prompt, 24)
     c = gm.make_cache()
     assert pkg.generate_step(gm, c, prompt, 24, prefill_step=8) == ar
@@ -271,13 +271,14 @@ def test_decode_past_1024_cached_keys_equals_the_oracle(pkg, ctx):
     oc = om.new_cache()
     c.reset()
     seq = np.concatenate([prompt, np.array(ar, np.uint32)])
-    for a in range(0, 1020, 4):
+    for a in range(0, 508, 4):
         ids = seq[a:a + 4]
         want = om.forward(oc, ids)
         got = gm.forward(c, ids).numpy()
-        if a >= 1000:
+        if a >= 488:
             assert np.array_equal(got, want), a
-    for T in (3, 2, 1, 4, 2):   # 1020 .. 1032: short form, the crossing window, long form
+    for T in (3, 2, 1, 4, 2, 4, 4, 4, 4, 4, 4, 4, 4, 3):   # 508 .. 555: short form, the crossing window, long form
+                                                           # with whole blocks of keys and every tail length
         ids = rng.integers(0, cfg.vocab, T).astype(np.uint32)
         assert np.array_equal(gm.forward(c, ids).numpy(), om.forward(oc, ids)), (T, c.offset)
     om.free_cache(oc)
