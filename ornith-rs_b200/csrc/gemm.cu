@@ -16,12 +16,14 @@
 //   - a CTA owns (feature tile of 128, up to NT token tiles) and keeps NT accumulators of
 //     128 x BN float32 in tensor memory (NT * BN <= 512 columns);
 //   - per block of 64 weights along K: one warp's elected lane brings the NT token tiles
-//     [BN, 64] bf16 with TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, this GPU's memory, no
-//     multicast); eight warps dequantise the 128 x 64 weight tile from the row records in HBM
-//     straight into shared memory in the same swizzled K-major layout (one thread per feature
-//     row: Q4_K / Q6_K / affine-8 / bf16 -> bf16); another elected lane issues 4 * NT
-//     tcgen05.mma (128 x BN x 16, kind::f16, bf16 inputs, f32 accumulate) and commits the stage
-//     back to the producers;
+//     [BN, 64] bf16 and the raw bytes of the 128 x 64 weight tile with TMA (cp.async.bulk.tensor.2d,
+//     this GPU's memory, no multicast); eight (or four) warps dequantise the tile (one thread per
+//     feature row: Q4_K / Q6_K / affine-8 / affine-4 -> bf16) and store it with tcgen05.st into TENSOR
+//     MEMORY, where the MMA takes its A operand from (row = lane, two bf16 per column): a 16 KB tile
+//     per K block neither crosses shared memory twice nor needs a proxy fence (bf16 weights land in
+//     shared memory swizzled and are read from there); another elected lane issues 4 * NT tcgen05.mma
+//     (128 x BN x 16, kind::f16, bf16 inputs, f32 accumulate) and commits the stage back to the
+//     producers;
 //   - the eight dequantising warps then read the accumulators (tcgen05.ld, one TMEM lane = one
 //     feature per thread), round to bfloat16 and store y[token, feature].
 // Stages are a ring guarded by mbarriers; every wait is bounded and reports through the context's
@@ -52,7 +54,8 @@ constexpr int BK = 64;             // weights per K block: one 128-byte swizzle 
 // feature row of a tile) for launches with one or two CTAs per SM, 4 (one thread per row) for
 // launches of narrow items, where up to four small CTAs share an SM
 constexpr int gemm_threads(int dqw) { return 64 + 32 * dqw; }
-constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccColsMax = 384;   // accumulator columns of an item: the rest of tensor memory holds weight tiles
+constexpr uint32_t kWCols = BK / 2;     // tensor-memory columns of one dequantised 128 x 64 tile (two bf16 per column)
 constexpr int kSplitMaxRows = 512;                      // dense products up to this many rows may split K
 constexpr size_t kSplitPartialBytes = (size_t)64 << 20;  // f32 partials of one launch
 constexpr size_t kSplitTiles = 4096;                     // arrival counters
@@ -80,7 +83,8 @@ struct GemmParams {
   const uint32_t* row_map;   // nullable: output row of sorted row p
   int BN, NT, stages /*IN ring*/, w_stages /*W ring*/, f_tiles;
   uint32_t stage_bytes;
-  uint32_t tmem_cols;  // power of two >= NT * BN (and >= 32): what the CTA takes of tensor memory
+  uint32_t tmem_cols;  // power of two >= acc_cols + the W ring's columns (and >= 32): what the CTA takes of tensor memory
+  uint32_t acc_cols;   // NT * BN rounded up to 32: the accumulators; the dequantised weight tiles follow
   int splits;          // dense products over few rows: an item is one of `splits` ranges of the K blocks of a tile
   float* partial;      // [tile][split][token][128 features] f32 partial sums of the split items
   int* arrivals;       // [tile] how many splits of the tile have stored their partial (the last one reduces)
@@ -153,6 +157,26 @@ ORN_D void tmem_ld16(uint32_t taddr, uint32_t* v) {
       : "r"(taddr));
 }
 ORN_D void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 16 registers of every lane to 16 columns of the warp's 32 tensor-memory lanes (lane i of the warp = row i)
+ORN_D void tmem_st16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+      "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+ORN_D void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]^T: A is 128 lanes x 8 columns (16 bf16 of K per row)
+ORN_D void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 ORN_D uint4 lds128(uint32_t addr) {
   uint4 v;
@@ -169,23 +193,51 @@ ORN_D uint32_t lds16(uint32_t addr) {
   asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
-ORN_D void st_chunk(uint32_t row_addr, int rsw, int c, uint32_t a, uint32_t b, uint32_t cc, uint32_t d) {
-  // 16-byte chunk c of a 128-byte row, at its swizzled place (chunk index xor row mod 8)
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)((c ^ rsw) << 4)), "r"(a), "r"(b),
-               "r"(cc), "r"(d)
-               : "memory");
+// Four code bytes of a word -> two words of two bfloat16 each, w = a * q + b per byte q, in two
+// packed fused multiply-adds on the code word itself: a code byte dropped into a float's bit
+// pattern IS a float that is linear in the code.
+//   * codes below 128 go into the third byte of 0x3F000000, already shifted left by s bits so that
+//     they fill the byte's top (s = 3 for 4-bit codes, 1 for 6-bit ones): the float is
+//     0.5 + (q << s) / 256, hence w = (a 2^(8-s)) * F + (b - a 2^(7-s)); both constants are exact
+//     up to one float32 rounding of b - a 2^(7-s), which is of the size of w itself;
+//   * 8-bit codes go into the second byte of 0x47000000: the float is 32768 + q and
+//     w = a * F + (b - 32768 a), whose constant carries an error of a / 512 at most (far below the
+//     bfloat16 rounding of an affine weight, which is of the size of 64 a).
+// This path agrees with the mat-vec to rounding, not bit for bit.
+template <int I>  // top-aligned code bytes I and I + 1 of w as a packed pair of floats
+ORN_D uint64_t code_pair_hi(uint32_t w) {
+  // selector nibbles, result byte 3..0: magic byte 3 (0x3F), code byte, magic bytes 1 and 0 (0)
+  return pk2(__uint_as_float(__byte_perm(w, 0x3F000000u, 0x7054 + 256 * I)),
+             __uint_as_float(__byte_perm(w, 0x3F000000u, 0x7054 + 256 * (I + 1))));
 }
-// two floats -> packed bfloat16x2, round to nearest even (lo in the low half)
-ORN_D uint32_t pack_bf2(float lo, float hi) {
+template <int I>  // 8-bit code bytes I and I + 1 of w as the packed pair (32768 + q_I, 32768 + q_I+1)
+ORN_D uint64_t code_pair_8(uint32_t w) {
+  return pk2(__uint_as_float(__byte_perm(w, 0x47000000u, 0x7604 + 16 * I)),
+             __uint_as_float(__byte_perm(w, 0x47000000u, 0x7604 + 16 * (I + 1))));
+}
+ORN_D uint32_t bf2_of(uint64_t p) {  // packed pair of floats -> two bfloat16, the first in the low half
   uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  asm("{\n"
+      ".reg .f32 x, y;\n"
+      "mov.b64 {x, y}, %1;\n"
+      "cvt.rn.bf16x2.f32 %0, y, x;\n"
+      "}\n"
+      : "=r"(r)
+      : "l"(p));
   return r;
 }
+template <bool kEightBit>
+ORN_D void codes4_bf(uint32_t w, uint64_t a2, uint64_t b2, uint32_t& o0, uint32_t& o1) {
+  o0 = bf2_of(ffma2(a2, kEightBit ? code_pair_8<0>(w) : code_pair_hi<0>(w), b2));
+  o1 = bf2_of(ffma2(a2, kEightBit ? code_pair_8<2>(w) : code_pair_hi<2>(w), b2));
+}
+// (w >> sh) << up for every byte's field, as one rotation (the bits that wrap land outside the mask)
+ORN_D uint32_t field_up(uint32_t w, int sh, int up) { return __funnelshift_r(w, w, (sh - up) & 31); }
 
 // The raw bytes of a K block arrive by TMA as boxes of [128 rows x 16 / 32 / 64 bytes] cut out of
 // the row records (no swizzle: row r of a box is at r * box bytes).  A thread dequantises HALF of
-// one feature row's K block: 32 weights -> 64 bytes of bfloat16 (chunks 4*half .. 4*half+3 of the
-// row's 128 bytes in the swizzled MMA tile).
+// one feature row's K block: 32 weights -> 16 words of two bfloat16 each, in K order (word w of the
+// half = weights 2w, 2w + 1), which become 16 tensor-memory columns of the row's lane.
 //
 // Raw tile layout per format (byte offsets inside the stage's raw area) and the record offsets
 // (x coordinates, multiples of 16) the boxes are cut at, for K block kb (b = kb / 4):
@@ -209,7 +261,7 @@ template <> struct Fmt<ORN_BF16> {
     tma_load_2d(raw, wsw, kb * BK, row, bar);
   }
   static constexpr uint32_t kTxBytes = kWTileBytes;
-  ORN_D static void convert(uint32_t, int, int, int, uint32_t, const RecGeom&) {}
+  ORN_D static void convert(uint32_t, int, int, int, uint32_t*, const RecGeom&) {}
 };
 
 // affine 8-bit, group 64: w = scale * q + bias (one fma, as the embedding lookup computes it)
@@ -220,23 +272,14 @@ template <> struct Fmt<ORN_A8> {
     tma_load_2d(raw, m64, kb * 64, row, bar);
     tma_load_2d(raw + 8192, m16, (int)g.b0 + ((4 * kb) & ~15), row, bar);
   }
-  ORN_D static void convert(uint32_t raw, int r, int kb, int half, uint32_t row_addr, const RecGeom&) {
+  ORN_D static void convert(uint32_t raw, int r, int kb, int half, uint32_t* out, const RecGeom&) {
     const uint4 q0 = lds128(raw + r * 64 + half * 32), q1 = lds128(raw + r * 64 + half * 32 + 16);
     const uint32_t sb = lds32(raw + 8192 + r * 16 + ((4 * kb) & 15));
-    const float sc = bf_lo(sb), bi = bf_hi(sb);
-    const uint4 q[2] = {q0, q1};
+    const float sc = bf_lo(sb), bi = fmaf(-32768.0f, sc, bf_hi(sb));
+    const uint64_t a2 = pk2(sc, sc), b2 = pk2(bi, bi);
+    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint32_t w[4] = {q[h].x, q[h].y, q[h].z, q[h].w};
-      uint32_t o[8];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        o[2 * i] = pack_bf2(fmaf(sc, byte_f<0>(w[i]), bi), fmaf(sc, byte_f<1>(w[i]), bi));
-        o[2 * i + 1] = pack_bf2(fmaf(sc, byte_f<2>(w[i]), bi), fmaf(sc, byte_f<3>(w[i]), bi));
-      }
-      st_chunk(row_addr, r & 7, 4 * half + 2 * h, o[0], o[1], o[2], o[3]);
-      st_chunk(row_addr, r & 7, 4 * half + 2 * h + 1, o[4], o[5], o[6], o[7]);
-    }
+    for (int i = 0; i < 8; ++i) codes4_bf<true>(w[i], a2, b2, out[2 * i], out[2 * i + 1]);
   }
 };
 
@@ -248,18 +291,18 @@ template <> struct Fmt<ORN_A4> {
     tma_load_2d(raw, m32, kb * 32, row, bar);
     tma_load_2d(raw + 4096, m16, (int)g.b0 + ((8 * kb) & ~15), row, bar);
   }
-  ORN_D static void convert(uint32_t raw, int r, int kb, int half, uint32_t row_addr, const RecGeom&) {
+  ORN_D static void convert(uint32_t raw, int r, int kb, int half, uint32_t* out, const RecGeom&) {
     const uint4 q = lds128(raw + r * 32 + half * 16);
     const uint32_t sb = lds32(raw + 4096 + r * 16 + ((8 * kb) & 15) + 4 * half);
-    const float sc = bf_lo(sb), bi = bf_hi(sb);
+    const float sc = bf_lo(sb), a32 = 32.0f * sc, bi = fmaf(-16.0f, sc, bf_hi(sb));
+    const uint64_t a2 = pk2(a32, a32), b2 = pk2(bi, bi);
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {  // one word = 8 weights = one 16-byte chunk of bfloat16
-      const uint32_t l4 = w[c] & 0x0F0F0F0Fu, h4 = (w[c] >> 4) & 0x0F0F0F0Fu;
-      st_chunk(row_addr, r & 7, 4 * half + c, pack_bf2(fmaf(sc, byte_f<0>(l4), bi), fmaf(sc, byte_f<0>(h4), bi)),
-               pack_bf2(fmaf(sc, byte_f<1>(l4), bi), fmaf(sc, byte_f<1>(h4), bi)),
-               pack_bf2(fmaf(sc, byte_f<2>(l4), bi), fmaf(sc, byte_f<2>(h4), bi)),
-               pack_bf2(fmaf(sc, byte_f<3>(l4), bi), fmaf(sc, byte_f<3>(h4), bi)));
+    for (int c = 0; c < 4; ++c) {  // one word = 8 weights = 4 words of bfloat16 pairs (low nibble first)
+      const uint32_t l4 = field_up(w[c], 0, 3) & 0x78787878u, h4 = field_up(w[c], 4, 3) & 0x78787878u;
+      // weights 2b, 2b + 1 = (low, high) nibble of byte b: interleave the two nibble words bytewise
+      codes4_bf<false>(__byte_perm(l4, h4, 0x5140), a2, b2, out[4 * c], out[4 * c + 1]);
+      codes4_bf<false>(__byte_perm(l4, h4, 0x7362), a2, b2, out[4 * c + 2], out[4 * c + 3]);
     }
   }
 };
@@ -274,25 +317,17 @@ template <> struct Fmt<ORN_Q4K> {
     tma_load_2d(raw, m32, (kb >> 2) * 128 + (kb & 3) * 32, row, bar);
     tma_load_2d(raw + 4096, m16, (int)g.b0 + (kb >> 2) * 16, row, bar);
   }
-  ORN_D static void convert(uint32_t raw, int r, int kb, int half, uint32_t row_addr, const RecGeom&) {
+  ORN_D static void convert(uint32_t raw, int r, int kb, int half, uint32_t* out, const RecGeom&) {
     const uint4 qa = lds128(raw + r * 32), qb = lds128(raw + r * 32 + 16), hdr = lds128(raw + 4096 + r * 16);
     const float d = h2f((uint16_t)(hdr.x & 0xffff)), dmin = h2f((uint16_t)(hdr.x >> 16));
     float sc, m;
     q4k_scale_min(2 * (kb & 3) + half, hdr.y, hdr.z, hdr.w, &sc, &m);
-    const float a = d * sc, nb = -(dmin * m);
+    const float a = d * sc, a32 = 32.0f * a, nb = fmaf(-16.0f, a, -(dmin * m));
+    const uint64_t a2 = pk2(a32, a32), b2 = pk2(nb, nb);
     const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
     const int sh = 4 * half;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {  // 8 code bytes -> one chunk of this half
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const uint32_t n4 = (w[2 * c + j] >> sh) & 0x0F0F0F0Fu;
-        o[2 * j] = pack_bf2(fmaf(a, byte_f<0>(n4), nb), fmaf(a, byte_f<1>(n4), nb));
-        o[2 * j + 1] = pack_bf2(fmaf(a, byte_f<2>(n4), nb), fmaf(a, byte_f<3>(n4), nb));
-      }
-      st_chunk(row_addr, r & 7, 4 * half + c, o[0], o[1], o[2], o[3]);
-    }
+    for (int i = 0; i < 8; ++i) codes4_bf<false>(field_up(w[i], sh, 3) & 0x78787878u, a2, b2, out[2 * i], out[2 * i + 1]);
   }
 };
 
@@ -309,28 +344,24 @@ template <> struct Fmt<ORN_Q6K> {
     tma_load_2d(raw + 12288, m16, (int)g.b0 + b * 16, row, bar);
     tma_load_2d(raw + 14336, m16, (int)(g.b0 + g.b1) + ((2 * b) & ~15), row, bar);
   }
-  ORN_D static void convert(uint32_t raw, int r, int kb, int set, uint32_t row_addr, const RecGeom&) {
+  ORN_D static void convert(uint32_t raw, int r, int kb, int set, uint32_t* out, const RecGeom&) {
     const int b = kb >> 2, half128 = (kb >> 1) & 1, hi = kb & 1;
     const uint4 l0 = lds128(raw + r * 64 + 32 * set), l1 = lds128(raw + r * 64 + 32 * set + 16);
     const uint4 h0 = lds128(raw + 8192 + r * 32), h1 = lds128(raw + 8192 + r * 32 + 16);
     const uint32_t sc2 = lds16(raw + 12288 + r * 16 + 8 * half128 + 4 * hi + 2 * set);
     const float d = h2f((uint16_t)lds16(raw + 14336 + r * 16 + ((2 * b) & 15)));
     const float s0 = d * (float)(int8_t)(sc2 & 0xff), s1 = d * (float)(int8_t)(sc2 >> 8);
+    // w = s (q - 32) = 128 s (0.5 + q / 128) - 96 s
+    const uint64_t a20 = pk2(128.0f * s0, 128.0f * s0), a21 = pk2(128.0f * s1, 128.0f * s1);
+    const uint64_t b20 = pk2(-96.0f * s0, -96.0f * s0), b21 = pk2(-96.0f * s1, -96.0f * s1);
     const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
     const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
     const int hs = 2 * set + 4 * hi;  // bit position of this code set's two high bits in qh
     const int ls = 4 * hi;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const float sv = c < 2 ? s0 : s1;
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const uint32_t q = ((lw[2 * c + j] >> ls) & 0x0F0F0F0Fu) | (((hw[2 * c + j] >> hs) & 0x03030303u) << 4);
-        o[2 * j] = pack_bf2(sv * byte_m32_f<0>(q), sv * byte_m32_f<1>(q));
-        o[2 * j + 1] = pack_bf2(sv * byte_m32_f<2>(q), sv * byte_m32_f<3>(q));
-      }
-      st_chunk(row_addr, r & 7, 4 * set + c, o[0], o[1], o[2], o[3]);
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t q = (field_up(lw[i], ls, 1) & 0x1E1E1E1Eu) | (field_up(hw[i], hs, 5) & 0x60606060u);  // code << 1
+      codes4_bf<false>(q, i < 4 ? a20 : a21, i < 4 ? b20 : b21, out[2 * i], out[2 * i + 1]);
     }
   }
 };
@@ -377,10 +408,11 @@ struct GemmMaps {
   WeightMaps w[kMaxJobs];
 };
 
-// Two rings per CTA.  The IN ring (deep: TMA latency is a few thousand cycles) holds what TMA brings
-// per K block: the raw weight boxes and the token tiles.  The W ring (two or three 16 KB slots) holds
-// the dequantised weight tile the MMAs read.  bf16 weights need no dequantisation: their box lands
-// swizzled in the IN ring and the MMAs read it there.
+// Two rings per CTA.  The IN ring in shared memory (deep: TMA latency is a few thousand cycles) holds
+// what TMA brings per K block: the raw weight boxes and the token tiles.  The W ring in tensor memory
+// (two or three slots of 32 columns behind the accumulators) holds the dequantised weight tile the
+// MMAs read as their A operand.  bf16 weights need no dequantisation: their box lands swizzled in the
+// IN ring and the MMAs read it there (A from shared memory).
 //   landed[i]   TMA boxes of IN slot i arrived            (producer's expect_tx)
 //   full[w]     W slot w dequantised                       (one arrival per dequantising warp)
 //   in_free[i]  the MMAs that read IN slot i are done      (tcgen05.commit)
@@ -397,7 +429,7 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem0 = (smem_addr(smem_raw) + 1023u) & ~1023u;  // swizzled tiles want 1024-byte alignment
   const int SI = P.stages, SW = P.w_stages;
-  const uint32_t in0 = smem0 + (uint32_t)SW * kWTileBytes;  // W ring first, then the IN ring
+  const uint32_t in0 = smem0;
   const uint32_t bar_landed = smem_addr(&s_bar[0]), bar_in_free = smem_addr(&s_bar[kMaxIn]);
   const uint32_t bar_full = smem_addr(&s_bar[2 * kMaxIn]), bar_w_free = smem_addr(&s_bar[2 * kMaxIn + kMaxW]);
   const uint32_t bar_acc_full = smem_addr(&s_bar[2 * kMaxIn + 2 * kMaxW]), bar_acc_empty = bar_acc_full + 8;
@@ -469,12 +501,15 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
           if (!ok) break;
           tc_fence_after();
           const uint32_t inb = in0 + si * P.stage_bytes;
-          const uint32_t wa = kDirect ? inb : smem0 + sw * kWTileBytes, xa = inb + kInRaw;
+          const uint32_t xa = inb + kInRaw;
+          const uint32_t wt = tmem + P.acc_cols + (uint32_t)sw * kWCols;  // this K block's weight tile in tensor memory
           for (int t = 0; t < nt; ++t)
 #pragma unroll
-            for (int j = 0; j < BK / 16; ++j)
-              tc_mma(tmem + (uint32_t)(t * P.BN), smem_desc(wa + j * 32), smem_desc(xa + t * x_tile_bytes + j * 32), idesc,
-                     (kb > w.kb0 || j > 0) ? 1u : 0u);
+            for (int j = 0; j < BK / 16; ++j) {
+              const uint64_t xb = smem_desc(xa + t * x_tile_bytes + j * 32);
+              if (kDirect) tc_mma(tmem + (uint32_t)(t * P.BN), smem_desc(inb + j * 32), xb, idesc, (kb > w.kb0 || j > 0) ? 1u : 0u);
+              else tc_mma_ts(tmem + (uint32_t)(t * P.BN), wt + j * 8, xb, idesc, (kb > w.kb0 || j > 0) ? 1u : 0u);
+            }
           tc_commit(bar_in_free + 8 * si);  // both slots are free once these MMAs have read them
           tc_commit(bar_w_free + 8 * sw);
         }
@@ -486,10 +521,10 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
   } else {
     // ---- dequantising warps, then the epilogue of the item
     const int dq = threadIdx.x - 64;   // 0 .. 32 * DQW - 1
-    const int r = dq & 127;            // feature row of the tile this thread dequantises
-    const int half = dq >> 7;          // DQW == 8: which 32 of the K block's 64 weights (DQW == 4: both)
-    const int q = warp & 3;            // TMEM lane quadrant this warp may read
-    const int colhalf = (warp - 2) >> 2;  // DQW == 8: the two warps of a quadrant split the 16-column groups
+    const int q = warp & 3;            // tensor-memory lane quadrant this warp may touch
+    const int r = 32 * q + lane;       // feature row of the tile this thread dequantises = its tensor-memory lane
+    const int colhalf = (warp - 2) >> 2;  // DQW == 8: the two warps of a quadrant split a K block's weights and the
+                                          // epilogue's 16-column groups (DQW == 4: one warp does both halves)
     uint32_t acc_ph = 0, si_ph = 0, sw_ph = 0;
     int si = 0, sw = 0;
     Item w;
@@ -500,13 +535,20 @@ __global__ void __launch_bounds__(gemm_threads(DQW), DQW == 4 ? 4 : 1) k_qgemm(c
         ok = mbar_wait(bar_w_free + 8 * sw, sw_ph ^ 1u, P.err) && mbar_wait(bar_landed + 8 * si, si_ph, P.err);
         if (!ok) break;
         if (!kDirect) {
+          tc_fence_after();  // the MMAs that read this slot's last tile are done (w_free)
+          const uint32_t wt = tmem + ((uint32_t)(q * 32) << 16) + P.acc_cols + (uint32_t)sw * kWCols;
+          uint32_t o[16];
           if (DQW == 8) {
-            F::convert(in0 + si * P.stage_bytes, r, kb, half, smem0 + sw * kWTileBytes + (uint32_t)r * 128u, geo);
+            F::convert(in0 + si * P.stage_bytes, r, kb, colhalf, o, geo);
+            tmem_st16(wt + 16 * colhalf, o);
           } else {
-            F::convert(in0 + si * P.stage_bytes, r, kb, 0, smem0 + sw * kWTileBytes + (uint32_t)r * 128u, geo);
-            F::convert(in0 + si * P.stage_bytes, r, kb, 1, smem0 + sw * kWTileBytes + (uint32_t)r * 128u, geo);
+            F::convert(in0 + si * P.stage_bytes, r, kb, 0, o, geo);
+            tmem_st16(wt, o);
+            F::convert(in0 + si * P.stage_bytes, r, kb, 1, o, geo);
+            tmem_st16(wt + 16, o);
           }
-          fence_async_smem();  // the tensor core reads these bytes through the async proxy
+          tmem_st_wait();
+          tc_fence_before();  // ordered before the MMA thread's reads through the barrier below
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_full + 8 * sw);
@@ -802,15 +844,21 @@ int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, voi
   // tokens per item: 256 for dense products over many rows (a weight tile is dequantised once for
   // all of them; more would leave the IN ring too shallow to cover the TMA latency), a few tiles for
   // routed rows (an expert with more rows than that takes several items)
-  P.NT = (int)kTmemCols / BN;
+  P.NT = (int)kAccColsMax / BN;
   if (grp == nullptr) P.NT = std::min(std::min(P.NT, (rows + BN - 1) / BN), BN >= 128 ? 2 : 8);
   else P.NT = std::min(P.NT, BN >= 64 ? 4 : 2);
   if (P.NT > 8) P.NT = 8;
-  // shared memory: the W ring, then as many IN slots as fit (TMA latency wants depth)
+  // shared memory: as many IN slots as fit (TMA latency wants depth); tensor memory: the accumulators, then the W ring
   const uint32_t in_raw = L->kind == ORN_BF16 ? kWTileBytes : raw_bytes(L->kind);
   P.stage_bytes = in_raw + (uint32_t)P.NT * BN * 128u;
-  P.tmem_cols = 32;
-  while ((int)P.tmem_cols < P.NT * BN) P.tmem_cols <<= 1;
+  P.acc_cols = ((uint32_t)(P.NT * BN) + 31u) & ~31u;
+  const bool direct = L->kind == ORN_BF16;
+  auto tmem_need = [&](int ws) {  // power of two that holds the accumulators and ws weight tiles
+    uint32_t c = 32;
+    while (c < P.acc_cols + (direct ? 0u : (uint32_t)ws * kWCols)) c <<= 1;
+    return c;
+  };
+  P.tmem_cols = tmem_need(2);
   // Dense products over few rows are one token group: the K loop of an item is a chain of short
   // latency-bound steps (about 0.65 us per K block), so the blocks of a tile are split over several
   // CTAs whose f32 partials the last of them adds in split order.  The number of splits depends on
@@ -844,35 +892,37 @@ int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, voi
   size_t smem = 0;
   // Launches of many narrow items (routed experts with a few rows each): small CTAs of 4 dequantising
   // warps, two-slot rings, up to four per SM: an item's K loop is a latency chain, four chains overlap.
-  if (P.tmem_cols <= 128 && est_items > 2 * ctx->sm_count && P.splits == 1) {
-    const int ws = L->kind == ORN_BF16 ? 1 : 2;
-    const size_t need = 1024 + (size_t)ws * kWTileBytes + 2 * (size_t)P.stage_bytes;
+  if (tmem_need(2) <= 128 && est_items > 2 * ctx->sm_count && P.splits == 1) {
+    // four CTAs share the SM's 512 tensor-memory columns and its shared memory: up to four IN slots each
+    int st = (int)(((226 * 1024) / 4 - 2048) / P.stage_bytes);
+    st = std::min(st, 4);
+    if (st < 2) st = 2;
+    const size_t need = 1024 + (size_t)st * P.stage_bytes;
     const int fit = (int)((226 * 1024) / (need + 1024));  // + static shared memory and the allocation granule
     if (fit >= 3) {
-      ctas = std::min(4, fit); dqw = 4; P.w_stages = ws; P.stages = 2;
+      ctas = std::min(4, fit); dqw = 4; P.w_stages = direct ? 1 : 2; P.stages = st;
+      P.tmem_cols = tmem_need(2);
       smem = need;
     }
   }
-  if (ctas == 1 && P.tmem_cols <= 256 && est_items > ctx->sm_count) {
+  if (ctas == 1 && tmem_need(2) <= 256 && est_items > ctx->sm_count) {
     const size_t budget2 = 108 * 1024;
-    const int ws = L->kind == ORN_BF16 ? 1 : 2;
-    const int st = (int)std::min<size_t>(kMaxIn, (budget2 - (size_t)ws * kWTileBytes) / P.stage_bytes);
+    const int ws = direct ? 1 : (tmem_need(3) <= 256 ? 3 : 2);
+    const int st = (int)std::min<size_t>(kMaxIn, budget2 / P.stage_bytes);
     if (st >= 3) {
       ctas = 2; P.w_stages = ws; P.stages = st;
-      smem = 1024 + (size_t)ws * kWTileBytes + (size_t)st * P.stage_bytes;
+      P.tmem_cols = tmem_need(ws);
+      smem = 1024 + (size_t)st * P.stage_bytes;
     }
   }
   if (ctas == 1) {
-    P.w_stages = L->kind == ORN_BF16 ? 1 : kMaxW;
+    P.w_stages = direct ? 1 : kMaxW;
+    P.tmem_cols = tmem_need(P.w_stages);
     const size_t budget = 200 * 1024;
-    P.stages = (int)std::min<size_t>(kMaxIn, (budget - (size_t)P.w_stages * kWTileBytes) / P.stage_bytes);
-    if (P.stages < 2) {
-      P.w_stages = L->kind == ORN_BF16 ? 1 : 2;
-      P.stages = (int)std::min<size_t>(kMaxIn, (budget - (size_t)P.w_stages * kWTileBytes) / P.stage_bytes);
-    }
+    P.stages = (int)std::min<size_t>(kMaxIn, budget / P.stage_bytes);
     if (P.stages < 2) ORN_FAIL(ctx, ORN_ERR_ARG, "gemm: stage does not fit twice into shared memory");
     // one CTA per SM (it may take all of tensor memory): pad the launch's shared memory above half of the SM's
-    smem = 1024 + (size_t)P.w_stages * kWTileBytes + (size_t)P.stages * P.stage_bytes;
+    smem = 1024 + (size_t)P.stages * P.stage_bytes;
     if (smem < 120 * 1024) smem = 120 * 1024;
   }
   GemmMaps maps;
