@@ -61,7 +61,7 @@ constexpr size_t kSplitPartialBytes = (size_t)64 << 20;  // f32 partials of one 
 constexpr size_t kSplitTiles = 4096;                     // arrival counters
 constexpr uint32_t kWTileBytes = BM * BK * 2;
 constexpr int kMaxIn = 12;  // IN ring slots (raw weight boxes + token tiles)
-constexpr int kMaxW = 3;    // W ring slots (dequantised weight tile)
+constexpr int kMaxW = 4;    // W ring slots (dequantised weight tile)
 constexpr uint32_t kGemmWaitLimit = 1u << 16;  // try_wait rounds (each may sleep kGemmHintNs)
 constexpr uint32_t kGemmHintNs = 20000;
 
@@ -900,14 +900,16 @@ int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, voi
     const size_t need = 1024 + (size_t)st * P.stage_bytes;
     const int fit = (int)((226 * 1024) / (need + 1024));  // + static shared memory and the allocation granule
     if (fit >= 3) {
-      ctas = std::min(4, fit); dqw = 4; P.w_stages = direct ? 1 : 2; P.stages = st;
-      P.tmem_cols = tmem_need(2);
+      // the weight ring takes what the accumulators leave of the CTA's 128 columns: hand-offs between the
+      // dequantising warps and the MMA thread are a round trip of several hundred cycles per slot
+      ctas = std::min(4, fit); dqw = 4; P.w_stages = direct ? 1 : std::min<int>(kMaxW, (128 - (int)P.acc_cols) / (int)kWCols); P.stages = st;
+      P.tmem_cols = tmem_need(P.w_stages);
       smem = need;
     }
   }
   if (ctas == 1 && tmem_need(2) <= 256 && est_items > ctx->sm_count) {
     const size_t budget2 = 108 * 1024;
-    const int ws = direct ? 1 : (tmem_need(3) <= 256 ? 3 : 2);
+    const int ws = direct ? 1 : std::min<int>(kMaxW, (256 - (int)P.acc_cols) / (int)kWCols);
     const int st = (int)std::min<size_t>(kMaxIn, budget2 / P.stage_bytes);
     if (st >= 3) {
       ctas = 2; P.w_stages = ws; P.stages = st;
@@ -916,7 +918,7 @@ int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, voi
     }
   }
   if (ctas == 1) {
-    P.w_stages = direct ? 1 : kMaxW;
+    P.w_stages = direct ? 1 : std::min<int>(kMaxW, (512 - (int)P.acc_cols) / (int)kWCols);
     P.tmem_cols = tmem_need(P.w_stages);
     const size_t budget = 200 * 1024;
     P.stages = (int)std::min<size_t>(kMaxIn, budget / P.stage_bytes);
