@@ -87,6 +87,73 @@ __global__ void ep_map_kernel(const uint32_t* all_inds, int routes, int base, in
   const int e = (int)all_inds[i] - base;
   rhs_local[i] = (e >= 0 && e < e_local) ? (uint32_t)e : 0xFFFFFFFFu;
 }
+// ep_map + counting sort of the routes in one launch of one CTA (a decode batch has a few thousand routes
+// at most): seg[e] = first sorted position of local expert e, seg[e_local] = routes this rank owns,
+// perm[p] = route at sorted position p; inside an expert the routes keep their order (counting_sort,
+// src/ops/moe.rs:463-508).  Rounds of 1024 routes: a warp counts its 32 routes per expert, a scan over
+// the warps gives every warp its offset inside the expert, the rank inside the warp is a match mask.
+constexpr int kRouteMaxLocal = 256;   // local experts the one-launch form handles
+constexpr int kRouteMaxRoutes = 8192;
+__global__ void __launch_bounds__(1024) ep_route_kernel(const uint32_t* all_inds, int routes, int base, int e_local,
+                                                        int* seg /*[e_local + 1]*/, uint32_t* perm) {
+  __shared__ int s_seg[kRouteMaxLocal + 1];          // exclusive scan of the counts
+  __shared__ int s_done[kRouteMaxLocal];             // routes of the expert placed by earlier rounds
+  __shared__ uint16_t s_cnt[32][kRouteMaxLocal];     // this round: routes per (warp, expert), then the warp's offset
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  auto local = [&](int i) {
+    const int e = i < routes ? (int)all_inds[i] - base : -1;
+    return (e >= 0 && e < e_local) ? e : -1;
+  };
+  // totals per expert
+  for (int e = threadIdx.x; e <= e_local; e += blockDim.x) s_seg[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < routes; i += blockDim.x) {
+    const int e = local(i);
+    if (e >= 0) atomicAdd(&s_seg[e], 1);
+  }
+  __syncthreads();
+  if (warp == 0) {  // exclusive scan, 32 experts per step
+    int carry = 0;
+    for (int e0 = 0; e0 <= e_local; e0 += 32) {
+      const int e = e0 + lane;
+      const int c = e < e_local ? s_seg[e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+      }
+      if (e <= e_local) s_seg[e] = carry + incl - c;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  for (int e = threadIdx.x; e < e_local; e += blockDim.x) s_done[e] = 0;
+  __syncthreads();
+  for (int e = threadIdx.x; e <= e_local; e += blockDim.x) seg[e] = s_seg[e];
+  // stable placement
+  for (int i0 = 0; i0 < routes; i0 += blockDim.x) {
+    for (int e = lane; e < e_local; e += 32) s_cnt[warp][e] = 0;
+    __syncwarp();
+    const int i = i0 + threadIdx.x;
+    const int e = local(i);
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(same & ((1u << lane) - 1u));
+    if (e >= 0 && rank_in_warp == 0) s_cnt[warp][e] = (uint16_t)__popc(same);
+    __syncthreads();
+    for (int x = threadIdx.x; x < e_local; x += blockDim.x) {  // offsets of the warps inside expert x, then its new total
+      int acc = s_done[x];
+      for (int w = 0; w < 32; ++w) {
+        const int c = s_cnt[w][x];
+        s_cnt[w][x] = (uint16_t)acc;
+        acc += c;
+      }
+      s_done[x] = acc;
+    }
+    __syncthreads();
+    if (e >= 0) perm[s_seg[e] + s_cnt[warp][e] + rank_in_warp] = (uint32_t)i;
+    __syncthreads();
+  }
+}
 // lhs[i] = i / k: the row a route belongs to
 __global__ void ep_iota_kernel(uint32_t* lhs, int n, int k) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -276,9 +343,14 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
 #define EPCK(call) do { int rc__ = (call); if (rc__ != ORN_OK) return rc__; } while (0)
   // ---- home: routing and the shared expert (one launch per matrix over all R rows)
   uint32_t* inds = dev_inds_out ? dev_inds_out : ep->inds;
-  EPCK(k_grouped_gemv(ctx, s, gate, dev_x, ep->seg1, ep->gates, nullptr, R));
-  EPCK(k_softmax_precise(ctx, s, ep->gates, R, E, ep->probs));
-  EPCK(k_router_topk(ctx, s, ep->probs, R, E, k, inds, ep->scores));
+  // the router and the shared expert's gate in one launch (neither depends on the exchange)
+  EPCK(k_grouped_gemv2(ctx, s, gate, ep->gates, sh_egate, ep->gs, dev_x, ep->seg1, R));
+  if (E <= 512) {
+    EPCK(k_softmax_topk(ctx, s, ep->gates, R, E, k, inds, ep->scores));
+  } else {
+    EPCK(k_softmax_precise(ctx, s, ep->gates, R, E, ep->probs));
+    EPCK(k_router_topk(ctx, s, ep->probs, R, E, k, inds, ep->scores));
+  }
   // ---- every rank learns the whole routing table and the rows
   const uint32_t* all_inds = inds;
   const bf16_t* all_x = dev_x;
@@ -292,7 +364,6 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
     all_x = ep->all_x;
   }
   // the shared expert does not depend on the exchange: it runs while the gathered table lands
-  EPCK(k_grouped_gemv(ctx, s, sh_egate, dev_x, ep->seg1, ep->gs, nullptr, R));
   const bool wide_shared = !ep->exact && R >= 16 && H % 64 == 0 && SI % 64 == 0;
   if (wide_shared) {  // like the routed experts: one dense contraction per matrix over all R rows
     if (sh_gate->kind == sh_up->kind && sh_gate->K == sh_up->K) {  // one launch for both (a row's bits do not depend on the tile shape)
@@ -308,13 +379,23 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
     EPCK(k_grouped_gemv(ctx, s, sh_gate, dev_x, ep->seg1, ep->sg, nullptr, R));
     EPCK(k_grouped_gemv(ctx, s, sh_up, dev_x, ep->seg1, ep->su, nullptr, R));
   }
-  EPCK(k_swiglu(ctx, s, ep->sg, ep->su, R * SI, ep->sact));
-  if (wide_shared) EPCK(f_qgemm(ctx, s, sh_down, ep->sact, R, ep->sy, H, nullptr, nullptr));
-  else EPCK(k_grouped_gemv(ctx, s, sh_down, ep->sact, ep->seg1, ep->sy, nullptr, R));
+  // the shared expert's SwiGLU and down projection: with the routed experts' (one launch for both SwiGLUs)
+  // on the tensor-core path, right here otherwise
+  const bool joint_swiglu = !ep->exact;
+  if (!joint_swiglu) {
+    EPCK(k_swiglu(ctx, s, ep->sg, ep->su, R * SI, ep->sact));
+    if (wide_shared) EPCK(f_qgemm(ctx, s, sh_down, ep->sact, R, ep->sy, H, nullptr, nullptr));
+    else EPCK(k_grouped_gemv(ctx, s, sh_down, ep->sact, ep->seg1, ep->sy, nullptr, R));
+  }
   // ---- owner: this rank's routes, sorted by expert
-  ep_map_kernel<<<(routes + 255) / 256, 256, 0, s>>>(all_inds, routes, ep->rank * el, el, ep->rhs_local);
-  EPCK(orn_launch_check(ctx, "ep_map"));
-  EPCK(f_route_sort(ctx, s, ep->rhs_local, routes, el, ep->seg, ep->seg + el + 1, ep->perm));
+  if (el <= kRouteMaxLocal && routes <= kRouteMaxRoutes) {
+    ep_route_kernel<<<1, 1024, 0, s>>>(all_inds, routes, ep->rank * el, el, ep->seg, ep->perm);
+    EPCK(orn_launch_check(ctx, "ep_route"));
+  } else {
+    ep_map_kernel<<<(routes + 255) / 256, 256, 0, s>>>(all_inds, routes, ep->rank * el, el, ep->rhs_local);
+    EPCK(orn_launch_check(ctx, "ep_map"));
+    EPCK(f_route_sort(ctx, s, ep->rhs_local, routes, el, ep->seg, ep->seg + el + 1, ep->perm));
+  }
   const int* n_owned = ep->seg + el;  // device: seg[el] = number of routes this rank owns
   ep_gather_kernel<<<routes, 128, 0, s>>>(all_x, ep->lhs, ep->perm, n_owned, H, ep->xs);
   EPCK(orn_launch_check(ctx, "ep_gather"));
@@ -340,8 +421,9 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
       EPCK(f_qgemm(ctx, s, sw_gate, ep->xs, routes, ep->eg, I, &sorted, ep->gemm_scratch));
       EPCK(f_qgemm(ctx, s, sw_up, ep->xs, routes, ep->eu, I, &sorted, ep->gemm_scratch));
     }
-    ep_swiglu_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(ep->eg, ep->eu, n_owned, I, ep->eact);
-    EPCK(orn_launch_check(ctx, "ep_swiglu"));
+    EPCK(k_swiglu2(ctx, s, ep->sg, ep->su, (size_t)R * SI, ep->sact, ep->eg, ep->eu, n_owned, I, ep->eact));
+    if (wide_shared) EPCK(f_qgemm(ctx, s, sh_down, ep->sact, R, ep->sy, H, nullptr, nullptr));
+    else EPCK(k_grouped_gemv(ctx, s, sh_down, ep->sact, ep->seg1, ep->sy, nullptr, R));
     EPCK(f_qgemm(ctx, s, sw_down, ep->eact, routes, ret, H, &back, ep->gemm_scratch));
   }
   // ---- the return: one fixed-size block per pair of ranks

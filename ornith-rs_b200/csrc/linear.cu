@@ -480,14 +480,17 @@ ORN_D void grouped_rows(const LinDev& L, int64_t rowbase, int row0, int row_end,
 template <int KIND, int R, int SU>
 __global__ void __launch_bounds__(kGroupThreads)
 grouped_gemv_kernel(LinDev L, const bf16_t* __restrict__ xs, const int* __restrict__ seg, bf16_t* __restrict__ y,
-                    const uint32_t* __restrict__ row_map, int rows_per_block) {
+                    const uint32_t* __restrict__ row_map, int rows_per_block, LinDev L2, bf16_t* __restrict__ y2, int blocks1) {
   extern __shared__ __align__(16) uint8_t gsm[];
   bf16_t* xsm = reinterpret_cast<bf16_t*>(gsm);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int e = blockIdx.y;
   const int first = seg[e], n = seg[e + 1] - first;
   if (n <= 0) return;
-  const int chunk0 = blockIdx.x * rows_per_block;
+  // a second matrix over the same rows (same format and row length) rides in the blocks behind the first one's
+  int bx = blockIdx.x;
+  if (bx >= blocks1) { L = L2; y = y2; bx -= blocks1; }
+  const int chunk0 = bx * rows_per_block;
   const int row_end = min(L.O, chunk0 + rows_per_block);
   // the expert's rows in passes of four; blockIdx.z takes every gridDim.z-th pass
   for (int m0 = kGroupBatch * blockIdx.z; m0 < n; m0 += kGroupBatch * gridDim.z) {
@@ -510,7 +513,7 @@ grouped_gemv_kernel(LinDev L, const bf16_t* __restrict__ xs, const int* __restri
 
 template <int KIND>
 int launch_grouped(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf16_t* xs, const int* seg, bf16_t* y,
-                   const uint32_t* row_map, int max_rows) {
+                   const uint32_t* row_map, int max_rows, const orn_linear* L2 = nullptr, bf16_t* y2 = nullptr) {
   const size_t smem = (size_t)kGroupBatch * L->K * sizeof(bf16_t);
   if (smem > 48 * 1024) ORN_FAIL(ctx, ORN_ERR_ARG, "grouped gemv: rows longer than 6144 weights");
   // passes of four rows spread over blockIdx.z: all of them for one dense matrix over many rows,
@@ -520,10 +523,12 @@ int launch_grouped(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf1
   if (z > 64) z = 64;
   // one small dense matrix (a router) over many rows: narrower blocks so that the launch fills the part
   const int rpb = (L->E == 1 && L->O <= 1024) ? 32 : kGroupRows;
-  dim3 grid((L->O + rpb - 1) / rpb, L->E, z);
+  const int blocks1 = (L->O + rpb - 1) / rpb, blocks2 = L2 ? (L2->O + rpb - 1) / rpb : 0;
+  dim3 grid(blocks1 + blocks2, L->E, z);
   const int units = L->K / Fmt<KIND>::kWeightsPerUnit;
-  if (units > 32) grouped_gemv_kernel<KIND, 2, 2><<<grid, kGroupThreads, smem, st>>>(lin_dev(L), xs, seg, y, row_map, rpb);
-  else grouped_gemv_kernel<KIND, 4, 1><<<grid, kGroupThreads, smem, st>>>(lin_dev(L), xs, seg, y, row_map, rpb);
+  const LinDev d1 = lin_dev(L), d2 = L2 ? lin_dev(L2) : d1;
+  if (units > 32) grouped_gemv_kernel<KIND, 2, 2><<<grid, kGroupThreads, smem, st>>>(d1, xs, seg, y, row_map, rpb, d2, y2, blocks1);
+  else grouped_gemv_kernel<KIND, 4, 1><<<grid, kGroupThreads, smem, st>>>(d1, xs, seg, y, row_map, rpb, d2, y2, blocks1);
   return orn_launch_check(ctx, "grouped_gemv");
 }
 }  // namespace
@@ -538,6 +543,23 @@ int k_grouped_gemv(orn_ctx* ctx, cudaStream_t st, const orn_linear* L, const bf1
     case ORN_A8: return launch_grouped<ORN_A8>(ctx, st, L, xs, seg, y, row_map, max_rows);
     case ORN_A4: return launch_grouped<ORN_A4>(ctx, st, L, xs, seg, y, row_map, max_rows);
     default: return launch_grouped<ORN_BF16>(ctx, st, L, xs, seg, y, row_map, max_rows);
+  }
+}
+
+// two dense matrices of one format and row length over the same rows in one launch (the router and the
+// shared expert's gate): each output has the bits of its own launch
+int k_grouped_gemv2(orn_ctx* ctx, cudaStream_t st, const orn_linear* L1, bf16_t* y1, const orn_linear* L2, bf16_t* y2,
+                    const bf16_t* xs, const int* seg, int max_rows) {
+  if (L1->kind != L2->kind || L1->K != L2->K || L1->E != 1 || L2->E != 1) {
+    int rc = k_grouped_gemv(ctx, st, L1, xs, seg, y1, nullptr, max_rows);
+    return rc != ORN_OK ? rc : k_grouped_gemv(ctx, st, L2, xs, seg, y2, nullptr, max_rows);
+  }
+  switch (L1->kind) {
+    case ORN_Q4K: return launch_grouped<ORN_Q4K>(ctx, st, L1, xs, seg, y1, nullptr, max_rows, L2, y2);
+    case ORN_Q6K: return launch_grouped<ORN_Q6K>(ctx, st, L1, xs, seg, y1, nullptr, max_rows, L2, y2);
+    case ORN_A8: return launch_grouped<ORN_A8>(ctx, st, L1, xs, seg, y1, nullptr, max_rows, L2, y2);
+    case ORN_A4: return launch_grouped<ORN_A4>(ctx, st, L1, xs, seg, y1, nullptr, max_rows, L2, y2);
+    default: return launch_grouped<ORN_BF16>(ctx, st, L1, xs, seg, y1, nullptr, max_rows, L2, y2);
   }
 }
 

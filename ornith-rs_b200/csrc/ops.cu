@@ -153,6 +153,77 @@ __global__ void router_topk_kernel(const bf16_t* __restrict__ gates, int n, int 
   }
 }
 
+// softmax_kernel and router_topk_kernel in one launch (the decode batch's router): the bfloat16
+// probabilities stay in shared memory, warp 0 then selects from them.  Same arithmetic, same bits.
+__global__ void softmax_topk_kernel(const bf16_t* __restrict__ x, int n, int k, uint32_t* __restrict__ inds,
+                                    bf16_t* __restrict__ scores) {
+  __shared__ float red[32];
+  __shared__ float probs[32 * kRouterMaxPerLane];
+  const int row = blockIdx.x;
+  const int64_t base = (int64_t)row * n;
+  const int i0 = threadIdx.x * 4;
+  float v[4];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[i] = (i0 + i < n) ? bf2f(x[base + i0 + i]) : -INFINITY;
+    m = fmaxf(m, v[i]);
+  }
+  m = block_max(m, red);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (i0 + i < n) {
+      v[i] = orn_expf(v[i] - m);
+      acc = acc + v[i];
+    }
+  const float total = block_sum_ordered(acc, red);
+  const float inv = 1.0f / total;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (i0 + i < n) probs[i0 + i] = bfr(v[i] * inv);
+  __syncthreads();
+  if (threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
+  float pv[kRouterMaxPerLane];
+  int held = 0;
+#pragma unroll
+  for (int s = 0; s < kRouterMaxPerLane; ++s) {
+    const int i = lane + 32 * s;
+    pv[s] = -INFINITY;
+    if (i < n) { pv[s] = probs[i]; held = s + 1; }
+  }
+  for (int r = 0; r < k; ++r) {
+    float best = -INFINITY;
+    uint32_t besti = 0;
+#pragma unroll
+    for (int s = 0; s < kRouterMaxPerLane; ++s) {
+      const uint32_t i = lane + 32 * s;
+      if (s < held && (pv[s] > best || (pv[s] == best && i > besti))) { best = pv[s]; besti = i; }
+    }
+    const float mm = warp_max(best);
+    const uint32_t mi = warp_max_u32(best == mm ? besti + 1 : 0u) - 1;
+#pragma unroll
+    for (int s = 0; s < kRouterMaxPerLane; ++s)
+      if ((mi & 31) == (uint32_t)lane && (mi >> 5) == (uint32_t)s) pv[s] = -INFINITY;
+    if (lane == 0) {
+      const int slot = row * k + (k - 1 - r);
+      inds[slot] = mi;
+      scores[slot] = f2bf(probs[mi]);
+    }
+  }
+}
+
+// two SwiGLU jobs in one launch: n1 elements of (g1, u1) and *n2_rows x width2 elements of (g2, u2)
+__global__ void swiglu2_kernel(const bf16_t* g1, const bf16_t* u1, size_t n1, bf16_t* out1, const bf16_t* g2, const bf16_t* u2,
+                               const int* n2_rows, int width2, bf16_t* out2) {
+  const size_t n2 = (size_t)(*n2_rows) * width2;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n1 + n2; i += (size_t)gridDim.x * blockDim.x) {
+    if (i < n1) out1[i] = f2bf(orn_swiglu_bf(bf2f(g1[i]), bf2f(u1[i])));
+    else out2[i - n1] = f2bf(orn_swiglu_bf(bf2f(g2[i - n1]), bf2f(u2[i - n1])));
+  }
+}
+
 // kernels/moe.metal:207-244: bfloat16 arithmetic, ascending j
 __global__ void moe_combine_kernel(const bf16_t* __restrict__ scores, const bf16_t* __restrict__ y,
                                    const bf16_t* __restrict__ gate, const bf16_t* __restrict__ shared,
@@ -276,6 +347,16 @@ int k_router_topk(orn_ctx* ctx, cudaStream_t s, const bf16_t* gates, int rows, i
   if (n > 32 * kRouterMaxPerLane || k > n) ORN_FAIL(ctx, ORN_ERR_ARG, "router_topk: n > 512 or k > n");
   router_topk_kernel<<<rows, 32, 0, s>>>(gates, n, k, inds, scores);
   return orn_launch_check(ctx, "router_topk");
+}
+int k_softmax_topk(orn_ctx* ctx, cudaStream_t s, const bf16_t* x, int rows, int n, int k, uint32_t* inds, bf16_t* scores) {
+  if (n > 32 * kRouterMaxPerLane || k > n) ORN_FAIL(ctx, ORN_ERR_ARG, "softmax_topk: n > 512 or k > n");
+  softmax_topk_kernel<<<rows, norm_threads(n), 0, s>>>(x, n, k, inds, scores);
+  return orn_launch_check(ctx, "softmax_topk");
+}
+int k_swiglu2(orn_ctx* ctx, cudaStream_t s, const bf16_t* g1, const bf16_t* u1, size_t n1, bf16_t* out1, const bf16_t* g2,
+              const bf16_t* u2, const int* n2_rows, int width2, bf16_t* out2) {
+  swiglu2_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(g1, u1, n1, out1, g2, u2, n2_rows, width2, out2);
+  return orn_launch_check(ctx, "swiglu2");
 }
 int k_moe_combine(orn_ctx* ctx, cudaStream_t s, const bf16_t* scores, const bf16_t* y,
                   const bf16_t* gate, const bf16_t* shared, int T, int k, int dim, int normalize,

@@ -165,6 +165,8 @@ int k_gather_gemv(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_
                   const uint32_t* lhs, const uint32_t* rhs, int rows, bf16_t* y);
 int k_grouped_gemv(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const bf16_t* xs, const int* seg, bf16_t* y,
                    const uint32_t* row_map /*nullable*/, int max_rows /*upper bound of the rows of one expert*/);
+int k_grouped_gemv2(orn_ctx* ctx, cudaStream_t st, const orn_linear* L1, bf16_t* y1, const orn_linear* L2, bf16_t* y2,
+                    const bf16_t* xs, const int* seg, int max_rows);
 int k_kq_dequantize(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, int e, float* out);
 int k_embedding(orn_ctx* ctx, cudaStream_t s, const orn_linear* L, const uint32_t* ids, int T,
                 bf16_t* out);
@@ -191,6 +193,9 @@ int k_sigmoid_gate(orn_ctx* ctx, cudaStream_t s, const bf16_t* gate, const bf16_
 int k_swiglu(orn_ctx* ctx, cudaStream_t s, const bf16_t* g, const bf16_t* u, int n, bf16_t* out);
 int k_add(orn_ctx* ctx, cudaStream_t s, const bf16_t* a, const bf16_t* b, int n, bf16_t* out);
 int k_softmax_precise(orn_ctx* ctx, cudaStream_t s, const bf16_t* x, int rows, int n, bf16_t* out);
+int k_softmax_topk(orn_ctx* ctx, cudaStream_t s, const bf16_t* x, int rows, int n, int k, uint32_t* inds, bf16_t* scores);
+int k_swiglu2(orn_ctx* ctx, cudaStream_t s, const bf16_t* g1, const bf16_t* u1, size_t n1, bf16_t* out1, const bf16_t* g2,
+              const bf16_t* u2, const int* n2_rows, int width2, bf16_t* out2);
 int k_router_topk(orn_ctx* ctx, cudaStream_t s, const bf16_t* gates, int rows, int n, int k,
                   uint32_t* inds, bf16_t* scores);
 int k_moe_combine(orn_ctx* ctx, cudaStream_t s, const bf16_t* scores, const bf16_t* y,
