@@ -1500,12 +1500,13 @@ __global__ void __launch_bounds__(gdn_threads(kGdnMaxT)) k_gdn(GdnParams p) {
   const int cur = *p.cur;
   const float* sin = p.ring + (size_t)(cur % p.nring) * ssz + off;
   float S[32];
-  if (owner) {
+  if (owner) {  // a thread's 32 state floats are one 128-byte line: four requests of a whole sector each
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float4 v4 = *reinterpret_cast<const float4*>(sin + 4 * i);
-      S[4 * i] = v4.x; S[4 * i + 1] = v4.y; S[4 * i + 2] = v4.z; S[4 * i + 3] = v4.w;
-    }
+    for (int i = 0; i < 4; ++i)
+      asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                   : "=f"(S[8 * i]), "=f"(S[8 * i + 1]), "=f"(S[8 * i + 2]), "=f"(S[8 * i + 3]), "=f"(S[8 * i + 4]),
+                     "=f"(S[8 * i + 5]), "=f"(S[8 * i + 6]), "=f"(S[8 * i + 7])
+                   : "l"(sin + 8 * i));
   }
   // The state and the ring position were written by an earlier step (a graph launch, a copy or a
   // host read lies in between), not by the kernel this one may overlap: only what follows reads
@@ -1652,8 +1653,11 @@ __global__ void __launch_bounds__(gdn_threads(kGdnMaxT)) k_gdn(GdnParams p) {
     else if (t + 1 == p.T) sout = p.ring + (size_t)((cur + 1) % p.nring) * ssz + off;
     if (sout != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        *reinterpret_cast<float4*>(sout + 4 * i) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+      for (int i = 0; i < 4; ++i)
+        asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(sout + 8 * i), "f"(S[8 * i]),
+                     "f"(S[8 * i + 1]), "f"(S[8 * i + 2]), "f"(S[8 * i + 3]), "f"(S[8 * i + 4]), "f"(S[8 * i + 5]),
+                     "f"(S[8 * i + 6]), "f"(S[8 * i + 7])
+                     : "memory");
     }
   }
   if (p.gated_out == nullptr) return;
