@@ -218,7 +218,9 @@ def ep_decode(pkg, ctx, dist, rank, world, model, cfg, steps=8, warmup=3, total_
             "launches_per_step": int(launches // steps), "h2d_bytes_per_step": B * 4 + B * T * 4 + B * 4,
             "d2h_bytes_per_step": B * 4 + B * T * 4, "targets_checksum": check,
             "scope": "MTP depth-1 cycle: draft pass + verify pass (trunk, lm_head, greedy) + per-sequence commit and re-encode",
-            "parallelism": "dp%d over sequences x ep%d over experts" % (world, world)}
+            "parallelism": "dp%d over sequences x ep%d over experts" % (world, world),
+            "exchange": "none (one rank)" if group is None else
+                        ("the library's kernels over peer memory" if group.peer_windows else "NCCL collectives")}
 
 
 def draft_bytes(cfg, head_rows):
@@ -613,8 +615,10 @@ def ep_moe_layer(pkg, ctx, dist, rank, world, exact=False, steps=30, warmup=5):
             "peak_source": which, "launches_per_layer": int(launches), "checksum": check,
             "routed_experts": "grouped row-invariant mat-vec (bits of the single-GPU block)" if exact
                               else "grouped tensor-core product (tcgen05), routing and combine row-invariant",
-            "collectives": "all-gather of routing indices and rows, all-to-all of fixed return blocks (NCCL, library stream)"
-                           if world > 1 else "none (one rank)"}
+            "collectives": "none (one rank)" if world == 1 else
+                           "rows and routing indices stored into every rank's window, expert outputs stored into their home "
+                           "rank's window (the library's kernels over peer memory, flags with bounded waits)" if group.peer_windows else
+                           "all-gather of routing indices and rows, all-to-all of fixed return blocks (NCCL, library stream)"}
 
 
 def oracle_check(pkg, ctx):

@@ -429,6 +429,10 @@ int32_t orn_batch_mtp_draft(orn_batch* bt, orn_ep* ep /*nullable*/, const uint32
                             uint32_t* host_drafts);
 int32_t orn_ep_world(const orn_ep* ep);
 int32_t orn_ep_rank(const orn_ep* ep);
+/* 1 when the group's per-layer exchanges run as the library's own kernels over peer memory (every rank
+ * mapped the exchange windows of all the others at orn_ep_init), 0 when they are NCCL collectives (one
+ * rank, more than 8 ranks, windows that could not be mapped, or ORN_EP_NCCL=1 in the environment). */
+int32_t orn_ep_peer_windows(const orn_ep* ep);
 
 /* host copies of the shared elementary functions, so that a checker can
  * compare them with its own restatement without a GPU */

@@ -1,7 +1,13 @@
 // Expert-parallel sparse MoE block: the 256 experts are split evenly over the ranks of one node
 // (expert e lives on rank e / (E / world)), token rows stay with the rank that owns their
-// sequence, and one layer costs two small collectives each way over NVLink (NCCL, stream-ordered
-// on the context's stream; no peer pointers, no multicast loads).
+// sequence, and one layer costs one small exchange each way over NVLink.  The exchanges are the
+// library's own kernels over peer memory: every rank maps the others' exchange windows (CUDA IPC),
+// stores its rows straight into them with plain stores and raises a flag there; a rank goes on when
+// the flags of all its peers have reached the call's sequence number (bounded wait, error flag).
+// A decode batch moves a few hundred KB per layer, so the exchange is latency, not bandwidth: two
+// kernels per layer instead of NCCL's two grouped collectives (about 40 us each among 8 ranks).
+// NCCL remains for the set-up (window handles) and as the exchange when the windows cannot be mapped
+// (ORN_EP_NCCL=1 forces it).  No multicast loads, no TMA from peer memory.
 //
 // The reference is single-GPU (README.md:217-221); what it has is the block this distributes,
 // sparse_moe_block (src/ops/moe.rs:662-741), and the building block an expert owner needs: rows
@@ -183,6 +189,73 @@ __global__ void ep_select_kernel(const bf16_t* recv, const uint32_t* inds, int e
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
+
+// ---- the exchange over peer memory ---------------------------------------------------------------
+constexpr int kEpMaxPeers = 8;
+constexpr unsigned kEpSpinLimit = 1u << 22;  // polls of 200 ns: about a second, then the error flag
+struct EpPeers {
+  uint8_t* win[kEpMaxPeers];  // exchange window of every rank, as mapped into this process
+};
+// The last CTA of a grid to get here (its stores and everybody else's are fenced) tells every peer that
+// this rank's part of call number `epoch` is in place, then waits until all peers have said the same.
+// sync[0] = arrivals of this grid, sync[1] = calls so far (both in this rank's own memory).
+ORN_D void ep_signal_and_wait(const EpPeers& peers, int W, int rank, size_t off_flags, int* sync, int* err) {
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&sync[0], 1) == (int)(gridDim.x * gridDim.y) - 1 ? 1 : 0;
+  __syncthreads();
+  if (!s_last || threadIdx.x >= 32) return;
+  __threadfence_system();
+  const int epoch = sync[1] + 1;
+  const int lane = threadIdx.x;
+  if (lane < W) {
+    volatile int* theirs = reinterpret_cast<volatile int*>(peers.win[lane] + off_flags) + rank;
+    *theirs = epoch;
+  }
+  if (lane < W) {
+    volatile int* mine = reinterpret_cast<volatile int*>(peers.win[rank] + off_flags) + lane;
+    unsigned spins = 0;
+    while (*mine - epoch < 0) {
+      if (++spins > kEpSpinLimit) { atomicExch(err, 1); break; }
+      __nanosleep(200);
+    }
+  }
+  __syncwarp();
+  __threadfence_system();
+  if (lane == 0) { sync[0] = 0; sync[1] = epoch; }
+}
+// all-gather by stores: this rank's R rows and R * k routing indices into slot `rank` of every window
+__global__ void __launch_bounds__(256) ep_push_kernel(EpPeers peers, int W, int rank, const bf16_t* x, const uint32_t* inds,
+                                                      int R, int H, int k, size_t off_x, size_t off_inds, size_t off_flags,
+                                                      int* sync, int* err) {
+  const int d = blockIdx.y;
+  const size_t nx = (size_t)R * H / 8;
+  uint4* dx = reinterpret_cast<uint4*>(peers.win[d] + off_x) + (size_t)rank * nx;
+  const uint4* sx = reinterpret_cast<const uint4*>(x);
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nx; i += (size_t)gridDim.x * blockDim.x) dx[i] = sx[i];
+  if (blockIdx.x == 0) {
+    uint32_t* di = reinterpret_cast<uint32_t*>(peers.win[d] + off_inds) + (size_t)rank * R * k;
+    for (int i = threadIdx.x; i < R * k; i += blockDim.x) di[i] = inds[i];
+  }
+  ep_signal_and_wait(peers, W, rank, off_flags, sync, err);
+}
+// the return: sorted row p of this rank is route perm[p] of the whole table = slot (route mod blk) of the
+// expert outputs of home rank (route / blk); the row goes straight to its place there
+__global__ void __launch_bounds__(256) ep_return_kernel(EpPeers peers, int W, int rank, const bf16_t* ret, const uint32_t* perm,
+                                                        const int* n_owned, int blk, int H, size_t off_ey, size_t off_flags,
+                                                        int* sync, int* err) {
+  const int n = *n_owned;
+  for (int p = blockIdx.x; p < n; p += gridDim.x) {
+    const int route = (int)perm[p];
+    const int d = route / blk, j = route - d * blk;
+    const uint4* src = reinterpret_cast<const uint4*>(ret + (size_t)route * H);
+    uint4* dst = reinterpret_cast<uint4*>(peers.win[d] + off_ey) + (size_t)j * (H / 8);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+  }
+  ep_signal_and_wait(peers, W, rank, off_flags, sync, err);
+}
+
 }  // namespace
 
 // scratch for one shape (R, H, E, k, I, SI)
@@ -191,6 +264,11 @@ struct EpBufs {
   uint32_t *inds, *all_inds, *rhs_local, *lhs, *perm;
   int *seg, *seg1;
   void* gemm_scratch;
+  // the exchange over peer memory: all_x, all_inds and ey then live in this rank's window at these offsets
+  // (the same on every rank), flags = [2][world] call numbers (gather, return), sync = [2][2] local counters
+  bool p2p = false;
+  size_t off_x = 0, off_inds = 0, off_ey = 0, off_flags = 0;
+  int* sync = nullptr;
 };
 struct EpSet {
   EpBufs bufs{};
@@ -201,6 +279,11 @@ struct orn_ep : EpBufs {
   int rank = 0, world = 1;
   bool exact = false;  // routed experts through the row-invariant grouped mat-vec instead of the tensor cores
   ncclComm_t comm = nullptr;
+  // exchange windows (one per rank, mapped into every process of the group); null = NCCL exchanges
+  uint8_t* win = nullptr;
+  size_t win_bytes = 0, win_used = 0;
+  EpPeers peers{};
+  std::vector<void*> peer_maps;  // what cudaIpcOpenMemHandle returned, to close
   // One scratch set per shape a caller has used, kept until the group is destroyed: a caller may
   // have captured a call into a CUDA graph, whose kernel arguments are these addresses.
   std::map<std::array<size_t, 6>, EpSet> sets;
@@ -229,10 +312,31 @@ int ep_reserve(orn_ep* ep, int R, int H, int E, int k, int I, int SI) {
   };
   A(&b.gates, (size_t)R * E); A(&b.probs, (size_t)R * E); A(&b.scores, (size_t)R * k); A(&b.inds, (size_t)R * k);
   A(&b.sg, (size_t)R * SI); A(&b.su, (size_t)R * SI); A(&b.sact, (size_t)R * SI); A(&b.sy, (size_t)R * H); A(&b.gs, (size_t)R);
-  A(&b.all_inds, routes); A(&b.all_x, G * H); A(&b.rhs_local, routes); A(&b.lhs, routes); A(&b.perm, routes);
+  // the exchanged buffers: in this rank's window when the group has one (the same offsets on every rank:
+  // all ranks reserve the same shapes in the same order, as the collectives they replace already require)
+  auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t need_win = up256(G * H * sizeof(bf16_t)) + up256(routes * sizeof(uint32_t)) + up256((size_t)R * k * H * sizeof(bf16_t)) + 256;
+  b.p2p = ep->win != nullptr && ep->win_used + need_win <= ep->win_bytes;
+  if (b.p2p) {
+    size_t o = ep->win_used;
+    b.off_x = o; o += up256(G * H * sizeof(bf16_t));
+    b.off_inds = o; o += up256(routes * sizeof(uint32_t));
+    b.off_ey = o; o += up256((size_t)R * k * H * sizeof(bf16_t));
+    b.off_flags = o; o += 256;   // [2][world <= 8] ints, zero since the window was made
+    ep->win_used = o;
+    b.all_x = reinterpret_cast<bf16_t*>(ep->win + b.off_x);
+    b.all_inds = reinterpret_cast<uint32_t*>(ep->win + b.off_inds);
+    b.ey = reinterpret_cast<bf16_t*>(ep->win + b.off_ey);
+    A(&b.sync, (size_t)4);
+    if (rc == ORN_OK) rc = cudaMemset(b.sync, 0, 4 * sizeof(int)) == cudaSuccess ? ORN_OK : ORN_ERR_CUDA;
+  } else {
+    A(&b.all_inds, routes); A(&b.all_x, G * H); A(&b.ey, (size_t)R * k * H);
+  }
+  A(&b.rhs_local, routes); A(&b.lhs, routes); A(&b.perm, routes);
   A(&b.seg, 2 * el + 4); A(&b.seg1, (size_t)2);
   A(&b.xs, routes * H); A(&b.eg, routes * I); A(&b.eu, routes * I); A(&b.eact, routes * I);
-  A(&b.ret_send, routes * H); A(&b.ret_recv, routes * H); A(&b.ey, (size_t)R * k * H);
+  A(&b.ret_send, routes * H);
+  if (!b.p2p) A(&b.ret_recv, routes * H);
   if (rc == ORN_OK) {
     const size_t big = std::max(qgemm_scratch_bytes((int)routes, (int)el, H), qgemm_scratch_bytes((int)routes, (int)el, I));
     rc = orn_alloc(ctx, big, &b.gemm_scratch);
@@ -252,6 +356,53 @@ int ep_reserve(orn_ep* ep, int R, int H, int E, int k, int I, int SI) {
   static_cast<EpBufs&>(*ep) = set.bufs;
   ep->sets.emplace(key, std::move(set));
   return ORN_OK;
+}
+
+// One window per rank, zeroed, its IPC handle gathered over NCCL, every peer's window mapped here.  Every
+// rank takes part in the gathers whatever happened to it before, and the group uses the windows only if
+// every rank mapped all of them (a flag gathered the same way), so the ranks always agree.
+constexpr size_t kEpWindowBytes = (size_t)96 << 20;
+void ep_map_windows(orn_ep* ep, NcclApi* api) {
+  orn_ctx* ctx = ep->ctx;
+  const int W = ep->world;
+  struct Slot { cudaIpcMemHandle_t h; int ok; int pad[15]; };
+  static_assert(sizeof(Slot) == 128, "one gathered slot");
+  Slot mine{};
+  uint8_t* win = nullptr;
+  mine.ok = cudaMalloc((void**)&win, kEpWindowBytes) == cudaSuccess && cudaMemset(win, 0, kEpWindowBytes) == cudaSuccess &&
+            cudaDeviceSynchronize() == cudaSuccess && cudaIpcGetMemHandle(&mine.h, win) == cudaSuccess;
+  Slot* dev = nullptr;
+  std::vector<Slot> all(W);
+  bool gathered = cudaMalloc((void**)&dev, sizeof(Slot) * (W + 1)) == cudaSuccess;
+  auto gather = [&]() {  // mine -> all, over NCCL on the context's stream
+    if (!gathered) return false;
+    if (cudaMemcpyAsync(dev + W, &mine, sizeof mine, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) return false;
+    if (api->AllGather(dev + W, dev, sizeof(Slot), ncclChar, ep->comm, ctx->stream) != ncclSuccess) return false;
+    if (cudaMemcpyAsync(all.data(), dev, sizeof(Slot) * W, cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess) return false;
+    return cudaStreamSynchronize(ctx->stream) == cudaSuccess;
+  };
+  bool ok = gather();
+  for (int r = 0; ok && r < W; ++r) ok = all[r].ok != 0;
+  std::vector<void*> maps;
+  EpPeers peers{};
+  for (int r = 0; ok && r < W; ++r) {
+    if (r == ep->rank) { peers.win[r] = win; continue; }
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, all[r].h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { ok = false; cudaGetLastError(); break; }
+    maps.push_back(p);
+    peers.win[r] = static_cast<uint8_t*>(p);
+  }
+  mine.ok = ok ? 1 : 0;   // second round: did everybody map everything?
+  bool all_ok = gather();
+  for (int r = 0; all_ok && r < W; ++r) all_ok = all[r].ok != 0;
+  if (dev) cudaFree(dev);
+  if (all_ok) {
+    ep->win = win; ep->win_bytes = kEpWindowBytes; ep->win_used = 0; ep->peers = peers; ep->peer_maps = maps;
+    return;
+  }
+  for (void* p : maps) cudaIpcCloseMemHandle(p);
+  if (win) cudaFree(win);
+  cudaGetLastError();
 }
 
 #define EP_NCCL(ctx, api, call)                                                              \
@@ -298,6 +449,9 @@ int32_t orn_ep_init(orn_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
       delete ep;
       ORN_FAIL(ctx, ORN_ERR_CUDA, std::string("ncclCommInitRank: ") + api->GetErrorString(r));
     }
+    // exchange windows over peer memory; on any failure the group keeps NCCL for its exchanges
+    const char* force = getenv("ORN_EP_NCCL");
+    if (world <= kEpMaxPeers && !(force && force[0] == '1')) ep_map_windows(ep, api);
   }
   *out = ep;
   return ORN_OK;
@@ -305,6 +459,7 @@ int32_t orn_ep_init(orn_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
 
 int32_t orn_ep_world(const orn_ep* ep) { return ep ? ep->world : 0; }
 int32_t orn_ep_rank(const orn_ep* ep) { return ep ? ep->rank : -1; }
+int32_t orn_ep_peer_windows(const orn_ep* ep) { return ep && ep->win != nullptr ? 1 : 0; }
 
 int32_t orn_ep_destroy(orn_ep* ep) {
   if (!ep) return ORN_OK;
@@ -315,6 +470,10 @@ int32_t orn_ep_destroy(orn_ep* ep) {
   }
   for (auto& kv : ep->sets)
     for (void* p : kv.second.allocs) cudaFree(p);
+  // every rank leaves its peers' windows before anybody frees one: the caller destroys the groups of
+  // all ranks together, and a window is only stored to inside a block call
+  for (void* p : ep->peer_maps) cudaIpcCloseMemHandle(p);
+  if (ep->win) cudaFree(ep->win);
   delete ep;
   return ORN_OK;
 }
@@ -354,7 +513,13 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
   // ---- every rank learns the whole routing table and the rows
   const uint32_t* all_inds = inds;
   const bf16_t* all_x = dev_x;
-  if (W > 1) {
+  if (W > 1 && ep->p2p) {
+    ep_push_kernel<<<dim3(4, W), 256, 0, s>>>(ep->peers, W, ep->rank, dev_x, inds, R, H, k, ep->off_x, ep->off_inds, ep->off_flags,
+                                             ep->sync, ctx->dev_err);
+    EPCK(orn_launch_check(ctx, "ep_push"));
+    all_inds = ep->all_inds;
+    all_x = ep->all_x;
+  } else if (W > 1) {
     EP_NCCL(ctx, api, api->GroupStart());
     EP_NCCL(ctx, api, api->AllGather(inds, ep->all_inds, (size_t)R * k, ncclUint32, ep->comm, s));
     EP_NCCL(ctx, api, api->AllGather(dev_x, ep->all_x, (size_t)R * H, ncclBfloat16, ep->comm, s));
@@ -427,7 +592,11 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
     EPCK(f_qgemm(ctx, s, sw_down, ep->eact, routes, ret, H, &back, ep->gemm_scratch));
   }
   // ---- the return: one fixed-size block per pair of ranks
-  if (W > 1) {
+  if (W > 1 && ep->p2p) {
+    ep_return_kernel<<<std::min(routes, 2 * ctx->sm_count), 256, 0, s>>>(ep->peers, W, ep->rank, ep->ret_send, ep->perm, n_owned, blk, H,
+                                                                         ep->off_ey, ep->off_flags + 32, ep->sync + 2, ctx->dev_err);
+    EPCK(orn_launch_check(ctx, "ep_return"));
+  } else if (W > 1) {
     const size_t n = (size_t)blk * H;
     EP_NCCL(ctx, api, api->GroupStart());
     for (int d = 0; d < W; ++d) {

@@ -291,9 +291,10 @@ def shard_experts(ctx, lin, rank, world):
 # --------------------------------------------------------------------------- the library's block
 class LibEp:
     """orn_ep: the expert-parallel block inside the library (csrc/ep.cu).  The plan is derived on
-    the device from the all-gathered routing table, the collectives are NCCL calls the library
-    enqueues on the context's stream, the expert owner runs the grouped mat-vec: no torch in the
-    data path and no host read inside the block.  exact=True runs the routed experts through the
+    the device from the gathered routing table, the two exchanges per layer are the library's own
+    kernels over peer memory (`peer_windows` tells; NCCL collectives otherwise), enqueued on the
+    context's stream, the expert owner runs the grouped product: no torch in the data path and no
+    host read inside the block.  exact=True runs the routed experts through the
     row-invariant grouped mat-vec (bit-identical to the single-GPU block) instead of the grouped
     tensor-core product (identical routing, rows equal to rounding).  `uid` is the 128-byte id rank 0 got from
     `LibEp.unique_id(lib)` and the caller carried to the other ranks; a world of one needs none."""
@@ -310,6 +311,7 @@ class LibEp:
             buf = (C.c_uint8 * 128).from_buffer_copy(bytes(uid))
         ctx.check(ctx._lib.orn_ep_init(ctx.h, buf, rank, world, 1 if exact else 0, C.byref(h)), "orn_ep_init")
         self.h = h
+        self.peer_windows = bool(ctx._lib.orn_ep_peer_windows(h))
 
     @staticmethod
     def unique_id(lib):

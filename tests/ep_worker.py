@@ -34,6 +34,8 @@ def batch_main(out, seed):
     box = [ep.LibEp.unique_id(ctx._lib) if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
     group = ep.LibEp(ctx, rank, world, box[0], exact=True)
+    # the exchanges run over peer memory unless the environment asks for NCCL
+    assert group.peer_windows == (os.environ.get("ORN_EP_NCCL") != "1"), "exchange windows were not mapped"
     cfg = hp.tiny_config(pkg.Config)
     gm = hp.upload_model(pkg, ctx, cfg, hp.tiny_model_weights(cfg, seed=seed))
     rng = np.random.default_rng(100 + rank)

@@ -156,18 +156,21 @@ def test_library_block_two_gpus_equal_the_single_device_block(tmp_path):
         assert np.array_equal(np.load("%s.%d.npy" % (out, r)), want)
 
 
-def test_batched_mtp_decode_over_two_gpus_equals_the_single_sequence_engine(tmp_path):
+@pytest.mark.parametrize("exchange", ["peer memory", "nccl"])
+def test_batched_mtp_decode_over_two_gpus_equals_the_single_sequence_engine(tmp_path, exchange):
     """Whole-model batched decode with the experts of every layer (and of the MTP head) split over two
     ranks: each rank's sequences, stepped through prompt windows and MTP depth-1 cycles with the
     expert-parallel block, reproduce the single-sequence engine bit for bit (the worker compares
-    drafts, targets and hidden rows and exits non-zero on any difference)."""
+    drafts, targets and hidden rows and exits non-zero on any difference).  Once with the library's own
+    exchange kernels over peer memory (the worker asserts that the windows were mapped), once with the
+    NCCL collectives they replace."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     port, out = _free_port(), str(tmp_path / "ok")
     procs = []
     for rank in range(2):
         env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
-                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", ORN_EP_NCCL="1" if exchange == "nccl" else "0")
         procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "ep_worker.py"), "batch", out, "31"], env=env))
     for p in procs:
         assert p.wait(timeout=600) == 0
