@@ -127,7 +127,7 @@ int32_t orn_sync(orn_ctx* ctx) {
   ORN_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   if (flag != 0) {
     cudaMemsetAsync(ctx->dev_err, 0, sizeof(int), ctx->stream);
-    ORN_FAIL(ctx, ORN_ERR_TIMEOUT, "a kernel gave up waiting for its own asynchronous copies");
+    ORN_FAIL(ctx, ORN_ERR_TIMEOUT, "a kernel gave up waiting (for its own asynchronous copies, or for a peer of an expert-parallel group)");
   }
   return ORN_OK;
 }
