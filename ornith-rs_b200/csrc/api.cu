@@ -115,6 +115,9 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
   cudaFree(ctx->attn_partial);
   cudaFree(ctx->attn_arrivals);
   cudaFree(ctx->split_arrivals);
+  if (ctx->side) cudaStreamDestroy(ctx->side);
+  if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+  if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return ORN_OK;

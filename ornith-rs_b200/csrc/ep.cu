@@ -405,6 +405,29 @@ void ep_map_windows(orn_ep* ep, NcclApi* api) {
   cudaGetLastError();
 }
 
+// the context's side stream and its two events, made on first use (never inside a capture: the first call
+// of a block shape is always eager); false when they cannot be had or ORN_EP_SERIAL=1 asks for one stream
+bool ep_side_stream(orn_ctx* ctx) {
+  static int serial = -1;
+  if (serial < 0) { const char* e = getenv("ORN_EP_SERIAL"); serial = (e && e[0] == '1') ? 1 : 0; }
+  if (serial) return false;
+  if (ctx->side != nullptr) return true;
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(ctx->stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return false;
+  cudaStream_t side = nullptr;
+  cudaEvent_t a = nullptr, b = nullptr;
+  if (cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess) {
+    if (side) cudaStreamDestroy(side);
+    if (a) cudaEventDestroy(a);
+    cudaGetLastError();
+    return false;
+  }
+  ctx->side = side; ctx->ev_fork = a; ctx->ev_join = b;
+  return true;
+}
+
 #define EP_NCCL(ctx, api, call)                                                              \
   do {                                                                                       \
     ncclResult_t r__ = (call);                                                               \
@@ -528,17 +551,26 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
     all_inds = ep->all_inds;
     all_x = ep->all_x;
   }
-  // the shared expert does not depend on the exchange: it runs while the gathered table lands
+  // The shared expert depends on the block's input only: on the tensor-core path its three launches run on
+  // the context's side stream beside the routed chain (forked here, joined before the combine; inside a
+  // captured step the two become parallel branches of the graph).  With few rows per rank every kernel of
+  // the block is a short latency chain and the SMs are mostly idle, so the two chains overlap.
+  const bool side = !ep->exact && ctx->kt == nullptr && ep_side_stream(ctx);
+  cudaStream_t ss = side ? ctx->side : s;
+  if (side) {
+    ORN_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev_fork, s));
+    ORN_CHECK_CUDA(ctx, cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+  }
   const bool wide_shared = !ep->exact && R >= 16 && H % 64 == 0 && SI % 64 == 0;
   if (wide_shared) {  // like the routed experts: one dense contraction per matrix over all R rows
     if (sh_gate->kind == sh_up->kind && sh_gate->K == sh_up->K) {  // one launch for both (a row's bits do not depend on the tile shape)
       const orn_linear* pl[2] = {sh_gate, sh_up};
       void* py[2] = {ep->sg, ep->su};
       const int ld[2] = {SI, SI};
-      EPCK(f_qgemm_multi(ctx, s, pl, py, ld, 2, dev_x, R));
+      EPCK(f_qgemm_multi(ctx, ss, pl, py, ld, 2, dev_x, R));
     } else {
-      EPCK(f_qgemm(ctx, s, sh_gate, dev_x, R, ep->sg, SI, nullptr, nullptr));
-      EPCK(f_qgemm(ctx, s, sh_up, dev_x, R, ep->su, SI, nullptr, nullptr));
+      EPCK(f_qgemm(ctx, ss, sh_gate, dev_x, R, ep->sg, SI, nullptr, nullptr));
+      EPCK(f_qgemm(ctx, ss, sh_up, dev_x, R, ep->su, SI, nullptr, nullptr));
     }
   } else {
     EPCK(k_grouped_gemv(ctx, s, sh_gate, dev_x, ep->seg1, ep->sg, nullptr, R));
@@ -546,12 +578,13 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
   }
   // the shared expert's SwiGLU and down projection: with the routed experts' (one launch for both SwiGLUs)
   // on the tensor-core path, right here otherwise
-  const bool joint_swiglu = !ep->exact;
+  const bool joint_swiglu = !ep->exact && !side;
   if (!joint_swiglu) {
-    EPCK(k_swiglu(ctx, s, ep->sg, ep->su, R * SI, ep->sact));
-    if (wide_shared) EPCK(f_qgemm(ctx, s, sh_down, ep->sact, R, ep->sy, H, nullptr, nullptr));
-    else EPCK(k_grouped_gemv(ctx, s, sh_down, ep->sact, ep->seg1, ep->sy, nullptr, R));
+    EPCK(k_swiglu(ctx, ss, ep->sg, ep->su, R * SI, ep->sact));
+    if (wide_shared) EPCK(f_qgemm(ctx, ss, sh_down, ep->sact, R, ep->sy, H, nullptr, nullptr));
+    else EPCK(k_grouped_gemv(ctx, ss, sh_down, ep->sact, ep->seg1, ep->sy, nullptr, R));
   }
+  if (side) ORN_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev_join, ctx->side));
   // ---- owner: this rank's routes, sorted by expert
   if (el <= kRouteMaxLocal && routes <= kRouteMaxRoutes) {
     ep_route_kernel<<<1, 1024, 0, s>>>(all_inds, routes, ep->rank * el, el, ep->seg, ep->perm);
@@ -586,9 +619,14 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
       EPCK(f_qgemm(ctx, s, sw_gate, ep->xs, routes, ep->eg, I, &sorted, ep->gemm_scratch));
       EPCK(f_qgemm(ctx, s, sw_up, ep->xs, routes, ep->eu, I, &sorted, ep->gemm_scratch));
     }
-    EPCK(k_swiglu2(ctx, s, ep->sg, ep->su, (size_t)R * SI, ep->sact, ep->eg, ep->eu, n_owned, I, ep->eact));
-    if (wide_shared) EPCK(f_qgemm(ctx, s, sh_down, ep->sact, R, ep->sy, H, nullptr, nullptr));
-    else EPCK(k_grouped_gemv(ctx, s, sh_down, ep->sact, ep->seg1, ep->sy, nullptr, R));
+    if (joint_swiglu) {
+      EPCK(k_swiglu2(ctx, s, ep->sg, ep->su, (size_t)R * SI, ep->sact, ep->eg, ep->eu, n_owned, I, ep->eact));
+      if (wide_shared) EPCK(f_qgemm(ctx, s, sh_down, ep->sact, R, ep->sy, H, nullptr, nullptr));
+      else EPCK(k_grouped_gemv(ctx, s, sh_down, ep->sact, ep->seg1, ep->sy, nullptr, R));
+    } else {
+      ep_swiglu_kernel<<<ctx->sm_count * 4, 256, 0, s>>>(ep->eg, ep->eu, n_owned, I, ep->eact);
+      EPCK(orn_launch_check(ctx, "ep_swiglu"));
+    }
     EPCK(f_qgemm(ctx, s, sw_down, ep->eact, routes, ret, H, &back, ep->gemm_scratch));
   }
   // ---- the return: one fixed-size block per pair of ranks
@@ -609,6 +647,7 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
     EPCK(orn_launch_check(ctx, "ep_select"));
   }
   // ---- home: combine in the reference's order
+  if (side) ORN_CHECK_CUDA(ctx, cudaStreamWaitEvent(s, ctx->ev_join, 0));
   EPCK(k_moe_combine(ctx, s, ep->scores, ep->ey, ep->gs, ep->sy, R, k, H, norm_topk, dev_out));
 #undef EPCK
   return ORN_OK;

@@ -17,6 +17,10 @@
 struct orn_ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
+  // a second stream for work that does not depend on the main chain (the shared expert beside the routed
+  // experts of an expert-parallel block): forked and joined with the two events, also inside a capture
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   std::string err;
   int64_t launches = 0;  // kernels launched through this context
   int sm_count = 148;
