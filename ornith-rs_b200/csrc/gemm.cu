@@ -867,7 +867,9 @@ int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, voi
   P.splits = 1; P.partial = nullptr; P.arrivals = nullptr;
   if (grp == nullptr && rows <= kSplitMaxRows && L->K / BK >= 8) {
     const int tiles = P.f_tiles * ((rows + P.NT * BN - 1) / (P.NT * BN));
-    int sp = std::max(1, ctx->sm_count / tiles);                  // one round of items over the SMs
+    // one round of items over the SMs, two CTAs on each where the tiles alone would leave SMs idle
+    // (97 tiles of an input projection: three splits instead of none)
+    int sp = std::max(1, (tiles > ctx->sm_count / 2 ? 2 * ctx->sm_count : ctx->sm_count) / tiles);
     sp = std::min(sp, std::min(8, L->K / BK / 4));               // at least 4 K blocks per item
     if (sp > 1) {                                                 // no split may be empty
       const int KBn = L->K / BK, per = (KBn + sp - 1) / sp;
