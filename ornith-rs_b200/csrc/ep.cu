@@ -96,15 +96,15 @@ __global__ void ep_map_kernel(const uint32_t* all_inds, int routes, int base, in
 // ep_map + counting sort of the routes in one launch of one CTA (a decode batch has a few thousand routes
 // at most): seg[e] = first sorted position of local expert e, seg[e_local] = routes this rank owns,
 // perm[p] = route at sorted position p; inside an expert the routes keep their order (counting_sort,
-// src/ops/moe.rs:463-508).  Rounds of 1024 routes: a warp counts its 32 routes per expert, a scan over
+// src/ops/moe.rs:463-508).  Passes of 1024 routes: a warp counts its 32 routes per expert, a scan over
 // the warps gives every warp its offset inside the expert, the rank inside the warp is a match mask.
 constexpr int kRouteMaxLocal = 256;   // local experts the one-launch form handles
 constexpr int kRouteMaxRoutes = 8192;
 __global__ void __launch_bounds__(1024) ep_route_kernel(const uint32_t* all_inds, int routes, int base, int e_local,
                                                         int* seg /*[e_local + 1]*/, uint32_t* perm) {
   __shared__ int s_seg[kRouteMaxLocal + 1];          // exclusive scan of the counts
-  __shared__ int s_done[kRouteMaxLocal];             // routes of the expert placed by earlier rounds
-  __shared__ uint16_t s_cnt[32][kRouteMaxLocal];     // this round: routes per (warp, expert), then the warp's offset
+  __shared__ int s_done[kRouteMaxLocal];             // routes of the expert placed by earlier passes
+  __shared__ uint16_t s_cnt[32][kRouteMaxLocal];     // this pass of 1024 routes: routes per (warp, expert), then the warp's offset
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   auto local = [&](int i) {
     const int e = i < routes ? (int)all_inds[i] - base : -1;
