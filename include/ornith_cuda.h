@@ -101,6 +101,11 @@ int32_t orn_ctx_ktime_end(orn_ctx* ctx, char* host_buf, size_t nbytes);
  * give-up path runs with nothing in flight; the following orn_sync returns ORN_ERR_TIMEOUT once and
  * the context stays usable. */
 int32_t orn_debug_wait_probe(orn_ctx* ctx, uint32_t rounds);
+/* the same for the expert-parallel exchange over peer memory: the gather kernel of a group of two, run
+ * against a window of this process in which nobody plays the second rank; it raises its own flag, waits
+ * a few seconds for the peer's, gives up, and the following orn_sync returns ORN_ERR_TIMEOUT once.
+ * One GPU, one process, no peer. */
+int32_t orn_debug_ep_wait_probe(orn_ctx* ctx);
 
 /* device-side stopwatch on the context's stream (CUDA events; the reference's
  * ORNITH_PROF GPUStart/GPUEnd sums, src/metal/mod.rs:197-284) */

@@ -101,6 +101,7 @@ SIGNATURES = {
     "orn_ep_world": (i32, [vp]),
     "orn_ep_rank": (i32, [vp]),
     "orn_ep_peer_windows": (i32, [vp]),
+    "orn_debug_ep_wait_probe": (i32, [vp]),
     "orn_batch_create": (i32, [vp, i32, i32, i32, i32, c_void_pp]),
     "orn_batch_destroy": (i32, [vp]),
     "orn_batch_reset": (i32, [vp]),

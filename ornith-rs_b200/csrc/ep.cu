@@ -192,7 +192,7 @@ __global__ void ep_select_kernel(const bf16_t* recv, const uint32_t* inds, int e
 
 // ---- the exchange over peer memory ---------------------------------------------------------------
 constexpr int kEpMaxPeers = 8;
-constexpr unsigned kEpSpinLimit = 1u << 22;  // polls of 200 ns: about a second, then the error flag
+constexpr unsigned kEpSpinLimit = 1u << 22;  // polls with a 200 ns sleep between them: a few seconds, then the error flag
 struct EpPeers {
   uint8_t* win[kEpMaxPeers];  // exchange window of every rank, as mapped into this process
 };
@@ -478,6 +478,27 @@ int32_t orn_ep_init(orn_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
   }
   *out = ep;
   return ORN_OK;
+}
+
+int32_t orn_debug_ep_wait_probe(orn_ctx* ctx) {
+  if (!ctx) return ORN_ERR_ARG;
+  // a window in which rank 0's flag gets written and rank 1's never does; no rows to move
+  uint8_t* win = nullptr;
+  int* sync = nullptr;
+  ORN_CHECK_CUDA(ctx, cudaMalloc((void**)&win, 4096));
+  if (cudaMalloc((void**)&sync, 4 * sizeof(int)) != cudaSuccess) { cudaFree(win); ORN_FAIL(ctx, ORN_ERR_ALLOC, "ep wait probe: out of memory"); }
+  cudaMemsetAsync(win, 0, 4096, ctx->stream);
+  cudaMemsetAsync(sync, 0, 4 * sizeof(int), ctx->stream);
+  EpPeers peers{};
+  peers.win[0] = win; peers.win[1] = win;
+  ep_push_kernel<<<dim3(1, 2), 256, 0, ctx->stream>>>(peers, 2, 0, reinterpret_cast<const bf16_t*>(win),
+                                                      reinterpret_cast<const uint32_t*>(win), 0, 8, 1, 1024, 2048, 3072, sync,
+                                                      ctx->dev_err);
+  int rc = orn_launch_check(ctx, "ep_push");
+  cudaStreamSynchronize(ctx->stream);   // the kernel has given up by now; the error flag stays for orn_sync
+  cudaFree(win);
+  cudaFree(sync);
+  return rc;
 }
 
 int32_t orn_ep_world(const orn_ep* ep) { return ep ? ep->world : 0; }

@@ -172,6 +172,27 @@ def test_bounded_wait_gives_up_and_the_context_survives(pkg, ctx):
     L.free()
 
 
+def test_exchange_wait_for_a_peer_gives_up_and_the_context_survives(pkg, ctx):
+    """The expert-parallel exchange over peer memory waits for its peers' flags with a limit: the gather
+    kernel of a group of two, with nobody playing the second rank, gives up after a few seconds, the
+    status is ORN_ERR_TIMEOUT once, and the context works afterwards.  No peer, no fault, no hang."""
+    import time
+    lib = ctx._lib
+    ctx.sync()
+    t0 = time.time()
+    assert lib.orn_debug_ep_wait_probe(ctx.h) == 0
+    assert time.time() - t0 < 10.0
+    assert lib.orn_sync(ctx.h) == -4  # ORN_ERR_TIMEOUT
+    assert b"gave up waiting" in lib.orn_last_error(ctx.h)
+    assert lib.orn_sync(ctx.h) == 0
+    rng = np.random.default_rng(6)
+    W = hp.make_weights(rng, orc.A8, 1, 64, 256)
+    x = hp.f32_to_bf16(rng.standard_normal((1, 256)).astype(np.float32))
+    L = pkg.Linear.from_numpy(ctx, W.kind, W.w, W.s, W.b, E=1, O=64, K=256)
+    assert np.array_equal(L.matmul(ctx.upload(x), 1).numpy(), orc.gemv(W, x, 1))
+    L.free()
+
+
 def test_frspec_can_be_replaced_after_decoding(pkg, ctx, full4):
     """A second id list after graphs were captured: the cycle graph that drafted through the old
     pruned head is dropped and captured again (its arguments would point at freed memory)."""
