@@ -111,6 +111,8 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
   if (ctx->t0) cudaEventDestroy(ctx->t0);
   if (ctx->t1) cudaEventDestroy(ctx->t1);
   cudaFree(ctx->dev_err);
+  cudaFree(ctx->split_partial_side);
+  cudaFree(ctx->split_arrivals_side);
   cudaFree(ctx->split_partial);
   cudaFree(ctx->attn_partial);
   cudaFree(ctx->attn_arrivals);
@@ -122,6 +124,31 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
   delete ctx;
   return ORN_OK;
 }
+
+}  // extern "C"
+
+bool orn_side_stream(orn_ctx* ctx) {
+  static int one = -1;
+  if (one < 0) { const char* e = getenv("ORN_NO_SIDE_STREAM"); one = (e && e[0] == '1') ? 1 : 0; }
+  if (one || ctx->kt != nullptr) return false;
+  if (ctx->side != nullptr) return true;
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(ctx->stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return false;
+  cudaStream_t side = nullptr;
+  cudaEvent_t a = nullptr, b = nullptr;
+  if (cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess) {
+    if (side) cudaStreamDestroy(side);
+    if (a) cudaEventDestroy(a);
+    cudaGetLastError();
+    return false;
+  }
+  ctx->side = side; ctx->ev_fork = a; ctx->ev_join = b;
+  return true;
+}
+
+extern "C" {
 
 int32_t orn_sync(orn_ctx* ctx) {
   if (!ctx) return ORN_ERR_ARG;

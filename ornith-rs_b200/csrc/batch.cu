@@ -356,19 +356,33 @@ int batch_mm_multi(orn_batch* bt, const orn_linear* const* Ls, bf16_t* const* ys
     for (int i = 0; i < n; ++i) CK(batch_mm(bt, Ls[i], x, R, ys[i]));
     return ORN_OK;
   }
+  // the first group of matrices on the main stream, the others beside it on the side stream (a small
+  // projection of another format next to the big one is a launch of a few CTAs that would otherwise wait
+  // its turn); the side stream's products have their own split-K scratch
+  bool forked = false;
   int i = 0;
   while (i < n) {
     int j = i + 1;
     while (j < n && j - i < 4 && Ls[j]->kind == Ls[i]->kind && Ls[j]->K == Ls[i]->K && Ls[i]->K % 64 == 0) ++j;
-    if (j - i == 1) {
-      CK(batch_mm(bt, Ls[i], x, R, ys[i]));
-    } else {
-      void* yv[4];
-      int ld[4];
-      for (int k = i; k < j; ++k) { yv[k - i] = ys[k]; ld[k - i] = Ls[k]->O; }
-      CK(f_qgemm_multi(ctx, ctx->stream, Ls + i, yv, ld, j - i, x, R));
+    cudaStream_t st = ctx->stream;
+    if (i > 0 && Ls[i]->K % 64 == 0 && orn_side_stream(ctx)) {
+      if (!forked) {
+        ORN_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev_fork, ctx->stream));
+        ORN_CHECK_CUDA(ctx, cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+        forked = true;
+      }
+      st = ctx->side;
     }
+    void* yv[4];
+    int ld[4];
+    for (int k = i; k < j; ++k) { yv[k - i] = ys[k]; ld[k - i] = Ls[k]->O; }
+    if (Ls[i]->K % 64 == 0) CK(f_qgemm_multi(ctx, st, Ls + i, yv, ld, j - i, x, R));
+    else for (int k = i; k < j; ++k) CK(batch_mm(bt, Ls[k], x, R, ys[k]));
     i = j;
+  }
+  if (forked) {
+    ORN_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev_join, ctx->side));
+    ORN_CHECK_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
   }
   return ORN_OK;
 }

@@ -405,29 +405,6 @@ void ep_map_windows(orn_ep* ep, NcclApi* api) {
   cudaGetLastError();
 }
 
-// the context's side stream and its two events, made on first use (never inside a capture: the first call
-// of a block shape is always eager); false when they cannot be had or ORN_EP_SERIAL=1 asks for one stream
-bool ep_side_stream(orn_ctx* ctx) {
-  static int serial = -1;
-  if (serial < 0) { const char* e = getenv("ORN_EP_SERIAL"); serial = (e && e[0] == '1') ? 1 : 0; }
-  if (serial) return false;
-  if (ctx->side != nullptr) return true;
-  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(ctx->stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) return false;
-  cudaStream_t side = nullptr;
-  cudaEvent_t a = nullptr, b = nullptr;
-  if (cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess ||
-      cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess ||
-      cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess) {
-    if (side) cudaStreamDestroy(side);
-    if (a) cudaEventDestroy(a);
-    cudaGetLastError();
-    return false;
-  }
-  ctx->side = side; ctx->ev_fork = a; ctx->ev_join = b;
-  return true;
-}
-
 #define EP_NCCL(ctx, api, call)                                                              \
   do {                                                                                       \
     ncclResult_t r__ = (call);                                                               \
@@ -576,7 +553,7 @@ int32_t orn_ep_moe_block(orn_ep* ep, const orn_linear* gate, const orn_linear* s
   // the context's side stream beside the routed chain (forked here, joined before the combine; inside a
   // captured step the two become parallel branches of the graph).  With few rows per rank every kernel of
   // the block is a short latency chain and the SMs are mostly idle, so the two chains overlap.
-  const bool side = !ep->exact && ctx->kt == nullptr && ep_side_stream(ctx);
+  const bool side = !ep->exact && orn_side_stream(ctx);
   cudaStream_t ss = side ? ctx->side : s;
   if (side) {
     ORN_CHECK_CUDA(ctx, cudaEventRecord(ctx->ev_fork, s));

@@ -878,12 +878,16 @@ int f_qgemm_multi(orn_ctx* ctx, cudaStream_t s, const orn_linear* const* Ls, voi
     const int groups = (rows + P.NT * BN - 1) / (P.NT * BN);
     const size_t need = (size_t)P.f_tiles * groups * sp * (size_t)(P.NT * BN) * BM * sizeof(float);
     if (sp > 1 && need <= kSplitPartialBytes && (size_t)P.f_tiles * groups <= kSplitTiles) {
-      if (ctx->split_partial == nullptr) {
-        ORN_CHECK_CUDA(ctx, cudaMalloc((void**)&ctx->split_partial, kSplitPartialBytes));
-        ORN_CHECK_CUDA(ctx, cudaMalloc((void**)&ctx->split_arrivals, kSplitTiles * sizeof(int)));
-        ORN_CHECK_CUDA(ctx, cudaMemset(ctx->split_arrivals, 0, kSplitTiles * sizeof(int)));
+      // products on the side stream run beside products on the main one: a scratch of their own
+      const bool on_side = ctx->side != nullptr && s == ctx->side;
+      float*& partial = on_side ? ctx->split_partial_side : ctx->split_partial;
+      int*& arrivals = on_side ? ctx->split_arrivals_side : ctx->split_arrivals;
+      if (partial == nullptr) {
+        ORN_CHECK_CUDA(ctx, cudaMalloc((void**)&partial, kSplitPartialBytes));
+        ORN_CHECK_CUDA(ctx, cudaMalloc((void**)&arrivals, kSplitTiles * sizeof(int)));
+        ORN_CHECK_CUDA(ctx, cudaMemset(arrivals, 0, kSplitTiles * sizeof(int)));
       }
-      P.splits = sp; P.partial = ctx->split_partial; P.arrivals = ctx->split_arrivals;
+      P.splits = sp; P.partial = partial; P.arrivals = arrivals;
     }
   }
   // A launch of narrow items with more items than SMs runs two CTAs per SM (each with half the

@@ -41,6 +41,8 @@ struct orn_ctx {
   int* attn_arrivals = nullptr;
   float* split_partial = nullptr;
   int* split_arrivals = nullptr;
+  float* split_partial_side = nullptr;  // the same for products launched on the side stream
+  int* split_arrivals_side = nullptr;
 };
 
 // Records an event after the launch just made and attributes the device time
@@ -111,6 +113,11 @@ static inline LinDev lin_dev(const orn_linear* l) {
     (ctx)->err = (msg);          \
     return (code);               \
   } while (0)
+
+// the context's side stream and its fork / join events, made on first use (never inside a capture); false
+// when they cannot be had, inside a capture that began before they existed, with per-kernel timing on, or
+// when ORN_NO_SIDE_STREAM=1 asks for one stream
+bool orn_side_stream(orn_ctx* ctx);
 
 static inline int orn_launch_check(orn_ctx* ctx, const char* what) {
   cudaError_t e = cudaGetLastError();
