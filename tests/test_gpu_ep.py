@@ -132,6 +132,11 @@ def test_library_block_world_of_one_equals_the_oracle(pkg, ctx, ep):
     y2 = group.moe_block(L, ctx.upload(x2), 37, k, 1)
     ctx.sync()
     assert np.array_equal(y2.numpy(), orc.moe_block(ws, x2, 37, k, 1)[0])
+    # more routes than one pass of the route kernel takes (1024): 1600 routes, sorted in two passes
+    x3 = eh.rows_of(23, 0, 200, H)
+    y3 = group.moe_block(L, ctx.upload(x3), 200, k, 1)
+    ctx.sync()
+    assert np.array_equal(y3.numpy(), orc.moe_block(ws, x3, 200, k, 1)[0])
     group.close()
     for l in L.values():
         l.free()
