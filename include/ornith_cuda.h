@@ -226,8 +226,11 @@ int32_t orn_moe_block(orn_ctx* ctx, const orn_linear* gate, const orn_linear* sw
 /* ---- expert parallelism over the GPUs of one node (no counterpart in the reference, which is
  * single-GPU, README.md:217-221; the block it distributes is sparse_moe_block, moe.rs:662-741,
  * and the owner's work is the sorted expert path, moe.rs:283-314,463-508).  Experts are split
- * evenly: expert e lives on rank e / (E / world).  One process per GPU; the collectives are NCCL
- * calls on the context's stream (libnccl.so.2 is resolved at run time; world == 1 needs none).
+ * evenly: expert e lives on rank e / (E / world).  One process per GPU; the two exchanges of a layer are
+ * the library's own kernels over peer memory (exchange windows mapped at orn_ep_init, flags with bounded
+ * waits) or, where the windows cannot be had, NCCL collectives on the context's stream (libnccl.so.2 is
+ * resolved at run time; world == 1 needs none).  All ranks call the block with the same shapes in the
+ * same order and destroy their groups together.
  * orn_ep_unique_id: rank 0 makes the 128-byte NCCL id, the caller carries it to the other ranks.
  * orn_ep_init: collective over all ranks.  orn_ep_moe_block: collective; R rows per rank (the same
  * R everywhere); gate, the shared expert and its gate are replicated, sw_* hold this rank's
