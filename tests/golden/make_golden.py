@@ -46,6 +46,17 @@ def main(ref_root):
         blocks_q=blocks_q, deq_q=deq_q, qs_q=qs_q, scales_q=scales_q, dm_q=dm_q.view(np.uint16),
         blocks_r=blocks_r, deq_r=deq_r, qs_r=qs_r, scales_r=scales_r, dm_r=dm_r.view(np.uint16))
 
+    # 2b. Q6_K artifact layout: raw 210-byte ggml blocks (ql 128, qh 64, scales 16, d 2) cut into the three
+    # tensors an artifact stores by the reference's own split (tools/q4k.py:75-96): ql|qh together, the
+    # int8 sub-block scales, one float16 d per block
+    rng6 = np.random.default_rng(20240608)   # a stream of its own: the other fixtures keep their values
+    blocks6 = rng6.integers(0, 256, (24 * 2, 210)).astype(np.uint8)
+    d6 = (np.abs(rng6.standard_normal(24 * 2)) * 1e-3).astype(np.float16)
+    blocks6[:, 208:210] = d6.view(np.uint8).reshape(-1, 2)
+    qs6, scales6, dm6 = q4k.split(blocks6, 24, 2, kind="q6_K")
+    np.savez_compressed(os.path.join(HERE, "q6k_golden.npz"), blocks=blocks6, qs=qs6, scales=scales6,
+                        dm=dm6.view(np.uint16))
+
     # 3. affine 8-bit group-64 quantise + pack
     wa = (rng.standard_normal((16, 256)) * 0.02).astype(np.float32)
     q, s, b = aq.quantize(wa, group_size=64, bits=8)

@@ -124,6 +124,33 @@ def test_bf16_rounding_matches_reference():
     assert hp.f32_to_bf16(np.array([1.01171875], np.float32))[0] == 0x3F82
 
 
+def test_q6k_artifact_layout_is_the_reference_split():
+    """Raw 210-byte Q6_K blocks cut into artifact tensors by the reference's own tools/q4k.py split
+    (fixture): ql|qh in one tensor, int8 sub-block scales, one float16 d per block.  The oracle reading
+    those tensors gives what ggml's published dequantize_row_q6_K gives on the raw blocks (ql at byte 0,
+    qh at 128, scales at 192, d at 208), restated here in numpy on the BLOCK form."""
+    g = np.load(os.path.join(G, "q6k_golden.npz"))
+    blocks = g["blocks"]                                    # [48, 210]
+    qs = np.ascontiguousarray(g["qs"]).view(np.uint8)       # [24, 2 * 192]
+    assert np.array_equal(qs.reshape(48, 192), blocks[:, :192])
+    assert np.array_equal(g["scales"].reshape(48, 16), blocks[:, 192:208])
+    assert np.array_equal(g["dm"].reshape(48), np.ascontiguousarray(blocks[:, 208:210]).view(np.uint16).reshape(48))
+    out = orc.q6k_dequantize(np.ascontiguousarray(qs), np.ascontiguousarray(g["scales"]).view(np.int8),
+                             np.ascontiguousarray(g["dm"]))
+    ql, qh = blocks[:, 0:128].astype(np.int32), blocks[:, 128:192].astype(np.int32)
+    sc = np.ascontiguousarray(blocks[:, 192:208]).view(np.int8).astype(np.float32)
+    d = np.ascontiguousarray(blocks[:, 208:210]).view(np.float16).astype(np.float32)[:, 0]
+    ref = np.zeros((48, 256), np.float32)
+    for n in range(2):            # the two 128-weight halves of a block
+        for l in range(32):
+            a, b_, h = ql[:, 64 * n + l], ql[:, 64 * n + l + 32], qh[:, 32 * n + l]
+            codes = ((a & 0xF) | ((h & 3) << 4), (b_ & 0xF) | (((h >> 2) & 3) << 4),
+                     (a >> 4) | (((h >> 4) & 3) << 4), (b_ >> 4) | (((h >> 6) & 3) << 4))
+            for c, q in enumerate(codes):
+                ref[:, 128 * n + 32 * c + l] = d * sc[:, 8 * n + l // 16 + 2 * c] * (q - 32)
+    assert np.array_equal(out.reshape(48, 256).view(np.uint32), ref.view(np.uint32))
+
+
 def test_q6k_dequantize_formula():
     # kernels/q6k.metal:47-77 restated independently in numpy
     rng = np.random.default_rng(3)
