@@ -57,6 +57,27 @@ def main(ref_root):
     np.savez_compressed(os.path.join(HERE, "q6k_golden.npz"), blocks=blocks6, qs=qs6, scales=scales6,
                         dm=dm6.view(np.uint16))
 
+    # 2c. the FR-Spec id file as the reference's own tool writes it (tools/merge_frspec.py write_ids: the
+    # module needs a tokenizer at import, so only its two file functions and its constants are taken)
+    import ast
+    import tempfile as _tf
+    tree = ast.parse(open(os.path.join(ref_root, "tools", "merge_frspec.py")).read())
+    keep = [n for n in tree.body
+            if isinstance(n, ast.Import)
+            or (isinstance(n, ast.FunctionDef) and n.name in ("read_ids", "write_ids"))
+            or (isinstance(n, ast.Assign) and any(getattr(t, "id", "") == "VOCAB" for t in n.targets))]
+    ns = {}
+    exec(compile(ast.Module(keep, []), "merge_frspec_subset", "exec"), ns)
+    rngf = np.random.default_rng(20240609)
+    ids_in = rngf.integers(0, 248320, 300).astype(np.uint32)
+    ids_in[10:20] = ids_in[0:10]                     # duplicates, unsorted: the tool sorts and dedupes
+    with _tf.TemporaryDirectory() as td:
+        n_written = ns["write_ids"](os.path.join(td, "ids.bin"), ids_in.tolist())
+        raw = open(os.path.join(td, "ids.bin"), "rb").read()
+        assert ns["read_ids"](os.path.join(td, "ids.bin")) == sorted(set(int(i) for i in ids_in))
+    np.savez_compressed(os.path.join(HERE, "frspec_ids_golden.npz"), ids_in=ids_in, file_bytes=np.frombuffer(raw, np.uint8),
+                        n=np.int64(n_written))
+
     # 3. affine 8-bit group-64 quantise + pack
     wa = (rng.standard_normal((16, 256)) * 0.02).astype(np.float32)
     q, s, b = aq.quantize(wa, group_size=64, bits=8)

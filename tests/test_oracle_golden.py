@@ -124,6 +124,23 @@ def test_bf16_rounding_matches_reference():
     assert hp.f32_to_bf16(np.array([1.01171875], np.float32))[0] == 0x3F82
 
 
+def test_frspec_id_file_is_the_reference_tools(tmp_path):
+    """The id file the reference's tools/merge_frspec.py writes (fixture: 300 ids with duplicates, which
+    the tool sorts and dedupes): u32 count, then the ids, little endian.  The writer the GPU loader tests
+    use produces the same bytes for the same list, so `orn_frspec_load` is tested on the tool's format."""
+    g = np.load(os.path.join(G, "frspec_ids_golden.npz"))
+    want = np.unique(g["ids_in"]).astype(np.uint32)
+    raw = g["file_bytes"].tobytes()
+    assert int(g["n"]) == len(want)
+    assert np.frombuffer(raw[:4], "<u4")[0] == len(want)
+    assert np.array_equal(np.frombuffer(raw[4:], "<u4"), want)
+    cfg = hp.tiny_config(orc.Config)
+    d = hp.write_artifact(str(tmp_path / "art"), cfg, hp.tiny_model_weights(cfg, seed=1), frspec_ids=want % cfg.vocab)
+    mine = open(os.path.join(d, "ids.bin"), "rb").read()
+    assert mine[:4] == raw[:4] and len(mine) == len(raw)
+    assert np.array_equal(np.frombuffer(mine[4:], "<u4"), want % cfg.vocab)
+
+
 def test_q6k_artifact_layout_is_the_reference_split():
     """Raw 210-byte Q6_K blocks cut into artifact tensors by the reference's own tools/q4k.py split
     (fixture): ql|qh in one tensor, int8 sub-block scales, one float16 d per block.  The oracle reading
