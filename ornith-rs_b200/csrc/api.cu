@@ -128,8 +128,7 @@ int32_t orn_ctx_destroy(orn_ctx* ctx) {
 }  // extern "C"
 
 bool orn_side_stream(orn_ctx* ctx) {
-  static int one = -1;
-  if (one < 0) { const char* e = getenv("ORN_NO_SIDE_STREAM"); one = (e && e[0] == '1') ? 1 : 0; }
+  static const bool one = [] { const char* e = getenv("ORN_NO_SIDE_STREAM"); return e && e[0] == '1'; }();  // set once, thread-safe
   if (one || ctx->kt != nullptr) return false;
   if (ctx->side != nullptr) return true;
   cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;

@@ -390,8 +390,11 @@ int moe_fused(orn_model* m, const Moe& moe, const bf16_t* a, const bf16_t* b, co
 // (ORN_LONG_CONTEXT_KEYS moves the threshold, for measurements: 0 = never)
 constexpr int kLongContext = 512;
 int long_context(int keys) {
-  static int thr = -1;
-  if (thr < 0) { const char* e = getenv("ORN_LONG_CONTEXT_KEYS"); thr = e ? atoi(e) : kLongContext; if (thr <= 0) thr = 1 << 30; }
+  static const int thr = [] {  // set once, thread-safe
+    const char* e = getenv("ORN_LONG_CONTEXT_KEYS");
+    const int t = e ? atoi(e) : kLongContext;
+    return t <= 0 ? 1 << 30 : t;
+  }();
   return keys > thr ? 1 : 0;
 }
 
